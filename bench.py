@@ -1,0 +1,468 @@
+#!/usr/bin/env python
+"""Benchmark of the b200 backend: HBM GB/s against the roofline and tokens/s per op.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W]            # the CUDA backend
+    python bench.py --impl reference [--steps K] [--warmup W]      # the reference's CPU path
+    torchrun --nproc-per-node N ... bench.py --gpus N ...          # one process per GPU
+
+Headline (the JSON line's `value`): tokens/s of the fused residual-add + RMSNorm
+configuration (bf16, x and residual [16384, 8192]).  A step is one launch of the
+op over one batch.  With N GPUs every rank runs the full configuration on its
+own tokens (token-sharded data parallel, no collective on the data path), so
+the job processes N batches per step: weak scaling.
+
+The same line also carries, under `per_op`, achieved GB/s, the fraction of the
+measured HBM peak and tokens/s for all five configurations (RMSNorm fp32,
+add+RMSNorm bf16, rotary q/k bf16, SwiGLU bf16, MoE route/index/permute/unpermute).
+
+Timing: CUDA events on the launching stream (torch's current stream), warm-up
+first, a device synchronize and a barrier on both sides, max over ranks.  Every
+timed launch streams more bytes than the 126 MB L2 holds; configurations whose
+footprint is close to L2 rotate through disjoint buffer sets.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import torch
+
+REPO = Path(__file__).resolve().parent
+sys.path.insert(0, str(REPO))
+
+FALLBACK_HBM_GBS = 6650.0  # used only when MEASURED_PEAKS.json is absent
+SPEC_HBM_GBS = 8000.0
+L2_BYTES = 126 * 1024 * 1024
+
+# DRAM bytes (read + write) per launch of the dominant kernel at the headline
+# configuration, from an ncu capture; the summary it comes from is under profiles/.
+# None until a capture has been taken for the current kernel.
+NCU_TRAFFIC_BYTES: dict[str, int | None] = {"add_rms_norm": None}
+
+
+def measured_peak() -> tuple[float, str]:
+    path = REPO / "MEASURED_PEAKS.json"
+    try:
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    except (OSError, KeyError, ValueError):
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+# ------------------------------------------------------------------ clocks --
+
+class ClockSampler:
+    """nvidia-smi sampling in the background; only reads, never sets, GPU state."""
+
+    FIELDS = "timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown," \
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int) -> None:
+        self.proc = None
+        self.windows: list[tuple[float, float]] = []
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )
+        except OSError:
+            self.proc = None
+
+    def mark(self, start: float, end: float) -> None:
+        self.windows.append((start, end))
+
+    def finish(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        import datetime
+
+        clocks, max_clocks, power, reasons = [], [], [], set()
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) != 8:
+                continue
+            try:
+                stamp = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                sm, sm_max, watts = float(parts[1]), float(parts[2]), float(parts[3])
+            except ValueError:
+                continue
+            if self.windows and not any(lo <= stamp <= hi for lo, hi in self.windows):
+                continue
+            clocks.append(sm)
+            max_clocks.append(sm_max)
+            power.append(watts)
+            for name, flag in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[4:]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if not clocks:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples inside the timed windows"]}
+        return {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max(max_clocks), "power_w_max": max(power),
+                "samples": len(clocks), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------- op runners --
+
+def make_runner(workload, device):
+    """Returns (run, n_buffer_sets): `run(i)` enqueues one launch on buffer set i straight through the
+    C ABI, with outputs allocated up front, so the timed loop holds no allocation and no tensor bookkeeping."""
+    import ctypes
+
+    from popcorn_b200 import _lib
+
+    w = workload
+    lib = _lib.library()
+    footprint = sum(w.algorithmic_bytes.values())
+    nsets = max(1, min(8, -(-4 * L2_BYTES // max(footprint, 1))))
+    sets = [{k: v.to(device).clone() for k, v in w.inputs.items()} for _ in range(nsets)]
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    keep = [sets]
+
+    def bind(name, arg_sets):
+        fn = getattr(lib, name)
+
+        def run(i: int) -> None:
+            status = fn(*arg_sets[i % nsets])
+            if status != 0:
+                raise _lib.B200Error(name, status, lib.b200_status_string(status).decode(), lib.b200_last_error().decode())
+
+        run.keep = keep  # the buffers live as long as the closure
+        return run, nsets
+
+    if w.name == "rms_norm":
+        rows, cols = sets[0]["x"].shape
+        outs = [torch.empty_like(s["x"]) for s in sets]
+        keep.append(outs)
+        return bind("b200_rms_norm", [(p(s["x"]), p(sets[0]["weight"]), ctypes.c_void_p(0), p(o), rows, cols, cols, cols,
+                                       _lib.F32, w.args["eps"], stream) for s, o in zip(sets, outs)])
+    if w.name == "add_rms_norm":
+        rows, cols = sets[0]["x"].shape
+        outs = [(torch.empty_like(s["x"]), torch.empty_like(s["x"])) for s in sets]
+        keep.append(outs)
+        return bind("b200_add_rms_norm", [(p(s["x"]), p(s["residual"]), p(sets[0]["weight"]), p(o[0]), p(o[1]), rows, cols,
+                                           cols, cols, cols, cols, _lib.BF16, w.args["eps"], w.args["offset"], stream)
+                                          for s, o in zip(sets, outs)])
+    if w.name == "rotary_embedding":
+        b, sq, hq, d = sets[0]["q"].shape
+        hk = sets[0]["k"].shape[2]
+        return bind("b200_rope_qk", [(p(s["q"]), p(s["k"]), p(sets[0]["cos"]), p(sets[0]["sin"]), b, sq, hq, hk, d, d // 2,
+                                      sq * hq * d, hq * d, d, sq * hk * d, hk * d, d, _lib.BF16, _lib.F32, 0, stream) for s in sets])
+    if w.name == "swiglu":
+        rows, cols = sets[0]["gate_up"].shape[0], w.args["cols"]
+        outs = [torch.empty((rows, cols), dtype=torch.bfloat16, device=device) for _ in sets]
+        keep.append(outs)
+        return bind("b200_swiglu", [(p(s["gate_up"]), ctypes.c_void_p(s["gate_up"].data_ptr() + 2 * cols), p(o), rows, cols,
+                                     2 * cols, 2 * cols, cols, _lib.BF16, stream) for s, o in zip(sets, outs)])
+    raise ValueError(w.name)
+
+
+def time_launches(run, steps: int, warmup: int, device) -> float:
+    """Average milliseconds per call of run(i) over `steps` back-to-back calls."""
+    for i in range(warmup):
+        run(i)
+    torch.cuda.synchronize(device)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(steps):
+        run(i)
+    end.record()
+    torch.cuda.synchronize(device)
+    return start.elapsed_time(end) / steps
+
+
+def steps_for(nbytes: int, target_s: float = 0.4, lo: int = 20, hi: int = 2000) -> int:
+    return max(lo, min(hi, int(target_s / (nbytes / 6.0e12))))
+
+
+def bench_single_kernel_ops(device, peak_gbs: float, sampler: ClockSampler, which: list[str]) -> dict:
+    from popcorn_b200 import workloads
+
+    out = {}
+    for key in which:
+        w = workloads.CONFIGS[key]()
+        nbytes = sum(w.algorithmic_bytes.values())
+        run, nsets = make_runner(w, device)
+        steps = steps_for(nbytes)
+        t0 = time.time()
+        ms = time_launches(run, steps, 5, device)
+        sampler.mark(t0, time.time())
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[key] = {"ms": round(ms, 5), "gb_s": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak_gbs, 4),
+                    "frac_of_8tbs": round(gbs / SPEC_HBM_GBS, 4), "tokens_per_s": round(w.tokens / (ms * 1e-3), 1),
+                    "algorithmic_bytes": nbytes, "steps": steps, "buffer_sets": nsets}
+        del run, w
+        torch.cuda.empty_cache()
+    return out
+
+
+def bench_moe(device, peak_gbs: float, sampler: ClockSampler) -> dict:
+    """Config 5 phase by phase: route, index (3 small kernels), permute, unpermute."""
+    from popcorn_b200 import ops, workloads
+
+    w = workloads.moe_bf16()
+    x, logits = w.inputs["x"].to(device), w.inputs["router_logits"].to(device)
+    experts, top_k = w.args["experts"], w.args["top_k"]
+    idx, wts = ops.moe_route(logits, top_k)
+    counts, offsets, perm, pos = ops.moe_index(idx, experts)
+    rows, *_ = ops.moe_permute(x, idx, experts)
+
+    from popcorn_b200 import _lib
+    import ctypes
+
+    tokens, hidden = x.shape
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    y = torch.empty_like(x)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    phases = {
+        "route": lambda i: ops.moe_route(logits, top_k),
+        "index": lambda i: ops.moe_index(idx, experts),
+        # permute and unpermute alone, straight through the C ABI (moe_permute the op also rebuilds the index)
+        "permute": lambda i: _lib.call("b200_moe_permute", p(x), p(pos), p(rows), tokens, top_k, hidden, hidden, hidden, _lib.BF16, stream),
+        "unpermute": lambda i: _lib.call("b200_moe_unpermute", p(rows), p(wts), p(pos), p(y), tokens, top_k, hidden, hidden, hidden, _lib.BF16, stream),
+    }
+    out = {}
+    total_ms = 0.0
+    for name, run in phases.items():
+        nbytes = w.algorithmic_bytes[name]
+        steps = steps_for(nbytes, hi=300)
+        t0 = time.time()
+        ms = time_launches(run, steps, 3, device)
+        sampler.mark(t0, time.time())
+        total_ms += ms
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = {"ms": round(ms, 5), "gb_s": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak_gbs, 4),
+                     "frac_of_8tbs": round(gbs / SPEC_HBM_GBS, 4), "algorithmic_bytes": nbytes, "steps": steps}
+    out["tokens_per_s"] = round(w.tokens / (total_ms * 1e-3), 1)
+    out["ms"] = round(total_ms, 5)
+    return out
+
+
+# ------------------------------------------------------------ CPU baseline --
+
+def cpu_reference_fn(key: str, fraction: float):
+    """(fn, tokens): the CPU oracle bound to a token sample of configuration `key`, inputs built once."""
+    from oracle import reference_ops as oracle
+    from popcorn_b200 import workloads
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    w = workloads.CONFIGS[key](scale=fraction)
+    i = w.inputs
+    if key == "rms_norm_fp32":
+        fn = lambda: oracle.rms_norm(i["x"], i["weight"], None, w.args["eps"])  # noqa: E731
+    elif key == "add_rms_norm_bf16":
+        fn = lambda: oracle.add_rms_norm(i["x"], i["residual"], i["weight"], w.args["eps"], w.args["offset"])  # noqa: E731
+    elif key == "rotary_bf16":
+        fn = lambda: (oracle.rotary_embedding(i["q"], i["cos"], i["sin"]), oracle.rotary_embedding(i["k"], i["cos"], i["sin"]))  # noqa: E731
+    elif key == "swiglu_bf16":
+        c = w.args["cols"]
+        fn = lambda: oracle.swiglu(i["gate_up"][:, :c], i["gate_up"][:, c:])  # noqa: E731
+    else:
+        def fn():
+            idx, wts = oracle.moe_route(i["router_logits"], w.args["top_k"])
+            rows, _, _, _, pos = oracle.moe_permute(i["x"], idx, w.args["experts"])
+            return oracle.moe_unpermute(rows, wts.float(), pos)
+    return fn, w.tokens
+
+
+def cpu_reference_time(key: str, fraction: float, repeats: int = 5) -> tuple[float, int, str]:
+    """Best-of-`repeats` seconds of the CPU oracle on a token sample of configuration `key`."""
+    fn, tokens = cpu_reference_fn(key, fraction)
+    best = float("inf")
+    with torch.no_grad():
+        fn()  # warm-up
+        for _ in range(repeats):
+            t0 = time.perf_counter()
+            fn()
+            best = min(best, time.perf_counter() - t0)
+    return best, tokens, f"{tokens} tokens ({fraction:g} of the configuration), best of {repeats}"
+
+
+def run_reference_arm(args) -> None:
+    """The reference's own CPU implementation of the headline path (the oracle port), all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    fraction = 1 / 4
+    fn, tokens = cpu_reference_fn("add_rms_norm_bf16", fraction)
+    with torch.no_grad():
+        for _ in range(max(args.warmup, 0)):
+            fn()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            fn()
+        seconds = time.perf_counter() - t0
+    ms = seconds * 1e3 / args.steps
+    value = tokens / (ms * 1e-3)
+    cores = os.cpu_count() or 1
+    line = {
+        "impl": "reference", "metric": "tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": 0,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "add_rms_norm bf16 x,residual [16384, 8192], weight [8192], eps 1e-5 (BASELINE config 2)"},
+        "cpu_baseline": {"value": round(value, 1), "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": f"each step = {tokens} tokens ({fraction:g} of the configuration); "
+                                   "PyTorch CPU restatement of popcorn's add_rms_norm reference, all host threads"},
+        "e2e": {"value": round(value, 1), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# -------------------------------------------------------------------- main --
+
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__.splitlines()[0])
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--warmup", type=int, default=10)
+    parser.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    parser.add_argument("--skip-per-op", action="store_true", help="only the headline loop (used for profiling captures)")
+    parser.add_argument("--scale", type=float, default=1.0, help="shrink the headline token count (profiling captures only)")
+    args = parser.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the b200 backend has no CPU path")
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+
+    from popcorn_b200 import _lib, build, ops, workloads
+
+    build.build()
+    peak_gbs, peak_kind = measured_peak()
+    sampler = ClockSampler(local) if rank == 0 else None
+
+    # ---- headline: add_rms_norm bf16, device-resident inputs, exactly K timed steps
+    w = workloads.add_rms_norm_bf16(scale=args.scale)
+    nbytes = w.algorithmic_bytes["add_rms_norm"]
+    run, nsets = make_runner(w, device)
+    for i in range(args.warmup):
+        run(i)
+    torch.cuda.synchronize(device)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    launches_before = _lib.launch_count()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    wall0 = time.time()
+    start.record()
+    for i in range(args.steps):
+        run(i)
+    end.record()
+    torch.cuda.synchronize(device)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    wall1 = time.time()
+    launches = _lib.launch_count() - launches_before
+    elapsed_ms = torch.tensor([start.elapsed_time(end)], device=device, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(elapsed_ms, op=dist.ReduceOp.MAX)
+    elapsed_ms = float(elapsed_ms.item())
+    ms_per_step = elapsed_ms / args.steps
+    value = world * w.tokens / (ms_per_step * 1e-3)
+    achieved = nbytes / (ms_per_step * 1e-3) / 1e9
+    if sampler is not None:
+        sampler.mark(wall0, wall1)
+
+    # ---- end to end: pinned host buffers in, both results back out, through the public op
+    host_in = {k: w.inputs[k].pin_memory() for k in ("x", "residual")}
+    weight_dev = w.inputs["weight"].to(device)
+    host_out = [torch.empty_like(w.inputs["x"]).pin_memory() for _ in range(2)]
+    h2d = sum(t.numel() * t.element_size() for t in host_in.values())
+    d2h = sum(t.numel() * t.element_size() for t in host_out)
+
+    def e2e_step() -> None:
+        xd = host_in["x"].to(device, non_blocking=True)
+        rd = host_in["residual"].to(device, non_blocking=True)
+        y, s = ops.add_rms_norm(xd, rd, weight_dev, w.args["eps"], w.args["offset"])
+        host_out[0].copy_(y, non_blocking=True)
+        host_out[1].copy_(s, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    torch.cuda.synchronize(device)
+    if dist is not None:
+        dist.barrier()
+    t0 = time.time()
+    start.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    end.record()
+    torch.cuda.synchronize(device)
+    e2e_ms = torch.tensor([start.elapsed_time(end) / e2e_steps], device=device, dtype=torch.float64)
+    if dist is not None:
+        dist.barrier()
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    if sampler is not None:
+        sampler.mark(t0, time.time())
+    e2e_value = world * w.tokens / (float(e2e_ms.item()) * 1e-3)
+    del host_in, host_out, run
+    torch.cuda.empty_cache()
+
+    # ---- the other configurations, per op (rank 0 reports its own GPU)
+    per_op = {}
+    if not args.skip_per_op and rank == 0:
+        per_op = bench_single_kernel_ops(device, peak_gbs, sampler, ["rms_norm_fp32", "add_rms_norm_bf16", "rotary_bf16", "swiglu_bf16"])
+        per_op["moe_bf16"] = bench_moe(device, peak_gbs, sampler)
+    if dist is not None:
+        dist.barrier()
+
+    if rank == 0:
+        clocks = sampler.finish()
+        cpu = None
+        if world == 1 and not args.skip_per_op:
+            seconds, cpu_tokens, note = cpu_reference_time("add_rms_norm_bf16", 1.0)
+            cpu = {"value": round(cpu_tokens / seconds, 1), "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
+                   "sample": note + "; PyTorch CPU restatement of popcorn's add_rms_norm reference, all host threads"}
+        traffic = NCU_TRAFFIC_BYTES["add_rms_norm"]
+        line = {
+            "metric": "tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {
+                "workload": f"add_rms_norm bf16 x,residual [{w.tokens}, 8192], weight [8192], eps 1e-5 (BASELINE config 2), per GPU",
+                "sharding": "tokens, one full batch per GPU, no collective", "l2": "inputs_larger_than_L2 (1 GiB streamed per launch)",
+                "timing": "CUDA events on the launching stream, max over ranks",
+            },
+            "roofline": {"bound": "hbm", "kernel": "rms_rows_kernel<bf16,256,4,add>", "achieved": round(achieved, 1), "peak": peak_gbs,
+                         "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": round(achieved / peak_gbs, 4),
+                         "frac_of_8tbs": round(achieved / SPEC_HBM_GBS, 4), "algorithmic_bytes_per_launch": nbytes,
+                         "traffic": None if traffic is None else int(traffic * args.scale)},
+            "cpu_baseline": cpu,
+            "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "per_op": per_op,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,222 @@
+/*
+ * popcorn_b200.h — C ABI of libpopcorn_b200.so
+ *
+ * A single CUDA (sm_100a) backend for the memory-bound transformer-layer ops of
+ * tilde-research/popcorn: RMSNorm, residual-add + RMSNorm, rotary embedding,
+ * SwiGLU forward, and MoE routing / permute / unpermute.
+ *
+ * Conventions shared by every entry point
+ *   - all pointers are DEVICE pointers on the current device unless a comment
+ *     says "host"; the library never allocates, frees, synchronises or throws;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default
+ *     stream); work is enqueued on it and the call returns at once;
+ *   - leading dimensions / strides are in ELEMENTS of the tensor's dtype, the
+ *     innermost dimension is always contiguous;
+ *   - the return value is a b200_status; b200_last_error() gives a
+ *     human-readable reason for the calling thread's last non-zero status;
+ *   - zero-sized problems (rows == 0, tokens == 0 ...) return B200_OK and
+ *     launch nothing.
+ *
+ * The reference has no C interface for these ops: its one first-party CUDA
+ * kernel is bound with pybind11 + ATen (src/popcorn/impls/swiglu.cu:132-135,
+ * loaded by src/popcorn/impls/_cuda.py:17-23).  Each function below names the
+ * reference Python callable whose arithmetic it reproduces.
+ */
+#ifndef POPCORN_B200_H_
+#define POPCORN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_ABI_VERSION 1
+
+typedef enum b200_dtype {
+  B200_F32 = 0,
+  B200_F16 = 1,
+  B200_BF16 = 2
+} b200_dtype;
+
+typedef enum b200_status {
+  B200_OK = 0,
+  B200_ERR_NULL_POINTER = 1,  /* a required pointer is NULL */
+  B200_ERR_DTYPE = 2,         /* dtype enum not supported by this entry point */
+  B200_ERR_SHAPE = 3,         /* negative size, stride smaller than extent, size over a stated limit */
+  B200_ERR_ALIGNMENT = 4,     /* pointer not aligned to its element size */
+  B200_ERR_LAUNCH = 5,        /* cudaGetLastError() after the launch was not cudaSuccess */
+  B200_ERR_SCRATCH = 6,       /* scratch buffer too small or misaligned */
+  B200_ERR_DEVICE = 7         /* current device is not compute capability 10.x */
+} b200_status;
+
+/* ABI version of the loaded library (== B200_ABI_VERSION it was built with). */
+int b200_version(void);
+
+/* Static name of a status code. Host pointer, never NULL. */
+const char* b200_status_string(int status);
+
+/* Detail text for the calling thread's most recent failure. Host pointer, never NULL. */
+const char* b200_last_error(void);
+
+/* Number of kernels this library has launched in the calling process (all threads). */
+uint64_t b200_launch_count(void);
+
+/*
+ * y = round_T(x * rsqrt(mean(x^2) + eps)) * weight (+ bias)
+ *
+ * Replaces rms_norm(x, weight, bias=None, eps=1e-6), src/popcorn/kernels/rms_norm.py:16-30,
+ * with rms() from src/popcorn/kernels/_utils.py:14-16.  For 16-bit dtypes the
+ * normalised value is rounded to T before the weight multiply and the product
+ * is rounded again (and once more after the bias add), as the reference's
+ * tensor-by-tensor evaluation does.  The row sum of squares is accumulated in
+ * fp32.  x, y: [rows, cols]; weight, bias: [cols] of the same dtype; bias may
+ * be NULL; y may alias x.
+ */
+int b200_rms_norm(const void* x, const void* weight, const void* bias, void* y,
+                  int64_t rows, int64_t cols, int64_t ldx, int64_t ldy,
+                  int dtype, double eps, void* stream);
+
+/*
+ * s = round_T(x + residual);  y = round_T(round_T(s * rsqrt(mean(s^2) + eps)) * round_T(weight + offset))
+ *
+ * Replaces add_rms_norm(x, residual, weight, eps=1e-6, offset=0.0),
+ * src/popcorn/kernels/add_rms_norm.py:8-23.  Both outputs are written:
+ * y (normalised) and s (the new residual stream).  s may alias x or residual,
+ * y may alias the other one.
+ */
+int b200_add_rms_norm(const void* x, const void* residual, const void* weight,
+                      void* y, void* s,
+                      int64_t rows, int64_t cols,
+                      int64_t ldx, int64_t ldr, int64_t ldy, int64_t lds,
+                      int dtype, double eps, double offset, void* stream);
+
+/*
+ * Rotary position embedding over x[batch, seq, heads, head_dim]:
+ *   interleaved == 0 (GPT-NeoX halves): (x[j], x[half + j]) rotated by angle (seq, j)
+ *   interleaved != 0 (GPT-J pairs):     (x[2j], x[2j + 1])
+ *   y1 = x1*cos - x2*sin, y2 = x1*sin + x2*cos, every product and sum rounded to
+ *   fp32 separately (no fused multiply-add), one rounding to T at the end;
+ *   channels >= 2*half are copied through.
+ *
+ * Replaces rotary_embedding(x, cos, sin, interleaved=False),
+ * src/popcorn/kernels/rotary_embedding.py:12-40.  cos, sin: [seq, half]
+ * contiguous, dtype cs_dtype (fp32 or the same 16-bit type as x).  out may
+ * equal x (in place); otherwise the two must not overlap.  Strides are those of
+ * the batch, seq and heads dimensions, so q and k may be views into one fused
+ * qkv buffer.
+ */
+int b200_rope(const void* x, const void* cos, const void* sin, void* out,
+              int64_t batch, int64_t seq, int64_t heads, int64_t head_dim, int64_t half,
+              int64_t x_stride_b, int64_t x_stride_s, int64_t x_stride_h,
+              int64_t o_stride_b, int64_t o_stride_s, int64_t o_stride_h,
+              int dtype, int cs_dtype, int interleaved, void* stream);
+
+/*
+ * The same rotation applied to q[batch, seq, q_heads, head_dim] and
+ * k[batch, seq, k_heads, head_dim] in ONE launch, in place, so that the
+ * cos/sin row of a position is fetched once for both.  Equivalent to two
+ * b200_rope calls with out == x (the reference calls rotary_embedding once per
+ * tensor, src/popcorn/kernels/rotary_embedding.py:12-40).
+ */
+int b200_rope_qk(void* q, void* k, const void* cos, const void* sin,
+                 int64_t batch, int64_t seq, int64_t q_heads, int64_t k_heads,
+                 int64_t head_dim, int64_t half,
+                 int64_t q_stride_b, int64_t q_stride_s, int64_t q_stride_h,
+                 int64_t k_stride_b, int64_t k_stride_s, int64_t k_stride_h,
+                 int dtype, int cs_dtype, int interleaved, void* stream);
+
+/*
+ * out = round_T(round_T(silu(a)) * b),  silu(a) = a / (1 + exp(-a)) in fp32
+ *
+ * Replaces swiglu(a, b) = F.silu(a) * b, src/popcorn/kernels/swiglu.py:9-18
+ * (the incumbent CUDA kernel is src/popcorn/impls/swiglu.cu:25-41, 77-101).
+ * a, b, out: [rows, cols] with independent leading dimensions, so the gate and
+ * up halves of one [rows, 2*cols] buffer are passed without a copy.
+ */
+int b200_swiglu(const void* a, const void* b, void* out,
+                int64_t rows, int64_t cols, int64_t lda, int64_t ldb, int64_t ldo,
+                int dtype, void* stream);
+
+/*
+ * MoE routing: probs = softmax(fp32(logits)) over experts; the top_k largest
+ * (descending, ties to the lower expert index); weights = picked / sum(picked).
+ *
+ * Replaces the routing lines of momoe, src/popcorn/kernels/momoe.py:47-49
+ * (same arithmetic in src/popcorn/impls/momoe_tl.py:1277-1279).
+ * logits: [tokens, experts] (ld_logits elements per row); indices: int32
+ * [tokens, top_k]; weights: fp32 [tokens, top_k].  Limits: experts <= 1024,
+ * top_k <= min(experts, 32).
+ */
+int b200_moe_route(const void* logits, int32_t* indices, float* weights,
+                   int64_t tokens, int64_t experts, int64_t top_k, int64_t ld_logits,
+                   int logits_dtype, void* stream);
+
+/*
+ * Bytes of device scratch b200_moe_index needs for this problem size
+ * (written to *bytes, a host pointer).
+ */
+int b200_moe_index_scratch_bytes(int64_t tokens, int64_t top_k, int64_t experts, size_t* bytes);
+
+/*
+ * Expert histogram, exclusive scan and the stable permutation index.
+ *   counts[e]   = number of (token, slot) pairs routed to expert e
+ *   offsets[e]  = sum of counts[0..e), offsets[experts] = tokens*top_k
+ *   perm_token[p] = token id of the pair at sorted position p; pairs are sorted
+ *                 by (expert, token), i.e. a stable sort of the flattened
+ *                 indices by expert
+ *   pos[t, k]   = sorted position of pair (t, k)  (inverse map)
+ *
+ * Replaces find_used_experts + scatter_cols_kernel,
+ * src/popcorn/impls/momoe_tl.py:1071-1161 (counts :1135, prefix :1094-1101,
+ * col_idx :1104-1112).  The reference does not materialise `pos`.
+ * indices must lie in [0, experts) (the output of b200_moe_route does); a pair
+ * with an out-of-range expert is left out of counts, perm_token and pos.  Limits:
+ * experts <= 1024, tokens*top_k < 2^31.  `scratch` needs
+ * b200_moe_index_scratch_bytes() bytes, 16-byte aligned; its contents are
+ * overwritten.
+ */
+int b200_moe_index(const int32_t* indices, int64_t tokens, int64_t top_k, int64_t experts,
+                   int32_t* counts, int32_t* offsets, int32_t* perm_token, int32_t* pos,
+                   void* scratch, size_t scratch_bytes, void* stream);
+
+/*
+ * Permute (scatter form): rows[pos[t, k], :] = x[t, :] for every slot k.
+ * Each token row is read once and written top_k times.
+ *
+ * Replaces the row gather of src/popcorn/impls/momoe_tl.py:156-158 (fused into
+ * lin1_kernel) and making_nice_scatter_kernel :408-476.
+ */
+int b200_moe_permute(const void* x, const int32_t* pos, void* rows,
+                     int64_t tokens, int64_t top_k, int64_t hidden,
+                     int64_t ldx, int64_t ldrows, int dtype, void* stream);
+
+/*
+ * Gather form: out[p, :] = x[src_row[p], :] for p in [0, n_rows).
+ * Used on the receiving side of the expert-parallel exchange and wherever only
+ * perm_token is at hand.  Same reference lines as b200_moe_permute.
+ */
+int b200_moe_gather(const void* x, const int32_t* src_row, void* out,
+                    int64_t n_rows, int64_t hidden, int64_t ldx, int64_t ldo,
+                    int dtype, void* stream);
+
+/*
+ * Weighted unpermute-combine:
+ *   y[t, :] = round_T( sum_k weights[t, k] * fp32(rows[pos[t, k], :]) )
+ * accumulated in fp32 in ascending pos order (= ascending expert index), each
+ * product and each sum rounded separately, one rounding to T at the end.
+ *
+ * Replaces the gate-weighted sum of src/popcorn/kernels/momoe.py:52-53
+ * (einsum "bsed,bse->bsd" in fp32, then one cast); the Triton path does it in
+ * lin2_kernel, src/popcorn/impls/momoe_tl.py:295-304 and :398.
+ */
+int b200_moe_unpermute(const void* rows, const float* weights, const int32_t* pos, void* y,
+                       int64_t tokens, int64_t top_k, int64_t hidden,
+                       int64_t ldrows, int64_t ldy, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* POPCORN_B200_H_ */

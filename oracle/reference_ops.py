@@ -1,0 +1,174 @@
+"""CPU restatement of popcorn's PyTorch references for the b200 backend's ops.
+
+TEST INFRASTRUCTURE ONLY.  This module is the checker the CUDA kernels are
+compared against (tests/, the smoke entry point, and bench.py's CPU-baseline and
+reference arms).  Nothing under popcorn_b200/ imports it and it is never the
+thing that is shipped or measured as the product.
+
+Parity status
+  * rms_norm, add_rms_norm, rotary_embedding, swiglu, and the routing lines of
+    momoe restate registered popcorn references; they are pinned by the golden
+    vectors in tests/golden/, which were produced by running the real reference
+    (popcorn 0.1.1 imported from its source tree; see tests/golden/make_golden.py).
+  * moe_index / moe_permute / moe_unpermute have NO standalone counterpart in
+    the reference (the steps exist only fused inside the Triton `momoe`
+    implementation), and the reference holds no test that pins their indices:
+    for those three the index-level parity is unpinned.  What is pinned is the
+    end-to-end chain: route -> permute -> per-expert MLP -> unpermute built from
+    these functions reproduces the registered `momoe` reference output on the
+    golden cases (tests/test_oracle_golden.py).
+
+Every function runs on CPU tensors with plain torch ops, in the same order of
+operations (and therefore the same intermediate roundings) as the reference.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor
+
+
+def _to_fp32_or_wider(t: Tensor) -> Tensor:
+    """Reference: upcast(), src/popcorn/kernels/_utils.py:6-7."""
+    return t.to(torch.promote_types(t.dtype, torch.float32))
+
+
+def _unit_rms(t: Tensor, eps: float) -> Tensor:
+    """Reference: rms(), src/popcorn/kernels/_utils.py:14-16 (result cast back to t.dtype)."""
+    wide = _to_fp32_or_wider(t)
+    mean_sq = wide.square().mean(dim=-1, keepdim=True)
+    return (wide * torch.rsqrt(mean_sq + eps)).to(t.dtype)
+
+
+def rms_norm(x: Tensor, weight: Tensor, bias: Tensor | None = None, eps: float = 1e-6) -> Tensor:
+    """Reference: rms_norm, src/popcorn/kernels/rms_norm.py:16-30."""
+    y = _unit_rms(x, eps) * weight
+    if bias is not None:
+        y = y + bias
+    return y
+
+
+def add_rms_norm(x: Tensor, residual: Tensor, weight: Tensor, eps: float = 1e-6, offset: float = 0.0) -> tuple[Tensor, Tensor]:
+    """Reference: add_rms_norm, src/popcorn/kernels/add_rms_norm.py:8-23."""
+    stream = x + residual
+    return _unit_rms(stream, eps) * (weight + offset), stream
+
+
+def rotary_embedding(x: Tensor, cos: Tensor, sin: Tensor, interleaved: bool = False) -> Tensor:
+    """Reference: rotary_embedding, src/popcorn/kernels/rotary_embedding.py:15-40."""
+    half = cos.shape[-1]
+    c = _to_fp32_or_wider(cos)[None, :, None, :]
+    s = _to_fp32_or_wider(sin)[None, :, None, :]
+    if interleaved:
+        first = _to_fp32_or_wider(x[..., 0 : 2 * half : 2])
+        second = _to_fp32_or_wider(x[..., 1 : 2 * half : 2])
+        turned = torch.stack((first * c - second * s, first * s + second * c), dim=-1).flatten(-2)
+    else:
+        first = _to_fp32_or_wider(x[..., :half])
+        second = _to_fp32_or_wider(x[..., half : 2 * half])
+        turned = torch.cat((first * c - second * s, first * s + second * c), dim=-1)
+    turned = turned.to(x.dtype)
+    if 2 * half == x.shape[-1]:
+        return turned
+    return torch.cat((turned, x[..., 2 * half :]), dim=-1)
+
+
+def swiglu(a: Tensor, b: Tensor) -> Tensor:
+    """Reference: swiglu, src/popcorn/kernels/swiglu.py:10-18."""
+    return F.silu(a) * b
+
+
+def moe_route(router_logits: Tensor, top_k: int) -> tuple[Tensor, Tensor]:
+    """Reference: routing lines of momoe, src/popcorn/kernels/momoe.py:47-49.
+
+    Returns (indices int32 [..., top_k], weights float32-or-wider [..., top_k]); indices are
+    in torch.topk order (descending probability)."""
+    probs = torch.softmax(_to_fp32_or_wider(router_logits), dim=-1)
+    picked = probs.topk(top_k, dim=-1)
+    weights = picked.values / picked.values.sum(dim=-1, keepdim=True)
+    return picked.indices.to(torch.int32), weights
+
+
+def route_is_unambiguous(router_logits: Tensor, top_k: int) -> bool:
+    """True when no row has equal probabilities among its top_k + 1 largest.
+
+    torch.topk does not define an order among equal values, so index parity can
+    only be demanded of inputs for which this holds."""
+    probs = torch.softmax(_to_fp32_or_wider(router_logits), dim=-1)
+    width = min(top_k + 1, probs.shape[-1])
+    head = probs.topk(width, dim=-1).values
+    return bool((head[..., :-1] != head[..., 1:]).all()) if width > 1 else True
+
+
+def moe_index(indices: Tensor, experts: int) -> tuple[Tensor, Tensor, Tensor, Tensor]:
+    """Restates find_used_experts / scatter_cols_kernel, src/popcorn/impls/momoe_tl.py:1071-1161.
+
+    counts  = pairs per expert                     (:1135  counts = mask.sum(1))
+    offsets = exclusive prefix, total at the end   (:1085-1101)
+    perm    = token ids, ascending inside each expert, experts in order (:1104-1112 col_idx)
+    pos     = inverse map [tokens, top_k] (not materialised by the reference)
+    All int32."""
+    tokens, top_k = indices.shape
+    flat = indices.reshape(-1).to(torch.int64)
+    counts = torch.bincount(flat, minlength=experts)[:experts]
+    offsets = torch.zeros(experts + 1, dtype=torch.int64)
+    offsets[1:] = torch.cumsum(counts, 0)
+    order = torch.sort(flat, stable=True).indices  # flat pair id at each sorted position
+    perm = torch.div(order, top_k, rounding_mode="floor")
+    pos = torch.empty(tokens * top_k, dtype=torch.int64)
+    pos[order] = torch.arange(tokens * top_k, dtype=torch.int64)
+    return counts.to(torch.int32), offsets.to(torch.int32), perm.to(torch.int32), pos.view(tokens, top_k).to(torch.int32)
+
+
+def moe_permute(x: Tensor, indices: Tensor, experts: int) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
+    """Row gather of src/popcorn/impls/momoe_tl.py:156-158 / :408-476: rows[p] = x[perm[p]]."""
+    counts, offsets, perm, pos = moe_index(indices, experts)
+    rows = x.index_select(0, perm.to(torch.int64))
+    return rows, counts, offsets, perm, pos
+
+
+def moe_gather(x: Tensor, src_rows: Tensor) -> Tensor:
+    return x.index_select(0, src_rows.to(torch.int64))
+
+
+def moe_unpermute(rows: Tensor, weights: Tensor, pos: Tensor) -> Tensor:
+    """Gate-weighted sum back to token order, src/popcorn/kernels/momoe.py:52-53.
+
+    The reference contracts the expert axis with an fp32 einsum and casts once.
+    The summation order of an einsum is not specified; this restatement fixes it
+    to ascending expert index (= ascending pos), one rounded fp32 product and one
+    rounded fp32 add per term, starting from +0."""
+    tokens, top_k = pos.shape
+    order = torch.argsort(pos.to(torch.int64), dim=1)
+    pos_sorted = torch.gather(pos.to(torch.int64), 1, order)
+    w_sorted = torch.gather(weights.to(torch.float32), 1, order)
+    acc = torch.zeros((tokens, rows.shape[1]), dtype=torch.float32)
+    for k in range(top_k):
+        term = rows.index_select(0, pos_sorted[:, k]).to(torch.float32) * w_sorted[:, k : k + 1]
+        acc = acc + term
+    return acc.to(rows.dtype)
+
+
+def momoe_from_steps(x: Tensor, gate_weight: Tensor, up_weight: Tensor, down_weight: Tensor, router_logits: Tensor, top_k: int) -> Tensor:
+    """The registered `momoe` op (src/popcorn/kernels/momoe.py:34-53) rebuilt from the steps above.
+
+    Used only to pin route / permute / unpermute end to end against the reference's output:
+    tokens are routed, permuted into expert-contiguous rows, each expert's slice goes through
+    its SwiGLU MLP in fp32, and the results are combined by moe_unpermute."""
+    lead = x.shape[:-1]
+    hidden = x.shape[-1]
+    experts = gate_weight.shape[0]
+    flat = _to_fp32_or_wider(x).reshape(-1, hidden)
+    indices, weights = moe_route(router_logits.reshape(-1, experts), top_k)
+    rows, counts, offsets, _, pos = moe_permute(flat, indices, experts)
+    out_rows = torch.empty_like(rows)
+    for e in range(experts):
+        lo, hi = int(offsets[e]), int(offsets[e + 1])
+        if hi == lo:
+            continue
+        chunk = rows[lo:hi]
+        hidden_act = (chunk @ _to_fp32_or_wider(up_weight[e])) * F.silu(chunk @ _to_fp32_or_wider(gate_weight[e]))
+        out_rows[lo:hi] = hidden_act @ _to_fp32_or_wider(down_weight[e])
+    y = moe_unpermute(out_rows, weights.to(torch.float32), pos)
+    return y.reshape(*lead, hidden).to(x.dtype)

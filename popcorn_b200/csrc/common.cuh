@@ -1,0 +1,159 @@
+// Shared device/host helpers for the sm_100a kernels of libpopcorn_b200.
+//
+// Numeric rule used throughout: a value is rounded to the storage type T at
+// every point where the PyTorch reference materialises a tensor of that type,
+// and every fp32 product / sum is rounded on its own (explicit *_rn intrinsics,
+// which the compiler never contracts into a fused multiply-add).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/popcorn_b200.h"
+
+namespace b200 {
+
+// ---------------------------------------------------------------- host side --
+
+// Records a failure reason for the calling thread and returns `status`.
+int fail(int status, const char* fmt, ...);
+// cudaGetLastError() -> status, counting the launch when it succeeded.
+int after_launch(const char* kernel);
+// B200_OK when the current device is compute capability 10.x.
+int check_device();
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+inline size_t dtype_size(int dtype) { return dtype == B200_F32 ? 4 : 2; }
+inline bool dtype_ok(int dtype) { return dtype == B200_F32 || dtype == B200_F16 || dtype == B200_BF16; }
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+#define B200_REQUIRE_PTR(p)                                                        \
+  do {                                                                             \
+    if ((p) == nullptr) return ::b200::fail(B200_ERR_NULL_POINTER, "%s: %s is NULL", __func__, #p); \
+  } while (0)
+
+// -------------------------------------------------------------- device side --
+
+constexpr int kVecBytes = 16;  // every fast path moves 128-bit words
+
+template <typename T>
+struct Num;
+
+template <>
+struct Num<float> {
+  static constexpr int kVec = 4;
+  static __device__ __forceinline__ float up(float v) { return v; }
+  static __device__ __forceinline__ float down(float v) { return v; }
+  // round-trip through the storage type: identity for fp32
+  static __device__ __forceinline__ float rt(float v) { return v; }
+  static __device__ __forceinline__ void unpack(const uint4& v, float (&f)[4]) {
+    f[0] = __uint_as_float(v.x);
+    f[1] = __uint_as_float(v.y);
+    f[2] = __uint_as_float(v.z);
+    f[3] = __uint_as_float(v.w);
+  }
+  static __device__ __forceinline__ uint4 pack(const float (&f)[4]) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+  }
+};
+
+template <>
+struct Num<__nv_bfloat16> {
+  static constexpr int kVec = 8;
+  static __device__ __forceinline__ float up(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 down(float v) { return __float2bfloat16_rn(v); }
+  static __device__ __forceinline__ float rt(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+  // bf16 -> fp32 is a 16-bit shift of the bit pattern
+  static __device__ __forceinline__ void unpack2(uint32_t w, float& lo, float& hi) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xffff0000u);
+  }
+  static __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&p);
+  }
+  static __device__ __forceinline__ void unpack(const uint4& v, float (&f)[8]) {
+    unpack2(v.x, f[0], f[1]);
+    unpack2(v.y, f[2], f[3]);
+    unpack2(v.z, f[4], f[5]);
+    unpack2(v.w, f[6], f[7]);
+  }
+  static __device__ __forceinline__ uint4 pack(const float (&f)[8]) {
+    return make_uint4(pack2(f[0], f[1]), pack2(f[2], f[3]), pack2(f[4], f[5]), pack2(f[6], f[7]));
+  }
+};
+
+template <>
+struct Num<__half> {
+  static constexpr int kVec = 8;
+  static __device__ __forceinline__ float up(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half down(float v) { return __float2half_rn(v); }
+  static __device__ __forceinline__ float rt(float v) { return __half2float(__float2half_rn(v)); }
+  static __device__ __forceinline__ void unpack2(uint32_t w, float& lo, float& hi) {
+    float2 f = __half22float2(*reinterpret_cast<__half2*>(&w));
+    lo = f.x;
+    hi = f.y;
+  }
+  static __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __half2 p = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&p);
+  }
+  static __device__ __forceinline__ void unpack(const uint4& v, float (&f)[8]) {
+    unpack2(v.x, f[0], f[1]);
+    unpack2(v.y, f[2], f[3]);
+    unpack2(v.z, f[4], f[5]);
+    unpack2(v.w, f[6], f[7]);
+  }
+  static __device__ __forceinline__ uint4 pack(const float (&f)[8]) {
+    return make_uint4(pack2(f[0], f[1]), pack2(f[2], f[3]), pack2(f[4], f[5]), pack2(f[6], f[7]));
+  }
+};
+
+// 128-bit global accesses. Inputs are read once: bypass L1 allocation (a
+// coherent load, not .nc, because several entry points allow out == in).
+// Outputs are written once: streaming store.
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+// Plain (cacheable) 128-bit load for data another thread of this kernel may have written.
+__device__ __forceinline__ uint4 ld_plain(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+// Read-only 128-bit load that may stay in L1 (weights, cos/sin rows: reused by many warps).
+__device__ __forceinline__ uint4 ld_reuse(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ void st_stream(void* p, const uint4& v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Dispatch a runtime dtype enum to a template parameter.
+#define B200_DISPATCH_DTYPE(dtype, T, ...)              \
+  do {                                                  \
+    switch (dtype) {                                    \
+      case B200_F32: {                                  \
+        using T = float;                                \
+        __VA_ARGS__;                                    \
+      } break;                                          \
+      case B200_F16: {                                  \
+        using T = __half;                               \
+        __VA_ARGS__;                                    \
+      } break;                                          \
+      default: {                                        \
+        using T = __nv_bfloat16;                        \
+        __VA_ARGS__;                                    \
+      } break;                                          \
+    }                                                   \
+  } while (0)
+
+}  // namespace b200

@@ -1,0 +1,604 @@
+// MoE token routing, permutation index, permute and weighted unpermute for sm_100a.
+//
+//   route      softmax over experts, top-k, renormalise        (momoe.py:47-49)
+//   index      expert histogram, scan, stable permutation      (momoe_tl.py:1071-1161)
+//   permute    rows[pos[t,k]] = x[t]    (one read, top_k writes per token row)
+//   gather     out[p] = x[src[p]]
+//   unpermute  y[t] = sum_k w[t,k] * rows[pos[t,k]], fp32, ascending expert order (momoe.py:52-53)
+//
+// Bound: HBM for permute / gather / unpermute (pure row traffic, 128-bit
+// accesses, a warp moves 512 contiguous bytes per step); route and index move
+// only a few MB and are latency-bound.
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kMaxExperts = 1024;
+constexpr int kMaxTopK = 32;
+constexpr unsigned kFull = 0xffffffffu;
+
+// ------------------------------------------------------------------ route --
+
+template <typename L>
+__device__ __forceinline__ float logit_to_float(const L* p, int64_t i);
+template <>
+__device__ __forceinline__ float logit_to_float<float>(const float* p, int64_t i) { return __ldg(p + i); }
+template <>
+__device__ __forceinline__ float logit_to_float<__half>(const __half* p, int64_t i) { return __half2float(p[i]); }
+template <>
+__device__ __forceinline__ float logit_to_float<__nv_bfloat16>(const __nv_bfloat16* p, int64_t i) { return __bfloat162float(p[i]); }
+
+// One warp per token; lane l holds experts l, l + 32, ... (NPL of them).
+// Selection runs on the logits (exp and the shared denominator are monotone, so
+// the order is that of the probabilities) with ties going to the lower index.
+template <typename L, int NPL>
+__global__ void __launch_bounds__(256)
+route_kernel(const L* __restrict__ logits, int32_t* __restrict__ indices, float* __restrict__ weights,
+             int64_t tokens, int experts, int top_k, int64_t ld) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = static_cast<int64_t>(gridDim.x) * 8;
+  for (int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); t < tokens; t += warps) {
+    float v[NPL];
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int e = lane + 32 * i;
+      v[i] = e < experts ? logit_to_float<L>(logits, t * ld + e) : -INFINITY;
+      m = fmaxf(m, v[i]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(kFull, m, o));
+    float p[NPL];
+    float part = 0.f;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      p[i] = lane + 32 * i < experts ? expf(__fsub_rn(v[i], m)) : 0.f;
+      part = __fadd_rn(part, p[i]);
+    }
+    const float denom = warp_sum(part);
+
+    unsigned taken = 0;  // bit i: my i-th expert is already picked
+    float my_prob = 0.f;
+    int my_idx = 0;
+    float picked_sum = 0.f;
+    for (int k = 0; k < top_k; ++k) {
+      float best = -INFINITY;
+      int best_e = 0x7fffffff;
+      int best_i = -1;
+#pragma unroll
+      for (int i = 0; i < NPL; ++i) {
+        const int e = lane + 32 * i;
+        const bool free_slot = e < experts && !((taken >> i) & 1u);
+        // a NaN logit never wins a comparison; -inf loses to everything but ties by index
+        if (free_slot && (best_i < 0 || v[i] > best)) {
+          best = v[i];
+          best_e = e;
+          best_i = i;
+        }
+      }
+      float wv = best;
+      int we = best_e;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(kFull, wv, o);
+        const int oe = __shfl_xor_sync(kFull, we, o);
+        const bool other_wins = (oe != 0x7fffffff) && (we == 0x7fffffff || ov > wv || (ov == wv && oe < we) || (wv != wv && ov == ov));
+        if (other_wins) {
+          wv = ov;
+          we = oe;
+        }
+      }
+      // the owner of expert `we` marks it and publishes its probability
+      const bool mine = best_i >= 0 && best_e == we;
+      float prob = 0.f;
+      if (mine) {
+        taken |= 1u << best_i;
+#pragma unroll
+        for (int i = 0; i < NPL; ++i)
+          if (i == best_i) prob = __fdiv_rn(p[i], denom);
+      }
+      prob = __shfl_sync(kFull, prob, we & 31);
+      picked_sum = __fadd_rn(picked_sum, prob);
+      if (lane == k) {
+        my_prob = prob;
+        my_idx = we;
+      }
+    }
+    if (lane < top_k) {
+      indices[t * top_k + lane] = my_idx;
+      weights[t * top_k + lane] = __fdiv_rn(my_prob, picked_sum);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ index --
+
+constexpr int kIndexThreads = 256;
+constexpr int kPairsPerThread = 8;
+constexpr int kPairsPerBlock = kIndexThreads * kPairsPerThread;  // 2048 (token, slot) pairs
+
+// Step 1: per-block expert histogram -> block_hist[e * nblk + b].
+__global__ void __launch_bounds__(kIndexThreads)
+index_hist_kernel(const int32_t* __restrict__ idx, int64_t pairs, int experts, int nblk,
+                  int32_t* __restrict__ block_hist) {
+  extern __shared__ int hist[];
+  for (int e = threadIdx.x; e < experts; e += kIndexThreads) hist[e] = 0;
+  __syncthreads();
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kPairsPerBlock;
+#pragma unroll
+  for (int r = 0; r < kPairsPerThread; ++r) {
+    const int64_t i = base + r * kIndexThreads + threadIdx.x;
+    if (i < pairs) {
+      const int e = idx[i];
+      if (e >= 0 && e < experts) atomicAdd(&hist[e], 1);
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += kIndexThreads)
+    block_hist[static_cast<int64_t>(e) * nblk + blockIdx.x] = hist[e];
+}
+
+// Step 2 (one CTA): per expert, exclusive scan of its block counts in place and
+// its total; then the exclusive scan of the totals over experts.
+__global__ void __launch_bounds__(1024)
+index_scan_kernel(int32_t* __restrict__ block_hist, int experts, int nblk,
+                  int32_t* __restrict__ counts, int32_t* __restrict__ offsets) {
+  __shared__ int total[kMaxExperts];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  for (int e = warp; e < experts; e += 32) {
+    int32_t* h = block_hist + static_cast<int64_t>(e) * nblk;
+    int running = 0;
+    for (int b0 = 0; b0 < nblk; b0 += 32) {
+      const int b = b0 + lane;
+      const int c = b < nblk ? h[b] : 0;
+      int incl = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(kFull, incl, o);
+        if (lane >= o) incl += up;
+      }
+      if (b < nblk) h[b] = running + incl - c;
+      running += __shfl_sync(kFull, incl, 31);
+    }
+    if (lane == 0) total[e] = running;
+  }
+  __syncthreads();
+  // experts <= 1024: thread e owns expert e; scan 1024 slots through warp scans
+  __shared__ int warp_tot[32];
+  const int e = threadIdx.x;
+  const int c = e < experts ? total[e] : 0;
+  int incl = c;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int up = __shfl_up_sync(kFull, incl, o);
+    if (lane >= o) incl += up;
+  }
+  if (lane == 31) warp_tot[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int w = warp_tot[lane];
+    int wi = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(kFull, wi, o);
+      if (lane >= o) wi += up;
+    }
+    warp_tot[lane] = wi - w;  // exclusive
+  }
+  __syncthreads();
+  const int excl = warp_tot[warp] + incl - c;
+  if (e < experts) {
+    counts[e] = c;
+    offsets[e] = excl;
+    if (e == experts - 1) offsets[experts] = excl + c;
+  }
+}
+
+// Step 3: every pair gets offsets[e] + (pairs of e in earlier blocks) + (pairs of e
+// earlier in this block).  A warp walks its 256 consecutive pairs 32 at a time;
+// __match_any_sync ranks equal experts inside a step by lane, which is pair order.
+__global__ void __launch_bounds__(kIndexThreads)
+index_scatter_kernel(const int32_t* __restrict__ idx, int64_t pairs, int top_k, int experts, int nblk,
+                     const int32_t* __restrict__ block_hist, const int32_t* __restrict__ offsets,
+                     int32_t* __restrict__ perm_token, int32_t* __restrict__ pos) {
+  extern __shared__ int whist[];  // [8 warps][experts]
+  constexpr int kWarps = kIndexThreads / 32;
+  constexpr int kPairsPerWarp = kPairsPerBlock / kWarps;  // 256
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < kWarps * experts; i += kIndexThreads) whist[i] = 0;
+  __syncthreads();
+  const int64_t wbase = static_cast<int64_t>(blockIdx.x) * kPairsPerBlock + warp * kPairsPerWarp;
+  int my_e[kPairsPerThread];
+#pragma unroll
+  for (int r = 0; r < kPairsPerThread; ++r) {
+    const int64_t i = wbase + r * 32 + lane;
+    int e = -1;
+    if (i < pairs) {
+      e = idx[i];
+      if (e < 0 || e >= experts) e = -1;
+    }
+    my_e[r] = e;
+    if (e >= 0) atomicAdd(&whist[warp * experts + e], 1);
+  }
+  __syncthreads();
+  // exclusive prefix over the warps of this block, seeded with the global base
+  for (int e = threadIdx.x; e < experts; e += kIndexThreads) {
+    int running = offsets[e] + block_hist[static_cast<int64_t>(e) * nblk + blockIdx.x];
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const int c = whist[w * experts + e];
+      whist[w * experts + e] = running;
+      running += c;
+    }
+  }
+  __syncthreads();
+  int* cursor = whist + warp * experts;
+#pragma unroll
+  for (int r = 0; r < kPairsPerThread; ++r) {
+    const int64_t i = wbase + r * 32 + lane;
+    const int e = my_e[r];
+    const unsigned same = __match_any_sync(kFull, e);
+    const int rank = __popc(same & ((1u << lane) - 1u));
+    int dst = -1;
+    if (e >= 0) dst = cursor[e] + rank;
+    __syncwarp();
+    if (e >= 0 && rank == 0) cursor[e] += __popc(same);
+    __syncwarp();
+    if (i < pairs) {
+      pos[i] = dst;
+      if (dst >= 0) perm_token[dst] = static_cast<int32_t>(static_cast<uint32_t>(i) / static_cast<uint32_t>(top_k));
+    }
+  }
+}
+
+// ---------------------------------------------------- permute / gather --
+
+// Word types for pure row copies: the widest one every address is aligned to.
+template <typename W>
+__device__ __forceinline__ W ld_word(const W* p) { return *p; }
+template <>
+__device__ __forceinline__ uint4 ld_word<uint4>(const uint4* p) { return ld_stream(p); }
+template <typename W>
+__device__ __forceinline__ void st_word(W* p, const W& v) { *p = v; }
+template <>
+__device__ __forceinline__ void st_word<uint4>(uint4* p, const uint4& v) { st_stream(p, v); }
+
+// One warp per token: read the row once (UNROLL words per lane at a time) and
+// write it to each of its top_k destinations.
+template <typename W>
+__global__ void __launch_bounds__(256)
+permute_kernel(const W* __restrict__ x, const int32_t* __restrict__ pos, W* __restrict__ rows,
+               int64_t tokens, int top_k, int words, int64_t ldx, int64_t ldrows) {
+  constexpr int UNROLL = 4;
+  const int lane = threadIdx.x & 31;
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  const int my_dst = lane < top_k ? pos[t * top_k + lane] : -1;
+  const W* src = x + t * ldx;
+  for (int w0 = lane; w0 < words; w0 += 32 * UNROLL) {
+    W v[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+      if (w0 + 32 * u < words) v[u] = ld_word<W>(src + w0 + 32 * u);
+    for (int k = 0; k < top_k; ++k) {
+      const int dst = __shfl_sync(kFull, my_dst, k);
+      if (dst < 0) continue;
+      W* out = rows + static_cast<int64_t>(dst) * ldrows;
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u)
+        if (w0 + 32 * u < words) st_word<W>(out + w0 + 32 * u, v[u]);
+    }
+  }
+}
+
+// One warp per output row.
+template <typename W>
+__global__ void __launch_bounds__(256)
+gather_kernel(const W* __restrict__ x, const int32_t* __restrict__ src_row, W* __restrict__ out,
+              int64_t n_rows, int words, int64_t ldx, int64_t ldo) {
+  constexpr int UNROLL = 8;
+  const int lane = threadIdx.x & 31;
+  const int64_t r = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (r >= n_rows) return;
+  const int s = src_row[r];
+  if (s < 0) return;
+  const W* src = x + static_cast<int64_t>(s) * ldx;
+  W* dst = out + r * ldo;
+  for (int w0 = lane; w0 < words; w0 += 32 * UNROLL) {
+    W v[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+      if (w0 + 32 * u < words) v[u] = ld_word<W>(src + w0 + 32 * u);
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+      if (w0 + 32 * u < words) st_word<W>(dst + w0 + 32 * u, v[u]);
+  }
+}
+
+// -------------------------------------------------------------- unpermute --
+
+// One warp per token.  Lanes < top_k hold (pos, weight); the slots are visited
+// in ascending pos, which is ascending expert index.  VEC: 128-bit words.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256)
+unpermute_kernel(const T* __restrict__ rows, const float* __restrict__ weights, const int32_t* __restrict__ pos,
+                 T* __restrict__ y, int64_t tokens, int top_k, int hidden, int64_t ldrows, int64_t ldy) {
+  constexpr int V = VEC ? Num<T>::kVec : 1;
+  constexpr int KB = 8;  // slots fetched together
+  const int lane = threadIdx.x & 31;
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  int my_pos = -1;
+  float my_w = 0.f;
+  if (lane < top_k) {
+    my_pos = pos[t * top_k + lane];
+    my_w = weights[t * top_k + lane];
+  }
+  // rank of my slot among the valid ones (equal pos values keep slot order)
+  int rank = 0;
+  int valid = 0;
+  for (int j = 0; j < top_k; ++j) {
+    const int pj = __shfl_sync(kFull, my_pos, j);
+    if (pj >= 0) {
+      ++valid;
+      if (pj < my_pos || (pj == my_pos && j < lane)) ++rank;
+    }
+  }
+  if (my_pos < 0) rank = -1;
+  // ord_pos / ord_w: lane r holds the r-th slot in visiting order
+  int ord_pos = -1;
+  float ord_w = 0.f;
+  for (int r = 0; r < valid; ++r) {
+    const unsigned who = __ballot_sync(kFull, rank == r);
+    const int src = __ffs(who) - 1;
+    const int pp = __shfl_sync(kFull, my_pos, src);
+    const float ww = __shfl_sync(kFull, my_w, src);
+    if (lane == r) {
+      ord_pos = pp;
+      ord_w = ww;
+    }
+  }
+  const int words = hidden / V;
+  T* out = y + t * ldy;
+  for (int w = lane; w < words; w += 32) {
+    float acc[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc[j] = 0.f;
+    for (int k0 = 0; k0 < valid; k0 += KB) {
+      uint4 v[KB];
+      T sv[KB];
+#pragma unroll
+      for (int k = 0; k < KB; ++k) {
+        const int pp = __shfl_sync(kFull, ord_pos, (k0 + k) & 31);
+        if (k0 + k < valid) {
+          const T* src = rows + static_cast<int64_t>(pp) * ldrows + static_cast<int64_t>(w) * V;
+          if constexpr (VEC) v[k] = ld_stream(src);
+          else sv[k] = *src;
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < KB; ++k) {
+        const float ww = __shfl_sync(kFull, ord_w, (k0 + k) & 31);
+        if (k0 + k < valid) {
+          if constexpr (VEC) {
+            float f[V];
+            Num<T>::unpack(v[k], f);
+#pragma unroll
+            for (int j = 0; j < V; ++j) acc[j] = __fadd_rn(acc[j], __fmul_rn(ww, f[j]));
+          } else {
+            acc[0] = __fadd_rn(acc[0], __fmul_rn(ww, Num<T>::up(sv[k])));
+          }
+        }
+      }
+    }
+    if constexpr (VEC) {
+      st_stream(out + static_cast<int64_t>(w) * V, Num<T>::pack(acc));
+    } else {
+      out[w] = Num<T>::down(acc[0]);
+    }
+  }
+}
+
+template <typename W>
+bool rows_aligned(const void* a, const void* b, int64_t row_bytes, int64_t lda_bytes, int64_t ldb_bytes) {
+  return aligned(a, sizeof(W)) && aligned(b, sizeof(W)) && row_bytes % sizeof(W) == 0 && lda_bytes % sizeof(W) == 0 &&
+         ldb_bytes % sizeof(W) == 0;
+}
+
+int nblk_for(int64_t pairs) { return static_cast<int>(ceil_div(pairs, kPairsPerBlock)); }
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_moe_route(const void* logits, int32_t* indices, float* weights,
+                              int64_t tokens, int64_t experts, int64_t top_k, int64_t ld_logits,
+                              int logits_dtype, void* stream) {
+  if (!dtype_ok(logits_dtype)) return fail(B200_ERR_DTYPE, "%s: unsupported logits dtype %d", __func__, logits_dtype);
+  if (tokens < 0 || experts < 1 || experts > kMaxExperts)
+    return fail(B200_ERR_SHAPE, "%s: need tokens >= 0 and 1 <= experts <= %d (got %lld, %lld)", __func__, kMaxExperts, (long long)tokens, (long long)experts);
+  if (top_k < 1 || top_k > experts || top_k > kMaxTopK)
+    return fail(B200_ERR_SHAPE, "%s: need 1 <= top_k <= min(experts, %d) (got %lld)", __func__, kMaxTopK, (long long)top_k);
+  if (ld_logits < experts) return fail(B200_ERR_SHAPE, "%s: ld_logits smaller than experts", __func__);
+  if (tokens == 0) return B200_OK;
+  B200_REQUIRE_PTR(logits);
+  B200_REQUIRE_PTR(indices);
+  B200_REQUIRE_PTR(weights);
+  if (!aligned(logits, dtype_size(logits_dtype)) || !aligned(indices, 4) || !aligned(weights, 4))
+    return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to the element size", __func__);
+  if (int rc = check_device()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t want = ceil_div(tokens, 8);
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 64;
+  const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
+  const int E = static_cast<int>(experts), K = static_cast<int>(top_k);
+#define B200_ROUTE(L, NPL) \
+  route_kernel<L, NPL><<<grid, 256, 0, st>>>(static_cast<const L*>(logits), indices, weights, tokens, E, K, ld_logits)
+#define B200_ROUTE_NPL(L)                  \
+  do {                                     \
+    if (E <= 32) B200_ROUTE(L, 1);         \
+    else if (E <= 64) B200_ROUTE(L, 2);    \
+    else if (E <= 128) B200_ROUTE(L, 4);   \
+    else if (E <= 256) B200_ROUTE(L, 8);   \
+    else if (E <= 512) B200_ROUTE(L, 16);  \
+    else B200_ROUTE(L, 32);                \
+  } while (0)
+  if (logits_dtype == B200_F32) B200_ROUTE_NPL(float);
+  else if (logits_dtype == B200_F16) B200_ROUTE_NPL(__half);
+  else B200_ROUTE_NPL(__nv_bfloat16);
+#undef B200_ROUTE_NPL
+#undef B200_ROUTE
+  return after_launch("route_kernel");
+}
+
+static int index_check(const char* fn, int64_t tokens, int64_t top_k, int64_t experts) {
+  if (tokens < 0 || top_k < 1 || experts < 1 || experts > kMaxExperts)
+    return fail(B200_ERR_SHAPE, "%s: need tokens >= 0, top_k >= 1, 1 <= experts <= %d", fn, kMaxExperts);
+  if (tokens * top_k >= 0x7fffffffLL) return fail(B200_ERR_SHAPE, "%s: tokens*top_k must be below 2^31", fn);
+  return B200_OK;
+}
+
+extern "C" int b200_moe_index_scratch_bytes(int64_t tokens, int64_t top_k, int64_t experts, size_t* bytes) {
+  B200_REQUIRE_PTR(bytes);
+  if (int rc = index_check(__func__, tokens, top_k, experts)) return rc;
+  const int64_t nblk = nblk_for(tokens * top_k);
+  *bytes = static_cast<size_t>((nblk > 0 ? nblk : 1) * experts) * sizeof(int32_t);
+  return B200_OK;
+}
+
+extern "C" int b200_moe_index(const int32_t* indices, int64_t tokens, int64_t top_k, int64_t experts,
+                              int32_t* counts, int32_t* offsets, int32_t* perm_token, int32_t* pos,
+                              void* scratch, size_t scratch_bytes, void* stream) {
+  if (int rc = index_check(__func__, tokens, top_k, experts)) return rc;
+  B200_REQUIRE_PTR(counts);
+  B200_REQUIRE_PTR(offsets);
+  B200_REQUIRE_PTR(scratch);
+  const int64_t pairs = tokens * top_k;
+  if (pairs > 0) {
+    B200_REQUIRE_PTR(indices);
+    B200_REQUIRE_PTR(perm_token);
+    B200_REQUIRE_PTR(pos);
+  }
+  const int nblk = nblk_for(pairs);
+  const size_t need = static_cast<size_t>((nblk > 0 ? nblk : 1) * experts) * sizeof(int32_t);
+  if (scratch_bytes < need || !aligned(scratch, 16))
+    return fail(B200_ERR_SCRATCH, "%s: scratch needs %zu bytes, 16-byte aligned (got %zu)", __func__, need, scratch_bytes);
+  if (!aligned(indices, 4) || !aligned(counts, 4) || !aligned(offsets, 4) || !aligned(perm_token, 4) || !aligned(pos, 4))
+    return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to 4 bytes", __func__);
+  if (int rc = check_device()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int E = static_cast<int>(experts);
+  int32_t* block_hist = static_cast<int32_t*>(scratch);
+  if (nblk > 0) {
+    index_hist_kernel<<<nblk, kIndexThreads, E * sizeof(int), st>>>(indices, pairs, E, nblk, block_hist);
+    if (int rc = after_launch("index_hist_kernel")) return rc;
+  }
+  index_scan_kernel<<<1, 1024, 0, st>>>(block_hist, E, nblk, counts, offsets);
+  if (int rc = after_launch("index_scan_kernel")) return rc;
+  if (nblk > 0) {
+    index_scatter_kernel<<<nblk, kIndexThreads, 8 * E * sizeof(int), st>>>(
+        indices, pairs, static_cast<int>(top_k), E, nblk, block_hist, offsets, perm_token, pos);
+    if (int rc = after_launch("index_scatter_kernel")) return rc;
+  }
+  return B200_OK;
+}
+
+namespace {
+template <typename W>
+int launch_permute(const void* x, const int32_t* pos, void* rows, int64_t tokens, int top_k, int64_t row_bytes,
+                   int64_t ldx_bytes, int64_t ldr_bytes, cudaStream_t st) {
+  permute_kernel<W><<<static_cast<unsigned>(ceil_div(tokens, 8)), 256, 0, st>>>(
+      static_cast<const W*>(x), pos, static_cast<W*>(rows), tokens, top_k, static_cast<int>(row_bytes / sizeof(W)),
+      ldx_bytes / static_cast<int64_t>(sizeof(W)), ldr_bytes / static_cast<int64_t>(sizeof(W)));
+  return after_launch("permute_kernel");
+}
+template <typename W>
+int launch_gather(const void* x, const int32_t* src, void* out, int64_t n_rows, int64_t row_bytes,
+                  int64_t ldx_bytes, int64_t ldo_bytes, cudaStream_t st) {
+  gather_kernel<W><<<static_cast<unsigned>(ceil_div(n_rows, 8)), 256, 0, st>>>(
+      static_cast<const W*>(x), src, static_cast<W*>(out), n_rows, static_cast<int>(row_bytes / sizeof(W)),
+      ldx_bytes / static_cast<int64_t>(sizeof(W)), ldo_bytes / static_cast<int64_t>(sizeof(W)));
+  return after_launch("gather_kernel");
+}
+}  // namespace
+
+extern "C" int b200_moe_permute(const void* x, const int32_t* pos, void* rows,
+                                int64_t tokens, int64_t top_k, int64_t hidden,
+                                int64_t ldx, int64_t ldrows, int dtype, void* stream) {
+  if (!dtype_ok(dtype)) return fail(B200_ERR_DTYPE, "%s: unsupported dtype %d", __func__, dtype);
+  if (tokens < 0 || hidden < 0 || top_k < 1 || top_k > kMaxTopK)
+    return fail(B200_ERR_SHAPE, "%s: need tokens, hidden >= 0 and 1 <= top_k <= %d", __func__, kMaxTopK);
+  if (ldx < hidden || ldrows < hidden) return fail(B200_ERR_SHAPE, "%s: leading dimension smaller than hidden", __func__);
+  if (tokens > 0x7fffffffLL * 8 || hidden > 0x7fffffffLL / 4) return fail(B200_ERR_SHAPE, "%s: problem too large", __func__);
+  if (tokens == 0 || hidden == 0) return B200_OK;
+  B200_REQUIRE_PTR(x);
+  B200_REQUIRE_PTR(pos);
+  B200_REQUIRE_PTR(rows);
+  const int64_t es = static_cast<int64_t>(dtype_size(dtype));
+  if (!aligned(x, es) || !aligned(rows, es) || !aligned(pos, 4))
+    return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to the element size", __func__);
+  if (int rc = check_device()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int K = static_cast<int>(top_k);
+  const int64_t rb = hidden * es, lxb = ldx * es, lrb = ldrows * es;
+  if (rows_aligned<uint4>(x, rows, rb, lxb, lrb)) return launch_permute<uint4>(x, pos, rows, tokens, K, rb, lxb, lrb, st);
+  if (rows_aligned<uint32_t>(x, rows, rb, lxb, lrb)) return launch_permute<uint32_t>(x, pos, rows, tokens, K, rb, lxb, lrb, st);
+  return launch_permute<uint16_t>(x, pos, rows, tokens, K, rb, lxb, lrb, st);
+}
+
+extern "C" int b200_moe_gather(const void* x, const int32_t* src_row, void* out,
+                               int64_t n_rows, int64_t hidden, int64_t ldx, int64_t ldo,
+                               int dtype, void* stream) {
+  if (!dtype_ok(dtype)) return fail(B200_ERR_DTYPE, "%s: unsupported dtype %d", __func__, dtype);
+  if (n_rows < 0 || hidden < 0) return fail(B200_ERR_SHAPE, "%s: negative size", __func__);
+  if (ldx < hidden || ldo < hidden) return fail(B200_ERR_SHAPE, "%s: leading dimension smaller than hidden", __func__);
+  if (n_rows > 0x7fffffffLL * 8 || hidden > 0x7fffffffLL / 4) return fail(B200_ERR_SHAPE, "%s: problem too large", __func__);
+  if (n_rows == 0 || hidden == 0) return B200_OK;
+  B200_REQUIRE_PTR(x);
+  B200_REQUIRE_PTR(src_row);
+  B200_REQUIRE_PTR(out);
+  const int64_t es = static_cast<int64_t>(dtype_size(dtype));
+  if (!aligned(x, es) || !aligned(out, es) || !aligned(src_row, 4))
+    return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to the element size", __func__);
+  if (int rc = check_device()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t rb = hidden * es, lxb = ldx * es, lob = ldo * es;
+  if (rows_aligned<uint4>(x, out, rb, lxb, lob)) return launch_gather<uint4>(x, src_row, out, n_rows, rb, lxb, lob, st);
+  if (rows_aligned<uint32_t>(x, out, rb, lxb, lob)) return launch_gather<uint32_t>(x, src_row, out, n_rows, rb, lxb, lob, st);
+  return launch_gather<uint16_t>(x, src_row, out, n_rows, rb, lxb, lob, st);
+}
+
+extern "C" int b200_moe_unpermute(const void* rows, const float* weights, const int32_t* pos, void* y,
+                                  int64_t tokens, int64_t top_k, int64_t hidden,
+                                  int64_t ldrows, int64_t ldy, int dtype, void* stream) {
+  if (!dtype_ok(dtype)) return fail(B200_ERR_DTYPE, "%s: unsupported dtype %d", __func__, dtype);
+  if (tokens < 0 || hidden < 0 || top_k < 1 || top_k > kMaxTopK)
+    return fail(B200_ERR_SHAPE, "%s: need tokens, hidden >= 0 and 1 <= top_k <= %d", __func__, kMaxTopK);
+  if (ldrows < hidden || ldy < hidden) return fail(B200_ERR_SHAPE, "%s: leading dimension smaller than hidden", __func__);
+  if (tokens > 0x7fffffffLL * 8 || hidden > 0x7fffffffLL) return fail(B200_ERR_SHAPE, "%s: problem too large", __func__);
+  if (tokens == 0 || hidden == 0) return B200_OK;
+  B200_REQUIRE_PTR(rows);
+  B200_REQUIRE_PTR(weights);
+  B200_REQUIRE_PTR(pos);
+  B200_REQUIRE_PTR(y);
+  const size_t es = dtype_size(dtype);
+  if (!aligned(rows, es) || !aligned(y, es) || !aligned(weights, 4) || !aligned(pos, 4))
+    return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to the element size", __func__);
+  if (int rc = check_device()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>(ceil_div(tokens, 8));
+  const int K = static_cast<int>(top_k), H = static_cast<int>(hidden);
+  B200_DISPATCH_DTYPE(dtype, T, {
+    constexpr int V = Num<T>::kVec;
+    const bool vec = hidden % V == 0 && ldrows % V == 0 && ldy % V == 0 && aligned(rows, 16) && aligned(y, 16);
+    if (vec)
+      unpermute_kernel<T, true><<<grid, 256, 0, st>>>(static_cast<const T*>(rows), weights, pos, static_cast<T*>(y), tokens, K, H, ldrows, ldy);
+    else
+      unpermute_kernel<T, false><<<grid, 256, 0, st>>>(static_cast<const T*>(rows), weights, pos, static_cast<T*>(y), tokens, K, H, ldrows, ldy);
+  });
+  return after_launch("unpermute_kernel");
+}

@@ -1,0 +1,142 @@
+// SwiGLU forward for sm_100a:  out = round_T(round_T(silu(a)) * b).
+//
+// Bound: HBM (2 reads + 1 write per element, ~25 fp32 instructions).  `a` and `b`
+// are addressed through their own leading dimensions, so the two column halves
+// of a fused [rows, 2*cols] gate_up buffer are consumed in place; the
+// incumbent (src/popcorn/impls/swiglu.cu:80-81) copies them to contiguous
+// buffers first.
+//
+// Arithmetic follows F.silu(a) * b of src/popcorn/kernels/swiglu.py:18 as PyTorch
+// evaluates it for a 16-bit dtype: silu = a / (1 + exp(-a)) in fp32, rounded to
+// T, then the product computed in fp32 and rounded to T again.
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+template <typename T>
+__device__ __forceinline__ float swiglu_one(float a, float b) {
+  const float e = expf(-a);
+  const float silu = __fdiv_rn(a, __fadd_rn(1.0f, e));
+  return Num<T>::rt(__fmul_rn(Num<T>::rt(silu), b));
+}
+
+// Each thread owns UNROLL 128-bit words, THREADS words apart, so a warp always
+// touches 512 contiguous bytes of one row.  (row, word) of the first word comes
+// from one division; the rest follow by carry.
+template <typename T, int UNROLL, typename Index>
+__global__ void __launch_bounds__(256)
+swiglu_vec_kernel(const T* a, const T* b, T* out, Index total_words, Index words_per_row,
+                  int64_t lda, int64_t ldb, int64_t ldo) {
+  constexpr int V = Num<T>::kVec;
+  constexpr int THREADS = 256;
+  const Index first = static_cast<Index>(blockIdx.x) * (THREADS * UNROLL) + threadIdx.x;
+  Index row = first / words_per_row;
+  Index word = first - row * words_per_row;
+
+  uint4 va[UNROLL], vb[UNROLL];
+  int64_t off_o[UNROLL];
+  bool ok[UNROLL];
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) {
+    ok[u] = first + static_cast<Index>(u) * THREADS < total_words;
+    va[u] = make_uint4(0, 0, 0, 0);
+    vb[u] = make_uint4(0, 0, 0, 0);
+    if (ok[u]) {
+      va[u] = ld_stream(a + static_cast<int64_t>(row) * lda + static_cast<int64_t>(word) * V);
+      vb[u] = ld_stream(b + static_cast<int64_t>(row) * ldb + static_cast<int64_t>(word) * V);
+    }
+    off_o[u] = static_cast<int64_t>(row) * ldo + static_cast<int64_t>(word) * V;
+    word += THREADS;
+    if (word >= words_per_row) {
+      if (words_per_row >= THREADS) {  // at most one row boundary crossed
+        word -= words_per_row;
+        ++row;
+      } else {
+        const Index next = first + static_cast<Index>(u + 1) * THREADS;
+        row = next / words_per_row;
+        word = next - row * words_per_row;
+      }
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) {
+    float fa[V], fb[V];
+    Num<T>::unpack(va[u], fa);
+    Num<T>::unpack(vb[u], fb);
+#pragma unroll
+    for (int j = 0; j < V; ++j) fa[j] = swiglu_one<T>(fa[j], fb[j]);
+    if (ok[u]) st_stream(out + off_o[u], Num<T>::pack(fa));
+  }
+}
+
+// Any width, any alignment.
+template <typename T>
+__global__ void __launch_bounds__(256)
+swiglu_scalar_kernel(const T* a, const T* b, T* out, int64_t rows, int64_t cols,
+                     int64_t lda, int64_t ldb, int64_t ldo) {
+  const int64_t total = rows * cols;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / cols, c = i - r * cols;
+    out[r * ldo + c] = Num<T>::down(swiglu_one<T>(Num<T>::up(a[r * lda + c]), Num<T>::up(b[r * ldb + c])));
+  }
+}
+
+template <typename T>
+int run(const void* a, const void* b, void* out, int64_t rows, int64_t cols,
+        int64_t lda, int64_t ldb, int64_t ldo, cudaStream_t st) {
+  constexpr int V = Num<T>::kVec;
+  constexpr int UNROLL = 4;
+  const bool vec = cols % V == 0 && lda % V == 0 && ldb % V == 0 && ldo % V == 0 && aligned(a, 16) &&
+                   aligned(b, 16) && aligned(out, 16);
+  if (vec) {
+    int64_t wpr = cols / V;
+    int64_t n_rows = rows;
+    if (lda == cols && ldb == cols && ldo == cols) {  // fully contiguous: one long row
+      wpr = rows * wpr;
+      n_rows = 1;
+    }
+    const int64_t total = n_rows * wpr;
+    const int64_t grid = ceil_div(total, 256 * UNROLL);
+    if (grid > 0x7fffffffLL) return fail(B200_ERR_SHAPE, "b200_swiglu: problem too large for one launch");
+    if (total < 0x7fffffffLL) {
+      swiglu_vec_kernel<T, UNROLL, uint32_t><<<static_cast<unsigned>(grid), 256, 0, st>>>(
+          static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), static_cast<uint32_t>(total),
+          static_cast<uint32_t>(wpr), lda, ldb, ldo);
+    } else {
+      swiglu_vec_kernel<T, UNROLL, uint64_t><<<static_cast<unsigned>(grid), 256, 0, st>>>(
+          static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), static_cast<uint64_t>(total),
+          static_cast<uint64_t>(wpr), lda, ldb, ldo);
+    }
+    return after_launch("swiglu_vec_kernel");
+  }
+  const int64_t want = ceil_div(rows * cols, 256);
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
+  swiglu_scalar_kernel<T><<<static_cast<unsigned>(want < cap ? want : cap), 256, 0, st>>>(
+      static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), rows, cols, lda, ldb, ldo);
+  return after_launch("swiglu_scalar_kernel");
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_swiglu(const void* a, const void* b, void* out, int64_t rows, int64_t cols,
+                           int64_t lda, int64_t ldb, int64_t ldo, int dtype, void* stream) {
+  if (!dtype_ok(dtype)) return fail(B200_ERR_DTYPE, "%s: unsupported dtype %d", __func__, dtype);
+  if (rows < 0 || cols < 0) return fail(B200_ERR_SHAPE, "%s: negative size", __func__);
+  if (rows == 0 || cols == 0) return B200_OK;
+  B200_REQUIRE_PTR(a);
+  B200_REQUIRE_PTR(b);
+  B200_REQUIRE_PTR(out);
+  if (lda < cols || ldb < cols || ldo < cols) return fail(B200_ERR_SHAPE, "%s: leading dimension smaller than cols", __func__);
+  const size_t es = dtype_size(dtype);
+  if (!aligned(a, es) || !aligned(b, es) || !aligned(out, es))
+    return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to the element size", __func__);
+  if (int rc = check_device()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  B200_DISPATCH_DTYPE(dtype, T, return run<T>(a, b, out, rows, cols, lda, ldb, ldo, st));
+  return B200_OK;
+}

@@ -1,0 +1,55 @@
+"""Op declarations on the local registry mirror, each with the `b200` backend attached.
+
+The four existing popcorn ops keep popcorn's names, parameter order and defaults
+(src/popcorn/kernels/rms_norm.py:16-21, add_rms_norm.py:8-14,
+rotary_embedding.py:15-20, swiglu.py:10); the MoE steps are new ops because
+popcorn only has them fused inside `momoe` (src/popcorn/kernels/momoe.py:47-53).
+The declaration bodies are never executed: an op here is its signature plus the
+backends registered on it.
+"""
+
+from __future__ import annotations
+
+from popcorn_b200.registry import register_kernel
+
+BACKEND = "b200"
+
+
+@register_kernel
+def rms_norm(x, weight, bias=None, eps=1e-6):
+    """Root-mean-square normalization over the last dimension."""
+
+
+@register_kernel
+def add_rms_norm(x, residual, weight, eps=1e-6, offset=0.0):
+    """Residual add fused with RMS norm; returns (normalized sum, new residual stream)."""
+
+
+@register_kernel
+def rotary_embedding(x, cos, sin, interleaved=False):
+    """Rotary position embedding, GPT-NeoX halves or GPT-J interleaved pairs."""
+
+
+@register_kernel
+def swiglu(a, b):
+    """SwiGLU gating: silu(a) * b."""
+
+
+@register_kernel
+def moe_route(router_logits, top_k=2):
+    """Softmax over experts, top-k selection, renormalized gate weights."""
+
+
+@register_kernel
+def moe_permute(x, indices, experts):
+    """Stable sort of (token, slot) pairs by expert and the row gather into that order."""
+
+
+@register_kernel
+def moe_unpermute(rows, weights, pos):
+    """Gate-weighted sum of expert rows back into token order."""
+
+
+for _op in (rms_norm, add_rms_norm, rotary_embedding, swiglu, moe_route, moe_permute, moe_unpermute):
+    _op.register(BACKEND, source=f"popcorn_b200.ops.{_op.name}", forward_only=True)
+del _op

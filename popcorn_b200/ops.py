@@ -1,0 +1,313 @@
+"""The ops of the `b200` backend, with the signatures of popcorn's references.
+
+Each function takes CUDA tensors, allocates its outputs with torch, and enqueues
+one or more sm_100a kernels of libpopcorn_b200.so on the current stream of the
+input's device.  Nothing here computes on the host and nothing falls back to
+PyTorch arithmetic: a CPU tensor, an unsupported dtype or a missing library is
+an error.  The ops are forward-only (no autograd), like popcorn backends
+registered with ``forward_only=True``
+(src/popcorn/core/dispatcher.py:130-131).
+
+Signatures served (names and order are popcorn's):
+  rms_norm(x, weight, bias=None, eps=1e-6)                 src/popcorn/kernels/rms_norm.py:16-21
+  add_rms_norm(x, residual, weight, eps=1e-6, offset=0.0)  src/popcorn/kernels/add_rms_norm.py:8-14
+  rotary_embedding(x, cos, sin, interleaved=False)         src/popcorn/kernels/rotary_embedding.py:15-20
+  swiglu(a, b)                                             src/popcorn/kernels/swiglu.py:10
+and the MoE steps popcorn only has fused inside `momoe`
+(src/popcorn/kernels/momoe.py:47-53, src/popcorn/impls/momoe_tl.py:1071-1161):
+  moe_route, moe_index, moe_permute, moe_gather, moe_unpermute.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+from torch import Tensor
+
+from popcorn_b200 import _lib
+
+_DTYPES = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
+
+
+def _dtype_code(t: Tensor, what: str) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError(f"{what}: dtype {t.dtype} is not supported (float32, float16, bfloat16)") from None
+
+
+def _require_cuda(*tensors: Tensor | None) -> torch.device:
+    device = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("popcorn_b200 ops run on CUDA tensors only; there is no CPU implementation")
+        if device is None:
+            device = t.device
+        elif t.device != device:
+            raise RuntimeError(f"tensors live on different devices: {device} and {t.device}")
+    assert device is not None
+    return device
+
+
+def _forbid_grad(*tensors: Tensor | None) -> None:
+    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors):
+        raise RuntimeError("popcorn_b200 ops are forward-only; call them under torch.no_grad() or detach the inputs")
+
+
+def _rows(t: Tensor) -> tuple[Tensor, int]:
+    """View `t` [..., D] as [rows, D] with a contiguous last dim; returns (view, leading dimension)."""
+    width = t.shape[-1]
+    if t.dim() == 2 and (t.stride(1) == 1 or width == 1):
+        return t, (t.stride(0) if t.shape[0] > 1 else max(width, 1))
+    if t.dim() >= 1 and (t.stride(-1) == 1 or width == 1):
+        try:
+            flat = t.view(-1, width)
+        except RuntimeError:
+            flat = None
+        if flat is not None and (flat.stride(1) == 1 or width == 1):
+            return flat, (flat.stride(0) if flat.shape[0] > 1 else max(width, 1))
+    flat = t.reshape(-1, width).contiguous()
+    return flat, max(width, 1)
+
+
+def _ptr(t: Tensor | None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream(device: torch.device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def rms_norm(x: Tensor, weight: Tensor, bias: Tensor | None = None, eps: float = 1e-6) -> Tensor:
+    """Root-mean-square normalisation over the last dimension (rms_norm.py:16-30)."""
+    device = _require_cuda(x, weight, bias)
+    _forbid_grad(x, weight, bias)
+    code = _dtype_code(x, "rms_norm")
+    width = x.shape[-1]
+    if weight.shape != (width,) or (bias is not None and bias.shape != (width,)):
+        raise ValueError(f"rms_norm: weight/bias must have shape ({width},)")
+    if weight.dtype != x.dtype or (bias is not None and bias.dtype != x.dtype):
+        raise TypeError("rms_norm: weight and bias must have the dtype of x")
+    x2, ldx = _rows(x)
+    y = torch.empty(x.shape, dtype=x.dtype, device=device)
+    y2 = y.view(-1, width)
+    with torch.cuda.device(device):
+        _lib.call(
+            "b200_rms_norm", _ptr(x2), _ptr(weight.contiguous()), _ptr(None if bias is None else bias.contiguous()), _ptr(y2),
+            x2.shape[0], width, ldx, max(width, 1), code, float(eps), _stream(device),
+        )
+    return y
+
+
+def add_rms_norm(
+    x: Tensor, residual: Tensor, weight: Tensor, eps: float = 1e-6, offset: float = 0.0
+) -> tuple[Tensor, Tensor]:
+    """s = x + residual; returns (rms_norm(s) * (weight + offset), s) (add_rms_norm.py:8-23)."""
+    device = _require_cuda(x, residual, weight)
+    _forbid_grad(x, residual, weight)
+    code = _dtype_code(x, "add_rms_norm")
+    width = x.shape[-1]
+    if residual.shape != x.shape:
+        raise ValueError("add_rms_norm: x and residual must have the same shape")
+    if weight.shape != (width,):
+        raise ValueError(f"add_rms_norm: weight must have shape ({width},)")
+    if residual.dtype != x.dtype or weight.dtype != x.dtype:
+        raise TypeError("add_rms_norm: residual and weight must have the dtype of x")
+    x2, ldx = _rows(x)
+    r2, ldr = _rows(residual)
+    y = torch.empty(x.shape, dtype=x.dtype, device=device)
+    s = torch.empty(x.shape, dtype=x.dtype, device=device)
+    ld = max(width, 1)
+    with torch.cuda.device(device):
+        _lib.call(
+            "b200_add_rms_norm", _ptr(x2), _ptr(r2), _ptr(weight.contiguous()), _ptr(y), _ptr(s),
+            x2.shape[0], width, ldx, ldr, ld, ld, code, float(eps), float(offset), _stream(device),
+        )
+    return y, s
+
+
+def _rope_check(x: Tensor, cos: Tensor, sin: Tensor, name: str) -> tuple[int, int]:
+    if x.dim() != 4:
+        raise ValueError(f"{name}: x must be [batch, seq, heads, head_dim]")
+    if cos.shape != sin.shape or cos.dim() != 2 or cos.shape[0] != x.shape[1]:
+        raise ValueError(f"{name}: cos and sin must both be [seq, half]")
+    half = cos.shape[1]
+    if 2 * half > x.shape[-1]:
+        raise ValueError(f"{name}: 2*half={2 * half} exceeds head_dim={x.shape[-1]}")
+    if cos.dtype != sin.dtype or cos.dtype not in (torch.float32, x.dtype):
+        raise TypeError(f"{name}: cos/sin must be float32 or the dtype of x")
+    if x.shape[-1] > 1 and x.stride(-1) != 1:
+        raise ValueError(f"{name}: the head_dim dimension of x must be contiguous")
+    return half, _DTYPES[cos.dtype]
+
+
+def rotary_embedding(x: Tensor, cos: Tensor, sin: Tensor, interleaved: bool = False) -> Tensor:
+    """Rotary position embedding, out of place (rotary_embedding.py:15-40)."""
+    device = _require_cuda(x, cos, sin)
+    _forbid_grad(x)
+    code = _dtype_code(x, "rotary_embedding")
+    half, cs_code = _rope_check(x, cos, sin, "rotary_embedding")
+    out = torch.empty(x.shape, dtype=x.dtype, device=device)
+    b, s, h, d = x.shape
+    with torch.cuda.device(device):
+        _lib.call(
+            "b200_rope", _ptr(x), _ptr(cos.contiguous()), _ptr(sin.contiguous()), _ptr(out), b, s, h, d, half,
+            x.stride(0), x.stride(1), x.stride(2), out.stride(0), out.stride(1), out.stride(2),
+            code, cs_code, int(bool(interleaved)), _stream(device),
+        )
+    return out
+
+
+def rotary_embedding_(x: Tensor, cos: Tensor, sin: Tensor, interleaved: bool = False) -> Tensor:
+    """In-place variant of rotary_embedding: rotates x where it lies and returns it."""
+    device = _require_cuda(x, cos, sin)
+    _forbid_grad(x)
+    code = _dtype_code(x, "rotary_embedding_")
+    half, cs_code = _rope_check(x, cos, sin, "rotary_embedding_")
+    b, s, h, d = x.shape
+    with torch.cuda.device(device):
+        _lib.call(
+            "b200_rope", _ptr(x), _ptr(cos.contiguous()), _ptr(sin.contiguous()), _ptr(x), b, s, h, d, half,
+            x.stride(0), x.stride(1), x.stride(2), x.stride(0), x.stride(1), x.stride(2),
+            code, cs_code, int(bool(interleaved)), _stream(device),
+        )
+    return x
+
+
+def rotary_embedding_qk_(q: Tensor, k: Tensor, cos: Tensor, sin: Tensor, interleaved: bool = False) -> tuple[Tensor, Tensor]:
+    """Rotate q and k in place with one launch (the cos/sin row is fetched once for both)."""
+    device = _require_cuda(q, k, cos, sin)
+    _forbid_grad(q, k)
+    code = _dtype_code(q, "rotary_embedding_qk_")
+    if k.dtype != q.dtype:
+        raise TypeError("rotary_embedding_qk_: q and k must share a dtype")
+    half, cs_code = _rope_check(q, cos, sin, "rotary_embedding_qk_")
+    _rope_check(k, cos, sin, "rotary_embedding_qk_")
+    if q.shape[:2] != k.shape[:2] or q.shape[-1] != k.shape[-1]:
+        raise ValueError("rotary_embedding_qk_: q and k must agree in batch, seq and head_dim")
+    b, s, hq, d = q.shape
+    with torch.cuda.device(device):
+        _lib.call(
+            "b200_rope_qk", _ptr(q), _ptr(k), _ptr(cos.contiguous()), _ptr(sin.contiguous()), b, s, hq, k.shape[2], d, half,
+            q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+            code, cs_code, int(bool(interleaved)), _stream(device),
+        )
+    return q, k
+
+
+def swiglu(a: Tensor, b: Tensor) -> Tensor:
+    """silu(a) * b (swiglu.py:10-18); a and b may be strided column halves of one buffer."""
+    device = _require_cuda(a, b)
+    _forbid_grad(a, b)
+    code = _dtype_code(a, "swiglu")
+    if a.shape != b.shape or a.dtype != b.dtype:
+        raise ValueError("swiglu: a and b must have the same shape and dtype")
+    width = a.shape[-1]
+    a2, lda = _rows(a)
+    b2, ldb = _rows(b)
+    out = torch.empty(a.shape, dtype=a.dtype, device=device)
+    with torch.cuda.device(device):
+        _lib.call("b200_swiglu", _ptr(a2), _ptr(b2), _ptr(out), a2.shape[0], width, lda, ldb, max(width, 1), code, _stream(device))
+    return out
+
+
+def moe_route(router_logits: Tensor, top_k: int) -> tuple[Tensor, Tensor]:
+    """softmax over experts -> top_k -> renormalise (momoe.py:47-49).
+
+    Returns (indices int32 [..., top_k] in descending-probability order, weights float32 [..., top_k])."""
+    device = _require_cuda(router_logits)
+    _forbid_grad(router_logits)
+    code = _dtype_code(router_logits, "moe_route")
+    experts = router_logits.shape[-1]
+    logits2, ld = _rows(router_logits)
+    lead = router_logits.shape[:-1]
+    indices = torch.empty((*lead, top_k), dtype=torch.int32, device=device)
+    weights = torch.empty((*lead, top_k), dtype=torch.float32, device=device)
+    with torch.cuda.device(device):
+        _lib.call("b200_moe_route", _ptr(logits2), _ptr(indices), _ptr(weights), logits2.shape[0], experts, int(top_k), ld, code, _stream(device))
+    return indices, weights
+
+
+def moe_index(indices: Tensor, experts: int) -> tuple[Tensor, Tensor, Tensor, Tensor]:
+    """Expert histogram, exclusive scan and stable permutation (momoe_tl.py:1071-1161).
+
+    indices: int32 [tokens, top_k].  Returns (counts [experts], offsets [experts + 1],
+    perm [tokens*top_k] = token id at each sorted position, pos [tokens, top_k] = sorted
+    position of each pair), all int32."""
+    device = _require_cuda(indices)
+    if indices.dim() != 2 or indices.dtype != torch.int32:
+        raise TypeError("moe_index: indices must be an int32 [tokens, top_k] tensor")
+    indices = indices.contiguous()
+    tokens, top_k = indices.shape
+    counts = torch.empty(experts, dtype=torch.int32, device=device)
+    offsets = torch.empty(experts + 1, dtype=torch.int32, device=device)
+    perm = torch.empty(tokens * top_k, dtype=torch.int32, device=device)
+    pos = torch.empty((tokens, top_k), dtype=torch.int32, device=device)
+    need = ctypes.c_size_t(0)
+    _lib.call("b200_moe_index_scratch_bytes", tokens, top_k, int(experts), ctypes.byref(need))
+    scratch = torch.empty(max(need.value, 16), dtype=torch.uint8, device=device)
+    with torch.cuda.device(device):
+        _lib.call(
+            "b200_moe_index", _ptr(indices), tokens, top_k, int(experts), _ptr(counts), _ptr(offsets), _ptr(perm), _ptr(pos),
+            _ptr(scratch), ctypes.c_size_t(scratch.numel()), _stream(device),
+        )
+    return counts, offsets, perm, pos
+
+
+def moe_permute(x: Tensor, indices: Tensor, experts: int) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
+    """Gather token rows into expert-contiguous order (momoe_tl.py:156-158, 408-476).
+
+    x: [tokens, hidden]; indices: int32 [tokens, top_k].  Returns (rows [tokens*top_k, hidden],
+    counts, offsets, perm, pos); rows[p] = x[perm[p]], pairs sorted stably by expert."""
+    device = _require_cuda(x, indices)
+    _forbid_grad(x)
+    code = _dtype_code(x, "moe_permute")
+    if x.dim() != 2 or indices.dim() != 2 or indices.shape[0] != x.shape[0]:
+        raise ValueError("moe_permute: x must be [tokens, hidden] and indices [tokens, top_k]")
+    counts, offsets, perm, pos = moe_index(indices, experts)
+    tokens, hidden = x.shape
+    top_k = indices.shape[1]
+    x2, ldx = _rows(x)
+    rows = torch.empty((tokens * top_k, hidden), dtype=x.dtype, device=device)
+    with torch.cuda.device(device):
+        _lib.call("b200_moe_permute", _ptr(x2), _ptr(pos), _ptr(rows), tokens, top_k, hidden, ldx, max(hidden, 1), code, _stream(device))
+    return rows, counts, offsets, perm, pos
+
+
+def moe_gather(x: Tensor, src_rows: Tensor) -> Tensor:
+    """out[p] = x[src_rows[p]] for an int32 row index (negative entries leave the row unwritten)."""
+    device = _require_cuda(x, src_rows)
+    _forbid_grad(x)
+    code = _dtype_code(x, "moe_gather")
+    if x.dim() != 2 or src_rows.dim() != 1 or src_rows.dtype != torch.int32:
+        raise TypeError("moe_gather: x must be [rows, hidden] and src_rows an int32 vector")
+    x2, ldx = _rows(x)
+    hidden = x.shape[1]
+    out = torch.empty((src_rows.shape[0], hidden), dtype=x.dtype, device=device)
+    with torch.cuda.device(device):
+        _lib.call("b200_moe_gather", _ptr(x2), _ptr(src_rows.contiguous()), _ptr(out), src_rows.shape[0], hidden, ldx, max(hidden, 1), code, _stream(device))
+    return out
+
+
+def moe_unpermute(rows: Tensor, weights: Tensor, pos: Tensor) -> Tensor:
+    """y[t] = sum_k weights[t, k] * rows[pos[t, k]] in fp32, ascending expert order (momoe.py:52-53)."""
+    device = _require_cuda(rows, weights, pos)
+    _forbid_grad(rows, weights)
+    code = _dtype_code(rows, "moe_unpermute")
+    if rows.dim() != 2 or weights.shape != pos.shape or pos.dim() != 2:
+        raise ValueError("moe_unpermute: rows must be [n, hidden]; weights and pos [tokens, top_k]")
+    if weights.dtype != torch.float32 or pos.dtype != torch.int32:
+        raise TypeError("moe_unpermute: weights must be float32 and pos int32")
+    tokens, top_k = pos.shape
+    hidden = rows.shape[1]
+    r2, ldr = _rows(rows)
+    y = torch.empty((tokens, hidden), dtype=rows.dtype, device=device)
+    with torch.cuda.device(device):
+        _lib.call(
+            "b200_moe_unpermute", _ptr(r2), _ptr(weights.contiguous()), _ptr(pos.contiguous()), _ptr(y),
+            tokens, top_k, hidden, ldr, max(hidden, 1), code, _stream(device),
+        )
+    return y

@@ -1,0 +1,109 @@
+"""Attach the `b200` backend to popcorn's own registry.
+
+    import popcorn_b200.plugin
+    popcorn_b200.plugin.register()            # needs `popcorn` importable
+    popcorn.KERNELS["rms_norm"](x, w, backend="b200")
+
+For the four ops popcorn already defines, this is one `op.register(name,
+source=..., forward_only=True)` line each, the same form popcorn's own backends
+use (src/popcorn/kernels/rms_norm.py:33-59, add_rms_norm.py:26-28,
+rotary_embedding.py:43-45, swiglu.py:21-31).  The sources are bare: each
+popcorn_b200.ops function takes the reference's parameters positionally in the
+reference's order, which is what popcorn checks when the source is first
+resolved (src/popcorn/core/dispatcher.py:184-201).
+
+popcorn has no standalone MoE routing / permute / unpermute ops: those steps are
+fused inside `momoe` (src/popcorn/kernels/momoe.py:47-53,
+src/popcorn/impls/momoe_tl.py:1071-1161).  `register()` therefore also defines
+three new ops with `register_kernel`.  popcorn requires every op to carry a
+PyTorch definition of its semantics; the three small torch functions below are
+those definitions.  popcorn's harness may call them as the op's `torch` entry;
+no code path of popcorn_b200 ever does.
+"""
+
+from typing import Any
+
+import torch
+from torch import Tensor
+
+BACKEND = "b200"
+EXISTING_OPS = ("rms_norm", "add_rms_norm", "rotary_embedding", "swiglu")
+NEW_OPS = ("moe_route", "moe_permute", "moe_unpermute")
+
+_SUPPORTED = (torch.float32, torch.float16, torch.bfloat16)
+
+
+def accepts(**arguments: Any) -> bool:
+    """Dispatch predicate: CUDA tensors in a dtype the kernels implement."""
+    tensors = [value for value in arguments.values() if isinstance(value, Tensor)]
+    return bool(tensors) and all(
+        t.is_cuda and (not t.is_floating_point() or t.dtype in _SUPPORTED) for t in tensors
+    )
+
+
+def _define_moe_ops(popcorn: Any) -> None:
+    from jaxtyping import Float, Int
+
+    register_kernel, Tag = popcorn.register_kernel, popcorn.Tag
+
+    @register_kernel(test_args={"top_k": [2, 8]}, tags={Tag.FEATURE_MIXER})
+    def moe_route(
+        router_logits: Float[Tensor, "tokens experts"],
+        top_k: int = 2,
+    ) -> tuple[Int[Tensor, "tokens top_k"], Float[Tensor, "tokens top_k"]]:
+        r"""Softmax top-k routing with the picked probabilities renormalized to sum one.
+
+        $$w_e = \frac{p_e}{\sum_{e' \in \mathrm{top}k(p)} p_{e'}}, \qquad p = \mathrm{softmax}(r)$$
+        """
+        probs = torch.softmax(router_logits.to(torch.promote_types(router_logits.dtype, torch.float32)), -1)
+        picked = probs.topk(top_k, -1)
+        return picked.indices.to(torch.int32), picked.values / picked.values.sum(-1, keepdim=True)
+
+    @register_kernel(tags={Tag.FEATURE_MIXER})
+    def moe_permute(
+        x: Float[Tensor, "tokens hidden"],
+        indices: Int[Tensor, "tokens top_k"],
+        experts: int,
+    ) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
+        r"""Stable sort of (token, slot) pairs by expert, and the token rows gathered into that order.
+
+        $$\mathrm{rows}_p = x_{\pi(p)}, \qquad \pi = \mathrm{argsort}_{\mathrm{stable}}(\mathrm{indices})$$
+        """
+        tokens, top_k = indices.shape
+        flat = indices.reshape(-1).long()
+        counts = torch.bincount(flat, minlength=experts)[:experts]
+        offsets = torch.cat((counts.new_zeros(1), counts.cumsum(0)))
+        order = torch.sort(flat, stable=True).indices
+        perm = order // top_k
+        pos = torch.empty_like(order)
+        pos[order] = torch.arange(order.numel(), device=order.device)
+        return x[perm], counts.int(), offsets.int(), perm.int(), pos.view(tokens, top_k).int()
+
+    @register_kernel(tags={Tag.FEATURE_MIXER})
+    def moe_unpermute(
+        rows: Float[Tensor, "rows hidden"],
+        weights: Float[Tensor, "tokens slots"],
+        pos: Int[Tensor, "tokens slots"],
+    ) -> Float[Tensor, "tokens hidden"]:
+        r"""Gate-weighted sum of expert rows back into token order, accumulated in fp32.
+
+        $$y_t = \sum_k w_{t,k}\, \mathrm{rows}_{\mathrm{pos}(t,k)}$$
+        """
+        picked = rows[pos.long()].to(torch.promote_types(rows.dtype, torch.float32))
+        return torch.einsum("tkd,tk->td", picked, weights.to(picked.dtype)).to(rows.dtype)
+
+
+def register(backend: str = BACKEND) -> list[str]:
+    """Register the b200 backend on popcorn's ops; returns the names of the ops it now serves."""
+    import popcorn
+    import popcorn.kernels  # noqa: F401  (fills popcorn.KERNELS)
+
+    served = []
+    if not all(name in popcorn.KERNELS for name in NEW_OPS):
+        _define_moe_ops(popcorn)
+    for name in (*EXISTING_OPS, *NEW_OPS):
+        op = popcorn.KERNELS[name]
+        if backend not in op.available_backends():
+            op.register(backend, source=f"popcorn_b200.ops.{name}", predicate=accepts, forward_only=True)
+        served.append(name)
+    return served

@@ -1,0 +1,159 @@
+"""Generate tests/golden/*.npz by running the REAL popcorn references.
+
+Run it where the reference source tree is available:
+
+    PYTHONPATH=<popcorn checkout>/src python tests/golden/make_golden.py
+
+It imports `popcorn.kernels`, draws inputs the way popcorn's own harness does
+(src/popcorn/bench/grid.py:682-715: a CPU generator seeded per case, `torch.randn`
+in fp32 in signature order, an optional affine transform, then a cast to the
+case dtype), calls `KERNELS[op].reference(...)` on CPU and stores inputs and
+outputs bit-exactly.  The committed fixtures let the oracle be checked on
+machines where popcorn itself is not installed.
+"""
+
+from __future__ import annotations
+
+import os
+import sys
+import tempfile
+import warnings
+from pathlib import Path
+
+import torch
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[2]))
+from tests.golden.golden_io import save_case  # noqa: E402
+
+os.environ.setdefault("POPCORN_CACHE_DIR", tempfile.mkdtemp(prefix="popcorn-cache-"))
+warnings.filterwarnings("ignore")
+import popcorn.kernels  # noqa: E402,F401
+from popcorn import KERNELS  # noqa: E402
+
+BF16, F16, F32 = torch.bfloat16, torch.float16, torch.float32
+
+
+def randn(gen: torch.Generator, *shape: int) -> torch.Tensor:
+    return torch.randn(shape, generator=gen)
+
+
+def rms_norm_cases() -> None:
+    ref = KERNELS["rms_norm"].reference
+    for name, seed, rows, cols, dtype, eps, with_bias in [
+        ("rms_norm_f32_5x64", 0, 5, 64, F32, 1e-6, False),
+        ("rms_norm_f32_3x50_bias", 1, 3, 50, F32, 1e-5, True),
+        ("rms_norm_bf16_7x264_bias", 2, 7, 264, BF16, 1e-5, True),
+        ("rms_norm_bf16_4x1024", 3, 4, 1024, BF16, 1e-6, False),
+        ("rms_norm_f16_3x40", 4, 3, 40, F16, 1e-6, False),
+    ]:
+        gen = torch.Generator().manual_seed(seed)
+        x = randn(gen, rows, cols).to(dtype)
+        weight = (1 + 0.1 * randn(gen, cols)).to(dtype)
+        bias = randn(gen, cols).to(dtype) if with_bias else None
+        y = ref(x, weight, bias, eps)
+        tensors = {"x": x, "weight": weight, "y": y}
+        if bias is not None:
+            tensors["bias"] = bias
+        save_case(name, tensors, {"op": "rms_norm", "eps": eps})
+
+
+def add_rms_norm_cases() -> None:
+    ref = KERNELS["add_rms_norm"].reference
+    for name, seed, rows, cols, dtype, eps, offset in [
+        ("add_rms_norm_bf16_6x256", 10, 6, 256, BF16, 1e-5, 0.0),
+        ("add_rms_norm_bf16_4x72_offset1", 11, 4, 72, BF16, 1e-6, 1.0),
+        ("add_rms_norm_f32_3x50", 12, 3, 50, F32, 1e-6, 0.0),
+        ("add_rms_norm_f16_5x128_offset1", 13, 5, 128, F16, 1e-5, 1.0),
+        ("add_rms_norm_bf16_2x8192", 14, 2, 8192, BF16, 1e-5, 0.0),
+    ]:
+        gen = torch.Generator().manual_seed(seed)
+        x = randn(gen, rows, cols).to(dtype)
+        residual = randn(gen, rows, cols).to(dtype)
+        weight = (1 + 0.1 * randn(gen, cols)).to(dtype)
+        y, s = ref(x, residual, weight, eps, offset)
+        save_case(name, {"x": x, "residual": residual, "weight": weight, "y": y, "s": s},
+                  {"op": "add_rms_norm", "eps": eps, "offset": offset})
+
+
+def rope_tables(seq: int, half: int, theta: float = 500000.0) -> tuple[torch.Tensor, torch.Tensor]:
+    inv = theta ** (-torch.arange(0, 2 * half, 2, dtype=torch.float32) / (2 * half))
+    ang = torch.outer(torch.arange(seq, dtype=torch.float32), inv)
+    return ang.cos(), ang.sin()
+
+
+def rotary_cases() -> None:
+    ref = KERNELS["rotary_embedding"].reference
+    for name, seed, shape, half, dtype, cs_dtype, interleaved in [
+        ("rope_bf16_neox_2x16x4x64", 20, (2, 16, 4, 64), 32, BF16, F32, False),
+        ("rope_bf16_neox_partial_1x8x2x64_h16", 21, (1, 8, 2, 64), 16, BF16, F32, False),
+        ("rope_bf16_gptj_2x8x3x32", 22, (2, 8, 3, 32), 16, BF16, F32, True),
+        ("rope_f32_neox_1x8x2x16", 23, (1, 8, 2, 16), 8, F32, F32, False),
+        ("rope_f16_neox_cs16_2x4x2x32", 24, (2, 4, 2, 32), 16, F16, F16, False),
+        ("rope_bf16_neox_odd_1x5x3x20_h5", 25, (1, 5, 3, 20), 5, BF16, F32, False),
+        ("rope_bf16_neox_2x8x8x128", 26, (2, 8, 8, 128), 64, BF16, F32, False),
+    ]:
+        gen = torch.Generator().manual_seed(seed)
+        x = randn(gen, *shape).to(dtype)
+        cos, sin = rope_tables(shape[1], half)
+        cos, sin = cos.to(cs_dtype), sin.to(cs_dtype)
+        y = ref(x, cos, sin, interleaved)
+        save_case(name, {"x": x, "cos": cos, "sin": sin, "y": y}, {"op": "rotary_embedding", "interleaved": interleaved})
+
+
+def swiglu_cases() -> None:
+    ref = KERNELS["swiglu"].reference
+    for name, seed, rows, cols, dtype, scale in [
+        ("swiglu_bf16_9x136", 30, 9, 136, BF16, 1.0),
+        ("swiglu_bf16_4x1024_wide", 31, 4, 1024, BF16, 4.0),
+        ("swiglu_f32_5x33", 32, 5, 33, F32, 1.0),
+        ("swiglu_f16_6x72", 33, 6, 72, F16, 2.0),
+    ]:
+        gen = torch.Generator().manual_seed(seed)
+        gate_up = (scale * randn(gen, rows, 2 * cols)).to(dtype)
+        a, b = gate_up[:, :cols], gate_up[:, cols:]
+        save_case(name, {"gate_up": gate_up, "y": ref(a, b)}, {"op": "swiglu"})
+
+
+def momoe_cases() -> None:
+    ref = KERNELS["momoe"].reference
+    for name, seed, batch, seq, hidden, inter, experts, top_k in [
+        ("momoe_f32_e8_k1", 40, 2, 12, 32, 16, 8, 1),
+        ("momoe_f32_e8_k2", 41, 2, 12, 32, 16, 8, 2),
+        ("momoe_f32_e8_k6", 42, 1, 20, 32, 16, 8, 6),
+        ("momoe_f32_e64_k8", 43, 1, 48, 16, 8, 64, 8),
+    ]:
+        gen = torch.Generator().manual_seed(seed)
+        # signature order: x, gate_weight, up_weight, down_weight, router_logits (momoe.py:34-41);
+        # weights are scaled by 1/sqrt(fan_in) as the reference's test_inputs do (momoe.py:26-30)
+        x = randn(gen, batch, seq, hidden)
+        gate_w = randn(gen, experts, hidden, inter) / hidden**0.5
+        up_w = randn(gen, experts, hidden, inter) / hidden**0.5
+        down_w = randn(gen, experts, inter, hidden) / inter**0.5
+        logits = randn(gen, batch, seq, experts)
+        y = ref(x, gate_w, up_w, down_w, logits, top_k)
+        # the routing lines on their own (momoe.py:47-49), for the route oracle
+        probs = torch.softmax(logits.float(), -1)
+        picked = probs.topk(top_k, -1)
+        gates = picked.values / picked.values.sum(-1, keepdim=True)
+        save_case(
+            name,
+            {"x": x, "gate_weight": gate_w, "up_weight": up_w, "down_weight": down_w, "router_logits": logits,
+             "y": y, "topk_indices": picked.indices.to(torch.int32), "topk_weights": gates},
+            {"op": "momoe", "top_k": top_k},
+        )
+
+
+def main() -> None:
+    torch.manual_seed(0)
+    rms_norm_cases()
+    add_rms_norm_cases()
+    rotary_cases()
+    swiglu_cases()
+    momoe_cases()
+    import popcorn
+
+    print("popcorn", getattr(popcorn, "__version__", "?"), "torch", torch.__version__)
+
+
+if __name__ == "__main__":
+    main()

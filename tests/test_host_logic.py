@@ -1,0 +1,158 @@
+"""Host-side behaviour that needs no GPU: the registry mirror, the popcorn plugin, input checks."""
+
+import importlib.util
+import os
+import sys
+import warnings
+from pathlib import Path
+
+import pytest
+import torch
+
+from popcorn_b200 import kernels, ops, registry, workloads
+
+
+def test_ops_refuse_cpu_tensors():
+    x = torch.randn(4, 8)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        ops.rms_norm(x, torch.ones(8))
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        ops.swiglu(x, x)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        ops.moe_route(x, 2)
+
+
+def test_missing_library_is_an_import_error(monkeypatch, tmp_path):
+    from popcorn_b200 import _lib
+
+    _lib.library.cache_clear()
+    monkeypatch.setattr(_lib, "LIBRARY_PATH", tmp_path / "nope.so")
+    with pytest.raises(ImportError, match="popcorn_b200.build"):
+        _lib.library()
+    _lib.library.cache_clear()
+
+
+def test_rows_view_keeps_strided_halves_in_place():
+    gate_up = torch.zeros(6, 32)
+    a, lda = ops._rows(gate_up[:, :16])
+    b, ldb = ops._rows(gate_up[:, 16:])
+    assert lda == ldb == 32 and a.data_ptr() == gate_up.data_ptr() and b.data_ptr() == gate_up.data_ptr() + 16 * 4
+    flat, ld = ops._rows(torch.zeros(2, 3, 8))
+    assert flat.shape == (6, 8) and ld == 8
+    copied, ld = ops._rows(torch.zeros(4, 8, 3).transpose(1, 2))  # last dim not contiguous -> packed copy
+    assert copied.is_contiguous() and ld == 8
+
+
+def test_mirror_registry_surface():
+    assert set(registry.KERNELS) >= {"rms_norm", "add_rms_norm", "rotary_embedding", "swiglu", "moe_route", "moe_permute", "moe_unpermute"}
+    op = kernels.rms_norm
+    assert op.available_backends() == ("b200",)
+    assert op.params == ("x", "weight", "bias", "eps")
+    with pytest.raises(registry.DispatchError, match="unknown backend"):
+        op["fla"]
+    with pytest.raises(ValueError, match="already registered"):
+        op.register("b200", source="popcorn_b200.ops.rms_norm")
+    with pytest.raises(ValueError, match="invalid backend name"):
+        op.register("Not Valid")
+
+
+def test_mirror_dispatch_forced_scoped_and_ordered():
+    calls = []
+
+    @registry.register_kernel(name="_test_scale")
+    def scale(x, factor=2.0):
+        """Multiply."""
+
+    try:
+        scale.register("first")(lambda x, factor: calls.append("first") or x * factor)
+        scale.register("second", predicate=lambda **kw: kw["factor"] != 3.0)(lambda x, factor: calls.append("second") or x * factor)
+        x = torch.ones(2)
+        assert torch.equal(scale(x), x * 2) and calls == ["first"]
+        assert torch.equal(scale(x, backend="second"), x * 2) and calls[-1] == "second"
+        assert torch.equal(scale["second"](x, 4.0), x * 4) and calls[-1] == "second"
+        with scale["second"] as scoped:
+            scoped(x)
+            assert calls[-1] == "second"
+        scale(x)
+        assert calls[-1] == "first"
+        with pytest.raises(registry.DispatchError, match="rejected call"):
+            scale(x, 3.0, backend="second")
+        with pytest.raises(TypeError, match="parameters must be exactly"):
+            scale.register("bad")(lambda x: x)
+        assert "bad" not in scale.available_backends()
+    finally:
+        del registry.KERNELS["_test_scale"]
+
+
+def test_forward_only_backend_declines_grad():
+    x = torch.ones(3, requires_grad=True)
+    with pytest.raises(registry.DispatchError, match="no backward implementation"):
+        kernels.swiglu(x, x, backend="b200")
+    with pytest.raises(registry.DispatchError, match="no registered backend"):
+        kernels.swiglu(x, x)
+
+
+def test_workload_shapes_and_bytes():
+    w = workloads.add_rms_norm_bf16(scale=1 / 1024)
+    assert w.inputs["x"].shape == (16, 8192) and w.inputs["x"].dtype == torch.bfloat16
+    assert w.algorithmic_bytes["add_rms_norm"] == 4 * 16 * 8192 * 2 + 8192 * 2
+    full = {"rms_norm_fp32": 134_234_112, "add_rms_norm_bf16": 1_073_758_208, "swiglu_bf16": 2_818_572_288}
+    # byte formulas at full size, without materialising the tensors
+    assert 2 * 4096 * 4096 * 4 + 4096 * 4 == full["rms_norm_fp32"]
+    assert 4 * 16384 * 8192 * 2 + 8192 * 2 == full["add_rms_norm_bf16"]
+    assert 3 * 32768 * 14336 * 2 == full["swiglu_bf16"]
+    m = workloads.moe_bf16(scale=1 / 256)
+    assert m.algorithmic_bytes["permute"] == 256 * 4096 * 2 + 2048 * 4096 * 2 + 2048 * 4
+    shard = m.shard(1, 2)
+    assert shard.tokens == 128 and shard.inputs["x"].shape[0] == 128
+    assert torch.equal(shard.inputs["x"], m.inputs["x"][128:])
+    r = workloads.rotary_bf16(scale=0.25, seq=64)
+    assert r.inputs["q"].shape == (2, 64, 32, 128) and r.inputs["cos"].shape == (64, 64)
+    assert r.shard(0, 2).inputs["q"].shape[0] == 1 and r.shard(0, 2).inputs["cos"].shape == (64, 64)
+
+
+REFERENCE_SRC = Path("/root/reference/src")
+HAVE_POPCORN = importlib.util.find_spec("popcorn") is not None or (REFERENCE_SRC / "popcorn").is_dir()
+
+
+@pytest.mark.skipif(not HAVE_POPCORN, reason="popcorn itself is not importable on this machine")
+def test_plugin_registers_on_real_popcorn(tmp_path, monkeypatch):
+    if importlib.util.find_spec("popcorn") is None:
+        monkeypatch.syspath_prepend(str(REFERENCE_SRC))
+    monkeypatch.setenv("POPCORN_CACHE_DIR", str(tmp_path))
+    warnings.filterwarnings("ignore")
+    import popcorn
+
+    from popcorn_b200 import plugin
+
+    served = plugin.register()
+    assert served == [*plugin.EXISTING_OPS, *plugin.NEW_OPS]
+    assert plugin.register() == served  # idempotent
+    for name in served:
+        op = popcorn.KERNELS[name]
+        assert "b200" in op.available_backends()
+        assert op["b200"].forward_only
+    # existing ops keep the reference last and their other backends intact
+    assert popcorn.KERNELS["swiglu"].available_backends()[-1] == "torch"
+    # popcorn resolves the bare source and checks it against the reference signature
+    impl = popcorn.KERNELS["add_rms_norm"]["b200"]
+    impl._prepare()
+    assert impl.source_fn is ops.add_rms_norm
+    # CPU calls are declined by the predicate rather than served by a fallback
+    x = torch.randn(4, 8)
+    with pytest.raises(popcorn.core.errors.DispatchError, match="rejected"):
+        popcorn.KERNELS["swiglu"](x, x, backend="b200")
+    # unforced CPU calls still reach popcorn's own torch reference
+    assert torch.equal(popcorn.KERNELS["swiglu"](x, x), torch.nn.functional.silu(x) * x)
+    # the new ops' torch definitions agree with the oracle
+    from oracle import reference_ops as oracle
+
+    logits = torch.randn(32, 8, generator=torch.Generator().manual_seed(3))
+    idx, w = popcorn.KERNELS["moe_route"].reference(logits, 2)
+    oidx, ow = oracle.moe_route(logits, 2)
+    assert torch.equal(idx, oidx) and torch.equal(w, ow)
+    got = popcorn.KERNELS["moe_permute"].reference(x.repeat(8, 1), idx, 8)
+    want = oracle.moe_permute(x.repeat(8, 1), oidx, 8)
+    assert all(torch.equal(g, w_) for g, w_ in zip(got, want))
+    y = popcorn.KERNELS["moe_unpermute"].reference(want[0], ow, want[4])
+    torch.testing.assert_close(y, oracle.moe_unpermute(want[0], ow, want[4]), rtol=1e-5, atol=1e-6)

@@ -1,0 +1,111 @@
+"""The CPU oracle against golden vectors produced by the real popcorn references.
+
+The fixtures were written by tests/golden/make_golden.py, which imports popcorn
+and calls KERNELS[op].reference on CPU.  Floating-point outputs must agree to
+within one unit in the last place of the output dtype (they are bit-identical on
+the machine that generated them; a host with another SIMD width may order the
+row sums of the norms differently); integer outputs must be equal.
+"""
+
+import pytest
+import torch
+
+from oracle import reference_ops as oracle
+from tests.golden.golden_io import case_names, load_case
+
+ULP = {torch.float32: 2.0**-23, torch.float16: 2.0**-10, torch.bfloat16: 2.0**-7}
+
+
+def assert_close_ulps(got, want, ulps=1.0):
+    assert got.dtype == want.dtype and got.shape == want.shape
+    g, w = got.double(), want.double()
+    tol = ulps * ULP[want.dtype] * w.abs().clamp_min(2.0**-20)
+    bad = (g - w).abs() > tol
+    assert not bad.any(), f"{int(bad.sum())} of {bad.numel()} elements differ by more than {ulps} ulp"
+
+
+def names(prefix):
+    found = [n for n in case_names() if n.startswith(prefix)]
+    assert found, f"no golden case named {prefix}*"
+    return found
+
+
+@pytest.mark.parametrize("name", names("rms_norm"))
+def test_rms_norm(name):
+    t, meta = load_case(name)
+    assert_close_ulps(oracle.rms_norm(t["x"], t["weight"], t.get("bias"), meta["eps"]), t["y"])
+
+
+@pytest.mark.parametrize("name", names("add_rms_norm"))
+def test_add_rms_norm(name):
+    t, meta = load_case(name)
+    y, s = oracle.add_rms_norm(t["x"], t["residual"], t["weight"], meta["eps"], meta["offset"])
+    assert torch.equal(s, t["s"])
+    assert_close_ulps(y, t["y"])
+
+
+@pytest.mark.parametrize("name", names("rope"))
+def test_rotary_embedding(name):
+    t, meta = load_case(name)
+    assert torch.equal(oracle.rotary_embedding(t["x"], t["cos"], t["sin"], meta["interleaved"]), t["y"])
+
+
+@pytest.mark.parametrize("name", names("swiglu"))
+def test_swiglu(name):
+    t, _ = load_case(name)
+    cols = t["gate_up"].shape[1] // 2
+    assert_close_ulps(oracle.swiglu(t["gate_up"][:, :cols], t["gate_up"][:, cols:]), t["y"])
+
+
+@pytest.mark.parametrize("name", names("momoe"))
+def test_route(name):
+    t, meta = load_case(name)
+    logits = t["router_logits"]
+    assert oracle.route_is_unambiguous(logits, meta["top_k"])
+    indices, weights = oracle.moe_route(logits, meta["top_k"])
+    assert torch.equal(indices, t["topk_indices"])
+    assert_close_ulps(weights, t["topk_weights"], ulps=2)
+
+
+@pytest.mark.parametrize("name", names("momoe"))
+def test_route_permute_unpermute_chain_reproduces_momoe(name):
+    """route -> permute -> expert MLPs -> unpermute equals the registered momoe reference."""
+    t, meta = load_case(name)
+    y = oracle.momoe_from_steps(t["x"], t["gate_weight"], t["up_weight"], t["down_weight"], t["router_logits"], meta["top_k"])
+    # fp32 matmuls summed in a different order than the reference's einsum
+    torch.testing.assert_close(y, t["y"], rtol=1e-4, atol=1e-5)
+
+
+def test_index_is_a_stable_sort_by_expert():
+    gen = torch.Generator().manual_seed(7)
+    tokens, top_k, experts = 97, 4, 11
+    indices = torch.stack([torch.randperm(experts, generator=gen)[:top_k] for _ in range(tokens)]).to(torch.int32)
+    counts, offsets, perm, pos = oracle.moe_index(indices, experts)
+    assert int(counts.sum()) == tokens * top_k and int(offsets[-1]) == tokens * top_k
+    assert torch.equal(offsets[1:] - offsets[:-1], counts)
+    flat = indices.reshape(-1)
+    for e in range(experts):
+        lo, hi = int(offsets[e]), int(offsets[e + 1])
+        expect = torch.nonzero((indices == e).any(dim=1)).reshape(-1).to(torch.int32)
+        assert torch.equal(perm[lo:hi], expect)  # ascending token ids: the reference's col_idx
+    assert torch.equal(perm[pos.reshape(-1).long()], torch.arange(tokens).repeat_interleave(top_k).to(torch.int32))
+    assert torch.equal(flat[(pos.reshape(-1).argsort())], flat.sort(stable=True).values)
+
+
+def test_unpermute_matches_einsum():
+    """The fixed summation order stays within fp32 rounding of the reference's einsum (momoe.py:53)."""
+    gen = torch.Generator().manual_seed(8)
+    tokens, top_k, experts, hidden = 50, 3, 6, 24
+    x = torch.randn(tokens, hidden, generator=gen)
+    logits = torch.randn(tokens, experts, generator=gen)
+    indices, weights = oracle.moe_route(logits, top_k)
+    rows, _, _, _, pos = oracle.moe_permute(x, indices, experts)
+    rows = rows * 1.5
+    y = oracle.moe_unpermute(rows, weights, pos)
+    dense = torch.zeros(tokens, experts, hidden)
+    gates = torch.zeros(tokens, experts)
+    for t in range(tokens):
+        for k in range(top_k):
+            dense[t, indices[t, k]] = rows[pos[t, k]]
+            gates[t, indices[t, k]] = weights[t, k]
+    torch.testing.assert_close(y, torch.einsum("ted,te->td", dense, gates), rtol=1e-5, atol=1e-6)
