@@ -186,18 +186,20 @@ def steps_for(nbytes: int, target_s: float = 0.4, lo: int = 20, hi: int = 2000) 
     return max(lo, min(hi, int(target_s / (nbytes / 6.0e12))))
 
 
-def bench_single_kernel_ops(device, peak_gbs: float, sampler: ClockSampler, which: list[str]) -> dict:
+def bench_single_kernel_ops(device, peak_gbs: float, sampler, which: list[str], scale: float = 1.0,
+                            steps: int | None = None, warmup: int = 5) -> dict:
     from popcorn_b200 import workloads
 
     out = {}
     for key in which:
-        w = workloads.CONFIGS[key]()
+        w = workloads.CONFIGS[key](scale=scale)
         nbytes = sum(w.algorithmic_bytes.values())
         run, nsets = make_runner(w, device)
-        steps = steps_for(nbytes)
+        steps = steps or steps_for(nbytes)
         t0 = time.time()
-        ms = time_launches(run, steps, 5, device)
-        sampler.mark(t0, time.time())
+        ms = time_launches(run, steps, warmup, device)
+        if sampler is not None:
+            sampler.mark(t0, time.time())
         gbs = nbytes / (ms * 1e-3) / 1e9
         out[key] = {"ms": round(ms, 5), "gb_s": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak_gbs, 4),
                     "frac_of_8tbs": round(gbs / SPEC_HBM_GBS, 4), "tokens_per_s": round(w.tokens / (ms * 1e-3), 1),
@@ -207,11 +209,11 @@ def bench_single_kernel_ops(device, peak_gbs: float, sampler: ClockSampler, whic
     return out
 
 
-def bench_moe(device, peak_gbs: float, sampler: ClockSampler) -> dict:
+def bench_moe(device, peak_gbs: float, sampler, scale: float = 1.0, fixed_steps: int | None = None, warmup: int = 3) -> dict:
     """Config 5 phase by phase: route, index (3 small kernels), permute, unpermute."""
     from popcorn_b200 import ops, workloads
 
-    w = workloads.moe_bf16()
+    w = workloads.moe_bf16(scale=scale)
     x, logits = w.inputs["x"].to(device), w.inputs["router_logits"].to(device)
     experts, top_k = w.args["experts"], w.args["top_k"]
     idx, wts = ops.moe_route(logits, top_k)
@@ -236,10 +238,11 @@ def bench_moe(device, peak_gbs: float, sampler: ClockSampler) -> dict:
     total_ms = 0.0
     for name, run in phases.items():
         nbytes = w.algorithmic_bytes[name]
-        steps = steps_for(nbytes, hi=300)
+        steps = fixed_steps or steps_for(nbytes, hi=300)
         t0 = time.time()
-        ms = time_launches(run, steps, 3, device)
-        sampler.mark(t0, time.time())
+        ms = time_launches(run, steps, warmup, device)
+        if sampler is not None:
+            sampler.mark(t0, time.time())
         total_ms += ms
         gbs = nbytes / (ms * 1e-3) / 1e9
         out[name] = {"ms": round(ms, 5), "gb_s": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak_gbs, 4),
@@ -328,7 +331,9 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", choices=["b200", "reference"], default="b200")
     parser.add_argument("--skip-per-op", action="store_true", help="only the headline loop (used for profiling captures)")
-    parser.add_argument("--scale", type=float, default=1.0, help="shrink the headline token count (profiling captures only)")
+    parser.add_argument("--scale", type=float, default=1.0, help="shrink the token count (profiling captures only)")
+    parser.add_argument("--only", choices=["rms_norm_fp32", "add_rms_norm_bf16", "rotary_bf16", "swiglu_bf16", "moe_bf16"],
+                        help="time one configuration's kernels alone and print a short JSON (profiling captures)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -353,6 +358,13 @@ def main() -> None:
 
     build.build()
     peak_gbs, peak_kind = measured_peak()
+    if args.only:
+        if args.only == "moe_bf16":
+            result = bench_moe(device, peak_gbs, None, args.scale, args.steps, args.warmup)
+        else:
+            result = bench_single_kernel_ops(device, peak_gbs, None, [args.only], args.scale, args.steps, args.warmup)[args.only]
+        print(json.dumps({"only": args.only, "scale": args.scale, "steps": args.steps, **result}), flush=True)
+        return
     sampler = ClockSampler(local) if rank == 0 else None
 
     # ---- headline: add_rms_norm bf16, device-resident inputs, exactly K timed steps

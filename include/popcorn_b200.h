@@ -64,6 +64,14 @@ const char* b200_last_error(void);
 uint64_t b200_launch_count(void);
 
 /*
+ * Diagnostic: how many bounded waits on an asynchronous copy ran out on the
+ * current device since the library was loaded (a kernel whose wait runs out
+ * takes a slower path with ordinary loads; results stay correct).  Expected
+ * value: 0.  Unlike every other entry point this one synchronises the device.
+ */
+uint64_t b200_wait_timeouts(void);
+
+/*
  * y = round_T(x * rsqrt(mean(x^2) + eps)) * weight (+ bias)
  *
  * Replaces rms_norm(x, weight, bias=None, eps=1e-6), src/popcorn/kernels/rms_norm.py:16-30,

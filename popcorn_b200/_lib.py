@@ -30,6 +30,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "b200_status_string": (ctypes.c_char_p, [_int]),
     "b200_last_error": (ctypes.c_char_p, []),
     "b200_launch_count": (ctypes.c_uint64, []),
+    "b200_wait_timeouts": (ctypes.c_uint64, []),
     "b200_rms_norm": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _int, _dbl, _ptr]),
     "b200_add_rms_norm": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _int, _dbl, _dbl, _ptr]),
     "b200_rope": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _ptr]),
@@ -87,3 +88,8 @@ def call(name: str, *args: object) -> None:
 
 def launch_count() -> int:
     return int(library().b200_launch_count())
+
+
+def wait_timeouts() -> int:
+    """Bounded waits that ran out on the current device (0 unless a copy never landed); synchronises."""
+    return int(library().b200_wait_timeouts())

@@ -25,6 +25,8 @@ int after_launch(const char* kernel);
 int check_device();
 // Number of SMs of the current device (cached per device).
 int sm_count();
+// Bounded waits that ran out, per source file that uses bulk asynchronous copies.
+unsigned int rope_wait_timeouts();
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 inline size_t dtype_size(int dtype) { return dtype == B200_F32 ? 4 : 2; }
@@ -50,6 +52,7 @@ struct Num<float> {
   static __device__ __forceinline__ float down(float v) { return v; }
   // round-trip through the storage type: identity for fp32
   static __device__ __forceinline__ float rt(float v) { return v; }
+  static __device__ __forceinline__ void round2(float&, float&) {}
   static __device__ __forceinline__ void unpack(const uint4& v, float (&f)[4]) {
     f[0] = __uint_as_float(v.x);
     f[1] = __uint_as_float(v.y);
@@ -76,6 +79,10 @@ struct Num<__nv_bfloat16> {
     __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&p);
   }
+  // Round two fp32 values to bf16 and back with ONE packed conversion. The scalar
+  // cvt.rn.bf16.f32 issues on the quarter-rate conversion pipe and made kernels
+  // that round per element pipe-bound; the packed form does not.
+  static __device__ __forceinline__ void round2(float& a, float& b) { unpack2(pack2(a, b), a, b); }
   static __device__ __forceinline__ void unpack(const uint4& v, float (&f)[8]) {
     unpack2(v.x, f[0], f[1]);
     unpack2(v.y, f[2], f[3]);
@@ -102,6 +109,7 @@ struct Num<__half> {
     __half2 p = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&p);
   }
+  static __device__ __forceinline__ void round2(float& a, float& b) { unpack2(pack2(a, b), a, b); }
   static __device__ __forceinline__ void unpack(const uint4& v, float (&f)[8]) {
     unpack2(v.x, f[0], f[1]);
     unpack2(v.y, f[2], f[3]);

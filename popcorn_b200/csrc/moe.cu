@@ -9,6 +9,8 @@
 // Bound: HBM for permute / gather / unpermute (pure row traffic, 128-bit
 // accesses, a warp moves 512 contiguous bytes per step); route and index move
 // only a few MB and are latency-bound.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -29,9 +31,24 @@ __device__ __forceinline__ float logit_to_float<__half>(const __half* p, int64_t
 template <>
 __device__ __forceinline__ float logit_to_float<__nv_bfloat16>(const __nv_bfloat16* p, int64_t i) { return __bfloat162float(p[i]); }
 
-// One warp per token; lane l holds experts l, l + 32, ... (NPL of them).
-// Selection runs on the logits (exp and the shared denominator are monotone, so
-// the order is that of the probabilities) with ties going to the lower index.
+// Monotone map fp32 -> u32 (larger float, larger key); NaN maps to 0 and never wins.
+__device__ __forceinline__ uint32_t order_key(float v) {
+  const uint32_t u = __float_as_uint(v);
+  if (v != v) return 0u;
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_value(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+// One warp per token; lane l holds experts l, l + 32, ... (NPL of them) as
+// order-preserving integer keys.  Each of the top_k rounds is two warp-wide
+// integer reductions (redux.sync): the largest key, then the lowest expert index
+// holding it.  Selection runs on the logits: exp and the shared softmax
+// denominator are monotone, so this is the order of the probabilities, with ties
+// going to the lower index.  The softmax denominator cancels in
+// picked / sum(picked), so the weights are exp(l_k - l_top) / sum_j exp(l_j - l_top)
+// over the picked logits.
 template <typename L, int NPL>
 __global__ void __launch_bounds__(256)
 route_kernel(const L* __restrict__ logits, int32_t* __restrict__ indices, float* __restrict__ weights,
@@ -39,75 +56,45 @@ route_kernel(const L* __restrict__ logits, int32_t* __restrict__ indices, float*
   const int lane = threadIdx.x & 31;
   const int64_t warps = static_cast<int64_t>(gridDim.x) * 8;
   for (int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); t < tokens; t += warps) {
-    float v[NPL];
-    float m = -INFINITY;
+    uint32_t key[NPL];
 #pragma unroll
     for (int i = 0; i < NPL; ++i) {
       const int e = lane + 32 * i;
-      v[i] = e < experts ? logit_to_float<L>(logits, t * ld + e) : -INFINITY;
-      m = fmaxf(m, v[i]);
+      key[i] = e < experts ? order_key(logit_to_float<L>(logits, t * ld + e)) : 0u;
     }
+    uint32_t taken = 0;  // bit i: my i-th expert is picked (or does not exist)
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(kFull, m, o));
-    float p[NPL];
-    float part = 0.f;
-#pragma unroll
-    for (int i = 0; i < NPL; ++i) {
-      p[i] = lane + 32 * i < experts ? expf(__fsub_rn(v[i], m)) : 0.f;
-      part = __fadd_rn(part, p[i]);
-    }
-    const float denom = warp_sum(part);
+    for (int i = 0; i < NPL; ++i)
+      if (lane + 32 * i >= experts) taken |= 1u << i;
 
-    unsigned taken = 0;  // bit i: my i-th expert is already picked
-    float my_prob = 0.f;
+    uint32_t my_key = 0;
     int my_idx = 0;
-    float picked_sum = 0.f;
     for (int k = 0; k < top_k; ++k) {
-      float best = -INFINITY;
-      int best_e = 0x7fffffff;
+      uint32_t best = 0;
       int best_i = -1;
 #pragma unroll
       for (int i = 0; i < NPL; ++i) {
-        const int e = lane + 32 * i;
-        const bool free_slot = e < experts && !((taken >> i) & 1u);
-        // a NaN logit never wins a comparison; -inf loses to everything but ties by index
-        if (free_slot && (best_i < 0 || v[i] > best)) {
-          best = v[i];
-          best_e = e;
+        const bool free_slot = !((taken >> i) & 1u);
+        if (free_slot && (best_i < 0 || key[i] > best)) {
+          best = key[i];
           best_i = i;
         }
       }
-      float wv = best;
-      int we = best_e;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(kFull, wv, o);
-        const int oe = __shfl_xor_sync(kFull, we, o);
-        const bool other_wins = (oe != 0x7fffffff) && (we == 0x7fffffff || ov > wv || (ov == wv && oe < we) || (wv != wv && ov == ov));
-        if (other_wins) {
-          wv = ov;
-          we = oe;
-        }
-      }
-      // the owner of expert `we` marks it and publishes its probability
-      const bool mine = best_i >= 0 && best_e == we;
-      float prob = 0.f;
-      if (mine) {
-        taken |= 1u << best_i;
-#pragma unroll
-        for (int i = 0; i < NPL; ++i)
-          if (i == best_i) prob = __fdiv_rn(p[i], denom);
-      }
-      prob = __shfl_sync(kFull, prob, we & 31);
-      picked_sum = __fadd_rn(picked_sum, prob);
+      const uint32_t top = __reduce_max_sync(kFull, best_i >= 0 ? best : 0u);
+      const uint32_t cand = (best_i >= 0 && best == top) ? static_cast<uint32_t>(lane + 32 * best_i) : 0xffffffffu;
+      const uint32_t who = __reduce_min_sync(kFull, cand);
+      if (best_i >= 0 && cand == who) taken |= 1u << best_i;
       if (lane == k) {
-        my_prob = prob;
-        my_idx = we;
+        my_key = top;
+        my_idx = static_cast<int>(who);
       }
     }
+    const float top_logit = key_value(__shfl_sync(kFull, my_key, 0));
+    const float p = lane < top_k ? expf(__fsub_rn(key_value(my_key), top_logit)) : 0.f;
+    const float denom = warp_sum(p);
     if (lane < top_k) {
       indices[t * top_k + lane] = my_idx;
-      weights[t * top_k + lane] = __fdiv_rn(my_prob, picked_sum);
+      weights[t * top_k + lane] = __fdiv_rn(p, denom);
     }
   }
 }
@@ -267,7 +254,8 @@ template <>
 __device__ __forceinline__ void st_word<uint4>(uint4* p, const uint4& v) { st_stream(p, v); }
 
 // One warp per token: read the row once (UNROLL words per lane at a time) and
-// write it to each of its top_k destinations.
+// write it to each of its top_k destinations.  Loop bounds are the same for all
+// lanes of a warp, because the destinations travel by shuffle.
 template <typename W>
 __global__ void __launch_bounds__(256)
 permute_kernel(const W* __restrict__ x, const int32_t* __restrict__ pos, W* __restrict__ rows,
@@ -275,21 +263,21 @@ permute_kernel(const W* __restrict__ x, const int32_t* __restrict__ pos, W* __re
   constexpr int UNROLL = 4;
   const int lane = threadIdx.x & 31;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-  if (t >= tokens) return;
+  if (t >= tokens) return;  // whole warps leave together
   const int my_dst = lane < top_k ? pos[t * top_k + lane] : -1;
   const W* src = x + t * ldx;
-  for (int w0 = lane; w0 < words; w0 += 32 * UNROLL) {
+  for (int w0 = 0; w0 < words; w0 += 32 * UNROLL) {
     W v[UNROLL];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u)
-      if (w0 + 32 * u < words) v[u] = ld_word<W>(src + w0 + 32 * u);
+      if (w0 + lane + 32 * u < words) v[u] = ld_word<W>(src + w0 + lane + 32 * u);
     for (int k = 0; k < top_k; ++k) {
       const int dst = __shfl_sync(kFull, my_dst, k);
       if (dst < 0) continue;
       W* out = rows + static_cast<int64_t>(dst) * ldrows;
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u)
-        if (w0 + 32 * u < words) st_word<W>(out + w0 + 32 * u, v[u]);
+        if (w0 + lane + 32 * u < words) st_word<W>(out + w0 + lane + 32 * u, v[u]);
     }
   }
 }
@@ -321,16 +309,23 @@ gather_kernel(const W* __restrict__ x, const int32_t* __restrict__ src_row, W* _
 // -------------------------------------------------------------- unpermute --
 
 // One warp per token.  Lanes < top_k hold (pos, weight); the slots are visited
-// in ascending pos, which is ascending expert index.  VEC: 128-bit words.
+// in ascending pos, which is ascending expert index.  The sorted row offsets and
+// weights sit in shared memory (one line per warp).  Rows are fetched eight at a
+// time, one 128-bit word per lane, and the NEXT batch of eight is already in
+// flight while the current one is accumulated.  VEC: 128-bit words.
 template <typename T, bool VEC>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 unpermute_kernel(const T* __restrict__ rows, const float* __restrict__ weights, const int32_t* __restrict__ pos,
                  T* __restrict__ y, int64_t tokens, int top_k, int hidden, int64_t ldrows, int64_t ldy) {
   constexpr int V = VEC ? Num<T>::kVec : 1;
-  constexpr int KB = 8;  // slots fetched together
+  constexpr int KB = 8;  // rows fetched together
+  using Word = typename std::conditional<VEC, uint4, T>::type;
+  __shared__ int64_t s_off[8][kMaxTopK];
+  __shared__ float s_w[8][kMaxTopK];
   const int lane = threadIdx.x & 31;
-  const int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-  if (t >= tokens) return;
+  const int wid = threadIdx.x >> 5;
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + wid;
+  if (t >= tokens) return;  // whole warps leave together; no block-wide barrier below
   int my_pos = -1;
   float my_w = 0.f;
   if (lane < top_k) {
@@ -347,57 +342,79 @@ unpermute_kernel(const T* __restrict__ rows, const float* __restrict__ weights, 
       if (pj < my_pos || (pj == my_pos && j < lane)) ++rank;
     }
   }
-  if (my_pos < 0) rank = -1;
-  // ord_pos / ord_w: lane r holds the r-th slot in visiting order
-  int ord_pos = -1;
-  float ord_w = 0.f;
-  for (int r = 0; r < valid; ++r) {
-    const unsigned who = __ballot_sync(kFull, rank == r);
-    const int src = __ffs(who) - 1;
-    const int pp = __shfl_sync(kFull, my_pos, src);
-    const float ww = __shfl_sync(kFull, my_w, src);
-    if (lane == r) {
-      ord_pos = pp;
-      ord_w = ww;
-    }
+  if (my_pos >= 0) {
+    s_off[wid][rank] = static_cast<int64_t>(my_pos) * ldrows;
+    s_w[wid][rank] = my_w;
   }
+  __syncwarp();
+
   const int words = hidden / V;
+  const int steps = (words + 31) / 32;
+  const int nb = (valid + KB - 1) / KB;
+  const int total = steps * nb;
   T* out = y + t * ldy;
-  for (int w = lane; w < words; w += 32) {
-    float acc[V];
+  float acc[V];
+
+  auto fetch = [&](Word (&buf)[KB], int item) {
+    const int step = nb == 1 ? item : item / nb;
+    const int b = item - step * nb;
+    const int w = step * 32 + lane;
 #pragma unroll
-    for (int j = 0; j < V; ++j) acc[j] = 0.f;
-    for (int k0 = 0; k0 < valid; k0 += KB) {
-      uint4 v[KB];
-      T sv[KB];
-#pragma unroll
-      for (int k = 0; k < KB; ++k) {
-        const int pp = __shfl_sync(kFull, ord_pos, (k0 + k) & 31);
-        if (k0 + k < valid) {
-          const T* src = rows + static_cast<int64_t>(pp) * ldrows + static_cast<int64_t>(w) * V;
-          if constexpr (VEC) v[k] = ld_stream(src);
-          else sv[k] = *src;
-        }
+    for (int k = 0; k < KB; ++k) {
+      const int kk = b * KB + k;
+      if (kk < valid && w < words) {
+        const T* src = rows + s_off[wid][kk] + static_cast<int64_t>(w) * V;
+        if constexpr (VEC) buf[k] = ld_stream(src);
+        else buf[k] = *src;
       }
+    }
+  };
+  auto reduce = [&](const Word (&buf)[KB], int item) {
+    const int step = nb == 1 ? item : item / nb;
+    const int b = item - step * nb;
+    const int w = step * 32 + lane;
+    if (b == 0) {
 #pragma unroll
-      for (int k = 0; k < KB; ++k) {
-        const float ww = __shfl_sync(kFull, ord_w, (k0 + k) & 31);
-        if (k0 + k < valid) {
-          if constexpr (VEC) {
-            float f[V];
-            Num<T>::unpack(v[k], f);
+      for (int j = 0; j < V; ++j) acc[j] = 0.f;
+    }
 #pragma unroll
-            for (int j = 0; j < V; ++j) acc[j] = __fadd_rn(acc[j], __fmul_rn(ww, f[j]));
-          } else {
-            acc[0] = __fadd_rn(acc[0], __fmul_rn(ww, Num<T>::up(sv[k])));
-          }
+    for (int k = 0; k < KB; ++k) {
+      const int kk = b * KB + k;
+      if (kk < valid && w < words) {
+        const float ww = s_w[wid][kk];
+        if constexpr (VEC) {
+          float f[V];
+          Num<T>::unpack(buf[k], f);
+#pragma unroll
+          for (int j = 0; j < V; ++j) acc[j] = __fadd_rn(acc[j], __fmul_rn(ww, f[j]));
+        } else {
+          acc[0] = __fadd_rn(acc[0], __fmul_rn(ww, Num<T>::up(buf[k])));
         }
       }
     }
-    if constexpr (VEC) {
-      st_stream(out + static_cast<int64_t>(w) * V, Num<T>::pack(acc));
-    } else {
-      out[w] = Num<T>::down(acc[0]);
+    if (b == nb - 1 && w < words) {
+      if constexpr (VEC) st_stream(out + static_cast<int64_t>(w) * V, Num<T>::pack(acc));
+      else out[w] = Num<T>::down(acc[0]);
+    }
+  };
+
+  if (total == 0) {  // no valid slot: the row is zero
+    for (int w = lane; w < words; w += 32) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] = 0.f;
+      if constexpr (VEC) st_stream(out + static_cast<int64_t>(w) * V, Num<T>::pack(acc));
+      else out[w] = Num<T>::down(0.f);
+    }
+    return;
+  }
+  Word a[KB], b[KB];
+  fetch(a, 0);
+  for (int i = 0; i < total; i += 2) {
+    if (i + 1 < total) fetch(b, i + 1);
+    reduce(a, i);
+    if (i + 1 < total) {
+      if (i + 2 < total) fetch(a, i + 2);
+      reduce(b, i + 1);
     }
   }
 }

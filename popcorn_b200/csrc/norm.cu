@@ -29,6 +29,22 @@ __device__ __forceinline__ float scale_one(float h, float r, float w, float b, b
   return y;
 }
 
+// The same for two neighbouring elements, rounding them pairwise (h0, h1 in, y0, y1 out).
+// The LAST rounding to T is left to the caller's pack.
+template <typename T>
+__device__ __forceinline__ void scale_two(float& h0, float& h1, float r, float w0, float w1, float b0, float b1, bool has_bias) {
+  h0 = __fmul_rn(h0, r);
+  h1 = __fmul_rn(h1, r);
+  Num<T>::round2(h0, h1);
+  h0 = __fmul_rn(h0, w0);
+  h1 = __fmul_rn(h1, w1);
+  if (has_bias) {
+    Num<T>::round2(h0, h1);
+    h0 = __fadd_rn(h0, b0);
+    h1 = __fadd_rn(h1, b1);
+  }
+}
+
 // One row per group of TPR threads, ITEMS 128-bit words per thread, the row held
 // in registers.  THREADS / TPR rows per CTA.  ADD selects add_rms_norm.
 template <typename T, int TPR, int ITEMS, bool ADD>
@@ -75,8 +91,9 @@ rms_rows_kernel(const T* x, const T* res, const T* __restrict__ weight,
       float g[V];
       Num<T>::unpack(rdata[i], g);
 #pragma unroll
-      for (int j = 0; j < V; ++j) f[j] = Num<T>::rt(__fadd_rn(f[j], g[j]));
-      data[i] = Num<T>::pack(f);  // s, already rounded to T
+      for (int j = 0; j < V; ++j) f[j] = __fadd_rn(f[j], g[j]);
+      data[i] = Num<T>::pack(f);  // s = x + residual, rounded to T by the pack
+      Num<T>::unpack(data[i], f);
       if (ok[i]) st_stream(s_out + row * lds + static_cast<int64_t>(lane_in_row + i * TPR) * V, data[i]);
     }
 #pragma unroll
@@ -111,11 +128,16 @@ rms_rows_kernel(const T* x, const T* res, const T* __restrict__ weight,
 #pragma unroll
       for (int j = 0; j < V; ++j) b[j] = 0.f;
     }
+    if constexpr (ADD) {
 #pragma unroll
-    for (int j = 0; j < V; ++j) {
-      float wj = ADD ? Num<T>::rt(__fadd_rn(w[j], offset)) : w[j];
-      f[j] = scale_one<T>(f[j], r, wj, b[j], has_bias);
+      for (int j = 0; j < V; j += 2) {
+        w[j] = __fadd_rn(w[j], offset);
+        w[j + 1] = __fadd_rn(w[j + 1], offset);
+        Num<T>::round2(w[j], w[j + 1]);
+      }
     }
+#pragma unroll
+    for (int j = 0; j < V; j += 2) scale_two<T>(f[j], f[j + 1], r, w[j], w[j + 1], b[j], b[j + 1], has_bias);
     st_stream(y + row * ldy + col, Num<T>::pack(f));
   }
 }

@@ -1,15 +1,15 @@
 // Rotary position embedding (GPT-NeoX halves or GPT-J pairs) for sm_100a.
 //
 // Bound: HBM (each element of q / k read once and written once; the fp32
-// cos/sin table is small and stays in L2).  One warp owns one sequence
-// position: it keeps that position's cos/sin values in registers and walks
-// over the heads of q and, in the fused entry point, k, for one or more batch
-// entries.  The eight warps of a CTA share a position and differ in batch, so
-// the cos/sin row is pulled into L1 once per CTA.
+// cos/sin table is small and stays in L2).  A CTA owns a tile of consecutive
+// sequence positions: the tile's cos/sin rows are staged in shared memory by
+// bulk asynchronous copies, and each thread rotates one fixed (head, channel
+// group) of q or k over the tile's positions, for one or more batch entries.
 //
 // Arithmetic follows src/popcorn/kernels/rotary_embedding.py:28-40 of the
 // reference: fp32 products and sums rounded one by one, one final rounding.
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace b200 {
 namespace {
@@ -63,100 +63,171 @@ __device__ __forceinline__ void load_cs(const CS* p, float (&f)[N]) {
   }
 }
 
+// The same from shared memory.
+template <typename CS, int N>
+__device__ __forceinline__ void load_cs_shared(const CS* p, float (&f)[N]) {
+  if constexpr (sizeof(CS) == 4) {
+    if constexpr (N == 2) {
+      const float2 v = *reinterpret_cast<const float2*>(p);
+      f[0] = v.x;
+      f[1] = v.y;
+    } else {
+#pragma unroll
+      for (int i = 0; i < N / 4; ++i) {
+        const float4 v = *reinterpret_cast<const float4*>(p + 4 * i);
+        f[4 * i] = v.x;
+        f[4 * i + 1] = v.y;
+        f[4 * i + 2] = v.z;
+        f[4 * i + 3] = v.w;
+      }
+    }
+  } else {
+    if constexpr (N == 4) {
+      const uint2 v = *reinterpret_cast<const uint2*>(p);
+      Num<CS>::unpack2(v.x, f[0], f[1]);
+      Num<CS>::unpack2(v.y, f[2], f[3]);
+    } else {
+      static_assert(N == 8, "16-bit cos/sin come in groups of 4 or 8");
+      Num<CS>::unpack(*reinterpret_cast<const uint4*>(p), f);
+    }
+  }
+}
+
 __device__ __forceinline__ void rotate(float x1, float x2, float c, float s, float& y1, float& y2) {
   y1 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s));
   y2 = __fadd_rn(__fmul_rn(x1, s), __fmul_rn(x2, c));
 }
 
-// A "unit" is the smallest piece one lane rotates on its own:
+// A "unit" is the smallest piece one thread rotates on its own:
 //   NeoX:        one 128-bit word of the first half plus its partner in the second half
 //   interleaved: one 128-bit word (V/2 adjacent pairs)
-// FIXED: 32 is a multiple of the units per head, so a lane meets the same
-// channel group at every step and loads its cos/sin once.
-template <typename T, typename CS, bool INTERLEAVED, bool FIXED>
-__global__ void __launch_bounds__(256) rope_warp_kernel(const RopeArgs p) {
+// A position of q and k together holds units_per_pos = (q_heads + k_heads) * units_per_head
+// of them.  A CTA is laid out as `groups` x `tpp` threads: thread (g, r) owns unit r
+// (and r + tpp, ... if a position has more units than tpp) of the TS consecutive
+// positions of group g, so its head, channel group and tensor are fixed and found
+// once.  The CTA's cos/sin rows (groups * TS positions, contiguous in the table)
+// are staged in shared memory by two bulk asynchronous copies while the first
+// loads of x are already in flight.
+constexpr int kRopeTS = 4;
+
+template <typename T, typename CS, bool INTERLEAVED>
+__global__ void __launch_bounds__(512, 2) rope_tile_kernel(const RopeArgs p, int tpp, int groups) {
   constexpr int V = Num<T>::kVec;
   constexpr int NCS = INTERLEAVED ? V / 2 : V;  // cos values per unit
-  constexpr int UNROLL = 4;
-  const int lane = threadIdx.x & 31;
-  const int64_t warp = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-  const int64_t pos = warp / p.batch_split;
-  const int split = static_cast<int>(warp - pos * p.batch_split);
-  if (pos >= p.seq) return;
+  constexpr int TS = kRopeTS;
+  extern __shared__ __align__(16) unsigned char rope_smem[];
+  __shared__ __align__(8) uint64_t bar;
 
-  const int uph = (INTERLEAVED ? 2 * p.half : p.half) / V;  // units per head
-  const CS* cos_row = static_cast<const CS*>(p.cos) + pos * p.half;
-  const CS* sin_row = static_cast<const CS*>(p.sin) + pos * p.half;
-  float c[NCS], s[NCS];
-  if (FIXED) {
-    const int g = lane % uph;
-    load_cs<CS, NCS>(cos_row + g * NCS, c);
-    load_cs<CS, NCS>(sin_row + g * NCS, s);
+  const int tile_positions = groups * TS;
+  const int64_t tiles = (p.seq + tile_positions - 1) / tile_positions;
+  const int64_t tile = blockIdx.x % tiles;
+  const int split = static_cast<int>(blockIdx.x / tiles);
+  const int64_t pos0 = tile * tile_positions;
+  const int n_pos = static_cast<int>(p.seq - pos0 < tile_positions ? p.seq - pos0 : tile_positions);
+
+  CS* cos_s = reinterpret_cast<CS*>(rope_smem);
+  CS* sin_s = cos_s + static_cast<size_t>(tile_positions) * p.half;
+  const uint32_t table_bytes = static_cast<uint32_t>(n_pos) * p.half * sizeof(CS);
+  const CS* cos_g = static_cast<const CS*>(p.cos) + pos0 * p.half;
+  const CS* sin_g = static_cast<const CS*>(p.sin) + pos0 * p.half;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_init_fence();
+    mbar_arrive_expect(&bar, 2 * table_bytes);
+    bulk_load(cos_s, cos_g, table_bytes, &bar);
+    bulk_load(sin_s, sin_g, table_bytes, &bar);
   }
+  __syncthreads();  // the barrier is initialised before anyone polls it
+
+  const int grp = threadIdx.x / tpp;
+  const int r0 = threadIdx.x - grp * tpp;
+  const int uph = (INTERLEAVED ? 2 * p.half : p.half) / V;  // units per head
+  const int heads0 = p.t[0].heads;
+  const int upp = (heads0 + (p.n_tensors > 1 ? p.t[1].heads : 0)) * uph;
+  const int gpos = grp * TS;  // first position of my group inside the tile
   const int tail_words = (p.head_dim - 2 * p.half) / V;
 
+  // Wait for the tables.  If the bounded wait runs out anywhere in the CTA, all
+  // threads fill the tables with ordinary loads instead.
+  {
+    const bool ok = mbar_wait(&bar, 0);
+    if (__syncthreads_or(!ok)) {
+      const int n = n_pos * p.half;
+      for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        cos_s[i] = cos_g[i];
+        sin_s[i] = sin_g[i];
+      }
+      __syncthreads();
+    }
+  }
+
   for (int b = split; b < p.batch; b += p.batch_split) {
-    for (int ti = 0; ti < p.n_tensors; ++ti) {
+    for (int r = r0; r < upp; r += tpp) {
+      int hh = r / uph;
+      const int g = r - hh * uph;
+      const int ti = hh >= heads0 ? 1 : 0;
+      if (ti) hh -= heads0;
       const RopeTensor& t = p.t[ti];
-      const T* xin = static_cast<const T*>(t.x) + b * t.xs_b + pos * t.xs_s;
-      T* xout = static_cast<T*>(t.out) + b * t.os_b + pos * t.os_s;
-      const int units = t.heads * uph;
-      for (int u0 = lane; u0 < units; u0 += 32 * UNROLL) {
-        uint4 v1[UNROLL], v2[INTERLEAVED ? 1 : UNROLL];
-        int64_t off_o[UNROLL];
-        int grp[UNROLL];
+      const int64_t in_off = b * t.xs_b + (pos0 + gpos) * t.xs_s + hh * t.xs_h + static_cast<int64_t>(g) * V;
+      const int64_t out_off = b * t.os_b + (pos0 + gpos) * t.os_s + hh * t.os_h + static_cast<int64_t>(g) * V;
+      const T* xin = static_cast<const T*>(t.x) + in_off;
+      T* xout = static_cast<T*>(t.out) + out_off;
+
+      uint4 v1[TS], v2[INTERLEAVED ? 1 : TS];
 #pragma unroll
-        for (int k = 0; k < UNROLL; ++k) {
-          const int u = u0 + 32 * k;
-          const int h = u / uph;
-          grp[k] = u - h * uph;
-          const int64_t off_i = h * t.xs_h + static_cast<int64_t>(grp[k]) * V;
-          off_o[k] = h * t.os_h + static_cast<int64_t>(grp[k]) * V;
-          if (u < units) {
-            v1[k] = ld_stream(xin + off_i);
-            if constexpr (!INTERLEAVED) v2[k] = ld_stream(xin + off_i + p.half);
-          }
-        }
-#pragma unroll
-        for (int k = 0; k < UNROLL; ++k) {
-          if (u0 + 32 * k >= units) continue;
-          if (!FIXED) {
-            load_cs<CS, NCS>(cos_row + grp[k] * NCS, c);
-            load_cs<CS, NCS>(sin_row + grp[k] * NCS, s);
-          }
-          float a[V];
-          Num<T>::unpack(v1[k], a);
-          if constexpr (INTERLEAVED) {
-#pragma unroll
-            for (int j = 0; j < V / 2; ++j) {
-              float y1, y2;
-              rotate(a[2 * j], a[2 * j + 1], c[j], s[j], y1, y2);
-              a[2 * j] = y1;
-              a[2 * j + 1] = y2;
-            }
-            st_stream(xout + off_o[k], Num<T>::pack(a));
-          } else {
-            float d[V];
-            Num<T>::unpack(v2[k], d);
-#pragma unroll
-            for (int j = 0; j < V; ++j) {
-              float y1, y2;
-              rotate(a[j], d[j], c[j], s[j], y1, y2);
-              a[j] = y1;
-              d[j] = y2;
-            }
-            st_stream(xout + off_o[k], Num<T>::pack(a));
-            st_stream(xout + off_o[k] + p.half, Num<T>::pack(d));
-          }
+      for (int k = 0; k < TS; ++k) {
+        if (gpos + k < n_pos) {
+          v1[k] = ld_stream(xin + k * t.xs_s);
+          if constexpr (!INTERLEAVED) v2[k] = ld_stream(xin + k * t.xs_s + p.half);
         }
       }
-      // channels past the rotated ones pass through (nothing to do in place)
-      if (tail_words > 0 && t.x != t.out) {
+#pragma unroll
+      for (int k = 0; k < TS; ++k) {
+        if (gpos + k >= n_pos) continue;
+        float c[NCS], sn[NCS];
+        load_cs_shared<CS, NCS>(cos_s + (gpos + k) * p.half + g * NCS, c);
+        load_cs_shared<CS, NCS>(sin_s + (gpos + k) * p.half + g * NCS, sn);
+        float a[V];
+        Num<T>::unpack(v1[k], a);
+        if constexpr (INTERLEAVED) {
+#pragma unroll
+          for (int j = 0; j < V / 2; ++j) {
+            float y1, y2;
+            rotate(a[2 * j], a[2 * j + 1], c[j], sn[j], y1, y2);
+            a[2 * j] = y1;
+            a[2 * j + 1] = y2;
+          }
+          st_stream(xout + k * t.os_s, Num<T>::pack(a));
+        } else {
+          float d[V];
+          Num<T>::unpack(v2[k], d);
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            float y1, y2;
+            rotate(a[j], d[j], c[j], sn[j], y1, y2);
+            a[j] = y1;
+            d[j] = y2;
+          }
+          st_stream(xout + k * t.os_s, Num<T>::pack(a));
+          st_stream(xout + k * t.os_s + p.half, Num<T>::pack(d));
+        }
+      }
+    }
+    // channels past the rotated ones pass through (nothing to do in place)
+    if (tail_words > 0) {
+      for (int ti = 0; ti < p.n_tensors; ++ti) {
+        const RopeTensor& t = p.t[ti];
+        if (t.x == t.out) continue;
         const int words = t.heads * tail_words;
-        for (int w = lane; w < words; w += 32) {
-          const int h = w / tail_words;
-          const int64_t j = 2 * p.half + static_cast<int64_t>(w - h * tail_words) * V;
-          st_stream(xout + h * t.os_h + j, ld_stream(xin + h * t.xs_h + j));
+        for (int k = 0; k < TS; ++k) {
+          if (gpos + k >= n_pos) break;
+          const T* xin = static_cast<const T*>(t.x) + b * t.xs_b + (pos0 + gpos + k) * t.xs_s;
+          T* xout = static_cast<T*>(t.out) + b * t.os_b + (pos0 + gpos + k) * t.os_s;
+          for (int w = r0; w < words; w += tpp) {
+            const int h = w / tail_words;
+            const int64_t j = 2 * p.half + static_cast<int64_t>(w - h * tail_words) * V;
+            st_stream(xout + h * t.os_h + j, ld_stream(xin + h * t.xs_h + j));
+          }
         }
       }
     }
@@ -210,21 +281,29 @@ int run(RopeArgs& p, cudaStream_t st) {
     vec = vec && aligned(t.x, 16) && aligned(t.out, 16) && t.xs_b % V == 0 && t.xs_s % V == 0 && t.xs_h % V == 0 &&
           t.os_b % V == 0 && t.os_s % V == 0 && t.os_h % V == 0;
   }
+  // bulk copies need 16-byte aligned table rows
+  vec = vec && (static_cast<size_t>(p.half) * sizeof(CS)) % 16 == 0 && aligned(p.cos, 16) && aligned(p.sin, 16);
   if (vec) {
-    // enough warps to fill the machine several times over, else split the batch
-    const int64_t want = static_cast<int64_t>(sm_count()) * 64 * 4;
-    int split = p.batch;
-    while (split > 1 && p.seq * split > want && split % 2 == 0) split /= 2;
-    p.batch_split = split;
-    const int64_t warps = p.seq * split;
-    const int64_t grid = ceil_div(warps, 8);
-    if (grid > 0x7fffffffLL) return fail(B200_ERR_SHAPE, "b200_rope: problem too large for one launch");
     const int uph = (INTERLEAVED ? 2 * p.half : p.half) / V;
-    if (32 % uph == 0)
-      rope_warp_kernel<T, CS, INTERLEAVED, true><<<static_cast<unsigned>(grid), 256, 0, st>>>(p);
-    else
-      rope_warp_kernel<T, CS, INTERLEAVED, false><<<static_cast<unsigned>(grid), 256, 0, st>>>(p);
-    return after_launch("rope_warp_kernel");
+    int64_t upp = static_cast<int64_t>(p.t[0].heads + (p.n_tensors > 1 ? p.t[1].heads : 0)) * uph;
+    // threads per position: all its units if they fit in a CTA, in whole warps
+    int tpp = static_cast<int>(upp < 512 ? (upp + 31) / 32 * 32 : 512);
+    int groups = 256 / tpp > 0 ? 256 / tpp : 1;
+    const int threads = tpp * groups;
+    const int tile_positions = groups * kRopeTS;
+    const int64_t tiles = ceil_div(p.seq, tile_positions);
+    // one CTA per (tile, batch entry) unless that is far more CTAs than the machine needs
+    const int64_t want = static_cast<int64_t>(sm_count()) * 64;
+    int split = p.batch;
+    while (split > 1 && tiles * split > want && split % 2 == 0) split /= 2;
+    p.batch_split = split;
+    const int64_t grid = tiles * split;
+    if (grid > 0x7fffffffLL) return fail(B200_ERR_SHAPE, "b200_rope: problem too large for one launch");
+    const size_t smem = 2 * static_cast<size_t>(tile_positions) * p.half * sizeof(CS);
+    if (smem <= 48 * 1024) {
+      rope_tile_kernel<T, CS, INTERLEAVED><<<static_cast<unsigned>(grid), threads, smem, st>>>(p, tpp, groups);
+      return after_launch("rope_tile_kernel");
+    }
   }
   p.batch_split = 1;
   rope_scalar_kernel<T, CS, INTERLEAVED><<<static_cast<unsigned>(sm_count()) * 8, 256, 0, st>>>(p);
@@ -250,6 +329,9 @@ int validate(const char* fn, int64_t batch, int64_t seq, int64_t head_dim, int64
 }
 
 }  // namespace
+
+unsigned int rope_wait_timeouts() { return read_wait_timeouts(); }
+
 }  // namespace b200
 
 using namespace b200;

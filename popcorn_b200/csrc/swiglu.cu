@@ -14,11 +14,21 @@
 namespace b200 {
 namespace {
 
+__device__ __forceinline__ float silu_f32(float a) { return __fdiv_rn(a, __fadd_rn(1.0f, expf(-a))); }
+
 template <typename T>
 __device__ __forceinline__ float swiglu_one(float a, float b) {
-  const float e = expf(-a);
-  const float silu = __fdiv_rn(a, __fadd_rn(1.0f, e));
-  return Num<T>::rt(__fmul_rn(Num<T>::rt(silu), b));
+  return Num<T>::rt(__fmul_rn(Num<T>::rt(silu_f32(a)), b));
+}
+
+// Two neighbouring elements at once, so that each rounding to T is one packed conversion.
+template <typename T>
+__device__ __forceinline__ void swiglu_two(float& a0, float& a1, float b0, float b1) {
+  a0 = silu_f32(a0);
+  a1 = silu_f32(a1);
+  Num<T>::round2(a0, a1);
+  a0 = __fmul_rn(a0, b0);
+  a1 = __fmul_rn(a1, b1);  // the final rounding to T happens in the pack
 }
 
 // Each thread owns UNROLL 128-bit words, THREADS words apart, so a warp always
@@ -65,7 +75,7 @@ swiglu_vec_kernel(const T* a, const T* b, T* out, Index total_words, Index words
     Num<T>::unpack(va[u], fa);
     Num<T>::unpack(vb[u], fb);
 #pragma unroll
-    for (int j = 0; j < V; ++j) fa[j] = swiglu_one<T>(fa[j], fb[j]);
+    for (int j = 0; j < V; j += 2) swiglu_two<T>(fa[j], fa[j + 1], fb[j], fb[j + 1]);
     if (ok[u]) st_stream(out + off_o[u], Num<T>::pack(fa));
   }
 }

@@ -32,7 +32,10 @@ def check(got, want, *, exact_fraction=0.999, what=""):
     worst = float(diff.max())
     same = float((got == want).double().mean())
     assert worst <= MAX_ABS[want.dtype], f"{what}: max-abs {worst:.3e} exceeds {MAX_ABS[want.dtype]:.0e} ({int((diff > MAX_ABS[want.dtype]).sum())} elements)"
-    assert same >= exact_fraction, f"{what}: only {same:.6f} of elements are bit-identical"
+    # the intermediate roundings of a 16-bit dtype hide last-bit fp32 differences (another exp, another
+    # summation order); in fp32 those differences are visible, so there only the max-abs bound applies
+    if want.dtype != torch.float32:
+        assert same >= exact_fraction, f"{what}: only {same:.6f} of elements are bit-identical"
 
 
 def randn(seed, *shape, dtype=F32, scale=1.0):
