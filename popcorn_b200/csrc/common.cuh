@@ -33,6 +33,29 @@ inline size_t dtype_size(int dtype) { return dtype == B200_F32 ? 4 : 2; }
 inline bool dtype_ok(int dtype) { return dtype == B200_F32 || dtype == B200_F16 || dtype == B200_BF16; }
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+// Whether kernels are launched with programmatic dependent launch (see launch()).
+bool pdl_enabled();
+
+// Launch `kernel` on `st`.  With programmatic dependent launch the grid may be
+// scheduled while the previous kernel of the stream is still draining; every
+// kernel of this library calls pdl_prologue() before its first global access,
+// which blocks until that previous kernel has completed and its writes are
+// visible, so stream order is preserved and only launch latency overlaps.
+template <typename... Params, typename... Args>
+inline void launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = pdl_enabled() ? 1 : 0;
+  (void)cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 #define B200_REQUIRE_PTR(p)                                                        \
   do {                                                                             \
     if ((p) == nullptr) return ::b200::fail(B200_ERR_NULL_POINTER, "%s: %s is NULL", __func__, #p); \
@@ -41,6 +64,14 @@ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 // -------------------------------------------------------------- device side --
 
 constexpr int kVecBytes = 16;  // every fast path moves 128-bit words
+
+// First statement of every kernel: let the next kernel of the stream begin its
+// launch, then wait until the previous one has completed (a no-op for a grid
+// that was launched without programmatic dependent launch).
+__device__ __forceinline__ void pdl_prologue() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 
 template <typename T>
 struct Num;
@@ -83,6 +114,12 @@ struct Num<__nv_bfloat16> {
   // cvt.rn.bf16.f32 issues on the quarter-rate conversion pipe and made kernels
   // that round per element pipe-bound; the packed form does not.
   static __device__ __forceinline__ void round2(float& a, float& b) { unpack2(pack2(a, b), a, b); }
+  // Product of two packed pairs, each rounded once to bf16.  A bf16 x bf16 product is exact in
+  // fp32, so this equals round(fp32(a) * fp32(b)), the way the reference multiplies two bf16 tensors.
+  static __device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
+    __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
   static __device__ __forceinline__ void unpack(const uint4& v, float (&f)[8]) {
     unpack2(v.x, f[0], f[1]);
     unpack2(v.y, f[2], f[3]);
@@ -110,6 +147,11 @@ struct Num<__half> {
     return *reinterpret_cast<uint32_t*>(&p);
   }
   static __device__ __forceinline__ void round2(float& a, float& b) { unpack2(pack2(a, b), a, b); }
+  // fp16 x fp16 is exact in fp32 as well (22 significant bits): one rounding, like the reference.
+  static __device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
+    __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
   static __device__ __forceinline__ void unpack(const uint4& v, float (&f)[8]) {
     unpack2(v.x, f[0], f[1]);
     unpack2(v.y, f[2], f[3]);

@@ -53,6 +53,7 @@ template <typename L, int NPL>
 __global__ void __launch_bounds__(256)
 route_kernel(const L* __restrict__ logits, int32_t* __restrict__ indices, float* __restrict__ weights,
              int64_t tokens, int experts, int top_k, int64_t ld) {
+  pdl_prologue();
   const int lane = threadIdx.x & 31;
   const int64_t warps = static_cast<int64_t>(gridDim.x) * 8;
   for (int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); t < tokens; t += warps) {
@@ -109,6 +110,7 @@ constexpr int kPairsPerBlock = kIndexThreads * kPairsPerThread;  // 2048 (token,
 __global__ void __launch_bounds__(kIndexThreads)
 index_hist_kernel(const int32_t* __restrict__ idx, int64_t pairs, int experts, int nblk,
                   int32_t* __restrict__ block_hist) {
+  pdl_prologue();
   extern __shared__ int hist[];
   for (int e = threadIdx.x; e < experts; e += kIndexThreads) hist[e] = 0;
   __syncthreads();
@@ -131,6 +133,7 @@ index_hist_kernel(const int32_t* __restrict__ idx, int64_t pairs, int experts, i
 __global__ void __launch_bounds__(1024)
 index_scan_kernel(int32_t* __restrict__ block_hist, int experts, int nblk,
                   int32_t* __restrict__ counts, int32_t* __restrict__ offsets) {
+  pdl_prologue();
   __shared__ int total[kMaxExperts];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -190,6 +193,7 @@ __global__ void __launch_bounds__(kIndexThreads)
 index_scatter_kernel(const int32_t* __restrict__ idx, int64_t pairs, int top_k, int experts, int nblk,
                      const int32_t* __restrict__ block_hist, const int32_t* __restrict__ offsets,
                      int32_t* __restrict__ perm_token, int32_t* __restrict__ pos) {
+  pdl_prologue();
   extern __shared__ int whist[];  // [8 warps][experts]
   constexpr int kWarps = kIndexThreads / 32;
   constexpr int kPairsPerWarp = kPairsPerBlock / kWarps;  // 256
@@ -260,6 +264,7 @@ template <typename W>
 __global__ void __launch_bounds__(256)
 permute_kernel(const W* __restrict__ x, const int32_t* __restrict__ pos, W* __restrict__ rows,
                int64_t tokens, int top_k, int words, int64_t ldx, int64_t ldrows) {
+  pdl_prologue();
   constexpr int UNROLL = 4;
   const int lane = threadIdx.x & 31;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
@@ -287,6 +292,7 @@ template <typename W>
 __global__ void __launch_bounds__(256)
 gather_kernel(const W* __restrict__ x, const int32_t* __restrict__ src_row, W* __restrict__ out,
               int64_t n_rows, int words, int64_t ldx, int64_t ldo) {
+  pdl_prologue();
   constexpr int UNROLL = 8;
   const int lane = threadIdx.x & 31;
   const int64_t r = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
@@ -317,6 +323,7 @@ template <typename T, bool VEC>
 __global__ void __launch_bounds__(256, 2)
 unpermute_kernel(const T* __restrict__ rows, const float* __restrict__ weights, const int32_t* __restrict__ pos,
                  T* __restrict__ y, int64_t tokens, int top_k, int hidden, int64_t ldrows, int64_t ldy) {
+  pdl_prologue();
   constexpr int V = VEC ? Num<T>::kVec : 1;
   constexpr int KB = 8;  // rows fetched together
   using Word = typename std::conditional<VEC, uint4, T>::type;
@@ -454,7 +461,7 @@ extern "C" int b200_moe_route(const void* logits, int32_t* indices, float* weigh
   const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
   const int E = static_cast<int>(experts), K = static_cast<int>(top_k);
 #define B200_ROUTE(L, NPL) \
-  route_kernel<L, NPL><<<grid, 256, 0, st>>>(static_cast<const L*>(logits), indices, weights, tokens, E, K, ld_logits)
+  launch(route_kernel<L, NPL>, grid, 256, 0, st, static_cast<const L*>(logits), indices, weights, tokens, E, K, ld_logits)
 #define B200_ROUTE_NPL(L)                  \
   do {                                     \
     if (E <= 32) B200_ROUTE(L, 1);         \
@@ -511,13 +518,13 @@ extern "C" int b200_moe_index(const int32_t* indices, int64_t tokens, int64_t to
   const int E = static_cast<int>(experts);
   int32_t* block_hist = static_cast<int32_t*>(scratch);
   if (nblk > 0) {
-    index_hist_kernel<<<nblk, kIndexThreads, E * sizeof(int), st>>>(indices, pairs, E, nblk, block_hist);
+    launch(index_hist_kernel, nblk, kIndexThreads, E * sizeof(int), st, indices, pairs, E, nblk, block_hist);
     if (int rc = after_launch("index_hist_kernel")) return rc;
   }
-  index_scan_kernel<<<1, 1024, 0, st>>>(block_hist, E, nblk, counts, offsets);
+  launch(index_scan_kernel, 1, 1024, 0, st, block_hist, E, nblk, counts, offsets);
   if (int rc = after_launch("index_scan_kernel")) return rc;
   if (nblk > 0) {
-    index_scatter_kernel<<<nblk, kIndexThreads, 8 * E * sizeof(int), st>>>(
+    launch(index_scatter_kernel, nblk, kIndexThreads, 8 * E * sizeof(int), st,
         indices, pairs, static_cast<int>(top_k), E, nblk, block_hist, offsets, perm_token, pos);
     if (int rc = after_launch("index_scatter_kernel")) return rc;
   }
@@ -528,7 +535,7 @@ namespace {
 template <typename W>
 int launch_permute(const void* x, const int32_t* pos, void* rows, int64_t tokens, int top_k, int64_t row_bytes,
                    int64_t ldx_bytes, int64_t ldr_bytes, cudaStream_t st) {
-  permute_kernel<W><<<static_cast<unsigned>(ceil_div(tokens, 8)), 256, 0, st>>>(
+  launch(permute_kernel<W>, static_cast<unsigned>(ceil_div(tokens, 8)), 256, 0, st,
       static_cast<const W*>(x), pos, static_cast<W*>(rows), tokens, top_k, static_cast<int>(row_bytes / sizeof(W)),
       ldx_bytes / static_cast<int64_t>(sizeof(W)), ldr_bytes / static_cast<int64_t>(sizeof(W)));
   return after_launch("permute_kernel");
@@ -536,7 +543,7 @@ int launch_permute(const void* x, const int32_t* pos, void* rows, int64_t tokens
 template <typename W>
 int launch_gather(const void* x, const int32_t* src, void* out, int64_t n_rows, int64_t row_bytes,
                   int64_t ldx_bytes, int64_t ldo_bytes, cudaStream_t st) {
-  gather_kernel<W><<<static_cast<unsigned>(ceil_div(n_rows, 8)), 256, 0, st>>>(
+  launch(gather_kernel<W>, static_cast<unsigned>(ceil_div(n_rows, 8)), 256, 0, st,
       static_cast<const W*>(x), src, static_cast<W*>(out), n_rows, static_cast<int>(row_bytes / sizeof(W)),
       ldx_bytes / static_cast<int64_t>(sizeof(W)), ldo_bytes / static_cast<int64_t>(sizeof(W)));
   return after_launch("gather_kernel");
@@ -613,9 +620,9 @@ extern "C" int b200_moe_unpermute(const void* rows, const float* weights, const 
     constexpr int V = Num<T>::kVec;
     const bool vec = hidden % V == 0 && ldrows % V == 0 && ldy % V == 0 && aligned(rows, 16) && aligned(y, 16);
     if (vec)
-      unpermute_kernel<T, true><<<grid, 256, 0, st>>>(static_cast<const T*>(rows), weights, pos, static_cast<T*>(y), tokens, K, H, ldrows, ldy);
+      launch(unpermute_kernel<T, true>, grid, 256, 0, st, static_cast<const T*>(rows), weights, pos, static_cast<T*>(y), tokens, K, H, ldrows, ldy);
     else
-      unpermute_kernel<T, false><<<grid, 256, 0, st>>>(static_cast<const T*>(rows), weights, pos, static_cast<T*>(y), tokens, K, H, ldrows, ldy);
+      launch(unpermute_kernel<T, false>, grid, 256, 0, st, static_cast<const T*>(rows), weights, pos, static_cast<T*>(y), tokens, K, H, ldrows, ldy);
   });
   return after_launch("unpermute_kernel");
 }

@@ -29,22 +29,6 @@ __device__ __forceinline__ float scale_one(float h, float r, float w, float b, b
   return y;
 }
 
-// The same for two neighbouring elements, rounding them pairwise (h0, h1 in, y0, y1 out).
-// The LAST rounding to T is left to the caller's pack.
-template <typename T>
-__device__ __forceinline__ void scale_two(float& h0, float& h1, float r, float w0, float w1, float b0, float b1, bool has_bias) {
-  h0 = __fmul_rn(h0, r);
-  h1 = __fmul_rn(h1, r);
-  Num<T>::round2(h0, h1);
-  h0 = __fmul_rn(h0, w0);
-  h1 = __fmul_rn(h1, w1);
-  if (has_bias) {
-    Num<T>::round2(h0, h1);
-    h0 = __fadd_rn(h0, b0);
-    h1 = __fadd_rn(h1, b1);
-  }
-}
-
 // One row per group of TPR threads, ITEMS 128-bit words per thread, the row held
 // in registers.  THREADS / TPR rows per CTA.  ADD selects add_rms_norm.
 template <typename T, int TPR, int ITEMS, bool ADD>
@@ -57,6 +41,7 @@ rms_rows_kernel(const T* x, const T* res, const T* __restrict__ weight,
   constexpr int THREADS = TPR < 256 ? 256 : TPR;
   constexpr int ROWS_PER_CTA = THREADS / TPR;
   constexpr int WARPS_PER_ROW = TPR / 32;
+  pdl_prologue();
 
   const int tid = threadIdx.x;
   const int sub = tid / TPR;        // which row of this CTA
@@ -119,26 +104,52 @@ rms_rows_kernel(const T* x, const T* res, const T* __restrict__ weight,
   for (int i = 0; i < ITEMS; ++i) {
     if (!ok[i]) continue;
     const int64_t col = static_cast<int64_t>(lane_in_row + i * TPR) * V;
-    float f[V], w[V], b[V];
-    Num<T>::unpack(data[i], f);
-    Num<T>::unpack(ld_reuse(weight + col), w);
-    if (has_bias) {
-      Num<T>::unpack(ld_reuse(bias + col), b);
-    } else {
+    if constexpr (sizeof(T) == 4) {
+      float f[V], w[V], b[V];
+      Num<T>::unpack(data[i], f);
+      Num<T>::unpack(ld_reuse(weight + col), w);
+      if (has_bias) Num<T>::unpack(ld_reuse(bias + col), b);
 #pragma unroll
-      for (int j = 0; j < V; ++j) b[j] = 0.f;
-    }
-    if constexpr (ADD) {
-#pragma unroll
-      for (int j = 0; j < V; j += 2) {
-        w[j] = __fadd_rn(w[j], offset);
-        w[j + 1] = __fadd_rn(w[j + 1], offset);
-        Num<T>::round2(w[j], w[j + 1]);
+      for (int j = 0; j < V; ++j) {
+        const float wj = ADD ? __fadd_rn(w[j], offset) : w[j];
+        f[j] = __fmul_rn(__fmul_rn(f[j], r), wj);
+        if (has_bias) f[j] = __fadd_rn(f[j], b[j]);
       }
-    }
+      st_stream(y + row * ldy + col, Num<T>::pack(f));
+    } else {
+      // 16-bit: h * r in fp32, one packed rounding to T, then the packed product with the weight
+      // word (a product of two 16-bit values is rounded once, as in the reference)
+      const uint4 wv = ld_reuse(weight + col);
+      uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+      if (ADD && offset != 0.f) {
 #pragma unroll
-    for (int j = 0; j < V; j += 2) scale_two<T>(f[j], f[j + 1], r, w[j], w[j + 1], b[j], b[j + 1], has_bias);
-    st_stream(y + row * ldy + col, Num<T>::pack(f));
+        for (int j = 0; j < 4; ++j) {
+          float lo, hi;
+          Num<T>::unpack2(ww[j], lo, hi);
+          ww[j] = Num<T>::pack2(__fadd_rn(lo, offset), __fadd_rn(hi, offset));
+        }
+      }
+      const uint32_t wd[4] = {data[i].x, data[i].y, data[i].z, data[i].w};
+      uint32_t wo[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float lo, hi;
+        Num<T>::unpack2(wd[j], lo, hi);
+        wo[j] = Num<T>::mul2(Num<T>::pack2(__fmul_rn(lo, r), __fmul_rn(hi, r)), ww[j]);
+      }
+      if (has_bias) {
+        const uint4 bv = ld_reuse(bias + col);
+        const uint32_t wb[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float lo, hi, blo, bhi;
+          Num<T>::unpack2(wo[j], lo, hi);
+          Num<T>::unpack2(wb[j], blo, bhi);
+          wo[j] = Num<T>::pack2(__fadd_rn(lo, blo), __fadd_rn(hi, bhi));
+        }
+      }
+      st_stream(y + row * ldy + col, make_uint4(wo[0], wo[1], wo[2], wo[3]));
+    }
   }
 }
 
@@ -149,6 +160,7 @@ rms_stream_kernel(const T* x, const T* res, const T* __restrict__ weight,
                   const T* __restrict__ bias, T* y, T* s_out,
                   int64_t cols, int64_t ldx, int64_t ldr, int64_t ldy, int64_t lds,
                   float cols_f, float eps, float offset) {
+  pdl_prologue();
   const int64_t row = blockIdx.x;
   const T* xr = x + row * ldx;
   const T* rr = ADD ? res + row * ldr : nullptr;
@@ -189,7 +201,7 @@ void launch_rows(const void* x, const void* res, const void* w, const void* b, v
   constexpr int THREADS = TPR < 256 ? 256 : TPR;
   constexpr int ROWS_PER_CTA = THREADS / TPR;
   const unsigned grid = static_cast<unsigned>(ceil_div(rows, ROWS_PER_CTA));
-  rms_rows_kernel<T, TPR, ITEMS, ADD><<<grid, THREADS, 0, st>>>(
+  launch(rms_rows_kernel<T, TPR, ITEMS, ADD>, grid, THREADS, 0, st,
       static_cast<const T*>(x), static_cast<const T*>(res), static_cast<const T*>(w), static_cast<const T*>(b),
       static_cast<T*>(y), static_cast<T*>(s), rows, nvec, ldx, ldr, ldy, lds, cols_f, eps, offset);
 }
@@ -220,7 +232,7 @@ int run(const void* x, const void* res, const void* w, const void* b, void* y, v
     B200_ROWS(1024, 8);
 #undef B200_ROWS
   }
-  rms_stream_kernel<T, ADD><<<static_cast<unsigned>(rows), 256, 0, st>>>(
+  launch(rms_stream_kernel<T, ADD>, static_cast<unsigned>(rows), 256, 0, st,
       static_cast<const T*>(x), static_cast<const T*>(res), static_cast<const T*>(w), static_cast<const T*>(b),
       static_cast<T*>(y), static_cast<T*>(s), cols, ldx, ldr, ldy, lds, cols_f, eps, offset);
   return after_launch("rms_stream_kernel");

@@ -118,6 +118,7 @@ __global__ void __launch_bounds__(512, 2) rope_tile_kernel(const RopeArgs p, int
   extern __shared__ __align__(16) unsigned char rope_smem[];
   __shared__ __align__(8) uint64_t bar;
 
+  pdl_prologue();
   const int tile_positions = groups * TS;
   const int64_t tiles = (p.seq + tile_positions - 1) / tile_positions;
   const int64_t tile = blockIdx.x % tiles;
@@ -147,8 +148,30 @@ __global__ void __launch_bounds__(512, 2) rope_tile_kernel(const RopeArgs p, int
   const int gpos = grp * TS;  // first position of my group inside the tile
   const int tail_words = (p.head_dim - 2 * p.half) / V;
 
-  // Wait for the tables.  If the bounded wait runs out anywhere in the CTA, all
-  // threads fill the tables with ordinary loads instead.
+  uint4 v1[TS], v2[INTERLEAVED ? 1 : TS];
+  // the loads of one (batch, unit) item: TS positions, one or two words each
+  auto issue_loads = [&](int b, int r) {
+    int hh = r / uph;
+    const int g = r - hh * uph;
+    const int ti = hh >= heads0 ? 1 : 0;
+    if (ti) hh -= heads0;
+    const RopeTensor& t = p.t[ti];
+    const T* xin = static_cast<const T*>(t.x) + b * t.xs_b + (pos0 + gpos) * t.xs_s + hh * t.xs_h + static_cast<int64_t>(g) * V;
+#pragma unroll
+    for (int k = 0; k < TS; ++k) {
+      if (gpos + k < n_pos) {
+        v1[k] = ld_stream(xin + k * t.xs_s);
+        if constexpr (!INTERLEAVED) v2[k] = ld_stream(xin + k * t.xs_s + p.half);
+      }
+    }
+  };
+
+  // The first item's loads go out before anyone waits for the tables.
+  bool first = true;
+  if (split < p.batch && r0 < upp) issue_loads(split, r0);
+
+  // Wait for the tables (every thread, at this one place).  If the bounded wait
+  // runs out anywhere in the CTA, all threads fill the tables with ordinary loads.
   {
     const bool ok = mbar_wait(&bar, 0);
     if (__syncthreads_or(!ok)) {
@@ -163,24 +186,14 @@ __global__ void __launch_bounds__(512, 2) rope_tile_kernel(const RopeArgs p, int
 
   for (int b = split; b < p.batch; b += p.batch_split) {
     for (int r = r0; r < upp; r += tpp) {
+      if (!first) issue_loads(b, r);
+      first = false;
       int hh = r / uph;
       const int g = r - hh * uph;
       const int ti = hh >= heads0 ? 1 : 0;
       if (ti) hh -= heads0;
       const RopeTensor& t = p.t[ti];
-      const int64_t in_off = b * t.xs_b + (pos0 + gpos) * t.xs_s + hh * t.xs_h + static_cast<int64_t>(g) * V;
-      const int64_t out_off = b * t.os_b + (pos0 + gpos) * t.os_s + hh * t.os_h + static_cast<int64_t>(g) * V;
-      const T* xin = static_cast<const T*>(t.x) + in_off;
-      T* xout = static_cast<T*>(t.out) + out_off;
-
-      uint4 v1[TS], v2[INTERLEAVED ? 1 : TS];
-#pragma unroll
-      for (int k = 0; k < TS; ++k) {
-        if (gpos + k < n_pos) {
-          v1[k] = ld_stream(xin + k * t.xs_s);
-          if constexpr (!INTERLEAVED) v2[k] = ld_stream(xin + k * t.xs_s + p.half);
-        }
-      }
+      T* xout = static_cast<T*>(t.out) + b * t.os_b + (pos0 + gpos) * t.os_s + hh * t.os_h + static_cast<int64_t>(g) * V;
 #pragma unroll
       for (int k = 0; k < TS; ++k) {
         if (gpos + k >= n_pos) continue;
@@ -237,6 +250,7 @@ __global__ void __launch_bounds__(512, 2) rope_tile_kernel(const RopeArgs p, int
 // Any shape, any alignment: one thread per (batch, position, head, channel pair or tail channel).
 template <typename T, typename CS, bool INTERLEAVED>
 __global__ void __launch_bounds__(256) rope_scalar_kernel(const RopeArgs p) {
+  pdl_prologue();
   const int per_head = p.half + (p.head_dim - 2 * p.half);  // pairs, then pass-through channels
   for (int ti = 0; ti < p.n_tensors; ++ti) {
     const RopeTensor& t = p.t[ti];
@@ -301,12 +315,12 @@ int run(RopeArgs& p, cudaStream_t st) {
     if (grid > 0x7fffffffLL) return fail(B200_ERR_SHAPE, "b200_rope: problem too large for one launch");
     const size_t smem = 2 * static_cast<size_t>(tile_positions) * p.half * sizeof(CS);
     if (smem <= 48 * 1024) {
-      rope_tile_kernel<T, CS, INTERLEAVED><<<static_cast<unsigned>(grid), threads, smem, st>>>(p, tpp, groups);
+      launch(rope_tile_kernel<T, CS, INTERLEAVED>, static_cast<unsigned>(grid), threads, smem, st, p, tpp, groups);
       return after_launch("rope_tile_kernel");
     }
   }
   p.batch_split = 1;
-  rope_scalar_kernel<T, CS, INTERLEAVED><<<static_cast<unsigned>(sm_count()) * 8, 256, 0, st>>>(p);
+  launch(rope_scalar_kernel<T, CS, INTERLEAVED>, static_cast<unsigned>(sm_count()) * 8, 256, 0, st, p);
   return after_launch("rope_scalar_kernel");
 }
 

@@ -3,6 +3,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -58,6 +59,14 @@ int check_device() {
   if (major != 10)
     return fail(B200_ERR_DEVICE, "libpopcorn_b200 is built for sm_100a only; current device is compute capability %d.x", major);
   return B200_OK;
+}
+
+bool pdl_enabled() {
+  static const bool enabled = [] {
+    const char* v = getenv("B200_PDL");
+    return v == nullptr || v[0] != '0';
+  }();
+  return enabled;
 }
 
 int sm_count() {

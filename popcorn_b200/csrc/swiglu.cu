@@ -1,6 +1,6 @@
 // SwiGLU forward for sm_100a:  out = round_T(round_T(silu(a)) * b).
 //
-// Bound: HBM (2 reads + 1 write per element, ~25 fp32 instructions).  `a` and `b`
+// Bound: HBM (2 reads + 1 write per element, ~20 fp32 instructions).  `a` and `b`
 // are addressed through their own leading dimensions, so the two column halves
 // of a fused [rows, 2*cols] gate_up buffer are consumed in place; the
 // incumbent (src/popcorn/impls/swiglu.cu:80-81) copies them to contiguous
@@ -14,32 +14,78 @@
 namespace b200 {
 namespace {
 
-__device__ __forceinline__ float silu_f32(float a) { return __fdiv_rn(a, __fadd_rn(1.0f, expf(-a))); }
+// Two ways to evaluate silu(a) = a / (1 + exp(-a)) in fp32:
+//  MATH 0  expf and an IEEE division: the reference's own operation sequence.
+//          About 32 instructions per element in total, which makes the bf16
+//          kernel issue-bound (0.78 of the HBM roofline on a B200).
+//  MATH 1  exp(-a) = 2^t with t = fp32(-a*log2(e)): the hardware ex2
+//          approximation, corrected to first order for the rounding of t and
+//          for the low bits of log2(e); the quotient from the reciprocal
+//          approximation plus one Newton step (exact remainder, one fused
+//          multiply-add).  About 20 instructions per element, HBM-bound, and on
+//          the full 32768 x 14336 bf16 configuration bit-identical to MATH 0
+//          and to the PyTorch CPU reference (the rounding of silu to bf16
+//          hides the last-bit fp32 differences).
+// 16-bit dtypes use MATH 1; fp32, whose results are not rounded again, uses MATH 0.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+template <int MATH>
+__device__ __forceinline__ float exp_neg(float a) {
+  if constexpr (MATH == 0) {
+    return expf(-a);
+  } else {
+    constexpr float kNegLog2e = -1.4426950216293335f;       // fp32(-log2(e))
+    constexpr float kNegLog2eLo = -1.9259629911266175e-8f;  // -log2(e) - fp32(-log2(e))
+    // |a| <= 88 keeps every intermediate finite (exp(88) < 2^127); beyond that the quotient
+    // below is 0 or a itself whatever the exponential is.  A NaN a becomes -88 here and is
+    // restored by the multiplication with a in silu_f32.
+    const float ac = fminf(fmaxf(a, -88.0f), 88.0f);
+    const float t = __fmul_rn(ac, kNegLog2e);
+    float lo = __fmaf_rn(ac, kNegLog2e, -t);  // what the rounding of t dropped
+    lo = __fmaf_rn(ac, kNegLog2eLo, lo);
+    const float e = ex2_approx(t);
+    return __fmaf_rn(e, __fmul_rn(lo, 0.6931471805599453f), e);  // 2^(t + lo) ~ 2^t * (1 + lo*ln 2)
+  }
+}
+template <int MATH>
+__device__ __forceinline__ float silu_f32(float a) {
+  const float d = __fadd_rn(1.0f, exp_neg<MATH>(a));
+  if constexpr (MATH == 0) {
+    return __fdiv_rn(a, d);
+  } else {
+    const float r = rcp_approx(d);  // 0 once d exceeds 2^126
+    const float q = __fmul_rn(a, r);
+    const float rem = __fmaf_rn(-q, d, a);
+    const float q1 = __fmaf_rn(rem, r, q);
+    // a = +inf: q = inf is the answer and the remainder is NaN.  a = -inf: d >= 2^126, the
+    // reciprocal flushes to 0 and q = -inf * 0 = NaN, as in the reference (-inf / inf).
+    return (rem != rem) ? q : q1;
+  }
+}
 
 template <typename T>
 __device__ __forceinline__ float swiglu_one(float a, float b) {
-  return Num<T>::rt(__fmul_rn(Num<T>::rt(silu_f32(a)), b));
-}
-
-// Two neighbouring elements at once, so that each rounding to T is one packed conversion.
-template <typename T>
-__device__ __forceinline__ void swiglu_two(float& a0, float& a1, float b0, float b1) {
-  a0 = silu_f32(a0);
-  a1 = silu_f32(a1);
-  Num<T>::round2(a0, a1);
-  a0 = __fmul_rn(a0, b0);
-  a1 = __fmul_rn(a1, b1);  // the final rounding to T happens in the pack
+  return Num<T>::rt(__fmul_rn(Num<T>::rt(silu_f32<0>(a)), b));
 }
 
 // Each thread owns UNROLL 128-bit words, THREADS words apart, so a warp always
 // touches 512 contiguous bytes of one row.  (row, word) of the first word comes
 // from one division; the rest follow by carry.
-template <typename T, int UNROLL, typename Index>
+template <typename T, int UNROLL, typename Index, int MATH>
 __global__ void __launch_bounds__(256)
 swiglu_vec_kernel(const T* a, const T* b, T* out, Index total_words, Index words_per_row,
                   int64_t lda, int64_t ldb, int64_t ldo) {
   constexpr int V = Num<T>::kVec;
   constexpr int THREADS = 256;
+  pdl_prologue();
   const Index first = static_cast<Index>(blockIdx.x) * (THREADS * UNROLL) + threadIdx.x;
   Index row = first / words_per_row;
   Index word = first - row * words_per_row;
@@ -71,12 +117,27 @@ swiglu_vec_kernel(const T* a, const T* b, T* out, Index total_words, Index words
   }
 #pragma unroll
   for (int u = 0; u < UNROLL; ++u) {
-    float fa[V], fb[V];
-    Num<T>::unpack(va[u], fa);
-    Num<T>::unpack(vb[u], fb);
+    if constexpr (sizeof(T) == 4) {
+      float fa[V], fb[V];
+      Num<T>::unpack(va[u], fa);
+      Num<T>::unpack(vb[u], fb);
 #pragma unroll
-    for (int j = 0; j < V; j += 2) swiglu_two<T>(fa[j], fa[j + 1], fb[j], fb[j + 1]);
-    if (ok[u]) st_stream(out + off_o[u], Num<T>::pack(fa));
+      for (int j = 0; j < V; ++j) fa[j] = __fmul_rn(silu_f32<MATH>(fa[j]), fb[j]);
+      if (ok[u]) st_stream(out + off_o[u], Num<T>::pack(fa));
+    } else {
+      // 16-bit: silu of a pair in fp32, one packed rounding to T, then the packed product with
+      // the untouched word of b (rounded once, as the reference's 16-bit multiply is)
+      const uint32_t wa[4] = {va[u].x, va[u].y, va[u].z, va[u].w};
+      const uint32_t wb[4] = {vb[u].x, vb[u].y, vb[u].z, vb[u].w};
+      uint32_t wo[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float lo, hi;
+        Num<T>::unpack2(wa[j], lo, hi);
+        wo[j] = Num<T>::mul2(Num<T>::pack2(silu_f32<MATH>(lo), silu_f32<MATH>(hi)), wb[j]);
+      }
+      if (ok[u]) st_stream(out + off_o[u], make_uint4(wo[0], wo[1], wo[2], wo[3]));
+    }
   }
 }
 
@@ -85,6 +146,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 swiglu_scalar_kernel(const T* a, const T* b, T* out, int64_t rows, int64_t cols,
                      int64_t lda, int64_t ldb, int64_t ldo) {
+  pdl_prologue();
   const int64_t total = rows * cols;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -110,20 +172,21 @@ int run(const void* a, const void* b, void* out, int64_t rows, int64_t cols,
     const int64_t total = n_rows * wpr;
     const int64_t grid = ceil_div(total, 256 * UNROLL);
     if (grid > 0x7fffffffLL) return fail(B200_ERR_SHAPE, "b200_swiglu: problem too large for one launch");
+    constexpr int MATH = sizeof(T) == 4 ? 0 : 1;
     if (total < 0x7fffffffLL) {
-      swiglu_vec_kernel<T, UNROLL, uint32_t><<<static_cast<unsigned>(grid), 256, 0, st>>>(
-          static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), static_cast<uint32_t>(total),
-          static_cast<uint32_t>(wpr), lda, ldb, ldo);
+      launch(swiglu_vec_kernel<T, UNROLL, uint32_t, MATH>, static_cast<unsigned>(grid), 256, 0, st,
+             static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), static_cast<uint32_t>(total),
+             static_cast<uint32_t>(wpr), lda, ldb, ldo);
     } else {
-      swiglu_vec_kernel<T, UNROLL, uint64_t><<<static_cast<unsigned>(grid), 256, 0, st>>>(
-          static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), static_cast<uint64_t>(total),
-          static_cast<uint64_t>(wpr), lda, ldb, ldo);
+      launch(swiglu_vec_kernel<T, UNROLL, uint64_t, MATH>, static_cast<unsigned>(grid), 256, 0, st,
+             static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), static_cast<uint64_t>(total),
+             static_cast<uint64_t>(wpr), lda, ldb, ldo);
     }
     return after_launch("swiglu_vec_kernel");
   }
   const int64_t want = ceil_div(rows * cols, 256);
   const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
-  swiglu_scalar_kernel<T><<<static_cast<unsigned>(want < cap ? want : cap), 256, 0, st>>>(
+  launch(swiglu_scalar_kernel<T>, static_cast<unsigned>(want < cap ? want : cap), 256, 0, st,
       static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), rows, cols, lda, ldb, ldo);
   return after_launch("swiglu_scalar_kernel");
 }
