@@ -252,6 +252,45 @@ def bench_moe(device, peak_gbs: float, sampler, scale: float = 1.0, fixed_steps:
     return out
 
 
+def bench_moe_expert_parallel(device, world: int, rank: int, dist, steps: int = 20, warmup: int = 3) -> dict:
+    """Config 5 sharded over the ranks: 65536 / world tokens and 64 / world experts per GPU.
+
+    One step = dispatch (route, index, permute, all-to-all, reorder) + combine (reorder, all-to-all,
+    weighted unpermute); the expert MLPs between the two are not part of this path.  Strong scaling:
+    the job's token count is fixed.  Time is the max over ranks of the CUDA-event time per step."""
+    from popcorn_b200 import workloads
+    from popcorn_b200.expert_parallel import ExpertParallel
+
+    w = workloads.moe_bf16().shard(rank, world)
+    x, logits = w.inputs["x"].to(device), w.inputs["router_logits"].to(device)
+    ep = ExpertParallel(w.args["experts"], w.args["top_k"])
+    state = None
+    for _ in range(warmup):
+        state = ep.dispatch(x, logits)
+        ep.combine(state.rows, state)
+    torch.cuda.synchronize(device)
+    dist.barrier()
+    torch.cuda.synchronize(device)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        state = ep.dispatch(x, logits)
+        ep.combine(state.rows, state)
+    end.record()
+    torch.cuda.synchronize(device)
+    ms = torch.tensor([start.elapsed_time(end) / steps], device=device, dtype=torch.float64)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+    hidden_bytes = x.shape[1] * x.element_size()
+    sent_remote = (sum(state.send_counts) - state.send_counts[rank]) * hidden_bytes
+    link = torch.tensor([float(sent_remote)], device=device, dtype=torch.float64)
+    dist.all_reduce(link, op=dist.ReduceOp.MAX)
+    return {"ms": round(ms, 4), "tokens_per_s": round(65536 / (ms * 1e-3), 1), "scaling": "strong (65536 tokens over all ranks)",
+            "tokens_per_rank": int(x.shape[0]), "experts_per_rank": ep.local_experts,
+            "nvlink_bytes_out_per_rank_per_exchange": int(link.item()), "exchanges_per_step": 2,
+            "exchange": "NCCL all_to_all_single with split sizes"}
+
+
 # ------------------------------------------------------------ CPU baseline --
 
 def cpu_reference_fn(key: str, fraction: float):
@@ -442,6 +481,10 @@ def main() -> None:
         per_op["moe_bf16"] = bench_moe(device, peak_gbs, sampler)
     if dist is not None:
         dist.barrier()
+        if not args.skip_per_op:
+            ep_result = bench_moe_expert_parallel(device, world, rank, dist)
+            if rank == 0:
+                per_op["moe_bf16_expert_parallel"] = ep_result
 
     if rank == 0:
         clocks = sampler.finish()

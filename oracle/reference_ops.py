@@ -128,6 +128,14 @@ def moe_permute(x: Tensor, indices: Tensor, experts: int) -> tuple[Tensor, Tenso
     return rows, counts, offsets, perm, pos
 
 
+def moe_scatter_rows(x: Tensor, pos: Tensor) -> Tensor:
+    """rows[pos[t, k]] = x[t]: the same gather written from the token side."""
+    tokens, top_k = pos.shape
+    rows = torch.empty((tokens * top_k, x.shape[1]), dtype=x.dtype)
+    rows[pos.reshape(-1).to(torch.int64)] = x.repeat_interleave(top_k, dim=0)
+    return rows
+
+
 def moe_gather(x: Tensor, src_rows: Tensor) -> Tensor:
     return x.index_select(0, src_rows.to(torch.int64))
 

@@ -15,7 +15,7 @@ Signatures served (names and order are popcorn's):
   swiglu(a, b)                                             src/popcorn/kernels/swiglu.py:10
 and the MoE steps popcorn only has fused inside `momoe`
 (src/popcorn/kernels/momoe.py:47-53, src/popcorn/impls/momoe_tl.py:1071-1161):
-  moe_route, moe_index, moe_permute, moe_gather, moe_unpermute.
+  moe_route, moe_index, moe_scatter_rows, moe_permute, moe_gather, moe_unpermute.
 """
 
 from __future__ import annotations
@@ -257,24 +257,34 @@ def moe_index(indices: Tensor, experts: int) -> tuple[Tensor, Tensor, Tensor, Te
     return counts, offsets, perm, pos
 
 
+def moe_scatter_rows(x: Tensor, pos: Tensor) -> Tensor:
+    """rows[pos[t, k]] = x[t] for every slot k: each token row is read once and written top_k times.
+
+    `pos` is the inverse permutation from moe_index; a negative entry skips that slot."""
+    device = _require_cuda(x, pos)
+    _forbid_grad(x)
+    code = _dtype_code(x, "moe_scatter_rows")
+    if x.dim() != 2 or pos.dim() != 2 or pos.shape[0] != x.shape[0] or pos.dtype != torch.int32:
+        raise ValueError("moe_scatter_rows: x must be [tokens, hidden] and pos int32 [tokens, top_k]")
+    tokens, hidden = x.shape
+    top_k = pos.shape[1]
+    x2, ldx = _rows(x)
+    rows = torch.empty((tokens * top_k, hidden), dtype=x.dtype, device=device)
+    with torch.cuda.device(device):
+        _lib.call("b200_moe_permute", _ptr(x2), _ptr(pos.contiguous()), _ptr(rows), tokens, top_k, hidden, ldx, max(hidden, 1), code, _stream(device))
+    return rows
+
+
 def moe_permute(x: Tensor, indices: Tensor, experts: int) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
     """Gather token rows into expert-contiguous order (momoe_tl.py:156-158, 408-476).
 
     x: [tokens, hidden]; indices: int32 [tokens, top_k].  Returns (rows [tokens*top_k, hidden],
     counts, offsets, perm, pos); rows[p] = x[perm[p]], pairs sorted stably by expert."""
-    device = _require_cuda(x, indices)
-    _forbid_grad(x)
-    code = _dtype_code(x, "moe_permute")
+    _require_cuda(x, indices)
     if x.dim() != 2 or indices.dim() != 2 or indices.shape[0] != x.shape[0]:
         raise ValueError("moe_permute: x must be [tokens, hidden] and indices [tokens, top_k]")
     counts, offsets, perm, pos = moe_index(indices, experts)
-    tokens, hidden = x.shape
-    top_k = indices.shape[1]
-    x2, ldx = _rows(x)
-    rows = torch.empty((tokens * top_k, hidden), dtype=x.dtype, device=device)
-    with torch.cuda.device(device):
-        _lib.call("b200_moe_permute", _ptr(x2), _ptr(pos), _ptr(rows), tokens, top_k, hidden, ldx, max(hidden, 1), code, _stream(device))
-    return rows, counts, offsets, perm, pos
+    return moe_scatter_rows(x, pos), counts, offsets, perm, pos
 
 
 def moe_gather(x: Tensor, src_rows: Tensor) -> Tensor:

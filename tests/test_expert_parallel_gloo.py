@@ -1,0 +1,108 @@
+"""Expert-parallel dispatch / combine over world_size-2 (and 4) gloo process groups on CPU.
+
+The exchange logic (split sizes, all-to-all, reorder, inverse) is what is under
+test; the per-rank compute steps are the CPU oracle's, injected through
+`local_ops`.  The result must equal the single-process oracle bit for bit:
+the concatenation of the ranks' expert-major rows is the global stable
+permutation, and combine() returns what a single-process unpermute returns.
+"""
+
+import os
+import socket
+import types
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import reference_ops as oracle
+from popcorn_b200.expert_parallel import ExpertParallel, exchange_plan, expand_segments
+
+CPU_OPS = types.SimpleNamespace(
+    moe_route=oracle.moe_route, moe_index=oracle.moe_index, moe_scatter_rows=oracle.moe_scatter_rows,
+    moe_gather=oracle.moe_gather, moe_unpermute=oracle.moe_unpermute,
+)
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _inputs(tokens, hidden, experts, seed=11):
+    gen = torch.Generator().manual_seed(seed)
+    return torch.randn(tokens, hidden, generator=gen).to(torch.bfloat16), torch.randn(tokens, experts, generator=gen)
+
+
+def _worker(rank, world, port, tokens, hidden, experts, top_k, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        x, logits = _inputs(tokens, hidden, experts)
+        lo, hi = tokens * rank // world, tokens * (rank + 1) // world
+        ep = ExpertParallel(experts, top_k, local_ops=CPU_OPS)
+        state = ep.dispatch(x[lo:hi], logits[lo:hi])
+        # "expert computation": scale every row by (1 + its global expert id / 8)
+        scale = torch.ones(state.rows.shape[0])
+        for e in range(ep.local_experts):
+            a, b = int(state.expert_offsets[e]), int(state.expert_offsets[e + 1])
+            scale[a:b] = 1 + (rank * ep.local_experts + e) / 8
+        processed = (state.rows.float() * scale[:, None]).to(torch.bfloat16)
+        y = ep.combine(processed, state)
+        out[rank] = (state.rows, state.expert_offsets, y, state.send_counts, state.recv_counts)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,tokens,experts,top_k", [(2, 64, 8, 2), (2, 37, 4, 3), (4, 50, 8, 4), (2, 16, 2, 1)])
+def test_dispatch_and_combine_equal_the_single_process_result(world, tokens, experts, top_k):
+    hidden = 24
+    manager = mp.Manager()
+    out = manager.dict()
+    mp.spawn(_worker, args=(world, _free_port(), tokens, hidden, experts, top_k, out), nprocs=world, join=True)
+
+    x, logits = _inputs(tokens, hidden, experts)
+    indices, weights = oracle.moe_route(logits, top_k)
+    rows, counts, offsets, perm, pos = oracle.moe_permute(x, indices, experts)
+    per_rank = experts // world
+    for rank in range(world):
+        got_rows, got_offsets, _, send_counts, recv_counts = out[rank]
+        lo, hi = int(offsets[rank * per_rank]), int(offsets[(rank + 1) * per_rank])
+        assert torch.equal(got_rows, rows[lo:hi]), f"rank {rank}: rows are not the global stable permutation"
+        assert torch.equal(got_offsets, offsets[rank * per_rank : (rank + 1) * per_rank + 1] - lo)
+        assert sum(recv_counts) == hi - lo
+        assert sum(send_counts) == (tokens * (rank + 1) // world - tokens * rank // world) * top_k
+    expert_of_row = torch.repeat_interleave(torch.arange(experts), counts.long())
+    processed = (rows.float() * (1 + expert_of_row / 8)[:, None]).to(torch.bfloat16)
+    want = oracle.moe_unpermute(processed, weights, pos)
+    got = torch.cat([out[rank][2] for rank in range(world)])
+    assert torch.equal(got, want)
+
+
+def test_exchange_plan_small_example():
+    # 2 ranks, 4 experts (2 per rank); counts_all[source, expert]
+    counts_all = torch.tensor([[3, 0, 2, 1], [1, 4, 0, 2]], dtype=torch.int32)
+    send, recv, start, length, offsets = exchange_plan(counts_all, rank=0)
+    assert send == [3, 3] and recv == [3, 5]
+    # arrived on rank 0: [src0: e0 x3, e1 x0 | src1: e0 x1, e1 x4]; output order: e0(src0, src1), e1(src0, src1)
+    assert start.tolist() == [0, 3, 3, 4] and length.tolist() == [3, 1, 0, 4]
+    assert offsets.tolist() == [0, 4, 8]
+    assert expand_segments(start, length, 8, "cpu").tolist() == [0, 1, 2, 3, 4, 5, 6, 7]
+    send, recv, start, length, offsets = exchange_plan(counts_all, rank=1)
+    assert send == [5, 2] and recv == [3, 2]
+    assert start.tolist() == [0, 3, 2, 3] and length.tolist() == [2, 0, 1, 2]
+    assert expand_segments(start, length, 5, "cpu").tolist() == [0, 1, 2, 3, 4]
+    with pytest.raises(ValueError):
+        exchange_plan(torch.zeros(3, 4, dtype=torch.int32), 0)
+
+
+def test_expand_segments_reorders():
+    # rank 0 of 2 owns experts 0 and 1.  arrived = [src0: e0 e0 e1 | src1: e0 e1 e1]
+    # -> output e0(src0 x2, src1 x1), e1(src0 x1, src1 x2)
+    counts_all = torch.tensor([[2, 1, 5, 0], [1, 2, 0, 7]], dtype=torch.int32)
+    _, recv, start, length, offsets = exchange_plan(counts_all, rank=0)
+    assert recv == [3, 3]
+    assert expand_segments(start, length, 6, "cpu").tolist() == [0, 1, 3, 2, 4, 5]
+    assert offsets.tolist() == [0, 3, 6]
