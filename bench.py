@@ -252,7 +252,7 @@ def bench_moe(device, peak_gbs: float, sampler, scale: float = 1.0, fixed_steps:
     return out
 
 
-def bench_moe_expert_parallel(device, world: int, rank: int, dist, steps: int = 20, warmup: int = 3) -> dict:
+def bench_moe_expert_parallel(device, world: int, rank: int, dist, exchange: str, steps: int = 20, warmup: int = 3) -> dict:
     """Config 5 sharded over the ranks: 65536 / world tokens and 64 / world experts per GPU.
 
     One step = dispatch (route, index, permute, all-to-all, reorder) + combine (reorder, all-to-all,
@@ -263,11 +263,11 @@ def bench_moe_expert_parallel(device, world: int, rank: int, dist, steps: int = 
 
     w = workloads.moe_bf16().shard(rank, world)
     x, logits = w.inputs["x"].to(device), w.inputs["router_logits"].to(device)
-    ep = ExpertParallel(w.args["experts"], w.args["top_k"])
+    ep = ExpertParallel(w.args["experts"], w.args["top_k"], exchange=exchange)
     state = None
     for _ in range(warmup):
         state = ep.dispatch(x, logits)
-        ep.combine(state.rows, state)
+        ep.combine(state.rows if exchange == "nccl" else state.out_rows, state)
     torch.cuda.synchronize(device)
     dist.barrier()
     torch.cuda.synchronize(device)
@@ -275,7 +275,7 @@ def bench_moe_expert_parallel(device, world: int, rank: int, dist, steps: int = 
     start.record()
     for _ in range(steps):
         state = ep.dispatch(x, logits)
-        ep.combine(state.rows, state)
+        ep.combine(state.rows if exchange == "nccl" else state.out_rows, state)
     end.record()
     torch.cuda.synchronize(device)
     ms = torch.tensor([start.elapsed_time(end) / steps], device=device, dtype=torch.float64)
@@ -288,7 +288,9 @@ def bench_moe_expert_parallel(device, world: int, rank: int, dist, steps: int = 
     return {"ms": round(ms, 4), "tokens_per_s": round(65536 / (ms * 1e-3), 1), "scaling": "strong (65536 tokens over all ranks)",
             "tokens_per_rank": int(x.shape[0]), "experts_per_rank": ep.local_experts,
             "nvlink_bytes_out_per_rank_per_exchange": int(link.item()), "exchanges_per_step": 2,
-            "exchange": "NCCL all_to_all_single with split sizes"}
+            "nvlink_gb_s_per_direction": round(link.item() * 2 / (ms * 1e-3) / 1e9, 1),
+            "exchange": "NCCL all_to_all_single with split sizes" if exchange == "nccl"
+            else "fused: permute kernel stores into peer memory, unpermute kernel loads from peer memory"}
 
 
 # ------------------------------------------------------------ CPU baseline --
@@ -364,6 +366,11 @@ def run_reference_arm(args) -> None:
 # -------------------------------------------------------------------- main --
 
 def main() -> None:
+    # Libraries (NCCL among them) may print to stdout; the contract is ONE JSON line there.
+    # Keep the real stdout aside and point fd 1 at stderr until the line is printed.
+    real_stdout = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    sys.stdout = real_stdout
     parser = argparse.ArgumentParser(description=__doc__.splitlines()[0])
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=200)
@@ -482,9 +489,13 @@ def main() -> None:
     if dist is not None:
         dist.barrier()
         if not args.skip_per_op:
-            ep_result = bench_moe_expert_parallel(device, world, rank, dist)
-            if rank == 0:
-                per_op["moe_bf16_expert_parallel"] = ep_result
+            for exchange in ("nccl", "p2p"):
+                try:
+                    ep_result = bench_moe_expert_parallel(device, world, rank, dist, exchange)
+                except Exception as error:  # symmetric memory may be unavailable on a given box: report, do not hide
+                    ep_result = {"error": f"{type(error).__name__}: {error}"}
+                if rank == 0:
+                    per_op[f"moe_bf16_expert_parallel_{exchange}"] = ep_result
 
     if rank == 0:
         clocks = sampler.finish()

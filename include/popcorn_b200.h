@@ -223,6 +223,46 @@ int b200_moe_unpermute(const void* rows, const float* weights, const int32_t* po
                        int64_t tokens, int64_t top_k, int64_t hidden,
                        int64_t ldrows, int64_t ldy, int dtype, void* stream);
 
+/*
+ * Expert-parallel forms.  The reference has no distributed code (its momoe op is
+ * single-GPU, src/popcorn/kernels/momoe.py:34-53); these are the permute and
+ * unpermute steps of src/popcorn/impls/momoe_tl.py:156-158 / :295-304 with the
+ * rows living in SEVERAL buffers: entry r of `bufs` (a HOST array of n_bufs <= 16
+ * device pointers) is rank r's exchange buffer, mapped into the calling process
+ * (CUDA peer / symmetric memory).  Rows cross NVLink inside the kernel, as
+ * ordinary 128-bit stores (permute) or loads (unpermute); the caller orders the
+ * ranks around the call (all writes landed before anyone reads; all reads done
+ * before anyone overwrites).
+ */
+
+/*
+ * For each (token, slot) pair: dst_rank = indices / experts_per_rank and
+ * dst_row = dst_base[expert] + (pos - local_offsets[expert]), the pair's row in the
+ * owning rank's buffer.  dst_base[e] is the row at which this rank's block for
+ * expert e starts in that buffer (from the all-gathered counts); local_offsets is
+ * the `offsets` output of b200_moe_index on this rank.  All arrays int32;
+ * dst_rank, dst_row: [tokens, top_k].
+ */
+int b200_moe_ep_destinations(const int32_t* indices, const int32_t* pos, const int32_t* local_offsets,
+                             const int32_t* dst_base, int64_t tokens, int64_t top_k, int64_t experts,
+                             int64_t experts_per_rank, int32_t* dst_rank, int32_t* dst_row, void* stream);
+
+/* bufs[dst_buf[t, k]][dst_row[t, k], :] = x[t, :]; a negative dst_row skips the slot. */
+int b200_moe_permute_multi(const void* x, const int32_t* dst_buf, const int32_t* dst_row,
+                           void* const* bufs, int64_t n_bufs,
+                           int64_t tokens, int64_t top_k, int64_t hidden,
+                           int64_t ldx, int64_t ldrows, int dtype, void* stream);
+
+/*
+ * y[t, :] = round_T( sum_k weights[t, k] * fp32(bufs[src_buf[t, k]][src_row[t, k], :]) ), accumulated in
+ * ascending (buffer, row) order, which is ascending expert index when buffers hold contiguous expert
+ * blocks in rank order.  Same arithmetic as b200_moe_unpermute.
+ */
+int b200_moe_unpermute_multi(void* const* bufs, int64_t n_bufs, const int32_t* src_buf, const int32_t* src_row,
+                             const float* weights, void* y,
+                             int64_t tokens, int64_t top_k, int64_t hidden,
+                             int64_t ldrows, int64_t ldy, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

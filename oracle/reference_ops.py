@@ -136,6 +136,15 @@ def moe_scatter_rows(x: Tensor, pos: Tensor) -> Tensor:
     return rows
 
 
+def moe_ep_destinations(indices: Tensor, pos: Tensor, local_offsets: Tensor, dst_base: Tensor, experts_per_rank: int) -> tuple[Tensor, Tensor]:
+    """Expert-parallel addressing (no counterpart in the reference, which is single-GPU): the owner rank of
+    each pair's expert and the pair's row in that rank's expert-major buffer."""
+    e = indices.to(torch.int64)
+    dst_rank = torch.div(e, experts_per_rank, rounding_mode="floor")
+    dst_row = dst_base.to(torch.int64)[e] + (pos.to(torch.int64) - local_offsets.to(torch.int64)[e])
+    return dst_rank.to(torch.int32), dst_row.to(torch.int32)
+
+
 def moe_gather(x: Tensor, src_rows: Tensor) -> Tensor:
     return x.index_select(0, src_rows.to(torch.int64))
 

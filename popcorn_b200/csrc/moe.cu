@@ -257,19 +257,37 @@ __device__ __forceinline__ void st_word(W* p, const W& v) { *p = v; }
 template <>
 __device__ __forceinline__ void st_word<uint4>(uint4* p, const uint4& v) { st_stream(p, v); }
 
+// Destination / source buffers of the multi-buffer forms: buffer 0 is this GPU's
+// own memory in the single-GPU entry points; in the expert-parallel ones entry r is
+// rank r's exchange buffer, mapped into this process (peer memory over NVLink).
+constexpr int kMaxBuffers = 16;
+struct BufferTable {
+  void* base[kMaxBuffers];
+};
+
 // One warp per token: read the row once (UNROLL words per lane at a time) and
-// write it to each of its top_k destinations.  Loop bounds are the same for all
-// lanes of a warp, because the destinations travel by shuffle.
+// write it to each of its top_k destinations (buffer dst_buf[t,k], row pos[t,k];
+// dst_buf == nullptr means buffer 0).  Loop bounds are the same for all lanes of
+// a warp, because the destinations travel by shuffle.  With peer buffers in the
+// table this kernel IS the dispatch half of the expert-parallel exchange: each row
+// goes from local HBM straight into the owning rank's memory with ordinary
+// 128-bit stores, with no staging copy and no separate collective.
 template <typename W>
 __global__ void __launch_bounds__(256)
-permute_kernel(const W* __restrict__ x, const int32_t* __restrict__ pos, W* __restrict__ rows,
-               int64_t tokens, int top_k, int words, int64_t ldx, int64_t ldrows) {
+permute_kernel(const W* __restrict__ x, const int32_t* __restrict__ pos, const int32_t* __restrict__ dst_buf,
+               const BufferTable bufs, int64_t tokens, int top_k, int words, int64_t ldx, int64_t ldrows) {
   pdl_prologue();
   constexpr int UNROLL = 4;
   const int lane = threadIdx.x & 31;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   if (t >= tokens) return;  // whole warps leave together
-  const int my_dst = lane < top_k ? pos[t * top_k + lane] : -1;
+  int my_dst = -1, my_buf = 0;
+  if (lane < top_k) {
+    my_dst = pos[t * top_k + lane];
+    if (dst_buf != nullptr) my_buf = dst_buf[t * top_k + lane];
+  }
+  // destination row address of slot `lane`
+  W* my_out = my_dst >= 0 ? static_cast<W*>(bufs.base[my_buf]) + static_cast<int64_t>(my_dst) * ldrows : nullptr;
   const W* src = x + t * ldx;
   for (int w0 = 0; w0 < words; w0 += 32 * UNROLL) {
     W v[UNROLL];
@@ -277,9 +295,8 @@ permute_kernel(const W* __restrict__ x, const int32_t* __restrict__ pos, W* __re
     for (int u = 0; u < UNROLL; ++u)
       if (w0 + lane + 32 * u < words) v[u] = ld_word<W>(src + w0 + lane + 32 * u);
     for (int k = 0; k < top_k; ++k) {
-      const int dst = __shfl_sync(kFull, my_dst, k);
-      if (dst < 0) continue;
-      W* out = rows + static_cast<int64_t>(dst) * ldrows;
+      W* out = reinterpret_cast<W*>(__shfl_sync(kFull, reinterpret_cast<unsigned long long>(my_out), k));
+      if (out == nullptr) continue;
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u)
         if (w0 + lane + 32 * u < words) st_word<W>(out + w0 + lane + 32 * u, v[u]);
@@ -314,15 +331,19 @@ gather_kernel(const W* __restrict__ x, const int32_t* __restrict__ src_row, W* _
 
 // -------------------------------------------------------------- unpermute --
 
-// One warp per token.  Lanes < top_k hold (pos, weight); the slots are visited
-// in ascending pos, which is ascending expert index.  The sorted row offsets and
-// weights sit in shared memory (one line per warp).  Rows are fetched eight at a
+// One warp per token.  Lanes < top_k hold (buffer, pos, weight); the slots are
+// visited in ascending (buffer, pos), which is ascending expert index.  The sorted
+// row addresses and weights sit in shared memory (one line per warp).  With peer
+// buffers in the table this kernel IS the combine half of the expert-parallel
+// exchange: the token's owner reads the expert outputs straight out of the other
+// ranks' memory with ordinary 128-bit loads while it accumulates.  Rows are fetched eight at a
 // time, one 128-bit word per lane, and the NEXT batch of eight is already in
 // flight while the current one is accumulated.  VEC: 128-bit words.
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(256, 2)
-unpermute_kernel(const T* __restrict__ rows, const float* __restrict__ weights, const int32_t* __restrict__ pos,
-                 T* __restrict__ y, int64_t tokens, int top_k, int hidden, int64_t ldrows, int64_t ldy) {
+unpermute_kernel(const BufferTable bufs, const int32_t* __restrict__ src_buf, const float* __restrict__ weights,
+                 const int32_t* __restrict__ pos, T* __restrict__ y, int64_t tokens, int top_k, int hidden,
+                 int64_t ldrows, int64_t ldy) {
   pdl_prologue();
   constexpr int V = VEC ? Num<T>::kVec : 1;
   constexpr int KB = 8;  // rows fetched together
@@ -333,24 +354,28 @@ unpermute_kernel(const T* __restrict__ rows, const float* __restrict__ weights, 
   const int wid = threadIdx.x >> 5;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + wid;
   if (t >= tokens) return;  // whole warps leave together; no block-wide barrier below
-  int my_pos = -1;
+  int my_pos = -1, my_buf = 0;
   float my_w = 0.f;
   if (lane < top_k) {
     my_pos = pos[t * top_k + lane];
     my_w = weights[t * top_k + lane];
+    if (src_buf != nullptr) my_buf = src_buf[t * top_k + lane];
   }
-  // rank of my slot among the valid ones (equal pos values keep slot order)
+  // rank of my slot among the valid ones, by (buffer, row); equal keys keep slot order.
+  // Buffers hold contiguous expert blocks in rank order, so this is ascending expert index.
   int rank = 0;
   int valid = 0;
   for (int j = 0; j < top_k; ++j) {
     const int pj = __shfl_sync(kFull, my_pos, j);
+    const int bj = __shfl_sync(kFull, my_buf, j);
     if (pj >= 0) {
       ++valid;
-      if (pj < my_pos || (pj == my_pos && j < lane)) ++rank;
+      if (bj < my_buf || (bj == my_buf && (pj < my_pos || (pj == my_pos && j < lane)))) ++rank;
     }
   }
   if (my_pos >= 0) {
-    s_off[wid][rank] = static_cast<int64_t>(my_pos) * ldrows;
+    // absolute byte address of the row
+    s_off[wid][rank] = reinterpret_cast<int64_t>(bufs.base[my_buf]) + static_cast<int64_t>(my_pos) * ldrows * static_cast<int64_t>(sizeof(T));
     s_w[wid][rank] = my_w;
   }
   __syncwarp();
@@ -370,7 +395,7 @@ unpermute_kernel(const T* __restrict__ rows, const float* __restrict__ weights, 
     for (int k = 0; k < KB; ++k) {
       const int kk = b * KB + k;
       if (kk < valid && w < words) {
-        const T* src = rows + s_off[wid][kk] + static_cast<int64_t>(w) * V;
+        const T* src = reinterpret_cast<const T*>(s_off[wid][kk]) + static_cast<int64_t>(w) * V;
         if constexpr (VEC) buf[k] = ld_stream(src);
         else buf[k] = *src;
       }
@@ -531,13 +556,14 @@ extern "C" int b200_moe_index(const int32_t* indices, int64_t tokens, int64_t to
   return B200_OK;
 }
 
+namespace b200 {
 namespace {
 template <typename W>
-int launch_permute(const void* x, const int32_t* pos, void* rows, int64_t tokens, int top_k, int64_t row_bytes,
-                   int64_t ldx_bytes, int64_t ldr_bytes, cudaStream_t st) {
+int launch_permute(const void* x, const int32_t* pos, const int32_t* dst_buf, const BufferTable& bufs, int64_t tokens,
+                   int top_k, int64_t row_bytes, int64_t ldx_bytes, int64_t ldr_bytes, cudaStream_t st) {
   launch(permute_kernel<W>, static_cast<unsigned>(ceil_div(tokens, 8)), 256, 0, st,
-      static_cast<const W*>(x), pos, static_cast<W*>(rows), tokens, top_k, static_cast<int>(row_bytes / sizeof(W)),
-      ldx_bytes / static_cast<int64_t>(sizeof(W)), ldr_bytes / static_cast<int64_t>(sizeof(W)));
+         static_cast<const W*>(x), pos, dst_buf, bufs, tokens, top_k, static_cast<int>(row_bytes / sizeof(W)),
+         ldx_bytes / static_cast<int64_t>(sizeof(W)), ldr_bytes / static_cast<int64_t>(sizeof(W)));
   return after_launch("permute_kernel");
 }
 template <typename W>
@@ -549,29 +575,62 @@ int launch_gather(const void* x, const int32_t* src, void* out, int64_t n_rows, 
   return after_launch("gather_kernel");
 }
 }  // namespace
+}  // namespace b200
 
-extern "C" int b200_moe_permute(const void* x, const int32_t* pos, void* rows,
-                                int64_t tokens, int64_t top_k, int64_t hidden,
-                                int64_t ldx, int64_t ldrows, int dtype, void* stream) {
-  if (!dtype_ok(dtype)) return fail(B200_ERR_DTYPE, "%s: unsupported dtype %d", __func__, dtype);
+namespace b200 {
+namespace {
+// Shared body of b200_moe_permute and b200_moe_permute_multi.
+int permute_impl(const char* fn, const void* x, const int32_t* dst_buf, const int32_t* pos, void* const* bufs, int64_t n_bufs,
+                 int64_t tokens, int64_t top_k, int64_t hidden, int64_t ldx, int64_t ldrows, int dtype, void* stream) {
+  if (!dtype_ok(dtype)) return fail(B200_ERR_DTYPE, "%s: unsupported dtype %d", fn, dtype);
   if (tokens < 0 || hidden < 0 || top_k < 1 || top_k > kMaxTopK)
-    return fail(B200_ERR_SHAPE, "%s: need tokens, hidden >= 0 and 1 <= top_k <= %d", __func__, kMaxTopK);
-  if (ldx < hidden || ldrows < hidden) return fail(B200_ERR_SHAPE, "%s: leading dimension smaller than hidden", __func__);
-  if (tokens > 0x7fffffffLL * 8 || hidden > 0x7fffffffLL / 4) return fail(B200_ERR_SHAPE, "%s: problem too large", __func__);
+    return fail(B200_ERR_SHAPE, "%s: need tokens, hidden >= 0 and 1 <= top_k <= %d", fn, kMaxTopK);
+  if (n_bufs < 1 || n_bufs > kMaxBuffers) return fail(B200_ERR_SHAPE, "%s: need 1 <= n_bufs <= %d", fn, kMaxBuffers);
+  if (ldx < hidden || ldrows < hidden) return fail(B200_ERR_SHAPE, "%s: leading dimension smaller than hidden", fn);
+  if (tokens > 0x7fffffffLL * 8 || hidden > 0x7fffffffLL / 4) return fail(B200_ERR_SHAPE, "%s: problem too large", fn);
   if (tokens == 0 || hidden == 0) return B200_OK;
   B200_REQUIRE_PTR(x);
   B200_REQUIRE_PTR(pos);
-  B200_REQUIRE_PTR(rows);
+  B200_REQUIRE_PTR(bufs);
+  if (n_bufs > 1) B200_REQUIRE_PTR(dst_buf);
   const int64_t es = static_cast<int64_t>(dtype_size(dtype));
-  if (!aligned(x, es) || !aligned(rows, es) || !aligned(pos, 4))
-    return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to the element size", __func__);
+  BufferTable table{};
+  bool all16 = true;
+  for (int64_t i = 0; i < n_bufs; ++i) {
+    if (bufs[i] == nullptr) return fail(B200_ERR_NULL_POINTER, "%s: bufs[%lld] is NULL", fn, (long long)i);
+    if (!aligned(bufs[i], es)) return fail(B200_ERR_ALIGNMENT, "%s: bufs[%lld] not aligned to the element size", fn, (long long)i);
+    all16 = all16 && aligned(bufs[i], 16);
+    table.base[i] = bufs[i];
+  }
+  if (!aligned(x, es) || !aligned(pos, 4) || (dst_buf && !aligned(dst_buf, 4)))
+    return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to the element size", fn);
   if (int rc = check_device()) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int K = static_cast<int>(top_k);
   const int64_t rb = hidden * es, lxb = ldx * es, lrb = ldrows * es;
-  if (rows_aligned<uint4>(x, rows, rb, lxb, lrb)) return launch_permute<uint4>(x, pos, rows, tokens, K, rb, lxb, lrb, st);
-  if (rows_aligned<uint32_t>(x, rows, rb, lxb, lrb)) return launch_permute<uint32_t>(x, pos, rows, tokens, K, rb, lxb, lrb, st);
-  return launch_permute<uint16_t>(x, pos, rows, tokens, K, rb, lxb, lrb, st);
+  const void* probe = all16 ? x : static_cast<const char*>(x) + 4;  // a table entry that is only 4-byte aligned rules out 16-byte words
+  if (rows_aligned<uint4>(probe, x, rb, lxb, lrb)) return launch_permute<uint4>(x, pos, dst_buf, table, tokens, K, rb, lxb, lrb, st);
+  bool all4 = true;
+  for (int64_t i = 0; i < n_bufs; ++i) all4 = all4 && aligned(bufs[i], 4);
+  if (all4 && rows_aligned<uint32_t>(x, x, rb, lxb, lrb)) return launch_permute<uint32_t>(x, pos, dst_buf, table, tokens, K, rb, lxb, lrb, st);
+  return launch_permute<uint16_t>(x, pos, dst_buf, table, tokens, K, rb, lxb, lrb, st);
+}
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_moe_permute(const void* x, const int32_t* pos, void* rows,
+                                int64_t tokens, int64_t top_k, int64_t hidden,
+                                int64_t ldx, int64_t ldrows, int dtype, void* stream) {
+  void* const one[1] = {rows};
+  if (rows == nullptr && tokens > 0 && hidden > 0) return fail(B200_ERR_NULL_POINTER, "%s: rows is NULL", __func__);
+  return permute_impl(__func__, x, nullptr, pos, one, 1, tokens, top_k, hidden, ldx, ldrows, dtype, stream);
+}
+
+extern "C" int b200_moe_permute_multi(const void* x, const int32_t* dst_buf, const int32_t* dst_row,
+                                      void* const* bufs, int64_t n_bufs,
+                                      int64_t tokens, int64_t top_k, int64_t hidden,
+                                      int64_t ldx, int64_t ldrows, int dtype, void* stream) {
+  return permute_impl(__func__, x, dst_buf, dst_row, bufs, n_bufs, tokens, top_k, hidden, ldx, ldrows, dtype, stream);
 }
 
 extern "C" int b200_moe_gather(const void* x, const int32_t* src_row, void* out,
@@ -596,33 +655,112 @@ extern "C" int b200_moe_gather(const void* x, const int32_t* src_row, void* out,
   return launch_gather<uint16_t>(x, src_row, out, n_rows, rb, lxb, lob, st);
 }
 
-extern "C" int b200_moe_unpermute(const void* rows, const float* weights, const int32_t* pos, void* y,
-                                  int64_t tokens, int64_t top_k, int64_t hidden,
-                                  int64_t ldrows, int64_t ldy, int dtype, void* stream) {
-  if (!dtype_ok(dtype)) return fail(B200_ERR_DTYPE, "%s: unsupported dtype %d", __func__, dtype);
+namespace b200 {
+namespace {
+int unpermute_impl(const char* fn, void* const* bufs, int64_t n_bufs, const int32_t* src_buf, const int32_t* pos,
+                   const float* weights, void* y, int64_t tokens, int64_t top_k, int64_t hidden,
+                   int64_t ldrows, int64_t ldy, int dtype, void* stream) {
+  if (!dtype_ok(dtype)) return fail(B200_ERR_DTYPE, "%s: unsupported dtype %d", fn, dtype);
   if (tokens < 0 || hidden < 0 || top_k < 1 || top_k > kMaxTopK)
-    return fail(B200_ERR_SHAPE, "%s: need tokens, hidden >= 0 and 1 <= top_k <= %d", __func__, kMaxTopK);
-  if (ldrows < hidden || ldy < hidden) return fail(B200_ERR_SHAPE, "%s: leading dimension smaller than hidden", __func__);
-  if (tokens > 0x7fffffffLL * 8 || hidden > 0x7fffffffLL) return fail(B200_ERR_SHAPE, "%s: problem too large", __func__);
+    return fail(B200_ERR_SHAPE, "%s: need tokens, hidden >= 0 and 1 <= top_k <= %d", fn, kMaxTopK);
+  if (n_bufs < 1 || n_bufs > kMaxBuffers) return fail(B200_ERR_SHAPE, "%s: need 1 <= n_bufs <= %d", fn, kMaxBuffers);
+  if (ldrows < hidden || ldy < hidden) return fail(B200_ERR_SHAPE, "%s: leading dimension smaller than hidden", fn);
+  if (tokens > 0x7fffffffLL * 8 || hidden > 0x7fffffffLL) return fail(B200_ERR_SHAPE, "%s: problem too large", fn);
   if (tokens == 0 || hidden == 0) return B200_OK;
-  B200_REQUIRE_PTR(rows);
+  B200_REQUIRE_PTR(bufs);
   B200_REQUIRE_PTR(weights);
   B200_REQUIRE_PTR(pos);
   B200_REQUIRE_PTR(y);
+  if (n_bufs > 1) B200_REQUIRE_PTR(src_buf);
   const size_t es = dtype_size(dtype);
-  if (!aligned(rows, es) || !aligned(y, es) || !aligned(weights, 4) || !aligned(pos, 4))
-    return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to the element size", __func__);
+  BufferTable table{};
+  bool all16 = true;
+  for (int64_t i = 0; i < n_bufs; ++i) {
+    if (bufs[i] == nullptr) return fail(B200_ERR_NULL_POINTER, "%s: bufs[%lld] is NULL", fn, (long long)i);
+    if (!aligned(bufs[i], es)) return fail(B200_ERR_ALIGNMENT, "%s: bufs[%lld] not aligned to the element size", fn, (long long)i);
+    all16 = all16 && aligned(bufs[i], 16);
+    table.base[i] = bufs[i];
+  }
+  if (!aligned(y, es) || !aligned(weights, 4) || !aligned(pos, 4) || (src_buf && !aligned(src_buf, 4)))
+    return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to the element size", fn);
   if (int rc = check_device()) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned grid = static_cast<unsigned>(ceil_div(tokens, 8));
   const int K = static_cast<int>(top_k), H = static_cast<int>(hidden);
   B200_DISPATCH_DTYPE(dtype, T, {
     constexpr int V = Num<T>::kVec;
-    const bool vec = hidden % V == 0 && ldrows % V == 0 && ldy % V == 0 && aligned(rows, 16) && aligned(y, 16);
+    const bool vec = hidden % V == 0 && ldrows % V == 0 && ldy % V == 0 && all16 && aligned(y, 16);
     if (vec)
-      launch(unpermute_kernel<T, true>, grid, 256, 0, st, static_cast<const T*>(rows), weights, pos, static_cast<T*>(y), tokens, K, H, ldrows, ldy);
+      launch(unpermute_kernel<T, true>, grid, 256, 0, st, table, src_buf, weights, pos, static_cast<T*>(y), tokens, K, H, ldrows, ldy);
     else
-      launch(unpermute_kernel<T, false>, grid, 256, 0, st, static_cast<const T*>(rows), weights, pos, static_cast<T*>(y), tokens, K, H, ldrows, ldy);
+      launch(unpermute_kernel<T, false>, grid, 256, 0, st, table, src_buf, weights, pos, static_cast<T*>(y), tokens, K, H, ldrows, ldy);
   });
   return after_launch("unpermute_kernel");
+}
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_moe_unpermute(const void* rows, const float* weights, const int32_t* pos, void* y,
+                                  int64_t tokens, int64_t top_k, int64_t hidden,
+                                  int64_t ldrows, int64_t ldy, int dtype, void* stream) {
+  void* const one[1] = {const_cast<void*>(rows)};
+  if (rows == nullptr && tokens > 0 && hidden > 0) return fail(B200_ERR_NULL_POINTER, "%s: rows is NULL", __func__);
+  return unpermute_impl(__func__, one, 1, nullptr, pos, weights, y, tokens, top_k, hidden, ldrows, ldy, dtype, stream);
+}
+
+extern "C" int b200_moe_unpermute_multi(void* const* bufs, int64_t n_bufs, const int32_t* src_buf, const int32_t* src_row,
+                                        const float* weights, void* y,
+                                        int64_t tokens, int64_t top_k, int64_t hidden,
+                                        int64_t ldrows, int64_t ldy, int dtype, void* stream) {
+  return unpermute_impl(__func__, bufs, n_bufs, src_buf, src_row, weights, y, tokens, top_k, hidden, ldrows, ldy, dtype, stream);
+}
+
+// --------------------------------------------------- expert-parallel plan --
+
+namespace b200 {
+namespace {
+// For every (token, slot): the rank that owns its expert and the row it takes in that
+// rank's exchange buffer.  dst_base[e] is where this rank's rows for expert e start there;
+// the row inside that block is the pair's position among this rank's pairs of e.
+__global__ void __launch_bounds__(256)
+ep_destinations_kernel(const int32_t* __restrict__ indices, const int32_t* __restrict__ pos,
+                       const int32_t* __restrict__ local_offsets, const int32_t* __restrict__ dst_base,
+                       int64_t pairs, int experts, int experts_per_rank,
+                       int32_t* __restrict__ dst_rank, int32_t* __restrict__ dst_row) {
+  pdl_prologue();
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= pairs) return;
+  const int e = indices[i];
+  const int p = pos[i];
+  if (e < 0 || e >= experts || p < 0) {
+    dst_rank[i] = 0;
+    dst_row[i] = -1;
+    return;
+  }
+  dst_rank[i] = e / experts_per_rank;
+  dst_row[i] = dst_base[e] + (p - local_offsets[e]);
+}
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_moe_ep_destinations(const int32_t* indices, const int32_t* pos, const int32_t* local_offsets,
+                                        const int32_t* dst_base, int64_t tokens, int64_t top_k, int64_t experts,
+                                        int64_t experts_per_rank, int32_t* dst_rank, int32_t* dst_row, void* stream) {
+  if (int rc = index_check(__func__, tokens, top_k, experts)) return rc;
+  if (experts_per_rank < 1 || experts % experts_per_rank != 0)
+    return fail(B200_ERR_SHAPE, "%s: experts_per_rank must divide experts", __func__);
+  const int64_t pairs = tokens * top_k;
+  if (pairs == 0) return B200_OK;
+  B200_REQUIRE_PTR(indices);
+  B200_REQUIRE_PTR(pos);
+  B200_REQUIRE_PTR(local_offsets);
+  B200_REQUIRE_PTR(dst_base);
+  B200_REQUIRE_PTR(dst_rank);
+  B200_REQUIRE_PTR(dst_row);
+  if (!aligned(indices, 4) || !aligned(pos, 4) || !aligned(local_offsets, 4) || !aligned(dst_base, 4) || !aligned(dst_rank, 4) || !aligned(dst_row, 4))
+    return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to 4 bytes", __func__);
+  if (int rc = check_device()) return rc;
+  launch(ep_destinations_kernel, static_cast<unsigned>(ceil_div(pairs, 256)), 256, 0, static_cast<cudaStream_t>(stream),
+         indices, pos, local_offsets, dst_base, pairs, static_cast<int>(experts), static_cast<int>(experts_per_rank), dst_rank, dst_row);
+  return after_launch("ep_destinations_kernel");
 }

@@ -24,6 +24,16 @@ sizes swapped, weighted unpermute on the owner rank.
 The per-rank compute steps come from `local_ops` (default: popcorn_b200.ops, the
 CUDA kernels).  Tests of the exchange logic on CPU processes pass a namespace of
 CPU functions with the same signatures and run it over the gloo backend.
+
+exchange="p2p" (CUDA only) fuses each exchange into the kernel next to it.  Every
+rank owns two symmetric buffers that all ranks map (torch symmetric memory over
+NVLink): `recv`, which the ranks' permute kernels fill with ordinary stores
+straight from their token rows, already in the final (expert, source rank, token)
+order, and `out`, from which the token owners' unpermute kernels load the expert
+outputs while they accumulate.  A step then has no bulk collective, no send or
+receive staging buffer and no reorder pass: only the small all-gather of the
+counts and one tiny all-reduce per direction that orders the ranks around the
+kernel.
 """
 
 from __future__ import annotations
@@ -36,6 +46,30 @@ import torch.distributed as dist
 from torch import Tensor
 
 
+def p2p_plan(counts_all: Tensor, rank: int) -> tuple[Tensor, list[int], Tensor]:
+    """Addressing for the fused exchange, from the gathered counts (host arithmetic).
+
+    Returns (dst_base int32 [experts], rows_per_rank, expert_offsets int32 [local_experts + 1]):
+    dst_base[e] is the row in the buffer of e's owner at which THIS rank's rows for expert e start:
+    the owner's buffer is expert-major, and inside an expert the source ranks follow in rank order;
+    rows_per_rank[r] is how many rows rank r receives in total; expert_offsets delimit this rank's
+    own experts inside its buffer."""
+    world, experts = counts_all.shape
+    if experts % world != 0:
+        raise ValueError(f"experts={experts} must be a multiple of the world size {world}")
+    per_rank = experts // world
+    c = counts_all.to(torch.int64)
+    total = c.sum(0)  # rows per expert over all sources
+    blocks = total.view(world, per_rank)
+    expert_base = (torch.cumsum(blocks, 1) - blocks).view(-1)  # start of each expert inside its owner's buffer
+    before_me = c[:rank].sum(0)  # rows of lower source ranks inside the expert
+    dst_base = (expert_base + before_me).to(torch.int32)
+    rows_per_rank = blocks.sum(1).tolist()
+    expert_offsets = torch.zeros(per_rank + 1, dtype=torch.int64)
+    expert_offsets[1:] = torch.cumsum(blocks[rank], 0)
+    return dst_base, rows_per_rank, expert_offsets.to(torch.int32)
+
+
 @dataclass
 class Dispatched:
     """What dispatch() hands to the expert computation, plus what combine() needs later."""
@@ -46,8 +80,11 @@ class Dispatched:
     pos: Tensor             # int32 [local_tokens, top_k] positions in this rank's send buffer
     send_counts: list[int]  # rows sent to each rank
     recv_counts: list[int]  # rows received from each rank
-    reorder: Tensor         # int32 [received]: rows[p] = arrived[reorder[p]]
+    reorder: Tensor | None  # int32 [received]: rows[p] = arrived[reorder[p]]  (exchange="nccl")
     counts_all: Tensor      # int32 [world, experts] (host tensor)
+    dst_rank: Tensor | None = None  # int32 [local_tokens, top_k]: owner of each pair's expert   (exchange="p2p")
+    dst_row: Tensor | None = None   # int32 [local_tokens, top_k]: row in the owner's buffer      (exchange="p2p")
+    out_rows: Tensor | None = None  # [received, hidden] view of the symmetric output buffer: write expert results here
 
 
 def exchange_plan(counts_all: Tensor, rank: int) -> tuple[list[int], list[int], Tensor, Tensor, Tensor]:
@@ -88,19 +125,90 @@ def expand_segments(source_start: Tensor, length: Tensor, total: int, device: to
 class ExpertParallel:
     """Token-sharded routing with block-sharded experts over a torch.distributed group."""
 
-    def __init__(self, experts: int, top_k: int, group: Any = None, local_ops: Any = None) -> None:
+    def __init__(self, experts: int, top_k: int, group: Any = None, local_ops: Any = None,
+                 exchange: str = "nccl", capacity_rows: int | None = None) -> None:
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         if experts % self.world != 0:
             raise ValueError(f"experts={experts} must be a multiple of the world size {self.world}")
+        if exchange not in ("nccl", "p2p"):
+            raise ValueError("exchange must be 'nccl' or 'p2p'")
         self.experts, self.top_k = experts, top_k
         self.local_experts = experts // self.world
         if local_ops is None:
             from popcorn_b200 import ops as local_ops
         self.ops = local_ops
+        self.exchange = exchange
+        self.capacity_rows = capacity_rows
+        self._symmetric = None  # (recv, out, recv_ptrs, out_ptrs, capacity, hidden, dtype), built on first use
+        self._flag: Tensor | None = None
+
+    # -- fused exchange over peer memory ------------------------------------------------------------
+
+    def _buffers(self, x: Tensor):
+        """The two symmetric row buffers, allocated and mapped on the first dispatch."""
+        if self._symmetric is not None:
+            recv, out, recv_ptrs, out_ptrs, capacity, hidden, dtype = self._symmetric
+            if hidden != x.shape[1] or dtype != x.dtype:
+                raise ValueError("ExpertParallel(exchange='p2p') was set up for another hidden size or dtype")
+            return self._symmetric
+        import os
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer loads/stores only
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = self.group if self.group is not None else dist.group.WORLD
+        hidden = x.shape[1]
+        # worst case: every pair of every rank is routed to one rank
+        capacity = self.capacity_rows or x.shape[0] * self.top_k * self.world
+        cap = torch.tensor([capacity], dtype=torch.int64, device=x.device)
+        dist.all_reduce(cap, op=dist.ReduceOp.MAX, group=self.group)  # ranks must agree on the shape
+        capacity = int(cap.item())
+        recv = symm_mem.empty((capacity, hidden), dtype=x.dtype, device=x.device)
+        out = symm_mem.empty((capacity, hidden), dtype=x.dtype, device=x.device)
+        recv_handle = symm_mem.rendezvous(recv, group)
+        out_handle = symm_mem.rendezvous(out, group)
+        self._symmetric = (recv, out, [int(p) for p in recv_handle.buffer_ptrs], [int(p) for p in out_handle.buffer_ptrs],
+                           capacity, hidden, x.dtype)
+        self._handles = (recv_handle, out_handle)  # keep the mappings alive
+        self._flag = torch.zeros(1, dtype=torch.int32, device=x.device)
+        return self._symmetric
+
+    def _order_ranks(self) -> None:
+        """Stream-ordered rendezvous: returns (on the stream) once every rank's earlier work has completed."""
+        dist.all_reduce(self._flag, group=self.group)
+
+    def _dispatch_p2p(self, x: Tensor, router_logits: Tensor) -> Dispatched:
+        ops = self.ops
+        recv, out, recv_ptrs, _, capacity, _, _ = self._buffers(x)
+        indices, weights = ops.moe_route(router_logits, self.top_k)
+        counts, offsets, _, pos = ops.moe_index(indices, self.experts)
+        gathered = torch.empty(self.world * self.experts, dtype=torch.int32, device=counts.device)
+        # also orders the ranks: nobody overwrites a buffer that a peer is still reading from the last step
+        dist.all_gather_into_tensor(gathered, counts.contiguous(), group=self.group)
+        counts_all = gathered.view(self.world, self.experts).cpu()
+        dst_base, rows_per_rank, expert_offsets = p2p_plan(counts_all, self.rank)
+        if max(rows_per_rank) > capacity:
+            raise RuntimeError(f"a rank would receive {max(rows_per_rank)} rows, over the exchange capacity of {capacity}")
+        dst_rank, dst_row = ops.moe_ep_destinations(indices, pos, offsets, dst_base.to(x.device, non_blocking=True), self.local_experts)
+        ops.moe_permute_multi(x, dst_rank, dst_row, recv_ptrs)  # rows go straight into their owners' memory
+        self._order_ranks()  # every rank's stores have landed
+        received = rows_per_rank[self.rank]
+        send_counts = counts_all[self.rank].view(self.world, self.local_experts).sum(1).tolist()
+        return Dispatched(recv[:received], expert_offsets, weights, pos, send_counts, [], None, counts_all,
+                          dst_rank, dst_row, out[:received])
+
+    def _combine_p2p(self, expert_rows: Tensor, state: Dispatched) -> Tensor:
+        _, out, _, out_ptrs, _, hidden, dtype = self._symmetric
+        if expert_rows.data_ptr() != out.data_ptr():
+            out[: expert_rows.shape[0]].copy_(expert_rows)  # results computed elsewhere: stage them for the peers
+        self._order_ranks()  # every rank's expert outputs are complete
+        return self.ops.moe_unpermute_multi(out_ptrs, state.dst_rank, state.dst_row, state.weights, hidden, dtype)
 
     def dispatch(self, x: Tensor, router_logits: Tensor) -> Dispatched:
+        if self.exchange == "p2p":
+            return self._dispatch_p2p(x, router_logits)
         ops = self.ops
         indices, weights = ops.moe_route(router_logits, self.top_k)
         counts, _, _, pos = ops.moe_index(indices, self.experts)
@@ -118,6 +226,8 @@ class ExpertParallel:
         return Dispatched(rows, expert_offsets, weights, pos, send_counts, recv_counts, reorder, counts_all)
 
     def combine(self, expert_rows: Tensor, state: Dispatched) -> Tensor:
+        if self.exchange == "p2p":
+            return self._combine_p2p(expert_rows, state)
         ops = self.ops
         total = expert_rows.shape[0]
         inverse = torch.empty(total, dtype=torch.int32, device=expert_rows.device)

@@ -321,3 +321,75 @@ def moe_unpermute(rows: Tensor, weights: Tensor, pos: Tensor) -> Tensor:
             tokens, top_k, hidden, ldr, max(hidden, 1), code, _stream(device),
         )
     return y
+
+
+def _pointer_array(pointers: list[int]) -> ctypes.Array:
+    return (ctypes.c_void_p * len(pointers))(*pointers)
+
+
+def moe_ep_destinations(
+    indices: Tensor, pos: Tensor, local_offsets: Tensor, dst_base: Tensor, experts_per_rank: int
+) -> tuple[Tensor, Tensor]:
+    """Owner rank and row in the owner's exchange buffer for every (token, slot) pair (all int32).
+
+    dst_rank = indices // experts_per_rank; dst_row = dst_base[expert] + (pos - local_offsets[expert])."""
+    device = _require_cuda(indices, pos, local_offsets, dst_base)
+    tokens, top_k = indices.shape
+    experts = dst_base.shape[0]
+    for name, t in (("indices", indices), ("pos", pos), ("local_offsets", local_offsets), ("dst_base", dst_base)):
+        if t.dtype != torch.int32:
+            raise TypeError(f"moe_ep_destinations: {name} must be int32")
+    dst_rank = torch.empty((tokens, top_k), dtype=torch.int32, device=device)
+    dst_row = torch.empty((tokens, top_k), dtype=torch.int32, device=device)
+    with torch.cuda.device(device):
+        _lib.call(
+            "b200_moe_ep_destinations", _ptr(indices.contiguous()), _ptr(pos.contiguous()), _ptr(local_offsets.contiguous()),
+            _ptr(dst_base.contiguous()), tokens, top_k, experts, int(experts_per_rank), _ptr(dst_rank), _ptr(dst_row), _stream(device),
+        )
+    return dst_rank, dst_row
+
+
+def moe_permute_multi(x: Tensor, dst_buf: Tensor, dst_row: Tensor, buffer_ptrs: list[int], ld_rows: int | None = None) -> None:
+    """buffer[dst_buf[t, k]][dst_row[t, k]] = x[t]: the dispatch half of the expert-parallel exchange.
+
+    buffer_ptrs: device addresses of every rank's exchange buffer as mapped into this process (row-major,
+    `ld_rows` elements per row, default hidden).  The rows are stored straight into peer memory."""
+    device = _require_cuda(x, dst_buf, dst_row)
+    _forbid_grad(x)
+    code = _dtype_code(x, "moe_permute_multi")
+    if x.dim() != 2 or dst_buf.shape != dst_row.shape or dst_row.dim() != 2 or dst_row.shape[0] != x.shape[0]:
+        raise ValueError("moe_permute_multi: x must be [tokens, hidden]; dst_buf and dst_row [tokens, top_k]")
+    if dst_buf.dtype != torch.int32 or dst_row.dtype != torch.int32:
+        raise TypeError("moe_permute_multi: dst_buf and dst_row must be int32")
+    tokens, hidden = x.shape
+    x2, ldx = _rows(x)
+    with torch.cuda.device(device):
+        _lib.call(
+            "b200_moe_permute_multi", _ptr(x2), _ptr(dst_buf.contiguous()), _ptr(dst_row.contiguous()), _pointer_array(buffer_ptrs),
+            len(buffer_ptrs), tokens, dst_row.shape[1], hidden, ldx, ld_rows or max(hidden, 1), code, _stream(device),
+        )
+
+
+def moe_unpermute_multi(
+    buffer_ptrs: list[int], src_buf: Tensor, src_row: Tensor, weights: Tensor, hidden: int, dtype: torch.dtype, ld_rows: int | None = None
+) -> Tensor:
+    """y[t] = sum_k weights[t, k] * buffer[src_buf[t, k]][src_row[t, k]]: the combine half of the exchange.
+
+    The rows are loaded straight out of peer memory; accumulation is fp32 in ascending expert order."""
+    device = _require_cuda(src_buf, src_row, weights)
+    if src_buf.shape != src_row.shape or weights.shape != src_row.shape or src_row.dim() != 2:
+        raise ValueError("moe_unpermute_multi: src_buf, src_row and weights must all be [tokens, top_k]")
+    if src_buf.dtype != torch.int32 or src_row.dtype != torch.int32 or weights.dtype != torch.float32:
+        raise TypeError("moe_unpermute_multi: src_buf / src_row must be int32 and weights float32")
+    try:
+        code = _DTYPES[dtype]
+    except KeyError:
+        raise TypeError(f"moe_unpermute_multi: dtype {dtype} is not supported") from None
+    tokens, top_k = src_row.shape
+    y = torch.empty((tokens, hidden), dtype=dtype, device=device)
+    with torch.cuda.device(device):
+        _lib.call(
+            "b200_moe_unpermute_multi", _pointer_array(buffer_ptrs), len(buffer_ptrs), _ptr(src_buf.contiguous()), _ptr(src_row.contiguous()),
+            _ptr(weights.contiguous()), _ptr(y), tokens, top_k, hidden, ld_rows or max(hidden, 1), max(hidden, 1), code, _stream(device),
+        )
+    return y

@@ -17,7 +17,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from oracle import reference_ops as oracle
-from popcorn_b200.expert_parallel import ExpertParallel, exchange_plan, expand_segments
+from popcorn_b200.expert_parallel import ExpertParallel, exchange_plan, expand_segments, p2p_plan
 
 CPU_OPS = types.SimpleNamespace(
     moe_route=oracle.moe_route, moe_index=oracle.moe_index, moe_scatter_rows=oracle.moe_scatter_rows,
@@ -106,3 +106,51 @@ def test_expand_segments_reorders():
     assert recv == [3, 3]
     assert expand_segments(start, length, 6, "cpu").tolist() == [0, 1, 3, 2, 4, 5]
     assert offsets.tolist() == [0, 3, 6]
+
+
+@pytest.mark.parametrize("world,tokens,experts,top_k", [(2, 64, 8, 2), (4, 51, 8, 3), (8, 200, 64, 8), (1, 30, 4, 2)])
+def test_fused_exchange_addressing_emulated_on_cpu(world, tokens, experts, top_k):
+    """All ranks' pushes, emulated in one process: every rank's buffer ends up in the global stable
+    order, and pulling with the same addresses reproduces the single-process unpermute."""
+    hidden = 16
+    x, logits = _inputs(tokens, hidden, experts, seed=13)
+    indices, weights = oracle.moe_route(logits, top_k)
+    rows, counts, offsets, perm, pos = oracle.moe_permute(x, indices, experts)
+    per_rank = experts // world
+    bounds = [tokens * r // world for r in range(world + 1)]
+    local = []
+    for r in range(world):
+        idx_r = indices[bounds[r] : bounds[r + 1]]
+        counts_r, offsets_r, _, pos_r = oracle.moe_index(idx_r, experts)
+        local.append((idx_r, counts_r, offsets_r, pos_r))
+    counts_all = torch.stack([c for _, c, _, _ in local])
+    buffers = [torch.full((tokens * top_k, hidden), float("nan"), dtype=torch.bfloat16) for _ in range(world)]
+    addresses = []
+    for r in range(world):
+        idx_r, _, offsets_r, pos_r = local[r]
+        dst_base, rows_per_rank, expert_offsets = p2p_plan(counts_all, r)
+        dst_rank, dst_row = oracle.moe_ep_destinations(idx_r, pos_r, offsets_r, dst_base, per_rank)
+        addresses.append((dst_rank, dst_row))
+        xr = x[bounds[r] : bounds[r + 1]]
+        for t in range(xr.shape[0]):
+            for k in range(top_k):
+                buffers[int(dst_rank[t, k])][int(dst_row[t, k])] = xr[t]
+        lo = int(offsets[r * per_rank])
+        assert torch.equal(expert_offsets, offsets[r * per_rank : (r + 1) * per_rank + 1] - lo)
+        assert rows_per_rank == [int(offsets[(q + 1) * per_rank] - offsets[q * per_rank]) for q in range(world)]
+    for r in range(world):
+        lo, hi = int(offsets[r * per_rank]), int(offsets[(r + 1) * per_rank])
+        assert torch.equal(buffers[r][: hi - lo], rows[lo:hi]), f"rank {r}: buffer is not in the global stable order"
+    # pull: (rank, row) ascending is ascending expert, so the accumulation order is the oracle's
+    want = oracle.moe_unpermute(rows, weights, pos)
+    for r in range(world):
+        dst_rank, dst_row = addresses[r]
+        w_r = weights[bounds[r] : bounds[r + 1]]
+        key = dst_rank.long() * (tokens * top_k) + dst_row.long()
+        order = key.argsort(dim=1)
+        acc = torch.zeros(dst_rank.shape[0], hidden)
+        for k in range(top_k):
+            sel = order[:, k]
+            picked = torch.stack([buffers[int(dst_rank[t, sel[t]])][int(dst_row[t, sel[t]])] for t in range(dst_rank.shape[0])]) if dst_rank.shape[0] else torch.zeros(0, hidden)
+            acc = acc + picked.float() * w_r.gather(1, sel[:, None])
+        assert torch.equal(acc.to(torch.bfloat16), want[bounds[r] : bounds[r + 1]])

@@ -24,7 +24,7 @@ def _inputs(tokens, hidden, experts):
     return torch.randn(tokens, hidden, generator=gen).to(torch.bfloat16), torch.randn(tokens, experts, generator=gen)
 
 
-def _worker(rank, world, port, tokens, hidden, experts, top_k, out):
+def _worker(rank, world, port, tokens, hidden, experts, top_k, exchange, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     device = torch.device("cuda", rank)
     torch.cuda.set_device(device)
@@ -34,21 +34,24 @@ def _worker(rank, world, port, tokens, hidden, experts, top_k, out):
 
         x, logits = _inputs(tokens, hidden, experts)
         lo, hi = tokens * rank // world, tokens * (rank + 1) // world
-        ep = ExpertParallel(experts, top_k)
-        state = ep.dispatch(x[lo:hi].to(device), logits[lo:hi].to(device))
-        processed = (state.rows.float() * 1.5).to(torch.bfloat16)
-        y = ep.combine(processed, state)
+        ep = ExpertParallel(experts, top_k, exchange=exchange)
+        for _ in range(2):  # the second step reuses the exchange buffers
+            state = ep.dispatch(x[lo:hi].to(device), logits[lo:hi].to(device))
+            rows = state.rows.clone()
+            processed = (state.rows.float() * 1.5).to(torch.bfloat16)
+            y = ep.combine(processed, state)
         torch.cuda.synchronize(device)
-        out[rank] = (state.rows.cpu(), state.expert_offsets.cpu(), y.cpu())
+        out[rank] = (rows.cpu(), state.expert_offsets.cpu(), y.cpu())
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_dispatch_and_combine_on_two_gpus():
+@pytest.mark.parametrize("exchange", ["nccl", "p2p"])
+def test_dispatch_and_combine_on_two_gpus(exchange):
     world, tokens, hidden, experts, top_k = 2, 4096, 1024, 16, 4
     out = mp.Manager().dict()
-    mp.spawn(_worker, args=(world, _free_port(), tokens, hidden, experts, top_k, out), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), tokens, hidden, experts, top_k, exchange, out), nprocs=world, join=True)
     x, logits = _inputs(tokens, hidden, experts)
     assert oracle.route_is_unambiguous(logits, top_k)
     indices, weights = oracle.moe_route(logits, top_k)
