@@ -190,6 +190,38 @@ int b200_moe_index(const int32_t* indices, int64_t tokens, int64_t top_k, int64_
                    void* scratch, size_t scratch_bytes, void* stream);
 
 /*
+ * b200_moe_index for callers that cannot hand over a workspace.  (This entry point
+ * has no counterpart in the reference; it exists for hosts of this library, not
+ * to mirror a popcorn function.)
+ *
+ * Who needs it: a serving process that plans all of its device memory at start-up
+ * and forbids cudaMalloc afterwards (an allocation synchronises the device and can
+ * fail once memory is fragmented), or a plugin host that gives the library neither
+ * an allocator nor a scratch pointer.  Such a caller still owns the inputs and the
+ * four outputs; only the intermediate per-block histogram, which b200_moe_index
+ * takes as `scratch`, lives inside the library here, in a fixed 1 MiB device array
+ * that every GPU loading the library holds until the process exits.
+ *
+ * Limit: ceil(tokens*top_k / 2048) * experts * 4 bytes must fit in that array
+ * (b200_moe_index_static_max_bytes reports its size); e.g. 64 experts allow up to
+ * 8,388,608 (token, slot) pairs.  Larger problems return B200_ERR_SCRATCH and
+ * should use b200_moe_index.  Results are identical to b200_moe_index.
+ *
+ * The first call on each device looks up the array's device address (with that
+ * device current) and remembers it; make that first call before any stream
+ * capture begins.  No call allocates or frees device memory.  All calls on a
+ * device share the one array, which keeps whatever the last call left in it (the
+ * kernels overwrite every entry they later read, so no clearing is needed); two
+ * calls whose kernels overlap on the GPU, e.g. on different streams, race on it.
+ */
+int b200_moe_index_static(const int32_t* indices, int64_t tokens, int64_t top_k, int64_t experts,
+                          int32_t* counts, int32_t* offsets, int32_t* perm_token, int32_t* pos,
+                          void* stream);
+
+/* Size in bytes of the built-in scratch array of b200_moe_index_static (written to *bytes, a host pointer). */
+int b200_moe_index_static_max_bytes(size_t* bytes);
+
+/*
  * Permute (scatter form): rows[pos[t, k], :] = x[t, :] for every slot k.
  * Each token row is read once and written top_k times.
  *

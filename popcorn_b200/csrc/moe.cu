@@ -9,6 +9,7 @@
 // Bound: HBM for permute / gather / unpermute (pure row traffic, 128-bit
 // accesses, a warp moves 512 contiguous bytes per step); route and index move
 // only a few MB and are latency-bound.
+#include <mutex>
 #include <type_traits>
 
 #include "common.cuh"
@@ -551,6 +552,93 @@ extern "C" int b200_moe_index(const int32_t* indices, int64_t tokens, int64_t to
   if (nblk > 0) {
     launch(index_scatter_kernel, nblk, kIndexThreads, 8 * E * sizeof(int), st,
         indices, pairs, static_cast<int>(top_k), E, nblk, block_hist, offsets, perm_token, pos);
+    if (int rc = after_launch("index_scatter_kernel")) return rc;
+  }
+  return B200_OK;
+}
+
+// ------------------------------------------------- index without a workspace --
+
+namespace b200 {
+namespace {
+// Scratch of b200_moe_index_static: the per-block expert histogram, kept in the
+// library image instead of being passed in.  1 MiB per GPU that loads the library,
+// held until the process exits.  On the host this name is only a stand-in for the
+// symbol; the device address comes from cudaGetSymbolAddress, once per device.
+constexpr size_t kStaticScratchBytes = size_t{1} << 20;
+static __device__ __align__(256) unsigned char g_index_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevicesStatic = 64;
+std::mutex g_static_mutex;
+void* g_static_address[kMaxDevicesStatic] = {};  // per device, filled on that device's first call
+
+// Device address of g_index_scratch on the CURRENT device (looked up on the first call per device).
+int static_scratch(void** address) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevicesStatic) {
+    (void)cudaGetLastError();
+    return fail(B200_ERR_DEVICE, "b200_moe_index_static: no usable CUDA device is current");
+  }
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_address[dev] == nullptr) {
+    void* ptr = nullptr;
+    const cudaError_t err = cudaGetSymbolAddress(&ptr, g_index_scratch);
+    if (err != cudaSuccess || ptr == nullptr) {
+      (void)cudaGetLastError();
+      return fail(B200_ERR_SCRATCH, "b200_moe_index_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(err));
+    }
+    g_static_address[dev] = ptr;
+  }
+  *address = g_static_address[dev];
+  return B200_OK;
+}
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_moe_index_static_max_bytes(size_t* bytes) {
+  B200_REQUIRE_PTR(bytes);
+  *bytes = kStaticScratchBytes;
+  return B200_OK;
+}
+
+extern "C" int b200_moe_index_static(const int32_t* indices, int64_t tokens, int64_t top_k, int64_t experts,
+                                     int32_t* counts, int32_t* offsets, int32_t* perm_token, int32_t* pos,
+                                     void* stream) {
+  if (int rc = index_check(__func__, tokens, top_k, experts)) return rc;
+  B200_REQUIRE_PTR(counts);
+  B200_REQUIRE_PTR(offsets);
+  const int64_t pairs = tokens * top_k;
+  if (pairs > 0) {
+    B200_REQUIRE_PTR(indices);
+    B200_REQUIRE_PTR(perm_token);
+    B200_REQUIRE_PTR(pos);
+  }
+  const int nblk = nblk_for(pairs);
+  const size_t need = static_cast<size_t>((nblk > 0 ? nblk : 1) * experts) * sizeof(int32_t);
+  if (need > kStaticScratchBytes)
+    return fail(B200_ERR_SCRATCH,
+                "%s: tokens*top_k=%lld with %lld experts needs %zu bytes of scratch, over the built-in %zu; "
+                "use b200_moe_index with a caller-provided workspace",
+                __func__, (long long)pairs, (long long)experts, need, kStaticScratchBytes);
+  if (!aligned(indices, 4) || !aligned(counts, 4) || !aligned(offsets, 4) || !aligned(perm_token, 4) || !aligned(pos, 4))
+    return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to 4 bytes", __func__);
+  if (int rc = check_device()) return rc;
+  void* scratch = nullptr;
+  if (int rc = static_scratch(&scratch)) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int E = static_cast<int>(experts);
+  // The histogram kernel writes every entry the two later kernels read, so nothing
+  // left over from an earlier call has to be cleared first.
+  int32_t* block_hist = static_cast<int32_t*>(scratch);
+  if (nblk > 0) {
+    launch(index_hist_kernel, nblk, kIndexThreads, E * sizeof(int), st, indices, pairs, E, nblk, block_hist);
+    if (int rc = after_launch("index_hist_kernel")) return rc;
+  }
+  launch(index_scan_kernel, 1, 1024, 0, st, block_hist, E, nblk, counts, offsets);
+  if (int rc = after_launch("index_scan_kernel")) return rc;
+  if (nblk > 0) {
+    launch(index_scatter_kernel, nblk, kIndexThreads, 8 * E * sizeof(int), st,
+           indices, pairs, static_cast<int>(top_k), E, nblk, block_hist, offsets, perm_token, pos);
     if (int rc = after_launch("index_scatter_kernel")) return rc;
   }
   return B200_OK;
