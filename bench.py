@@ -251,6 +251,63 @@ def bench_moe(device, peak_gbs: float, sampler, scale: float = 1.0, fixed_steps:
     return out
 
 
+def torch_eager_incumbent(device, per_op: dict, records_root: str | None) -> None:
+    """The incumbent on the same GPU: the references' own PyTorch code run eagerly on CUDA tensors.
+
+    Adds `torch_eager_gpu_ms` (and the speed-up over it) to each single-kernel entry of `per_op`, and, when
+    `records_root` is given, writes popcorn report rows (schema 3) for the configurations popcorn can
+    represent as a case, with error gauges measured against an fp64 evaluation on a 512-token sample."""
+    from oracle import reference_ops as reference
+    from popcorn_b200 import ops, records, workloads
+
+    def timed(fn, reps=10):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize(device)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(reps):
+            fn()
+        end.record()
+        torch.cuda.synchronize(device)
+        return start.elapsed_time(end) / reps
+
+    def gauge(mine, native, truth):
+        return {"err": float((mine.double() - truth).abs().max()), "budget": float((native.double() - truth).abs().max()),
+                "scale": max(1.0, float(truth.abs().max()))}
+
+    rows = []
+    cases = records.benchmark_configs()
+    for key in ("rms_norm_fp32", "add_rms_norm_bf16", "rotary_bf16", "swiglu_bf16"):
+        w = workloads.CONFIGS[key]().to(device)
+        i = w.inputs
+        if key == "rms_norm_fp32":
+            call = lambda f, t: (f.rms_norm(t["x"], t["weight"], None, w.args["eps"]),)  # noqa: E731
+        elif key == "add_rms_norm_bf16":
+            call = lambda f, t: f.add_rms_norm(t["x"], t["residual"], t["weight"], w.args["eps"], w.args["offset"])  # noqa: E731
+        elif key == "rotary_bf16":
+            call = lambda f, t: (f.rotary_embedding(t["q"], t["cos"], t["sin"]), f.rotary_embedding(t["k"], t["cos"], t["sin"]))  # noqa: E731
+        else:
+            c = w.args["cols"]
+            call = lambda f, t: (f.swiglu(t["gate_up"][:, :c], t["gate_up"][:, c:]),)  # noqa: E731
+        eager_ms = timed(lambda: call(reference, i))
+        per_op[key]["torch_eager_gpu_ms"] = round(eager_ms, 4)
+        per_op[key]["speedup_vs_torch_eager_gpu"] = round(eager_ms / per_op[key]["ms"], 2)
+        if records_root and key in cases:
+            op_name, config = cases[key]
+            sample = {k: (v[:512] if v.dim() == 2 and v.shape[0] > 512 else v) for k, v in i.items()}
+            wide = {k: v.double() for k, v in sample.items()}
+            mine, native, truth = call(ops, sample), call(reference, sample), call(reference, wide)
+            gauges = {str(n): gauge(m, nat, tr) for n, (m, nat, tr) in enumerate(zip(mine, native, truth))}
+            rows.append(records.make_row(op_name, config, device=torch.cuda.get_device_name(device), torch_version=torch.__version__,
+                                         fwd_ms=per_op[key]["ms"], ref_fwd_ms=eager_ms, gauges=gauges, reps=per_op[key]["steps"]))
+        del w, i
+        torch.cuda.empty_cache()
+    if records_root and rows:
+        paths = records.write_rows(rows, records_root)
+        per_op["popcorn_report_rows"] = [str(path) for path in paths]
+
+
 def bench_moe_expert_parallel(device, world: int, rank: int, dist, exchange: str, steps: int = 20, warmup: int = 3) -> dict:
     """Config 5 sharded over the ranks: 65536 / world tokens and 64 / world experts per GPU.
 
@@ -377,6 +434,7 @@ def main() -> None:
     parser.add_argument("--impl", choices=["b200", "reference"], default="b200")
     parser.add_argument("--skip-per-op", action="store_true", help="only the headline loop (used for profiling captures)")
     parser.add_argument("--scale", type=float, default=1.0, help="shrink the token count (profiling captures only)")
+    parser.add_argument("--records", metavar="DIR", help="also write popcorn report rows (schema 3) under DIR/v3/reports")
     parser.add_argument("--only", choices=["rms_norm_fp32", "add_rms_norm_bf16", "rotary_bf16", "swiglu_bf16", "moe_bf16"],
                         help="time one configuration's kernels alone and print a short JSON (profiling captures)")
     args = parser.parse_args()
@@ -485,6 +543,8 @@ def main() -> None:
     if not args.skip_per_op and rank == 0:
         per_op = bench_single_kernel_ops(device, peak_gbs, sampler, ["rms_norm_fp32", "add_rms_norm_bf16", "rotary_bf16", "swiglu_bf16"])
         per_op["moe_bf16"] = bench_moe(device, peak_gbs, sampler)
+        if world == 1:
+            torch_eager_incumbent(device, per_op, args.records)
     if dist is not None:
         dist.barrier()
         if not args.skip_per_op:
