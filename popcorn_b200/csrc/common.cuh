@@ -181,6 +181,40 @@ __device__ __forceinline__ void st_stream(void* p, const uint4& v) {
   asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+// Two fp32 operations per instruction (Blackwell packed fp32).  Each half is rounded to
+// nearest-even on its own, exactly like the scalar __fmul_rn / __fadd_rn / __fsub_rn.
+struct Float2x {
+  unsigned long long bits;
+};
+__device__ __forceinline__ Float2x pack_f2(float lo, float hi) {
+  Float2x r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r.bits) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f2(Float2x v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v.bits));
+}
+__device__ __forceinline__ Float2x mul_f2(Float2x a, Float2x b) {
+  Float2x r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r.bits) : "l"(a.bits), "l"(b.bits));
+  return r;
+}
+// NOTE: the assembler fuses a packed product with a following packed add or sub into one fused
+// multiply-add when the product has no other use (measured: the result then equals
+// fma(-d, s, a*c) in every case; --fmad=false and adding through fma(p, +-1, q) do not stop it).
+// Where the reference rounds product and sum separately, take the products packed and add them
+// with the scalar __fadd_rn / __fsub_rn.
+__device__ __forceinline__ Float2x add_f2(Float2x a, Float2x b) {
+  Float2x r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r.bits) : "l"(a.bits), "l"(b.bits));
+  return r;
+}
+__device__ __forceinline__ Float2x sub_f2(Float2x a, Float2x b) {
+  Float2x r;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r.bits) : "l"(a.bits), "l"(b.bits));
+  return r;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));

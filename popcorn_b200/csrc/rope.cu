@@ -214,12 +214,23 @@ __global__ void __launch_bounds__(512, 2) rope_tile_kernel(const RopeArgs p, int
         } else {
           float d[V];
           Num<T>::unpack(v2[k], d);
+          // The four products of two channels come from packed fp32x2 multiplies (each half rounded
+          // on its own, identical to __fmul_rn); the difference and the sum stay scalar, because the
+          // assembler turns a packed product followed by a packed add/sub into one fused
+          // multiply-add (measured), which would change the rounding.
 #pragma unroll
-          for (int j = 0; j < V; ++j) {
-            float y1, y2;
-            rotate(a[j], d[j], c[j], sn[j], y1, y2);
-            a[j] = y1;
-            d[j] = y2;
+          for (int j = 0; j < V; j += 2) {
+            const Float2x x1 = pack_f2(a[j], a[j + 1]), x2 = pack_f2(d[j], d[j + 1]);
+            const Float2x cc = pack_f2(c[j], c[j + 1]), ss = pack_f2(sn[j], sn[j + 1]);
+            float ac0, ac1, ds0, ds1, as0, as1, dc0, dc1;
+            unpack_f2(mul_f2(x1, cc), ac0, ac1);
+            unpack_f2(mul_f2(x2, ss), ds0, ds1);
+            unpack_f2(mul_f2(x1, ss), as0, as1);
+            unpack_f2(mul_f2(x2, cc), dc0, dc1);
+            a[j] = __fsub_rn(ac0, ds0);
+            a[j + 1] = __fsub_rn(ac1, ds1);
+            d[j] = __fadd_rn(as0, dc0);
+            d[j + 1] = __fadd_rn(as1, dc1);
           }
           st_stream(xout + k * t.os_s, Num<T>::pack(a));
           st_stream(xout + k * t.os_s + p.half, Num<T>::pack(d));
