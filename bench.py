@@ -158,6 +158,14 @@ def make_runner(workload, device):
         hk = sets[0]["k"].shape[2]
         return bind("b200_rope_qk", [(p(s["q"]), p(s["k"]), p(sets[0]["cos"]), p(sets[0]["sin"]), b, sq, hq, hk, d, d // 2,
                                       sq * hq * d, hq * d, d, sq * hk * d, hk * d, d, _lib.BF16, _lib.F32, 0, stream) for s in sets])
+    if w.name == "rope":
+        b, hq, sq, d = sets[0]["q"].shape
+        hk = sets[0]["k"].shape[1]
+        outs = [(torch.empty_like(s["q"]), torch.empty_like(s["k"])) for s in sets]
+        keep.append(outs)
+        return bind("b200_rope_paired", [(p(s["q"]), p(s["k"]), p(sets[0]["cos"]), p(sets[0]["sin"]), p(o[0]), p(o[1]), b, hq, hk, sq, d, 1,
+                                          hq * sq * d, sq * d, d, hk * sq * d, sq * d, d, hq * sq * d, sq * d, d, hk * sq * d, sq * d, d,
+                                          _lib.BF16, stream) for s, o in zip(sets, outs)])
     if w.name == "swiglu":
         rows, cols = sets[0]["gate_up"].shape[0], w.args["cols"]
         outs = [torch.empty((rows, cols), dtype=torch.bfloat16, device=device) for _ in sets]
@@ -435,7 +443,7 @@ def main() -> None:
     parser.add_argument("--skip-per-op", action="store_true", help="only the headline loop (used for profiling captures)")
     parser.add_argument("--scale", type=float, default=1.0, help="shrink the token count (profiling captures only)")
     parser.add_argument("--records", metavar="DIR", help="also write popcorn report rows (schema 3) under DIR/v3/reports")
-    parser.add_argument("--only", choices=["rms_norm_fp32", "add_rms_norm_bf16", "rotary_bf16", "swiglu_bf16", "moe_bf16"],
+    parser.add_argument("--only", choices=["rms_norm_fp32", "add_rms_norm_bf16", "rotary_bf16", "swiglu_bf16", "paired_rope_bf16", "moe_bf16"],
                         help="time one configuration's kernels alone and print a short JSON (profiling captures)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
@@ -541,7 +549,7 @@ def main() -> None:
     # ---- the other configurations, per op (rank 0 reports its own GPU)
     per_op = {}
     if not args.skip_per_op and rank == 0:
-        per_op = bench_single_kernel_ops(device, peak_gbs, sampler, ["rms_norm_fp32", "add_rms_norm_bf16", "rotary_bf16", "swiglu_bf16"])
+        per_op = bench_single_kernel_ops(device, peak_gbs, sampler, ["rms_norm_fp32", "add_rms_norm_bf16", "rotary_bf16", "swiglu_bf16", "paired_rope_bf16"])
         per_op["moe_bf16"] = bench_moe(device, peak_gbs, sampler)
         if world == 1:
             torch_eager_incumbent(device, per_op, args.records)

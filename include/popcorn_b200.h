@@ -136,6 +136,24 @@ int b200_rope_qk(void* q, void* k, const void* cos, const void* sin,
                  int dtype, int cs_dtype, int interleaved, void* stream);
 
 /*
+ * Paired Llama-style rotary embedding of queries and keys, out of place:
+ *   y = round_T(round_T(x * cos) + round_T(rot(x) * sin)),  rot(x) = (-x[half:], x[:half]),  x in {q, k}
+ * with every product and the sum rounded to T, as the reference's tensor arithmetic does.
+ *
+ * Replaces rope(q, k, cos, sin), src/popcorn/kernels/rope.py:24-36.  Layout (batch, heads, seq,
+ * head_dim) with batch/head/seq strides and a contiguous head_dim; cos, sin: [cos_batch, seq,
+ * head_dim] contiguous in the dtype of q, cos_batch 1 or batch.  The full tables are used (the second
+ * half is not assumed to repeat the first).  q_out / k_out must not overlap q / k.
+ */
+int b200_rope_paired(const void* q, const void* k, const void* cos, const void* sin, void* q_out, void* k_out,
+                     int64_t batch, int64_t q_heads, int64_t k_heads, int64_t seq, int64_t head_dim, int64_t cos_batch,
+                     int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                     int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+                     int64_t qo_stride_b, int64_t qo_stride_h, int64_t qo_stride_s,
+                     int64_t ko_stride_b, int64_t ko_stride_h, int64_t ko_stride_s,
+                     int dtype, void* stream);
+
+/*
  * out = round_T(round_T(silu(a)) * b),  silu(a) = a / (1 + exp(-a)) in fp32
  *
  * Replaces swiglu(a, b) = F.silu(a) * b, src/popcorn/kernels/swiglu.py:9-18
@@ -146,6 +164,18 @@ int b200_rope_qk(void* q, void* k, const void* cos, const void* sin,
 int b200_swiglu(const void* a, const void* b, void* out,
                 int64_t rows, int64_t cols, int64_t lda, int64_t ldb, int64_t ldo,
                 int dtype, void* stream);
+
+/*
+ * Backward of b200_swiglu: grad_a = round_T(round_T(g*b) * dsilu(a)), grad_b = round_T(g * round_T(silu(a))),
+ * dsilu(a) = s * (1 + a * (1 - s)), s = sigmoid(a), in fp32.
+ *
+ * Replaces what autograd derives from the reference F.silu(a) * b, src/popcorn/kernels/swiglu.py:18
+ * (the incumbent backward kernel is src/popcorn/impls/swiglu.cu:43-66).  All five matrices are
+ * [rows, cols] with their own leading dimensions; grad_a and grad_b may be the two halves of one buffer.
+ */
+int b200_swiglu_backward(const void* grad_out, const void* a, const void* b, void* grad_a, void* grad_b,
+                         int64_t rows, int64_t cols, int64_t ldg, int64_t lda, int64_t ldb,
+                         int64_t ldda, int64_t lddb, int dtype, void* stream);
 
 /*
  * MoE routing: probs = softmax(fp32(logits)) over experts; the top_k largest

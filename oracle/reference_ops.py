@@ -74,6 +74,16 @@ def rotary_embedding(x: Tensor, cos: Tensor, sin: Tensor, interleaved: bool = Fa
     return torch.cat((turned, x[..., 2 * half :]), dim=-1)
 
 
+def rope(q: Tensor, k: Tensor, cos: Tensor, sin: Tensor) -> tuple[Tensor, Tensor]:
+    """Reference: rope, src/popcorn/kernels/rope.py:8-36 (layout batch, heads, seq, head_dim)."""
+    def turned(x: Tensor) -> Tensor:
+        first, second = x.chunk(2, -1)
+        return torch.cat((-second, first), -1)
+
+    c, s = cos[:, None], sin[:, None]
+    return q * c + turned(q) * s, k * c + turned(k) * s
+
+
 def swiglu(a: Tensor, b: Tensor) -> Tensor:
     """Reference: swiglu, src/popcorn/kernels/swiglu.py:10-18."""
     return F.silu(a) * b

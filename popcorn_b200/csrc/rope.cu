@@ -335,6 +335,150 @@ int run(RopeArgs& p, cudaStream_t st) {
   return after_launch("rope_scalar_kernel");
 }
 
+// ------------------------------------------------------------ paired rope --
+//
+// rope(q, k, cos, sin) of the reference (src/popcorn/kernels/rope.py:24-36): layout
+// (batch, heads, seq, head_dim), tables [cos_batch, seq, head_dim] in the dtype of q, and the
+// arithmetic done tensor by tensor in that dtype:
+//   y = round_T(round_T(x * cos) + round_T(rot(x) * sin)),  rot(x) = (-x[half:], x[:half])
+struct PairedTensor {
+  const void* x;
+  void* out;
+  int64_t xs_b, xs_h, xs_s;
+  int64_t os_b, os_h, os_s;
+  int heads;
+};
+struct PairedArgs {
+  PairedTensor t[2];
+  const void* cos;
+  const void* sin;
+  int64_t cs_stride_b;  // 0 when the tables have one batch entry
+  int64_t seq;
+  int batch;
+  int head_dim;
+};
+
+// One unit = a 128-bit word of the first half of a row and its partner in the second half.
+// A thread owns one (position, unit): it keeps the four table words it needs in registers and
+// walks over all heads of q and k of one batch entry, four heads in flight at a time.
+template <typename T>
+__global__ void __launch_bounds__(256) rope_paired_kernel(const PairedArgs p) {
+  constexpr int V = Num<T>::kVec;
+  constexpr int UNROLL = 4;
+  pdl_prologue();
+  const int half = p.head_dim / 2;
+  const int upr = half / V;  // units per row
+  const int tile_pos = 256 / upr;
+  const int64_t tiles = (p.seq + tile_pos - 1) / tile_pos;
+  const int64_t tile = blockIdx.x % tiles;
+  const int b = static_cast<int>(blockIdx.x / tiles);
+  const int unit = threadIdx.x % upr;
+  const int64_t pos = tile * tile_pos + threadIdx.x / upr;
+  if (threadIdx.x / upr >= tile_pos || pos >= p.seq) return;
+
+  const T* cos = static_cast<const T*>(p.cos) + b * p.cs_stride_b + pos * p.head_dim + unit * V;
+  const T* sin = static_cast<const T*>(p.sin) + b * p.cs_stride_b + pos * p.head_dim + unit * V;
+  const uint4 c1 = ld_reuse(cos), c2 = ld_reuse(cos + half), s1 = ld_reuse(sin), s2 = ld_reuse(sin + half);
+
+  auto combine = [](uint4 x, uint4 c, uint4 r, uint4 sn, bool negate_r) {
+    if constexpr (sizeof(T) == 4) {
+      float fx[4], fc[4], fr[4], fs[4];
+      Num<T>::unpack(x, fx);
+      Num<T>::unpack(c, fc);
+      Num<T>::unpack(r, fr);
+      Num<T>::unpack(sn, fs);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) fx[j] = __fadd_rn(__fmul_rn(fx[j], fc[j]), __fmul_rn(negate_r ? -fr[j] : fr[j], fs[j]));
+      return Num<T>::pack(fx);
+    } else {
+      const uint32_t flip = negate_r ? 0x80008000u : 0u;  // sign bits of both 16-bit halves
+      const uint32_t wx[4] = {x.x, x.y, x.z, x.w}, wc[4] = {c.x, c.y, c.z, c.w};
+      const uint32_t wr[4] = {r.x, r.y, r.z, r.w}, ws[4] = {sn.x, sn.y, sn.z, sn.w};
+      uint32_t wo[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float a0, a1, b0, b1;
+        Num<T>::unpack2(Num<T>::mul2(wx[j], wc[j]), a0, a1);          // round_T(x * cos)
+        Num<T>::unpack2(Num<T>::mul2(wr[j] ^ flip, ws[j]), b0, b1);   // round_T(rot(x) * sin)
+        wo[j] = Num<T>::pack2(__fadd_rn(a0, b0), __fadd_rn(a1, b1));
+      }
+      return make_uint4(wo[0], wo[1], wo[2], wo[3]);
+    }
+  };
+
+  for (int ti = 0; ti < 2; ++ti) {
+    const PairedTensor& t = p.t[ti];
+    const T* xin = static_cast<const T*>(t.x) + b * t.xs_b + pos * t.xs_s + unit * V;
+    T* xout = static_cast<T*>(t.out) + b * t.os_b + pos * t.os_s + unit * V;
+    for (int h0 = 0; h0 < t.heads; h0 += UNROLL) {
+      uint4 lo[UNROLL], hi[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        if (h0 + u < t.heads) {
+          lo[u] = ld_stream(xin + (h0 + u) * t.xs_h);
+          hi[u] = ld_stream(xin + (h0 + u) * t.xs_h + half);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        if (h0 + u < t.heads) {
+          st_stream(xout + (h0 + u) * t.os_h, combine(lo[u], c1, hi[u], s1, true));
+          st_stream(xout + (h0 + u) * t.os_h + half, combine(hi[u], c2, lo[u], s2, false));
+        }
+      }
+    }
+  }
+}
+
+// Any head_dim (even), any alignment.
+template <typename T>
+__global__ void __launch_bounds__(256) rope_paired_scalar_kernel(const PairedArgs p) {
+  pdl_prologue();
+  const int half = p.head_dim / 2;
+  for (int ti = 0; ti < 2; ++ti) {
+    const PairedTensor& t = p.t[ti];
+    const int64_t total = static_cast<int64_t>(p.batch) * t.heads * p.seq * p.head_dim;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+      const int j = static_cast<int>(i % p.head_dim);
+      int64_t r = i / p.head_dim;
+      const int64_t pos = r % p.seq;
+      r /= p.seq;
+      const int h = static_cast<int>(r % t.heads);
+      const int64_t b = r / t.heads;
+      const T* xin = static_cast<const T*>(t.x) + b * t.xs_b + h * t.xs_h + pos * t.xs_s;
+      const float x = Num<T>::up(xin[j]);
+      const float rot = j < half ? -Num<T>::up(xin[j + half]) : Num<T>::up(xin[j - half]);
+      const int64_t ci = b * p.cs_stride_b + pos * p.head_dim + j;
+      const float c = Num<T>::up(static_cast<const T*>(p.cos)[ci]), sn = Num<T>::up(static_cast<const T*>(p.sin)[ci]);
+      const float y = __fadd_rn(Num<T>::rt(__fmul_rn(x, c)), Num<T>::rt(__fmul_rn(rot, sn)));
+      static_cast<T*>(t.out)[b * t.os_b + h * t.os_h + pos * t.os_s + j] = Num<T>::down(y);
+    }
+  }
+}
+
+template <typename T>
+int run_paired(const PairedArgs& p, cudaStream_t st) {
+  constexpr int V = Num<T>::kVec;
+  const int half = p.head_dim / 2;
+  bool vec = half % V == 0 && half / V <= 256 && aligned(p.cos, 16) && aligned(p.sin, 16) && p.cs_stride_b % V == 0;
+  for (int i = 0; i < 2; ++i) {
+    const PairedTensor& t = p.t[i];
+    if (t.heads == 0) continue;
+    vec = vec && aligned(t.x, 16) && aligned(t.out, 16) && t.xs_b % V == 0 && t.xs_h % V == 0 && t.xs_s % V == 0 &&
+          t.os_b % V == 0 && t.os_h % V == 0 && t.os_s % V == 0;
+  }
+  if (vec) {
+    const int tile_pos = 256 / (half / V);
+    const int64_t grid = ceil_div(p.seq, tile_pos) * p.batch;
+    if (grid > 0x7fffffffLL) return fail(B200_ERR_SHAPE, "b200_rope_paired: problem too large for one launch");
+    launch(rope_paired_kernel<T>, static_cast<unsigned>(grid), 256, 0, st, p);
+    return after_launch("rope_paired_kernel");
+  }
+  launch(rope_paired_scalar_kernel<T>, static_cast<unsigned>(sm_count()) * 8, 256, 0, st, p);
+  return after_launch("rope_paired_scalar_kernel");
+}
+
 template <typename T>
 int run_cs(RopeArgs& p, int cs_dtype, int interleaved, cudaStream_t st) {
   if (cs_dtype == B200_F32) {
@@ -426,5 +570,47 @@ extern "C" int b200_rope_qk(void* q, void* k, const void* cos, const void* sin,
   p.head_dim = static_cast<int>(head_dim);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   B200_DISPATCH_DTYPE(dtype, T, return run_cs<T>(p, cs_dtype, interleaved, st));
+  return B200_OK;
+}
+
+extern "C" int b200_rope_paired(const void* q, const void* k, const void* cos, const void* sin, void* q_out, void* k_out,
+                                int64_t batch, int64_t q_heads, int64_t k_heads, int64_t seq, int64_t head_dim, int64_t cos_batch,
+                                int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                                int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+                                int64_t qo_stride_b, int64_t qo_stride_h, int64_t qo_stride_s,
+                                int64_t ko_stride_b, int64_t ko_stride_h, int64_t ko_stride_s,
+                                int dtype, void* stream) {
+  if (!dtype_ok(dtype)) return fail(B200_ERR_DTYPE, "%s: unsupported dtype %d", __func__, dtype);
+  if (batch < 0 || q_heads < 0 || k_heads < 0 || seq < 0 || head_dim < 0) return fail(B200_ERR_SHAPE, "%s: negative size", __func__);
+  if (head_dim % 2 != 0) return fail(B200_ERR_SHAPE, "%s: head_dim=%lld must be even", __func__, (long long)head_dim);
+  if (cos_batch != 1 && cos_batch != batch) return fail(B200_ERR_SHAPE, "%s: cos_batch must be 1 or batch", __func__);
+  if (batch > 0x7fffffffLL || q_heads > (1 << 20) || k_heads > (1 << 20) || head_dim > (1 << 20))
+    return fail(B200_ERR_SHAPE, "%s: size out of range", __func__);
+  if (batch == 0 || seq == 0 || head_dim == 0 || (q_heads == 0 && k_heads == 0)) return B200_OK;
+  if (q_heads > 0) {
+    B200_REQUIRE_PTR(q);
+    B200_REQUIRE_PTR(q_out);
+  }
+  if (k_heads > 0) {
+    B200_REQUIRE_PTR(k);
+    B200_REQUIRE_PTR(k_out);
+  }
+  B200_REQUIRE_PTR(cos);
+  B200_REQUIRE_PTR(sin);
+  const size_t es = dtype_size(dtype);
+  if (!aligned(q, es) || !aligned(k, es) || !aligned(q_out, es) || !aligned(k_out, es) || !aligned(cos, es) || !aligned(sin, es))
+    return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to the element size", __func__);
+  if (int rc = check_device()) return rc;
+  PairedArgs p{};
+  p.t[0] = PairedTensor{q, q_out, q_stride_b, q_stride_h, q_stride_s, qo_stride_b, qo_stride_h, qo_stride_s, static_cast<int>(q_heads)};
+  p.t[1] = PairedTensor{k, k_out, k_stride_b, k_stride_h, k_stride_s, ko_stride_b, ko_stride_h, ko_stride_s, static_cast<int>(k_heads)};
+  p.cos = cos;
+  p.sin = sin;
+  p.cs_stride_b = cos_batch == 1 ? 0 : seq * head_dim;
+  p.seq = seq;
+  p.batch = static_cast<int>(batch);
+  p.head_dim = static_cast<int>(head_dim);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  B200_DISPATCH_DTYPE(dtype, T, return run_paired<T>(p, st));
   return B200_OK;
 }

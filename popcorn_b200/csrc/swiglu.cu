@@ -141,6 +141,106 @@ swiglu_vec_kernel(const T* a, const T* b, T* out, Index total_words, Index words
   }
 }
 
+// ---------------------------------------------------------------- backward --
+//
+// out = round_T(silu(a)) * b.  PyTorch's autograd of the reference evaluates, tensor by tensor,
+//   db = round_T(g * round_T(silu(a)))
+//   gs = round_T(g * b)                                  (gradient reaching silu)
+//   da = round_T(gs * (s * (1 + a * (1 - s)))),  s = 1 / (1 + exp(-a)) in fp32
+// and this kernel does the same in one pass (3 reads, 2 writes per element).
+template <int MATH>
+__device__ __forceinline__ float dsilu_f32(float a) {
+  const float d = __fadd_rn(1.0f, exp_neg<MATH>(a));
+  const float s = MATH == 0 ? __fdiv_rn(1.0f, d) : rcp_approx(d);
+  return __fmul_rn(s, __fmaf_rn(a, __fsub_rn(1.0f, s), 1.0f));
+}
+
+template <typename T, int UNROLL, typename Index, int MATH>
+__global__ void __launch_bounds__(256)
+swiglu_bwd_vec_kernel(const T* g, const T* a, const T* b, T* da, T* db, Index total_words, Index words_per_row,
+                      int64_t ldg, int64_t lda, int64_t ldb, int64_t ldda, int64_t lddb) {
+  constexpr int V = Num<T>::kVec;
+  constexpr int THREADS = 256;
+  pdl_prologue();
+  const Index first = static_cast<Index>(blockIdx.x) * (THREADS * UNROLL) + threadIdx.x;
+  uint4 vg[UNROLL], va[UNROLL], vb[UNROLL];
+  int64_t off_da[UNROLL], off_db[UNROLL];
+  bool ok[UNROLL];
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) {
+    const Index idx = first + static_cast<Index>(u) * THREADS;
+    ok[u] = idx < total_words;
+    const Index row = idx / words_per_row;
+    const int64_t word = static_cast<int64_t>(idx - row * words_per_row) * V;
+    const int64_t r = static_cast<int64_t>(row);
+    vg[u] = va[u] = vb[u] = make_uint4(0, 0, 0, 0);
+    if (ok[u]) {
+      vg[u] = ld_stream(g + r * ldg + word);
+      va[u] = ld_stream(a + r * lda + word);
+      vb[u] = ld_stream(b + r * ldb + word);
+    }
+    off_da[u] = r * ldda + word;
+    off_db[u] = r * lddb + word;
+  }
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) {
+    float fg[V], fa[V], fb[V], ra[V], rb[V];
+    Num<T>::unpack(vg[u], fg);
+    Num<T>::unpack(va[u], fa);
+    Num<T>::unpack(vb[u], fb);
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      const float s = Num<T>::rt(silu_f32<MATH>(fa[j]));
+      rb[j] = __fmul_rn(fg[j], s);
+      const float gs = Num<T>::rt(__fmul_rn(fg[j], fb[j]));
+      ra[j] = __fmul_rn(gs, dsilu_f32<MATH>(fa[j]));
+    }
+    if (ok[u]) {
+      st_stream(da + off_da[u], Num<T>::pack(ra));
+      st_stream(db + off_db[u], Num<T>::pack(rb));
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+swiglu_bwd_scalar_kernel(const T* g, const T* a, const T* b, T* da, T* db, int64_t rows, int64_t cols,
+                         int64_t ldg, int64_t lda, int64_t ldb, int64_t ldda, int64_t lddb) {
+  pdl_prologue();
+  const int64_t total = rows * cols;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / cols, c = i - r * cols;
+    const float fg = Num<T>::up(g[r * ldg + c]), fa = Num<T>::up(a[r * lda + c]), fb = Num<T>::up(b[r * ldb + c]);
+    db[r * lddb + c] = Num<T>::down(__fmul_rn(fg, Num<T>::rt(silu_f32<0>(fa))));
+    da[r * ldda + c] = Num<T>::down(__fmul_rn(Num<T>::rt(__fmul_rn(fg, fb)), dsilu_f32<0>(fa)));
+  }
+}
+
+template <typename T>
+int run_bwd(const void* g, const void* a, const void* b, void* da, void* db, int64_t rows, int64_t cols,
+            int64_t ldg, int64_t lda, int64_t ldb, int64_t ldda, int64_t lddb, cudaStream_t st) {
+  constexpr int V = Num<T>::kVec;
+  constexpr int UNROLL = 2;
+  constexpr int MATH = sizeof(T) == 4 ? 0 : 1;
+  const bool vec = cols % V == 0 && ldg % V == 0 && lda % V == 0 && ldb % V == 0 && ldda % V == 0 && lddb % V == 0 &&
+                   aligned(g, 16) && aligned(a, 16) && aligned(b, 16) && aligned(da, 16) && aligned(db, 16);
+  const int64_t wpr = cols / V;
+  const int64_t total = rows * wpr;
+  if (vec && total < 0x7fffffffLL) {
+    launch(swiglu_bwd_vec_kernel<T, UNROLL, uint32_t, MATH>, static_cast<unsigned>(ceil_div(total, 256 * UNROLL)), 256, 0, st,
+           static_cast<const T*>(g), static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(da), static_cast<T*>(db),
+           static_cast<uint32_t>(total), static_cast<uint32_t>(wpr), ldg, lda, ldb, ldda, lddb);
+    return after_launch("swiglu_bwd_vec_kernel");
+  }
+  const int64_t want = ceil_div(rows * cols, 256);
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
+  launch(swiglu_bwd_scalar_kernel<T>, static_cast<unsigned>(want < cap ? want : cap), 256, 0, st,
+         static_cast<const T*>(g), static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(da), static_cast<T*>(db),
+         rows, cols, ldg, lda, ldb, ldda, lddb);
+  return after_launch("swiglu_bwd_scalar_kernel");
+}
+
 // Any width, any alignment.
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -211,5 +311,27 @@ extern "C" int b200_swiglu(const void* a, const void* b, void* out, int64_t rows
   if (int rc = check_device()) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   B200_DISPATCH_DTYPE(dtype, T, return run<T>(a, b, out, rows, cols, lda, ldb, ldo, st));
+  return B200_OK;
+}
+
+extern "C" int b200_swiglu_backward(const void* grad_out, const void* a, const void* b, void* grad_a, void* grad_b,
+                                    int64_t rows, int64_t cols, int64_t ldg, int64_t lda, int64_t ldb,
+                                    int64_t ldda, int64_t lddb, int dtype, void* stream) {
+  if (!dtype_ok(dtype)) return fail(B200_ERR_DTYPE, "%s: unsupported dtype %d", __func__, dtype);
+  if (rows < 0 || cols < 0) return fail(B200_ERR_SHAPE, "%s: negative size", __func__);
+  if (rows == 0 || cols == 0) return B200_OK;
+  B200_REQUIRE_PTR(grad_out);
+  B200_REQUIRE_PTR(a);
+  B200_REQUIRE_PTR(b);
+  B200_REQUIRE_PTR(grad_a);
+  B200_REQUIRE_PTR(grad_b);
+  if (ldg < cols || lda < cols || ldb < cols || ldda < cols || lddb < cols)
+    return fail(B200_ERR_SHAPE, "%s: leading dimension smaller than cols", __func__);
+  const size_t es = dtype_size(dtype);
+  if (!aligned(grad_out, es) || !aligned(a, es) || !aligned(b, es) || !aligned(grad_a, es) || !aligned(grad_b, es))
+    return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to the element size", __func__);
+  if (int rc = check_device()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  B200_DISPATCH_DTYPE(dtype, T, return run_bwd<T>(grad_out, a, b, grad_a, grad_b, rows, cols, ldg, lda, ldb, ldda, lddb, st));
   return B200_OK;
 }

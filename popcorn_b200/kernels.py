@@ -1,8 +1,8 @@
 """Op declarations on the local registry mirror, each with the `b200` backend attached.
 
-The four existing popcorn ops keep popcorn's names, parameter order and defaults
+The five existing popcorn ops keep popcorn's names, parameter order and defaults
 (src/popcorn/kernels/rms_norm.py:16-21, add_rms_norm.py:8-14,
-rotary_embedding.py:15-20, swiglu.py:10); the MoE steps are new ops because
+rotary_embedding.py:15-20, rope.py:24-29, swiglu.py:10); the MoE steps are new ops because
 popcorn only has them fused inside `momoe` (src/popcorn/kernels/momoe.py:47-53).
 The declaration bodies are never executed: an op here is its signature plus the
 backends registered on it.
@@ -31,6 +31,11 @@ def rotary_embedding(x, cos, sin, interleaved=False):
 
 
 @register_kernel
+def rope(q, k, cos, sin):
+    """Paired Llama-style rotary embedding of queries and keys, layout (batch, heads, seq, head_dim)."""
+
+
+@register_kernel
 def swiglu(a, b):
     """SwiGLU gating: silu(a) * b."""
 
@@ -50,6 +55,9 @@ def moe_unpermute(rows, weights, pos):
     """Gate-weighted sum of expert rows back into token order."""
 
 
-for _op in (rms_norm, add_rms_norm, rotary_embedding, swiglu, moe_route, moe_permute, moe_unpermute):
+# swiglu and rotary_embedding have backward kernels and are registered in their differentiable form
+for _op in (rms_norm, add_rms_norm, rope, moe_route, moe_permute, moe_unpermute):
     _op.register(BACKEND, source=f"popcorn_b200.ops.{_op.name}", forward_only=True)
+for _op in (rotary_embedding, swiglu):
+    _op.register(BACKEND, source=f"popcorn_b200.autograd.{_op.name}")
 del _op

@@ -13,6 +13,7 @@ Signatures served (names and order are popcorn's):
   add_rms_norm(x, residual, weight, eps=1e-6, offset=0.0)  src/popcorn/kernels/add_rms_norm.py:8-14
   rotary_embedding(x, cos, sin, interleaved=False)         src/popcorn/kernels/rotary_embedding.py:15-20
   swiglu(a, b)                                             src/popcorn/kernels/swiglu.py:10
+  rope(q, k, cos, sin)                                     src/popcorn/kernels/rope.py:24-29
 and the MoE steps popcorn only has fused inside `momoe`
 (src/popcorn/kernels/momoe.py:47-53, src/popcorn/impls/momoe_tl.py:1071-1161):
   moe_route, moe_index, moe_scatter_rows, moe_permute, moe_gather, moe_unpermute.
@@ -198,6 +199,35 @@ def rotary_embedding_qk_(q: Tensor, k: Tensor, cos: Tensor, sin: Tensor, interle
     return q, k
 
 
+def rope(q: Tensor, k: Tensor, cos: Tensor, sin: Tensor) -> tuple[Tensor, Tensor]:
+    """Paired Llama-style rotary embedding of q and k, layout (batch, heads, seq, head_dim) (rope.py:24-36)."""
+    device = _require_cuda(q, k, cos, sin)
+    _forbid_grad(q, k)
+    code = _dtype_code(q, "rope")
+    if q.dim() != 4 or k.dim() != 4 or q.shape[0] != k.shape[0] or q.shape[2:] != k.shape[2:]:
+        raise ValueError("rope: q and k must be [batch, heads, seq, head_dim] and agree in batch, seq and head_dim")
+    batch, q_heads, seq, head_dim = q.shape
+    if cos.shape != sin.shape or cos.dim() != 3 or cos.shape[1:] != (seq, head_dim) or cos.shape[0] not in (1, batch):
+        raise ValueError("rope: cos and sin must be [1 or batch, seq, head_dim]")
+    if not (k.dtype == cos.dtype == sin.dtype == q.dtype):
+        raise TypeError("rope: q, k, cos and sin must share a dtype")
+    if head_dim % 2:
+        raise ValueError("rope: head_dim must be even")
+    q = q if head_dim <= 1 or q.stride(-1) == 1 else q.contiguous()
+    k = k if head_dim <= 1 or k.stride(-1) == 1 else k.contiguous()
+    q_out = torch.empty(q.shape, dtype=q.dtype, device=device)
+    k_out = torch.empty(k.shape, dtype=k.dtype, device=device)
+    with torch.cuda.device(device):
+        _lib.call(
+            "b200_rope_paired", _ptr(q), _ptr(k), _ptr(cos.contiguous()), _ptr(sin.contiguous()), _ptr(q_out), _ptr(k_out),
+            batch, q_heads, k.shape[1], seq, head_dim, cos.shape[0],
+            q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+            q_out.stride(0), q_out.stride(1), q_out.stride(2), k_out.stride(0), k_out.stride(1), k_out.stride(2),
+            code, _stream(device),
+        )
+    return q_out, k_out
+
+
 def swiglu(a: Tensor, b: Tensor) -> Tensor:
     """silu(a) * b (swiglu.py:10-18); a and b may be strided column halves of one buffer."""
     device = _require_cuda(a, b)
@@ -212,6 +242,25 @@ def swiglu(a: Tensor, b: Tensor) -> Tensor:
     with torch.cuda.device(device):
         _lib.call("b200_swiglu", _ptr(a2), _ptr(b2), _ptr(out), a2.shape[0], width, lda, ldb, max(width, 1), code, _stream(device))
     return out
+
+
+def swiglu_backward(grad_out: Tensor, a: Tensor, b: Tensor) -> tuple[Tensor, Tensor]:
+    """Gradients of swiglu(a, b) with respect to a and b (what autograd derives from swiglu.py:18)."""
+    device = _require_cuda(grad_out, a, b)
+    code = _dtype_code(a, "swiglu_backward")
+    if not (grad_out.shape == a.shape == b.shape) or not (grad_out.dtype == a.dtype == b.dtype):
+        raise ValueError("swiglu_backward: grad_out, a and b must share shape and dtype")
+    width = a.shape[-1]
+    g2, ldg = _rows(grad_out)
+    a2, lda = _rows(a)
+    b2, ldb = _rows(b)
+    grad_a = torch.empty(a.shape, dtype=a.dtype, device=device)
+    grad_b = torch.empty(a.shape, dtype=a.dtype, device=device)
+    ld = max(width, 1)
+    with torch.cuda.device(device):
+        _lib.call("b200_swiglu_backward", _ptr(g2), _ptr(a2), _ptr(b2), _ptr(grad_a), _ptr(grad_b), a2.shape[0], width,
+                  ldg, lda, ldb, ld, ld, code, _stream(device))
+    return grad_a, grad_b
 
 
 def moe_route(router_logits: Tensor, top_k: int) -> tuple[Tensor, Tensor]:

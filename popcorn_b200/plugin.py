@@ -4,10 +4,10 @@
     popcorn_b200.plugin.register()            # needs `popcorn` importable
     popcorn.KERNELS["rms_norm"](x, w, backend="b200")
 
-For the four ops popcorn already defines, this is one `op.register(name,
+For the five ops popcorn already defines, this is one `op.register(name,
 source=..., forward_only=True)` line each, the same form popcorn's own backends
 use (src/popcorn/kernels/rms_norm.py:33-59, add_rms_norm.py:26-28,
-rotary_embedding.py:43-45, swiglu.py:21-31).  The sources are bare: each
+rotary_embedding.py:43-45, rope.py:39, swiglu.py:21-31).  The sources are bare: each
 popcorn_b200.ops function takes the reference's parameters positionally in the
 reference's order, which is what popcorn checks when the source is first
 resolved (src/popcorn/core/dispatcher.py:184-201).
@@ -27,8 +27,9 @@ import torch
 from torch import Tensor
 
 BACKEND = "b200"
-EXISTING_OPS = ("rms_norm", "add_rms_norm", "rotary_embedding", "swiglu")
+EXISTING_OPS = ("rms_norm", "add_rms_norm", "rotary_embedding", "rope", "swiglu")
 NEW_OPS = ("moe_route", "moe_permute", "moe_unpermute")
+DIFFERENTIABLE_OPS = ("swiglu", "rotary_embedding")
 
 _SUPPORTED = (torch.float32, torch.float16, torch.bfloat16)
 
@@ -104,6 +105,9 @@ def register(backend: str = BACKEND) -> list[str]:
     for name in (*EXISTING_OPS, *NEW_OPS):
         op = popcorn.KERNELS[name]
         if backend not in op.available_backends():
-            op.register(backend, source=f"popcorn_b200.ops.{name}", predicate=accepts, forward_only=True)
+            if name in DIFFERENTIABLE_OPS:  # backward kernels exist: serve training calls too
+                op.register(backend, source=f"popcorn_b200.autograd.{name}", predicate=accepts)
+            else:
+                op.register(backend, source=f"popcorn_b200.ops.{name}", predicate=accepts, forward_only=True)
         served.append(name)
     return served

@@ -35,6 +35,7 @@ REFERENCE_HASHES = {
     "rms_norm": "520d99dddf52",
     "add_rms_norm": "efa7d047c69a",
     "rotary_embedding": "54089714d061",
+    "rope": "1b989955d9be",
     "swiglu": "a2768d81c5aa",
     "moe_route": "3b877b7d155e",
     "moe_permute": "2d4425c300da",

@@ -43,12 +43,12 @@ class Workload:
             return t.narrow(dim, lo, hi - lo)
 
         per_token = {
-            "rms_norm": ("x",), "add_rms_norm": ("x", "residual"), "rotary_embedding": ("q", "k"),
+            "rms_norm": ("x",), "add_rms_norm": ("x", "residual"), "rotary_embedding": ("q", "k"), "rope": ("q", "k"),
             "swiglu": ("gate_up",), "moe": ("x", "router_logits"),
         }[self.name]
         inputs = {k: (cut(v) if k in per_token else v) for k, v in self.inputs.items()}
         first = inputs[per_token[0]]
-        tokens = first.shape[0] * (first.shape[1] if self.name == "rotary_embedding" else 1)
+        tokens = first.shape[0] * (first.shape[1] if self.name == "rotary_embedding" else first.shape[2] if self.name == "rope" else 1)
         scale = tokens / max(self.tokens, 1)
         nbytes = {k: int(v * scale) for k, v in self.algorithmic_bytes.items()}
         return Workload(self.name, self.dtype, tokens, inputs, dict(self.args), nbytes)
@@ -98,6 +98,20 @@ def rotary_bf16(scale: float = 1.0, batch: int = 8, seq: int = 4096, q_heads: in
                     {"interleaved": False}, {"rotary_embedding": nbytes})
 
 
+def paired_rope_bf16(scale: float = 1.0, batch: int = 8, seq: int = 4096, q_heads: int = 32, k_heads: int = 8, head_dim: int = 128) -> Workload:
+    """The shapes of config 3 in the layout of popcorn's paired `rope` op: q [8, 32, 4096, 128], k [8, 8, 4096, 128],
+    bf16 tables [1, 4096, 128] with the first half repeated (positions 0..seq-1, theta 500000), seed 2."""
+    batch = _scaled(batch, scale)
+    gen = torch.Generator().manual_seed(2)
+    q = torch.randn(batch, q_heads, seq, head_dim, generator=gen).to(torch.bfloat16)
+    k = torch.randn(batch, k_heads, seq, head_dim, generator=gen).to(torch.bfloat16)
+    cos, sin = rope_tables(seq, head_dim // 2)
+    cos = cos.repeat(1, 2)[None].to(torch.bfloat16)
+    sin = sin.repeat(1, 2)[None].to(torch.bfloat16)
+    nbytes = 2 * (q.numel() + k.numel()) * 2 + (cos.numel() + sin.numel()) * 2
+    return Workload("rope", torch.bfloat16, batch * seq, {"q": q, "k": k, "cos": cos, "sin": sin}, {}, {"rope": nbytes})
+
+
 def swiglu_bf16(scale: float = 1.0, rows: int = 32768, cols: int = 14336) -> Workload:
     """Config 4: gate_up [32768, 2*14336] bf16 ~ N(0,1); gate = first half, up = second half, seed 3."""
     rows = _scaled(rows, scale)
@@ -128,6 +142,7 @@ CONFIGS = {
     "rms_norm_fp32": rms_norm_fp32,
     "add_rms_norm_bf16": add_rms_norm_bf16,
     "rotary_bf16": rotary_bf16,
+    "paired_rope_bf16": paired_rope_bf16,
     "swiglu_bf16": swiglu_bf16,
     "moe_bf16": moe_bf16,
 }

@@ -100,6 +100,24 @@ def rotary_cases() -> None:
         save_case(name, {"x": x, "cos": cos, "sin": sin, "y": y}, {"op": "rotary_embedding", "interleaved": interleaved})
 
 
+def paired_rope_cases() -> None:
+    ref = KERNELS["rope"].reference
+    for name, seed, batch, hq, hk, seq, dim, dtype, cos_batch in [
+        ("pairedrope_bf16_2x4x2x16x64", 50, 2, 4, 2, 16, 64, BF16, 1),
+        ("pairedrope_bf16_2x8x2x8x128_cb2", 51, 2, 8, 2, 8, 128, BF16, 2),
+        ("pairedrope_f32_1x2x1x8x16", 52, 1, 2, 1, 8, 16, F32, 1),
+        ("pairedrope_f16_2x3x1x5x20", 53, 2, 3, 1, 5, 20, F16, 1),
+    ]:
+        gen = torch.Generator().manual_seed(seed)
+        q = randn(gen, batch, hq, seq, dim).to(dtype)
+        k = randn(gen, batch, hk, seq, dim).to(dtype)
+        # the reference's test inputs: cos / sin of a random angle table whose first half is repeated (rope.py:13-14)
+        cos = torch.cos(randn(gen, cos_batch, seq, dim)).chunk(2, -1)[0].repeat(1, 1, 2).to(dtype)
+        sin = torch.sin(randn(gen, cos_batch, seq, dim)).chunk(2, -1)[0].repeat(1, 1, 2).to(dtype)
+        yq, yk = ref(q, k, cos, sin)
+        save_case(name, {"q": q, "k": k, "cos": cos, "sin": sin, "yq": yq, "yk": yk}, {"op": "rope"})
+
+
 def swiglu_cases() -> None:
     ref = KERNELS["swiglu"].reference
     for name, seed, rows, cols, dtype, scale in [
@@ -148,6 +166,7 @@ def main() -> None:
     rms_norm_cases()
     add_rms_norm_cases()
     rotary_cases()
+    paired_rope_cases()
     swiglu_cases()
     momoe_cases()
     import popcorn

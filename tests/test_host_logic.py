@@ -85,11 +85,13 @@ def test_mirror_dispatch_forced_scoped_and_ordered():
 
 
 def test_forward_only_backend_declines_grad():
-    x = torch.ones(3, requires_grad=True)
+    x = torch.ones(3, 8, requires_grad=True)
+    w = torch.ones(8)
     with pytest.raises(registry.DispatchError, match="no backward implementation"):
-        kernels.swiglu(x, x, backend="b200")
+        kernels.rms_norm(x, w, backend="b200")
     with pytest.raises(registry.DispatchError, match="no registered backend"):
-        kernels.swiglu(x, x)
+        kernels.rms_norm(x, w)
+    assert not kernels.swiglu["b200"].forward_only and not kernels.rotary_embedding["b200"].forward_only
 
 
 def test_workload_shapes_and_bytes():
@@ -131,7 +133,7 @@ def test_plugin_registers_on_real_popcorn(tmp_path, monkeypatch):
     for name in served:
         op = popcorn.KERNELS[name]
         assert "b200" in op.available_backends()
-        assert op["b200"].forward_only
+        assert op["b200"].forward_only == (name not in plugin.DIFFERENTIABLE_OPS)
     # existing ops keep the reference last and their other backends intact
     assert popcorn.KERNELS["swiglu"].available_backends()[-1] == "torch"
     # popcorn resolves the bare source and checks it against the reference signature

@@ -50,6 +50,13 @@ def test_rotary_embedding(name):
     assert torch.equal(oracle.rotary_embedding(t["x"], t["cos"], t["sin"], meta["interleaved"]), t["y"])
 
 
+@pytest.mark.parametrize("name", names("pairedrope"))
+def test_paired_rope(name):
+    t, _ = load_case(name)
+    yq, yk = oracle.rope(t["q"], t["k"], t["cos"], t["sin"])
+    assert torch.equal(yq, t["yq"]) and torch.equal(yk, t["yk"])
+
+
 @pytest.mark.parametrize("name", names("swiglu"))
 def test_swiglu(name):
     t, _ = load_case(name)

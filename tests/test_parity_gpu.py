@@ -73,6 +73,35 @@ def test_golden_rotary(name):
     assert torch.equal(x.cpu(), t["y"]), f"{name}: in-place rotary output is not bit-identical"
 
 
+@pytest.mark.parametrize("name", [n for n in case_names() if n.startswith("pairedrope")])
+def test_golden_paired_rope(name):
+    t, _ = load_case(name)
+    yq, yk = ops.rope(gpu(t["q"]), gpu(t["k"]), gpu(t["cos"]), gpu(t["sin"]))
+    assert torch.equal(yq.cpu(), t["yq"]) and torch.equal(yk.cpu(), t["yk"]), f"{name}: paired rope is not bit-identical"
+
+
+PAIRED_ROPE_CASES = [
+    # batch, q_heads, k_heads, seq, head_dim, dtype, cos_batch
+    (2, 32, 8, 64, 128, BF16, 1), (3, 5, 1, 33, 64, BF16, 3), (1, 4, 4, 100, 256, BF16, 1), (2, 3, 2, 9, 96, F16, 1),
+    (2, 2, 1, 17, 32, F32, 2), (1, 3, 2, 7, 20, BF16, 1), (2, 2, 2, 5, 6, F32, 1), (1, 1, 1, 300, 16, BF16, 1),
+]
+
+
+@pytest.mark.parametrize("batch,hq,hk,seq,dim,dtype,cos_batch", PAIRED_ROPE_CASES)
+def test_paired_rope_shapes(batch, hq, hk, seq, dim, dtype, cos_batch):
+    q = randn(1400 + dim, batch, hq, seq, dim, dtype=dtype, scale=2.0)
+    k = randn(1401 + dim, batch, hk, seq, dim, dtype=dtype, scale=2.0)
+    cos = torch.cos(randn(1402, cos_batch, seq, dim)).to(dtype)  # second half NOT a copy of the first
+    sin = torch.sin(randn(1403, cos_batch, seq, dim)).to(dtype)
+    want_q, want_k = oracle.rope(q, k, cos, sin)
+    got_q, got_k = ops.rope(gpu(q), gpu(k), gpu(cos), gpu(sin))
+    assert torch.equal(got_q.cpu(), want_q) and torch.equal(got_k.cpu(), want_k)
+    # (batch, seq, heads, head_dim) storage viewed as (batch, heads, seq, head_dim): strided input
+    stored = gpu(q.transpose(1, 2).contiguous()).transpose(1, 2)
+    got_q2, _ = ops.rope(stored, gpu(k), gpu(cos), gpu(sin))
+    assert torch.equal(got_q2.cpu(), want_q)
+
+
 @pytest.mark.parametrize("name", [n for n in case_names() if n.startswith("swiglu")])
 def test_golden_swiglu(name):
     t, _ = load_case(name)
