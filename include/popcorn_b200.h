@@ -101,6 +101,26 @@ int b200_add_rms_norm(const void* x, const void* residual, const void* weight,
                       int dtype, double eps, double offset, void* stream);
 
 /*
+ * Backward of b200_rms_norm and b200_add_rms_norm: what autograd derives from the references
+ * (src/popcorn/kernels/_utils.py:14-16, rms_norm.py:29-30, add_rms_norm.py:22-23), with
+ * n = round_T(x * r), r = rsqrt(mean(x^2) + eps):
+ *   grad_weight = round_T(sum_rows round_T(g * n)),  grad_bias = round_T(sum_rows g)  (if grad_bias != NULL)
+ *   gn = round_T(g * w);  grad_x = round_T(gn * r - x * r^3 * mean_cols(gn * x))      (fp32 inside)
+ * For add_rms_norm w is round_T(weight + offset), `s` is the residual stream the forward pass returned,
+ * grad_s (may be NULL) is the gradient arriving on it, and grad_x = round_T(round_T(...) + grad_s) is
+ * the gradient of both x and residual.  Sums over rows are accumulated in fp32.
+ * scratch: b200_rms_norm_backward_scratch_bytes(rows, cols, grad_bias != NULL) bytes, 16-byte aligned.
+ */
+int b200_rms_norm_backward_scratch_bytes(int64_t rows, int64_t cols, int with_bias, size_t* bytes);
+int b200_rms_norm_backward(const void* grad_y, const void* x, const void* weight, void* grad_x, void* grad_weight,
+                           void* grad_bias, int64_t rows, int64_t cols, int64_t ldg, int64_t ldx, int64_t lddx,
+                           int dtype, double eps, void* scratch, size_t scratch_bytes, void* stream);
+int b200_add_rms_norm_backward(const void* grad_y, const void* grad_s, const void* s, const void* weight, void* grad_x,
+                               void* grad_weight, int64_t rows, int64_t cols, int64_t ldgy, int64_t ldgs, int64_t lds,
+                               int64_t lddx, int dtype, double eps, double offset, void* scratch, size_t scratch_bytes,
+                               void* stream);
+
+/*
  * Rotary position embedding over x[batch, seq, heads, head_dim]:
  *   interleaved == 0 (GPT-NeoX halves): (x[j], x[half + j]) rotated by angle (seq, j)
  *   interleaved != 0 (GPT-J pairs):     (x[2j], x[2j + 1])

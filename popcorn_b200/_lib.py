@@ -33,6 +33,9 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "b200_wait_timeouts": (ctypes.c_uint64, []),
     "b200_rms_norm": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _int, _dbl, _ptr]),
     "b200_add_rms_norm": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _int, _dbl, _dbl, _ptr]),
+    "b200_rms_norm_backward_scratch_bytes": (_int, [_i64, _i64, _int, ctypes.POINTER(_size)]),
+    "b200_rms_norm_backward": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _int, _dbl, _ptr, _size, _ptr]),
+    "b200_add_rms_norm_backward": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _int, _dbl, _dbl, _ptr, _size, _ptr]),
     "b200_rope": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _ptr]),
     "b200_rope_qk": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _ptr]),
     "b200_rope_paired": (_int, [_ptr] * 6 + [_i64] * 18 + [_int, _ptr]),

@@ -48,6 +48,52 @@ class _Rotary(torch.autograd.Function):
         return grad_x, None, None, None
 
 
+class _RmsNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: Tensor, weight: Tensor, bias: Tensor | None, eps: float) -> Tensor:
+        ctx.save_for_backward(x, weight)
+        ctx.with_bias, ctx.eps = bias is not None, eps
+        with torch.no_grad():
+            return ops.rms_norm(x, weight, bias, eps)
+
+    @staticmethod
+    def backward(ctx, grad_y: Tensor):
+        x, weight = ctx.saved_tensors
+        with torch.no_grad():
+            grad_x, grad_w, grad_b = ops.rms_norm_backward(grad_y.contiguous(), x, weight, ctx.with_bias, ctx.eps)
+        return grad_x, grad_w, grad_b, None
+
+
+class _AddRmsNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: Tensor, residual: Tensor, weight: Tensor, eps: float, offset: float):
+        with torch.no_grad():
+            y, s = ops.add_rms_norm(x, residual, weight, eps, offset)
+        ctx.save_for_backward(s, weight)
+        ctx.eps, ctx.offset = eps, offset
+        return y, s
+
+    @staticmethod
+    def backward(ctx, grad_y: Tensor | None, grad_s: Tensor | None):
+        s, weight = ctx.saved_tensors
+        if grad_y is None:  # only the residual stream was used downstream
+            return grad_s, grad_s, torch.zeros_like(weight), None, None
+        with torch.no_grad():
+            grad_x, grad_w = ops.add_rms_norm_backward(grad_y.contiguous(), None if grad_s is None else grad_s.contiguous(),
+                                                       s, weight, ctx.eps, ctx.offset)
+        return grad_x, grad_x, grad_w, None, None
+
+
+def rms_norm(x: Tensor, weight: Tensor, bias: Tensor | None = None, eps: float = 1e-6) -> Tensor:
+    """RMS norm with gradients for x, weight and bias."""
+    return _RmsNorm.apply(x, weight, bias, eps)
+
+
+def add_rms_norm(x: Tensor, residual: Tensor, weight: Tensor, eps: float = 1e-6, offset: float = 0.0) -> tuple[Tensor, Tensor]:
+    """Residual add + RMS norm with gradients for x, residual and weight."""
+    return _AddRmsNorm.apply(x, residual, weight, eps, offset)
+
+
 def swiglu(a: Tensor, b: Tensor) -> Tensor:
     """silu(a) * b with gradients for a and b."""
     return _SwiGLU.apply(a, b)

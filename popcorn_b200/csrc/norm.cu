@@ -238,6 +238,269 @@ int run(const void* x, const void* res, const void* w, const void* b, void* y, v
   return after_launch("rms_stream_kernel");
 }
 
+// ---------------------------------------------------------------- backward --
+//
+// y = round_T(round_T(h * r) * w) (+ b), h = fp32(x), r = rsqrt(mean(h^2) + eps).  What autograd
+// derives from the reference (src/popcorn/kernels/_utils.py:14-16, rms_norm.py:29-30,
+// add_rms_norm.py:22-23), tensor by tensor, with n = round_T(h * r):
+//   grad_b = sum_rows g                         grad_w = sum_rows round_T(g * n)
+//   gn = round_T(g * w)                         (fp32 from here on)
+//   gr = sum_cols gn * h                        gv = gr * (-0.5 * r^3)
+//   grad_h = gn * r + ((gv / cols) * 2) * h     grad_x = round_T(grad_h)
+// add_rms_norm: w is round_T(weight + offset), x is the saved residual stream s, and the gradient
+// arriving on s is added: grad_x = grad_residual = round_T(round_T(grad_h) + gs).
+//
+// Persistent CTAs: each walks over rows blockIdx.x, blockIdx.x + gridDim.x, ... with the row in
+// registers, keeps fp32 partial column sums for grad_w / grad_b in registers, and writes them to
+// its own line of the scratch buffer at the end; rms_bwd_reduce_kernel adds the lines up.
+template <typename T, int ITEMS, bool ADD, bool HAS_BIAS>
+__global__ void __launch_bounds__(256)
+rms_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ gs, const T* __restrict__ x,
+                    const T* __restrict__ weight, T* __restrict__ dx, float* __restrict__ part_w,
+                    float* __restrict__ part_b, int64_t rows, int nvec, int64_t ldg, int64_t ldgs, int64_t ldx,
+                    int64_t lddx, float cols_f, float eps, float offset) {
+  constexpr int V = Num<T>::kVec;
+  pdl_prologue();
+  __shared__ float red[2][2][8];  // [parity][quantity][warp]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  float accw[ITEMS][V], accb[HAS_BIAS ? ITEMS : 1][V];
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i)
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      accw[i][j] = 0.f;
+      if constexpr (HAS_BIAS) accb[i][j] = 0.f;
+    }
+  bool ok[ITEMS];
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) ok[i] = tid + i * 256 < nvec;
+
+  int parity = 0;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, parity ^= 1) {
+    uint4 xv[ITEMS], gv[ITEMS];
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      xv[i] = gv[i] = make_uint4(0, 0, 0, 0);
+      if (ok[i]) {
+        const int64_t col = static_cast<int64_t>(tid + i * 256) * V;
+        xv[i] = ld_stream(x + row * ldx + col);
+        gv[i] = ld_stream(gy + row * ldg + col);
+      }
+    }
+    // gn = round_T(g * w) replaces g in registers (fp32 for T = float, packed otherwise)
+    float sumsq = 0.f, dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      if (!ok[i]) continue;
+      const int64_t col = static_cast<int64_t>(tid + i * 256) * V;
+      float h[V], g[V], w[V];
+      Num<T>::unpack(xv[i], h);
+      Num<T>::unpack(gv[i], g);
+      Num<T>::unpack(ld_reuse(weight + col), w);
+#pragma unroll
+      for (int j = 0; j < V; j += 2) {
+        if constexpr (ADD) {
+          w[j] = __fadd_rn(w[j], offset);
+          w[j + 1] = __fadd_rn(w[j + 1], offset);
+          Num<T>::round2(w[j], w[j + 1]);
+        }
+        if constexpr (HAS_BIAS) {
+          accb[i][j] = __fadd_rn(accb[i][j], g[j]);
+          accb[i][j + 1] = __fadd_rn(accb[i][j + 1], g[j + 1]);
+        }
+        float gn0 = __fmul_rn(g[j], w[j]), gn1 = __fmul_rn(g[j + 1], w[j + 1]);
+        Num<T>::round2(gn0, gn1);
+        sumsq = __fmaf_rn(h[j], h[j], sumsq);
+        sumsq = __fmaf_rn(h[j + 1], h[j + 1], sumsq);
+        dot = __fmaf_rn(gn0, h[j], dot);
+        dot = __fmaf_rn(gn1, h[j + 1], dot);
+      }
+    }
+    sumsq = warp_sum(sumsq);
+    dot = warp_sum(dot);
+    if (lane == 0) {
+      red[parity][0][warp] = sumsq;
+      red[parity][1][warp] = dot;
+    }
+    __syncthreads();  // the other parity's slots are free again once everyone is past this point
+    float tot_sq = 0.f, tot_dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      tot_sq = __fadd_rn(tot_sq, red[parity][0][k]);
+      tot_dot = __fadd_rn(tot_dot, red[parity][1][k]);
+    }
+    const float r = inv_rms(tot_sq, cols_f, eps);
+    const float gv_scalar = __fmul_rn(tot_dot, __fmul_rn(-0.5f, __fmul_rn(__fmul_rn(r, r), r)));
+    const float coef = __fmul_rn(__fdiv_rn(gv_scalar, cols_f), 2.0f);
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      if (!ok[i]) continue;
+      const int64_t col = static_cast<int64_t>(tid + i * 256) * V;
+      float h[V], g[V], w[V], out[V], extra[V];
+      Num<T>::unpack(xv[i], h);
+      Num<T>::unpack(gv[i], g);
+      Num<T>::unpack(ld_reuse(weight + col), w);
+      if (ADD && gs != nullptr) Num<T>::unpack(ld_stream(gs + row * ldgs + col), extra);
+#pragma unroll
+      for (int j = 0; j < V; j += 2) {
+        if constexpr (ADD) {
+          w[j] = __fadd_rn(w[j], offset);
+          w[j + 1] = __fadd_rn(w[j + 1], offset);
+          Num<T>::round2(w[j], w[j + 1]);
+        }
+        float gn0 = __fmul_rn(g[j], w[j]), gn1 = __fmul_rn(g[j + 1], w[j + 1]);
+        Num<T>::round2(gn0, gn1);
+        float n0 = __fmul_rn(h[j], r), n1 = __fmul_rn(h[j + 1], r);
+        Num<T>::round2(n0, n1);
+        float gw0 = __fmul_rn(g[j], n0), gw1 = __fmul_rn(g[j + 1], n1);
+        Num<T>::round2(gw0, gw1);
+        accw[i][j] = __fadd_rn(accw[i][j], gw0);
+        accw[i][j + 1] = __fadd_rn(accw[i][j + 1], gw1);
+        out[j] = __fadd_rn(__fmul_rn(gn0, r), __fmul_rn(coef, h[j]));
+        out[j + 1] = __fadd_rn(__fmul_rn(gn1, r), __fmul_rn(coef, h[j + 1]));
+        if (ADD && gs != nullptr) {
+          Num<T>::round2(out[j], out[j + 1]);
+          out[j] = __fadd_rn(out[j], extra[j]);
+          out[j + 1] = __fadd_rn(out[j + 1], extra[j + 1]);
+        }
+      }
+      st_stream(dx + row * lddx + col, Num<T>::pack(out));
+    }
+  }
+  const int64_t cols = static_cast<int64_t>(nvec) * V;
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    if (!ok[i]) continue;
+    const int64_t col = static_cast<int64_t>(tid + i * 256) * V;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      part_w[blockIdx.x * cols + col + j] = accw[i][j];
+      if constexpr (HAS_BIAS) part_b[blockIdx.x * cols + col + j] = accb[i][j];
+    }
+  }
+}
+
+// Any width, any alignment: the same arithmetic with scalar accesses; each CTA accumulates its
+// partial column sums directly in its own scratch line (zeroed first by the CTA itself).
+template <typename T, bool ADD>
+__global__ void __launch_bounds__(256)
+rms_bwd_stream_kernel(const T* __restrict__ gy, const T* __restrict__ gs, const T* __restrict__ x,
+                      const T* __restrict__ weight, T* __restrict__ dx, float* __restrict__ part_w,
+                      float* __restrict__ part_b, int64_t rows, int64_t cols, int64_t ldg, int64_t ldgs, int64_t ldx,
+                      int64_t lddx, float cols_f, float eps, float offset) {
+  pdl_prologue();
+  __shared__ float red[2][8];
+  float* my_w = part_w + blockIdx.x * cols;
+  float* my_b = part_b ? part_b + blockIdx.x * cols : nullptr;
+  for (int64_t c = threadIdx.x; c < cols; c += 256) {
+    my_w[c] = 0.f;
+    if (my_b) my_b[c] = 0.f;
+  }
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    float sumsq = 0.f, dot = 0.f;
+    for (int64_t c = threadIdx.x; c < cols; c += 256) {
+      const float h = Num<T>::up(x[row * ldx + c]);
+      float w = Num<T>::up(weight[c]);
+      if (ADD) w = Num<T>::rt(__fadd_rn(w, offset));
+      const float gn = Num<T>::rt(__fmul_rn(Num<T>::up(gy[row * ldg + c]), w));
+      sumsq = __fmaf_rn(h, h, sumsq);
+      dot = __fmaf_rn(gn, h, dot);
+    }
+    sumsq = warp_sum(sumsq);
+    dot = warp_sum(dot);
+    __syncthreads();  // the previous row's readers are done with `red`
+    if ((threadIdx.x & 31) == 0) {
+      red[0][threadIdx.x >> 5] = sumsq;
+      red[1][threadIdx.x >> 5] = dot;
+    }
+    __syncthreads();
+    float tot_sq = 0.f, tot_dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      tot_sq = __fadd_rn(tot_sq, red[0][k]);
+      tot_dot = __fadd_rn(tot_dot, red[1][k]);
+    }
+    const float r = inv_rms(tot_sq, cols_f, eps);
+    const float coef = __fmul_rn(__fdiv_rn(__fmul_rn(tot_dot, __fmul_rn(-0.5f, __fmul_rn(__fmul_rn(r, r), r))), cols_f), 2.0f);
+    for (int64_t c = threadIdx.x; c < cols; c += 256) {
+      const float h = Num<T>::up(x[row * ldx + c]);
+      const float g = Num<T>::up(gy[row * ldg + c]);
+      float w = Num<T>::up(weight[c]);
+      if (ADD) w = Num<T>::rt(__fadd_rn(w, offset));
+      const float gn = Num<T>::rt(__fmul_rn(g, w));
+      const float n = Num<T>::rt(__fmul_rn(h, r));
+      my_w[c] = __fadd_rn(my_w[c], Num<T>::rt(__fmul_rn(g, n)));
+      if (my_b) my_b[c] = __fadd_rn(my_b[c], g);
+      float out = __fadd_rn(__fmul_rn(gn, r), __fmul_rn(coef, h));
+      if (ADD && gs != nullptr) out = __fadd_rn(Num<T>::rt(out), Num<T>::up(gs[row * ldgs + c]));
+      dx[row * lddx + c] = Num<T>::down(out);
+    }
+  }
+}
+
+// out[c] = round_T(sum over lines of part[line][c]), lines added in order.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rms_bwd_reduce_kernel(const float* __restrict__ part, int lines, int64_t cols, T* __restrict__ out) {
+  pdl_prologue();
+  const int64_t c = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (c >= cols) return;
+  float acc = 0.f;
+  for (int l = 0; l < lines; ++l) acc = __fadd_rn(acc, part[l * cols + c]);
+  out[c] = Num<T>::down(acc);
+}
+
+int bwd_lines(int64_t rows) {
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 2;
+  return static_cast<int>(rows < cap ? (rows > 0 ? rows : 1) : cap);
+}
+
+template <typename T, bool ADD>
+int run_bwd(const void* gy, const void* gs, const void* x, const void* w, void* dx, void* dw, void* db,
+            int64_t rows, int64_t cols, int64_t ldg, int64_t ldgs, int64_t ldx, int64_t lddx,
+            float eps, float offset, void* scratch, cudaStream_t st) {
+  constexpr int V = Num<T>::kVec;
+  const int lines = bwd_lines(rows);
+  float* part_w = static_cast<float*>(scratch);
+  float* part_b = db ? part_w + static_cast<int64_t>(lines) * cols : nullptr;
+  const float cols_f = static_cast<float>(cols);
+  bool vec = cols % V == 0 && ldg % V == 0 && ldx % V == 0 && lddx % V == 0 && aligned(gy, 16) && aligned(x, 16) &&
+             aligned(dx, 16) && aligned(w, 16) && cols / V <= 256 * 8;
+  if (gs) vec = vec && ldgs % V == 0 && aligned(gs, 16);
+  const T *tgy = static_cast<const T*>(gy), *tgs = static_cast<const T*>(gs), *tx = static_cast<const T*>(x), *tw = static_cast<const T*>(w);
+  T* tdx = static_cast<T*>(dx);
+  if (vec) {
+    const int nvec = static_cast<int>(cols / V);
+#define B200_BWD(ITEMS, BIAS)                                                                              \
+  launch(rms_bwd_rows_kernel<T, ITEMS, ADD, BIAS>, lines, 256, 0, st, tgy, tgs, tx, tw, tdx, part_w, part_b, \
+         rows, nvec, ldg, ldgs, ldx, lddx, cols_f, eps, offset)
+#define B200_BWD_ITEMS(BIAS)                 \
+  do {                                       \
+    if (nvec <= 256) B200_BWD(1, BIAS);      \
+    else if (nvec <= 512) B200_BWD(2, BIAS); \
+    else if (nvec <= 1024) B200_BWD(4, BIAS);\
+    else B200_BWD(8, BIAS);                  \
+  } while (0)
+    if (db) B200_BWD_ITEMS(true);
+    else B200_BWD_ITEMS(false);
+#undef B200_BWD_ITEMS
+#undef B200_BWD
+    if (int rc = after_launch("rms_bwd_rows_kernel")) return rc;
+  } else {
+    launch(rms_bwd_stream_kernel<T, ADD>, lines, 256, 0, st, tgy, tgs, tx, tw, tdx, part_w, part_b, rows, cols, ldg, ldgs,
+           ldx, lddx, cols_f, eps, offset);
+    if (int rc = after_launch("rms_bwd_stream_kernel")) return rc;
+  }
+  const unsigned grid = static_cast<unsigned>(ceil_div(cols, 256));
+  launch(rms_bwd_reduce_kernel<T>, grid, 256, 0, st, static_cast<const float*>(part_w), lines, cols, static_cast<T*>(dw));
+  if (int rc = after_launch("rms_bwd_reduce_kernel")) return rc;
+  if (db) {
+    launch(rms_bwd_reduce_kernel<T>, grid, 256, 0, st, static_cast<const float*>(part_b), lines, cols, static_cast<T*>(db));
+    if (int rc = after_launch("rms_bwd_reduce_kernel")) return rc;
+  }
+  return B200_OK;
+}
+
 int check_common(const char* fn, int64_t rows, int64_t cols, int dtype) {
   if (!dtype_ok(dtype)) return fail(B200_ERR_DTYPE, "%s: unsupported dtype %d", fn, dtype);
   if (rows < 0 || cols < 0) return fail(B200_ERR_SHAPE, "%s: negative size (rows=%lld, cols=%lld)", fn, (long long)rows, (long long)cols);
@@ -290,4 +553,54 @@ extern "C" int b200_add_rms_norm(const void* x, const void* residual, const void
   B200_DISPATCH_DTYPE(dtype, T, return (run<T, true>(x, residual, weight, nullptr, y, s, rows, cols, ldx, ldr, ldy, lds,
                                                       static_cast<float>(eps), static_cast<float>(offset), st)));
   return B200_OK;
+}
+
+extern "C" int b200_rms_norm_backward_scratch_bytes(int64_t rows, int64_t cols, int with_bias, size_t* bytes) {
+  B200_REQUIRE_PTR(bytes);
+  if (rows < 0 || cols < 0) return fail(B200_ERR_SHAPE, "%s: negative size", __func__);
+  if (int rc = check_device()) return rc;
+  const size_t lines = static_cast<size_t>(bwd_lines(rows));
+  *bytes = lines * static_cast<size_t>(cols > 0 ? cols : 1) * sizeof(float) * (with_bias ? 2 : 1);
+  return B200_OK;
+}
+
+static int norm_backward(const char* fn, bool add, const void* gy, const void* gs, const void* x, const void* weight, void* dx,
+                         void* dw, void* db, int64_t rows, int64_t cols, int64_t ldg, int64_t ldgs, int64_t ldx, int64_t lddx,
+                         int dtype, double eps, double offset, void* scratch, size_t scratch_bytes, void* stream) {
+  if (int rc = check_common(fn, rows, cols, dtype)) return rc;
+  if (cols == 0) return B200_OK;
+  if (gy == nullptr || x == nullptr || weight == nullptr || dx == nullptr || dw == nullptr || scratch == nullptr)
+    return fail(B200_ERR_NULL_POINTER, "%s: a required pointer is NULL", fn);
+  if (ldg < cols || ldx < cols || lddx < cols || (gs && ldgs < cols)) return fail(B200_ERR_SHAPE, "%s: leading dimension smaller than cols", fn);
+  const size_t es = dtype_size(dtype);
+  if (!aligned(gy, es) || !aligned(x, es) || !aligned(weight, es) || !aligned(dx, es) || !aligned(dw, es) || (gs && !aligned(gs, es)) ||
+      (db && !aligned(db, es)))
+    return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to the element size", fn);
+  if (int rc = check_device()) return rc;
+  const size_t need = static_cast<size_t>(bwd_lines(rows)) * static_cast<size_t>(cols) * sizeof(float) * (db ? 2 : 1);
+  if (scratch_bytes < need || !aligned(scratch, 16))
+    return fail(B200_ERR_SCRATCH, "%s: scratch needs %zu bytes, 16-byte aligned (got %zu)", fn, need, scratch_bytes);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const float e = static_cast<float>(eps), o = static_cast<float>(offset);
+  if (add) {
+    B200_DISPATCH_DTYPE(dtype, T, return (run_bwd<T, true>(gy, gs, x, weight, dx, dw, nullptr, rows, cols, ldg, ldgs, ldx, lddx, e, o, scratch, st)));
+  } else {
+    B200_DISPATCH_DTYPE(dtype, T, return (run_bwd<T, false>(gy, nullptr, x, weight, dx, dw, db, rows, cols, ldg, 0, ldx, lddx, e, 0.f, scratch, st)));
+  }
+  return B200_OK;
+}
+
+extern "C" int b200_rms_norm_backward(const void* grad_y, const void* x, const void* weight, void* grad_x, void* grad_weight,
+                                      void* grad_bias, int64_t rows, int64_t cols, int64_t ldg, int64_t ldx, int64_t lddx,
+                                      int dtype, double eps, void* scratch, size_t scratch_bytes, void* stream) {
+  return norm_backward(__func__, false, grad_y, nullptr, x, weight, grad_x, grad_weight, grad_bias, rows, cols, ldg, 0, ldx, lddx,
+                       dtype, eps, 0.0, scratch, scratch_bytes, stream);
+}
+
+extern "C" int b200_add_rms_norm_backward(const void* grad_y, const void* grad_s, const void* s, const void* weight, void* grad_x,
+                                          void* grad_weight, int64_t rows, int64_t cols, int64_t ldgy, int64_t ldgs, int64_t lds,
+                                          int64_t lddx, int dtype, double eps, double offset, void* scratch, size_t scratch_bytes,
+                                          void* stream) {
+  return norm_backward(__func__, true, grad_y, grad_s, s, weight, grad_x, grad_weight, nullptr, rows, cols, ldgy, ldgs, lds, lddx,
+                       dtype, eps, offset, scratch, scratch_bytes, stream);
 }

@@ -55,9 +55,9 @@ def moe_unpermute(rows, weights, pos):
     """Gate-weighted sum of expert rows back into token order."""
 
 
-# swiglu and rotary_embedding have backward kernels and are registered in their differentiable form
-for _op in (rms_norm, add_rms_norm, rope, moe_route, moe_permute, moe_unpermute):
+# ops with backward kernels are registered in their differentiable form
+for _op in (rope, moe_route, moe_permute, moe_unpermute):
     _op.register(BACKEND, source=f"popcorn_b200.ops.{_op.name}", forward_only=True)
-for _op in (rotary_embedding, swiglu):
+for _op in (rms_norm, add_rms_norm, rotary_embedding, swiglu):
     _op.register(BACKEND, source=f"popcorn_b200.autograd.{_op.name}")
 del _op

@@ -130,6 +130,52 @@ def add_rms_norm(
     return y, s
 
 
+def _norm_scratch(rows: int, cols: int, with_bias: bool, device: torch.device) -> Tensor:
+    need = ctypes.c_size_t(0)
+    with torch.cuda.device(device):
+        _lib.call("b200_rms_norm_backward_scratch_bytes", rows, cols, int(with_bias), ctypes.byref(need))
+    return torch.empty(max(need.value, 16), dtype=torch.uint8, device=device)
+
+
+def rms_norm_backward(grad_y: Tensor, x: Tensor, weight: Tensor, with_bias: bool = False, eps: float = 1e-6) -> tuple[Tensor, Tensor, Tensor | None]:
+    """(grad_x, grad_weight, grad_bias or None) of rms_norm(x, weight, bias, eps)."""
+    device = _require_cuda(grad_y, x, weight)
+    code = _dtype_code(x, "rms_norm_backward")
+    width = x.shape[-1]
+    if grad_y.shape != x.shape or weight.shape != (width,) or not (grad_y.dtype == weight.dtype == x.dtype):
+        raise ValueError("rms_norm_backward: grad_y must match x, and weight must be [hidden] of the same dtype")
+    g2, ldg = _rows(grad_y)
+    x2, ldx = _rows(x)
+    grad_x = torch.empty(x.shape, dtype=x.dtype, device=device)
+    grad_w = torch.empty(width, dtype=x.dtype, device=device)
+    grad_b = torch.empty(width, dtype=x.dtype, device=device) if with_bias else None
+    scratch = _norm_scratch(x2.shape[0], width, with_bias, device)
+    with torch.cuda.device(device):
+        _lib.call("b200_rms_norm_backward", _ptr(g2), _ptr(x2), _ptr(weight.contiguous()), _ptr(grad_x), _ptr(grad_w), _ptr(grad_b),
+                  x2.shape[0], width, ldg, ldx, max(width, 1), code, float(eps), _ptr(scratch), ctypes.c_size_t(scratch.numel()), _stream(device))
+    return grad_x, grad_w, grad_b
+
+
+def add_rms_norm_backward(grad_y: Tensor, grad_s: Tensor | None, s: Tensor, weight: Tensor, eps: float = 1e-6, offset: float = 0.0) -> tuple[Tensor, Tensor]:
+    """(grad_x = grad_residual, grad_weight) of add_rms_norm; `s` is the residual stream the forward returned."""
+    device = _require_cuda(grad_y, grad_s, s, weight)
+    code = _dtype_code(s, "add_rms_norm_backward")
+    width = s.shape[-1]
+    if grad_y.shape != s.shape or (grad_s is not None and grad_s.shape != s.shape) or weight.shape != (width,):
+        raise ValueError("add_rms_norm_backward: gradients must match s, and weight must be [hidden]")
+    gy2, ldgy = _rows(grad_y)
+    s2, lds = _rows(s)
+    gs2, ldgs = _rows(grad_s) if grad_s is not None else (None, 0)
+    grad_x = torch.empty(s.shape, dtype=s.dtype, device=device)
+    grad_w = torch.empty(width, dtype=s.dtype, device=device)
+    scratch = _norm_scratch(s2.shape[0], width, False, device)
+    with torch.cuda.device(device):
+        _lib.call("b200_add_rms_norm_backward", _ptr(gy2), _ptr(gs2), _ptr(s2), _ptr(weight.contiguous()), _ptr(grad_x), _ptr(grad_w),
+                  s2.shape[0], width, ldgy, ldgs, lds, max(width, 1), code, float(eps), float(offset),
+                  _ptr(scratch), ctypes.c_size_t(scratch.numel()), _stream(device))
+    return grad_x, grad_w
+
+
 def _rope_check(x: Tensor, cos: Tensor, sin: Tensor, name: str) -> tuple[int, int]:
     if x.dim() != 4:
         raise ValueError(f"{name}: x must be [batch, seq, heads, head_dim]")

@@ -29,7 +29,7 @@ from torch import Tensor
 BACKEND = "b200"
 EXISTING_OPS = ("rms_norm", "add_rms_norm", "rotary_embedding", "rope", "swiglu")
 NEW_OPS = ("moe_route", "moe_permute", "moe_unpermute")
-DIFFERENTIABLE_OPS = ("swiglu", "rotary_embedding")
+DIFFERENTIABLE_OPS = ("rms_norm", "add_rms_norm", "swiglu", "rotary_embedding")
 
 _SUPPORTED = (torch.float32, torch.float16, torch.bfloat16)
 

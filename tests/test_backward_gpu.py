@@ -91,3 +91,64 @@ def test_registry_serves_training_calls():
     out = kernels.swiglu(x, x, backend="b200")
     out.float().sum().backward()
     assert x.grad is not None and torch.isfinite(x.grad.float()).all()
+
+
+NORM_BWD_SHAPES = [(5, 64, torch.float32), (33, 256, torch.bfloat16), (64, 1024, torch.bfloat16), (40, 4096, torch.bfloat16), (300, 8192, torch.bfloat16),
+                   (7, 16384, torch.bfloat16), (9, 100, torch.float32), (6, 33, torch.bfloat16), (3, 40000, torch.float32), (130, 2048, torch.float16), (600, 512, torch.float32)]
+
+
+@pytest.mark.parametrize("rows,cols,dtype", NORM_BWD_SHAPES)
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_rms_norm_backward(rows, cols, dtype, with_bias):
+    x = randn(1500 + cols, rows, cols, dtype=dtype)
+    w = (1 + 0.1 * randn(1501, cols)).to(dtype)
+    b = randn(1502, cols, dtype=dtype) if with_bias else None
+    g = randn(1503 + cols, rows, cols, dtype=dtype)
+    leaves = [t.to(DEV).requires_grad_(True) for t in (x, w, *([b] if with_bias else []))]
+    y = diff.rms_norm(leaves[0], leaves[1], leaves[2] if with_bias else None, 1e-5)
+    grads = torch.autograd.grad(y, leaves, g.to(DEV))
+    fn = (lambda x_, w_, b_: oracle.rms_norm(x_, w_, b_, 1e-5)) if with_bias else (lambda x_, w_: oracle.rms_norm(x_, w_, None, 1e-5))
+    inputs = (x, w, b) if with_bias else (x, w)
+    native = oracle_grads(fn, inputs, g)
+    truth = oracle_grads(fn, inputs, g, wide=True)
+    for name, mine, nat, tru in zip(("grad_x", "grad_weight", "grad_bias"), grads, native, truth):
+        grade(mine, nat, tru, dtype, f"{name} {rows}x{cols}")
+
+
+@pytest.mark.parametrize("rows,cols,dtype", NORM_BWD_SHAPES[:8])
+@pytest.mark.parametrize("offset,use_s", [(0.0, True), (1.0, True), (0.0, False)])
+def test_add_rms_norm_backward(rows, cols, dtype, offset, use_s):
+    x = randn(1600 + cols, rows, cols, dtype=dtype)
+    r = randn(1601 + cols, rows, cols, dtype=dtype)
+    w = (1 + 0.1 * randn(1602, cols)).to(dtype)
+    gy = randn(1603 + cols, rows, cols, dtype=dtype)
+    gs = randn(1604 + cols, rows, cols, dtype=dtype)
+
+    def run(fn, tensors, wide=False):
+        leaves = [t.double().requires_grad_(True) if wide else t.clone().requires_grad_(True) for t in tensors]
+        y, s = fn(*leaves)
+        outs, seeds = ([y, s], [gy, gs]) if use_s else ([y], [gy])
+        seeds = [t.to(y.device).to(y.dtype) for t in seeds]
+        return torch.autograd.grad(outs, leaves, seeds)
+
+    fn = lambda x_, r_, w_: oracle.add_rms_norm(x_, r_, w_, 1e-5, offset)  # noqa: E731
+    native, truth = run(fn, (x, r, w)), run(fn, (x, r, w), wide=True)
+    mine = run(lambda x_, r_, w_: diff.add_rms_norm(x_, r_, w_, 1e-5, offset), (x.to(DEV), r.to(DEV), w.to(DEV)))
+    for name, m, nat, tru in zip(("grad_x", "grad_residual", "grad_weight"), mine, native, truth):
+        grade(m, nat, tru, dtype, f"{name} {rows}x{cols} offset={offset}")
+    assert torch.equal(mine[0], mine[1])
+
+
+def test_norm_backward_full_width_sample():
+    w = workloads.add_rms_norm_bf16(scale=1 / 16)
+    x, r, weight = (w.inputs[k] for k in ("x", "residual", "weight"))
+    gy = randn(1700, *x.shape, dtype=torch.bfloat16)
+    leaves = [t.to(DEV).requires_grad_(True) for t in (x, r, weight)]
+    y, s = diff.add_rms_norm(*leaves, 1e-5, 0.0)
+    mine = torch.autograd.grad(y, leaves, gy.to(DEV))
+    cpu = [t.clone().requires_grad_(True) for t in (x, r, weight)]
+    native = torch.autograd.grad(oracle.add_rms_norm(*cpu, 1e-5, 0.0)[0], cpu, gy)
+    for name, m, n in zip(("grad_x", "grad_residual", "grad_weight"), mine, native):
+        m = m.cpu()
+        print(f"\n[add_rms_norm backward {name}] elements={n.numel()} not-bit-identical={int((m != n).sum())} max-abs={float((m.float() - n.float()).abs().max()):.3e}")
+    assert float((mine[0].cpu().float() - native[0].float()).abs().max()) <= 2e-2

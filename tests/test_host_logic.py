@@ -85,13 +85,14 @@ def test_mirror_dispatch_forced_scoped_and_ordered():
 
 
 def test_forward_only_backend_declines_grad():
-    x = torch.ones(3, 8, requires_grad=True)
-    w = torch.ones(8)
+    q = torch.ones(1, 2, 4, 8, requires_grad=True)
+    table = torch.ones(1, 4, 8)
     with pytest.raises(registry.DispatchError, match="no backward implementation"):
-        kernels.rms_norm(x, w, backend="b200")
+        kernels.rope(q, q, table, table, backend="b200")
     with pytest.raises(registry.DispatchError, match="no registered backend"):
-        kernels.rms_norm(x, w)
-    assert not kernels.swiglu["b200"].forward_only and not kernels.rotary_embedding["b200"].forward_only
+        kernels.rope(q, q, table, table)
+    for op in (kernels.rms_norm, kernels.add_rms_norm, kernels.swiglu, kernels.rotary_embedding):
+        assert not op["b200"].forward_only
 
 
 def test_workload_shapes_and_bytes():
@@ -137,9 +138,14 @@ def test_plugin_registers_on_real_popcorn(tmp_path, monkeypatch):
     # existing ops keep the reference last and their other backends intact
     assert popcorn.KERNELS["swiglu"].available_backends()[-1] == "torch"
     # popcorn resolves the bare source and checks it against the reference signature
+    from popcorn_b200 import autograd as differentiable
+
     impl = popcorn.KERNELS["add_rms_norm"]["b200"]
     impl._prepare()
-    assert impl.source_fn is ops.add_rms_norm
+    assert impl.source_fn is differentiable.add_rms_norm
+    impl = popcorn.KERNELS["rope"]["b200"]
+    impl._prepare()
+    assert impl.source_fn is ops.rope
     # CPU calls are declined by the predicate rather than served by a fallback
     x = torch.randn(4, 8)
     with pytest.raises(popcorn.core.errors.DispatchError, match="rejected"):
