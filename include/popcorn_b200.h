@@ -186,6 +186,44 @@ int b200_swiglu(const void* a, const void* b, void* out,
                 int dtype, void* stream);
 
 /*
+ * out = round_T(round_T(gelu_tanh(a)) * b),  gelu_tanh(a) = 0.5*a*(1 + tanh(sqrt(2/pi)*(a + 0.044715*a^3)))
+ * evaluated in fp32 as a / (1 + exp(-2u)), which is the same function.
+ *
+ * Replaces geglu(a, b) = F.gelu(a, approximate="tanh") * b, src/popcorn/kernels/geglu.py:8-17.
+ * Same layout rules as b200_swiglu.
+ */
+int b200_geglu(const void* a, const void* b, void* out,
+               int64_t rows, int64_t cols, int64_t lda, int64_t ldb, int64_t ldo,
+               int dtype, void* stream);
+
+/*
+ * y = round_T( round_T(round_T(round_T(x*r) * weight) [+ bias]) * round_T(act(gate)) ),
+ * r = rsqrt(mean(x^2) + eps), act = silu (sigmoid_gate == 0) or sigmoid.
+ *
+ * Replaces rms_norm_gated(x, g, weight, bias=None, activation="swish", eps=1e-6),
+ * src/popcorn/kernels/rms_norm_gated.py:12-29.  bias may be NULL.
+ */
+int b200_rms_norm_gated(const void* x, const void* gate, const void* weight, const void* bias, void* y,
+                        int64_t rows, int64_t cols, int64_t ldx, int64_t ldg, int64_t ldy,
+                        int dtype, int sigmoid_gate, double eps, void* stream);
+
+/*
+ * y = x * rsqrt(sum(x^2) + eps) with every intermediate (x^2, the sum, + eps, rsqrt) rounded to T, as the
+ * reference's all-in-T expression does.  Replaces l2_norm(x, eps=1e-6), src/popcorn/kernels/l2_norm.py:8-14.
+ */
+int b200_l2_norm(const void* x, void* y, int64_t rows, int64_t cols, int64_t ldx, int64_t ldy,
+                 int dtype, double eps, void* stream);
+
+/*
+ * y = round_T((x*rstd - mean*rstd) * weight + bias), fp32 mean and biased variance over the row,
+ * rstd = 1/sqrt(var + eps).  Replaces layer_norm(x, weight, bias=None, eps=1e-6) = F.layer_norm(...),
+ * src/popcorn/kernels/layer_norm.py:8-20.  bias may be NULL.
+ */
+int b200_layer_norm(const void* x, const void* weight, const void* bias, void* y,
+                    int64_t rows, int64_t cols, int64_t ldx, int64_t ldy,
+                    int dtype, double eps, void* stream);
+
+/*
  * Backward of b200_swiglu: grad_a = round_T(round_T(g*b) * dsilu(a)), grad_b = round_T(g * round_T(silu(a))),
  * dsilu(a) = s * (1 + a * (1 - s)), s = sigmoid(a), in fp32.
  *

@@ -89,6 +89,29 @@ def swiglu(a: Tensor, b: Tensor) -> Tensor:
     return F.silu(a) * b
 
 
+def geglu(a: Tensor, b: Tensor) -> Tensor:
+    """Reference: geglu, src/popcorn/kernels/geglu.py:8-17."""
+    return F.gelu(a, approximate="tanh") * b
+
+
+def rms_norm_gated(x: Tensor, g: Tensor, weight: Tensor, bias: Tensor | None = None, activation: str = "swish", eps: float = 1e-6) -> Tensor:
+    """Reference: rms_norm_gated, src/popcorn/kernels/rms_norm_gated.py:12-29."""
+    out = _unit_rms(x, eps) * weight
+    if bias is not None:
+        out = out + bias
+    return out * (F.silu(g) if activation == "swish" else torch.sigmoid(g))
+
+
+def l2_norm(x: Tensor, eps: float = 1e-6) -> Tensor:
+    """Reference: l2_norm, src/popcorn/kernels/l2_norm.py:8-14."""
+    return x * torch.rsqrt(x.pow(2).sum(-1, keepdim=True) + eps)
+
+
+def layer_norm(x: Tensor, weight: Tensor, bias: Tensor | None = None, eps: float = 1e-6) -> Tensor:
+    """Reference: layer_norm, src/popcorn/kernels/layer_norm.py:8-20."""
+    return F.layer_norm(x, weight.shape, weight, bias, eps)
+
+
 def moe_route(router_logits: Tensor, top_k: int) -> tuple[Tensor, Tensor]:
     """Reference: routing lines of momoe, src/popcorn/kernels/momoe.py:47-49.
 

@@ -40,6 +40,10 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "b200_rope_qk": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _ptr]),
     "b200_rope_paired": (_int, [_ptr] * 6 + [_i64] * 18 + [_int, _ptr]),
     "b200_swiglu": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _int, _ptr]),
+    "b200_geglu": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _int, _ptr]),
+    "b200_rms_norm_gated": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _int, _int, _dbl, _ptr]),
+    "b200_l2_norm": (_int, [_ptr, _ptr, _i64, _i64, _i64, _i64, _int, _dbl, _ptr]),
+    "b200_layer_norm": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _int, _dbl, _ptr]),
     "b200_swiglu_backward": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _int, _ptr]),
     "b200_moe_route": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _int, _ptr]),
     "b200_moe_index_scratch_bytes": (_int, [_i64, _i64, _i64, ctypes.POINTER(_size)]),

@@ -1,0 +1,293 @@
+// Row-normalisation siblings of RMSNorm for sm_100a: gated RMSNorm, L2 norm, LayerNorm.
+//
+// Same shape as the RMSNorm kernel: one row per warp (rows up to 256 128-bit words) or per
+// 256-thread CTA (up to 2048 words), the row held in registers, one HBM read and one write per
+// element; anything wider or unaligned goes through the scalar two/three-pass kernel.
+//
+// Arithmetic follows the references tensor by tensor, including their roundings to T:
+//   rms_norm_gated  src/popcorn/kernels/rms_norm_gated.py:27-29
+//       y = round_T( round_T(round_T(round_T(h*r) * w) [+ b]) * round_T(act(g)) ),  act = silu | sigmoid
+//   l2_norm         src/popcorn/kernels/l2_norm.py:14   (everything in T)
+//       y = round_T( x * round_T(rsqrt(round_T(round_T(sum round_T(x^2)) + eps))) )
+//   layer_norm      src/popcorn/kernels/layer_norm.py:20 (F.layer_norm: fp32 statistics, one rounding)
+//       y = round_T( (x*rstd - mean*rstd) * w + b ),  rstd = 1/sqrt(var + eps), biased variance
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+enum Mode { kGatedSwish = 0, kGatedSigmoid = 1, kL2 = 2, kLayer = 3 };
+
+__device__ __forceinline__ float sigmoid_f32(float x) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))); }
+__device__ __forceinline__ float silu_ref_f32(float x) { return __fdiv_rn(x, __fadd_rn(1.0f, expf(-x))); }
+
+// Sum over the TPR threads of a row.  TPR == 32: shuffles only.  TPR == 256: one row per CTA, the
+// caller passes a distinct smem slot per reduction so that one barrier per reduction is enough.
+template <int TPR>
+__device__ __forceinline__ float row_sum(float v, float* slot) {
+  v = warp_sum(v);
+  if constexpr (TPR > 32) {
+    if ((threadIdx.x & 31) == 0) slot[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int k = 0; k < TPR / 32; ++k) total = __fadd_rn(total, slot[k]);
+    v = total;
+  }
+  return v;
+}
+
+template <typename T, int TPR, int ITEMS, int MODE>
+__global__ void __launch_bounds__(256)
+family_rows_kernel(const T* x, const T* gate, const T* __restrict__ weight, const T* __restrict__ bias, T* y,
+                   int64_t rows, int nvec, int64_t ldx, int64_t ldg, int64_t ldy, float cols_f, float eps) {
+  constexpr int V = Num<T>::kVec;
+  constexpr int ROWS_PER_CTA = 256 / TPR;
+  constexpr bool GATED = MODE == kGatedSwish || MODE == kGatedSigmoid;
+  pdl_prologue();
+  __shared__ float slots[2][8];
+  const int tid = threadIdx.x;
+  const int sub = tid / TPR, lane_in_row = tid % TPR;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * ROWS_PER_CTA + sub;
+  const bool row_ok = row < rows;
+
+  uint4 data[ITEMS], gdata[GATED ? ITEMS : 1];
+  bool ok[ITEMS];
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    ok[i] = row_ok && (lane_in_row + i * TPR) < nvec;
+    data[i] = make_uint4(0, 0, 0, 0);
+    const int64_t col = static_cast<int64_t>(lane_in_row + i * TPR) * V;
+    if (ok[i]) data[i] = ld_stream(x + row * ldx + col);
+    if constexpr (GATED) {
+      gdata[i] = make_uint4(0, 0, 0, 0);
+      if (ok[i]) gdata[i] = ld_stream(gate + row * ldg + col);
+    }
+  }
+
+  // first moment (LayerNorm) or sum of squares
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    float f[V];
+    Num<T>::unpack(data[i], f);
+#pragma unroll
+    for (int j = 0; j < V; j += 2) {
+      if constexpr (MODE == kLayer) {
+        acc = __fadd_rn(acc, __fadd_rn(f[j], f[j + 1]));
+      } else if constexpr (MODE == kL2) {
+        float s0 = __fmul_rn(f[j], f[j]), s1 = __fmul_rn(f[j + 1], f[j + 1]);
+        Num<T>::round2(s0, s1);  // x.pow(2) is a tensor of dtype T
+        acc = __fadd_rn(acc, __fadd_rn(s0, s1));
+      } else {
+        acc = __fmaf_rn(f[j], f[j], acc);
+        acc = __fmaf_rn(f[j + 1], f[j + 1], acc);
+      }
+    }
+  }
+  acc = row_sum<TPR>(acc, slots[0]);
+
+  float scale, shift = 0.f;  // y_pre = x * scale + shift
+  if constexpr (MODE == kLayer) {
+    const float mean = __fdiv_rn(acc, cols_f);
+    float var = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      if (!ok[i]) continue;
+      float f[V];
+      Num<T>::unpack(data[i], f);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float d = __fsub_rn(f[j], mean);
+        var = __fmaf_rn(d, d, var);
+      }
+    }
+    var = __fdiv_rn(row_sum<TPR>(var, slots[1]), cols_f);
+    scale = __frcp_rn(__fsqrt_rn(__fadd_rn(fmaxf(var, 0.f), eps)));
+    shift = -__fmul_rn(scale, mean);
+  } else if constexpr (MODE == kL2) {
+    const float total = Num<T>::rt(acc);                   // .sum(-1) returns dtype T
+    const float v = Num<T>::rt(__fadd_rn(total, eps));     // + eps, dtype T
+    scale = Num<T>::rt(__frcp_rn(__fsqrt_rn(v)));          // torch.rsqrt, dtype T
+  } else {
+    scale = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(acc, cols_f), eps)));
+  }
+  const bool has_bias = bias != nullptr;
+
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    if (!ok[i]) continue;
+    const int64_t col = static_cast<int64_t>(lane_in_row + i * TPR) * V;
+    float f[V], w[V], b[V], g[V];
+    Num<T>::unpack(data[i], f);
+    if constexpr (MODE != kL2) Num<T>::unpack(ld_reuse(weight + col), w);
+    if (MODE != kL2 && has_bias) Num<T>::unpack(ld_reuse(bias + col), b);
+    if constexpr (GATED) Num<T>::unpack(gdata[i], g);
+#pragma unroll
+    for (int j = 0; j < V; j += 2) {
+      float o0, o1;
+      if constexpr (MODE == kLayer) {
+        o0 = __fmul_rn(__fadd_rn(__fmul_rn(f[j], scale), shift), w[j]);
+        o1 = __fmul_rn(__fadd_rn(__fmul_rn(f[j + 1], scale), shift), w[j + 1]);
+        if (has_bias) {
+          o0 = __fadd_rn(o0, b[j]);
+          o1 = __fadd_rn(o1, b[j + 1]);
+        }
+      } else if constexpr (MODE == kL2) {
+        o0 = __fmul_rn(f[j], scale);
+        o1 = __fmul_rn(f[j + 1], scale);
+      } else {
+        o0 = __fmul_rn(f[j], scale);
+        o1 = __fmul_rn(f[j + 1], scale);
+        Num<T>::round2(o0, o1);
+        o0 = __fmul_rn(o0, w[j]);
+        o1 = __fmul_rn(o1, w[j + 1]);
+        Num<T>::round2(o0, o1);
+        if (has_bias) {
+          o0 = __fadd_rn(o0, b[j]);
+          o1 = __fadd_rn(o1, b[j + 1]);
+          Num<T>::round2(o0, o1);
+        }
+        float a0 = MODE == kGatedSwish ? silu_ref_f32(g[j]) : sigmoid_f32(g[j]);
+        float a1 = MODE == kGatedSwish ? silu_ref_f32(g[j + 1]) : sigmoid_f32(g[j + 1]);
+        Num<T>::round2(a0, a1);
+        o0 = __fmul_rn(o0, a0);
+        o1 = __fmul_rn(o1, a1);
+      }
+      f[j] = o0;
+      f[j + 1] = o1;
+    }
+    st_stream(y + row * ldy + col, Num<T>::pack(f));
+  }
+}
+
+// Any width, any alignment: one CTA per row, scalar accesses, the row re-read for every pass.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256)
+family_stream_kernel(const T* x, const T* gate, const T* __restrict__ weight, const T* __restrict__ bias, T* y,
+                     int64_t cols, int64_t ldx, int64_t ldg, int64_t ldy, float cols_f, float eps) {
+  constexpr bool GATED = MODE == kGatedSwish || MODE == kGatedSigmoid;
+  pdl_prologue();
+  __shared__ float slots[2][8];
+  const int64_t row = blockIdx.x;
+  const T* xr = x + row * ldx;
+  float acc = 0.f;
+  for (int64_t c = threadIdx.x; c < cols; c += 256) {
+    const float h = Num<T>::up(xr[c]);
+    if (MODE == kLayer) acc = __fadd_rn(acc, h);
+    else if (MODE == kL2) acc = __fadd_rn(acc, Num<T>::rt(__fmul_rn(h, h)));
+    else acc = __fmaf_rn(h, h, acc);
+  }
+  acc = row_sum<256>(acc, slots[0]);
+  float scale, shift = 0.f;
+  if (MODE == kLayer) {
+    const float mean = __fdiv_rn(acc, cols_f);
+    float var = 0.f;
+    for (int64_t c = threadIdx.x; c < cols; c += 256) {
+      const float d = __fsub_rn(Num<T>::up(xr[c]), mean);
+      var = __fmaf_rn(d, d, var);
+    }
+    var = __fdiv_rn(row_sum<256>(var, slots[1]), cols_f);
+    scale = __frcp_rn(__fsqrt_rn(__fadd_rn(fmaxf(var, 0.f), eps)));
+    shift = -__fmul_rn(scale, mean);
+  } else if (MODE == kL2) {
+    scale = Num<T>::rt(__frcp_rn(__fsqrt_rn(Num<T>::rt(__fadd_rn(Num<T>::rt(acc), eps)))));
+  } else {
+    scale = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(acc, cols_f), eps)));
+  }
+  const bool has_bias = bias != nullptr;
+  for (int64_t c = threadIdx.x; c < cols; c += 256) {
+    const float h = Num<T>::up(xr[c]);
+    float o;
+    if (MODE == kLayer) {
+      o = __fmul_rn(__fadd_rn(__fmul_rn(h, scale), shift), Num<T>::up(weight[c]));
+      if (has_bias) o = __fadd_rn(o, Num<T>::up(bias[c]));
+    } else if (MODE == kL2) {
+      o = __fmul_rn(h, scale);
+    } else {
+      o = Num<T>::rt(__fmul_rn(Num<T>::rt(__fmul_rn(h, scale)), Num<T>::up(weight[c])));
+      if (has_bias) o = Num<T>::rt(__fadd_rn(o, Num<T>::up(bias[c])));
+      const float g = GATED ? Num<T>::up(gate[row * ldg + c]) : 0.f;
+      o = __fmul_rn(o, Num<T>::rt(MODE == kGatedSwish ? silu_ref_f32(g) : sigmoid_f32(g)));
+    }
+    y[row * ldy + c] = Num<T>::down(o);
+  }
+}
+
+template <typename T, int MODE>
+int run(const void* x, const void* gate, const void* w, const void* b, void* y, int64_t rows, int64_t cols,
+        int64_t ldx, int64_t ldg, int64_t ldy, float eps, cudaStream_t st) {
+  constexpr int V = Num<T>::kVec;
+  constexpr bool GATED = MODE == kGatedSwish || MODE == kGatedSigmoid;
+  const float cols_f = static_cast<float>(cols);
+  bool vec = cols % V == 0 && ldx % V == 0 && ldy % V == 0 && aligned(x, 16) && aligned(y, 16) &&
+             (w == nullptr || aligned(w, 16)) && (b == nullptr || aligned(b, 16));
+  if (GATED) vec = vec && ldg % V == 0 && aligned(gate, 16);
+  const T *tx = static_cast<const T*>(x), *tg = static_cast<const T*>(gate), *tw = static_cast<const T*>(w), *tb = static_cast<const T*>(b);
+  T* ty = static_cast<T*>(y);
+  const int64_t nvec64 = cols / V;
+  if (vec && nvec64 <= 2048) {
+    const int nvec = static_cast<int>(nvec64);
+#define B200_FAMILY(TPR, ITEMS)                                                                                      \
+  launch(family_rows_kernel<T, TPR, ITEMS, MODE>, static_cast<unsigned>(ceil_div(rows, 256 / TPR)), 256, 0, st, tx, tg, \
+         tw, tb, ty, rows, nvec, ldx, ldg, ldy, cols_f, eps)
+    if (nvec <= 32) B200_FAMILY(32, 1);
+    else if (nvec <= 64) B200_FAMILY(32, 2);
+    else if (nvec <= 128) B200_FAMILY(32, 4);
+    else if (nvec <= 256) B200_FAMILY(32, 8);
+    else if (nvec <= 512) B200_FAMILY(256, 2);
+    else if (nvec <= 1024) B200_FAMILY(256, 4);
+    else B200_FAMILY(256, 8);
+#undef B200_FAMILY
+    return after_launch("family_rows_kernel");
+  }
+  launch(family_stream_kernel<T, MODE>, static_cast<unsigned>(rows), 256, 0, st, tx, tg, tw, tb, ty, cols, ldx, ldg, ldy, cols_f, eps);
+  return after_launch("family_stream_kernel");
+}
+
+int entry(const char* fn, int mode, const void* x, const void* gate, const void* weight, const void* bias, void* y,
+          int64_t rows, int64_t cols, int64_t ldx, int64_t ldg, int64_t ldy, int dtype, double eps, void* stream) {
+  if (!dtype_ok(dtype)) return fail(B200_ERR_DTYPE, "%s: unsupported dtype %d", fn, dtype);
+  if (rows < 0 || cols < 0) return fail(B200_ERR_SHAPE, "%s: negative size", fn);
+  if (rows > 0x7fffffffLL) return fail(B200_ERR_SHAPE, "%s: rows=%lld exceeds 2^31-1", fn, (long long)rows);
+  if (rows == 0 || cols == 0) return B200_OK;
+  const bool gated = mode == kGatedSwish || mode == kGatedSigmoid;
+  if (x == nullptr || y == nullptr || (mode != kL2 && weight == nullptr) || (gated && gate == nullptr))
+    return fail(B200_ERR_NULL_POINTER, "%s: a required pointer is NULL", fn);
+  if (ldx < cols || ldy < cols || (gated && ldg < cols)) return fail(B200_ERR_SHAPE, "%s: leading dimension smaller than cols", fn);
+  const size_t es = dtype_size(dtype);
+  if (!aligned(x, es) || !aligned(y, es) || !aligned(gate, es) || !aligned(weight, es) || !aligned(bias, es))
+    return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to the element size", fn);
+  if (int rc = check_device()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const float e = static_cast<float>(eps);
+  switch (mode) {
+    case kGatedSwish: B200_DISPATCH_DTYPE(dtype, T, return (run<T, kGatedSwish>(x, gate, weight, bias, y, rows, cols, ldx, ldg, ldy, e, st))); break;
+    case kGatedSigmoid: B200_DISPATCH_DTYPE(dtype, T, return (run<T, kGatedSigmoid>(x, gate, weight, bias, y, rows, cols, ldx, ldg, ldy, e, st))); break;
+    case kL2: B200_DISPATCH_DTYPE(dtype, T, return (run<T, kL2>(x, nullptr, nullptr, nullptr, y, rows, cols, ldx, 0, ldy, e, st))); break;
+    default: B200_DISPATCH_DTYPE(dtype, T, return (run<T, kLayer>(x, nullptr, weight, bias, y, rows, cols, ldx, 0, ldy, e, st))); break;
+  }
+  return B200_OK;
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_rms_norm_gated(const void* x, const void* gate, const void* weight, const void* bias, void* y,
+                                   int64_t rows, int64_t cols, int64_t ldx, int64_t ldg, int64_t ldy,
+                                   int dtype, int sigmoid_gate, double eps, void* stream) {
+  return entry(__func__, sigmoid_gate ? kGatedSigmoid : kGatedSwish, x, gate, weight, bias, y, rows, cols, ldx, ldg, ldy, dtype, eps, stream);
+}
+
+extern "C" int b200_l2_norm(const void* x, void* y, int64_t rows, int64_t cols, int64_t ldx, int64_t ldy,
+                            int dtype, double eps, void* stream) {
+  return entry(__func__, kL2, x, nullptr, nullptr, nullptr, y, rows, cols, ldx, 0, ldy, dtype, eps, stream);
+}
+
+extern "C" int b200_layer_norm(const void* x, const void* weight, const void* bias, void* y,
+                               int64_t rows, int64_t cols, int64_t ldx, int64_t ldy,
+                               int dtype, double eps, void* stream) {
+  return entry(__func__, kLayer, x, nullptr, weight, bias, y, rows, cols, ldx, 0, ldy, dtype, eps, stream);
+}

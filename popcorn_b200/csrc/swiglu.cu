@@ -55,9 +55,23 @@ __device__ __forceinline__ float exp_neg(float a) {
     return __fmaf_rn(e, __fmul_rn(lo, 0.6931471805599453f), e);  // 2^(t + lo) ~ 2^t * (1 + lo*ln 2)
   }
 }
-template <int MATH>
+// Argument t of the gate x / (1 + exp(-t)): t = x gives silu(x); t = 2*sqrt(2/pi)*(x + 0.044715*x^3)
+// gives the tanh-approximate gelu, since 0.5*(1 + tanh(u)) = 1 / (1 + exp(-2u)).
+enum Act { kSilu = 0, kGeluTanh = 1 };
+template <int ACT>
+__device__ __forceinline__ float gate_argument(float x) {
+  if constexpr (ACT == kSilu) {
+    return x;
+  } else {
+    const float cube = __fmul_rn(__fmul_rn(x, x), x);
+    const float inner = __fmul_rn(0.7978845608028654f, __fadd_rn(x, __fmul_rn(0.044715f, cube)));
+    return __fmul_rn(2.0f, inner);
+  }
+}
+
+template <int MATH, int ACT = kSilu>
 __device__ __forceinline__ float silu_f32(float a) {
-  const float d = __fadd_rn(1.0f, exp_neg<MATH>(a));
+  const float d = __fadd_rn(1.0f, exp_neg<MATH>(gate_argument<ACT>(a)));
   if constexpr (MATH == 0) {
     return __fdiv_rn(a, d);
   } else {
@@ -71,15 +85,15 @@ __device__ __forceinline__ float silu_f32(float a) {
   }
 }
 
-template <typename T>
+template <typename T, int ACT>
 __device__ __forceinline__ float swiglu_one(float a, float b) {
-  return Num<T>::rt(__fmul_rn(Num<T>::rt(silu_f32<0>(a)), b));
+  return Num<T>::rt(__fmul_rn(Num<T>::rt(silu_f32<0, ACT>(a)), b));
 }
 
 // Each thread owns UNROLL 128-bit words, THREADS words apart, so a warp always
 // touches 512 contiguous bytes of one row.  (row, word) of the first word comes
 // from one division; the rest follow by carry.
-template <typename T, int UNROLL, typename Index, int MATH>
+template <typename T, int UNROLL, typename Index, int MATH, int ACT>
 __global__ void __launch_bounds__(256)
 swiglu_vec_kernel(const T* a, const T* b, T* out, Index total_words, Index words_per_row,
                   int64_t lda, int64_t ldb, int64_t ldo) {
@@ -122,7 +136,7 @@ swiglu_vec_kernel(const T* a, const T* b, T* out, Index total_words, Index words
       Num<T>::unpack(va[u], fa);
       Num<T>::unpack(vb[u], fb);
 #pragma unroll
-      for (int j = 0; j < V; ++j) fa[j] = __fmul_rn(silu_f32<MATH>(fa[j]), fb[j]);
+      for (int j = 0; j < V; ++j) fa[j] = __fmul_rn(silu_f32<MATH, ACT>(fa[j]), fb[j]);
       if (ok[u]) st_stream(out + off_o[u], Num<T>::pack(fa));
     } else {
       // 16-bit: silu of a pair in fp32, one packed rounding to T, then the packed product with
@@ -134,7 +148,7 @@ swiglu_vec_kernel(const T* a, const T* b, T* out, Index total_words, Index words
       for (int j = 0; j < 4; ++j) {
         float lo, hi;
         Num<T>::unpack2(wa[j], lo, hi);
-        wo[j] = Num<T>::mul2(Num<T>::pack2(silu_f32<MATH>(lo), silu_f32<MATH>(hi)), wb[j]);
+        wo[j] = Num<T>::mul2(Num<T>::pack2(silu_f32<MATH, ACT>(lo), silu_f32<MATH, ACT>(hi)), wb[j]);
       }
       if (ok[u]) st_stream(out + off_o[u], make_uint4(wo[0], wo[1], wo[2], wo[3]));
     }
@@ -242,7 +256,7 @@ int run_bwd(const void* g, const void* a, const void* b, void* da, void* db, int
 }
 
 // Any width, any alignment.
-template <typename T>
+template <typename T, int ACT>
 __global__ void __launch_bounds__(256)
 swiglu_scalar_kernel(const T* a, const T* b, T* out, int64_t rows, int64_t cols,
                      int64_t lda, int64_t ldb, int64_t ldo) {
@@ -251,11 +265,11 @@ swiglu_scalar_kernel(const T* a, const T* b, T* out, int64_t rows, int64_t cols,
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t r = i / cols, c = i - r * cols;
-    out[r * ldo + c] = Num<T>::down(swiglu_one<T>(Num<T>::up(a[r * lda + c]), Num<T>::up(b[r * ldb + c])));
+    out[r * ldo + c] = Num<T>::down(swiglu_one<T, ACT>(Num<T>::up(a[r * lda + c]), Num<T>::up(b[r * ldb + c])));
   }
 }
 
-template <typename T>
+template <typename T, int ACT>
 int run(const void* a, const void* b, void* out, int64_t rows, int64_t cols,
         int64_t lda, int64_t ldb, int64_t ldo, cudaStream_t st) {
   constexpr int V = Num<T>::kVec;
@@ -274,11 +288,11 @@ int run(const void* a, const void* b, void* out, int64_t rows, int64_t cols,
     if (grid > 0x7fffffffLL) return fail(B200_ERR_SHAPE, "b200_swiglu: problem too large for one launch");
     constexpr int MATH = sizeof(T) == 4 ? 0 : 1;
     if (total < 0x7fffffffLL) {
-      launch(swiglu_vec_kernel<T, UNROLL, uint32_t, MATH>, static_cast<unsigned>(grid), 256, 0, st,
+      launch(swiglu_vec_kernel<T, UNROLL, uint32_t, MATH, ACT>, static_cast<unsigned>(grid), 256, 0, st,
              static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), static_cast<uint32_t>(total),
              static_cast<uint32_t>(wpr), lda, ldb, ldo);
     } else {
-      launch(swiglu_vec_kernel<T, UNROLL, uint64_t, MATH>, static_cast<unsigned>(grid), 256, 0, st,
+      launch(swiglu_vec_kernel<T, UNROLL, uint64_t, MATH, ACT>, static_cast<unsigned>(grid), 256, 0, st,
              static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), static_cast<uint64_t>(total),
              static_cast<uint64_t>(wpr), lda, ldb, ldo);
     }
@@ -286,7 +300,7 @@ int run(const void* a, const void* b, void* out, int64_t rows, int64_t cols,
   }
   const int64_t want = ceil_div(rows * cols, 256);
   const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
-  launch(swiglu_scalar_kernel<T>, static_cast<unsigned>(want < cap ? want : cap), 256, 0, st,
+  launch(swiglu_scalar_kernel<T, ACT>, static_cast<unsigned>(want < cap ? want : cap), 256, 0, st,
       static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), rows, cols, lda, ldb, ldo);
   return after_launch("swiglu_scalar_kernel");
 }
@@ -296,22 +310,35 @@ int run(const void* a, const void* b, void* out, int64_t rows, int64_t cols,
 
 using namespace b200;
 
-extern "C" int b200_swiglu(const void* a, const void* b, void* out, int64_t rows, int64_t cols,
-                           int64_t lda, int64_t ldb, int64_t ldo, int dtype, void* stream) {
-  if (!dtype_ok(dtype)) return fail(B200_ERR_DTYPE, "%s: unsupported dtype %d", __func__, dtype);
-  if (rows < 0 || cols < 0) return fail(B200_ERR_SHAPE, "%s: negative size", __func__);
+namespace b200 {
+namespace {
+template <int ACT>
+int gated_forward(const char* fn, const void* a, const void* b, void* out, int64_t rows, int64_t cols,
+                  int64_t lda, int64_t ldb, int64_t ldo, int dtype, void* stream) {
+  if (!dtype_ok(dtype)) return fail(B200_ERR_DTYPE, "%s: unsupported dtype %d", fn, dtype);
+  if (rows < 0 || cols < 0) return fail(B200_ERR_SHAPE, "%s: negative size", fn);
   if (rows == 0 || cols == 0) return B200_OK;
-  B200_REQUIRE_PTR(a);
-  B200_REQUIRE_PTR(b);
-  B200_REQUIRE_PTR(out);
-  if (lda < cols || ldb < cols || ldo < cols) return fail(B200_ERR_SHAPE, "%s: leading dimension smaller than cols", __func__);
+  if (a == nullptr || b == nullptr || out == nullptr) return fail(B200_ERR_NULL_POINTER, "%s: a, b or out is NULL", fn);
+  if (lda < cols || ldb < cols || ldo < cols) return fail(B200_ERR_SHAPE, "%s: leading dimension smaller than cols", fn);
   const size_t es = dtype_size(dtype);
   if (!aligned(a, es) || !aligned(b, es) || !aligned(out, es))
-    return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to the element size", __func__);
+    return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to the element size", fn);
   if (int rc = check_device()) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  B200_DISPATCH_DTYPE(dtype, T, return run<T>(a, b, out, rows, cols, lda, ldb, ldo, st));
+  B200_DISPATCH_DTYPE(dtype, T, return (run<T, ACT>(a, b, out, rows, cols, lda, ldb, ldo, st)));
   return B200_OK;
+}
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_swiglu(const void* a, const void* b, void* out, int64_t rows, int64_t cols,
+                           int64_t lda, int64_t ldb, int64_t ldo, int dtype, void* stream) {
+  return gated_forward<kSilu>(__func__, a, b, out, rows, cols, lda, ldb, ldo, dtype, stream);
+}
+
+extern "C" int b200_geglu(const void* a, const void* b, void* out, int64_t rows, int64_t cols,
+                          int64_t lda, int64_t ldb, int64_t ldo, int dtype, void* stream) {
+  return gated_forward<kGeluTanh>(__func__, a, b, out, rows, cols, lda, ldb, ldo, dtype, stream);
 }
 
 extern "C" int b200_swiglu_backward(const void* grad_out, const void* a, const void* b, void* grad_a, void* grad_b,

@@ -1,6 +1,6 @@
 """Op declarations on the local registry mirror, each with the `b200` backend attached.
 
-The five existing popcorn ops keep popcorn's names, parameter order and defaults
+The existing popcorn ops keep popcorn's names, parameter order and defaults
 (src/popcorn/kernels/rms_norm.py:16-21, add_rms_norm.py:8-14,
 rotary_embedding.py:15-20, rope.py:24-29, swiglu.py:10); the MoE steps are new ops because
 popcorn only has them fused inside `momoe` (src/popcorn/kernels/momoe.py:47-53).
@@ -41,6 +41,26 @@ def swiglu(a, b):
 
 
 @register_kernel
+def geglu(a, b):
+    """GEGLU gating with the tanh-approximate GELU: gelu(a) * b."""
+
+
+@register_kernel
+def rms_norm_gated(x, g, weight, bias=None, activation="swish", eps=1e-6):
+    """RMS norm scaled by a swish or sigmoid gate."""
+
+
+@register_kernel
+def l2_norm(x, eps=1e-6):
+    """L2 normalization along the last dimension."""
+
+
+@register_kernel
+def layer_norm(x, weight, bias=None, eps=1e-6):
+    """Layer normalization: standardize the last dimension, then scale and shift."""
+
+
+@register_kernel
 def moe_route(router_logits, top_k=2):
     """Softmax over experts, top-k selection, renormalized gate weights."""
 
@@ -56,7 +76,7 @@ def moe_unpermute(rows, weights, pos):
 
 
 # ops with backward kernels are registered in their differentiable form
-for _op in (rope, moe_route, moe_permute, moe_unpermute):
+for _op in (rope, geglu, rms_norm_gated, l2_norm, layer_norm, moe_route, moe_permute, moe_unpermute):
     _op.register(BACKEND, source=f"popcorn_b200.ops.{_op.name}", forward_only=True)
 for _op in (rms_norm, add_rms_norm, rotary_embedding, swiglu):
     _op.register(BACKEND, source=f"popcorn_b200.autograd.{_op.name}")

@@ -14,6 +14,10 @@ Signatures served (names and order are popcorn's):
   rotary_embedding(x, cos, sin, interleaved=False)         src/popcorn/kernels/rotary_embedding.py:15-20
   swiglu(a, b)                                             src/popcorn/kernels/swiglu.py:10
   rope(q, k, cos, sin)                                     src/popcorn/kernels/rope.py:24-29
+  geglu(a, b)                                              src/popcorn/kernels/geglu.py:9
+  rms_norm_gated(x, g, weight, bias=None, activation="swish", eps=1e-6)   src/popcorn/kernels/rms_norm_gated.py:13-20
+  l2_norm(x, eps=1e-6)                                     src/popcorn/kernels/l2_norm.py:9
+  layer_norm(x, weight, bias=None, eps=1e-6)               src/popcorn/kernels/layer_norm.py:9-14
 and the MoE steps popcorn only has fused inside `momoe`
 (src/popcorn/kernels/momoe.py:47-53, src/popcorn/impls/momoe_tl.py:1071-1161):
   moe_route, moe_index, moe_scatter_rows, moe_permute, moe_gather, moe_unpermute.
@@ -288,6 +292,74 @@ def swiglu(a: Tensor, b: Tensor) -> Tensor:
     with torch.cuda.device(device):
         _lib.call("b200_swiglu", _ptr(a2), _ptr(b2), _ptr(out), a2.shape[0], width, lda, ldb, max(width, 1), code, _stream(device))
     return out
+
+
+def geglu(a: Tensor, b: Tensor) -> Tensor:
+    """gelu_tanh(a) * b (geglu.py:8-17); a and b may be strided column halves of one buffer."""
+    device = _require_cuda(a, b)
+    _forbid_grad(a, b)
+    code = _dtype_code(a, "geglu")
+    if a.shape != b.shape or a.dtype != b.dtype:
+        raise ValueError("geglu: a and b must have the same shape and dtype")
+    width = a.shape[-1]
+    a2, lda = _rows(a)
+    b2, ldb = _rows(b)
+    out = torch.empty(a.shape, dtype=a.dtype, device=device)
+    with torch.cuda.device(device):
+        _lib.call("b200_geglu", _ptr(a2), _ptr(b2), _ptr(out), a2.shape[0], width, lda, ldb, max(width, 1), code, _stream(device))
+    return out
+
+
+def rms_norm_gated(x: Tensor, g: Tensor, weight: Tensor, bias: Tensor | None = None, activation: str = "swish", eps: float = 1e-6) -> Tensor:
+    """RMS norm scaled by a swish or sigmoid gate (rms_norm_gated.py:12-29)."""
+    device = _require_cuda(x, g, weight, bias)
+    _forbid_grad(x, g, weight, bias)
+    code = _dtype_code(x, "rms_norm_gated")
+    width = x.shape[-1]
+    if activation not in ("swish", "sigmoid"):
+        raise ValueError("rms_norm_gated: activation must be 'swish' or 'sigmoid'")
+    if g.shape != x.shape or weight.shape != (width,) or (bias is not None and bias.shape != (width,)):
+        raise ValueError("rms_norm_gated: g must match x; weight and bias must be [hidden]")
+    if not (g.dtype == weight.dtype == x.dtype) or (bias is not None and bias.dtype != x.dtype):
+        raise TypeError("rms_norm_gated: all tensors must share a dtype")
+    x2, ldx = _rows(x)
+    g2, ldg = _rows(g)
+    y = torch.empty(x.shape, dtype=x.dtype, device=device)
+    with torch.cuda.device(device):
+        _lib.call("b200_rms_norm_gated", _ptr(x2), _ptr(g2), _ptr(weight.contiguous()), _ptr(None if bias is None else bias.contiguous()), _ptr(y),
+                  x2.shape[0], width, ldx, ldg, max(width, 1), code, int(activation == "sigmoid"), float(eps), _stream(device))
+    return y
+
+
+def l2_norm(x: Tensor, eps: float = 1e-6) -> Tensor:
+    """x / sqrt(sum(x^2) + eps) over the last dimension, evaluated in the dtype of x (l2_norm.py:8-14)."""
+    device = _require_cuda(x)
+    _forbid_grad(x)
+    code = _dtype_code(x, "l2_norm")
+    width = x.shape[-1]
+    x2, ldx = _rows(x)
+    y = torch.empty(x.shape, dtype=x.dtype, device=device)
+    with torch.cuda.device(device):
+        _lib.call("b200_l2_norm", _ptr(x2), _ptr(y), x2.shape[0], width, ldx, max(width, 1), code, float(eps), _stream(device))
+    return y
+
+
+def layer_norm(x: Tensor, weight: Tensor, bias: Tensor | None = None, eps: float = 1e-6) -> Tensor:
+    """Layer normalisation over the last dimension (layer_norm.py:8-20)."""
+    device = _require_cuda(x, weight, bias)
+    _forbid_grad(x, weight, bias)
+    code = _dtype_code(x, "layer_norm")
+    width = x.shape[-1]
+    if weight.shape != (width,) or (bias is not None and bias.shape != (width,)):
+        raise ValueError(f"layer_norm: weight/bias must have shape ({width},)")
+    if weight.dtype != x.dtype or (bias is not None and bias.dtype != x.dtype):
+        raise TypeError("layer_norm: weight and bias must have the dtype of x")
+    x2, ldx = _rows(x)
+    y = torch.empty(x.shape, dtype=x.dtype, device=device)
+    with torch.cuda.device(device):
+        _lib.call("b200_layer_norm", _ptr(x2), _ptr(weight.contiguous()), _ptr(None if bias is None else bias.contiguous()), _ptr(y),
+                  x2.shape[0], width, ldx, max(width, 1), code, float(eps), _stream(device))
+    return y
 
 
 def swiglu_backward(grad_out: Tensor, a: Tensor, b: Tensor) -> tuple[Tensor, Tensor]:

@@ -4,7 +4,7 @@
     popcorn_b200.plugin.register()            # needs `popcorn` importable
     popcorn.KERNELS["rms_norm"](x, w, backend="b200")
 
-For the five ops popcorn already defines, this is one `op.register(name,
+For the nine ops popcorn already defines, this is one `op.register(name,
 source=..., forward_only=True)` line each, the same form popcorn's own backends
 use (src/popcorn/kernels/rms_norm.py:33-59, add_rms_norm.py:26-28,
 rotary_embedding.py:43-45, rope.py:39, swiglu.py:21-31).  The sources are bare: each
@@ -27,7 +27,7 @@ import torch
 from torch import Tensor
 
 BACKEND = "b200"
-EXISTING_OPS = ("rms_norm", "add_rms_norm", "rotary_embedding", "rope", "swiglu")
+EXISTING_OPS = ("rms_norm", "add_rms_norm", "rotary_embedding", "rope", "swiglu", "geglu", "rms_norm_gated", "l2_norm", "layer_norm")
 NEW_OPS = ("moe_route", "moe_permute", "moe_unpermute")
 DIFFERENTIABLE_OPS = ("rms_norm", "add_rms_norm", "swiglu", "rotary_embedding")
 

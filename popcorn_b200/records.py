@@ -37,6 +37,10 @@ REFERENCE_HASHES = {
     "rotary_embedding": "54089714d061",
     "rope": "1b989955d9be",
     "swiglu": "a2768d81c5aa",
+    "geglu": "1bbe631dff25",
+    "rms_norm_gated": "8c982cfacaf2",
+    "l2_norm": "d283c2e0ec98",
+    "layer_norm": "8a52ecd56f71",
     "moe_route": "3b877b7d155e",
     "moe_permute": "2d4425c300da",
     "moe_unpermute": "96a7326d99b2",

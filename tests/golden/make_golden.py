@@ -132,6 +132,42 @@ def swiglu_cases() -> None:
         save_case(name, {"gate_up": gate_up, "y": ref(a, b)}, {"op": "swiglu"})
 
 
+def sibling_cases() -> None:
+    for name, seed, rows, cols, dtype, scale in [("geglu_bf16_9x136", 60, 9, 136, BF16, 1.5), ("geglu_f32_5x33", 61, 5, 33, F32, 1.0), ("geglu_f16_6x72", 62, 6, 72, F16, 2.0)]:
+        gen = torch.Generator().manual_seed(seed)
+        gate_up = (scale * randn(gen, rows, 2 * cols)).to(dtype)
+        save_case(name, {"gate_up": gate_up, "y": KERNELS["geglu"].reference(gate_up[:, :cols], gate_up[:, cols:])}, {"op": "geglu"})
+    for name, seed, rows, cols, dtype, with_bias, activation, eps in [
+        ("rmsgated_bf16_6x256_swish", 70, 6, 256, BF16, False, "swish", 1e-6),
+        ("rmsgated_bf16_5x264_sigmoid_bias", 71, 5, 264, BF16, True, "sigmoid", 1e-5),
+        ("rmsgated_f32_3x50_swish_bias", 72, 3, 50, F32, True, "swish", 1e-6),
+        ("rmsgated_f16_4x128_sigmoid", 73, 4, 128, F16, False, "sigmoid", 1e-5),
+    ]:
+        gen = torch.Generator().manual_seed(seed)
+        x, g = randn(gen, rows, cols).to(dtype), randn(gen, rows, cols).to(dtype)
+        weight = (1 + 0.1 * randn(gen, cols)).to(dtype)
+        bias = randn(gen, cols).to(dtype) if with_bias else None
+        tensors = {"x": x, "g": g, "weight": weight, "y": KERNELS["rms_norm_gated"].reference(x, g, weight, bias, activation, eps)}
+        if bias is not None:
+            tensors["bias"] = bias
+        save_case(name, tensors, {"op": "rms_norm_gated", "activation": activation, "eps": eps})
+    for name, seed, rows, cols, dtype, eps in [("l2norm_bf16_40x128", 80, 40, 128, BF16, 1e-6), ("l2norm_f32_7x50", 81, 7, 50, F32, 1e-5),
+                                               ("l2norm_f16_5x264", 82, 5, 264, F16, 1e-6), ("l2norm_bf16_3x4096", 83, 3, 4096, BF16, 1e-5)]:
+        gen = torch.Generator().manual_seed(seed)
+        x = randn(gen, rows, cols).to(dtype)
+        save_case(name, {"x": x, "y": KERNELS["l2_norm"].reference(x, eps)}, {"op": "l2_norm", "eps": eps})
+    for name, seed, rows, cols, dtype, with_bias, eps in [("layernorm_bf16_6x256_bias", 90, 6, 256, BF16, True, 1e-6), ("layernorm_f32_5x50", 91, 5, 50, F32, False, 1e-5),
+                                                          ("layernorm_f16_4x136_bias", 92, 4, 136, F16, True, 1e-5), ("layernorm_bf16_3x4096", 93, 3, 4096, BF16, False, 1e-6)]:
+        gen = torch.Generator().manual_seed(seed)
+        x = (randn(gen, rows, cols) + 0.5).to(dtype)
+        weight = (1 + 0.1 * randn(gen, cols)).to(dtype)
+        bias = randn(gen, cols).to(dtype) if with_bias else None
+        tensors = {"x": x, "weight": weight, "y": KERNELS["layer_norm"].reference(x, weight, bias, eps)}
+        if bias is not None:
+            tensors["bias"] = bias
+        save_case(name, tensors, {"op": "layer_norm", "eps": eps})
+
+
 def momoe_cases() -> None:
     ref = KERNELS["momoe"].reference
     for name, seed, batch, seq, hidden, inter, experts, top_k in [
@@ -168,6 +204,7 @@ def main() -> None:
     rotary_cases()
     paired_rope_cases()
     swiglu_cases()
+    sibling_cases()
     momoe_cases()
     import popcorn
 

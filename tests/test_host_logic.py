@@ -44,7 +44,8 @@ def test_rows_view_keeps_strided_halves_in_place():
 
 
 def test_mirror_registry_surface():
-    assert set(registry.KERNELS) >= {"rms_norm", "add_rms_norm", "rotary_embedding", "swiglu", "moe_route", "moe_permute", "moe_unpermute"}
+    assert set(registry.KERNELS) >= {"rms_norm", "add_rms_norm", "rotary_embedding", "rope", "swiglu", "geglu", "rms_norm_gated", "l2_norm",
+                                     "layer_norm", "moe_route", "moe_permute", "moe_unpermute"}
     op = kernels.rms_norm
     assert op.available_backends() == ("b200",)
     assert op.params == ("x", "weight", "bias", "eps")

@@ -64,6 +64,31 @@ def test_swiglu(name):
     assert_close_ulps(oracle.swiglu(t["gate_up"][:, :cols], t["gate_up"][:, cols:]), t["y"])
 
 
+@pytest.mark.parametrize("name", names("geglu"))
+def test_geglu(name):
+    t, _ = load_case(name)
+    cols = t["gate_up"].shape[1] // 2
+    assert_close_ulps(oracle.geglu(t["gate_up"][:, :cols], t["gate_up"][:, cols:]), t["y"])
+
+
+@pytest.mark.parametrize("name", names("rmsgated"))
+def test_rms_norm_gated(name):
+    t, meta = load_case(name)
+    assert_close_ulps(oracle.rms_norm_gated(t["x"], t["g"], t["weight"], t.get("bias"), meta["activation"], meta["eps"]), t["y"])
+
+
+@pytest.mark.parametrize("name", names("l2norm"))
+def test_l2_norm(name):
+    t, meta = load_case(name)
+    assert_close_ulps(oracle.l2_norm(t["x"], meta["eps"]), t["y"])
+
+
+@pytest.mark.parametrize("name", names("layernorm"))
+def test_layer_norm(name):
+    t, meta = load_case(name)
+    assert_close_ulps(oracle.layer_norm(t["x"], t["weight"], t.get("bias"), meta["eps"]), t["y"])
+
+
 @pytest.mark.parametrize("name", names("momoe"))
 def test_route(name):
     t, meta = load_case(name)
