@@ -316,6 +316,46 @@ def torch_eager_incumbent(device, per_op: dict, records_root: str | None) -> Non
         per_op["popcorn_report_rows"] = [str(path) for path in paths]
 
 
+def bench_extra_ops(device, peak_gbs: float, sampler) -> dict:
+    """The ops beyond the five benchmark configurations, at the benchmark shapes they correspond to.
+
+    Timed through the public op functions (outputs allocated per call by the caching allocator, which does
+    not synchronise), 50 launches each; bytes = every input read once + every output written once."""
+    from popcorn_b200 import ops, workloads
+
+    out = {}
+
+    def run(name, fn, nbytes, steps=50):
+        t0 = time.time()
+        ms = time_launches(lambda i: fn(), steps, 3, device)
+        if sampler is not None:
+            sampler.mark(t0, time.time())
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = {"ms": round(ms, 5), "gb_s": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak_gbs, 4),
+                     "frac_of_8tbs": round(gbs / SPEC_HBM_GBS, 4), "algorithmic_bytes": nbytes}
+
+    w = workloads.swiglu_bf16().to(device)
+    gu, cols = w.inputs["gate_up"], w.args["cols"]
+    a, b = gu[:, :cols], gu[:, cols:]
+    grad = torch.randn(gu.shape[0], cols, device=device).to(torch.bfloat16)
+    n = a.numel() * 2
+    run("geglu_bf16 [32768, 2x14336]", lambda: ops.geglu(a, b), 3 * n)
+    run("swiglu_backward_bf16 [32768, 14336]", lambda: ops.swiglu_backward(grad, a, b), 5 * n)
+    del w, gu, a, b, grad
+    torch.cuda.empty_cache()
+
+    w = workloads.add_rms_norm_bf16().to(device)
+    x, r, weight = w.inputs["x"], w.inputs["residual"], w.inputs["weight"]
+    n = x.numel() * 2
+    run("rms_norm_gated_bf16 [16384, 8192]", lambda: ops.rms_norm_gated(x, r, weight), 3 * n)
+    run("layer_norm_bf16 [16384, 8192]", lambda: ops.layer_norm(x, weight, weight), 2 * n)
+    run("rms_norm_backward_bf16 [16384, 8192]", lambda: ops.rms_norm_backward(r, x, weight), 3 * n)
+    run("add_rms_norm_backward_bf16 [16384, 8192]", lambda: ops.add_rms_norm_backward(r, r, x, weight, 1e-5), 4 * n)
+    heads = x.view(-1, 128)  # per-head q/k normalisation: 1,048,576 rows of 128
+    run("l2_norm_bf16 [1048576, 128]", lambda: ops.l2_norm(heads), 2 * n)
+    return out
+
+
 def bench_moe_expert_parallel(device, world: int, rank: int, dist, exchange: str, steps: int = 20, warmup: int = 3) -> dict:
     """Config 5 sharded over the ranks: 65536 / world tokens and 64 / world experts per GPU.
 
@@ -553,6 +593,7 @@ def main() -> None:
         per_op["moe_bf16"] = bench_moe(device, peak_gbs, sampler)
         if world == 1:
             torch_eager_incumbent(device, per_op, args.records)
+            per_op["beyond_the_five_configs"] = bench_extra_ops(device, peak_gbs, sampler)
     if dist is not None:
         dist.barrier()
         if not args.skip_per_op:

@@ -11,6 +11,7 @@
 //       y = round_T( x * round_T(rsqrt(round_T(round_T(sum round_T(x^2)) + eps))) )
 //   layer_norm      src/popcorn/kernels/layer_norm.py:20 (F.layer_norm: fp32 statistics, one rounding)
 //       y = round_T( (x*rstd - mean*rstd) * w + b ),  rstd = 1/sqrt(var + eps), biased variance
+#include "activations.cuh"
 #include "common.cuh"
 
 namespace b200 {
@@ -18,8 +19,14 @@ namespace {
 
 enum Mode { kGatedSwish = 0, kGatedSigmoid = 1, kL2 = 2, kLayer = 3 };
 
-__device__ __forceinline__ float sigmoid_f32(float x) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))); }
-__device__ __forceinline__ float silu_ref_f32(float x) { return __fdiv_rn(x, __fadd_rn(1.0f, expf(-x))); }
+// Gate of the gated RMSNorm in fp32: the reference's operation sequence for fp32 tensors, the
+// corrected-ex2 / Newton forms (activations.cuh) for 16-bit ones, whose result is rounded to T anyway.
+template <typename T, int MODE>
+__device__ __forceinline__ float gate_act(float g) {
+  constexpr int MATH = sizeof(T) == 4 ? 0 : 1;
+  if constexpr (MODE == 0) return silu_f32<MATH>(g);
+  else return sigmoid_f32<MATH>(g);
+}
 
 // Sum over the TPR threads of a row.  TPR == 32: shuffles only.  TPR == 256: one row per CTA, the
 // caller passes a distinct smem slot per reduction so that one barrier per reduction is enough.
@@ -108,7 +115,9 @@ family_rows_kernel(const T* x, const T* gate, const T* __restrict__ weight, cons
   } else if constexpr (MODE == kL2) {
     const float total = Num<T>::rt(acc);                   // .sum(-1) returns dtype T
     const float v = Num<T>::rt(__fadd_rn(total, eps));     // + eps, dtype T
-    scale = Num<T>::rt(__frcp_rn(__fsqrt_rn(v)));          // torch.rsqrt, dtype T
+    // torch.rsqrt of a T tensor: 1/sqrt in fp32, one rounding.  (PyTorch's vectorised CPU loop rounds sqrt(v)
+    // to T before the reciprocal for 16-bit dtypes, its scalar tail does not; this is the tail's arithmetic.)
+    scale = Num<T>::rt(__frcp_rn(__fsqrt_rn(v)));
   } else {
     scale = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(acc, cols_f), eps)));
   }
@@ -148,8 +157,8 @@ family_rows_kernel(const T* x, const T* gate, const T* __restrict__ weight, cons
           o1 = __fadd_rn(o1, b[j + 1]);
           Num<T>::round2(o0, o1);
         }
-        float a0 = MODE == kGatedSwish ? silu_ref_f32(g[j]) : sigmoid_f32(g[j]);
-        float a1 = MODE == kGatedSwish ? silu_ref_f32(g[j + 1]) : sigmoid_f32(g[j + 1]);
+        float a0 = gate_act<T, MODE == kGatedSwish ? 0 : 1>(g[j]);
+        float a1 = gate_act<T, MODE == kGatedSwish ? 0 : 1>(g[j + 1]);
         Num<T>::round2(a0, a1);
         o0 = __fmul_rn(o0, a0);
         o1 = __fmul_rn(o1, a1);
@@ -208,7 +217,7 @@ family_stream_kernel(const T* x, const T* gate, const T* __restrict__ weight, co
       o = Num<T>::rt(__fmul_rn(Num<T>::rt(__fmul_rn(h, scale)), Num<T>::up(weight[c])));
       if (has_bias) o = Num<T>::rt(__fadd_rn(o, Num<T>::up(bias[c])));
       const float g = GATED ? Num<T>::up(gate[row * ldg + c]) : 0.f;
-      o = __fmul_rn(o, Num<T>::rt(MODE == kGatedSwish ? silu_ref_f32(g) : sigmoid_f32(g)));
+      o = __fmul_rn(o, Num<T>::rt(MODE == kGatedSwish ? silu_f32<0>(g) : sigmoid_f32<0>(g)));
     }
     y[row * ldy + c] = Num<T>::down(o);
   }
