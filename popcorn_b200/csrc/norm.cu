@@ -31,7 +31,15 @@ __device__ __forceinline__ float scale_one(float h, float r, float w, float b, b
 
 // One row per group of TPR threads, ITEMS 128-bit words per thread, the row held
 // in registers.  THREADS / TPR rows per CTA.  ADD selects add_rms_norm.
-template <typename T, int TPR, int ITEMS, bool ADD>
+// Sum over the TPR consecutive lanes of a row group (TPR <= 32, a power of two).
+template <int TPR>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int o = (TPR < 32 ? TPR : 32) / 2; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+template <typename T, int TPR, int ITEMS, bool ADD, int RU>
 __global__ void __launch_bounds__(TPR < 256 ? 256 : TPR)
 rms_rows_kernel(const T* x, const T* res, const T* __restrict__ weight,
                 const T* __restrict__ bias, T* y, T* s_out,
@@ -39,116 +47,122 @@ rms_rows_kernel(const T* x, const T* res, const T* __restrict__ weight,
                 float cols_f, float eps, float offset) {
   constexpr int V = Num<T>::kVec;
   constexpr int THREADS = TPR < 256 ? 256 : TPR;
-  constexpr int ROWS_PER_CTA = THREADS / TPR;
+  constexpr int GROUPS = THREADS / TPR;  // row groups per CTA; each owns RU consecutive rows
   constexpr int WARPS_PER_ROW = TPR / 32;
+  static_assert(RU == 1 || TPR <= 32, "several rows per group only for rows that fit a warp");
   pdl_prologue();
 
   const int tid = threadIdx.x;
-  const int sub = tid / TPR;        // which row of this CTA
+  const int sub = tid / TPR;
   const int lane_in_row = tid % TPR;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * ROWS_PER_CTA + sub;
-  const bool row_ok = row < rows;
+  const int64_t row0 = (static_cast<int64_t>(blockIdx.x) * GROUPS + sub) * RU;
 
-  uint4 data[ITEMS];
-  bool ok[ITEMS];
+  uint4 data[RU][ITEMS];
+  uint4 rdata[ADD ? RU : 1][ADD ? ITEMS : 1];
+  bool ok[RU][ITEMS];
+  // issue every load of every row before touching any of them
 #pragma unroll
-  for (int i = 0; i < ITEMS; ++i) ok[i] = row_ok && (lane_in_row + i * TPR) < nvec;
-
-  // issue every load of the row before touching any of them
-  uint4 rdata[ADD ? ITEMS : 1];
+  for (int u = 0; u < RU; ++u) {
+    const int64_t row = row0 + u;
 #pragma unroll
-  for (int i = 0; i < ITEMS; ++i) {
-    const int v = lane_in_row + i * TPR;
-    data[i] = make_uint4(0, 0, 0, 0);
-    if (ok[i]) data[i] = ld_stream(x + row * ldx + static_cast<int64_t>(v) * V);
-    if constexpr (ADD) {
-      rdata[i] = make_uint4(0, 0, 0, 0);
-      if (ok[i]) rdata[i] = ld_stream(res + row * ldr + static_cast<int64_t>(v) * V);
+    for (int i = 0; i < ITEMS; ++i) {
+      const int v = lane_in_row + i * TPR;
+      ok[u][i] = row < rows && v < nvec;
+      data[u][i] = make_uint4(0, 0, 0, 0);
+      if (ok[u][i]) data[u][i] = ld_stream(x + row * ldx + static_cast<int64_t>(v) * V);
+      if constexpr (ADD) {
+        rdata[u][i] = make_uint4(0, 0, 0, 0);
+        if (ok[u][i]) rdata[u][i] = ld_stream(res + row * ldr + static_cast<int64_t>(v) * V);
+      }
     }
   }
-
-  float acc = 0.f;
-#pragma unroll
-  for (int i = 0; i < ITEMS; ++i) {
-    float f[V];
-    Num<T>::unpack(data[i], f);
-    if constexpr (ADD) {
-      float g[V];
-      Num<T>::unpack(rdata[i], g);
-#pragma unroll
-      for (int j = 0; j < V; ++j) f[j] = __fadd_rn(f[j], g[j]);
-      data[i] = Num<T>::pack(f);  // s = x + residual, rounded to T by the pack
-      Num<T>::unpack(data[i], f);
-      if (ok[i]) st_stream(s_out + row * lds + static_cast<int64_t>(lane_in_row + i * TPR) * V, data[i]);
-    }
-#pragma unroll
-    for (int j = 0; j < V; ++j) acc = __fmaf_rn(f[j], f[j], acc);
-  }
-
-  acc = warp_sum(acc);
-  if (WARPS_PER_ROW > 1) {
-    __shared__ float partial[THREADS / 32];
-    const int warp = tid / 32;
-    if ((tid & 31) == 0) partial[warp] = acc;
-    __syncthreads();
-    float total = 0.f;
-    const int first = sub * WARPS_PER_ROW;
-#pragma unroll
-    for (int w = 0; w < WARPS_PER_ROW; ++w) total = __fadd_rn(total, partial[first + w]);
-    acc = total;
-  }
-  const float r = inv_rms(acc, cols_f, eps);
   const bool has_bias = bias != nullptr;
 
 #pragma unroll
-  for (int i = 0; i < ITEMS; ++i) {
-    if (!ok[i]) continue;
-    const int64_t col = static_cast<int64_t>(lane_in_row + i * TPR) * V;
-    if constexpr (sizeof(T) == 4) {
-      float f[V], w[V], b[V];
-      Num<T>::unpack(data[i], f);
-      Num<T>::unpack(ld_reuse(weight + col), w);
-      if (has_bias) Num<T>::unpack(ld_reuse(bias + col), b);
+  for (int u = 0; u < RU; ++u) {
+    const int64_t row = row0 + u;
+    float acc = 0.f;
 #pragma unroll
-      for (int j = 0; j < V; ++j) {
-        const float wj = ADD ? __fadd_rn(w[j], offset) : w[j];
-        f[j] = __fmul_rn(__fmul_rn(f[j], r), wj);
-        if (has_bias) f[j] = __fadd_rn(f[j], b[j]);
+    for (int i = 0; i < ITEMS; ++i) {
+      float f[V];
+      Num<T>::unpack(data[u][i], f);
+      if constexpr (ADD) {
+        float g[V];
+        Num<T>::unpack(rdata[u][i], g);
+#pragma unroll
+        for (int j = 0; j < V; ++j) f[j] = __fadd_rn(f[j], g[j]);
+        data[u][i] = Num<T>::pack(f);  // s = x + residual, rounded to T by the pack
+        Num<T>::unpack(data[u][i], f);
+        if (ok[u][i]) st_stream(s_out + row * lds + static_cast<int64_t>(lane_in_row + i * TPR) * V, data[u][i]);
       }
-      st_stream(y + row * ldy + col, Num<T>::pack(f));
-    } else {
-      // 16-bit: h * r in fp32, one packed rounding to T, then the packed product with the weight
-      // word (a product of two 16-bit values is rounded once, as in the reference)
-      const uint4 wv = ld_reuse(weight + col);
-      uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-      if (ADD && offset != 0.f) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc = __fmaf_rn(f[j], f[j], acc);
+    }
+
+    acc = group_sum<TPR>(acc);
+    if constexpr (WARPS_PER_ROW > 1) {
+      __shared__ float partial[THREADS / 32];
+      const int warp = tid / 32;
+      if ((tid & 31) == 0) partial[warp] = acc;
+      __syncthreads();
+      float total = 0.f;
+      const int first = sub * WARPS_PER_ROW;
+#pragma unroll
+      for (int w = 0; w < WARPS_PER_ROW; ++w) total = __fadd_rn(total, partial[first + w]);
+      acc = total;
+    }
+    const float r = inv_rms(acc, cols_f, eps);
+
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      if (!ok[u][i]) continue;
+      const int64_t col = static_cast<int64_t>(lane_in_row + i * TPR) * V;
+      if constexpr (sizeof(T) == 4) {
+        float f[V], w[V], b[V];
+        Num<T>::unpack(data[u][i], f);
+        Num<T>::unpack(ld_reuse(weight + col), w);
+        if (has_bias) Num<T>::unpack(ld_reuse(bias + col), b);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float wj = ADD ? __fadd_rn(w[j], offset) : w[j];
+          f[j] = __fmul_rn(__fmul_rn(f[j], r), wj);
+          if (has_bias) f[j] = __fadd_rn(f[j], b[j]);
+        }
+        st_stream(y + row * ldy + col, Num<T>::pack(f));
+      } else {
+        // 16-bit: h * r in fp32, one packed rounding to T, then the packed product with the weight
+        // word (a product of two 16-bit values is rounded once, as in the reference)
+        const uint4 wv = ld_reuse(weight + col);
+        uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+        if (ADD && offset != 0.f) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float lo, hi;
+            Num<T>::unpack2(ww[j], lo, hi);
+            ww[j] = Num<T>::pack2(__fadd_rn(lo, offset), __fadd_rn(hi, offset));
+          }
+        }
+        const uint32_t wd[4] = {data[u][i].x, data[u][i].y, data[u][i].z, data[u][i].w};
+        uint32_t wo[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           float lo, hi;
-          Num<T>::unpack2(ww[j], lo, hi);
-          ww[j] = Num<T>::pack2(__fadd_rn(lo, offset), __fadd_rn(hi, offset));
+          Num<T>::unpack2(wd[j], lo, hi);
+          wo[j] = Num<T>::mul2(Num<T>::pack2(__fmul_rn(lo, r), __fmul_rn(hi, r)), ww[j]);
         }
-      }
-      const uint32_t wd[4] = {data[i].x, data[i].y, data[i].z, data[i].w};
-      uint32_t wo[4];
+        if (has_bias) {
+          const uint4 bv = ld_reuse(bias + col);
+          const uint32_t wb[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float lo, hi;
-        Num<T>::unpack2(wd[j], lo, hi);
-        wo[j] = Num<T>::mul2(Num<T>::pack2(__fmul_rn(lo, r), __fmul_rn(hi, r)), ww[j]);
-      }
-      if (has_bias) {
-        const uint4 bv = ld_reuse(bias + col);
-        const uint32_t wb[4] = {bv.x, bv.y, bv.z, bv.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float lo, hi, blo, bhi;
-          Num<T>::unpack2(wo[j], lo, hi);
-          Num<T>::unpack2(wb[j], blo, bhi);
-          wo[j] = Num<T>::pack2(__fadd_rn(lo, blo), __fadd_rn(hi, bhi));
+          for (int j = 0; j < 4; ++j) {
+            float lo, hi, blo, bhi;
+            Num<T>::unpack2(wo[j], lo, hi);
+            Num<T>::unpack2(wb[j], blo, bhi);
+            wo[j] = Num<T>::pack2(__fadd_rn(lo, blo), __fadd_rn(hi, bhi));
+          }
         }
+        st_stream(y + row * ldy + col, make_uint4(wo[0], wo[1], wo[2], wo[3]));
       }
-      st_stream(y + row * ldy + col, make_uint4(wo[0], wo[1], wo[2], wo[3]));
     }
   }
 }
@@ -194,14 +208,14 @@ rms_stream_kernel(const T* x, const T* res, const T* __restrict__ weight,
   }
 }
 
-template <typename T, int TPR, int ITEMS, bool ADD>
+template <typename T, int TPR, int ITEMS, bool ADD, int RU = 1>
 void launch_rows(const void* x, const void* res, const void* w, const void* b, void* y, void* s,
                  int64_t rows, int nvec, int64_t ldx, int64_t ldr, int64_t ldy, int64_t lds,
                  float cols_f, float eps, float offset, cudaStream_t st) {
   constexpr int THREADS = TPR < 256 ? 256 : TPR;
-  constexpr int ROWS_PER_CTA = THREADS / TPR;
+  constexpr int ROWS_PER_CTA = THREADS / TPR * RU;
   const unsigned grid = static_cast<unsigned>(ceil_div(rows, ROWS_PER_CTA));
-  launch(rms_rows_kernel<T, TPR, ITEMS, ADD>, grid, THREADS, 0, st,
+  launch(rms_rows_kernel<T, TPR, ITEMS, ADD, RU>, grid, THREADS, 0, st,
       static_cast<const T*>(x), static_cast<const T*>(res), static_cast<const T*>(w), static_cast<const T*>(b),
       static_cast<T*>(y), static_cast<T*>(s), rows, nvec, ldx, ldr, ldy, lds, cols_f, eps, offset);
 }
@@ -221,7 +235,19 @@ int run(const void* x, const void* res, const void* w, const void* b, void* y, v
 #define B200_ROWS(TPR, ITEMS)                                                                                   \
   launch_rows<T, TPR, ITEMS, ADD>(x, res, w, b, y, s, rows, nvec, ldx, ldr, ldy, lds, cols_f, eps, offset, st); \
   return after_launch("rms_rows_kernel")
-    if (nvec <= 32) { B200_ROWS(32, 1); }
+    // short rows (per-head norms): several rows per warp, four rows per lane group in flight
+    if (nvec <= 8) {
+      launch_rows<T, 8, 1, ADD, 4>(x, res, w, b, y, s, rows, nvec, ldx, ldr, ldy, lds, cols_f, eps, offset, st);
+      return after_launch("rms_rows_kernel");
+    }
+    if (nvec <= 16) {
+      launch_rows<T, 16, 1, ADD, 4>(x, res, w, b, y, s, rows, nvec, ldx, ldr, ldy, lds, cols_f, eps, offset, st);
+      return after_launch("rms_rows_kernel");
+    }
+    if (nvec <= 32) {
+      launch_rows<T, 32, 1, ADD, 4>(x, res, w, b, y, s, rows, nvec, ldx, ldr, ldy, lds, cols_f, eps, offset, st);
+      return after_launch("rms_rows_kernel");
+    }
     if (nvec <= 64) { B200_ROWS(32, 2); }
     if (nvec <= 128) { B200_ROWS(32, 4); }
     if (nvec <= 256) { B200_ROWS(32, 8); }

@@ -28,11 +28,12 @@ __device__ __forceinline__ float gate_act(float g) {
   else return sigmoid_f32<MATH>(g);
 }
 
-// Sum over the TPR threads of a row.  TPR == 32: shuffles only.  TPR == 256: one row per CTA, the
+// Sum over the TPR threads of a row.  TPR <= 32: shuffles only (TPR consecutive lanes).  TPR == 256: one row per CTA, the
 // caller passes a distinct smem slot per reduction so that one barrier per reduction is enough.
 template <int TPR>
 __device__ __forceinline__ float row_sum(float v, float* slot) {
-  v = warp_sum(v);
+#pragma unroll
+  for (int o = (TPR < 32 ? TPR : 32) / 2; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
   if constexpr (TPR > 32) {
     if ((threadIdx.x & 31) == 0) slot[threadIdx.x >> 5] = v;
     __syncthreads();
@@ -44,33 +45,45 @@ __device__ __forceinline__ float row_sum(float v, float* slot) {
   return v;
 }
 
-template <typename T, int TPR, int ITEMS, int MODE>
+template <typename T, int TPR, int ITEMS, int MODE, int RU>
 __global__ void __launch_bounds__(256)
 family_rows_kernel(const T* x, const T* gate, const T* __restrict__ weight, const T* __restrict__ bias, T* y,
                    int64_t rows, int nvec, int64_t ldx, int64_t ldg, int64_t ldy, float cols_f, float eps) {
   constexpr int V = Num<T>::kVec;
-  constexpr int ROWS_PER_CTA = 256 / TPR;
+  constexpr int GROUPS = 256 / TPR;  // row groups per CTA; each owns RU consecutive rows
+  static_assert(RU == 1 || TPR <= 32, "several rows per group only for rows that fit a warp");
   constexpr bool GATED = MODE == kGatedSwish || MODE == kGatedSigmoid;
   pdl_prologue();
   __shared__ float slots[2][8];
   const int tid = threadIdx.x;
   const int sub = tid / TPR, lane_in_row = tid % TPR;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * ROWS_PER_CTA + sub;
-  const bool row_ok = row < rows;
+  const int64_t row0 = (static_cast<int64_t>(blockIdx.x) * GROUPS + sub) * RU;
 
-  uint4 data[ITEMS], gdata[GATED ? ITEMS : 1];
-  bool ok[ITEMS];
+  uint4 all_data[RU][ITEMS], all_gdata[GATED ? RU : 1][GATED ? ITEMS : 1];
+  bool all_ok[RU][ITEMS];
 #pragma unroll
-  for (int i = 0; i < ITEMS; ++i) {
-    ok[i] = row_ok && (lane_in_row + i * TPR) < nvec;
-    data[i] = make_uint4(0, 0, 0, 0);
-    const int64_t col = static_cast<int64_t>(lane_in_row + i * TPR) * V;
-    if (ok[i]) data[i] = ld_stream(x + row * ldx + col);
-    if constexpr (GATED) {
-      gdata[i] = make_uint4(0, 0, 0, 0);
-      if (ok[i]) gdata[i] = ld_stream(gate + row * ldg + col);
+  for (int u = 0; u < RU; ++u) {
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const int64_t row = row0 + u;
+      all_ok[u][i] = row < rows && (lane_in_row + i * TPR) < nvec;
+      all_data[u][i] = make_uint4(0, 0, 0, 0);
+      const int64_t col = static_cast<int64_t>(lane_in_row + i * TPR) * V;
+      if (all_ok[u][i]) all_data[u][i] = ld_stream(x + row * ldx + col);
+      if constexpr (GATED) {
+        all_gdata[u][i] = make_uint4(0, 0, 0, 0);
+        if (all_ok[u][i]) all_gdata[u][i] = ld_stream(gate + row * ldg + col);
+      }
     }
   }
+  const bool has_bias = bias != nullptr;
+
+#pragma unroll
+  for (int u = 0; u < RU; ++u) {
+  const int64_t row = row0 + u;
+  uint4(&data)[ITEMS] = all_data[u];
+  uint4(&gdata)[GATED ? ITEMS : 1] = all_gdata[GATED ? u : 0];
+  bool(&ok)[ITEMS] = all_ok[u];
 
   // first moment (LayerNorm) or sum of squares
   float acc = 0.f;
@@ -121,7 +134,6 @@ family_rows_kernel(const T* x, const T* gate, const T* __restrict__ weight, cons
   } else {
     scale = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(acc, cols_f), eps)));
   }
-  const bool has_bias = bias != nullptr;
 
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
@@ -168,6 +180,7 @@ family_rows_kernel(const T* x, const T* gate, const T* __restrict__ weight, cons
     }
     st_stream(y + row * ldy + col, Num<T>::pack(f));
   }
+  }  // rows of this group
 }
 
 // Any width, any alignment: one CTA per row, scalar accesses, the row re-read for every pass.
@@ -237,10 +250,14 @@ int run(const void* x, const void* gate, const void* w, const void* b, void* y, 
   const int64_t nvec64 = cols / V;
   if (vec && nvec64 <= 2048) {
     const int nvec = static_cast<int>(nvec64);
-#define B200_FAMILY(TPR, ITEMS)                                                                                      \
-  launch(family_rows_kernel<T, TPR, ITEMS, MODE>, static_cast<unsigned>(ceil_div(rows, 256 / TPR)), 256, 0, st, tx, tg, \
+#define B200_FAMILY_RU(TPR, ITEMS, RU)                                                                                        \
+  launch(family_rows_kernel<T, TPR, ITEMS, MODE, RU>, static_cast<unsigned>(ceil_div(rows, 256 / TPR * RU)), 256, 0, st, tx, tg, \
          tw, tb, ty, rows, nvec, ldx, ldg, ldy, cols_f, eps)
-    if (nvec <= 32) B200_FAMILY(32, 1);
+#define B200_FAMILY(TPR, ITEMS) B200_FAMILY_RU(TPR, ITEMS, 1)
+    // short rows (per-head norms): several rows per warp, four rows per lane group in flight
+    if (nvec <= 8) B200_FAMILY_RU(8, 1, 4);
+    else if (nvec <= 16) B200_FAMILY_RU(16, 1, 4);
+    else if (nvec <= 32) B200_FAMILY_RU(32, 1, 4);
     else if (nvec <= 64) B200_FAMILY(32, 2);
     else if (nvec <= 128) B200_FAMILY(32, 4);
     else if (nvec <= 256) B200_FAMILY(32, 8);
@@ -248,6 +265,7 @@ int run(const void* x, const void* gate, const void* w, const void* b, void* y, 
     else if (nvec <= 1024) B200_FAMILY(256, 4);
     else B200_FAMILY(256, 8);
 #undef B200_FAMILY
+#undef B200_FAMILY_RU
     return after_launch("family_rows_kernel");
   }
   launch(family_stream_kernel<T, MODE>, static_cast<unsigned>(rows), 256, 0, st, tx, tg, tw, tb, ty, cols, ldx, ldg, ldy, cols_f, eps);

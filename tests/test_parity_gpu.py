@@ -139,6 +139,8 @@ NORM_SHAPES = [
     (1, 8, BF16), (3, 256, BF16), (5, 264, BF16), (9, 512, F16), (7, 1024, BF16), (4, 2048, BF16), (3, 4096, BF16),
     (2, 8192, BF16), (2, 16384, BF16), (2, 32768, BF16), (1, 65536, BF16), (1, 65544, BF16), (1, 131072, BF16),
     (1000, 128, F32), (33, 4096, F32), (6, 100, F32), (5, 33, BF16), (4, 1023, F16), (2, 12288, F32), (2, 40000, F32),
+    # short rows: several rows per warp (8 and 16 lanes per row), ragged last group
+    (1030, 128, BF16), (515, 64, BF16), (301, 16, F32), (77, 72, F16), (3, 24, BF16),
 ]
 
 

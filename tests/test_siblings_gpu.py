@@ -49,7 +49,8 @@ def test_geglu_shapes(rows, cols, dtype):
 
 
 SHAPES = [(1, 8, BF16), (3, 256, BF16), (5, 264, BF16), (9, 512, F16), (7, 1024, BF16), (4, 2048, BF16), (3, 4096, BF16), (2, 8192, BF16), (2, 16384, BF16),
-          (1, 20000, BF16), (1000, 128, F32), (33, 4096, F32), (6, 100, F32), (5, 33, BF16), (2, 12288, F32)]
+          (1, 20000, BF16), (1000, 128, F32), (33, 4096, F32), (6, 100, F32), (5, 33, BF16), (2, 12288, F32),
+          (1030, 128, BF16), (515, 64, BF16), (301, 16, F32), (77, 72, F16)]
 
 
 @pytest.mark.parametrize("rows,cols,dtype", SHAPES)
