@@ -316,7 +316,7 @@ def torch_eager_incumbent(device, per_op: dict, records_root: str | None) -> Non
         per_op["popcorn_report_rows"] = [str(path) for path in paths]
 
 
-def bench_extra_ops(device, peak_gbs: float, sampler) -> dict:
+def bench_extra_ops(device, peak_gbs: float, sampler, scale: float = 1.0, steps: int = 50, match: str = "") -> dict:
     """The ops beyond the five benchmark configurations, at the benchmark shapes they correspond to.
 
     Timed through the public op functions (outputs allocated per call by the caching allocator, which does
@@ -325,7 +325,10 @@ def bench_extra_ops(device, peak_gbs: float, sampler) -> dict:
 
     out = {}
 
-    def run(name, fn, nbytes, steps=50):
+    def run(name, fn, nbytes):
+        if match not in name:
+            return
+        nbytes = int(nbytes)
         t0 = time.time()
         ms = time_launches(lambda i: fn(), steps, 3, device)
         if sampler is not None:
@@ -334,7 +337,7 @@ def bench_extra_ops(device, peak_gbs: float, sampler) -> dict:
         out[name] = {"ms": round(ms, 5), "gb_s": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak_gbs, 4),
                      "frac_of_8tbs": round(gbs / SPEC_HBM_GBS, 4), "algorithmic_bytes": nbytes}
 
-    w = workloads.swiglu_bf16().to(device)
+    w = workloads.swiglu_bf16(scale).to(device)
     gu, cols = w.inputs["gate_up"], w.args["cols"]
     a, b = gu[:, :cols], gu[:, cols:]
     grad = torch.randn(gu.shape[0], cols, device=device).to(torch.bfloat16)
@@ -344,7 +347,7 @@ def bench_extra_ops(device, peak_gbs: float, sampler) -> dict:
     del w, gu, a, b, grad
     torch.cuda.empty_cache()
 
-    w = workloads.add_rms_norm_bf16().to(device)
+    w = workloads.add_rms_norm_bf16(scale).to(device)
     x, r, weight = w.inputs["x"], w.inputs["residual"], w.inputs["weight"]
     n = x.numel() * 2
     run("rms_norm_gated_bf16 [16384, 8192]", lambda: ops.rms_norm_gated(x, r, weight), 3 * n)
@@ -353,6 +356,20 @@ def bench_extra_ops(device, peak_gbs: float, sampler) -> dict:
     run("add_rms_norm_backward_bf16 [16384, 8192]", lambda: ops.add_rms_norm_backward(r, r, x, weight, 1e-5), 4 * n)
     heads = x.view(-1, 128)  # per-head q/k normalisation: 1,048,576 rows of 128
     run("l2_norm_bf16 [1048576, 128]", lambda: ops.l2_norm(heads), 2 * n)
+    del w, x, r, weight, heads
+    torch.cuda.empty_cache()
+
+    # the rotary siblings at the shapes of config 3 (8 x 4096 positions, 32 + 8 heads of 128)
+    w = workloads.paired_rope_bf16(scale).to(device)
+    q, k, cos, sin = (w.inputs[name] for name in ("q", "k", "cos", "sin"))
+    head_weight = (1 + 0.1 * torch.randn(128, device=device)).to(torch.bfloat16)
+    n = 2 * (q.numel() + k.numel()) * 2
+    run("qk_norm_rope_bf16 q[8,32,4096,128] k[8,8,4096,128]", lambda: ops.qk_norm_rope(q, k, head_weight, head_weight, cos, sin),
+        n + 2 * cos.numel() * 2 + 2 * 128 * 2)
+    w3 = workloads.rotary_bf16(scale).to(device)
+    q3, k3 = w3.inputs["q"], w3.inputs["k"]
+    freqs = torch.stack((w3.inputs["cos"], w3.inputs["sin"]), -1).to(torch.bfloat16)
+    run("llama4_rope_bf16 q[8,4096,32,128] k[8,4096,8,128]", lambda: ops.llama4_rope(q3, k3, freqs), n + freqs.numel() * 2)
     return out
 
 
@@ -483,8 +500,10 @@ def main() -> None:
     parser.add_argument("--skip-per-op", action="store_true", help="only the headline loop (used for profiling captures)")
     parser.add_argument("--scale", type=float, default=1.0, help="shrink the token count (profiling captures only)")
     parser.add_argument("--records", metavar="DIR", help="also write popcorn report rows (schema 3) under DIR/v3/reports")
-    parser.add_argument("--only", choices=["rms_norm_fp32", "add_rms_norm_bf16", "rotary_bf16", "swiglu_bf16", "paired_rope_bf16", "moe_bf16"],
-                        help="time one configuration's kernels alone and print a short JSON (profiling captures)")
+    parser.add_argument("--only", choices=["rms_norm_fp32", "add_rms_norm_bf16", "rotary_bf16", "swiglu_bf16", "paired_rope_bf16", "moe_bf16", "extras"],
+                        help="time one configuration's kernels alone and print a short JSON (profiling captures); "
+                             "`extras` = the ops beyond the five configurations, filtered by --match")
+    parser.add_argument("--match", default="", help="with --only extras: run the ops whose name contains this text")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -512,6 +531,8 @@ def main() -> None:
     if args.only:
         if args.only == "moe_bf16":
             result = bench_moe(device, peak_gbs, None, args.scale, args.steps, args.warmup)
+        elif args.only == "extras":
+            result = bench_extra_ops(device, peak_gbs, None, args.scale, args.steps, args.match)
         else:
             result = bench_single_kernel_ops(device, peak_gbs, None, [args.only], args.scale, args.steps, args.warmup)[args.only]
         print(json.dumps({"only": args.only, "scale": args.scale, "steps": args.steps, **result}), flush=True)

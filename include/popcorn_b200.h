@@ -174,6 +174,43 @@ int b200_rope_paired(const void* q, const void* k, const void* cos, const void* 
                      int dtype, void* stream);
 
 /*
+ * Per-head RMS normalisation of queries and keys followed by the paired rotary embedding, one launch:
+ *   n = round_T(round_T(x * r) * w),  r = 1 / sqrt(mean(x^2 over head_dim) + eps) in fp32,  w = q_weight or k_weight
+ *   y = round_T(round_T(n * cos) + round_T(rot(n) * sin))
+ *
+ * Replaces qk_norm_rope(q, k, q_weight, k_weight, cos, sin, eps=1e-6), the fused op the reference
+ * builds in examples/03_write_a_kernel.ipynb (cell 3: reference; cells 7, 11: its Triton forward),
+ * = rope(rms_norm(q, q_weight), rms_norm(k, k_weight), cos, sin) of src/popcorn/kernels/rope.py:24-36
+ * and src/popcorn/kernels/_utils.py:14-16.  Layout and tables as in b200_rope_paired; q_weight, k_weight:
+ * [head_dim] contiguous in the dtype of q.
+ */
+int b200_qk_norm_rope(const void* q, const void* k, const void* q_weight, const void* k_weight,
+                      const void* cos, const void* sin, void* q_out, void* k_out,
+                      int64_t batch, int64_t q_heads, int64_t k_heads, int64_t seq, int64_t head_dim, int64_t cos_batch,
+                      int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                      int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+                      int64_t qo_stride_b, int64_t qo_stride_h, int64_t qo_stride_s,
+                      int64_t ko_stride_b, int64_t ko_stride_h, int64_t ko_stride_s,
+                      double eps, int dtype, void* stream);
+
+/*
+ * Llama 4 rotary embedding of queries and keys: channels are (real, imaginary) pairs multiplied by
+ * unit complex numbers given as (cos, sin) pairs,
+ *   y_re = round_T(round_T(re * f_re) - round_T(im * f_im)),  y_im = round_T(round_T(re * f_im) + round_T(im * f_re))
+ *
+ * Replaces llama4_rope(q, k, freqs), src/popcorn/kernels/llama4_rope.py:14-39.  Layout (batch, seq,
+ * heads, head_dim) with batch/seq/head strides and a contiguous head_dim; freqs: [seq, head_dim/2, 2]
+ * contiguous in the dtype of q.  q_out == q and k_out == k are allowed.
+ */
+int b200_llama4_rope(const void* q, const void* k, const void* freqs, void* q_out, void* k_out,
+                     int64_t batch, int64_t seq, int64_t q_heads, int64_t k_heads, int64_t head_dim,
+                     int64_t q_stride_b, int64_t q_stride_s, int64_t q_stride_h,
+                     int64_t k_stride_b, int64_t k_stride_s, int64_t k_stride_h,
+                     int64_t qo_stride_b, int64_t qo_stride_s, int64_t qo_stride_h,
+                     int64_t ko_stride_b, int64_t ko_stride_s, int64_t ko_stride_h,
+                     int dtype, void* stream);
+
+/*
  * out = round_T(round_T(silu(a)) * b),  silu(a) = a / (1 + exp(-a)) in fp32
  *
  * Replaces swiglu(a, b) = F.silu(a) * b, src/popcorn/kernels/swiglu.py:9-18

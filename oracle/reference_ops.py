@@ -84,6 +84,25 @@ def rope(q: Tensor, k: Tensor, cos: Tensor, sin: Tensor) -> tuple[Tensor, Tensor
     return q * c + turned(q) * s, k * c + turned(k) * s
 
 
+def qk_norm_rope(q: Tensor, k: Tensor, q_weight: Tensor, k_weight: Tensor, cos: Tensor, sin: Tensor, eps: float = 1e-6) -> tuple[Tensor, Tensor]:
+    """Reference: qk_norm_rope, examples/03_write_a_kernel.ipynb cell 3 (per-head RMSNorm via
+    src/popcorn/kernels/_utils.py:14-16, then the rotation of src/popcorn/kernels/rope.py:24-36)."""
+    return rope(_unit_rms(q, eps) * q_weight, _unit_rms(k, eps) * k_weight, cos, sin)
+
+
+def llama4_rope(q: Tensor, k: Tensor, freqs: Tensor) -> tuple[Tensor, Tensor]:
+    """Reference: llama4_rope, src/popcorn/kernels/llama4_rope.py:14-39 (layout batch, seq, heads, head_dim;
+    freqs [seq, head_dim/2, 2] = (cos, sin) per channel pair)."""
+    f_re, f_im = freqs[None, :, None, :, 0], freqs[None, :, None, :, 1]
+
+    def turned(x: Tensor) -> Tensor:
+        pairs = x.unflatten(-1, (-1, 2))
+        re, im = pairs[..., 0], pairs[..., 1]
+        return torch.stack((re * f_re - im * f_im, re * f_im + im * f_re), -1).flatten(-2)
+
+    return turned(q), turned(k)
+
+
 def swiglu(a: Tensor, b: Tensor) -> Tensor:
     """Reference: swiglu, src/popcorn/kernels/swiglu.py:10-18."""
     return F.silu(a) * b

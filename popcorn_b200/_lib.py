@@ -39,6 +39,8 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "b200_rope": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _ptr]),
     "b200_rope_qk": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _ptr]),
     "b200_rope_paired": (_int, [_ptr] * 6 + [_i64] * 18 + [_int, _ptr]),
+    "b200_qk_norm_rope": (_int, [_ptr] * 8 + [_i64] * 18 + [_dbl, _int, _ptr]),
+    "b200_llama4_rope": (_int, [_ptr] * 5 + [_i64] * 17 + [_int, _ptr]),
     "b200_swiglu": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _int, _ptr]),
     "b200_geglu": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _int, _ptr]),
     "b200_rms_norm_gated": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _int, _int, _dbl, _ptr]),

@@ -27,6 +27,7 @@ int check_device();
 int sm_count();
 // Bounded waits that ran out, per source file that uses bulk asynchronous copies.
 unsigned int rope_wait_timeouts();
+unsigned int norm_wait_timeouts();
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 inline size_t dtype_size(int dtype) { return dtype == B200_F32 ? 4 : 2; }
@@ -117,7 +118,15 @@ struct Num<__nv_bfloat16> {
   // Product of two packed pairs, each rounded once to bf16.  A bf16 x bf16 product is exact in
   // fp32, so this equals round(fp32(a) * fp32(b)), the way the reference multiplies two bf16 tensors.
   static __device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
-    __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+    __nv_bfloat162 r = __hmul2_rn(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+  // Sum of two packed pairs, each rounded once to bf16.  The reference adds two bf16 tensors as
+  // round_bf16(round_fp32(a + b)); the two roundings can only differ from one when the exact sum
+  // does not fit fp32 (exponents more than 16 apart) AND lies next to a bf16 tie (exponents about 8
+  // apart), which cannot both hold, so the packed add gives the reference's bits.
+  static __device__ __forceinline__ uint32_t add2(uint32_t a, uint32_t b) {
+    __nv_bfloat162 r = __hadd2_rn(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
     return *reinterpret_cast<uint32_t*>(&r);
   }
   static __device__ __forceinline__ void unpack(const uint4& v, float (&f)[8]) {
@@ -149,7 +158,13 @@ struct Num<__half> {
   static __device__ __forceinline__ void round2(float& a, float& b) { unpack2(pack2(a, b), a, b); }
   // fp16 x fp16 is exact in fp32 as well (22 significant bits): one rounding, like the reference.
   static __device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
-    __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    __half2 r = __hmul2_rn(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+  // Packed sum, one rounding per half; equal to round_fp16(round_fp32(a + b)) for the same reason as
+  // in the bf16 case (inexact in fp32 needs exponents more than 13 apart, a near-tie about 11).
+  static __device__ __forceinline__ uint32_t add2(uint32_t a, uint32_t b) {
+    __half2 r = __hadd2_rn(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
     return *reinterpret_cast<uint32_t*>(&r);
   }
   static __device__ __forceinline__ void unpack(const uint4& v, float (&f)[8]) {
@@ -207,6 +222,13 @@ __device__ __forceinline__ Float2x mul_f2(Float2x a, Float2x b) {
 __device__ __forceinline__ Float2x add_f2(Float2x a, Float2x b) {
   Float2x r;
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r.bits) : "l"(a.bits), "l"(b.bits));
+  return r;
+}
+// a * b + c with one rounding per half; only for places where the reference's own result is rounded
+// to a 16-bit type afterwards or is compared within a tolerance.
+__device__ __forceinline__ Float2x fma_f2(Float2x a, Float2x b, Float2x c) {
+  Float2x r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r.bits) : "l"(a.bits), "l"(b.bits), "l"(c.bits));
   return r;
 }
 __device__ __forceinline__ Float2x sub_f2(Float2x a, Float2x b) {

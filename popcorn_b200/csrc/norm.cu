@@ -9,7 +9,11 @@
 // Arithmetic follows src/popcorn/kernels/_utils.py:14-16 (rms),
 // src/popcorn/kernels/rms_norm.py:29-30 and src/popcorn/kernels/add_rms_norm.py:22-23
 // of the reference, including its intermediate roundings to the storage type.
+#include <algorithm>
+#include <cstdlib>
+
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace b200 {
 namespace {
@@ -279,16 +283,54 @@ int run(const void* x, const void* res, const void* w, const void* b, void* y, v
 // Persistent CTAs: each walks over rows blockIdx.x, blockIdx.x + gridDim.x, ... with the row in
 // registers, keeps fp32 partial column sums for grad_w / grad_b in registers, and writes them to
 // its own line of the scratch buffer at the end; rms_bwd_reduce_kernel adds the lines up.
-template <typename T, int ITEMS, bool ADD, bool HAS_BIAS>
+//
+// RING: a persistent CTA finishes a row (two passes with a barrier between them) before it can
+// ask for the next one, so with plain loads only about one row per CTA is in flight and the
+// kernel is latency-bound.  With RING the rows of gy, x (and gs) arrive through a ring of `stages`
+// shared-memory slots filled by bulk asynchronous copies that thread 0 issues `stages` rows
+// ahead; a slot is refilled one iteration after its row was consumed (after the barrier that
+// every thread reaches only when it is done with the previous row).  Waits on the copies are
+// bounded: when one runs out, the CTA marks the ring broken, reads the remaining rows with plain
+// loads (the data is the same) and thread 0 waits, bounded again, for copies still in flight
+// before it leaves.
+constexpr int kMaxRingStages = 8;
+
+template <typename T, int ITEMS, bool ADD, bool HAS_BIAS, bool RING>
 __global__ void __launch_bounds__(256)
 rms_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ gs, const T* __restrict__ x,
                     const T* __restrict__ weight, T* __restrict__ dx, float* __restrict__ part_w,
                     float* __restrict__ part_b, int64_t rows, int nvec, int64_t ldg, int64_t ldgs, int64_t ldx,
-                    int64_t lddx, float cols_f, float eps, float offset) {
+                    int64_t lddx, float cols_f, float eps, float offset, int stages) {
   constexpr int V = Num<T>::kVec;
   pdl_prologue();
   __shared__ float red[2][2][8];  // [parity][quantity][warp]
+  __shared__ uint64_t full[RING ? kMaxRingStages : 1];
+  __shared__ int ring_broken;
+  extern __shared__ __align__(128) unsigned char ring[];  // [stages][gy, x, (gs)][row_bytes]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t row_bytes = static_cast<uint32_t>(nvec) * kVecBytes;
+  const int nsrc = (ADD && gs != nullptr) ? 3 : 2;
+  int64_t issued = 0;  // thread 0: rows of this CTA whose copies have been issued
+  // copies of this CTA's `it`-th row into slot it % stages
+  auto issue = [&](int64_t it) {
+    const int64_t row = blockIdx.x + it * static_cast<int64_t>(gridDim.x);
+    const int slot = static_cast<int>(it % stages);
+    unsigned char* dst = ring + static_cast<size_t>(slot) * nsrc * row_bytes;
+    mbar_arrive_expect(&full[slot], nsrc * row_bytes);
+    bulk_load(dst, gy + row * ldg, row_bytes, &full[slot]);
+    bulk_load(dst + row_bytes, x + row * ldx, row_bytes, &full[slot]);
+    if (nsrc == 3) bulk_load(dst + 2 * row_bytes, gs + row * ldgs, row_bytes, &full[slot]);
+  };
+  const int64_t my_rows = blockIdx.x < rows ? (rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  if constexpr (RING) {
+    if (tid == 0) {
+      ring_broken = 0;
+      for (int k = 0; k < stages; ++k) mbar_init(&full[k], 1);
+      mbar_init_fence();
+      for (; issued < stages && issued < my_rows; ++issued) issue(issued);
+    }
+    __syncthreads();
+  }
   float accw[ITEMS][V], accb[HAS_BIAS ? ITEMS : 1][V];
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i)
@@ -301,45 +343,108 @@ rms_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ gs, const T*
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) ok[i] = tid + i * 256 < nvec;
 
+  // 16-bit types: the effective weight round_T(w + offset) of this thread's columns, packed, for all rows
+  // (with a bias gradient the second set of accumulators needs those registers, and the words are re-read per row)
+  constexpr bool KEEP_W = sizeof(T) == 2 && !HAS_BIAS;
+  uint32_t weff[KEEP_W ? ITEMS : 1][4];
+  auto weight_words = [&](int i, uint32_t (&out)[4]) {
+    if constexpr (KEEP_W) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) out[j] = weff[i][j];
+    } else {
+      const uint4 wv = ld_reuse(weight + static_cast<int64_t>(tid + i * 256) * V);
+      out[0] = wv.x, out[1] = wv.y, out[2] = wv.z, out[3] = wv.w;
+    }
+  };
+  if constexpr (KEEP_W) {
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      uint4 wv = make_uint4(0, 0, 0, 0);
+      if (ok[i]) wv = ld_reuse(weight + static_cast<int64_t>(tid + i * 256) * V);
+      const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        weff[i][j] = ww[j];
+        if constexpr (ADD) {
+          float w0, w1;
+          Num<T>::unpack2(ww[j], w0, w1);
+          weff[i][j] = Num<T>::pack2(__fadd_rn(w0, offset), __fadd_rn(w1, offset));
+        }
+      }
+    }
+  }
+
   int parity = 0;
-  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, parity ^= 1) {
+  int64_t it = 0;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, parity ^= 1, ++it) {
     uint4 xv[ITEMS], gv[ITEMS];
+    const unsigned char* slot = nullptr;  // this row in shared memory, when its copies have landed
+    if constexpr (RING) {
+      if (*static_cast<volatile int*>(&ring_broken) == 0) {
+        if (mbar_wait(&full[it % stages], static_cast<uint32_t>(it / stages) & 1u)) {
+          slot = ring + static_cast<size_t>(it % stages) * nsrc * row_bytes;
+        } else {
+          ring_broken = 1;
+        }
+      }
+    }
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
       xv[i] = gv[i] = make_uint4(0, 0, 0, 0);
       if (ok[i]) {
         const int64_t col = static_cast<int64_t>(tid + i * 256) * V;
-        xv[i] = ld_stream(x + row * ldx + col);
-        gv[i] = ld_stream(gy + row * ldg + col);
+        if (RING && slot != nullptr) {
+          gv[i] = *reinterpret_cast<const uint4*>(slot + (tid + i * 256) * kVecBytes);
+          xv[i] = *reinterpret_cast<const uint4*>(slot + row_bytes + (tid + i * 256) * kVecBytes);
+        } else {
+          xv[i] = ld_stream(x + row * ldx + col);
+          gv[i] = ld_stream(gy + row * ldg + col);
+        }
       }
     }
-    // gn = round_T(g * w) replaces g in registers (fp32 for T = float, packed otherwise)
     float sumsq = 0.f, dot = 0.f;
+    if constexpr (sizeof(T) == 2) {
+      // 16-bit types: gn = round_T(g * w) is one packed product per pair
 #pragma unroll
-    for (int i = 0; i < ITEMS; ++i) {
-      if (!ok[i]) continue;
-      const int64_t col = static_cast<int64_t>(tid + i * 256) * V;
-      float h[V], g[V], w[V];
-      Num<T>::unpack(xv[i], h);
-      Num<T>::unpack(gv[i], g);
-      Num<T>::unpack(ld_reuse(weight + col), w);
+      for (int i = 0; i < ITEMS; ++i) {
+        if (!ok[i]) continue;
+        const uint32_t wx[4] = {xv[i].x, xv[i].y, xv[i].z, xv[i].w}, wg[4] = {gv[i].x, gv[i].y, gv[i].z, gv[i].w};
+        uint32_t ww[4];
+        weight_words(i, ww);
 #pragma unroll
-      for (int j = 0; j < V; j += 2) {
-        if constexpr (ADD) {
-          w[j] = __fadd_rn(w[j], offset);
-          w[j + 1] = __fadd_rn(w[j + 1], offset);
-          Num<T>::round2(w[j], w[j + 1]);
+        for (int j = 0; j < 4; ++j) {
+          float h0, h1, gn0, gn1;
+          Num<T>::unpack2(wx[j], h0, h1);
+          Num<T>::unpack2(Num<T>::mul2(wg[j], ww[j]), gn0, gn1);
+          if constexpr (HAS_BIAS) {
+            float g0, g1;
+            Num<T>::unpack2(wg[j], g0, g1);
+            accb[i][2 * j] = __fadd_rn(accb[i][2 * j], g0);
+            accb[i][2 * j + 1] = __fadd_rn(accb[i][2 * j + 1], g1);
+          }
+          sumsq = __fmaf_rn(h0, h0, sumsq);
+          sumsq = __fmaf_rn(h1, h1, sumsq);
+          dot = __fmaf_rn(gn0, h0, dot);
+          dot = __fmaf_rn(gn1, h1, dot);
         }
-        if constexpr (HAS_BIAS) {
-          accb[i][j] = __fadd_rn(accb[i][j], g[j]);
-          accb[i][j + 1] = __fadd_rn(accb[i][j + 1], g[j + 1]);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) {
+        if (!ok[i]) continue;
+        const int64_t col = static_cast<int64_t>(tid + i * 256) * V;
+        float h[V], g[V], w[V];
+        Num<T>::unpack(xv[i], h);
+        Num<T>::unpack(gv[i], g);
+        Num<T>::unpack(ld_reuse(weight + col), w);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          if constexpr (ADD) w[j] = __fadd_rn(w[j], offset);
+          if constexpr (HAS_BIAS) accb[i][j] = __fadd_rn(accb[i][j], g[j]);
+          const float gn = __fmul_rn(g[j], w[j]);
+          sumsq = __fmaf_rn(h[j], h[j], sumsq);
+          dot = __fmaf_rn(gn, h[j], dot);
         }
-        float gn0 = __fmul_rn(g[j], w[j]), gn1 = __fmul_rn(g[j + 1], w[j + 1]);
-        Num<T>::round2(gn0, gn1);
-        sumsq = __fmaf_rn(h[j], h[j], sumsq);
-        sumsq = __fmaf_rn(h[j + 1], h[j + 1], sumsq);
-        dot = __fmaf_rn(gn0, h[j], dot);
-        dot = __fmaf_rn(gn1, h[j + 1], dot);
       }
     }
     sumsq = warp_sum(sumsq);
@@ -349,6 +454,10 @@ rms_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ gs, const T*
       red[parity][1][warp] = dot;
     }
     __syncthreads();  // the other parity's slots are free again once everyone is past this point
+    if constexpr (RING) {
+      // every thread is done with the previous row, whose ring slot can take this CTA's next unissued row
+      if (tid == 0 && it > 0 && issued < my_rows && *static_cast<volatile int*>(&ring_broken) == 0) issue(issued++);
+    }
     float tot_sq = 0.f, tot_dot = 0.f;
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
@@ -362,35 +471,50 @@ rms_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ gs, const T*
     for (int i = 0; i < ITEMS; ++i) {
       if (!ok[i]) continue;
       const int64_t col = static_cast<int64_t>(tid + i * 256) * V;
-      float h[V], g[V], w[V], out[V], extra[V];
-      Num<T>::unpack(xv[i], h);
-      Num<T>::unpack(gv[i], g);
-      Num<T>::unpack(ld_reuse(weight + col), w);
-      if (ADD && gs != nullptr) Num<T>::unpack(ld_stream(gs + row * ldgs + col), extra);
-#pragma unroll
-      for (int j = 0; j < V; j += 2) {
-        if constexpr (ADD) {
-          w[j] = __fadd_rn(w[j], offset);
-          w[j + 1] = __fadd_rn(w[j + 1], offset);
-          Num<T>::round2(w[j], w[j + 1]);
-        }
-        float gn0 = __fmul_rn(g[j], w[j]), gn1 = __fmul_rn(g[j + 1], w[j + 1]);
-        Num<T>::round2(gn0, gn1);
-        float n0 = __fmul_rn(h[j], r), n1 = __fmul_rn(h[j + 1], r);
-        Num<T>::round2(n0, n1);
-        float gw0 = __fmul_rn(g[j], n0), gw1 = __fmul_rn(g[j + 1], n1);
-        Num<T>::round2(gw0, gw1);
-        accw[i][j] = __fadd_rn(accw[i][j], gw0);
-        accw[i][j + 1] = __fadd_rn(accw[i][j + 1], gw1);
-        out[j] = __fadd_rn(__fmul_rn(gn0, r), __fmul_rn(coef, h[j]));
-        out[j + 1] = __fadd_rn(__fmul_rn(gn1, r), __fmul_rn(coef, h[j + 1]));
-        if (ADD && gs != nullptr) {
-          Num<T>::round2(out[j], out[j + 1]);
-          out[j] = __fadd_rn(out[j], extra[j]);
-          out[j + 1] = __fadd_rn(out[j + 1], extra[j + 1]);
-        }
+      uint4 extra_word = make_uint4(0, 0, 0, 0);
+      if (ADD && gs != nullptr) {
+        if (RING && slot != nullptr) extra_word = *reinterpret_cast<const uint4*>(slot + 2 * row_bytes + (tid + i * 256) * kVecBytes);
+        else extra_word = ld_stream(gs + row * ldgs + col);
       }
-      st_stream(dx + row * lddx + col, Num<T>::pack(out));
+      if constexpr (sizeof(T) == 2) {
+        // n = round_T(h * r), grad_w += round_T(g * n), grad_h = gn * r + coef * h (one fused multiply-add: the
+        // result is rounded to T, and graded against fp64 like the reference's own gradient)
+        const uint32_t wx[4] = {xv[i].x, xv[i].y, xv[i].z, xv[i].w}, wg[4] = {gv[i].x, gv[i].y, gv[i].z, gv[i].w};
+        const uint32_t we[4] = {extra_word.x, extra_word.y, extra_word.z, extra_word.w};
+        const Float2x r2 = pack_f2(r, r), coef2 = pack_f2(coef, coef);
+        uint32_t wo[4], ww[4];
+        weight_words(i, ww);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float h0, h1, gn0, gn1, gw0, gw1, o0, o1;
+          Num<T>::unpack2(wx[j], h0, h1);
+          const uint32_t n = Num<T>::pack2(__fmul_rn(h0, r), __fmul_rn(h1, r));
+          Num<T>::unpack2(Num<T>::mul2(wg[j], n), gw0, gw1);
+          accw[i][2 * j] = __fadd_rn(accw[i][2 * j], gw0);
+          accw[i][2 * j + 1] = __fadd_rn(accw[i][2 * j + 1], gw1);
+          Num<T>::unpack2(Num<T>::mul2(wg[j], ww[j]), gn0, gn1);
+          const Float2x h2 = pack_f2(h0, h1);
+          unpack_f2(fma_f2(pack_f2(gn0, gn1), r2, mul_f2(coef2, h2)), o0, o1);
+          wo[j] = Num<T>::pack2(o0, o1);
+          if (ADD && gs != nullptr) wo[j] = Num<T>::add2(wo[j], we[j]);
+        }
+        st_stream(dx + row * lddx + col, make_uint4(wo[0], wo[1], wo[2], wo[3]));
+      } else {
+        float h[V], g[V], w[V], out[V], extra[V];
+        Num<T>::unpack(xv[i], h);
+        Num<T>::unpack(gv[i], g);
+        Num<T>::unpack(ld_reuse(weight + col), w);
+        Num<T>::unpack(extra_word, extra);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          if constexpr (ADD) w[j] = __fadd_rn(w[j], offset);
+          const float gn = __fmul_rn(g[j], w[j]);
+          accw[i][j] = __fadd_rn(accw[i][j], __fmul_rn(g[j], __fmul_rn(h[j], r)));
+          out[j] = __fadd_rn(__fmul_rn(gn, r), __fmul_rn(coef, h[j]));
+          if (ADD && gs != nullptr) out[j] = __fadd_rn(out[j], extra[j]);
+        }
+        st_stream(dx + row * lddx + col, Num<T>::pack(out));
+      }
     }
   }
   const int64_t cols = static_cast<int64_t>(nvec) * V;
@@ -402,6 +526,16 @@ rms_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ gs, const T*
     for (int j = 0; j < V; ++j) {
       part_w[blockIdx.x * cols + col + j] = accw[i][j];
       if constexpr (HAS_BIAS) part_b[blockIdx.x * cols + col + j] = accb[i][j];
+    }
+  }
+  if constexpr (RING) {
+    // a broken ring may still have copies in flight into this CTA's shared memory: thread 0 stays
+    // (and with it the CTA's shared memory) until each slot's last issued copy has landed or a
+    // bounded wait has run out
+    __syncthreads();
+    if (tid == 0 && ring_broken != 0) {
+      for (int64_t k = issued > stages ? issued - stages : 0; k < issued; ++k)
+        (void)mbar_wait(&full[k % stages], static_cast<uint32_t>(k / stages) & 1u);
     }
   }
 }
@@ -476,6 +610,18 @@ rms_bwd_reduce_kernel(const float* __restrict__ part, int lines, int64_t cols, T
   out[c] = Num<T>::down(acc);
 }
 
+// Shared memory a backward CTA may use for its ring: two CTAs share an SM's 227 KB with their static buffers.
+constexpr size_t kRingBytesPerCta = 108 * 1024;
+
+// B200_BWD_RING=0 in the environment reads the rows with plain loads instead of the ring.
+bool ring_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("B200_BWD_RING");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+
 int bwd_lines(int64_t rows) {
   const int64_t cap = static_cast<int64_t>(sm_count()) * 2;
   return static_cast<int>(rows < cap ? (rows > 0 ? rows : 1) : cap);
@@ -497,9 +643,23 @@ int run_bwd(const void* gy, const void* gs, const void* x, const void* w, void* 
   T* tdx = static_cast<T*>(dx);
   if (vec) {
     const int nvec = static_cast<int>(cols / V);
-#define B200_BWD(ITEMS, BIAS)                                                                              \
-  launch(rms_bwd_rows_kernel<T, ITEMS, ADD, BIAS>, lines, 256, 0, st, tgy, tgs, tx, tw, tdx, part_w, part_b, \
-         rows, nvec, ldg, ldgs, ldx, lddx, cols_f, eps, offset)
+    // ring of bulk-copied rows: as many slots as fit twice into an SM's shared memory (two CTAs per SM), at least two
+    const size_t slot_bytes = static_cast<size_t>(gs ? 3 : 2) * nvec * kVecBytes;
+    const int stages = static_cast<int>(std::min<size_t>(kMaxRingStages, kRingBytesPerCta / slot_bytes));
+    const bool use_ring = stages >= 2 && ring_enabled();
+    const size_t ring_bytes = use_ring ? stages * slot_bytes : 0;
+#define B200_BWD_KERNEL(ITEMS, BIAS, RING)                                                                               \
+  do {                                                                                                                   \
+    auto kernel = rms_bwd_rows_kernel<T, ITEMS, ADD, BIAS, RING>;                                                        \
+    if (RING) (void)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(ring_bytes)); \
+    launch(kernel, lines, 256, ring_bytes, st, tgy, tgs, tx, tw, tdx, part_w, part_b, rows, nvec, ldg, ldgs, ldx, lddx,    \
+           cols_f, eps, offset, stages);                                                                                 \
+  } while (0)
+#define B200_BWD(ITEMS, BIAS)                     \
+  do {                                            \
+    if (use_ring) B200_BWD_KERNEL(ITEMS, BIAS, true); \
+    else B200_BWD_KERNEL(ITEMS, BIAS, false);     \
+  } while (0)
 #define B200_BWD_ITEMS(BIAS)                 \
   do {                                       \
     if (nvec <= 256) B200_BWD(1, BIAS);      \
@@ -511,6 +671,7 @@ int run_bwd(const void* gy, const void* gs, const void* x, const void* w, void* 
     else B200_BWD_ITEMS(false);
 #undef B200_BWD_ITEMS
 #undef B200_BWD
+#undef B200_BWD_KERNEL
     if (int rc = after_launch("rms_bwd_rows_kernel")) return rc;
   } else {
     launch(rms_bwd_stream_kernel<T, ADD>, lines, 256, 0, st, tgy, tgs, tx, tw, tdx, part_w, part_b, rows, cols, ldg, ldgs,
@@ -535,6 +696,9 @@ int check_common(const char* fn, int64_t rows, int64_t cols, int dtype) {
 }
 
 }  // namespace
+
+unsigned int norm_wait_timeouts() { return read_wait_timeouts(); }
+
 }  // namespace b200
 
 using namespace b200;

@@ -86,22 +86,44 @@ family_rows_kernel(const T* x, const T* gate, const T* __restrict__ weight, cons
   bool(&ok)[ITEMS] = all_ok[u];
 
   // first moment (LayerNorm) or sum of squares
+  constexpr bool HALF = sizeof(T) == 2;
   float acc = 0.f;
+  if constexpr (MODE == kLayer) {
+    Float2x acc2 = pack_f2(0.f, 0.f);  // two running sums, two elements per instruction
 #pragma unroll
-  for (int i = 0; i < ITEMS; ++i) {
-    float f[V];
-    Num<T>::unpack(data[i], f);
+    for (int i = 0; i < ITEMS; ++i) {
+      float f[V];
+      Num<T>::unpack(data[i], f);
 #pragma unroll
-    for (int j = 0; j < V; j += 2) {
-      if constexpr (MODE == kLayer) {
-        acc = __fadd_rn(acc, __fadd_rn(f[j], f[j + 1]));
-      } else if constexpr (MODE == kL2) {
-        float s0 = __fmul_rn(f[j], f[j]), s1 = __fmul_rn(f[j + 1], f[j + 1]);
-        Num<T>::round2(s0, s1);  // x.pow(2) is a tensor of dtype T
-        acc = __fadd_rn(acc, __fadd_rn(s0, s1));
+      for (int j = 0; j < V; j += 2) acc2 = add_f2(acc2, pack_f2(f[j], f[j + 1]));
+    }
+    float a0, a1;
+    unpack_f2(acc2, a0, a1);
+    acc = __fadd_rn(a0, a1);
+  } else {
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      if constexpr (MODE == kL2 && HALF) {
+        // x.pow(2) is a tensor of dtype T: packed product, one rounding per element
+        const uint32_t wx[4] = {data[i].x, data[i].y, data[i].z, data[i].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float s0, s1;
+          Num<T>::unpack2(Num<T>::mul2(wx[j], wx[j]), s0, s1);
+          acc = __fadd_rn(acc, __fadd_rn(s0, s1));
+        }
       } else {
-        acc = __fmaf_rn(f[j], f[j], acc);
-        acc = __fmaf_rn(f[j + 1], f[j + 1], acc);
+        float f[V];
+        Num<T>::unpack(data[i], f);
+#pragma unroll
+        for (int j = 0; j < V; j += 2) {
+          if constexpr (MODE == kL2) {
+            acc = __fadd_rn(acc, __fadd_rn(__fmul_rn(f[j], f[j]), __fmul_rn(f[j + 1], f[j + 1])));
+          } else {
+            acc = __fmaf_rn(f[j], f[j], acc);
+            acc = __fmaf_rn(f[j + 1], f[j + 1], acc);
+          }
+        }
       }
     }
   }
@@ -110,19 +132,22 @@ family_rows_kernel(const T* x, const T* gate, const T* __restrict__ weight, cons
   float scale, shift = 0.f;  // y_pre = x * scale + shift
   if constexpr (MODE == kLayer) {
     const float mean = __fdiv_rn(acc, cols_f);
-    float var = 0.f;
+    const Float2x neg_mean = pack_f2(-mean, -mean);
+    Float2x var2 = pack_f2(0.f, 0.f);
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
       if (!ok[i]) continue;
       float f[V];
       Num<T>::unpack(data[i], f);
 #pragma unroll
-      for (int j = 0; j < V; ++j) {
-        const float d = __fsub_rn(f[j], mean);
-        var = __fmaf_rn(d, d, var);
+      for (int j = 0; j < V; j += 2) {
+        const Float2x d = add_f2(pack_f2(f[j], f[j + 1]), neg_mean);
+        var2 = fma_f2(d, d, var2);
       }
     }
-    var = __fdiv_rn(row_sum<TPR>(var, slots[1]), cols_f);
+    float v0, v1;
+    unpack_f2(var2, v0, v1);
+    const float var = __fdiv_rn(row_sum<TPR>(__fadd_rn(v0, v1), slots[1]), cols_f);
     scale = __frcp_rn(__fsqrt_rn(__fadd_rn(fmaxf(var, 0.f), eps)));
     shift = -__fmul_rn(scale, mean);
   } else if constexpr (MODE == kL2) {
@@ -139,46 +164,65 @@ family_rows_kernel(const T* x, const T* gate, const T* __restrict__ weight, cons
   for (int i = 0; i < ITEMS; ++i) {
     if (!ok[i]) continue;
     const int64_t col = static_cast<int64_t>(lane_in_row + i * TPR) * V;
-    float f[V], w[V], b[V], g[V];
-    Num<T>::unpack(data[i], f);
-    if constexpr (MODE != kL2) Num<T>::unpack(ld_reuse(weight + col), w);
-    if (MODE != kL2 && has_bias) Num<T>::unpack(ld_reuse(bias + col), b);
-    if constexpr (GATED) Num<T>::unpack(gdata[i], g);
+    if constexpr (MODE == kLayer) {
+      // (x * scale + shift) * w + b in fp32 with two fused multiply-adds, two elements per instruction; the
+      // result is rounded to T once (F.layer_norm keeps fp32 until its output)
+      float f[V], w[V], b[V];
+      Num<T>::unpack(data[i], f);
+      Num<T>::unpack(ld_reuse(weight + col), w);
+      if (has_bias) Num<T>::unpack(ld_reuse(bias + col), b);
+      const Float2x scale2 = pack_f2(scale, scale), shift2 = pack_f2(shift, shift);
 #pragma unroll
-    for (int j = 0; j < V; j += 2) {
-      float o0, o1;
-      if constexpr (MODE == kLayer) {
-        o0 = __fmul_rn(__fadd_rn(__fmul_rn(f[j], scale), shift), w[j]);
-        o1 = __fmul_rn(__fadd_rn(__fmul_rn(f[j + 1], scale), shift), w[j + 1]);
-        if (has_bias) {
-          o0 = __fadd_rn(o0, b[j]);
-          o1 = __fadd_rn(o1, b[j + 1]);
-        }
-      } else if constexpr (MODE == kL2) {
-        o0 = __fmul_rn(f[j], scale);
-        o1 = __fmul_rn(f[j + 1], scale);
-      } else {
-        o0 = __fmul_rn(f[j], scale);
-        o1 = __fmul_rn(f[j + 1], scale);
-        Num<T>::round2(o0, o1);
-        o0 = __fmul_rn(o0, w[j]);
-        o1 = __fmul_rn(o1, w[j + 1]);
-        Num<T>::round2(o0, o1);
-        if (has_bias) {
-          o0 = __fadd_rn(o0, b[j]);
-          o1 = __fadd_rn(o1, b[j + 1]);
-          Num<T>::round2(o0, o1);
-        }
-        float a0 = gate_act<T, MODE == kGatedSwish ? 0 : 1>(g[j]);
-        float a1 = gate_act<T, MODE == kGatedSwish ? 0 : 1>(g[j + 1]);
-        Num<T>::round2(a0, a1);
-        o0 = __fmul_rn(o0, a0);
-        o1 = __fmul_rn(o1, a1);
+      for (int j = 0; j < V; j += 2) {
+        const Float2x t = fma_f2(pack_f2(f[j], f[j + 1]), scale2, shift2);
+        const Float2x o = has_bias ? fma_f2(t, pack_f2(w[j], w[j + 1]), pack_f2(b[j], b[j + 1])) : mul_f2(t, pack_f2(w[j], w[j + 1]));
+        unpack_f2(o, f[j], f[j + 1]);
       }
-      f[j] = o0;
-      f[j + 1] = o1;
+      st_stream(y + row * ldy + col, Num<T>::pack(f));
+    } else if constexpr (HALF) {
+      // 16-bit types: every product and sum of two T tensors is one packed instruction with the reference's rounding
+      const uint32_t wx[4] = {data[i].x, data[i].y, data[i].z, data[i].w};
+      uint32_t wo[4];
+      if constexpr (MODE == kL2) {
+        const uint32_t scale2 = Num<T>::pack2(scale, scale);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) wo[j] = Num<T>::mul2(wx[j], scale2);
+      } else {
+        const uint4 wv = ld_reuse(weight + col);
+        uint4 bv = make_uint4(0, 0, 0, 0);
+        if (has_bias) bv = ld_reuse(bias + col);
+        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w}, wb[4] = {bv.x, bv.y, bv.z, bv.w};
+        const uint32_t wg[4] = {gdata[i].x, gdata[i].y, gdata[i].z, gdata[i].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float h0, h1, g0, g1;
+          Num<T>::unpack2(wx[j], h0, h1);
+          Num<T>::unpack2(wg[j], g0, g1);
+          uint32_t t = Num<T>::mul2(Num<T>::pack2(__fmul_rn(h0, scale), __fmul_rn(h1, scale)), ww[j]);
+          if (has_bias) t = Num<T>::add2(t, wb[j]);
+          const uint32_t a = Num<T>::pack2(gate_act<T, MODE == kGatedSwish ? 0 : 1>(g0), gate_act<T, MODE == kGatedSwish ? 0 : 1>(g1));
+          wo[j] = Num<T>::mul2(t, a);
+        }
+      }
+      st_stream(y + row * ldy + col, make_uint4(wo[0], wo[1], wo[2], wo[3]));
+    } else {
+      float f[V], w[V], b[V], g[V];
+      Num<T>::unpack(data[i], f);
+      if constexpr (MODE != kL2) Num<T>::unpack(ld_reuse(weight + col), w);
+      if (MODE != kL2 && has_bias) Num<T>::unpack(ld_reuse(bias + col), b);
+      if constexpr (GATED) Num<T>::unpack(gdata[i], g);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        float o = __fmul_rn(f[j], scale);
+        if constexpr (MODE != kL2) {
+          o = __fmul_rn(o, w[j]);
+          if (has_bias) o = __fadd_rn(o, b[j]);
+          o = __fmul_rn(o, gate_act<T, MODE == kGatedSwish ? 0 : 1>(g[j]));
+        }
+        f[j] = o;
+      }
+      st_stream(y + row * ldy + col, Num<T>::pack(f));
     }
-    st_stream(y + row * ldy + col, Num<T>::pack(f));
   }
   }  // rows of this group
 }

@@ -8,6 +8,8 @@
 //
 // Arithmetic follows src/popcorn/kernels/rotary_embedding.py:28-40 of the
 // reference: fp32 products and sums rounded one by one, one final rounding.
+#include <algorithm>
+
 #include "common.cuh"
 #include "tma.cuh"
 
@@ -356,12 +358,27 @@ struct PairedArgs {
   int64_t seq;
   int batch;
   int head_dim;
+  // fused per-head RMS normalisation (qk_norm_rope): one weight row of head_dim per tensor
+  const void* weight[2];
+  float eps;
 };
+
+// 1 / sqrt(sum / n + eps) in separately rounded fp32 steps, like the norm kernels.
+__device__ __forceinline__ float inv_rms(float sumsq, float n, float eps) {
+  return __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(sumsq, n), eps)));
+}
 
 // One unit = a 128-bit word of the first half of a row and its partner in the second half.
 // A thread owns one (position, unit): it keeps the four table words it needs in registers and
 // walks over all heads of q and k of one batch entry, four heads in flight at a time.
-template <typename T>
+//
+// NORM fuses the per-head RMS normalisation of qk_norm_rope in front of the rotation
+// (examples/03_write_a_kernel.ipynb, cell 3): x <- round_T(round_T(x * r) * w) with
+// r = 1/sqrt(mean(x^2) + eps) in fp32.  The row's units sit in adjacent lanes (units per row is
+// a power of two <= 32 on this path), so the sum of squares is a few shuffles; lanes whose
+// position is past the end compute on the last position and store nothing, which keeps every
+// shuffle full-width.
+template <typename T, bool NORM>
 __global__ void __launch_bounds__(256) rope_paired_kernel(const PairedArgs p) {
   constexpr int V = Num<T>::kVec;
   constexpr int UNROLL = 4;
@@ -373,8 +390,13 @@ __global__ void __launch_bounds__(256) rope_paired_kernel(const PairedArgs p) {
   const int64_t tile = blockIdx.x % tiles;
   const int b = static_cast<int>(blockIdx.x / tiles);
   const int unit = threadIdx.x % upr;
-  const int64_t pos = tile * tile_pos + threadIdx.x / upr;
-  if (threadIdx.x / upr >= tile_pos || pos >= p.seq) return;
+  int64_t pos = tile * tile_pos + threadIdx.x / upr;
+  bool active = threadIdx.x / upr < tile_pos && pos < p.seq;
+  if constexpr (NORM) {
+    if (!active) pos = p.seq - 1;
+  } else {
+    if (!active) return;
+  }
 
   const T* cos = static_cast<const T*>(p.cos) + b * p.cs_stride_b + pos * p.head_dim + unit * V;
   const T* sin = static_cast<const T*>(p.sin) + b * p.cs_stride_b + pos * p.head_dim + unit * V;
@@ -396,20 +418,51 @@ __global__ void __launch_bounds__(256) rope_paired_kernel(const PairedArgs p) {
       const uint32_t wr[4] = {r.x, r.y, r.z, r.w}, ws[4] = {sn.x, sn.y, sn.z, sn.w};
       uint32_t wo[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float a0, a1, b0, b1;
-        Num<T>::unpack2(Num<T>::mul2(wx[j], wc[j]), a0, a1);          // round_T(x * cos)
-        Num<T>::unpack2(Num<T>::mul2(wr[j] ^ flip, ws[j]), b0, b1);   // round_T(rot(x) * sin)
-        wo[j] = Num<T>::pack2(__fadd_rn(a0, b0), __fadd_rn(a1, b1));
-      }
+      for (int j = 0; j < 4; ++j)  // round_T(round_T(x * cos) + round_T(rot(x) * sin)), all three packed
+        wo[j] = Num<T>::add2(Num<T>::mul2(wx[j], wc[j]), Num<T>::mul2(wr[j] ^ flip, ws[j]));
       return make_uint4(wo[0], wo[1], wo[2], wo[3]);
     }
   };
+
+  // x <- round_T(round_T(x * r) * w) on one 128-bit word
+  auto normalise = [](uint4 x, float r, uint4 w) {
+    float f[V];
+    Num<T>::unpack(x, f);
+    if constexpr (sizeof(T) == 4) {
+      float fw[V];
+      Num<T>::unpack(w, fw);
+#pragma unroll
+      for (int j = 0; j < V; ++j) f[j] = __fmul_rn(__fmul_rn(f[j], r), fw[j]);
+      return Num<T>::pack(f);
+    } else {
+      const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+      uint32_t wo[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        wo[j] = Num<T>::mul2(Num<T>::pack2(__fmul_rn(f[2 * j], r), __fmul_rn(f[2 * j + 1], r)), ww[j]);
+      return make_uint4(wo[0], wo[1], wo[2], wo[3]);
+    }
+  };
+  auto sum_squares = [](uint4 x, float acc) {
+    float f[V];
+    Num<T>::unpack(x, f);
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc = __fmaf_rn(f[j], f[j], acc);
+    return acc;
+  };
+  const float cols_f = static_cast<float>(p.head_dim);
 
   for (int ti = 0; ti < 2; ++ti) {
     const PairedTensor& t = p.t[ti];
     const T* xin = static_cast<const T*>(t.x) + b * t.xs_b + pos * t.xs_s + unit * V;
     T* xout = static_cast<T*>(t.out) + b * t.os_b + pos * t.os_s + unit * V;
+    uint4 w1 = {}, w2 = {};
+    if constexpr (NORM) {
+      if (t.heads > 0) {
+        w1 = ld_reuse(static_cast<const T*>(p.weight[ti]) + unit * V);
+        w2 = ld_reuse(static_cast<const T*>(p.weight[ti]) + unit * V + half);
+      }
+    }
     for (int h0 = 0; h0 < t.heads; h0 += UNROLL) {
       uint4 lo[UNROLL], hi[UNROLL];
 #pragma unroll
@@ -418,6 +471,19 @@ __global__ void __launch_bounds__(256) rope_paired_kernel(const PairedArgs p) {
           lo[u] = ld_stream(xin + (h0 + u) * t.xs_h);
           hi[u] = ld_stream(xin + (h0 + u) * t.xs_h + half);
         }
+      }
+      if constexpr (NORM) {
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          if (h0 + u < t.heads) {  // uniform over the CTA
+            float acc = sum_squares(hi[u], sum_squares(lo[u], 0.f));
+            for (int o = upr >> 1; o > 0; o >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, o));
+            const float r = inv_rms(acc, cols_f, p.eps);
+            lo[u] = normalise(lo[u], r, w1);
+            hi[u] = normalise(hi[u], r, w2);
+          }
+        }
+        if (!active) continue;
       }
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
@@ -457,11 +523,60 @@ __global__ void __launch_bounds__(256) rope_paired_scalar_kernel(const PairedArg
   }
 }
 
+// Fused norm + paired rope for any even head_dim and any alignment: one warp per (batch, head,
+// position) row, two passes over the row (the second one served by L1/L2).
 template <typename T>
+__global__ void __launch_bounds__(256) norm_rope_scalar_kernel(const PairedArgs p) {
+  pdl_prologue();
+  const int half = p.head_dim / 2;
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const int64_t n_warps = static_cast<int64_t>(gridDim.x) * 8;
+  const float cols_f = static_cast<float>(p.head_dim);
+  for (int ti = 0; ti < 2; ++ti) {
+    const PairedTensor& t = p.t[ti];
+    const T* weight = static_cast<const T*>(p.weight[ti]);
+    const int64_t rows = static_cast<int64_t>(p.batch) * t.heads * p.seq;
+    for (int64_t row = warp; row < rows; row += n_warps) {
+      const int64_t pos = row % p.seq;
+      const int h = static_cast<int>((row / p.seq) % t.heads);
+      const int64_t b = row / p.seq / t.heads;
+      const T* xin = static_cast<const T*>(t.x) + b * t.xs_b + h * t.xs_h + pos * t.xs_s;
+      T* xout = static_cast<T*>(t.out) + b * t.os_b + h * t.os_h + pos * t.os_s;
+      float acc = 0.f;
+      for (int j = lane; j < p.head_dim; j += 32) {
+        const float v = Num<T>::up(xin[j]);
+        acc = __fadd_rn(acc, __fmul_rn(v, v));
+      }
+      const float r = inv_rms(warp_sum(acc), cols_f, p.eps);
+      auto normed = [&](int j) {
+        return Num<T>::rt(__fmul_rn(Num<T>::rt(__fmul_rn(Num<T>::up(xin[j]), r)), Num<T>::up(weight[j])));
+      };
+      const T* cos = static_cast<const T*>(p.cos) + b * p.cs_stride_b + pos * p.head_dim;
+      const T* sin = static_cast<const T*>(p.sin) + b * p.cs_stride_b + pos * p.head_dim;
+      // out may alias x: a lane reads both partners of its channels before any lane stores them,
+      // because the loop below keeps the (j, j + half) pair in one lane
+      for (int j = lane; j < half; j += 32) {
+        const float a = normed(j), c = normed(j + half);
+        const float y1 = __fadd_rn(Num<T>::rt(__fmul_rn(a, Num<T>::up(cos[j]))), Num<T>::rt(__fmul_rn(-c, Num<T>::up(sin[j]))));
+        const float y2 = __fadd_rn(Num<T>::rt(__fmul_rn(c, Num<T>::up(cos[j + half]))), Num<T>::rt(__fmul_rn(a, Num<T>::up(sin[j + half]))));
+        xout[j] = Num<T>::down(y1);
+        xout[j + half] = Num<T>::down(y2);
+      }
+    }
+  }
+}
+
+template <typename T, bool NORM>
 int run_paired(const PairedArgs& p, cudaStream_t st) {
   constexpr int V = Num<T>::kVec;
   const int half = p.head_dim / 2;
   bool vec = half % V == 0 && half / V <= 256 && aligned(p.cos, 16) && aligned(p.sin, 16) && p.cs_stride_b % V == 0;
+  if (NORM) {
+    const int upr = half / V;
+    vec = vec && upr <= 32 && (upr & (upr - 1)) == 0 && upr > 0;
+    for (int i = 0; i < 2; ++i) vec = vec && (p.t[i].heads == 0 || aligned(p.weight[i], 16));
+  }
   for (int i = 0; i < 2; ++i) {
     const PairedTensor& t = p.t[i];
     if (t.heads == 0) continue;
@@ -472,11 +587,163 @@ int run_paired(const PairedArgs& p, cudaStream_t st) {
     const int tile_pos = 256 / (half / V);
     const int64_t grid = ceil_div(p.seq, tile_pos) * p.batch;
     if (grid > 0x7fffffffLL) return fail(B200_ERR_SHAPE, "b200_rope_paired: problem too large for one launch");
-    launch(rope_paired_kernel<T>, static_cast<unsigned>(grid), 256, 0, st, p);
+    launch(rope_paired_kernel<T, NORM>, static_cast<unsigned>(grid), 256, 0, st, p);
     return after_launch("rope_paired_kernel");
+  }
+  if (NORM) {
+    int64_t rows = 0;
+    for (int i = 0; i < 2; ++i) rows += static_cast<int64_t>(p.batch) * p.t[i].heads * p.seq;
+    const int64_t grid = std::min<int64_t>(ceil_div(rows, 8), static_cast<int64_t>(sm_count()) * 16);
+    launch(norm_rope_scalar_kernel<T>, static_cast<unsigned>(grid), 256, 0, st, p);
+    return after_launch("norm_rope_scalar_kernel");
   }
   launch(rope_paired_scalar_kernel<T>, static_cast<unsigned>(sm_count()) * 8, 256, 0, st, p);
   return after_launch("rope_paired_scalar_kernel");
+}
+
+
+// ------------------------------------------------------------ llama4 rope --
+//
+// llama4_rope(q, k, freqs) of the reference (src/popcorn/kernels/llama4_rope.py:14-39): layout
+// (batch, seq, heads, head_dim), channels taken as (real, imaginary) pairs, freqs
+// [seq, head_dim/2, 2] = (cos, sin) per pair in the dtype of q, arithmetic tensor by tensor in
+// that dtype:
+//   y_re = round_T(round_T(re * f_re) - round_T(im * f_im))
+//   y_im = round_T(round_T(re * f_im) + round_T(im * f_re))
+struct Llama4Tensor {
+  const void* x;
+  void* out;
+  int64_t xs_b, xs_s, xs_h;
+  int64_t os_b, os_s, os_h;
+  int heads;
+};
+struct Llama4Args {
+  Llama4Tensor t[2];
+  const void* freqs;
+  int64_t seq;
+  int batch;
+  int head_dim;
+};
+
+// A 128-bit word of x lines up with the 128-bit word of the freqs row at the same offset (both
+// hold whole pairs).  A thread owns one (position, word): the freqs word stays in registers
+// while it walks over the batch entries of its CTA and all heads of q and k.
+template <typename T>
+__global__ void __launch_bounds__(256) llama4_rope_kernel(const Llama4Args p, const int batch_per_cta) {
+  constexpr int V = Num<T>::kVec;
+  constexpr int UNROLL = 8;
+  pdl_prologue();
+  const int wpr = p.head_dim / V;  // words per row
+  const int tile_pos = 256 / wpr;
+  const int64_t tiles = (p.seq + tile_pos - 1) / tile_pos;
+  const int64_t tile = blockIdx.x % tiles;
+  const int b0 = static_cast<int>(blockIdx.x / tiles) * batch_per_cta;
+  const int word = threadIdx.x % wpr;
+  const int64_t pos = tile * tile_pos + threadIdx.x / wpr;
+  if (threadIdx.x / wpr >= tile_pos || pos >= p.seq) return;
+
+  const uint4 f = ld_reuse(static_cast<const T*>(p.freqs) + pos * p.head_dim + word * V);
+  // 16-bit types: (-f_im, f_re) per pair, so that the whole rotation is two packed products and one packed sum
+  //   (re, re) * (f_re, f_im) + (im, im) * (-f_im, f_re) = (re*f_re - im*f_im, re*f_im + im*f_re)
+  // (negating an operand negates the rounded product exactly)
+  uint32_t fs[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) fs[j] = __byte_perm(fs[j], 0, 0x1032) ^ 0x00008000u;
+
+  auto rotate = [&f, &fs](uint4 x) {
+    if constexpr (sizeof(T) == 4) {
+      float v[4], w[4];
+      Num<T>::unpack(x, v);
+      Num<T>::unpack(f, w);
+      float o[4];
+#pragma unroll
+      for (int j = 0; j < 4; j += 2) {
+        o[j] = __fsub_rn(__fmul_rn(v[j], w[j]), __fmul_rn(v[j + 1], w[j + 1]));
+        o[j + 1] = __fadd_rn(__fmul_rn(v[j], w[j + 1]), __fmul_rn(v[j + 1], w[j]));
+      }
+      return Num<T>::pack(o);
+    } else {
+      const uint32_t wx[4] = {x.x, x.y, x.z, x.w}, wf[4] = {f.x, f.y, f.z, f.w};
+      uint32_t wo[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        wo[j] = Num<T>::add2(Num<T>::mul2(__byte_perm(wx[j], 0, 0x1010), wf[j]), Num<T>::mul2(__byte_perm(wx[j], 0, 0x3232), fs[j]));
+      return make_uint4(wo[0], wo[1], wo[2], wo[3]);
+    }
+  };
+
+  const int b1 = min(b0 + batch_per_cta, p.batch);
+  for (int b = b0; b < b1; ++b) {
+    for (int ti = 0; ti < 2; ++ti) {
+      const Llama4Tensor& t = p.t[ti];
+      const T* xin = static_cast<const T*>(t.x) + b * t.xs_b + pos * t.xs_s + word * V;
+      T* xout = static_cast<T*>(t.out) + b * t.os_b + pos * t.os_s + word * V;
+      for (int h0 = 0; h0 < t.heads; h0 += UNROLL) {
+        uint4 v[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u)
+          if (h0 + u < t.heads) v[u] = ld_stream(xin + (h0 + u) * t.xs_h);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u)
+          if (h0 + u < t.heads) st_stream(xout + (h0 + u) * t.os_h, rotate(v[u]));
+      }
+    }
+  }
+}
+
+// Any even head_dim, any alignment: one thread per pair.
+template <typename T>
+__global__ void __launch_bounds__(256) llama4_rope_scalar_kernel(const Llama4Args p) {
+  pdl_prologue();
+  const int half = p.head_dim / 2;
+  for (int ti = 0; ti < 2; ++ti) {
+    const Llama4Tensor& t = p.t[ti];
+    const int64_t total = static_cast<int64_t>(p.batch) * p.seq * t.heads * half;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+      const int j = static_cast<int>(i % half);
+      int64_t r = i / half;
+      const int h = static_cast<int>(r % t.heads);
+      r /= t.heads;
+      const int64_t pos = r % p.seq;
+      const int64_t b = r / p.seq;
+      const T* xin = static_cast<const T*>(t.x) + b * t.xs_b + pos * t.xs_s + h * t.xs_h + 2 * j;
+      T* xout = static_cast<T*>(t.out) + b * t.os_b + pos * t.os_s + h * t.os_h + 2 * j;
+      const T* fr = static_cast<const T*>(p.freqs) + pos * p.head_dim + 2 * j;
+      const float re = Num<T>::up(xin[0]), im = Num<T>::up(xin[1]);
+      const float f_re = Num<T>::up(fr[0]), f_im = Num<T>::up(fr[1]);
+      const float y_re = __fsub_rn(Num<T>::rt(__fmul_rn(re, f_re)), Num<T>::rt(__fmul_rn(im, f_im)));
+      const float y_im = __fadd_rn(Num<T>::rt(__fmul_rn(re, f_im)), Num<T>::rt(__fmul_rn(im, f_re)));
+      xout[0] = Num<T>::down(y_re);
+      xout[1] = Num<T>::down(y_im);
+    }
+  }
+}
+
+template <typename T>
+int run_llama4(const Llama4Args& p, cudaStream_t st) {
+  constexpr int V = Num<T>::kVec;
+  bool vec = p.head_dim % V == 0 && p.head_dim / V <= 256 && aligned(p.freqs, 16);
+  for (int i = 0; i < 2; ++i) {
+    const Llama4Tensor& t = p.t[i];
+    if (t.heads == 0) continue;
+    vec = vec && aligned(t.x, 16) && aligned(t.out, 16) && t.xs_b % V == 0 && t.xs_s % V == 0 && t.xs_h % V == 0 &&
+          t.os_b % V == 0 && t.os_s % V == 0 && t.os_h % V == 0;
+  }
+  if (vec) {
+    const int tile_pos = 256 / (p.head_dim / V);
+    const int64_t tiles = ceil_div(p.seq, tile_pos);
+    // one CTA per (tile, batch entry) unless that is far more CTAs than the machine needs
+    const int64_t want = static_cast<int64_t>(sm_count()) * 32;
+    int per_cta = 1;
+    while (tiles * ceil_div(p.batch, per_cta) > want && per_cta < p.batch) per_cta *= 2;
+    const int64_t grid = tiles * ceil_div(p.batch, per_cta);
+    if (grid > 0x7fffffffLL) return fail(B200_ERR_SHAPE, "b200_llama4_rope: problem too large for one launch");
+    launch(llama4_rope_kernel<T>, static_cast<unsigned>(grid), 256, 0, st, p, per_cta);
+    return after_launch("llama4_rope_kernel");
+  }
+  launch(llama4_rope_scalar_kernel<T>, static_cast<unsigned>(sm_count()) * 8, 256, 0, st, p);
+  return after_launch("llama4_rope_scalar_kernel");
 }
 
 template <typename T>
@@ -573,6 +840,55 @@ extern "C" int b200_rope_qk(void* q, void* k, const void* cos, const void* sin,
   return B200_OK;
 }
 
+namespace {
+
+int paired_common(const char* fn, bool norm, const void* q, const void* k, const void* q_weight, const void* k_weight,
+                  const void* cos, const void* sin, void* q_out, void* k_out,
+                  int64_t batch, int64_t q_heads, int64_t k_heads, int64_t seq, int64_t head_dim, int64_t cos_batch,
+                  const int64_t (&qs)[3], const int64_t (&ks)[3], const int64_t (&qos)[3], const int64_t (&kos)[3],
+                  float eps, int dtype, void* stream) {
+  if (!dtype_ok(dtype)) return fail(B200_ERR_DTYPE, "%s: unsupported dtype %d", fn, dtype);
+  if (batch < 0 || q_heads < 0 || k_heads < 0 || seq < 0 || head_dim < 0) return fail(B200_ERR_SHAPE, "%s: negative size", fn);
+  if (head_dim % 2 != 0) return fail(B200_ERR_SHAPE, "%s: head_dim=%lld must be even", fn, (long long)head_dim);
+  if (cos_batch != 1 && cos_batch != batch) return fail(B200_ERR_SHAPE, "%s: cos_batch must be 1 or batch", fn);
+  if (batch > 0x7fffffffLL || q_heads > (1 << 20) || k_heads > (1 << 20) || head_dim > (1 << 20))
+    return fail(B200_ERR_SHAPE, "%s: size out of range", fn);
+  if (batch == 0 || seq == 0 || head_dim == 0 || (q_heads == 0 && k_heads == 0)) return B200_OK;
+  const size_t es = dtype_size(dtype);
+  if (q_heads > 0) {
+    if (q == nullptr || q_out == nullptr || (norm && q_weight == nullptr)) return fail(B200_ERR_NULL_POINTER, "%s: q, q_out or q_weight is NULL", fn);
+  }
+  if (k_heads > 0) {
+    if (k == nullptr || k_out == nullptr || (norm && k_weight == nullptr)) return fail(B200_ERR_NULL_POINTER, "%s: k, k_out or k_weight is NULL", fn);
+  }
+  if (cos == nullptr || sin == nullptr) return fail(B200_ERR_NULL_POINTER, "%s: cos or sin is NULL", fn);
+  if (!aligned(q, es) || !aligned(k, es) || !aligned(q_out, es) || !aligned(k_out, es) || !aligned(cos, es) || !aligned(sin, es) ||
+      !aligned(q_weight, es) || !aligned(k_weight, es))
+    return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to the element size", fn);
+  if (int rc = check_device()) return rc;
+  PairedArgs p{};
+  p.t[0] = PairedTensor{q, q_out, qs[0], qs[1], qs[2], qos[0], qos[1], qos[2], static_cast<int>(q_heads)};
+  p.t[1] = PairedTensor{k, k_out, ks[0], ks[1], ks[2], kos[0], kos[1], kos[2], static_cast<int>(k_heads)};
+  p.cos = cos;
+  p.sin = sin;
+  p.cs_stride_b = cos_batch == 1 ? 0 : seq * head_dim;
+  p.seq = seq;
+  p.batch = static_cast<int>(batch);
+  p.head_dim = static_cast<int>(head_dim);
+  p.weight[0] = q_weight;
+  p.weight[1] = k_weight;
+  p.eps = eps;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (norm) {
+    B200_DISPATCH_DTYPE(dtype, T, return (run_paired<T, true>(p, st)));
+  } else {
+    B200_DISPATCH_DTYPE(dtype, T, return (run_paired<T, false>(p, st)));
+  }
+  return B200_OK;
+}
+
+}  // namespace
+
 extern "C" int b200_rope_paired(const void* q, const void* k, const void* cos, const void* sin, void* q_out, void* k_out,
                                 int64_t batch, int64_t q_heads, int64_t k_heads, int64_t seq, int64_t head_dim, int64_t cos_batch,
                                 int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
@@ -580,10 +896,36 @@ extern "C" int b200_rope_paired(const void* q, const void* k, const void* cos, c
                                 int64_t qo_stride_b, int64_t qo_stride_h, int64_t qo_stride_s,
                                 int64_t ko_stride_b, int64_t ko_stride_h, int64_t ko_stride_s,
                                 int dtype, void* stream) {
+  const int64_t qs[3] = {q_stride_b, q_stride_h, q_stride_s}, ks[3] = {k_stride_b, k_stride_h, k_stride_s};
+  const int64_t qos[3] = {qo_stride_b, qo_stride_h, qo_stride_s}, kos[3] = {ko_stride_b, ko_stride_h, ko_stride_s};
+  return paired_common(__func__, false, q, k, nullptr, nullptr, cos, sin, q_out, k_out, batch, q_heads, k_heads, seq, head_dim,
+                       cos_batch, qs, ks, qos, kos, 0.f, dtype, stream);
+}
+
+extern "C" int b200_qk_norm_rope(const void* q, const void* k, const void* q_weight, const void* k_weight,
+                                 const void* cos, const void* sin, void* q_out, void* k_out,
+                                 int64_t batch, int64_t q_heads, int64_t k_heads, int64_t seq, int64_t head_dim, int64_t cos_batch,
+                                 int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                                 int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+                                 int64_t qo_stride_b, int64_t qo_stride_h, int64_t qo_stride_s,
+                                 int64_t ko_stride_b, int64_t ko_stride_h, int64_t ko_stride_s,
+                                 double eps, int dtype, void* stream) {
+  const int64_t qs[3] = {q_stride_b, q_stride_h, q_stride_s}, ks[3] = {k_stride_b, k_stride_h, k_stride_s};
+  const int64_t qos[3] = {qo_stride_b, qo_stride_h, qo_stride_s}, kos[3] = {ko_stride_b, ko_stride_h, ko_stride_s};
+  return paired_common(__func__, true, q, k, q_weight, k_weight, cos, sin, q_out, k_out, batch, q_heads, k_heads, seq, head_dim,
+                       cos_batch, qs, ks, qos, kos, static_cast<float>(eps), dtype, stream);
+}
+
+extern "C" int b200_llama4_rope(const void* q, const void* k, const void* freqs, void* q_out, void* k_out,
+                                int64_t batch, int64_t seq, int64_t q_heads, int64_t k_heads, int64_t head_dim,
+                                int64_t q_stride_b, int64_t q_stride_s, int64_t q_stride_h,
+                                int64_t k_stride_b, int64_t k_stride_s, int64_t k_stride_h,
+                                int64_t qo_stride_b, int64_t qo_stride_s, int64_t qo_stride_h,
+                                int64_t ko_stride_b, int64_t ko_stride_s, int64_t ko_stride_h,
+                                int dtype, void* stream) {
   if (!dtype_ok(dtype)) return fail(B200_ERR_DTYPE, "%s: unsupported dtype %d", __func__, dtype);
   if (batch < 0 || q_heads < 0 || k_heads < 0 || seq < 0 || head_dim < 0) return fail(B200_ERR_SHAPE, "%s: negative size", __func__);
   if (head_dim % 2 != 0) return fail(B200_ERR_SHAPE, "%s: head_dim=%lld must be even", __func__, (long long)head_dim);
-  if (cos_batch != 1 && cos_batch != batch) return fail(B200_ERR_SHAPE, "%s: cos_batch must be 1 or batch", __func__);
   if (batch > 0x7fffffffLL || q_heads > (1 << 20) || k_heads > (1 << 20) || head_dim > (1 << 20))
     return fail(B200_ERR_SHAPE, "%s: size out of range", __func__);
   if (batch == 0 || seq == 0 || head_dim == 0 || (q_heads == 0 && k_heads == 0)) return B200_OK;
@@ -595,22 +937,19 @@ extern "C" int b200_rope_paired(const void* q, const void* k, const void* cos, c
     B200_REQUIRE_PTR(k);
     B200_REQUIRE_PTR(k_out);
   }
-  B200_REQUIRE_PTR(cos);
-  B200_REQUIRE_PTR(sin);
+  B200_REQUIRE_PTR(freqs);
   const size_t es = dtype_size(dtype);
-  if (!aligned(q, es) || !aligned(k, es) || !aligned(q_out, es) || !aligned(k_out, es) || !aligned(cos, es) || !aligned(sin, es))
+  if (!aligned(q, es) || !aligned(k, es) || !aligned(q_out, es) || !aligned(k_out, es) || !aligned(freqs, es))
     return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to the element size", __func__);
   if (int rc = check_device()) return rc;
-  PairedArgs p{};
-  p.t[0] = PairedTensor{q, q_out, q_stride_b, q_stride_h, q_stride_s, qo_stride_b, qo_stride_h, qo_stride_s, static_cast<int>(q_heads)};
-  p.t[1] = PairedTensor{k, k_out, k_stride_b, k_stride_h, k_stride_s, ko_stride_b, ko_stride_h, ko_stride_s, static_cast<int>(k_heads)};
-  p.cos = cos;
-  p.sin = sin;
-  p.cs_stride_b = cos_batch == 1 ? 0 : seq * head_dim;
+  Llama4Args p{};
+  p.t[0] = Llama4Tensor{q, q_out, q_stride_b, q_stride_s, q_stride_h, qo_stride_b, qo_stride_s, qo_stride_h, static_cast<int>(q_heads)};
+  p.t[1] = Llama4Tensor{k, k_out, k_stride_b, k_stride_s, k_stride_h, ko_stride_b, ko_stride_s, ko_stride_h, static_cast<int>(k_heads)};
+  p.freqs = freqs;
   p.seq = seq;
   p.batch = static_cast<int>(batch);
   p.head_dim = static_cast<int>(head_dim);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  B200_DISPATCH_DTYPE(dtype, T, return run_paired<T>(p, st));
+  B200_DISPATCH_DTYPE(dtype, T, return run_llama4<T>(p, st));
   return B200_OK;
 }

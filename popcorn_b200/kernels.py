@@ -2,7 +2,8 @@
 
 The existing popcorn ops keep popcorn's names, parameter order and defaults
 (src/popcorn/kernels/rms_norm.py:16-21, add_rms_norm.py:8-14,
-rotary_embedding.py:15-20, rope.py:24-29, swiglu.py:10); the MoE steps are new ops because
+rotary_embedding.py:15-20, rope.py:24-29, llama4_rope.py:27-31, swiglu.py:10; qk_norm_rope is the
+fused op of examples/03_write_a_kernel.ipynb); the MoE steps are new ops because
 popcorn only has them fused inside `momoe` (src/popcorn/kernels/momoe.py:47-53).
 The declaration bodies are never executed: an op here is its signature plus the
 backends registered on it.
@@ -33,6 +34,16 @@ def rotary_embedding(x, cos, sin, interleaved=False):
 @register_kernel
 def rope(q, k, cos, sin):
     """Paired Llama-style rotary embedding of queries and keys, layout (batch, heads, seq, head_dim)."""
+
+
+@register_kernel
+def qk_norm_rope(q, k, q_weight, k_weight, cos, sin, eps=1e-6):
+    """Per-head RMS normalization of queries and keys followed by the paired rotary embedding."""
+
+
+@register_kernel
+def llama4_rope(q, k, freqs):
+    """Paired Llama 4 rotary embedding, frequencies as (cos, sin) pairs; layout (batch, seq, heads, head_dim)."""
 
 
 @register_kernel
@@ -76,7 +87,7 @@ def moe_unpermute(rows, weights, pos):
 
 
 # ops with backward kernels are registered in their differentiable form
-for _op in (rope, geglu, rms_norm_gated, l2_norm, layer_norm, moe_route, moe_permute, moe_unpermute):
+for _op in (rope, qk_norm_rope, llama4_rope, geglu, rms_norm_gated, l2_norm, layer_norm, moe_route, moe_permute, moe_unpermute):
     _op.register(BACKEND, source=f"popcorn_b200.ops.{_op.name}", forward_only=True)
 for _op in (rms_norm, add_rms_norm, rotary_embedding, swiglu):
     _op.register(BACKEND, source=f"popcorn_b200.autograd.{_op.name}")

@@ -278,6 +278,72 @@ def rope(q: Tensor, k: Tensor, cos: Tensor, sin: Tensor) -> tuple[Tensor, Tensor
     return q_out, k_out
 
 
+def qk_norm_rope(q: Tensor, k: Tensor, q_weight: Tensor, k_weight: Tensor, cos: Tensor, sin: Tensor, eps: float = 1e-6) -> tuple[Tensor, Tensor]:
+    """Per-head RMSNorm of q and k, then the paired rotary embedding, in one launch.
+
+    The fused op of the reference's kernel-writing notebook (examples/03_write_a_kernel.ipynb, cell 3),
+    equal to rope(rms_norm(q, q_weight), rms_norm(k, k_weight), cos, sin); layout (batch, heads, seq, head_dim).
+    """
+    device = _require_cuda(q, k, q_weight, k_weight, cos, sin)
+    _forbid_grad(q, k, q_weight, k_weight)
+    code = _dtype_code(q, "qk_norm_rope")
+    if q.dim() != 4 or k.dim() != 4 or q.shape[0] != k.shape[0] or q.shape[2:] != k.shape[2:]:
+        raise ValueError("qk_norm_rope: q and k must be [batch, heads, seq, head_dim] and agree in batch, seq and head_dim")
+    batch, q_heads, seq, head_dim = q.shape
+    if cos.shape != sin.shape or cos.dim() != 3 or cos.shape[1:] != (seq, head_dim) or cos.shape[0] not in (1, batch):
+        raise ValueError("qk_norm_rope: cos and sin must be [1 or batch, seq, head_dim]")
+    if q_weight.shape != (head_dim,) or k_weight.shape != (head_dim,):
+        raise ValueError("qk_norm_rope: q_weight and k_weight must be [head_dim]")
+    if not (k.dtype == cos.dtype == sin.dtype == q_weight.dtype == k_weight.dtype == q.dtype):
+        raise TypeError("qk_norm_rope: all tensors must share a dtype")
+    if head_dim % 2:
+        raise ValueError("qk_norm_rope: head_dim must be even")
+    q = q if head_dim <= 1 or q.stride(-1) == 1 else q.contiguous()
+    k = k if head_dim <= 1 or k.stride(-1) == 1 else k.contiguous()
+    q_out = torch.empty(q.shape, dtype=q.dtype, device=device)
+    k_out = torch.empty(k.shape, dtype=k.dtype, device=device)
+    with torch.cuda.device(device):
+        _lib.call(
+            "b200_qk_norm_rope", _ptr(q), _ptr(k), _ptr(q_weight.contiguous()), _ptr(k_weight.contiguous()),
+            _ptr(cos.contiguous()), _ptr(sin.contiguous()), _ptr(q_out), _ptr(k_out),
+            batch, q_heads, k.shape[1], seq, head_dim, cos.shape[0],
+            q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+            q_out.stride(0), q_out.stride(1), q_out.stride(2), k_out.stride(0), k_out.stride(1), k_out.stride(2),
+            float(eps), code, _stream(device),
+        )
+    return q_out, k_out
+
+
+def llama4_rope(q: Tensor, k: Tensor, freqs: Tensor) -> tuple[Tensor, Tensor]:
+    """Llama 4 rotary embedding of q and k, layout (batch, seq, heads, head_dim), freqs [seq, head_dim/2, 2]
+    as (cos, sin) pairs (llama4_rope.py:27-39)."""
+    device = _require_cuda(q, k, freqs)
+    _forbid_grad(q, k)
+    code = _dtype_code(q, "llama4_rope")
+    if q.dim() != 4 or k.dim() != 4 or q.shape[:2] != k.shape[:2] or q.shape[3] != k.shape[3]:
+        raise ValueError("llama4_rope: q and k must be [batch, seq, heads, head_dim] and agree in batch, seq and head_dim")
+    batch, seq, q_heads, head_dim = q.shape
+    if head_dim % 2:
+        raise ValueError("llama4_rope: head_dim must be even")
+    if freqs.shape != (seq, head_dim // 2, 2):
+        raise ValueError("llama4_rope: freqs must be [seq, head_dim/2, 2]")
+    if not (k.dtype == freqs.dtype == q.dtype):
+        raise TypeError("llama4_rope: q, k and freqs must share a dtype")
+    q = q if head_dim <= 1 or q.stride(-1) == 1 else q.contiguous()
+    k = k if head_dim <= 1 or k.stride(-1) == 1 else k.contiguous()
+    q_out = torch.empty(q.shape, dtype=q.dtype, device=device)
+    k_out = torch.empty(k.shape, dtype=k.dtype, device=device)
+    with torch.cuda.device(device):
+        _lib.call(
+            "b200_llama4_rope", _ptr(q), _ptr(k), _ptr(freqs.contiguous()), _ptr(q_out), _ptr(k_out),
+            batch, seq, q_heads, k.shape[2], head_dim,
+            q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+            q_out.stride(0), q_out.stride(1), q_out.stride(2), k_out.stride(0), k_out.stride(1), k_out.stride(2),
+            code, _stream(device),
+        )
+    return q_out, k_out
+
+
 def swiglu(a: Tensor, b: Tensor) -> Tensor:
     """silu(a) * b (swiglu.py:10-18); a and b may be strided column halves of one buffer."""
     device = _require_cuda(a, b)

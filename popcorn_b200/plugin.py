@@ -4,7 +4,7 @@
     popcorn_b200.plugin.register()            # needs `popcorn` importable
     popcorn.KERNELS["rms_norm"](x, w, backend="b200")
 
-For the nine ops popcorn already defines, this is one `op.register(name,
+For the ten ops popcorn already defines, this is one `op.register(name,
 source=..., forward_only=True)` line each, the same form popcorn's own backends
 use (src/popcorn/kernels/rms_norm.py:33-59, add_rms_norm.py:26-28,
 rotary_embedding.py:43-45, rope.py:39, swiglu.py:21-31).  The sources are bare: each
@@ -27,8 +27,8 @@ import torch
 from torch import Tensor
 
 BACKEND = "b200"
-EXISTING_OPS = ("rms_norm", "add_rms_norm", "rotary_embedding", "rope", "swiglu", "geglu", "rms_norm_gated", "l2_norm", "layer_norm")
-NEW_OPS = ("moe_route", "moe_permute", "moe_unpermute")
+EXISTING_OPS = ("rms_norm", "add_rms_norm", "rotary_embedding", "rope", "llama4_rope", "swiglu", "geglu", "rms_norm_gated", "l2_norm", "layer_norm")
+NEW_OPS = ("moe_route", "moe_permute", "moe_unpermute", "qk_norm_rope")
 DIFFERENTIABLE_OPS = ("rms_norm", "add_rms_norm", "swiglu", "rotary_embedding")
 
 _SUPPORTED = (torch.float32, torch.float16, torch.bfloat16)
@@ -94,14 +94,50 @@ def _define_moe_ops(popcorn: Any) -> None:
         return torch.einsum("tkd,tk->td", picked, weights.to(picked.dtype)).to(rows.dtype)
 
 
+def _define_qk_norm_rope(popcorn: Any) -> None:
+    """The fused op popcorn's kernel-writing notebook builds (examples/03_write_a_kernel.ipynb) but does not ship."""
+    from jaxtyping import Float
+
+    from popcorn.kernels._utils import rms
+
+    register_kernel, Tag = popcorn.register_kernel, popcorn.Tag
+    paired_rope = popcorn.KERNELS["rope"].reference
+
+    def repeated_halves(f):
+        return lambda t: f(t).chunk(2, -1)[0].repeat(1, 1, 2)
+
+    @register_kernel(
+        test_args={"eps": [1e-6]},
+        test_inputs={"cos": repeated_halves(torch.cos), "sin": repeated_halves(torch.sin)},
+        tags={Tag.NORMALIZATION, Tag.POSITIONAL, Tag.FUSED},
+    )
+    def qk_norm_rope(
+        q: Float[Tensor, "batch q_heads seq head_dim"],
+        k: Float[Tensor, "batch kv_heads seq head_dim"],
+        q_weight: Float[Tensor, "head_dim"],
+        k_weight: Float[Tensor, "head_dim"],
+        cos: Float[Tensor, "cos_batch seq head_dim"],
+        sin: Float[Tensor, "cos_batch seq head_dim"],
+        eps: float = 1e-6,
+    ) -> tuple[Float[Tensor, "batch q_heads seq head_dim"], Float[Tensor, "batch kv_heads seq head_dim"]]:
+        r"""RMS normalization of every query and key head, then the paired rotary embedding.
+
+        $$y = \hat{x} \odot \cos_t + \mathrm{rot}_{1/2}(\hat{x}) \odot \sin_t, \qquad
+          \hat{x} = \frac{x}{\sqrt{\overline{x^2} + \varepsilon}} \odot w$$
+        """
+        return paired_rope(rms(q, eps) * q_weight, rms(k, eps) * k_weight, cos, sin)
+
+
 def register(backend: str = BACKEND) -> list[str]:
     """Register the b200 backend on popcorn's ops; returns the names of the ops it now serves."""
     import popcorn
     import popcorn.kernels  # noqa: F401  (fills popcorn.KERNELS)
 
     served = []
-    if not all(name in popcorn.KERNELS for name in NEW_OPS):
+    if not all(name in popcorn.KERNELS for name in NEW_OPS[:3]):
         _define_moe_ops(popcorn)
+    if "qk_norm_rope" not in popcorn.KERNELS:
+        _define_qk_norm_rope(popcorn)
     for name in (*EXISTING_OPS, *NEW_OPS):
         op = popcorn.KERNELS[name]
         if backend not in op.available_backends():

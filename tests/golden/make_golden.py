@@ -118,6 +118,65 @@ def paired_rope_cases() -> None:
         save_case(name, {"q": q, "k": k, "cos": cos, "sin": sin, "yq": yq, "yk": yk}, {"op": "rope"})
 
 
+def notebook_qk_norm_rope():
+    """The reference of the fused op the kernel-writing notebook defines (examples/03_write_a_kernel.ipynb,
+    the code cell that registers `qk_norm_rope`), executed from the notebook as it stands."""
+    import json
+
+    import popcorn
+
+    notebook = Path(popcorn.__file__).resolve().parents[2] / "examples" / "03_write_a_kernel.ipynb"
+    cells = json.loads(notebook.read_text())["cells"]
+    source = next("".join(c["source"]) for c in cells if c["cell_type"] == "code" and "def qk_norm_rope(" in "".join(c["source"]))
+    from jaxtyping import Float
+    from popcorn import Tag, register_kernel
+    from popcorn.kernels._utils import rms
+
+    scope = {"torch": torch, "Tensor": torch.Tensor, "Float": Float, "KERNELS": KERNELS, "Tag": Tag,
+             "register_kernel": register_kernel, "rms": rms}
+    exec(compile(source, str(notebook), "exec", dont_inherit=True), scope)
+    return scope["qk_norm_rope"].reference
+
+
+def qk_norm_rope_cases() -> None:
+    ref = notebook_qk_norm_rope()
+    for name, seed, batch, hq, hk, seq, dim, dtype, cos_batch, eps in [
+        ("qknormrope_bf16_2x4x2x16x128", 60, 2, 4, 2, 16, 128, BF16, 1, 1e-6),
+        ("qknormrope_bf16_2x8x2x8x64_cb2", 61, 2, 8, 2, 8, 64, BF16, 2, 1e-5),
+        ("qknormrope_f32_1x2x1x8x16", 62, 1, 2, 1, 8, 16, F32, 1, 1e-6),
+        ("qknormrope_f16_2x3x1x5x20", 63, 2, 3, 1, 5, 20, F16, 1, 1e-6),
+    ]:
+        gen = torch.Generator().manual_seed(seed)
+        q = randn(gen, batch, hq, seq, dim).to(dtype)
+        k = randn(gen, batch, hk, seq, dim).to(dtype)
+        q_weight = randn(gen, dim).to(dtype)
+        k_weight = randn(gen, dim).to(dtype)
+        # the notebook's test tables: first half repeated, like a real rope cache (cell 3, `_table`)
+        cos = torch.cos(randn(gen, cos_batch, seq, dim)).chunk(2, -1)[0].repeat(1, 1, 2).to(dtype)
+        sin = torch.sin(randn(gen, cos_batch, seq, dim)).chunk(2, -1)[0].repeat(1, 1, 2).to(dtype)
+        yq, yk = ref(q, k, q_weight, k_weight, cos, sin, eps)
+        save_case(name, {"q": q, "k": k, "q_weight": q_weight, "k_weight": k_weight, "cos": cos, "sin": sin, "yq": yq, "yk": yk},
+                  {"op": "qk_norm_rope", "eps": eps})
+
+
+def llama4_rope_cases() -> None:
+    ref = KERNELS["llama4_rope"].reference
+    for name, seed, batch, seq, hq, hk, dim, dtype in [
+        ("llama4rope_bf16_2x16x4x2x64", 70, 2, 16, 4, 2, 64, BF16),
+        ("llama4rope_bf16_1x8x8x2x128", 71, 1, 8, 8, 2, 128, BF16),
+        ("llama4rope_f32_2x8x2x1x16", 72, 2, 8, 2, 1, 16, F32),
+        ("llama4rope_f16_2x5x3x1x20", 73, 2, 5, 3, 1, 20, F16),
+    ]:
+        gen = torch.Generator().manual_seed(seed)
+        q = randn(gen, batch, seq, hq, dim).to(dtype)
+        k = randn(gen, batch, seq, hk, dim).to(dtype)
+        # the reference's test inputs: unit (cos, sin) pairs of a random angle (llama4_rope.py:9-11)
+        angles = randn(gen, seq, dim // 2, 2)[..., 0]
+        freqs = torch.stack((angles.cos(), angles.sin()), -1).to(dtype)
+        yq, yk = ref(q, k, freqs)
+        save_case(name, {"q": q, "k": k, "freqs": freqs, "yq": yq, "yk": yk}, {"op": "llama4_rope"})
+
+
 def swiglu_cases() -> None:
     ref = KERNELS["swiglu"].reference
     for name, seed, rows, cols, dtype, scale in [
@@ -203,6 +262,8 @@ def main() -> None:
     add_rms_norm_cases()
     rotary_cases()
     paired_rope_cases()
+    qk_norm_rope_cases()
+    llama4_rope_cases()
     swiglu_cases()
     sibling_cases()
     momoe_cases()

@@ -57,6 +57,20 @@ def test_paired_rope(name):
     assert torch.equal(yq, t["yq"]) and torch.equal(yk, t["yk"])
 
 
+@pytest.mark.parametrize("name", names("qknormrope"))
+def test_qk_norm_rope(name):
+    t, meta = load_case(name)
+    yq, yk = oracle.qk_norm_rope(t["q"], t["k"], t["q_weight"], t["k_weight"], t["cos"], t["sin"], meta["eps"])
+    assert torch.equal(yq, t["yq"]) and torch.equal(yk, t["yk"])
+
+
+@pytest.mark.parametrize("name", names("llama4rope"))
+def test_llama4_rope(name):
+    t, _ = load_case(name)
+    yq, yk = oracle.llama4_rope(t["q"], t["k"], t["freqs"])
+    assert torch.equal(yq, t["yq"]) and torch.equal(yk, t["yk"])
+
+
 @pytest.mark.parametrize("name", names("swiglu"))
 def test_swiglu(name):
     t, _ = load_case(name)
