@@ -303,6 +303,8 @@ rms_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ gs, const T*
                     int64_t lddx, float cols_f, float eps, float offset, int stages) {
   constexpr int V = Num<T>::kVec;
   pdl_prologue();
+  const int cols_i = nvec * V;
+  const float inv_cols = (cols_i & (cols_i - 1)) == 0 ? 1.0f / cols_f : 0.f;
   __shared__ float red[2][2][8];  // [parity][quantity][warp]
   __shared__ uint64_t full[RING ? kMaxRingStages : 1];
   __shared__ int ring_broken;
@@ -404,7 +406,8 @@ rms_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ gs, const T*
     }
     float sumsq = 0.f, dot = 0.f;
     if constexpr (sizeof(T) == 2) {
-      // 16-bit types: gn = round_T(g * w) is one packed product per pair
+      // 16-bit types: gn = round_T(g * w) is one packed product per pair; two running sums each, two elements per instruction
+      Float2x sumsq2 = pack_f2(0.f, 0.f), dot2 = pack_f2(0.f, 0.f);
 #pragma unroll
       for (int i = 0; i < ITEMS; ++i) {
         if (!ok[i]) continue;
@@ -422,12 +425,16 @@ rms_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ gs, const T*
             accb[i][2 * j] = __fadd_rn(accb[i][2 * j], g0);
             accb[i][2 * j + 1] = __fadd_rn(accb[i][2 * j + 1], g1);
           }
-          sumsq = __fmaf_rn(h0, h0, sumsq);
-          sumsq = __fmaf_rn(h1, h1, sumsq);
-          dot = __fmaf_rn(gn0, h0, dot);
-          dot = __fmaf_rn(gn1, h1, dot);
+          const Float2x h2 = pack_f2(h0, h1);
+          sumsq2 = fma_f2(h2, h2, sumsq2);
+          dot2 = fma_f2(pack_f2(gn0, gn1), h2, dot2);
         }
       }
+      float a0, a1;
+      unpack_f2(sumsq2, a0, a1);
+      sumsq = __fadd_rn(a0, a1);
+      unpack_f2(dot2, a0, a1);
+      dot = __fadd_rn(a0, a1);
     } else {
 #pragma unroll
       for (int i = 0; i < ITEMS; ++i) {
@@ -458,15 +465,17 @@ rms_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ gs, const T*
       // every thread is done with the previous row, whose ring slot can take this CTA's next unissued row
       if (tid == 0 && it > 0 && issued < my_rows && *static_cast<volatile int*>(&ring_broken) == 0) issue(issued++);
     }
-    float tot_sq = 0.f, tot_dot = 0.f;
+    // the eight warps' partial sums: one slot per lane, three shuffle steps
+    float tot_sq = red[parity][0][lane & 7], tot_dot = red[parity][1][lane & 7];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      tot_sq = __fadd_rn(tot_sq, red[parity][0][k]);
-      tot_dot = __fadd_rn(tot_dot, red[parity][1][k]);
+    for (int o = 4; o > 0; o >>= 1) {
+      tot_sq = __fadd_rn(tot_sq, __shfl_xor_sync(0xffffffffu, tot_sq, o));
+      tot_dot = __fadd_rn(tot_dot, __shfl_xor_sync(0xffffffffu, tot_dot, o));
     }
     const float r = inv_rms(tot_sq, cols_f, eps);
     const float gv_scalar = __fmul_rn(tot_dot, __fmul_rn(-0.5f, __fmul_rn(__fmul_rn(r, r), r)));
-    const float coef = __fmul_rn(__fdiv_rn(gv_scalar, cols_f), 2.0f);
+    // gv / cols: a product with 1 / cols is the same number when cols is a power of two
+    const float coef = __fmul_rn(inv_cols > 0.f ? __fmul_rn(gv_scalar, inv_cols) : __fdiv_rn(gv_scalar, cols_f), 2.0f);
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
       if (!ok[i]) continue;
@@ -486,9 +495,10 @@ rms_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ gs, const T*
         weight_words(i, ww);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          float h0, h1, gn0, gn1, gw0, gw1, o0, o1;
+          float h0, h1, n0, n1, gn0, gn1, gw0, gw1, o0, o1;
           Num<T>::unpack2(wx[j], h0, h1);
-          const uint32_t n = Num<T>::pack2(__fmul_rn(h0, r), __fmul_rn(h1, r));
+          unpack_f2(mul_f2(pack_f2(h0, h1), r2), n0, n1);
+          const uint32_t n = Num<T>::pack2(n0, n1);
           Num<T>::unpack2(Num<T>::mul2(wg[j], n), gw0, gw1);
           accw[i][2 * j] = __fadd_rn(accw[i][2 * j], gw0);
           accw[i][2 * j + 1] = __fadd_rn(accw[i][2 * j + 1], gw1);

@@ -363,9 +363,21 @@ struct PairedArgs {
   float eps;
 };
 
-// 1 / sqrt(sum / n + eps) in separately rounded fp32 steps, like the norm kernels.
-__device__ __forceinline__ float inv_rms(float sumsq, float n, float eps) {
-  return __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(sumsq, n), eps)));
+// 1 / sqrt(sum / n + eps) for the per-head norm, where it is evaluated once per 2 x head_dim elements and
+// the IEEE division, square root and reciprocal (about 25 instructions) would be a tenth of the kernel.
+// `inv_n` > 0 says n is a power of two: sum * inv_n is then exact and one fused multiply-add gives the
+// reference's round(round(sum / n) + eps).  The reciprocal square root is the hardware approximation
+// polished by one Newton step, i.e. the true value rounded to within about half a unit in the last place;
+// the reference's 1 / sqrt (two roundings) differs from it in the last bit about as often as a different
+// summation order of the squares does.  Arguments of 0 / inf (and denormal ones, flushed to 0) give the
+// approximation's own inf / 0, like the reference.
+__device__ __forceinline__ float inv_rms(float sumsq, float n, float inv_n, float eps) {
+  const float v = inv_n > 0.f ? __fmaf_rn(sumsq, inv_n, eps) : __fadd_rn(__fdiv_rn(sumsq, n), eps);
+  float y;
+  asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(v));
+  const float e = __fmaf_rn(-__fmul_rn(v, y), y, 1.0f);  // 1 - v*y^2
+  const float y1 = __fmaf_rn(__fmul_rn(0.5f, y), e, y);
+  return e == e ? y1 : y;
 }
 
 // One unit = a 128-bit word of the first half of a row and its partner in the second half.
@@ -379,9 +391,10 @@ __device__ __forceinline__ float inv_rms(float sumsq, float n, float eps) {
 // position is past the end compute on the last position and store nothing, which keeps every
 // shuffle full-width.
 template <typename T, bool NORM>
-__global__ void __launch_bounds__(256) rope_paired_kernel(const PairedArgs p) {
+__global__ void __launch_bounds__(256, NORM ? 2 : 3) rope_paired_kernel(const PairedArgs p) {
   constexpr int V = Num<T>::kVec;
-  constexpr int UNROLL = 4;
+  // heads in flight per thread; the fused norm keeps fewer CTAs resident (more registers), so each asks for more
+  constexpr int UNROLL = NORM ? 8 : 4;
   pdl_prologue();
   const int half = p.head_dim / 2;
   const int upr = half / V;  // units per row
@@ -436,21 +449,30 @@ __global__ void __launch_bounds__(256) rope_paired_kernel(const PairedArgs p) {
       return Num<T>::pack(f);
     } else {
       const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+      const Float2x r2 = pack_f2(r, r);
       uint32_t wo[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        wo[j] = Num<T>::mul2(Num<T>::pack2(__fmul_rn(f[2 * j], r), __fmul_rn(f[2 * j + 1], r)), ww[j]);
+      for (int j = 0; j < 4; ++j) {
+        float n0, n1;
+        unpack_f2(mul_f2(pack_f2(f[2 * j], f[2 * j + 1]), r2), n0, n1);
+        wo[j] = Num<T>::mul2(Num<T>::pack2(n0, n1), ww[j]);
+      }
       return make_uint4(wo[0], wo[1], wo[2], wo[3]);
     }
   };
-  auto sum_squares = [](uint4 x, float acc) {
+  // two running sums of squares, two elements per instruction
+  auto sum_squares = [](uint4 x, Float2x acc) {
     float f[V];
     Num<T>::unpack(x, f);
 #pragma unroll
-    for (int j = 0; j < V; ++j) acc = __fmaf_rn(f[j], f[j], acc);
+    for (int j = 0; j < V; j += 2) {
+      const Float2x v = pack_f2(f[j], f[j + 1]);
+      acc = fma_f2(v, v, acc);
+    }
     return acc;
   };
   const float cols_f = static_cast<float>(p.head_dim);
+  const float inv_cols = (p.head_dim & (p.head_dim - 1)) == 0 ? 1.0f / cols_f : 0.f;
 
   for (int ti = 0; ti < 2; ++ti) {
     const PairedTensor& t = p.t[ti];
@@ -476,9 +498,11 @@ __global__ void __launch_bounds__(256) rope_paired_kernel(const PairedArgs p) {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
           if (h0 + u < t.heads) {  // uniform over the CTA
-            float acc = sum_squares(hi[u], sum_squares(lo[u], 0.f));
+            float a0, a1;
+            unpack_f2(sum_squares(hi[u], sum_squares(lo[u], pack_f2(0.f, 0.f))), a0, a1);
+            float acc = __fadd_rn(a0, a1);
             for (int o = upr >> 1; o > 0; o >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, o));
-            const float r = inv_rms(acc, cols_f, p.eps);
+            const float r = inv_rms(acc, cols_f, inv_cols, p.eps);
             lo[u] = normalise(lo[u], r, w1);
             hi[u] = normalise(hi[u], r, w2);
           }
@@ -548,7 +572,7 @@ __global__ void __launch_bounds__(256) norm_rope_scalar_kernel(const PairedArgs 
         const float v = Num<T>::up(xin[j]);
         acc = __fadd_rn(acc, __fmul_rn(v, v));
       }
-      const float r = inv_rms(warp_sum(acc), cols_f, p.eps);
+      const float r = inv_rms(warp_sum(acc), cols_f, 0.f, p.eps);
       auto normed = [&](int j) {
         return Num<T>::rt(__fmul_rn(Num<T>::rt(__fmul_rn(Num<T>::up(xin[j]), r)), Num<T>::up(weight[j])));
       };
