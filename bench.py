@@ -373,6 +373,67 @@ def bench_extra_ops(device, peak_gbs: float, sampler, scale: float = 1.0, steps:
     return out
 
 
+def measured_tensor_peak() -> tuple[float, float, str]:
+    """(burst, sustained) dense bf16 TFLOP/s of cuBLAS on this pool's B200s, else the fallback figures."""
+    try:
+        peaks = json.loads((REPO / "MEASURED_PEAKS.json").read_text())
+        return float(peaks["bf16_tflops"]), float(peaks["bf16_tflops_sustained"]), "measured"
+    except (OSError, KeyError, ValueError):
+        return 1590.0, 1400.0, "fallback"
+
+
+def bench_grouped_gemm(device, sampler, scale: float = 1.0, steps: int = 10, warmup: int = 3, inter: int = 1536) -> dict:
+    """The expert MLP on the rows of config 5: 65536 tokens x top-8 = 524288 rows of 4096 over 64 experts (8192 rows each
+    on average, routed by the config's own seeded logits), SwiGLU MLP with an intermediate size of 1536 per expert.
+
+    Two launches per step: gate/up projection + SwiGLU (2 * rows * 4096 * 3072 flop), down projection
+    (2 * rows * 1536 * 4096 flop).  Tensor-core bound: TFLOP/s against the measured cuBLAS bf16 peak."""
+    import ctypes
+
+    from popcorn_b200 import _lib, ops, workloads
+
+    w = workloads.moe_bf16(scale=scale).to(device)
+    x, logits = w.inputs["x"], w.inputs["router_logits"]
+    experts, top_k = w.args["experts"], w.args["top_k"]
+    hidden = x.shape[1]
+    idx, _ = ops.moe_route(logits, top_k)
+    rows, _, offsets, _, _ = ops.moe_permute(x, idx, experts)
+    del x, logits, idx
+    gen = torch.Generator(device=device).manual_seed(5)
+    gate = (torch.randn(experts, hidden, inter, device=device, generator=gen) / hidden ** 0.5).to(torch.bfloat16)
+    up = (torch.randn(experts, hidden, inter, device=device, generator=gen) / hidden ** 0.5).to(torch.bfloat16)
+    down = (torch.randn(experts, inter, hidden, device=device, generator=gen) / inter ** 0.5).to(torch.bfloat16)
+    total = rows.shape[0]
+    act = torch.empty(total, inter, device=device, dtype=torch.bfloat16)
+    out = torch.empty(total, hidden, device=device, dtype=torch.bfloat16)
+    lib = _lib.library()
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+
+    def check(status):
+        if status != 0:
+            raise _lib.B200Error("b200_moe_grouped_gemm", status, lib.b200_status_string(status).decode(), lib.b200_last_error().decode())
+
+    def gate_up(i):
+        check(lib.b200_moe_grouped_gemm(p(rows), p(gate), p(up), p(offsets), p(act), total, hidden, inter, experts, hidden, inter, _lib.BF16, stream))
+
+    def down_proj(i):
+        check(lib.b200_moe_grouped_gemm(p(act), p(down), ctypes.c_void_p(0), p(offsets), p(out), total, inter, hidden, experts, inter, hidden, _lib.BF16, stream))
+
+    burst, sustained, kind = measured_tensor_peak()
+    result = {"rows": total, "hidden": hidden, "intermediate": inter, "experts": experts, "peak_kind": kind}
+    for name, fn, flop in (("gate_up_swiglu", gate_up, 2.0 * total * hidden * 2 * inter), ("down", down_proj, 2.0 * total * inter * hidden)):
+        t0 = time.time()
+        ms = time_launches(fn, steps, warmup, device)
+        if sampler is not None:
+            sampler.mark(t0, time.time())
+        tflops = flop / (ms * 1e-3) / 1e12
+        result[name] = {"ms": round(ms, 4), "tflop_s": round(tflops, 1), "flop": flop, "frac_of_measured_burst": round(tflops / burst, 4),
+                        "frac_of_measured_sustained": round(tflops / sustained, 4)}
+    result["wait_timeouts"] = _lib.wait_timeouts()
+    return result
+
+
 def bench_moe_expert_parallel(device, world: int, rank: int, dist, exchange: str, steps: int = 20, warmup: int = 3) -> dict:
     """Config 5 sharded over the ranks: 65536 / world tokens and 64 / world experts per GPU.
 
@@ -500,7 +561,7 @@ def main() -> None:
     parser.add_argument("--skip-per-op", action="store_true", help="only the headline loop (used for profiling captures)")
     parser.add_argument("--scale", type=float, default=1.0, help="shrink the token count (profiling captures only)")
     parser.add_argument("--records", metavar="DIR", help="also write popcorn report rows (schema 3) under DIR/v3/reports")
-    parser.add_argument("--only", choices=["rms_norm_fp32", "add_rms_norm_bf16", "rotary_bf16", "swiglu_bf16", "paired_rope_bf16", "moe_bf16", "extras"],
+    parser.add_argument("--only", choices=["rms_norm_fp32", "add_rms_norm_bf16", "rotary_bf16", "swiglu_bf16", "paired_rope_bf16", "moe_bf16", "extras", "grouped_gemm"],
                         help="time one configuration's kernels alone and print a short JSON (profiling captures); "
                              "`extras` = the ops beyond the five configurations, filtered by --match")
     parser.add_argument("--match", default="", help="with --only extras: run the ops whose name contains this text")
@@ -533,6 +594,8 @@ def main() -> None:
             result = bench_moe(device, peak_gbs, None, args.scale, args.steps, args.warmup)
         elif args.only == "extras":
             result = bench_extra_ops(device, peak_gbs, None, args.scale, args.steps, args.match)
+        elif args.only == "grouped_gemm":
+            result = bench_grouped_gemm(device, None, args.scale, args.steps, args.warmup)
         else:
             result = bench_single_kernel_ops(device, peak_gbs, None, [args.only], args.scale, args.steps, args.warmup)[args.only]
         print(json.dumps({"only": args.only, "scale": args.scale, "steps": args.steps, **result}), flush=True)
@@ -615,6 +678,7 @@ def main() -> None:
         if world == 1:
             torch_eager_incumbent(device, per_op, args.records)
             per_op["beyond_the_five_configs"] = bench_extra_ops(device, peak_gbs, sampler)
+            per_op["moe_expert_mlp_bf16"] = bench_grouped_gemm(device, sampler)
     if dist is not None:
         dist.barrier()
         if not args.skip_per_op:

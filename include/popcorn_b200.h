@@ -393,6 +393,28 @@ int b200_moe_unpermute(const void* rows, const float* weights, const int32_t* po
  */
 
 /*
+ * Grouped expert GEMM over the expert-major row buffer that b200_moe_permute writes (tensor cores:
+ * tcgen05.mma with fp32 accumulators in tensor memory, operands staged by TMA):
+ *   weight2 == NULL:  out[p, :] = rows[p, :] @ weight[e(p)]
+ *   weight2 != NULL:  out[p, :] = silu(rows[p, :] @ weight[e(p)]) * (rows[p, :] @ weight2[e(p)])
+ * with e(p) the expert whose segment offsets[e] <= p < offsets[e + 1] contains row p; products are exact,
+ * sums are fp32, the result is rounded to the operand type once (the SwiGLU product is formed in fp32).
+ *
+ * Replaces the expert MLP steps of momoe: the registered reference's einsums over a dense
+ * [batch, seq, experts, .] tensor (src/popcorn/kernels/momoe.py:50-52) and the incumbent's lin1_kernel
+ * (gate and up projection + SwiGLU, src/popcorn/impls/momoe_tl.py:90-212) and lin2_kernel (down
+ * projection, :225-330).  The first form with the down weights is lin2, the second form with
+ * (gate_weight, up_weight) is lin1.  rows: [total_rows, k] with row stride ld_rows; weight, weight2:
+ * [experts, k, n] contiguous, the reference's layout; offsets: [experts + 1] int32 on the device, ascending,
+ * offsets[experts] <= total_rows; out: [total_rows, n] with row stride ld_out (rows outside every segment
+ * are left untouched).  dtype: B200_BF16 or B200_F16.  k, n, ld_rows, ld_out must be multiples of 8;
+ * all buffers 16-byte aligned; experts <= 1024.
+ */
+int b200_moe_grouped_gemm(const void* rows, const void* weight, const void* weight2, const int32_t* offsets, void* out,
+                          int64_t total_rows, int64_t k, int64_t n, int64_t experts, int64_t ld_rows, int64_t ld_out,
+                          int dtype, void* stream);
+
+/*
  * For each (token, slot) pair: dst_rank = indices / experts_per_rank and
  * dst_row = dst_base[expert] + (pos - local_offsets[expert]), the pair's row in the
  * owning rank's buffer.  dst_base[e] is the row at which this rank's block for

@@ -241,3 +241,25 @@ def momoe_from_steps(x: Tensor, gate_weight: Tensor, up_weight: Tensor, down_wei
         out_rows[lo:hi] = hidden_act @ _to_fp32_or_wider(down_weight[e])
     y = moe_unpermute(out_rows, weights.to(torch.float32), pos)
     return y.reshape(*lead, hidden).to(x.dtype)
+
+
+def moe_grouped_gemm(rows: Tensor, weight: Tensor, offsets: Tensor, up_weight: Tensor | None = None) -> Tensor:
+    """The expert MLP projections of momoe restricted to the rows each expert actually receives
+    (reference: src/popcorn/kernels/momoe.py:50-52, fp32 einsums over every (token, expert) pair; the
+    incumbent computes exactly these segments, src/popcorn/impls/momoe_tl.py:90-330).
+
+    out[p] = rows[p] @ weight[e], or silu(rows[p] @ weight[e]) * (rows[p] @ up_weight[e]), in fp32, rounded once.
+    Unpinned on its own (no standalone reference function); the chain route -> permute -> projections ->
+    unpermute is pinned against the registered momoe reference."""
+    out = torch.zeros(rows.shape[0], weight.shape[2], dtype=rows.dtype)
+    bounds = offsets.tolist()
+    for e in range(weight.shape[0]):
+        lo, hi = bounds[e], bounds[e + 1]
+        if hi <= lo:
+            continue
+        segment = rows[lo:hi].float()
+        y = segment @ weight[e].float()
+        if up_weight is not None:
+            y = F.silu(y) * (segment @ up_weight[e].float())
+        out[lo:hi] = y.to(rows.dtype)
+    return out

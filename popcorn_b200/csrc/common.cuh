@@ -28,6 +28,7 @@ int sm_count();
 // Bounded waits that ran out, per source file that uses bulk asynchronous copies.
 unsigned int rope_wait_timeouts();
 unsigned int norm_wait_timeouts();
+unsigned int gemm_wait_timeouts();
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 inline size_t dtype_size(int dtype) { return dtype == B200_F32 ? 4 : 2; }

@@ -1,0 +1,430 @@
+// Grouped expert GEMM for sm_100a: the dense step either side of the MoE permutation.
+//
+//   out[p, :] = rows[p, :] @ weight[e(p)]            (one weight matrix per expert)
+//   out[p, :] = (rows[p, :] @ up[e]) * silu(rows[p, :] @ gate[e])   (DUAL: both projections and SwiGLU in one pass)
+//
+// where e(p) is the expert whose segment offsets[e] <= p < offsets[e + 1] holds row p of the
+// expert-major `rows` buffer that b200_moe_permute writes.  This is what the reference's
+// lin1_kernel / lin2_kernel compute (src/popcorn/impls/momoe_tl.py:90-212 and 225-330) and what the
+// registered reference states as two einsums over a dense [batch, seq, experts, .] tensor
+// (src/popcorn/kernels/momoe.py:50-52); weights keep the reference's layout
+// [experts, in_features, out_features] with out_features contiguous.
+//
+// Bound: tensor cores.  One CTA owns a 128 x 256 output tile (DUAL: 128 x 128 of each projection,
+// side by side in one accumulator) of one expert:
+//   warp 0     producer: one lane issues tiled bulk-tensor copies (TMA, 128-byte swizzle) of the
+//              128 x 64 slice of `rows` and the 64 x 256 slice of the expert's weight into a
+//              4-slot shared-memory ring, completion counted on a `full` mbarrier per slot
+//   warp 1     one lane issues tcgen05.mma (M 128, N 256, K 16; A K-major, B N-major straight from
+//              the reference's weight layout) into one of two 256-column fp32 accumulators in
+//              tensor memory; tcgen05.commit releases the ring slot and, after the last K slice,
+//              publishes the accumulator
+//   warps 2-5  epilogue: tcgen05.ld of the finished accumulator (each warp its 32-lane quarter),
+//              conversion (and SwiGLU) in registers, a transpose through a small shared-memory tile so
+//              that every store instruction writes whole 128-byte row segments, and only the rows that
+//              belong to the expert; overlaps the next tile's main loop through the second accumulator
+// CTAs are persistent (one per SM) and walk the tile list (expert, n tile, m tile) derived on the
+// device from `offsets`, so the host never reads the routing result.
+//
+// Every wait is bounded (tma.cuh): a wait that runs out marks the CTA aborted, every role leaves
+// its loop, the CTA waits (bounded again) for copies and MMAs it still has in flight, frees its
+// tensor memory and returns; b200_wait_timeouts() reports it.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "activations.cuh"
+#include "common.cuh"
+#include "tma.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kBM = 128, kBN = 256, kBK = 64, kStages = 4, kUmmaK = 16;
+constexpr int kABytes = kBM * kBK * 2;           // 16 KiB
+constexpr int kBChunkBytes = kBK * 128;          // one 64-column chunk of the weight slice: 64 rows of 128 bytes
+constexpr int kBBytes = kBChunkBytes * (kBN / 64);  // 32 KiB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + slack to align the ring to the swizzle atom
+constexpr int kTmemCols = 512;                   // two accumulators of kBN fp32 columns
+constexpr int kMaxExperts = 1024;
+constexpr int kThreads = 192;
+
+// ---- tcgen05 / tensor-map wrappers (this CTA only: cta_group::1, no multicast anywhere) ----
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(smem_addr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_addr(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               ::"r"(smem_addr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(smem_addr(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(slot)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// Arrives once on `bar` when every tcgen05.mma this thread issued before has completed.
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]; `accumulate` = 0 overwrites D.
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns of tensor memory: lane l of the warp receives row (quarter * 32 + l).
+__device__ __forceinline__ void tmem_load_32(uint32_t addr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(addr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptors (sm_100 format: start >> 4 in bits 0-13, leading byte offset >> 4
+// in 16-29, stride byte offset >> 4 in 32-45, version 1 in 46-47, swizzle mode in 61-63; 2 = 128 bytes).
+//  A, K-major, rows of 128 bytes (64 K values): 8-row groups 1024 bytes apart (stride offset); the
+//     leading offset is not used by swizzled K-major layouts and is set to its canonical 1.
+//  B, N-major, rows of 128 bytes (64 N values) per K index: 8-row K groups 1024 bytes apart (stride
+//     offset), 64-column chunks one whole [64 x 128 B] block apart (leading offset).
+constexpr uint64_t kDescFixed = (uint64_t(1) << 46) | (uint64_t(2) << 61);
+constexpr uint64_t kDescA = kDescFixed | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32);
+constexpr uint64_t kDescB = kDescFixed | (uint64_t(kBChunkBytes >> 4) << 16) | (uint64_t(1024 >> 4) << 32);
+__device__ __forceinline__ uint64_t desc_at(uint64_t fixed, uint32_t smem_byte_addr) {
+  return fixed | ((smem_byte_addr >> 4) & 0x3fffu);
+}
+
+// Instruction descriptor of kind::f16: fp32 accumulate (bit 4), A/B format (0 fp16, 1 bf16) at bits 7
+// and 10, A K-major (bit 15 = 0), B N-major (bit 16 = 1), N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t format) {
+  return (1u << 4) | (format << 7) | (format << 10) | (1u << 16) | (uint32_t(kBN >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
+}
+
+struct GemmArgs {
+  const int32_t* offsets;  // [experts + 1], device
+  void* out;
+  int64_t ld_out;
+  int experts;
+  int n;        // output columns (per projection)
+  int k;
+  uint32_t idesc;
+};
+
+struct Tile {
+  int expert, row0, row_end, n0;
+};
+
+// tile -> (expert, m tile, n tile): tiles of one expert are consecutive, m fastest, so that CTAs running
+// together share the expert's weight slice in L2.
+__device__ __forceinline__ Tile decode_tile(int tile, const int* tile_start, const int32_t* offsets, int experts, int out_tile_n) {
+  int lo = 0, hi = experts;  // last expert with tile_start[e] <= tile
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (tile_start[mid] <= tile) lo = mid;
+    else hi = mid;
+  }
+  const int first = offsets[lo], end = offsets[lo + 1];
+  const int tiles_m = (end - first + kBM - 1) / kBM;
+  const int local = tile - tile_start[lo];
+  Tile t;
+  t.expert = lo;
+  t.row0 = first + (local % tiles_m) * kBM;
+  t.row_end = end;
+  t.n0 = (local / tiles_m) * out_tile_n;
+  return t;
+}
+
+template <typename T, bool DUAL>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_w,
+                    const __grid_constant__ CUtensorMap map_w2, const GemmArgs p) {
+  constexpr int OUT_N = DUAL ? kBN / 2 : kBN;  // output columns per tile
+  pdl_prologue();
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ uint64_t full[kStages], empty[kStages], acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int aborted;
+  __shared__ int tile_start[kMaxExperts + 1];
+  __shared__ uint4 staging[4][32][8];  // per epilogue warp: 32 rows x 128 bytes of finished output
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tiles_n = (p.n + OUT_N - 1) / OUT_N;
+  const int num_kb = (p.k + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    aborted = 0;
+    int total = 0;
+    for (int e = 0; e < p.experts; ++e) {
+      tile_start[e] = total;
+      const int count = p.offsets[e + 1] - p.offsets[e];
+      total += (count > 0 ? (count + kBM - 1) / kBM : 0) * tiles_n;
+    }
+    tile_start[p.experts] = total;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);  // one arrival per epilogue warp
+    }
+    mbar_init_fence();
+  }
+  if (warp == 1) tmem_alloc(&tmem_base_slot, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  const int total_tiles = tile_start[p.experts];
+  volatile int* abort_flag = &aborted;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- producer --
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+        const Tile t = decode_tile(tile, tile_start, p.offsets, p.experts, OUT_N);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          if (!mbar_wait(&empty[s], ((it / kStages) & 1u) ^ 1u)) {
+            *abort_flag = 1;
+            break;
+          }
+          unsigned char* a_dst = ring + s * kStageBytes;
+          unsigned char* b_dst = a_dst + kABytes;
+          mbar_arrive_expect(&full[s], kStageBytes);
+          tma_load_2d(a_dst, &map_rows, kb * kBK, t.row0, &full[s]);
+#pragma unroll
+          for (int c = 0; c < kBN / 64; ++c) {
+            if (DUAL && c >= kBN / 128) tma_load_3d(b_dst + c * kBChunkBytes, &map_w2, t.n0 + (c - kBN / 128) * 64, kb * kBK, t.expert, &full[s]);
+            else tma_load_3d(b_dst + c * kBChunkBytes, &map_w, t.n0 + c * 64, kb * kBK, t.expert, &full[s]);
+          }
+        }
+      }
+      if (*abort_flag) {
+        // copies already issued still write this CTA's shared memory: give each slot's last copy a bounded wait
+        for (uint32_t k = it > kStages ? it - kStages : 0; k < it; ++k) (void)mbar_wait(&full[k % kStages], (k / kStages) & 1u);
+      }
+    }
+  } else if (warp == 1) {
+    // ----------------------------------------------------------- MMA issuer --
+    if (lane == 0) {
+      uint32_t it = 0, local = 0;
+      bool pending = false;
+      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++local) {
+        const uint32_t acc = local & 1u;
+        if (!mbar_wait(&acc_empty[acc], ((local >> 1) & 1u) ^ 1u)) {
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kBN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          if (!mbar_wait(&full[s], (it / kStages) & 1u)) {
+            *abort_flag = 1;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_addr(ring + s * kStageBytes), b_addr = a_addr + kABytes;
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            // A: 16 K values = 32 bytes further along the swizzled 128-byte rows; B: 16 K rows = 2048 bytes further
+            mma_f16(d_tmem, desc_at(kDescA, a_addr + k * kUmmaK * 2), desc_at(kDescB, b_addr + k * kUmmaK * 128), p.idesc,
+                    (kb | k) != 0 ? 1u : 0u);
+          }
+          mma_commit(&empty[s]);  // the slot is free once these MMAs have read it
+          pending = true;
+        }
+        if (*abort_flag) break;
+        mma_commit(&acc_full[acc]);
+      }
+      if (*abort_flag && pending) {
+        // MMAs may still be running: a bounded wait on a fresh commit before tensor memory is freed
+        mma_commit(&acc_full[0]);
+        (void)mbar_wait(&acc_full[0], 0);
+        (void)mbar_wait(&acc_full[0], 1);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue --
+    const int quarter = warp & 3;  // the 32 tensor-memory lanes this warp may read
+    uint32_t local = 0;
+    T* out = static_cast<T*>(p.out);
+    for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++local) {
+      const Tile t = decode_tile(tile, tile_start, p.offsets, p.experts, OUT_N);
+      const uint32_t acc = local & 1u;
+      if (!mbar_wait(&acc_full[acc], (local >> 1) & 1u)) {
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * kBN + (static_cast<uint32_t>(quarter * 32) << 16);
+      const int warp_row0 = t.row0 + quarter * 32;
+      uint4(*mine)[8] = staging[quarter];
+#pragma unroll 1
+      for (int c = 0; c < OUT_N / 32; ++c) {
+        uint32_t v[32], u[32];
+        tmem_load_32(taddr + c * 32, v);
+        if constexpr (DUAL) tmem_load_32(taddr + OUT_N + c * 32, u);
+        tmem_load_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float lo = __uint_as_float(v[2 * j]), hi = __uint_as_float(v[2 * j + 1]);
+          if constexpr (DUAL) {
+            // columns 0..127 of the accumulator hold rows @ gate, 128..255 rows @ up
+            lo = __fmul_rn(silu_f32<1>(lo), __uint_as_float(u[2 * j]));
+            hi = __fmul_rn(silu_f32<1>(hi), __uint_as_float(u[2 * j + 1]));
+          }
+          packed[j] = Num<T>::pack2(lo, hi);
+        }
+        // lane = row: its 32 columns are four 16-byte pieces of the 128-byte staging row (piece index
+        // xor-ed with the row so that neither these writes nor the transposed reads conflict on banks)
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          mine[lane][((c & 1) * 4 + q) ^ (lane & 7)] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+        if (c & 1) {
+          // 64 finished columns of 32 rows: write them out as whole 128-byte row segments, four rows per instruction
+          __syncwarp();
+          const int piece = lane & 7;
+          const int col = t.n0 + (c - 1) * 32 + piece * 8;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = i * 4 + (lane >> 3);
+            const int row = warp_row0 + r;
+            if (row < t.row_end && col < p.n)
+              st_stream(out + static_cast<int64_t>(row) * p.ld_out + col, mine[r][piece ^ (r & 7)]);
+          }
+          __syncwarp();
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ------------------------------------------------------------------ host side --
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder, looked up through the runtime so that the library links against cudart only.
+EncodeTiled encoder() {
+  static EncodeTiled fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult status;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &status) == cudaSuccess &&
+        status == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiled>(ptr);
+    else
+      (void)cudaGetLastError();
+  });
+  return fn;
+}
+
+// rows [total_rows, k], row stride ld: box 64 (K) x 128 (rows), 128-byte swizzle, zero fill outside.
+bool encode_rows(CUtensorMap* map, CUtensorMapDataType type, const void* base, int64_t total_rows, int64_t k, int64_t ld) {
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(total_rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  const cuuint32_t box[2] = {kBK, kBM}, elem[2] = {1, 1};
+  return encoder()(map, type, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// weight [experts, k, n], n contiguous: box 64 (N) x 64 (K) x 1 (expert).
+bool encode_weight(CUtensorMap* map, CUtensorMapDataType type, const void* base, int64_t experts, int64_t k, int64_t n) {
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(experts)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(n) * 2, static_cast<cuuint64_t>(n) * static_cast<cuuint64_t>(k) * 2};
+  const cuuint32_t box[3] = {64, kBK, 1}, elem[3] = {1, 1, 1};
+  return encoder()(map, type, 3, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename T, bool DUAL>
+int run(const CUtensorMap& rows, const CUtensorMap& w, const CUtensorMap& w2, const GemmArgs& args, cudaStream_t st) {
+  auto kernel = grouped_gemm_kernel<T, DUAL>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(B200_ERR_LAUNCH, "b200_moe_grouped_gemm: cannot reserve %d bytes of shared memory", kSmemBytes);
+  }
+  launch(kernel, static_cast<unsigned>(sm_count()), kThreads, kSmemBytes, st, rows, w, w2, args);
+  return after_launch("grouped_gemm_kernel");
+}
+
+}  // namespace
+
+unsigned int gemm_wait_timeouts() { return read_wait_timeouts(); }
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_moe_grouped_gemm(const void* rows, const void* weight, const void* weight2, const int32_t* offsets, void* out,
+                                     int64_t total_rows, int64_t k, int64_t n, int64_t experts, int64_t ld_rows, int64_t ld_out,
+                                     int dtype, void* stream) {
+  if (dtype != B200_BF16 && dtype != B200_F16)
+    return fail(B200_ERR_DTYPE, "%s: dtype %d not supported (bf16 or fp16 operands, fp32 accumulation)", __func__, dtype);
+  if (total_rows < 0 || k < 0 || n < 0 || experts < 0) return fail(B200_ERR_SHAPE, "%s: negative size", __func__);
+  if (experts > kMaxExperts) return fail(B200_ERR_SHAPE, "%s: experts=%lld exceeds %d", __func__, (long long)experts, kMaxExperts);
+  if (total_rows > 0x7fffffffLL - kBM || k > 0x7fffffffLL || n > 0x7fffffffLL) return fail(B200_ERR_SHAPE, "%s: size out of range", __func__);
+  if (total_rows == 0 || n == 0 || experts == 0) return B200_OK;
+  B200_REQUIRE_PTR(rows);
+  B200_REQUIRE_PTR(weight);
+  B200_REQUIRE_PTR(offsets);
+  B200_REQUIRE_PTR(out);
+  if (k == 0) return fail(B200_ERR_SHAPE, "%s: k must be positive", __func__);
+  if (k % 8 != 0 || n % 8 != 0 || ld_rows % 8 != 0 || ld_out % 8 != 0)
+    return fail(B200_ERR_SHAPE, "%s: k, n and the row strides must be multiples of 8 elements (16-byte rows for the tensor maps)", __func__);
+  if (ld_rows < k || ld_out < n) return fail(B200_ERR_SHAPE, "%s: leading dimension smaller than the row", __func__);
+  if (!aligned(rows, 16) || !aligned(weight, 16) || !aligned(out, 16) || (weight2 && !aligned(weight2, 16)) || !aligned(offsets, 4))
+    return fail(B200_ERR_ALIGNMENT, "%s: rows, weights and out must be 16-byte aligned", __func__);
+  if (int rc = check_device()) return rc;
+  if (encoder() == nullptr) return fail(B200_ERR_LAUNCH, "%s: the driver does not provide cuTensorMapEncodeTiled", __func__);
+
+  const CUtensorMapDataType type = dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  alignas(64) CUtensorMap map_rows, map_w, map_w2;
+  if (!encode_rows(&map_rows, type, rows, total_rows, k, ld_rows) || !encode_weight(&map_w, type, weight, experts, k, n) ||
+      !encode_weight(&map_w2, type, weight2 ? weight2 : weight, experts, k, n))
+    return fail(B200_ERR_LAUNCH, "%s: tensor map encoding failed", __func__);
+
+  GemmArgs args{};
+  args.offsets = offsets;
+  args.out = out;
+  args.ld_out = ld_out;
+  args.experts = static_cast<int>(experts);
+  args.n = static_cast<int>(n);
+  args.k = static_cast<int>(k);
+  args.idesc = instr_desc(dtype == B200_BF16 ? 1u : 0u);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == B200_BF16) return weight2 ? run<__nv_bfloat16, true>(map_rows, map_w, map_w2, args, st) : run<__nv_bfloat16, false>(map_rows, map_w, map_w2, args, st);
+  return weight2 ? run<__half, true>(map_rows, map_w, map_w2, args, st) : run<__half, false>(map_rows, map_w, map_w2, args, st);
+}

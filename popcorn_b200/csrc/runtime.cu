@@ -99,7 +99,8 @@ const char* b200_last_error(void) { return b200::g_error; }
 uint64_t b200_launch_count(void) { return b200::g_launches.load(std::memory_order_relaxed); }
 
 uint64_t b200_wait_timeouts(void) {
-  return static_cast<uint64_t>(b200::rope_wait_timeouts()) + static_cast<uint64_t>(b200::norm_wait_timeouts());
+  return static_cast<uint64_t>(b200::rope_wait_timeouts()) + static_cast<uint64_t>(b200::norm_wait_timeouts()) +
+         static_cast<uint64_t>(b200::gemm_wait_timeouts());
 }
 
 }  // extern "C"

@@ -556,6 +556,36 @@ def moe_unpermute(rows: Tensor, weights: Tensor, pos: Tensor) -> Tensor:
     return y
 
 
+def moe_grouped_gemm(rows: Tensor, weight: Tensor, offsets: Tensor, up_weight: Tensor | None = None) -> Tensor:
+    """Expert MLP projection over the expert-major rows of `moe_permute` (momoe.py:50-52, momoe_tl.py:90-330).
+
+    out[p] = rows[p] @ weight[e(p)], or silu(rows[p] @ weight[e(p)]) * (rows[p] @ up_weight[e(p)]) when `up_weight`
+    is given (`weight` is then the gate projection); e(p) is the expert whose segment [offsets[e], offsets[e+1])
+    holds row p.  weight: [experts, in_features, out_features] as in the reference; fp32 accumulation on the tensor
+    cores, one rounding to the dtype of rows.  Rows outside every segment are zero."""
+    device = _require_cuda(rows, weight, offsets, *([up_weight] if up_weight is not None else []))
+    _forbid_grad(rows, weight)
+    code = _dtype_code(rows, "moe_grouped_gemm")
+    if rows.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError("moe_grouped_gemm: bf16 or fp16 operands only (fp32 accumulation)")
+    if rows.dim() != 2 or weight.dim() != 3 or weight.shape[1] != rows.shape[1]:
+        raise ValueError("moe_grouped_gemm: rows must be [n, in_features] and weight [experts, in_features, out_features]")
+    if weight.dtype != rows.dtype or (up_weight is not None and (up_weight.dtype != rows.dtype or up_weight.shape != weight.shape)):
+        raise ValueError("moe_grouped_gemm: weights must have the dtype of rows (and up_weight the shape of weight)")
+    experts, k, n = weight.shape
+    if offsets.dtype != torch.int32 or offsets.shape != (experts + 1,):
+        raise TypeError("moe_grouped_gemm: offsets must be int32 [experts + 1]")
+    r2, ldr = _rows(rows)
+    total = r2.shape[0]
+    out = torch.zeros((total, n), dtype=rows.dtype, device=device) if total else torch.empty((0, n), dtype=rows.dtype, device=device)
+    with torch.cuda.device(device):
+        _lib.call(
+            "b200_moe_grouped_gemm", _ptr(r2), _ptr(weight.contiguous()), _ptr(None if up_weight is None else up_weight.contiguous()),
+            _ptr(offsets.contiguous()), _ptr(out), total, k, n, experts, ldr, max(n, 1), code, _stream(device),
+        )
+    return out
+
+
 def _pointer_array(pointers: list[int]) -> ctypes.Array:
     return (ctypes.c_void_p * len(pointers))(*pointers)
 

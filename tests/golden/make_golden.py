@@ -229,19 +229,23 @@ def sibling_cases() -> None:
 
 def momoe_cases() -> None:
     ref = KERNELS["momoe"].reference
-    for name, seed, batch, seq, hidden, inter, experts, top_k in [
-        ("momoe_f32_e8_k1", 40, 2, 12, 32, 16, 8, 1),
-        ("momoe_f32_e8_k2", 41, 2, 12, 32, 16, 8, 2),
-        ("momoe_f32_e8_k6", 42, 1, 20, 32, 16, 8, 6),
-        ("momoe_f32_e64_k8", 43, 1, 48, 16, 8, 64, 8),
+    for name, seed, batch, seq, hidden, inter, experts, top_k, dtype in [
+        ("momoe_f32_e8_k1", 40, 2, 12, 32, 16, 8, 1, F32),
+        ("momoe_f32_e8_k2", 41, 2, 12, 32, 16, 8, 2, F32),
+        ("momoe_f32_e8_k6", 42, 1, 20, 32, 16, 8, 6, F32),
+        ("momoe_f32_e64_k8", 43, 1, 48, 16, 8, 64, 8, F32),
+        # 16-bit cases for the tensor-core expert projections (separate prefix: their tests carry 16-bit tolerances)
+        ("moe16_bf16_e8_k2", 44, 2, 40, 64, 32, 8, 2, BF16),
+        ("moe16_bf16_e16_k4", 45, 1, 300, 128, 72, 16, 4, BF16),
+        ("moe16_f16_e4_k2", 46, 1, 96, 64, 40, 4, 2, F16),
     ]:
         gen = torch.Generator().manual_seed(seed)
         # signature order: x, gate_weight, up_weight, down_weight, router_logits (momoe.py:34-41);
         # weights are scaled by 1/sqrt(fan_in) as the reference's test_inputs do (momoe.py:26-30)
-        x = randn(gen, batch, seq, hidden)
-        gate_w = randn(gen, experts, hidden, inter) / hidden**0.5
-        up_w = randn(gen, experts, hidden, inter) / hidden**0.5
-        down_w = randn(gen, experts, inter, hidden) / inter**0.5
+        x = randn(gen, batch, seq, hidden).to(dtype)
+        gate_w = (randn(gen, experts, hidden, inter) / hidden**0.5).to(dtype)
+        up_w = (randn(gen, experts, hidden, inter) / hidden**0.5).to(dtype)
+        down_w = (randn(gen, experts, inter, hidden) / inter**0.5).to(dtype)
         logits = randn(gen, batch, seq, experts)
         y = ref(x, gate_w, up_w, down_w, logits, top_k)
         # the routing lines on their own (momoe.py:47-49), for the route oracle
