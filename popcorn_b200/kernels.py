@@ -86,8 +86,19 @@ def moe_unpermute(rows, weights, pos):
     """Gate-weighted sum of expert rows back into token order."""
 
 
+@register_kernel
+def moe_grouped_gemm(rows, weight, offsets, up_weight=None):
+    """Per-expert projection of expert-major rows; with up_weight, silu(rows @ weight) * (rows @ up_weight)."""
+
+
+@register_kernel
+def momoe(x, gate_weight, up_weight, down_weight, router_logits, top_k=2):
+    """Mixture of experts over SwiGLU MLPs, routed to the top-k experts by softmax probability."""
+
+
 # ops with backward kernels are registered in their differentiable form
-for _op in (rope, qk_norm_rope, llama4_rope, geglu, rms_norm_gated, l2_norm, layer_norm, moe_route, moe_permute, moe_unpermute):
+for _op in (rope, qk_norm_rope, llama4_rope, geglu, rms_norm_gated, l2_norm, layer_norm, moe_route, moe_permute, moe_unpermute,
+            moe_grouped_gemm, momoe):
     _op.register(BACKEND, source=f"popcorn_b200.ops.{_op.name}", forward_only=True)
 for _op in (rms_norm, add_rms_norm, rotary_embedding, swiglu):
     _op.register(BACKEND, source=f"popcorn_b200.autograd.{_op.name}")

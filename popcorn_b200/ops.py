@@ -586,6 +586,32 @@ def moe_grouped_gemm(rows: Tensor, weight: Tensor, offsets: Tensor, up_weight: T
     return out
 
 
+def momoe(x: Tensor, gate_weight: Tensor, up_weight: Tensor, down_weight: Tensor, router_logits: Tensor, top_k: int = 2) -> Tensor:
+    """Mixture of SwiGLU expert MLPs, routed to the top-k experts by softmax probability (momoe.py:34-53).
+
+    The reference evaluates every expert on every token in fp32; here only the routed (token, expert) pairs are
+    computed: route -> permute into expert-major rows -> gate/up projection + SwiGLU and down projection on the tensor
+    cores (16-bit operands, fp32 accumulation, 16-bit intermediate, like the incumbent kernels,
+    momoe_tl.py:90-330) -> weighted unpermute in fp32.  x: [batch, seq, hidden] bf16 or fp16."""
+    device = _require_cuda(x, gate_weight, up_weight, down_weight, router_logits)
+    _forbid_grad(x, gate_weight, up_weight, down_weight, router_logits)
+    if x.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError("momoe: bf16 or fp16 activations and weights only (the expert projections run on 16-bit tensor-core operands)")
+    if not (gate_weight.dtype == up_weight.dtype == down_weight.dtype == x.dtype):
+        raise TypeError("momoe: x and the three weights must share a dtype")
+    experts, hidden, inter = gate_weight.shape
+    if x.shape[-1] != hidden or up_weight.shape != gate_weight.shape or down_weight.shape != (experts, inter, hidden):
+        raise ValueError("momoe: expected x [..., hidden], gate/up [experts, hidden, intermediate], down [experts, intermediate, hidden]")
+    if router_logits.shape != (*x.shape[:-1], experts):
+        raise ValueError("momoe: router_logits must be [..., experts] over the tokens of x")
+    flat = x.reshape(-1, hidden)
+    indices, weights = moe_route(router_logits.reshape(-1, experts).float(), int(top_k))
+    rows, _, offsets, _, pos = moe_permute(flat, indices, experts)
+    hidden_act = moe_grouped_gemm(rows, gate_weight, offsets, up_weight)
+    out_rows = moe_grouped_gemm(hidden_act, down_weight, offsets)
+    return moe_unpermute(out_rows, weights, pos).reshape(x.shape)
+
+
 def _pointer_array(pointers: list[int]) -> ctypes.Array:
     return (ctypes.c_void_p * len(pointers))(*pointers)
 

@@ -4,7 +4,7 @@
     popcorn_b200.plugin.register()            # needs `popcorn` importable
     popcorn.KERNELS["rms_norm"](x, w, backend="b200")
 
-For the ten ops popcorn already defines, this is one `op.register(name,
+For the eleven ops popcorn already defines, this is one `op.register(name,
 source=..., forward_only=True)` line each, the same form popcorn's own backends
 use (src/popcorn/kernels/rms_norm.py:33-59, add_rms_norm.py:26-28,
 rotary_embedding.py:43-45, rope.py:39, swiglu.py:21-31).  The sources are bare: each
@@ -27,7 +27,7 @@ import torch
 from torch import Tensor
 
 BACKEND = "b200"
-EXISTING_OPS = ("rms_norm", "add_rms_norm", "rotary_embedding", "rope", "llama4_rope", "swiglu", "geglu", "rms_norm_gated", "l2_norm", "layer_norm")
+EXISTING_OPS = ("rms_norm", "add_rms_norm", "rotary_embedding", "rope", "llama4_rope", "swiglu", "geglu", "rms_norm_gated", "l2_norm", "layer_norm", "momoe")
 NEW_OPS = ("moe_route", "moe_permute", "moe_unpermute", "qk_norm_rope")
 DIFFERENTIABLE_OPS = ("rms_norm", "add_rms_norm", "swiglu", "rotary_embedding")
 
@@ -40,6 +40,18 @@ def accepts(**arguments: Any) -> bool:
     return bool(tensors) and all(
         t.is_cuda and (not t.is_floating_point() or t.dtype in _SUPPORTED) for t in tensors
     )
+
+
+def accepts_16bit(**arguments: Any) -> bool:
+    """`accepts`, narrowed to bf16 / fp16 activations with weights of the same dtype: the expert projections of
+    momoe run on 16-bit tensor-core operands (router logits may be any supported float dtype)."""
+    x = arguments.get("x")
+    if not accepts(**arguments) or not isinstance(x, Tensor) or x.dtype not in (torch.float16, torch.bfloat16):
+        return False
+    return all(t.dtype == x.dtype for name, t in arguments.items() if isinstance(t, Tensor) and name.endswith("_weight"))
+
+
+PREDICATES = {"momoe": accepts_16bit}
 
 
 def _define_moe_ops(popcorn: Any) -> None:
@@ -141,9 +153,10 @@ def register(backend: str = BACKEND) -> list[str]:
     for name in (*EXISTING_OPS, *NEW_OPS):
         op = popcorn.KERNELS[name]
         if backend not in op.available_backends():
+            predicate = PREDICATES.get(name, accepts)
             if name in DIFFERENTIABLE_OPS:  # backward kernels exist: serve training calls too
-                op.register(backend, source=f"popcorn_b200.autograd.{name}", predicate=accepts)
+                op.register(backend, source=f"popcorn_b200.autograd.{name}", predicate=predicate)
             else:
-                op.register(backend, source=f"popcorn_b200.ops.{name}", predicate=accepts, forward_only=True)
+                op.register(backend, source=f"popcorn_b200.ops.{name}", predicate=predicate, forward_only=True)
         served.append(name)
     return served

@@ -96,6 +96,21 @@ def test_golden_momoe_through_the_grouped_projections(name):
     assert _lib.wait_timeouts() == 0
 
 
+@pytest.mark.parametrize("name", [n for n in case_names() if n.startswith("moe16")])
+def test_golden_momoe_op(name):
+    """The registered op itself, through the registry mirror, against the reference's output."""
+    from popcorn_b200 import kernels
+
+    t, meta = load_case(name)
+    y = kernels.momoe(gpu(t["x"]), gpu(t["gate_weight"]), gpu(t["up_weight"]), gpu(t["down_weight"]), gpu(t["router_logits"]),
+                      meta["top_k"], backend="b200")
+    assert y.shape == t["y"].shape and y.dtype == t["y"].dtype
+    assert float((y.cpu().float() - t["y"].float()).abs().max()) <= 2e-2, name
+    with pytest.raises(TypeError):
+        ops.momoe(gpu(t["x"].float()), gpu(t["gate_weight"].float()), gpu(t["up_weight"].float()), gpu(t["down_weight"].float()),
+                  gpu(t["router_logits"]), meta["top_k"])
+
+
 def test_empty_and_rejected_inputs():
     rows, weight, _, offsets = make([4, 4], 16, 16, BF16, 5300)
     empty = ops.moe_grouped_gemm(gpu(rows[:0]), gpu(weight), gpu(torch.zeros(3, dtype=torch.int32)))

@@ -147,6 +147,12 @@ def test_plugin_registers_on_real_popcorn(tmp_path, monkeypatch):
     impl = popcorn.KERNELS["rope"]["b200"]
     impl._prepare()
     assert impl.source_fn is ops.rope
+    for name in ("momoe", "llama4_rope", "qk_norm_rope"):
+        impl = popcorn.KERNELS[name]["b200"]
+        impl._prepare()  # the bare source must accept the reference's parameters positionally
+        assert impl.source_fn is getattr(ops, name)
+    # momoe is served for 16-bit activations only (tensor-core operands)
+    assert not plugin.accepts_16bit(x=torch.zeros(1, 2, 8), gate_weight=torch.zeros(2, 8, 8))
     # CPU calls are declined by the predicate rather than served by a fallback
     x = torch.randn(4, 8)
     with pytest.raises(popcorn.core.errors.DispatchError, match="rejected"):
