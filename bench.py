@@ -431,6 +431,17 @@ def bench_grouped_gemm(device, sampler, scale: float = 1.0, steps: int = 10, war
         result[name] = {"ms": round(ms, 4), "tflop_s": round(tflops, 1), "flop": flop, "frac_of_measured_burst": round(tflops / burst, 4),
                         "frac_of_measured_sustained": round(tflops / sustained, 4)}
     result["wait_timeouts"] = _lib.wait_timeouts()
+    # the library GEMM on the same box in the same run, same flop count: one batched cuBLAS matmul per projection over
+    # equal-size experts (total / experts rows each), without the SwiGLU epilogue and writing both projections out
+    if total % experts == 0:
+        per = total // experts
+        a3 = rows.view(experts, per, hidden)
+        gate_up_w = torch.cat((gate, up), dim=2)
+        act3 = act.view(experts, per, inter)
+        for name, fn, flop in (("cublas_bmm_gate_up", lambda i: torch.bmm(a3, gate_up_w), 2.0 * total * hidden * 2 * inter),
+                               ("cublas_bmm_down", lambda i: torch.bmm(act3, down), 2.0 * total * inter * hidden)):
+            ms = time_launches(fn, steps, warmup, device)
+            result[name] = {"ms": round(ms, 4), "tflop_s": round(flop / (ms * 1e-3) / 1e12, 1)}
     return result
 
 

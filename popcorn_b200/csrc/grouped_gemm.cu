@@ -14,7 +14,7 @@
 // side by side in one accumulator) of one expert:
 //   warp 0     producer: one lane issues tiled bulk-tensor copies (TMA, 128-byte swizzle) of the
 //              128 x 64 slice of `rows` and the 64 x 256 slice of the expert's weight into a
-//              4-slot shared-memory ring, completion counted on a `full` mbarrier per slot
+//              shared-memory ring, completion counted on a `full` mbarrier per slot
 //   warp 1     one lane issues tcgen05.mma (M 128, N 256, K 16; A K-major, B N-major straight from
 //              the reference's weight layout) into one of two 256-column fp32 accumulators in
 //              tensor memory; tcgen05.commit releases the ring slot and, after the last K slice,
@@ -26,11 +26,20 @@
 // CTAs are persistent (one per SM) and walk the tile list (expert, n tile, m tile) derived on the
 // device from `offsets`, so the host never reads the routing result.
 //
+// Pair mode (the default): two CTAs of a cluster work as one (tcgen05 cta_group::2) on a 256 x 256
+// tile.  Each loads its own 128 rows and only HALF of the weight slice (128 of the 256 columns), the
+// leader's MMA reads both halves across the pair, so per SM the shared-memory fill drops from 48 to
+// 32 KiB per K slice and the ring holds 6 slices instead of 4.  Copies of both CTAs complete on the
+// leader's `full` barrier; the leader's tcgen05.commit reaches the `empty` and `acc_full` barriers of
+// both CTAs; both epilogues arrive on the leader's `acc_empty`.
+//
 // Every wait is bounded (tma.cuh): a wait that runs out marks the CTA aborted, every role leaves
 // its loop, the CTA waits (bounded again) for copies and MMAs it still has in flight, frees its
 // tensor memory and returns; b200_wait_timeouts() reports it.
 #include <cuda.h>
 
+#include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 #include "activations.cuh"
@@ -40,50 +49,132 @@
 namespace b200 {
 namespace {
 
-constexpr int kBM = 128, kBN = 256, kBK = 64, kStages = 4, kUmmaK = 16;
+constexpr int kBM = 128, kBN = 256, kBK = 64, kUmmaK = 16;
 constexpr int kABytes = kBM * kBK * 2;           // 16 KiB
 constexpr int kBChunkBytes = kBK * 128;          // one 64-column chunk of the weight slice: 64 rows of 128 bytes
-constexpr int kBBytes = kBChunkBytes * (kBN / 64);  // 32 KiB
-constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + slack to align the ring to the swizzle atom
+constexpr int kMaxStages = 6;
+// Per CTA, with CTAS = 1 (alone) or 2 (pair): the weight columns it loads, its ring slot and ring depth.
+template <int CTAS>
+struct Ring {
+  static constexpr int kChunks = kBN / 64 / CTAS;            // 64-column chunks of the weight slice this CTA loads
+  static constexpr int kStageBytes = kABytes + kChunks * kBChunkBytes;  // 48 or 32 KiB
+  static constexpr int kStages = CTAS == 2 ? 6 : 4;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + slack to align the ring to the swizzle atom
+};
 constexpr int kTmemCols = 512;                   // two accumulators of kBN fp32 columns
 constexpr int kMaxExperts = 1024;
 constexpr int kThreads = 192;
 
-// ---- tcgen05 / tensor-map wrappers (this CTA only: cta_group::1, no multicast anywhere) ----
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(smem_addr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_addr(bar))
-               : "memory");
+// ---- tcgen05 / tensor-map wrappers; PAIR = the cta_group::2 forms.  No copy is addressed to more than one CTA. ----
+//
+// The producer and the MMA issuer are single threads whose instruction streams run beside a tensor pipe that
+// finishes a K slice every ~512 cycles, so their inner loops work on raw 32-bit shared-memory addresses and
+// counters that wrap (no division, no address conversion per copy).
+__device__ __forceinline__ bool mbar_wait_addr(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  atomicAdd(&g_wait_timeouts, 1u);
+  return false;
 }
-__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
-  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-               ::"r"(smem_addr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(smem_addr(bar))
-               : "memory");
+__device__ __forceinline__ void mbar_arrive_expect_addr(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// Tiled bulk-tensor copies into THIS CTA's shared memory; in a pair the bytes are counted on a barrier of the leader.
+template <bool PAIR>
+__device__ __forceinline__ void tma_2d(uint32_t dst, uint64_t map, int x, int y, uint32_t bar) {
+  if constexpr (PAIR)
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+  else
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+template <bool PAIR>
+__device__ __forceinline__ void tma_3d(uint32_t dst, uint64_t map, int x, int y, int z, uint32_t bar) {
+  if constexpr (PAIR)
+    asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
+  else
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
+}
+template <bool PAIR>
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(slot)), "r"(cols) : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  if constexpr (PAIR) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(slot)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  } else {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(slot)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
 }
+template <bool PAIR>
 __device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+  if constexpr (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+  else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-// Arrives once on `bar` when every tcgen05.mma this thread issued before has completed.
-__device__ __forceinline__ void mma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+// Arrives on `bar` (in a pair: on the barrier at that offset in BOTH CTAs) when every tcgen05.mma this thread
+// issued before has completed.
+template <bool PAIR>
+__device__ __forceinline__ void mma_commit_addr(uint32_t bar) {
+  if constexpr (PAIR)
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(static_cast<uint16_t>(3)) : "memory");
+  else
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-// D[tmem] (+)= A[smem] * B[smem]; `accumulate` = 0 overwrites D.
-__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-      ::"r"(d_tmem), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
-      : "memory");
+// D[tmem] (+)= A[smem] * B[smem] with the descriptors given as (low word, shared high word); `accumulate` = 0
+// overwrites D.  In a pair M is 256: each CTA contributes its 128 rows of A and its half of B and receives its
+// 128 rows of D.
+template <bool PAIR>
+__device__ __forceinline__ void mma_issue(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t a_hi, uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  if constexpr (PAIR)
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, {%7, %7, %7, %7, %7, %7, %7, %7}, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(a_hi), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+  else
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, {%7, %7, %7, %7}, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(a_hi), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
 }
+// ---- cluster helpers for the pair ----
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// The shared::cluster address of this CTA's shared-memory location `local` in the CTA of rank `rank`.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void remote_arrive(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // 32 lanes x 32 consecutive fp32 columns of tensor memory: lane l of the warp receives row (quarter * 32 + l).
 __device__ __forceinline__ void tmem_load_32(uint32_t addr, uint32_t (&v)[32]) {
   asm volatile(
@@ -108,14 +199,11 @@ __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::l
 constexpr uint64_t kDescFixed = (uint64_t(1) << 46) | (uint64_t(2) << 61);
 constexpr uint64_t kDescA = kDescFixed | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32);
 constexpr uint64_t kDescB = kDescFixed | (uint64_t(kBChunkBytes >> 4) << 16) | (uint64_t(1024 >> 4) << 32);
-__device__ __forceinline__ uint64_t desc_at(uint64_t fixed, uint32_t smem_byte_addr) {
-  return fixed | ((smem_byte_addr >> 4) & 0x3fffu);
-}
 
 // Instruction descriptor of kind::f16: fp32 accumulate (bit 4), A/B format (0 fp16, 1 bf16) at bits 7
-// and 10, A K-major (bit 15 = 0), B N-major (bit 16 = 1), N >> 3 at bit 17, M >> 4 at bit 24.
-__host__ __device__ constexpr uint32_t instr_desc(uint32_t format) {
-  return (1u << 4) | (format << 7) | (format << 10) | (1u << 16) | (uint32_t(kBN >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
+// and 10, A K-major (bit 15 = 0), B N-major (bit 16 = 1), N >> 3 at bit 17, M >> 4 at bit 24 (M = 256 for a pair).
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t format, int ctas) {
+  return (1u << 4) | (format << 7) | (format << 10) | (1u << 16) | (uint32_t(kBN >> 3) << 17) | (uint32_t((kBM * ctas) >> 4) << 24);
 }
 
 struct GemmArgs {
@@ -134,7 +222,7 @@ struct Tile {
 
 // tile -> (expert, m tile, n tile): tiles of one expert are consecutive, m fastest, so that CTAs running
 // together share the expert's weight slice in L2.
-__device__ __forceinline__ Tile decode_tile(int tile, const int* tile_start, const int32_t* offsets, int experts, int out_tile_n) {
+__device__ __forceinline__ Tile decode_tile(int tile, const int* tile_start, const int32_t* offsets, int experts, int out_tile_n, int tile_rows) {
   int lo = 0, hi = experts;  // last expert with tile_start[e] <= tile
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
@@ -142,33 +230,39 @@ __device__ __forceinline__ Tile decode_tile(int tile, const int* tile_start, con
     else hi = mid;
   }
   const int first = offsets[lo], end = offsets[lo + 1];
-  const int tiles_m = (end - first + kBM - 1) / kBM;
+  const int tiles_m = (end - first + tile_rows - 1) / tile_rows;
   const int local = tile - tile_start[lo];
   Tile t;
   t.expert = lo;
-  t.row0 = first + (local % tiles_m) * kBM;
+  t.row0 = first + (local % tiles_m) * tile_rows;
   t.row_end = end;
   t.n0 = (local / tiles_m) * out_tile_n;
   return t;
 }
 
-template <typename T, bool DUAL>
+template <typename T, bool DUAL, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_w2, const GemmArgs p) {
+  using R = Ring<CTAS>;
+  constexpr bool PAIR = CTAS == 2;
   constexpr int OUT_N = DUAL ? kBN / 2 : kBN;  // output columns per tile
+  constexpr int STAGES = R::kStages;
+  constexpr int TILE_ROWS = kBM * CTAS;
   pdl_prologue();
   extern __shared__ unsigned char smem_raw[];
-  __shared__ uint64_t full[kStages], empty[kStages], acc_full[2], acc_empty[2];
+  __shared__ uint64_t full[kMaxStages], empty[kMaxStages], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int aborted;
   __shared__ int tile_start[kMaxExperts + 1];
   __shared__ uint4 staging[4][32][8];  // per epilogue warp: 32 rows x 128 bytes of finished output
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = PAIR ? cluster_rank() : 0u;  // position in the pair; rank 0 leads
+  const int first_tile = PAIR ? blockIdx.x / 2 : blockIdx.x;
+  const int tile_step = PAIR ? gridDim.x / 2 : gridDim.x;
   unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tiles_n = (p.n + OUT_N - 1) / OUT_N;
-  const int num_kb = (p.k + kBK - 1) / kBK;
 
   if (threadIdx.x == 0) {
     aborted = 0;
@@ -176,91 +270,113 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     for (int e = 0; e < p.experts; ++e) {
       tile_start[e] = total;
       const int count = p.offsets[e + 1] - p.offsets[e];
-      total += (count > 0 ? (count + kBM - 1) / kBM : 0) * tiles_n;
+      total += (count > 0 ? (count + TILE_ROWS - 1) / TILE_ROWS : 0) * tiles_n;
     }
     tile_start[p.experts] = total;
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 4);  // one arrival per epilogue warp
+      mbar_init(&acc_empty[a], 4 * CTAS);  // one arrival per epilogue warp (of both CTAs in a pair)
     }
     mbar_init_fence();
   }
-  if (warp == 1) tmem_alloc(&tmem_base_slot, kTmemCols);
+  if (warp == 1) tmem_alloc<PAIR>(&tmem_base_slot, kTmemCols);
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync();  // the peer's barriers exist before anything is signalled on them
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   const int total_tiles = tile_start[p.experts];
   volatile int* abort_flag = &aborted;
+  const uint32_t ring_addr = smem_addr(ring), full_addr = smem_addr(&full[0]), empty_addr = smem_addr(&empty[0]);
 
   if (warp == 0) {
     // ------------------------------------------------------------- producer --
     if (lane == 0) {
-      uint32_t it = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
-        const Tile t = decode_tile(tile, tile_start, p.offsets, p.experts, OUT_N);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % kStages;
-          if (!mbar_wait(&empty[s], ((it / kStages) & 1u) ^ 1u)) {
+      uint32_t stage = 0, phase = 0, issued = 0;
+      // the barrier the copies complete on: this CTA's own, or in a pair the leader's
+      const uint32_t signal_addr = PAIR ? map_to_rank(full_addr, 0) : full_addr;
+      const uint64_t rows_map = reinterpret_cast<uint64_t>(&map_rows), w2_map = reinterpret_cast<uint64_t>(&map_w2);
+      // this CTA's share of the 256 accumulator columns: all of them alone, one half in a pair
+      // (DUAL: columns 0-127 are the gate projection, 128-255 the up projection of the same output columns)
+      const uint64_t b_map = (DUAL && PAIR && rank == 1) ? w2_map : reinterpret_cast<uint64_t>(&map_w);
+      for (int tile = first_tile; tile < total_tiles && !*abort_flag; tile += tile_step) {
+        const Tile t = decode_tile(tile, tile_start, p.offsets, p.experts, OUT_N, TILE_ROWS);
+        const int row0 = t.row0 + static_cast<int>(rank) * kBM;
+        const int col0 = t.n0 + ((!DUAL && PAIR) ? static_cast<int>(rank) * (kBN / 2) : 0);
+        for (int k0 = 0; k0 < p.k; k0 += kBK) {
+          if (!mbar_wait_addr(empty_addr + stage * 8, phase ^ 1u)) {
             *abort_flag = 1;
             break;
           }
-          unsigned char* a_dst = ring + s * kStageBytes;
-          unsigned char* b_dst = a_dst + kABytes;
-          mbar_arrive_expect(&full[s], kStageBytes);
-          tma_load_2d(a_dst, &map_rows, kb * kBK, t.row0, &full[s]);
+          const uint32_t a_dst = ring_addr + stage * R::kStageBytes, b_dst = a_dst + kABytes, bar = signal_addr + stage * 8;
+          if (rank == 0) mbar_arrive_expect_addr(full_addr + stage * 8, CTAS * R::kStageBytes);  // in a pair both CTAs' bytes land here
+          tma_2d<PAIR>(a_dst, rows_map, k0, row0, bar);
 #pragma unroll
-          for (int c = 0; c < kBN / 64; ++c) {
-            if (DUAL && c >= kBN / 128) tma_load_3d(b_dst + c * kBChunkBytes, &map_w2, t.n0 + (c - kBN / 128) * 64, kb * kBK, t.expert, &full[s]);
-            else tma_load_3d(b_dst + c * kBChunkBytes, &map_w, t.n0 + c * 64, kb * kBK, t.expert, &full[s]);
+          for (int c = 0; c < R::kChunks; ++c) {
+            if (DUAL && !PAIR && c >= R::kChunks / 2) tma_3d<PAIR>(b_dst + c * kBChunkBytes, w2_map, t.n0 + (c - R::kChunks / 2) * 64, k0, t.expert, bar);
+            else tma_3d<PAIR>(b_dst + c * kBChunkBytes, b_map, col0 + c * 64, k0, t.expert, bar);
+          }
+          ++issued;
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
           }
         }
       }
-      if (*abort_flag) {
-        // copies already issued still write this CTA's shared memory: give each slot's last copy a bounded wait
-        for (uint32_t k = it > kStages ? it - kStages : 0; k < it; ++k) (void)mbar_wait(&full[k % kStages], (k / kStages) & 1u);
+      if (*abort_flag && rank == 0) {
+        // copies already issued (by either CTA of a pair) still write shared memory: give each slot's last copy a bounded wait
+        for (uint32_t k = issued > STAGES ? issued - STAGES : 0; k < issued; ++k) (void)mbar_wait(&full[k % STAGES], (k / STAGES) & 1u);
       }
     }
   } else if (warp == 1) {
     // ----------------------------------------------------------- MMA issuer --
-    if (lane == 0) {
-      uint32_t it = 0, local = 0;
+    if (lane == 0 && rank == 0) {
+      uint32_t stage = 0, phase = 0, local = 0;
       bool pending = false;
-      for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++local) {
+      const uint32_t acc_full_addr = smem_addr(&acc_full[0]), acc_empty_addr = smem_addr(&acc_empty[0]);
+      const uint32_t a_hi = static_cast<uint32_t>(kDescA >> 32), b_hi = static_cast<uint32_t>(kDescB >> 32);
+      const uint32_t a_lo0 = static_cast<uint32_t>(kDescA) | (ring_addr >> 4), b_lo0 = static_cast<uint32_t>(kDescB) | ((ring_addr + kABytes) >> 4);
+      const uint32_t idesc = p.idesc;
+      for (int tile = first_tile; tile < total_tiles && !*abort_flag; tile += tile_step, ++local) {
         const uint32_t acc = local & 1u;
-        if (!mbar_wait(&acc_empty[acc], ((local >> 1) & 1u) ^ 1u)) {
+        if (!mbar_wait_addr(acc_empty_addr + acc * 8, ((local >> 1) & 1u) ^ 1u)) {
           *abort_flag = 1;
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kBN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % kStages;
-          if (!mbar_wait(&full[s], (it / kStages) & 1u)) {
+        uint32_t accumulate = 0;
+        for (int k0 = 0; k0 < p.k; k0 += kBK) {
+          if (!mbar_wait_addr(full_addr + stage * 8, phase)) {
             *abort_flag = 1;
             break;
           }
           tc_fence_after();
-          const uint32_t a_addr = smem_addr(ring + s * kStageBytes), b_addr = a_addr + kABytes;
+          // descriptor start fields advance in 16-byte units: a ring slot, then per MMA 16 K values = 32 bytes along
+          // A's swizzled 128-byte rows and 16 K rows = 2048 bytes of B
+          const uint32_t a_lo = a_lo0 + stage * (R::kStageBytes >> 4), b_lo = b_lo0 + stage * (R::kStageBytes >> 4);
 #pragma unroll
           for (int k = 0; k < kBK / kUmmaK; ++k) {
-            // A: 16 K values = 32 bytes further along the swizzled 128-byte rows; B: 16 K rows = 2048 bytes further
-            mma_f16(d_tmem, desc_at(kDescA, a_addr + k * kUmmaK * 2), desc_at(kDescB, b_addr + k * kUmmaK * 128), p.idesc,
-                    (kb | k) != 0 ? 1u : 0u);
+            mma_issue<PAIR>(d_tmem, a_lo + k * (kUmmaK * 2 >> 4), b_lo + k * (kUmmaK * 128 >> 4), a_hi, b_hi, idesc, accumulate);
+            accumulate = 1;
           }
-          mma_commit(&empty[s]);  // the slot is free once these MMAs have read it
+          mma_commit_addr<PAIR>(empty_addr + stage * 8);  // the slot (in both CTAs of a pair) is free once these MMAs have read it
           pending = true;
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
         }
         if (*abort_flag) break;
-        mma_commit(&acc_full[acc]);
+        mma_commit_addr<PAIR>(acc_full_addr + acc * 8);
       }
       if (*abort_flag && pending) {
         // MMAs may still be running: a bounded wait on a fresh commit before tensor memory is freed
-        mma_commit(&acc_full[0]);
+        mma_commit_addr<PAIR>(acc_full_addr);
         (void)mbar_wait(&acc_full[0], 0);
         (void)mbar_wait(&acc_full[0], 1);
       }
@@ -270,16 +386,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     const int quarter = warp & 3;  // the 32 tensor-memory lanes this warp may read
     uint32_t local = 0;
     T* out = static_cast<T*>(p.out);
-    for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++local) {
-      const Tile t = decode_tile(tile, tile_start, p.offsets, p.experts, OUT_N);
+    for (int tile = first_tile; tile < total_tiles && !*abort_flag; tile += tile_step, ++local) {
+      const Tile t = decode_tile(tile, tile_start, p.offsets, p.experts, OUT_N, TILE_ROWS);
       const uint32_t acc = local & 1u;
-      if (!mbar_wait(&acc_full[acc], (local >> 1) & 1u)) {
+      // one lane polls for the whole warp
+      const int ready = __shfl_sync(0xffffffffu, lane == 0 ? static_cast<int>(mbar_wait(&acc_full[acc], (local >> 1) & 1u)) : 0, 0);
+      if (!ready) {
         *abort_flag = 1;
         break;
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * kBN + (static_cast<uint32_t>(quarter * 32) << 16);
-      const int warp_row0 = t.row0 + quarter * 32;
+      const int warp_row0 = t.row0 + static_cast<int>(rank) * kBM + quarter * 32;
       uint4(*mine)[8] = staging[quarter];
 #pragma unroll 1
       for (int c = 0; c < OUT_N / 32; ++c) {
@@ -320,13 +438,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (lane == 0) {
+        if constexpr (PAIR) remote_arrive(map_to_rank(smem_addr(&acc_empty[acc]), 0));  // the leader issues the MMAs
+        else mbar_arrive(&acc_empty[acc]);
+      }
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if constexpr (PAIR) cluster_sync();  // neither CTA leaves while the other may still read its shared memory or signal its barriers
+  if (warp == 1) tmem_dealloc<PAIR>(tmem_base, kTmemCols);
 }
 
 // ------------------------------------------------------------------ host side --
@@ -369,15 +491,66 @@ bool encode_weight(CUtensorMap* map, CUtensorMapDataType type, const void* base,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <typename T, bool DUAL>
-int run(const CUtensorMap& rows, const CUtensorMap& w, const CUtensorMap& w2, const GemmArgs& args, cudaStream_t st) {
-  auto kernel = grouped_gemm_kernel<T, DUAL>;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) {
+// B200_GEMM_PAIR=0 in the environment runs every CTA on its own (cta_group::1); read at every call.
+bool pair_enabled() {
+  const char* v = std::getenv("B200_GEMM_PAIR");
+  return !(v && v[0] == '0');
+}
+
+constexpr int kNoClusters = -1000;  // run_with<., ., 2>: no cluster of two CTAs can be resident; the caller runs single CTAs instead
+
+template <typename T, bool DUAL, int CTAS>
+int run_with(const CUtensorMap& rows, const CUtensorMap& w, const CUtensorMap& w2, GemmArgs args, uint32_t format, cudaStream_t st) {
+  auto kernel = grouped_gemm_kernel<T, DUAL, CTAS>;
+  constexpr int smem = Ring<CTAS>::kSmemBytes;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
     (void)cudaGetLastError();
-    return fail(B200_ERR_LAUNCH, "b200_moe_grouped_gemm: cannot reserve %d bytes of shared memory", kSmemBytes);
+    return fail(B200_ERR_LAUNCH, "b200_moe_grouped_gemm: cannot reserve %d bytes of shared memory", smem);
   }
-  launch(kernel, static_cast<unsigned>(sm_count()), kThreads, kSmemBytes, st, rows, w, w2, args);
-  return after_launch("grouped_gemm_kernel");
+  args.idesc = instr_desc(format, CTAS);
+  cudaLaunchConfig_t config = {};
+  config.blockDim = dim3(kThreads);
+  config.dynamicSmemBytes = smem;
+  config.stream = st;
+  cudaLaunchAttribute attrs[2];
+  unsigned n_attrs = 0;
+  if (CTAS == 2) {
+    attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;
+    attrs[n_attrs].val.clusterDim.x = 2;
+    attrs[n_attrs].val.clusterDim.y = 1;
+    attrs[n_attrs].val.clusterDim.z = 1;
+    ++n_attrs;
+  }
+  config.attrs = attrs;
+  config.numAttrs = n_attrs;
+  int ctas = sm_count();
+  if (CTAS == 2) {
+    // persistent pairs: as many clusters as can be resident at once (an odd SM of a processing cluster has no partner)
+    config.gridDim = dim3(static_cast<unsigned>(ctas & ~1));
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess || clusters < 1) {
+      (void)cudaGetLastError();
+      return kNoClusters;
+    }
+    ctas = 2 * std::min(clusters, ctas / 2);
+  }
+  config.gridDim = dim3(static_cast<unsigned>(ctas));
+  if (pdl_enabled()) {
+    attrs[n_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n_attrs].val.programmaticStreamSerializationAllowed = 1;
+    config.numAttrs = ++n_attrs;
+  }
+  (void)cudaLaunchKernelEx(&config, kernel, rows, w, w2, args);
+  return after_launch(CTAS == 2 ? "grouped_gemm_kernel (pairs)" : "grouped_gemm_kernel");
+}
+
+template <typename T, bool DUAL>
+int run(const CUtensorMap& rows, const CUtensorMap& w, const CUtensorMap& w2, const GemmArgs& args, uint32_t format, cudaStream_t st) {
+  if (pair_enabled()) {
+    const int rc = run_with<T, DUAL, 2>(rows, w, w2, args, format, st);
+    if (rc != kNoClusters) return rc;
+  }
+  return run_with<T, DUAL, 1>(rows, w, w2, args, format, st);
 }
 
 }  // namespace
@@ -423,8 +596,8 @@ extern "C" int b200_moe_grouped_gemm(const void* rows, const void* weight, const
   args.experts = static_cast<int>(experts);
   args.n = static_cast<int>(n);
   args.k = static_cast<int>(k);
-  args.idesc = instr_desc(dtype == B200_BF16 ? 1u : 0u);
+  const uint32_t format = dtype == B200_BF16 ? 1u : 0u;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == B200_BF16) return weight2 ? run<__nv_bfloat16, true>(map_rows, map_w, map_w2, args, st) : run<__nv_bfloat16, false>(map_rows, map_w, map_w2, args, st);
-  return weight2 ? run<__half, true>(map_rows, map_w, map_w2, args, st) : run<__half, false>(map_rows, map_w, map_w2, args, st);
+  if (dtype == B200_BF16) return weight2 ? run<__nv_bfloat16, true>(map_rows, map_w, map_w2, args, format, st) : run<__nv_bfloat16, false>(map_rows, map_w, map_w2, args, format, st);
+  return weight2 ? run<__half, true>(map_rows, map_w, map_w2, args, format, st) : run<__half, false>(map_rows, map_w, map_w2, args, format, st);
 }
