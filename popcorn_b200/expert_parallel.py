@@ -236,3 +236,18 @@ class ExpertParallel:
         returned = torch.empty((sum(state.send_counts), expert_rows.shape[1]), dtype=expert_rows.dtype, device=expert_rows.device)
         dist.all_to_all_single(returned, outbound, state.send_counts, state.recv_counts, group=self.group)
         return ops.moe_unpermute(returned, state.weights, state.pos)
+
+    def momoe(self, x: Tensor, router_logits: Tensor, gate_weight: Tensor, up_weight: Tensor, down_weight: Tensor) -> Tensor:
+        """The whole expert-parallel MoE layer for this rank's tokens: dispatch, the SwiGLU expert MLPs of this rank's
+        experts on the tensor cores, combine (momoe of src/popcorn/kernels/momoe.py:34-53, sharded).
+
+        gate_weight / up_weight: [local_experts, hidden, intermediate], down_weight: [local_experts, intermediate, hidden]
+        — this rank's contiguous block of experts.  With exchange="p2p" the down projection writes straight into the
+        symmetric buffer the peers combine from."""
+        if gate_weight.shape[0] != self.local_experts:
+            raise ValueError(f"expected the weights of this rank's {self.local_experts} experts, got {gate_weight.shape[0]}")
+        state = self.dispatch(x, router_logits)
+        offsets = state.expert_offsets.to(x.device, non_blocking=True)
+        hidden_act = self.ops.moe_grouped_gemm(state.rows, gate_weight, offsets, up_weight)
+        expert_rows = self.ops.moe_grouped_gemm(hidden_act, down_weight, offsets, None, state.out_rows)
+        return self.combine(expert_rows, state)

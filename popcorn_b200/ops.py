@@ -556,13 +556,14 @@ def moe_unpermute(rows: Tensor, weights: Tensor, pos: Tensor) -> Tensor:
     return y
 
 
-def moe_grouped_gemm(rows: Tensor, weight: Tensor, offsets: Tensor, up_weight: Tensor | None = None) -> Tensor:
+def moe_grouped_gemm(rows: Tensor, weight: Tensor, offsets: Tensor, up_weight: Tensor | None = None, out: Tensor | None = None) -> Tensor:
     """Expert MLP projection over the expert-major rows of `moe_permute` (momoe.py:50-52, momoe_tl.py:90-330).
 
     out[p] = rows[p] @ weight[e(p)], or silu(rows[p] @ weight[e(p)]) * (rows[p] @ up_weight[e(p)]) when `up_weight`
     is given (`weight` is then the gate projection); e(p) is the expert whose segment [offsets[e], offsets[e+1])
     holds row p.  weight: [experts, in_features, out_features] as in the reference; fp32 accumulation on the tensor
-    cores, one rounding to the dtype of rows.  Rows outside every segment are zero."""
+    cores, one rounding to the dtype of rows.  Rows outside every segment are zero, or left as they are when the
+    caller supplies `out` ([n, out_features], contiguous rows)."""
     device = _require_cuda(rows, weight, offsets, *([up_weight] if up_weight is not None else []))
     _forbid_grad(rows, weight)
     code = _dtype_code(rows, "moe_grouped_gemm")
@@ -577,11 +578,15 @@ def moe_grouped_gemm(rows: Tensor, weight: Tensor, offsets: Tensor, up_weight: T
         raise TypeError("moe_grouped_gemm: offsets must be int32 [experts + 1]")
     r2, ldr = _rows(rows)
     total = r2.shape[0]
-    out = torch.zeros((total, n), dtype=rows.dtype, device=device) if total else torch.empty((0, n), dtype=rows.dtype, device=device)
+    if out is None:
+        out = torch.zeros((total, n), dtype=rows.dtype, device=device) if total else torch.empty((0, n), dtype=rows.dtype, device=device)
+    elif out.shape != (total, n) or out.dtype != rows.dtype or out.device != device or (total and n > 1 and out.stride(1) != 1):
+        raise ValueError("moe_grouped_gemm: out must be [n, out_features] in the dtype and on the device of rows")
+    ldo = out.stride(0) if total > 1 else max(n, 1)
     with torch.cuda.device(device):
         _lib.call(
             "b200_moe_grouped_gemm", _ptr(r2), _ptr(weight.contiguous()), _ptr(None if up_weight is None else up_weight.contiguous()),
-            _ptr(offsets.contiguous()), _ptr(out), total, k, n, experts, ldr, max(n, 1), code, _stream(device),
+            _ptr(offsets.contiguous()), _ptr(out), total, k, n, experts, ldr, ldo, code, _stream(device),
         )
     return out
 

@@ -67,3 +67,50 @@ def test_dispatch_and_combine_on_two_gpus(exchange):
     # the kernel's routing weights differ from the oracle's in the last fp32 bit
     assert float((got.float() - want.float()).abs().max()) <= 2e-2
     assert float((got == want).float().mean()) > 0.99
+
+
+def _mlp_weights(experts, hidden, inter):
+    gen = torch.Generator().manual_seed(22)
+    make = lambda a, b: (torch.randn(experts, a, b, generator=gen) / a ** 0.5).to(torch.bfloat16)  # noqa: E731
+    return make(hidden, inter), make(hidden, inter), make(inter, hidden)
+
+
+def _layer_worker(rank, world, port, tokens, hidden, inter, experts, top_k, exchange, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    device = torch.device("cuda", rank)
+    torch.cuda.set_device(device)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        from popcorn_b200.expert_parallel import ExpertParallel
+
+        x, logits = _inputs(tokens, hidden, experts)
+        gate, up, down = _mlp_weights(experts, hidden, inter)
+        lo, hi = tokens * rank // world, tokens * (rank + 1) // world
+        per = experts // world
+        mine = slice(rank * per, (rank + 1) * per)
+        ep = ExpertParallel(experts, top_k, exchange=exchange)
+        for _ in range(2):
+            y = ep.momoe(x[lo:hi].to(device), logits[lo:hi].to(device), gate[mine].to(device), up[mine].to(device), down[mine].to(device))
+        torch.cuda.synchronize(device)
+        out[rank] = y.cpu()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("exchange", ["nccl", "p2p"])
+def test_whole_moe_layer_on_two_gpus(exchange):
+    """dispatch -> tensor-core expert MLPs on each rank's experts -> combine equals the single-device chain."""
+    world, tokens, hidden, inter, experts, top_k = 2, 2048, 512, 256, 8, 2
+    out = mp.Manager().dict()
+    mp.spawn(_layer_worker, args=(world, _free_port(), tokens, hidden, inter, experts, top_k, exchange, out), nprocs=world, join=True)
+    x, logits = _inputs(tokens, hidden, experts)
+    gate, up, down = _mlp_weights(experts, hidden, inter)
+    indices, weights = oracle.moe_route(logits, top_k)
+    rows, _, offsets, _, pos = oracle.moe_permute(x, indices, experts)
+    hidden_act = oracle.moe_grouped_gemm(rows, gate, offsets, up)
+    want = oracle.moe_unpermute(oracle.moe_grouped_gemm(hidden_act, down, offsets), weights, pos)
+    got = torch.cat([out[rank] for rank in range(world)])
+    assert got.shape == want.shape
+    assert float((got.float() - want.float()).abs().max()) <= 2e-2
+    assert float((got == want).float().mean()) > 0.97
