@@ -547,7 +547,7 @@ def run_reference_arm(args) -> None:
         "impl": "reference", "metric": "tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": 0,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "add_rms_norm bf16 x,residual [16384, 8192], weight [8192], eps 1e-5 (BASELINE config 2)"},
+        "config": {"workload": "add_rms_norm bf16 x,residual [16384, 8192], weight [8192], eps 1e-5 (benchmark configuration 2)"},
         "cpu_baseline": {"value": round(value, 1), "unit": "tokens/s", "cores": cores, "kind": "port",
                          "sample": f"each step = {tokens} tokens ({fraction:g} of the configuration); "
                                    "PyTorch CPU restatement of popcorn's add_rms_norm reference, all host threads"},
@@ -714,7 +714,7 @@ def main() -> None:
             "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {
-                "workload": f"add_rms_norm bf16 x,residual [{w.tokens}, 8192], weight [8192], eps 1e-5 (BASELINE config 2), per GPU",
+                "workload": f"add_rms_norm bf16 x,residual [{w.tokens}, 8192], weight [8192], eps 1e-5 (benchmark configuration 2), per GPU",
                 "sharding": "tokens, one full batch per GPU, no collective", "l2": "inputs_larger_than_L2 (1 GiB streamed per launch)",
                 "timing": "CUDA events on the launching stream, max over ranks",
             },

@@ -49,16 +49,22 @@
 namespace b200 {
 namespace {
 
-constexpr int kBM = 128, kBN = 256, kBK = 64, kUmmaK = 16;
-constexpr int kABytes = kBM * kBK * 2;           // 16 KiB
-constexpr int kBChunkBytes = kBK * 128;          // one 64-column chunk of the weight slice: 64 rows of 128 bytes
-constexpr int kMaxStages = 6;
+constexpr int kBM = 128, kBN = 256, kBK = 64, kUmmaK = 16;  // kBK: K values per 128-byte swizzle span (one copy box)
+constexpr int kASubBytes = kBM * kBK * 2;        // 16 KiB: 128 rows x 64 K values
+constexpr int kMaxStages = 4;
 // Per CTA, with CTAS = 1 (alone) or 2 (pair): the weight columns it loads, its ring slot and ring depth.
+// A slot of a pair holds TWO 64-wide K spans: the single thread that issues the MMAs pays one barrier wait and
+// one commit per slot, and with eight MMAs per slot instead of four that fixed cost no longer outlasts the
+// tensor pipe (measured: 0.77 -> see the profile summary).
 template <int CTAS>
 struct Ring {
+  static constexpr int kSub = CTAS;                          // 64-wide K spans per slot
+  static constexpr int kSlotK = kBK * kSub;                  // K values per slot
   static constexpr int kChunks = kBN / 64 / CTAS;            // 64-column chunks of the weight slice this CTA loads
-  static constexpr int kStageBytes = kABytes + kChunks * kBChunkBytes;  // 48 or 32 KiB
-  static constexpr int kStages = CTAS == 2 ? 6 : 4;
+  static constexpr int kABytes = kSub * kASubBytes;
+  static constexpr int kBChunkBytes = kSlotK * 128;          // one 64-column chunk: kSlotK rows of 128 bytes
+  static constexpr int kStageBytes = kABytes + kChunks * kBChunkBytes;  // 48 KiB alone, 64 KiB in a pair
+  static constexpr int kStages = CTAS == 2 ? 3 : 4;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + slack to align the ring to the swizzle atom
 };
 constexpr int kTmemCols = 512;                   // two accumulators of kBN fp32 columns
@@ -198,7 +204,8 @@ __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::l
 //     offset), 64-column chunks one whole [64 x 128 B] block apart (leading offset).
 constexpr uint64_t kDescFixed = (uint64_t(1) << 46) | (uint64_t(2) << 61);
 constexpr uint64_t kDescA = kDescFixed | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32);
-constexpr uint64_t kDescB = kDescFixed | (uint64_t(kBChunkBytes >> 4) << 16) | (uint64_t(1024 >> 4) << 32);
+template <int CTAS>
+constexpr uint64_t kDescB = kDescFixed | (uint64_t(Ring<CTAS>::kBChunkBytes >> 4) << 16) | (uint64_t(1024 >> 4) << 32);
 
 // Instruction descriptor of kind::f16: fp32 accumulate (bit 4), A/B format (0 fp16, 1 bf16) at bits 7
 // and 10, A K-major (bit 15 = 0), B N-major (bit 16 = 1), N >> 3 at bit 17, M >> 4 at bit 24 (M = 256 for a pair).
@@ -220,9 +227,11 @@ struct Tile {
   int expert, row0, row_end, n0;
 };
 
-// tile -> (expert, m tile, n tile): tiles of one expert are consecutive, m fastest, so that CTAs running
-// together share the expert's weight slice in L2.
-__device__ __forceinline__ Tile decode_tile(int tile, const int* tile_start, const int32_t* offsets, int experts, int out_tile_n, int tile_rows) {
+// tile -> (expert, m tile, n tile): tiles of one expert are consecutive, n fastest, so that the CTAs running
+// together work on a few row blocks of ONE expert against all of its weight columns: their working set (a few MB
+// of rows plus the expert's weight matrix, 12-25 MB here) stays in L2 and every operand byte comes from DRAM once.
+// (m fastest sweeps the expert's whole row segment, 64 MB here, once per column tile, which L2 does not hold.)
+__device__ __forceinline__ Tile decode_tile(int tile, const int* tile_start, const int32_t* offsets, int experts, int out_tile_n, int tile_rows, int tiles_n) {
   int lo = 0, hi = experts;  // last expert with tile_start[e] <= tile
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
@@ -230,13 +239,12 @@ __device__ __forceinline__ Tile decode_tile(int tile, const int* tile_start, con
     else hi = mid;
   }
   const int first = offsets[lo], end = offsets[lo + 1];
-  const int tiles_m = (end - first + tile_rows - 1) / tile_rows;
   const int local = tile - tile_start[lo];
   Tile t;
   t.expert = lo;
-  t.row0 = first + (local % tiles_m) * tile_rows;
+  t.row0 = first + (local / tiles_n) * tile_rows;
   t.row_end = end;
-  t.n0 = (local / tiles_m) * out_tile_n;
+  t.n0 = (local % tiles_n) * out_tile_n;
   return t;
 }
 
@@ -304,21 +312,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
       // (DUAL: columns 0-127 are the gate projection, 128-255 the up projection of the same output columns)
       const uint64_t b_map = (DUAL && PAIR && rank == 1) ? w2_map : reinterpret_cast<uint64_t>(&map_w);
       for (int tile = first_tile; tile < total_tiles && !*abort_flag; tile += tile_step) {
-        const Tile t = decode_tile(tile, tile_start, p.offsets, p.experts, OUT_N, TILE_ROWS);
+        const Tile t = decode_tile(tile, tile_start, p.offsets, p.experts, OUT_N, TILE_ROWS, tiles_n);
         const int row0 = t.row0 + static_cast<int>(rank) * kBM;
         const int col0 = t.n0 + ((!DUAL && PAIR) ? static_cast<int>(rank) * (kBN / 2) : 0);
-        for (int k0 = 0; k0 < p.k; k0 += kBK) {
+        for (int k0 = 0; k0 < p.k; k0 += R::kSlotK) {
           if (!mbar_wait_addr(empty_addr + stage * 8, phase ^ 1u)) {
             *abort_flag = 1;
             break;
           }
-          const uint32_t a_dst = ring_addr + stage * R::kStageBytes, b_dst = a_dst + kABytes, bar = signal_addr + stage * 8;
+          const uint32_t a_dst = ring_addr + stage * R::kStageBytes, b_dst = a_dst + R::kABytes, bar = signal_addr + stage * 8;
           if (rank == 0) mbar_arrive_expect_addr(full_addr + stage * 8, CTAS * R::kStageBytes);  // in a pair both CTAs' bytes land here
-          tma_2d<PAIR>(a_dst, rows_map, k0, row0, bar);
+#pragma unroll
+          for (int j = 0; j < R::kSub; ++j) tma_2d<PAIR>(a_dst + j * kASubBytes, rows_map, k0 + j * kBK, row0, bar);  // past K: zero fill
 #pragma unroll
           for (int c = 0; c < R::kChunks; ++c) {
-            if (DUAL && !PAIR && c >= R::kChunks / 2) tma_3d<PAIR>(b_dst + c * kBChunkBytes, w2_map, t.n0 + (c - R::kChunks / 2) * 64, k0, t.expert, bar);
-            else tma_3d<PAIR>(b_dst + c * kBChunkBytes, b_map, col0 + c * 64, k0, t.expert, bar);
+            if (DUAL && !PAIR && c >= R::kChunks / 2) tma_3d<PAIR>(b_dst + c * R::kBChunkBytes, w2_map, t.n0 + (c - R::kChunks / 2) * 64, k0, t.expert, bar);
+            else tma_3d<PAIR>(b_dst + c * R::kBChunkBytes, b_map, col0 + c * 64, k0, t.expert, bar);
           }
           ++issued;
           if (++stage == STAGES) {
@@ -338,8 +347,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
       uint32_t stage = 0, phase = 0, local = 0;
       bool pending = false;
       const uint32_t acc_full_addr = smem_addr(&acc_full[0]), acc_empty_addr = smem_addr(&acc_empty[0]);
-      const uint32_t a_hi = static_cast<uint32_t>(kDescA >> 32), b_hi = static_cast<uint32_t>(kDescB >> 32);
-      const uint32_t a_lo0 = static_cast<uint32_t>(kDescA) | (ring_addr >> 4), b_lo0 = static_cast<uint32_t>(kDescB) | ((ring_addr + kABytes) >> 4);
+      const uint32_t a_hi = static_cast<uint32_t>(kDescA >> 32), b_hi = static_cast<uint32_t>(kDescB<CTAS> >> 32);
+      const uint32_t a_lo0 = static_cast<uint32_t>(kDescA) | (ring_addr >> 4);
+      const uint32_t b_lo0 = static_cast<uint32_t>(kDescB<CTAS>) | ((ring_addr + R::kABytes) >> 4);
       const uint32_t idesc = p.idesc;
       for (int tile = first_tile; tile < total_tiles && !*abort_flag; tile += tile_step, ++local) {
         const uint32_t acc = local & 1u;
@@ -350,18 +360,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kBN;
         uint32_t accumulate = 0;
-        for (int k0 = 0; k0 < p.k; k0 += kBK) {
+        for (int k0 = 0; k0 < p.k; k0 += R::kSlotK) {
           if (!mbar_wait_addr(full_addr + stage * 8, phase)) {
             *abort_flag = 1;
             break;
           }
           tc_fence_after();
           // descriptor start fields advance in 16-byte units: a ring slot, then per MMA 16 K values = 32 bytes along
-          // A's swizzled 128-byte rows and 16 K rows = 2048 bytes of B
+          // A's swizzled 128-byte rows (a new 16 KiB block every 64 K values) and 16 K rows = 2048 bytes of B
           const uint32_t a_lo = a_lo0 + stage * (R::kStageBytes >> 4), b_lo = b_lo0 + stage * (R::kStageBytes >> 4);
 #pragma unroll
-          for (int k = 0; k < kBK / kUmmaK; ++k) {
-            mma_issue<PAIR>(d_tmem, a_lo + k * (kUmmaK * 2 >> 4), b_lo + k * (kUmmaK * 128 >> 4), a_hi, b_hi, idesc, accumulate);
+          for (int k = 0; k < R::kSlotK / kUmmaK; ++k) {
+            constexpr int kPerSpan = kBK / kUmmaK;
+            mma_issue<PAIR>(d_tmem, a_lo + (k / kPerSpan) * (kASubBytes >> 4) + (k % kPerSpan) * (kUmmaK * 2 >> 4), b_lo + k * (kUmmaK * 128 >> 4),
+                            a_hi, b_hi, idesc, accumulate);
             accumulate = 1;
           }
           mma_commit_addr<PAIR>(empty_addr + stage * 8);  // the slot (in both CTAs of a pair) is free once these MMAs have read it
@@ -387,7 +399,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     uint32_t local = 0;
     T* out = static_cast<T*>(p.out);
     for (int tile = first_tile; tile < total_tiles && !*abort_flag; tile += tile_step, ++local) {
-      const Tile t = decode_tile(tile, tile_start, p.offsets, p.experts, OUT_N, TILE_ROWS);
+      const Tile t = decode_tile(tile, tile_start, p.offsets, p.experts, OUT_N, TILE_ROWS, tiles_n);
       const uint32_t acc = local & 1u;
       // one lane polls for the whole warp
       const int ready = __shfl_sync(0xffffffffu, lane == 0 ? static_cast<int>(mbar_wait(&acc_full[acc], (local >> 1) & 1u)) : 0, 0);
@@ -482,11 +494,11 @@ bool encode_rows(CUtensorMap* map, CUtensorMapDataType type, const void* base, i
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// weight [experts, k, n], n contiguous: box 64 (N) x 64 (K) x 1 (expert).
-bool encode_weight(CUtensorMap* map, CUtensorMapDataType type, const void* base, int64_t experts, int64_t k, int64_t n) {
+// weight [experts, k, n], n contiguous: box 64 (N) x slot_k (K) x 1 (expert).
+bool encode_weight(CUtensorMap* map, CUtensorMapDataType type, const void* base, int64_t experts, int64_t k, int64_t n, int slot_k) {
   const cuuint64_t dims[3] = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(experts)};
   const cuuint64_t strides[2] = {static_cast<cuuint64_t>(n) * 2, static_cast<cuuint64_t>(n) * static_cast<cuuint64_t>(k) * 2};
-  const cuuint32_t box[3] = {64, kBK, 1}, elem[3] = {1, 1, 1};
+  const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(slot_k), 1}, elem[3] = {1, 1, 1};
   return encoder()(map, type, 3, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -499,8 +511,21 @@ bool pair_enabled() {
 
 constexpr int kNoClusters = -1000;  // run_with<., ., 2>: no cluster of two CTAs can be resident; the caller runs single CTAs instead
 
+// What the tensor maps of one call describe.
+struct Operands {
+  const void *rows, *weight, *weight2;
+  int64_t total_rows, k, n, experts, ld_rows;
+  CUtensorMapDataType type;
+};
+
 template <typename T, bool DUAL, int CTAS>
-int run_with(const CUtensorMap& rows, const CUtensorMap& w, const CUtensorMap& w2, GemmArgs args, uint32_t format, cudaStream_t st) {
+int run_with(const Operands& op, GemmArgs args, uint32_t format, cudaStream_t st) {
+  alignas(64) CUtensorMap rows, w, w2;
+  constexpr int slot_k = Ring<CTAS>::kSlotK;
+  if (!encode_rows(&rows, op.type, op.rows, op.total_rows, op.k, op.ld_rows) ||
+      !encode_weight(&w, op.type, op.weight, op.experts, op.k, op.n, slot_k) ||
+      !encode_weight(&w2, op.type, op.weight2 ? op.weight2 : op.weight, op.experts, op.k, op.n, slot_k))
+    return fail(B200_ERR_LAUNCH, "b200_moe_grouped_gemm: tensor map encoding failed");
   auto kernel = grouped_gemm_kernel<T, DUAL, CTAS>;
   constexpr int smem = Ring<CTAS>::kSmemBytes;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
@@ -545,12 +570,12 @@ int run_with(const CUtensorMap& rows, const CUtensorMap& w, const CUtensorMap& w
 }
 
 template <typename T, bool DUAL>
-int run(const CUtensorMap& rows, const CUtensorMap& w, const CUtensorMap& w2, const GemmArgs& args, uint32_t format, cudaStream_t st) {
+int run(const Operands& op, const GemmArgs& args, uint32_t format, cudaStream_t st) {
   if (pair_enabled()) {
-    const int rc = run_with<T, DUAL, 2>(rows, w, w2, args, format, st);
+    const int rc = run_with<T, DUAL, 2>(op, args, format, st);
     if (rc != kNoClusters) return rc;
   }
-  return run_with<T, DUAL, 1>(rows, w, w2, args, format, st);
+  return run_with<T, DUAL, 1>(op, args, format, st);
 }
 
 }  // namespace
@@ -584,10 +609,7 @@ extern "C" int b200_moe_grouped_gemm(const void* rows, const void* weight, const
   if (encoder() == nullptr) return fail(B200_ERR_LAUNCH, "%s: the driver does not provide cuTensorMapEncodeTiled", __func__);
 
   const CUtensorMapDataType type = dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  alignas(64) CUtensorMap map_rows, map_w, map_w2;
-  if (!encode_rows(&map_rows, type, rows, total_rows, k, ld_rows) || !encode_weight(&map_w, type, weight, experts, k, n) ||
-      !encode_weight(&map_w2, type, weight2 ? weight2 : weight, experts, k, n))
-    return fail(B200_ERR_LAUNCH, "%s: tensor map encoding failed", __func__);
+  const Operands op{rows, weight, weight2, total_rows, k, n, experts, ld_rows, type};
 
   GemmArgs args{};
   args.offsets = offsets;
@@ -598,6 +620,6 @@ extern "C" int b200_moe_grouped_gemm(const void* rows, const void* weight, const
   args.k = static_cast<int>(k);
   const uint32_t format = dtype == B200_BF16 ? 1u : 0u;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == B200_BF16) return weight2 ? run<__nv_bfloat16, true>(map_rows, map_w, map_w2, args, format, st) : run<__nv_bfloat16, false>(map_rows, map_w, map_w2, args, format, st);
-  return weight2 ? run<__half, true>(map_rows, map_w, map_w2, args, format, st) : run<__half, false>(map_rows, map_w, map_w2, args, format, st);
+  if (dtype == B200_BF16) return weight2 ? run<__nv_bfloat16, true>(op, args, format, st) : run<__nv_bfloat16, false>(op, args, format, st);
+  return weight2 ? run<__half, true>(op, args, format, st) : run<__half, false>(op, args, format, st);
 }

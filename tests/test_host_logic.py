@@ -115,7 +115,7 @@ def test_workload_shapes_and_bytes():
     assert r.shard(0, 2).inputs["q"].shape[0] == 1 and r.shard(0, 2).inputs["cos"].shape == (64, 64)
 
 
-REFERENCE_SRC = Path("/root/reference/src")
+REFERENCE_SRC = Path(os.environ.get("POPCORN_SOURCE_TREE", "/root/reference/src"))
 HAVE_POPCORN = importlib.util.find_spec("popcorn") is not None or (REFERENCE_SRC / "popcorn").is_dir()
 
 
