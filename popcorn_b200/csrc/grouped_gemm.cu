@@ -231,7 +231,8 @@ struct Tile {
 // together work on a few row blocks of ONE expert against all of its weight columns: their working set (a few MB
 // of rows plus the expert's weight matrix, 12-25 MB here) stays in L2 and every operand byte comes from DRAM once.
 // (m fastest sweeps the expert's whole row segment, 64 MB here, once per column tile, which L2 does not hold.)
-__device__ __forceinline__ Tile decode_tile(int tile, const int* tile_start, const int32_t* offsets, int experts, int out_tile_n, int tile_rows, int tiles_n) {
+// (`offsets` is the CTA's shared-memory copy of the segment bounds: a tile switch costs no global-memory round trip.)
+__device__ __forceinline__ Tile decode_tile(int tile, const int* tile_start, const int* offsets, int experts, int out_tile_n, int tile_rows, int tiles_n) {
   int lo = 0, hi = experts;  // last expert with tile_start[e] <= tile
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
@@ -262,7 +263,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
   __shared__ uint64_t full[kMaxStages], empty[kMaxStages], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int aborted;
-  __shared__ int tile_start[kMaxExperts + 1];
+  __shared__ int tile_start[kMaxExperts + 1], seg[kMaxExperts + 1];
   __shared__ uint4 staging[4][32][8];  // per epilogue warp: 32 rows x 128 bytes of finished output
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -274,11 +275,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
 
   if (threadIdx.x == 0) {
     aborted = 0;
-    int total = 0;
+    int total = 0, lo = p.offsets[0];
+    seg[0] = lo;
     for (int e = 0; e < p.experts; ++e) {
       tile_start[e] = total;
-      const int count = p.offsets[e + 1] - p.offsets[e];
-      total += (count > 0 ? (count + TILE_ROWS - 1) / TILE_ROWS : 0) * tiles_n;
+      const int hi = p.offsets[e + 1];
+      seg[e + 1] = hi;
+      total += (hi > lo ? (hi - lo + TILE_ROWS - 1) / TILE_ROWS : 0) * tiles_n;
+      lo = hi;
     }
     tile_start[p.experts] = total;
     for (int s = 0; s < STAGES; ++s) {
@@ -312,7 +316,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
       // (DUAL: columns 0-127 are the gate projection, 128-255 the up projection of the same output columns)
       const uint64_t b_map = (DUAL && PAIR && rank == 1) ? w2_map : reinterpret_cast<uint64_t>(&map_w);
       for (int tile = first_tile; tile < total_tiles && !*abort_flag; tile += tile_step) {
-        const Tile t = decode_tile(tile, tile_start, p.offsets, p.experts, OUT_N, TILE_ROWS, tiles_n);
+        const Tile t = decode_tile(tile, tile_start, seg, p.experts, OUT_N, TILE_ROWS, tiles_n);
         const int row0 = t.row0 + static_cast<int>(rank) * kBM;
         const int col0 = t.n0 + ((!DUAL && PAIR) ? static_cast<int>(rank) * (kBN / 2) : 0);
         for (int k0 = 0; k0 < p.k; k0 += R::kSlotK) {
@@ -399,7 +403,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     uint32_t local = 0;
     T* out = static_cast<T*>(p.out);
     for (int tile = first_tile; tile < total_tiles && !*abort_flag; tile += tile_step, ++local) {
-      const Tile t = decode_tile(tile, tile_start, p.offsets, p.experts, OUT_N, TILE_ROWS, tiles_n);
+      const Tile t = decode_tile(tile, tile_start, seg, p.experts, OUT_N, TILE_ROWS, tiles_n);
       const uint32_t acc = local & 1u;
       // one lane polls for the whole warp
       const int ready = __shfl_sync(0xffffffffu, lane == 0 ? static_cast<int>(mbar_wait(&acc_full[acc], (local >> 1) & 1u)) : 0, 0);
