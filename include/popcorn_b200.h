@@ -407,8 +407,11 @@ int b200_moe_unpermute(const void* rows, const float* weights, const int32_t* po
  * (gate_weight, up_weight) is lin1.  rows: [total_rows, k] with row stride ld_rows; weight, weight2:
  * [experts, k, n] contiguous, the reference's layout; offsets: [experts + 1] int32 on the device, ascending,
  * offsets[experts] <= total_rows; out: [total_rows, n] with row stride ld_out (rows outside every segment
- * are left untouched).  dtype: B200_BF16 or B200_F16.  k, n, ld_rows, ld_out must be multiples of 8;
- * all buffers 16-byte aligned; experts <= 1024.
+ * are left untouched; segments are clamped to total_rows).  dtype: B200_BF16 or B200_F16.  k, n, ld_rows,
+ * ld_out must be multiples of 8; all buffers 16-byte aligned; experts <= 1024.  Each CTA takes a whole SM (about
+ * 219 KB of shared memory and all 512 tensor-memory columns), so other kernels that use tensor memory should not
+ * be run concurrently with this one on the same device.  B200_GEMM_PAIR=0 in the environment selects single CTAs
+ * (cta_group::1) instead of cluster pairs.
  */
 int b200_moe_grouped_gemm(const void* rows, const void* weight, const void* weight2, const int32_t* offsets, void* out,
                           int64_t total_rows, int64_t k, int64_t n, int64_t experts, int64_t ld_rows, int64_t ld_out,

@@ -220,6 +220,7 @@ struct GemmArgs {
   int experts;
   int n;        // output columns (per projection)
   int k;
+  int total_rows;  // rows of `rows` and `out`: nothing is stored past them, whatever `offsets` says
   uint32_t idesc;
 };
 
@@ -275,11 +276,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
 
   if (threadIdx.x == 0) {
     aborted = 0;
-    int total = 0, lo = p.offsets[0];
+    int total = 0, lo = max(p.offsets[0], 0);
     seg[0] = lo;
     for (int e = 0; e < p.experts; ++e) {
       tile_start[e] = total;
-      const int hi = p.offsets[e + 1];
+      const int hi = min(p.offsets[e + 1], p.total_rows);
       seg[e + 1] = hi;
       total += (hi > lo ? (hi - lo + TILE_ROWS - 1) / TILE_ROWS : 0) * tiles_n;
       lo = hi;
@@ -622,6 +623,7 @@ extern "C" int b200_moe_grouped_gemm(const void* rows, const void* weight, const
   args.experts = static_cast<int>(experts);
   args.n = static_cast<int>(n);
   args.k = static_cast<int>(k);
+  args.total_rows = static_cast<int>(total_rows);
   const uint32_t format = dtype == B200_BF16 ? 1u : 0u;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == B200_BF16) return weight2 ? run<__nv_bfloat16, true>(op, args, format, st) : run<__nv_bfloat16, false>(op, args, format, st);

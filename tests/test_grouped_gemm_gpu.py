@@ -111,6 +111,34 @@ def test_golden_momoe_op(name):
                   gpu(t["router_logits"]), meta["top_k"])
 
 
+def test_large_segments_against_the_library_matmul():
+    """Eight experts of 2048-2300 rows at the benchmark's hidden and intermediate sizes, against fp32 matmuls of the same
+    16-bit operands on the GPU (the CPU oracle would take minutes here)."""
+    counts = [2048, 2300, 2100, 2048, 2049, 2047, 2200, 2048]
+    rows, gate, up, offsets = make(counts, 4096, 1536, BF16, 5400)
+    d_rows, d_gate, d_up, d_off = gpu(rows), gpu(gate), gpu(up), gpu(offsets)
+    got = ops.moe_grouped_gemm(d_rows, d_gate, d_off, d_up)
+    down = gpu((randn(5403, len(counts), 1536, 4096) / 1536 ** 0.5).to(BF16))
+    got_down = ops.moe_grouped_gemm(got, down, d_off)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    bounds = offsets.tolist()
+    for e in range(len(counts)):
+        seg = d_rows[bounds[e]:bounds[e + 1]].float()
+        want = (torch.nn.functional.silu(seg @ d_gate[e].float()) * (seg @ d_up[e].float())).to(BF16)
+        close(got[bounds[e]:bounds[e + 1]], want.cpu(), f"expert {e} gate/up")
+        want_down = (got[bounds[e]:bounds[e + 1]].float() @ down[e].float()).to(BF16)
+        close(got_down[bounds[e]:bounds[e + 1]], want_down.cpu(), f"expert {e} down")
+    assert _lib.wait_timeouts() == 0
+
+
+def test_offsets_beyond_the_buffer_are_clamped():
+    rows, weight, _, offsets = make([100, 60], 64, 64, BF16, 5500)
+    wrong = offsets.clone()
+    wrong[-1] += 500  # claims rows the buffers do not have
+    got = ops.moe_grouped_gemm(gpu(rows), gpu(weight), gpu(wrong))
+    close(got, oracle.moe_grouped_gemm(rows, weight, offsets), "clamped offsets")
+
+
 def test_empty_and_rejected_inputs():
     rows, weight, _, offsets = make([4, 4], 16, 16, BF16, 5300)
     empty = ops.moe_grouped_gemm(gpu(rows[:0]), gpu(weight), gpu(torch.zeros(3, dtype=torch.int32)))
