@@ -273,6 +273,17 @@ int b200_swiglu_backward(const void* grad_out, const void* a, const void* b, voi
                          int64_t ldda, int64_t lddb, int dtype, void* stream);
 
 /*
+ * Backward of b200_geglu, same shapes and roundings as b200_swiglu_backward with the tanh-approximate GELU in
+ * place of silu: grad_a = round_T(round_T(g*b) * gelu'(a)), grad_b = round_T(g * round_T(gelu(a))).
+ *
+ * Replaces what autograd derives from the reference F.gelu(a, approximate="tanh") * b,
+ * src/popcorn/kernels/geglu.py:17.
+ */
+int b200_geglu_backward(const void* grad_out, const void* a, const void* b, void* grad_a, void* grad_b,
+                        int64_t rows, int64_t cols, int64_t ldg, int64_t lda, int64_t ldb,
+                        int64_t ldda, int64_t lddb, int dtype, void* stream);
+
+/*
  * MoE routing: probs = softmax(fp32(logits)) over experts; the top_k largest
  * (descending, ties to the lower expert index); weights = picked / sum(picked).
  *

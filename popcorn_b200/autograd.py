@@ -31,6 +31,58 @@ class _SwiGLU(torch.autograd.Function):
         return grad_a, grad_b
 
 
+class _GeGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a: Tensor, b: Tensor) -> Tensor:
+        ctx.save_for_backward(a, b)
+        with torch.no_grad():
+            return ops.geglu(a, b)
+
+    @staticmethod
+    def backward(ctx, grad_out: Tensor):
+        a, b = ctx.saved_tensors
+        with torch.no_grad():
+            grad_a, grad_b = ops.geglu_backward(grad_out.contiguous(), a, b)
+        return grad_a, grad_b
+
+
+class _PairedRope(torch.autograd.Function):
+    """rope(q, k, cos, sin): y1 = x1 c1 - x2 s1, y2 = x2 c2 + x1 s2 per half, so the transpose is the same kernel with
+    the sine table's halves swapped and negated (for a table with repeated halves: the opposite angle)."""
+
+    @staticmethod
+    def forward(ctx, q: Tensor, k: Tensor, cos: Tensor, sin: Tensor):
+        ctx.save_for_backward(cos, sin)
+        with torch.no_grad():
+            return ops.rope(q, k, cos, sin)
+
+    @staticmethod
+    def backward(ctx, grad_q: Tensor, grad_k: Tensor):
+        cos, sin = ctx.saved_tensors
+        first, second = sin.chunk(2, -1)
+        with torch.no_grad():
+            dq, dk = ops.rope(grad_q.contiguous(), grad_k.contiguous(), cos, -torch.cat((second, first), -1))
+        return dq, dk, None, None
+
+
+class _Llama4Rope(torch.autograd.Function):
+    """Multiplication by unit complex numbers: the transpose multiplies by their conjugates."""
+
+    @staticmethod
+    def forward(ctx, q: Tensor, k: Tensor, freqs: Tensor):
+        ctx.save_for_backward(freqs)
+        with torch.no_grad():
+            return ops.llama4_rope(q, k, freqs)
+
+    @staticmethod
+    def backward(ctx, grad_q: Tensor, grad_k: Tensor):
+        (freqs,) = ctx.saved_tensors
+        conjugate = torch.stack((freqs[..., 0], -freqs[..., 1]), -1)
+        with torch.no_grad():
+            dq, dk = ops.llama4_rope(grad_q.contiguous(), grad_k.contiguous(), conjugate)
+        return dq, dk, None
+
+
 class _Rotary(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x: Tensor, cos: Tensor, sin: Tensor, interleaved: bool) -> Tensor:
@@ -102,3 +154,18 @@ def swiglu(a: Tensor, b: Tensor) -> Tensor:
 def rotary_embedding(x: Tensor, cos: Tensor, sin: Tensor, interleaved: bool = False) -> Tensor:
     """Rotary embedding with a gradient for x (cos and sin are constants, as in the reference)."""
     return _Rotary.apply(x, cos.detach(), sin.detach(), interleaved)
+
+
+def geglu(a: Tensor, b: Tensor) -> Tensor:
+    """gelu_tanh(a) * b with gradients for a and b."""
+    return _GeGLU.apply(a, b)
+
+
+def rope(q: Tensor, k: Tensor, cos: Tensor, sin: Tensor) -> tuple[Tensor, Tensor]:
+    """Paired rotary embedding with gradients for q and k (cos and sin are constants, as in the reference)."""
+    return _PairedRope.apply(q, k, cos.detach(), sin.detach())
+
+
+def llama4_rope(q: Tensor, k: Tensor, freqs: Tensor) -> tuple[Tensor, Tensor]:
+    """Llama 4 rotary embedding with gradients for q and k (freqs are constants, as in the reference)."""
+    return _Llama4Rope.apply(q, k, freqs.detach())

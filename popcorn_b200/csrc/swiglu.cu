@@ -92,14 +92,22 @@ swiglu_vec_kernel(const T* a, const T* b, T* out, Index total_words, Index words
 //   gs = round_T(g * b)                                  (gradient reaching silu)
 //   da = round_T(gs * (s * (1 + a * (1 - s)))),  s = 1 / (1 + exp(-a)) in fp32
 // and this kernel does the same in one pass (3 reads, 2 writes per element).
-template <int MATH>
+// GEGLU (tanh approximation): with s = 1 / (1 + exp(-2u)) = 0.5 * (1 + tanh u), u = sqrt(2/pi) * (a + 0.044715 a^3),
+//   gelu'(a) = s + a * (1 - tanh^2 u) / 2 * u' = s * (1 + 2 a (1 - s) u'),  u' = sqrt(2/pi) * (1 + 3 * 0.044715 a^2),
+// the derivative PyTorch's gelu backward evaluates (0.5 (1 + tanh u) + 0.5 a (1 - tanh^2 u) u') in another arrangement.
+template <int MATH, int ACT = kSilu>
 __device__ __forceinline__ float dsilu_f32(float a) {
-  const float d = __fadd_rn(1.0f, exp_neg<MATH>(a));
+  const float d = __fadd_rn(1.0f, exp_neg<MATH>(gate_argument<ACT>(a)));
   const float s = MATH == 0 ? __fdiv_rn(1.0f, d) : rcp_approx(d);
-  return __fmul_rn(s, __fmaf_rn(a, __fsub_rn(1.0f, s), 1.0f));
+  if constexpr (ACT == kSilu) {
+    return __fmul_rn(s, __fmaf_rn(a, __fsub_rn(1.0f, s), 1.0f));
+  } else {
+    const float du = __fmul_rn(0.7978845608028654f, __fmaf_rn(__fmul_rn(3.0f * 0.044715f, a), a, 1.0f));
+    return __fmul_rn(s, __fmaf_rn(__fmul_rn(__fmul_rn(2.0f, a), __fsub_rn(1.0f, s)), du, 1.0f));
+  }
 }
 
-template <typename T, int UNROLL, typename Index, int MATH>
+template <typename T, int UNROLL, typename Index, int MATH, int ACT>
 __global__ void __launch_bounds__(256)
 swiglu_bwd_vec_kernel(const T* g, const T* a, const T* b, T* da, T* db, Index total_words, Index words_per_row,
                       int64_t ldg, int64_t lda, int64_t ldb, int64_t ldda, int64_t lddb) {
@@ -134,10 +142,10 @@ swiglu_bwd_vec_kernel(const T* g, const T* a, const T* b, T* da, T* db, Index to
     Num<T>::unpack(vb[u], fb);
 #pragma unroll
     for (int j = 0; j < V; ++j) {
-      const float s = Num<T>::rt(silu_f32<MATH>(fa[j]));
+      const float s = Num<T>::rt(silu_f32<MATH, ACT>(fa[j]));
       rb[j] = __fmul_rn(fg[j], s);
       const float gs = Num<T>::rt(__fmul_rn(fg[j], fb[j]));
-      ra[j] = __fmul_rn(gs, dsilu_f32<MATH>(fa[j]));
+      ra[j] = __fmul_rn(gs, dsilu_f32<MATH, ACT>(fa[j]));
     }
     if (ok[u]) {
       st_stream(da + off_da[u], Num<T>::pack(ra));
@@ -146,7 +154,7 @@ swiglu_bwd_vec_kernel(const T* g, const T* a, const T* b, T* da, T* db, Index to
   }
 }
 
-template <typename T>
+template <typename T, int ACT>
 __global__ void __launch_bounds__(256)
 swiglu_bwd_scalar_kernel(const T* g, const T* a, const T* b, T* da, T* db, int64_t rows, int64_t cols,
                          int64_t ldg, int64_t lda, int64_t ldb, int64_t ldda, int64_t lddb) {
@@ -156,12 +164,12 @@ swiglu_bwd_scalar_kernel(const T* g, const T* a, const T* b, T* da, T* db, int64
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t r = i / cols, c = i - r * cols;
     const float fg = Num<T>::up(g[r * ldg + c]), fa = Num<T>::up(a[r * lda + c]), fb = Num<T>::up(b[r * ldb + c]);
-    db[r * lddb + c] = Num<T>::down(__fmul_rn(fg, Num<T>::rt(silu_f32<0>(fa))));
-    da[r * ldda + c] = Num<T>::down(__fmul_rn(Num<T>::rt(__fmul_rn(fg, fb)), dsilu_f32<0>(fa)));
+    db[r * lddb + c] = Num<T>::down(__fmul_rn(fg, Num<T>::rt(silu_f32<0, ACT>(fa))));
+    da[r * ldda + c] = Num<T>::down(__fmul_rn(Num<T>::rt(__fmul_rn(fg, fb)), dsilu_f32<0, ACT>(fa)));
   }
 }
 
-template <typename T>
+template <typename T, int ACT>
 int run_bwd(const void* g, const void* a, const void* b, void* da, void* db, int64_t rows, int64_t cols,
             int64_t ldg, int64_t lda, int64_t ldb, int64_t ldda, int64_t lddb, cudaStream_t st) {
   constexpr int V = Num<T>::kVec;
@@ -172,14 +180,14 @@ int run_bwd(const void* g, const void* a, const void* b, void* da, void* db, int
   const int64_t wpr = cols / V;
   const int64_t total = rows * wpr;
   if (vec && total < 0x7fffffffLL) {
-    launch(swiglu_bwd_vec_kernel<T, UNROLL, uint32_t, MATH>, static_cast<unsigned>(ceil_div(total, 256 * UNROLL)), 256, 0, st,
+    launch(swiglu_bwd_vec_kernel<T, UNROLL, uint32_t, MATH, ACT>, static_cast<unsigned>(ceil_div(total, 256 * UNROLL)), 256, 0, st,
            static_cast<const T*>(g), static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(da), static_cast<T*>(db),
            static_cast<uint32_t>(total), static_cast<uint32_t>(wpr), ldg, lda, ldb, ldda, lddb);
     return after_launch("swiglu_bwd_vec_kernel");
   }
   const int64_t want = ceil_div(rows * cols, 256);
   const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
-  launch(swiglu_bwd_scalar_kernel<T>, static_cast<unsigned>(want < cap ? want : cap), 256, 0, st,
+  launch(swiglu_bwd_scalar_kernel<T, ACT>, static_cast<unsigned>(want < cap ? want : cap), 256, 0, st,
          static_cast<const T*>(g), static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(da), static_cast<T*>(db),
          rows, cols, ldg, lda, ldb, ldda, lddb);
   return after_launch("swiglu_bwd_scalar_kernel");
@@ -271,24 +279,40 @@ extern "C" int b200_geglu(const void* a, const void* b, void* out, int64_t rows,
   return gated_forward<kGeluTanh>(__func__, a, b, out, rows, cols, lda, ldb, ldo, dtype, stream);
 }
 
+namespace {
+
+int gate_backward(const char* fn, int act, const void* grad_out, const void* a, const void* b, void* grad_a, void* grad_b,
+                  int64_t rows, int64_t cols, int64_t ldg, int64_t lda, int64_t ldb, int64_t ldda, int64_t lddb, int dtype, void* stream) {
+  if (!dtype_ok(dtype)) return fail(B200_ERR_DTYPE, "%s: unsupported dtype %d", fn, dtype);
+  if (rows < 0 || cols < 0) return fail(B200_ERR_SHAPE, "%s: negative size", fn);
+  if (rows == 0 || cols == 0) return B200_OK;
+  if (grad_out == nullptr || a == nullptr || b == nullptr || grad_a == nullptr || grad_b == nullptr)
+    return fail(B200_ERR_NULL_POINTER, "%s: a required pointer is NULL", fn);
+  if (ldg < cols || lda < cols || ldb < cols || ldda < cols || lddb < cols)
+    return fail(B200_ERR_SHAPE, "%s: leading dimension smaller than cols", fn);
+  const size_t es = dtype_size(dtype);
+  if (!aligned(grad_out, es) || !aligned(a, es) || !aligned(b, es) || !aligned(grad_a, es) || !aligned(grad_b, es))
+    return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to the element size", fn);
+  if (int rc = check_device()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (act == kSilu) {
+    B200_DISPATCH_DTYPE(dtype, T, return (run_bwd<T, kSilu>(grad_out, a, b, grad_a, grad_b, rows, cols, ldg, lda, ldb, ldda, lddb, st)));
+  } else {
+    B200_DISPATCH_DTYPE(dtype, T, return (run_bwd<T, kGeluTanh>(grad_out, a, b, grad_a, grad_b, rows, cols, ldg, lda, ldb, ldda, lddb, st)));
+  }
+  return B200_OK;
+}
+
+}  // namespace
+
 extern "C" int b200_swiglu_backward(const void* grad_out, const void* a, const void* b, void* grad_a, void* grad_b,
                                     int64_t rows, int64_t cols, int64_t ldg, int64_t lda, int64_t ldb,
                                     int64_t ldda, int64_t lddb, int dtype, void* stream) {
-  if (!dtype_ok(dtype)) return fail(B200_ERR_DTYPE, "%s: unsupported dtype %d", __func__, dtype);
-  if (rows < 0 || cols < 0) return fail(B200_ERR_SHAPE, "%s: negative size", __func__);
-  if (rows == 0 || cols == 0) return B200_OK;
-  B200_REQUIRE_PTR(grad_out);
-  B200_REQUIRE_PTR(a);
-  B200_REQUIRE_PTR(b);
-  B200_REQUIRE_PTR(grad_a);
-  B200_REQUIRE_PTR(grad_b);
-  if (ldg < cols || lda < cols || ldb < cols || ldda < cols || lddb < cols)
-    return fail(B200_ERR_SHAPE, "%s: leading dimension smaller than cols", __func__);
-  const size_t es = dtype_size(dtype);
-  if (!aligned(grad_out, es) || !aligned(a, es) || !aligned(b, es) || !aligned(grad_a, es) || !aligned(grad_b, es))
-    return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to the element size", __func__);
-  if (int rc = check_device()) return rc;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  B200_DISPATCH_DTYPE(dtype, T, return run_bwd<T>(grad_out, a, b, grad_a, grad_b, rows, cols, ldg, lda, ldb, ldda, lddb, st));
-  return B200_OK;
+  return gate_backward(__func__, kSilu, grad_out, a, b, grad_a, grad_b, rows, cols, ldg, lda, ldb, ldda, lddb, dtype, stream);
+}
+
+extern "C" int b200_geglu_backward(const void* grad_out, const void* a, const void* b, void* grad_a, void* grad_b,
+                                   int64_t rows, int64_t cols, int64_t ldg, int64_t lda, int64_t ldb,
+                                   int64_t ldda, int64_t lddb, int dtype, void* stream) {
+  return gate_backward(__func__, kGeluTanh, grad_out, a, b, grad_a, grad_b, rows, cols, ldg, lda, ldb, ldda, lddb, dtype, stream);
 }

@@ -430,10 +430,19 @@ def layer_norm(x: Tensor, weight: Tensor, bias: Tensor | None = None, eps: float
 
 def swiglu_backward(grad_out: Tensor, a: Tensor, b: Tensor) -> tuple[Tensor, Tensor]:
     """Gradients of swiglu(a, b) with respect to a and b (what autograd derives from swiglu.py:18)."""
+    return _gate_backward("b200_swiglu_backward", grad_out, a, b)
+
+
+def geglu_backward(grad_out: Tensor, a: Tensor, b: Tensor) -> tuple[Tensor, Tensor]:
+    """Gradients of geglu(a, b) with respect to a and b (what autograd derives from geglu.py:17)."""
+    return _gate_backward("b200_geglu_backward", grad_out, a, b)
+
+
+def _gate_backward(entry: str, grad_out: Tensor, a: Tensor, b: Tensor) -> tuple[Tensor, Tensor]:
     device = _require_cuda(grad_out, a, b)
-    code = _dtype_code(a, "swiglu_backward")
+    code = _dtype_code(a, entry)
     if not (grad_out.shape == a.shape == b.shape) or not (grad_out.dtype == a.dtype == b.dtype):
-        raise ValueError("swiglu_backward: grad_out, a and b must share shape and dtype")
+        raise ValueError(f"{entry}: grad_out, a and b must share shape and dtype")
     width = a.shape[-1]
     g2, ldg = _rows(grad_out)
     a2, lda = _rows(a)
@@ -442,7 +451,7 @@ def swiglu_backward(grad_out: Tensor, a: Tensor, b: Tensor) -> tuple[Tensor, Ten
     grad_b = torch.empty(a.shape, dtype=a.dtype, device=device)
     ld = max(width, 1)
     with torch.cuda.device(device):
-        _lib.call("b200_swiglu_backward", _ptr(g2), _ptr(a2), _ptr(b2), _ptr(grad_a), _ptr(grad_b), a2.shape[0], width,
+        _lib.call(entry, _ptr(g2), _ptr(a2), _ptr(b2), _ptr(grad_a), _ptr(grad_b), a2.shape[0], width,
                   ldg, lda, ldb, ld, ld, code, _stream(device))
     return grad_a, grad_b
 

@@ -86,6 +86,54 @@ def test_rotary_backward(shape, half, dtype, interleaved):
     grade(grad, native, truth, dtype, "grad_x")
 
 
+@pytest.mark.parametrize("rows,cols,dtype", [(7, 136, torch.bfloat16), (64, 14336, torch.bfloat16), (5, 33, torch.bfloat16),
+                                              (33, 1000, torch.float16), (129, 257, torch.float32)])
+def test_geglu_backward(rows, cols, dtype):
+    gate_up = randn(1900 + cols, rows, 2 * cols, dtype=dtype, scale=2.0)
+    g = randn(1901 + cols, rows, cols, dtype=dtype)
+    a, b = gate_up[:, :cols], gate_up[:, cols:]
+    dev = gate_up.to(DEV).requires_grad_(True)
+    out = diff.geglu(dev[:, :cols], dev[:, cols:])
+    (grad,) = torch.autograd.grad(out, dev, g.to(DEV))
+    native = oracle_grads(oracle.geglu, (a, b), g)
+    truth = oracle_grads(oracle.geglu, (a, b), g, wide=True)
+    # like the forward op, the kernel evaluates gelu through 1 / (1 + exp(-2u)) instead of 1 + tanh(u): where the
+    # reference cancels, results land on the neighbouring 16-bit value
+    exact = 0.95 if dtype != torch.float32 else None
+    grade(grad[:, :cols], native[0], truth[0], dtype, "grad_a", exact)
+    grade(grad[:, cols:], native[1], truth[1], dtype, "grad_b", exact)
+
+
+@pytest.mark.parametrize("batch,hq,hk,seq,dim,dtype", [(2, 8, 2, 33, 128, torch.bfloat16), (1, 3, 1, 9, 64, torch.float16), (2, 2, 2, 5, 16, torch.float32)])
+def test_paired_rope_backward(batch, hq, hk, seq, dim, dtype):
+    q, k = randn(2000 + dim, batch, hq, seq, dim, dtype=dtype), randn(2001 + dim, batch, hk, seq, dim, dtype=dtype)
+    gq, gk = randn(2002 + dim, batch, hq, seq, dim, dtype=dtype), randn(2003 + dim, batch, hk, seq, dim, dtype=dtype)
+    cos = torch.cos(randn(2004, 1, seq, dim)).to(dtype)  # halves NOT repeated: the general transpose
+    sin = torch.sin(randn(2005, 1, seq, dim)).to(dtype)
+    leaves = [t.to(DEV).requires_grad_(True) for t in (q, k)]
+    outs = diff.rope(leaves[0], leaves[1], cos.to(DEV), sin.to(DEV))
+    grads = torch.autograd.grad(outs, leaves, [gq.to(DEV), gk.to(DEV)])
+    cpu = [t.clone().requires_grad_(True) for t in (q, k)]
+    native = torch.autograd.grad(oracle.rope(cpu[0], cpu[1], cos, sin), cpu, [gq, gk])
+    for mine, want in zip(grads, native):
+        assert torch.equal(mine.cpu(), want), "paired rope backward is not bit-identical to autograd of the reference"
+
+
+@pytest.mark.parametrize("batch,seq,hq,hk,dim,dtype", [(2, 33, 8, 2, 128, torch.bfloat16), (1, 9, 3, 1, 64, torch.float16), (2, 5, 2, 2, 16, torch.float32)])
+def test_llama4_rope_backward(batch, seq, hq, hk, dim, dtype):
+    q, k = randn(2100 + dim, batch, seq, hq, dim, dtype=dtype), randn(2101 + dim, batch, seq, hk, dim, dtype=dtype)
+    gq, gk = randn(2102 + dim, batch, seq, hq, dim, dtype=dtype), randn(2103 + dim, batch, seq, hk, dim, dtype=dtype)
+    angle = randn(2104, seq, dim // 2)
+    freqs = torch.stack((angle.cos(), angle.sin()), -1).to(dtype)
+    leaves = [t.to(DEV).requires_grad_(True) for t in (q, k)]
+    outs = diff.llama4_rope(leaves[0], leaves[1], freqs.to(DEV))
+    grads = torch.autograd.grad(outs, leaves, [gq.to(DEV), gk.to(DEV)])
+    cpu = [t.clone().requires_grad_(True) for t in (q, k)]
+    native = torch.autograd.grad(oracle.llama4_rope(cpu[0], cpu[1], freqs), cpu, [gq, gk])
+    for mine, want in zip(grads, native):
+        assert torch.equal(mine.cpu(), want), "llama4 rope backward is not bit-identical to autograd of the reference"
+
+
 def test_registry_serves_training_calls():
     x = randn(1300, 8, 256, dtype=torch.bfloat16).to(DEV).requires_grad_(True)
     out = kernels.swiglu(x, x, backend="b200")
