@@ -690,6 +690,12 @@ def main() -> None:
             torch_eager_incumbent(device, per_op, args.records)
             per_op["beyond_the_five_configs"] = bench_extra_ops(device, peak_gbs, sampler)
             per_op["moe_expert_mlp_bf16"] = bench_grouped_gemm(device, sampler)
+            # the CPU reference of every configuration on a bounded token sample, beside the GPU number
+            for key, fraction in (("rms_norm_fp32", 1.0), ("rotary_bf16", 1 / 8), ("swiglu_bf16", 1 / 8), ("moe_bf16", 1 / 64)):
+                seconds, cpu_tokens, note = cpu_reference_time(key, fraction, repeats=3)
+                cpu_rate = cpu_tokens / seconds
+                per_op[key]["cpu_reference"] = {"tokens_per_s": round(cpu_rate, 1), "cores": os.cpu_count() or 1, "sample": note,
+                                                "gpu_over_cpu": round(per_op[key]["tokens_per_s"] / cpu_rate, 1)}
     if dist is not None:
         dist.barrier()
         if not args.skip_per_op:
