@@ -46,6 +46,20 @@ import torch.distributed as dist
 from torch import Tensor
 
 
+def check_counts(counts_all: Tensor, rank: int) -> None:
+    """The gathered [world, experts] count table must be usable before any row moves: a malformed table (a rank that
+    posted garbage, a table of the wrong shape) is reported on the host instead of becoming a wild address."""
+    if counts_all.dim() != 2 or counts_all.shape[0] == 0:
+        raise ValueError(f"expected a [world, experts] count table, got shape {tuple(counts_all.shape)}")
+    world, experts = counts_all.shape
+    if experts % world != 0:
+        raise ValueError(f"experts={experts} must be a multiple of the world size {world}")
+    if not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside the table's world size {world}")
+    if counts_all.is_floating_point() or bool((counts_all < 0).any()):
+        raise ValueError("per-expert counts must be non-negative integers")
+
+
 def p2p_plan(counts_all: Tensor, rank: int) -> tuple[Tensor, list[int], Tensor]:
     """Addressing for the fused exchange, from the gathered counts (host arithmetic).
 
@@ -54,6 +68,7 @@ def p2p_plan(counts_all: Tensor, rank: int) -> tuple[Tensor, list[int], Tensor]:
     the owner's buffer is expert-major, and inside an expert the source ranks follow in rank order;
     rows_per_rank[r] is how many rows rank r receives in total; expert_offsets delimit this rank's
     own experts inside its buffer."""
+    check_counts(counts_all, rank)
     world, experts = counts_all.shape
     if experts % world != 0:
         raise ValueError(f"experts={experts} must be a multiple of the world size {world}")
@@ -94,6 +109,7 @@ def exchange_plan(counts_all: Tensor, rank: int) -> tuple[list[int], list[int], 
     Returns (send_counts, recv_counts, segment_source_start, segment_length, expert_offsets):
     segments are listed in output order (local expert major, source rank minor); segment i covers
     arrived[segment_source_start[i] : +segment_length[i]]."""
+    check_counts(counts_all, rank)
     world, experts = counts_all.shape
     if experts % world != 0:
         raise ValueError(f"experts={experts} must be a multiple of the world size {world}")

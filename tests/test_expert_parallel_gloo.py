@@ -154,3 +154,69 @@ def test_fused_exchange_addressing_emulated_on_cpu(world, tokens, experts, top_k
             picked = torch.stack([buffers[int(dst_rank[t, sel[t]])][int(dst_row[t, sel[t]])] for t in range(dst_rank.shape[0])]) if dst_rank.shape[0] else torch.zeros(0, hidden)
             acc = acc + picked.float() * w_r.gather(1, sel[:, None])
         assert torch.equal(acc.to(torch.bfloat16), want[bounds[r] : bounds[r + 1]])
+
+
+# ------------------------------------------------- failures, made on the host --
+
+def test_malformed_count_tables_are_rejected_before_any_row_moves():
+    good = torch.tensor([[3, 1, 0, 2], [0, 4, 1, 1]], dtype=torch.int32)
+    exchange_plan(good, 0)
+    p2p_plan(good, 1)
+    for bad, rank in ((good[:, :3], 0),                      # experts not divisible by the world size
+                      (good.clone().index_put_((torch.tensor(1), torch.tensor(2)), torch.tensor(-5, dtype=torch.int32)), 0),  # a negative count
+                      (good, 2),                             # a rank outside the table
+                      (good.float(), 0),                     # not integers
+                      (good.view(-1), 0)):                   # not a table
+        with pytest.raises(ValueError):
+            exchange_plan(bad, rank)
+        with pytest.raises(ValueError):
+            p2p_plan(bad, rank)
+
+
+def _absent_peer_worker(rank, world, port, out):
+    import datetime
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    try:
+        if rank == 1:
+            out[rank] = "left before the step"  # between steps, nothing of its own in flight
+            return
+        x, logits = _inputs(32, 64, 4)
+        ep = ExpertParallel(4, 2, local_ops=CPU_OPS)
+        try:
+            ep.dispatch(x[:16], logits[:16])
+            out[rank] = "no error"
+        except Exception as error:  # the count exchange cannot complete without the peer
+            out[rank] = f"error: {type(error).__name__}"
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+@pytest.mark.timeout(120)
+def test_a_rank_that_never_posts_its_counts_is_an_error_not_a_hang():
+    """One rank leaves before the step; the other's count exchange ends with an error inside the group's timeout."""
+    out = mp.Manager().dict()
+    mp.spawn(_absent_peer_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    assert out[1] == "left before the step"
+    assert out[0].startswith("error:"), out[0]
+
+
+def _capacity_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        table = torch.tensor([[40, 0], [25, 1]], dtype=torch.int32)  # rank 0 would receive 65 rows
+        _, rows_per_rank, _ = p2p_plan(table, rank)
+        out[rank] = rows_per_rank
+    finally:
+        dist.destroy_process_group()
+
+
+def test_every_rank_derives_the_same_receive_sizes():
+    out = mp.Manager().dict()
+    mp.spawn(_capacity_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    assert out[0] == out[1] == [65, 1]
