@@ -366,6 +366,10 @@ def bench_extra_ops(device, peak_gbs: float, sampler, scale: float = 1.0, steps:
     n = 2 * (q.numel() + k.numel()) * 2
     run("qk_norm_rope_bf16 q[8,32,4096,128] k[8,8,4096,128]", lambda: ops.qk_norm_rope(q, k, head_weight, head_weight, cos, sin),
         n + 2 * cos.numel() * 2 + 2 * 128 * 2)
+    grad_q, grad_k = torch.randn_like(q), torch.randn_like(k)
+    run("qk_norm_rope_backward_bf16 q[8,32,4096,128] k[8,8,4096,128]",
+        lambda: ops.qk_norm_rope_backward(grad_q, grad_k, q, k, head_weight, head_weight, cos, sin), 1.5 * n + 2 * cos.numel() * 2)
+    del grad_q, grad_k
     w3 = workloads.rotary_bf16(scale).to(device)
     q3, k3 = w3.inputs["q"], w3.inputs["k"]
     freqs = torch.stack((w3.inputs["cos"], w3.inputs["sin"]), -1).to(torch.bfloat16)

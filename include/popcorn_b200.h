@@ -194,6 +194,23 @@ int b200_qk_norm_rope(const void* q, const void* k, const void* q_weight, const 
                       double eps, int dtype, void* stream);
 
 /*
+ * Backward of b200_qk_norm_rope: gradients of q, k (contiguous [batch, heads, seq, head_dim]) and of the two
+ * weights ([head_dim]) from the gradients of the two outputs (contiguous, same shapes as q and k).  The row
+ * statistics are recomputed from q and k.  What autograd derives from the fused op's reference
+ * (examples/03_write_a_kernel.ipynb cell 3); the notebook's hand-written Triton backward is its cells 8-11.
+ * scratch: b200_qk_norm_rope_backward_scratch_bytes(batch, seq, head_dim, dtype) bytes of device memory,
+ * 16-byte aligned, written by the call (per-CTA partial column sums of the weight gradients).
+ */
+int b200_qk_norm_rope_backward_scratch_bytes(int64_t batch, int64_t seq, int64_t head_dim, int dtype, size_t* bytes);
+int b200_qk_norm_rope_backward(const void* grad_q_out, const void* grad_k_out, const void* q, const void* k,
+                               const void* q_weight, const void* k_weight, const void* cos, const void* sin,
+                               void* grad_q, void* grad_k, void* grad_q_weight, void* grad_k_weight,
+                               int64_t batch, int64_t q_heads, int64_t k_heads, int64_t seq, int64_t head_dim, int64_t cos_batch,
+                               int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                               int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+                               double eps, int dtype, void* scratch, size_t scratch_bytes, void* stream);
+
+/*
  * Llama 4 rotary embedding of queries and keys: channels are (real, imaginary) pairs multiplied by
  * unit complex numbers given as (cos, sin) pairs,
  *   y_re = round_T(round_T(re * f_re) - round_T(im * f_im)),  y_im = round_T(round_T(re * f_im) + round_T(im * f_re))

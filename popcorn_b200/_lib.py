@@ -41,6 +41,8 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "b200_rope_paired": (_int, [_ptr] * 6 + [_i64] * 18 + [_int, _ptr]),
     "b200_qk_norm_rope": (_int, [_ptr] * 8 + [_i64] * 18 + [_dbl, _int, _ptr]),
     "b200_llama4_rope": (_int, [_ptr] * 5 + [_i64] * 17 + [_int, _ptr]),
+    "b200_qk_norm_rope_backward_scratch_bytes": (_int, [_i64, _i64, _i64, _int, ctypes.POINTER(_size)]),
+    "b200_qk_norm_rope_backward": (_int, [_ptr] * 12 + [_i64] * 12 + [_dbl, _int, _ptr, _size, _ptr]),
     "b200_swiglu": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _int, _ptr]),
     "b200_geglu": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _int, _ptr]),
     "b200_rms_norm_gated": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _int, _int, _dbl, _ptr]),

@@ -65,6 +65,22 @@ class _PairedRope(torch.autograd.Function):
         return dq, dk, None, None
 
 
+class _QkNormRope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q: Tensor, k: Tensor, q_weight: Tensor, k_weight: Tensor, cos: Tensor, sin: Tensor, eps: float):
+        ctx.save_for_backward(q, k, q_weight, k_weight, cos, sin)
+        ctx.eps = eps
+        with torch.no_grad():
+            return ops.qk_norm_rope(q, k, q_weight, k_weight, cos, sin, eps)
+
+    @staticmethod
+    def backward(ctx, grad_q: Tensor, grad_k: Tensor):
+        q, k, q_weight, k_weight, cos, sin = ctx.saved_tensors
+        with torch.no_grad():
+            dq, dk, dqw, dkw = ops.qk_norm_rope_backward(grad_q, grad_k, q, k, q_weight, k_weight, cos, sin, ctx.eps)
+        return dq, dk, dqw, dkw, None, None, None
+
+
 class _Llama4Rope(torch.autograd.Function):
     """Multiplication by unit complex numbers: the transpose multiplies by their conjugates."""
 
@@ -169,3 +185,8 @@ def rope(q: Tensor, k: Tensor, cos: Tensor, sin: Tensor) -> tuple[Tensor, Tensor
 def llama4_rope(q: Tensor, k: Tensor, freqs: Tensor) -> tuple[Tensor, Tensor]:
     """Llama 4 rotary embedding with gradients for q and k (freqs are constants, as in the reference)."""
     return _Llama4Rope.apply(q, k, freqs.detach())
+
+
+def qk_norm_rope(q: Tensor, k: Tensor, q_weight: Tensor, k_weight: Tensor, cos: Tensor, sin: Tensor, eps: float = 1e-6) -> tuple[Tensor, Tensor]:
+    """Fused per-head RMSNorm + paired rotary embedding with gradients for q, k and both weights."""
+    return _QkNormRope.apply(q, k, q_weight, k_weight, cos.detach(), sin.detach(), eps)

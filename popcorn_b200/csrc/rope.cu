@@ -770,6 +770,243 @@ int run_llama4(const Llama4Args& p, cudaStream_t st) {
   return after_launch("llama4_rope_scalar_kernel");
 }
 
+
+// ------------------------------------------------- qk_norm_rope backward --
+//
+// What autograd derives from the fused op's reference (examples/03_write_a_kernel.ipynb, cell 3; the
+// notebook's own hand-written backward is cells 8-9), per head row x with n = round_T(x r), r = 1/rms(x):
+//   g   = transpose of the rotation applied to dy, in T:  g1 = dy1 c1 + dy2 s2,  g2 = dy2 c2 - dy1 s1
+//   dw += round_T(g * n)                       (summed over every row of the tensor)
+//   u   = round_T(g * w),  dx = round_T(u r - x r^3 <u, x> / head_dim)      (fp32 inside)
+// r is recomputed from x (no saved statistics).  Thread mapping as in rope_paired_kernel; the per-thread
+// column sums of dw are reduced over the positions of a warp by shuffles, over the warps of the CTA through
+// shared memory, and written to this CTA's line of `partial` ([gridDim.x][2][head_dim] fp32), which
+// sum_lines_kernel adds up.
+struct NormRopeBwdArgs {
+  PairedArgs fwd;        // q / k (inputs of the forward), tables, weights, eps; t[i].out = grad of the input
+  const void* dy[2];     // gradients of the outputs, contiguous [batch, heads, seq, head_dim]
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256, 2) norm_rope_bwd_kernel(const NormRopeBwdArgs a, float* __restrict__ partial) {
+  constexpr int V = Num<T>::kVec;
+  const PairedArgs& p = a.fwd;
+  pdl_prologue();
+  __shared__ float red[8][32 * 2 * 8];  // [warp][unit][lo|hi][element]: at most 32 units of 2 x 8 columns
+  const int half = p.head_dim / 2;
+  const int upr = half / V;  // units per row: a power of two <= 32 on this path
+  const int tile_pos = 256 / upr;
+  const int64_t tiles = (p.seq + tile_pos - 1) / tile_pos;
+  const int64_t tile = blockIdx.x % tiles;
+  const int b = static_cast<int>(blockIdx.x / tiles);
+  const int unit = threadIdx.x % upr, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int64_t pos = tile * tile_pos + threadIdx.x / upr;
+  const bool active = pos < p.seq;
+  if (!active) pos = p.seq - 1;  // keeps the shuffles full-width; contributes nothing
+  const float cols_f = static_cast<float>(p.head_dim);
+  const float inv_cols = (p.head_dim & (p.head_dim - 1)) == 0 ? 1.0f / cols_f : 0.f;
+
+  const T* cos = static_cast<const T*>(p.cos) + b * p.cs_stride_b + pos * p.head_dim + unit * V;
+  const T* sin = static_cast<const T*>(p.sin) + b * p.cs_stride_b + pos * p.head_dim + unit * V;
+  float c1[V], c2[V], s1[V], s2[V];
+  Num<T>::unpack(ld_reuse(cos), c1);
+  Num<T>::unpack(ld_reuse(cos + half), c2);
+  Num<T>::unpack(ld_reuse(sin), s1);
+  Num<T>::unpack(ld_reuse(sin + half), s2);
+
+  for (int ti = 0; ti < 2; ++ti) {
+    const PairedTensor& t = p.t[ti];
+    float acc_lo[V], acc_hi[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc_lo[j] = acc_hi[j] = 0.f;
+    if (t.heads > 0) {
+      float w1[V], w2[V];
+      Num<T>::unpack(ld_reuse(static_cast<const T*>(p.weight[ti]) + unit * V), w1);
+      Num<T>::unpack(ld_reuse(static_cast<const T*>(p.weight[ti]) + unit * V + half), w2);
+      const T* xin = static_cast<const T*>(t.x) + b * t.xs_b + pos * t.xs_s + unit * V;
+      T* dx = static_cast<T*>(t.out) + b * t.os_b + pos * t.os_s + unit * V;
+      const T* dy = static_cast<const T*>(a.dy[ti]) + (static_cast<int64_t>(b) * t.heads * p.seq + pos) * p.head_dim + unit * V;
+      for (int h = 0; h < t.heads; ++h) {
+        const uint4 x_lo = ld_stream(xin + h * t.xs_h), x_hi = ld_stream(xin + h * t.xs_h + half);
+        const uint4 d_lo = ld_stream(dy + static_cast<int64_t>(h) * p.seq * p.head_dim);
+        const uint4 d_hi = ld_stream(dy + static_cast<int64_t>(h) * p.seq * p.head_dim + half);
+        float x1[V], x2[V], d1[V], d2[V];
+        Num<T>::unpack(x_lo, x1);
+        Num<T>::unpack(x_hi, x2);
+        Num<T>::unpack(d_lo, d1);
+        Num<T>::unpack(d_hi, d2);
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < V; ++j) ss = __fmaf_rn(x2[j], x2[j], __fmaf_rn(x1[j], x1[j], ss));
+        for (int o = upr >> 1; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
+        const float r = inv_rms(ss, cols_f, inv_cols, p.eps);
+        float u1[V], u2[V], dot = 0.f;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float g1 = Num<T>::rt(__fadd_rn(Num<T>::rt(__fmul_rn(d1[j], c1[j])), Num<T>::rt(__fmul_rn(d2[j], s2[j]))));
+          const float g2 = Num<T>::rt(__fsub_rn(Num<T>::rt(__fmul_rn(d2[j], c2[j])), Num<T>::rt(__fmul_rn(d1[j], s1[j]))));
+          if (active) {
+            acc_lo[j] = __fadd_rn(acc_lo[j], Num<T>::rt(__fmul_rn(g1, Num<T>::rt(__fmul_rn(x1[j], r)))));
+            acc_hi[j] = __fadd_rn(acc_hi[j], Num<T>::rt(__fmul_rn(g2, Num<T>::rt(__fmul_rn(x2[j], r)))));
+          }
+          u1[j] = Num<T>::rt(__fmul_rn(g1, w1[j]));
+          u2[j] = Num<T>::rt(__fmul_rn(g2, w2[j]));
+          dot = __fmaf_rn(u2[j], x2[j], __fmaf_rn(u1[j], x1[j], dot));
+        }
+        for (int o = upr >> 1; o > 0; o >>= 1) dot = __fadd_rn(dot, __shfl_xor_sync(0xffffffffu, dot, o));
+        const float dot_over_n = inv_cols > 0.f ? __fmul_rn(dot, inv_cols) : __fdiv_rn(dot, cols_f);
+        const float coef = -__fmul_rn(__fmul_rn(__fmul_rn(r, r), r), dot_over_n);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          u1[j] = __fmaf_rn(u1[j], r, __fmul_rn(x1[j], coef));
+          u2[j] = __fmaf_rn(u2[j], r, __fmul_rn(x2[j], coef));
+        }
+        if (active) {
+          st_stream(dx + h * t.os_h, Num<T>::pack(u1));
+          st_stream(dx + h * t.os_h + half, Num<T>::pack(u2));
+        }
+      }
+    }
+    // column sums of this CTA: lanes with the same unit sit `upr` apart inside a warp
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      for (int o = upr; o < 32; o <<= 1) {
+        acc_lo[j] = __fadd_rn(acc_lo[j], __shfl_xor_sync(0xffffffffu, acc_lo[j], o));
+        acc_hi[j] = __fadd_rn(acc_hi[j], __shfl_xor_sync(0xffffffffu, acc_hi[j], o));
+      }
+    }
+    __syncthreads();  // `red` is free again (second tensor)
+    if (lane < upr) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        red[warp][(unit * 2 + 0) * 8 + j] = acc_lo[j];
+        red[warp][(unit * 2 + 1) * 8 + j] = acc_hi[j];
+      }
+    }
+    __syncthreads();
+    // when a position group spans several warps' worth of lanes (upr = 32) every warp holds other units' sums too:
+    // with upr <= 32 and 256 threads each warp covers 32 / upr positions of all units, so the eight warps add up
+    for (int idx = threadIdx.x; idx < upr * 2 * V; idx += 256) {
+      const int u = idx / (2 * V), part = (idx / V) & 1, j = idx % V;
+      float total = 0.f;
+#pragma unroll
+      for (int wv = 0; wv < 8; ++wv) total = __fadd_rn(total, red[wv][(u * 2 + part) * 8 + j]);
+      partial[(static_cast<int64_t>(blockIdx.x) * 2 + ti) * p.head_dim + part * half + u * V + j] = total;
+    }
+  }
+}
+
+// out[ti][c] = round_T(sum over lines of partial[line][ti][c]), lines added in order.
+template <typename T>
+__global__ void __launch_bounds__(256) sum_lines_kernel(const float* __restrict__ partial, int lines, int head_dim, T* __restrict__ dw0, T* __restrict__ dw1) {
+  pdl_prologue();
+  const int idx = blockIdx.x * 256 + threadIdx.x;
+  if (idx >= 2 * head_dim) return;
+  const int ti = idx / head_dim, c = idx % head_dim;
+  T* out = ti == 0 ? dw0 : dw1;
+  if (out == nullptr) return;
+  float acc = 0.f;
+  for (int l = 0; l < lines; ++l) acc = __fadd_rn(acc, partial[(static_cast<int64_t>(l) * 2 + ti) * head_dim + c]);
+  out[c] = Num<T>::down(acc);
+}
+
+// Any even head_dim, any alignment: one warp per (batch, head, position) row, column sums by atomic adds into
+// line 0 of `partial` (zeroed by the caller).
+template <typename T>
+__global__ void __launch_bounds__(256) norm_rope_bwd_scalar_kernel(const NormRopeBwdArgs a, float* __restrict__ partial) {
+  const PairedArgs& p = a.fwd;
+  pdl_prologue();
+  const int half = p.head_dim / 2;
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const int64_t n_warps = static_cast<int64_t>(gridDim.x) * 8;
+  const float cols_f = static_cast<float>(p.head_dim);
+  for (int ti = 0; ti < 2; ++ti) {
+    const PairedTensor& t = p.t[ti];
+    const T* weight = static_cast<const T*>(p.weight[ti]);
+    const int64_t rows = static_cast<int64_t>(p.batch) * t.heads * p.seq;
+    for (int64_t row = warp; row < rows; row += n_warps) {
+      const int64_t pos = row % p.seq;
+      const int h = static_cast<int>((row / p.seq) % t.heads);
+      const int64_t b = row / p.seq / t.heads;
+      const T* xin = static_cast<const T*>(t.x) + b * t.xs_b + h * t.xs_h + pos * t.xs_s;
+      T* dx = static_cast<T*>(t.out) + b * t.os_b + h * t.os_h + pos * t.os_s;
+      const T* dy = static_cast<const T*>(a.dy[ti]) + row * p.head_dim;
+      const T* cos = static_cast<const T*>(p.cos) + b * p.cs_stride_b + pos * p.head_dim;
+      const T* sin = static_cast<const T*>(p.sin) + b * p.cs_stride_b + pos * p.head_dim;
+      float ss = 0.f;
+      for (int j = lane; j < p.head_dim; j += 32) {
+        const float v = Num<T>::up(xin[j]);
+        ss = __fmaf_rn(v, v, ss);
+      }
+      const float r = inv_rms(warp_sum(ss), cols_f, 0.f, p.eps);
+      auto g_of = [&](int j) {  // transpose of the rotation at column j
+        if (j < half)
+          return Num<T>::rt(__fadd_rn(Num<T>::rt(__fmul_rn(Num<T>::up(dy[j]), Num<T>::up(cos[j]))),
+                                      Num<T>::rt(__fmul_rn(Num<T>::up(dy[j + half]), Num<T>::up(sin[j + half])))));
+        return Num<T>::rt(__fsub_rn(Num<T>::rt(__fmul_rn(Num<T>::up(dy[j]), Num<T>::up(cos[j]))),
+                                    Num<T>::rt(__fmul_rn(Num<T>::up(dy[j - half]), Num<T>::up(sin[j - half])))));
+      };
+      float dot = 0.f;
+      for (int j = lane; j < p.head_dim; j += 32) {
+        const float x = Num<T>::up(xin[j]), g = g_of(j);
+        atomicAdd(&partial[ti * p.head_dim + j], Num<T>::rt(__fmul_rn(g, Num<T>::rt(__fmul_rn(x, r)))));
+        dot = __fmaf_rn(Num<T>::rt(__fmul_rn(g, Num<T>::up(weight[j]))), x, dot);
+      }
+      dot = warp_sum(dot);
+      const float coef = -__fmul_rn(__fmul_rn(__fmul_rn(r, r), r), __fdiv_rn(dot, cols_f));
+      for (int j = lane; j < p.head_dim; j += 32) {
+        const float x = Num<T>::up(xin[j]);
+        const float u = Num<T>::rt(__fmul_rn(g_of(j), Num<T>::up(weight[j])));
+        dx[j] = Num<T>::down(__fmaf_rn(u, r, __fmul_rn(x, coef)));
+      }
+    }
+  }
+}
+
+int norm_rope_bwd_lines(int64_t batch, int64_t seq, int64_t head_dim, int elem_size) {
+  const int v = 16 / elem_size, half = static_cast<int>(head_dim / 2);
+  if (half % v != 0) return 1;
+  const int upr = half / v;
+  if (upr <= 0 || upr > 32 || (upr & (upr - 1)) != 0) return 1;
+  const int64_t lines = ceil_div(seq, 256 / upr) * batch;
+  return lines > 0x7fffffffLL ? 1 : static_cast<int>(lines);
+}
+
+template <typename T>
+int run_norm_rope_bwd(const NormRopeBwdArgs& a, void* dw0, void* dw1, float* scratch, cudaStream_t st) {
+  constexpr int V = Num<T>::kVec;
+  const PairedArgs& p = a.fwd;
+  const int half = p.head_dim / 2;
+  const int upr = half % V == 0 ? half / V : 0;
+  bool vec = upr > 0 && upr <= 32 && (upr & (upr - 1)) == 0 && aligned(p.cos, 16) && aligned(p.sin, 16) && p.cs_stride_b % V == 0;
+  for (int i = 0; i < 2; ++i) {
+    const PairedTensor& t = p.t[i];
+    if (t.heads == 0) continue;
+    vec = vec && aligned(t.x, 16) && aligned(t.out, 16) && aligned(a.dy[i], 16) && aligned(p.weight[i], 16) && t.xs_b % V == 0 &&
+          t.xs_h % V == 0 && t.xs_s % V == 0 && t.os_b % V == 0 && t.os_h % V == 0 && t.os_s % V == 0;
+  }
+  int lines = 1;
+  if (vec) {
+    lines = norm_rope_bwd_lines(p.batch, p.seq, p.head_dim, sizeof(T));
+    launch(norm_rope_bwd_kernel<T>, static_cast<unsigned>(lines), 256, 0, st, a, scratch);
+    if (int rc = after_launch("norm_rope_bwd_kernel")) return rc;
+  } else {
+    if (cudaMemsetAsync(scratch, 0, sizeof(float) * 2 * p.head_dim, st) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return fail(B200_ERR_LAUNCH, "b200_qk_norm_rope_backward: cannot clear the scratch buffer");
+    }
+    int64_t rows = 0;
+    for (int i = 0; i < 2; ++i) rows += static_cast<int64_t>(p.batch) * p.t[i].heads * p.seq;
+    const int64_t grid = std::max<int64_t>(1, std::min<int64_t>(ceil_div(rows, 8), static_cast<int64_t>(sm_count()) * 16));
+    launch(norm_rope_bwd_scalar_kernel<T>, static_cast<unsigned>(grid), 256, 0, st, a, scratch);
+    if (int rc = after_launch("norm_rope_bwd_scalar_kernel")) return rc;
+  }
+  launch(sum_lines_kernel<T>, static_cast<unsigned>(ceil_div(2 * p.head_dim, 256)), 256, 0, st, static_cast<const float*>(scratch), lines,
+         p.head_dim, static_cast<T*>(dw0), static_cast<T*>(dw1));
+  return after_launch("sum_lines_kernel");
+}
+
 template <typename T>
 int run_cs(RopeArgs& p, int cs_dtype, int interleaved, cudaStream_t st) {
   if (cs_dtype == B200_F32) {
@@ -975,5 +1212,71 @@ extern "C" int b200_llama4_rope(const void* q, const void* k, const void* freqs,
   p.head_dim = static_cast<int>(head_dim);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   B200_DISPATCH_DTYPE(dtype, T, return run_llama4<T>(p, st));
+  return B200_OK;
+}
+
+extern "C" int b200_qk_norm_rope_backward_scratch_bytes(int64_t batch, int64_t seq, int64_t head_dim, int dtype, size_t* bytes) {
+  B200_REQUIRE_PTR(bytes);
+  if (!dtype_ok(dtype)) return fail(B200_ERR_DTYPE, "%s: unsupported dtype %d", __func__, dtype);
+  if (batch < 0 || seq < 0 || head_dim < 0) return fail(B200_ERR_SHAPE, "%s: negative size", __func__);
+  const int lines = norm_rope_bwd_lines(batch, seq, head_dim, static_cast<int>(dtype_size(dtype)));
+  *bytes = static_cast<size_t>(lines > 0 ? lines : 1) * 2 * static_cast<size_t>(head_dim > 0 ? head_dim : 1) * sizeof(float);
+  return B200_OK;
+}
+
+extern "C" int b200_qk_norm_rope_backward(const void* grad_q_out, const void* grad_k_out, const void* q, const void* k,
+                                          const void* q_weight, const void* k_weight, const void* cos, const void* sin,
+                                          void* grad_q, void* grad_k, void* grad_q_weight, void* grad_k_weight,
+                                          int64_t batch, int64_t q_heads, int64_t k_heads, int64_t seq, int64_t head_dim, int64_t cos_batch,
+                                          int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_s,
+                                          int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_s,
+                                          double eps, int dtype, void* scratch, size_t scratch_bytes, void* stream) {
+  if (!dtype_ok(dtype)) return fail(B200_ERR_DTYPE, "%s: unsupported dtype %d", __func__, dtype);
+  if (batch < 0 || q_heads < 0 || k_heads < 0 || seq < 0 || head_dim < 0) return fail(B200_ERR_SHAPE, "%s: negative size", __func__);
+  if (head_dim % 2 != 0) return fail(B200_ERR_SHAPE, "%s: head_dim=%lld must be even", __func__, (long long)head_dim);
+  if (cos_batch != 1 && cos_batch != batch) return fail(B200_ERR_SHAPE, "%s: cos_batch must be 1 or batch", __func__);
+  if (batch > 0x7fffffffLL || q_heads > (1 << 20) || k_heads > (1 << 20) || head_dim > (1 << 20))
+    return fail(B200_ERR_SHAPE, "%s: size out of range", __func__);
+  if (head_dim == 0) return B200_OK;
+  if (scratch == nullptr) return fail(B200_ERR_NULL_POINTER, "%s: scratch is NULL", __func__);
+  if (q_heads > 0 && (grad_q_out == nullptr || q == nullptr || q_weight == nullptr || grad_q == nullptr || grad_q_weight == nullptr))
+    return fail(B200_ERR_NULL_POINTER, "%s: a query pointer is NULL", __func__);
+  if (k_heads > 0 && (grad_k_out == nullptr || k == nullptr || k_weight == nullptr || grad_k == nullptr || grad_k_weight == nullptr))
+    return fail(B200_ERR_NULL_POINTER, "%s: a key pointer is NULL", __func__);
+  if ((q_heads > 0 || k_heads > 0) && batch > 0 && seq > 0 && (cos == nullptr || sin == nullptr))
+    return fail(B200_ERR_NULL_POINTER, "%s: cos or sin is NULL", __func__);
+  const size_t es = dtype_size(dtype);
+  for (const void* ptr : {grad_q_out, grad_k_out, q, k, q_weight, k_weight, cos, sin, static_cast<const void*>(grad_q),
+                          static_cast<const void*>(grad_k), static_cast<const void*>(grad_q_weight), static_cast<const void*>(grad_k_weight)})
+    if (!aligned(ptr, es)) return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to the element size", __func__);
+  if (int rc = check_device()) return rc;
+  const size_t need = static_cast<size_t>(norm_rope_bwd_lines(batch, seq, head_dim, static_cast<int>(es))) * 2 * head_dim * sizeof(float);
+  if (scratch_bytes < need || !aligned(scratch, 16))
+    return fail(B200_ERR_SCRATCH, "%s: scratch needs %zu bytes, 16-byte aligned (got %zu)", __func__, need, scratch_bytes);
+  NormRopeBwdArgs a{};
+  PairedArgs& p = a.fwd;
+  // gradients of the inputs are written contiguously, [batch, heads, seq, head_dim]
+  p.t[0] = PairedTensor{q, grad_q, q_stride_b, q_stride_h, q_stride_s, q_heads * seq * head_dim, seq * head_dim, head_dim, static_cast<int>(q_heads)};
+  p.t[1] = PairedTensor{k, grad_k, k_stride_b, k_stride_h, k_stride_s, k_heads * seq * head_dim, seq * head_dim, head_dim, static_cast<int>(k_heads)};
+  p.cos = cos;
+  p.sin = sin;
+  p.cs_stride_b = cos_batch == 1 ? 0 : seq * head_dim;
+  p.seq = seq;
+  p.batch = static_cast<int>(batch);
+  p.head_dim = static_cast<int>(head_dim);
+  p.weight[0] = q_weight;
+  p.weight[1] = k_weight;
+  p.eps = static_cast<float>(eps);
+  a.dy[0] = grad_q_out;
+  a.dy[1] = grad_k_out;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (batch == 0 || seq == 0 || (q_heads == 0 && k_heads == 0)) {
+    // no rows: the weight gradients are zero
+    if (q_heads >= 0 && grad_q_weight) (void)cudaMemsetAsync(grad_q_weight, 0, head_dim * es, st);
+    if (k_heads >= 0 && grad_k_weight) (void)cudaMemsetAsync(grad_k_weight, 0, head_dim * es, st);
+    return B200_OK;
+  }
+  B200_DISPATCH_DTYPE(dtype, T, return run_norm_rope_bwd<T>(a, q_heads > 0 ? grad_q_weight : nullptr, k_heads > 0 ? grad_k_weight : nullptr,
+                                                             static_cast<float*>(scratch), st));
   return B200_OK;
 }

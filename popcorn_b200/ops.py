@@ -314,6 +314,37 @@ def qk_norm_rope(q: Tensor, k: Tensor, q_weight: Tensor, k_weight: Tensor, cos: 
     return q_out, k_out
 
 
+def qk_norm_rope_backward(grad_q_out: Tensor, grad_k_out: Tensor, q: Tensor, k: Tensor, q_weight: Tensor, k_weight: Tensor,
+                          cos: Tensor, sin: Tensor, eps: float = 1e-6) -> tuple[Tensor, Tensor, Tensor, Tensor]:
+    """(grad_q, grad_k, grad_q_weight, grad_k_weight) of qk_norm_rope; the row statistics are recomputed from q and k."""
+    device = _require_cuda(grad_q_out, grad_k_out, q, k, q_weight, k_weight, cos, sin)
+    code = _dtype_code(q, "qk_norm_rope_backward")
+    if grad_q_out.shape != q.shape or grad_k_out.shape != k.shape or q.dim() != 4 or k.dim() != 4:
+        raise ValueError("qk_norm_rope_backward: the output gradients must have the shapes of q and k")
+    batch, q_heads, seq, head_dim = q.shape
+    if not (grad_q_out.dtype == grad_k_out.dtype == k.dtype == q_weight.dtype == k_weight.dtype == cos.dtype == sin.dtype == q.dtype):
+        raise TypeError("qk_norm_rope_backward: all tensors must share a dtype")
+    q = q if head_dim <= 1 or q.stride(-1) == 1 else q.contiguous()
+    k = k if head_dim <= 1 or k.stride(-1) == 1 else k.contiguous()
+    grad_q = torch.empty(q.shape, dtype=q.dtype, device=device)
+    grad_k = torch.empty(k.shape, dtype=k.dtype, device=device)
+    grad_qw = torch.empty(head_dim, dtype=q.dtype, device=device)
+    grad_kw = torch.empty(head_dim, dtype=q.dtype, device=device)
+    need = ctypes.c_size_t(0)
+    with torch.cuda.device(device):
+        _lib.call("b200_qk_norm_rope_backward_scratch_bytes", batch, seq, head_dim, code, ctypes.byref(need))
+        scratch = torch.empty(max(need.value, 16), dtype=torch.uint8, device=device)
+        _lib.call(
+            "b200_qk_norm_rope_backward", _ptr(grad_q_out.contiguous()), _ptr(grad_k_out.contiguous()), _ptr(q), _ptr(k),
+            _ptr(q_weight.contiguous()), _ptr(k_weight.contiguous()), _ptr(cos.contiguous()), _ptr(sin.contiguous()),
+            _ptr(grad_q), _ptr(grad_k), _ptr(grad_qw), _ptr(grad_kw),
+            batch, q_heads, k.shape[1], seq, head_dim, cos.shape[0],
+            q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+            float(eps), code, _ptr(scratch), ctypes.c_size_t(scratch.numel()), _stream(device),
+        )
+    return grad_q, grad_k, grad_qw, grad_kw
+
+
 def llama4_rope(q: Tensor, k: Tensor, freqs: Tensor) -> tuple[Tensor, Tensor]:
     """Llama 4 rotary embedding of q and k, layout (batch, seq, heads, head_dim), freqs [seq, head_dim/2, 2]
     as (cos, sin) pairs (llama4_rope.py:27-39)."""

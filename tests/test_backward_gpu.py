@@ -134,6 +134,31 @@ def test_llama4_rope_backward(batch, seq, hq, hk, dim, dtype):
         assert torch.equal(mine.cpu(), want), "llama4 rope backward is not bit-identical to autograd of the reference"
 
 
+@pytest.mark.parametrize("batch,hq,hk,seq,dim,dtype", [(2, 8, 2, 33, 128, torch.bfloat16), (1, 3, 1, 70, 64, torch.float16), (2, 2, 2, 5, 16, torch.float32),
+                                                         (1, 2, 1, 9, 20, torch.bfloat16), (1, 4, 0, 40, 256, torch.bfloat16)])
+def test_qk_norm_rope_backward(batch, hq, hk, seq, dim, dtype):
+    q, k = randn(2200 + dim, batch, hq, seq, dim, dtype=dtype), randn(2201 + dim, batch, hk, seq, dim, dtype=dtype, scale=0.5)
+    qw, kw = (1 + 0.1 * randn(2202, dim)).to(dtype), (1 + 0.1 * randn(2203, dim)).to(dtype)
+    gq, gk = randn(2204 + dim, batch, hq, seq, dim, dtype=dtype), randn(2205 + dim, batch, hk, seq, dim, dtype=dtype)
+    angle = randn(2206, 1, seq, dim // 2)
+    cos, sin = torch.cos(angle).repeat(1, 1, 2).to(dtype), torch.sin(angle).repeat(1, 1, 2).to(dtype)
+    leaves = [t.to(DEV).requires_grad_(True) for t in (q, k, qw, kw)]
+    outs = diff.qk_norm_rope(*leaves, cos.to(DEV), sin.to(DEV), 1e-6)
+    grads = torch.autograd.grad(outs, leaves, [gq.to(DEV), gk.to(DEV)], allow_unused=True)
+
+    def reference(wide):
+        cast = (lambda t: t.double()) if wide else (lambda t: t.clone())
+        ls = [cast(t).requires_grad_(True) for t in (q, k, qw, kw)]
+        out = oracle.qk_norm_rope(*ls, cast(cos), cast(sin), 1e-6)
+        return torch.autograd.grad(out, ls, [cast(gq), cast(gk)], allow_unused=True)
+
+    native, truth = reference(False), reference(True)
+    for name, mine, nat, tru in zip(("grad_q", "grad_k", "grad_q_weight", "grad_k_weight"), grads, native, truth):
+        if tru is None or tru.numel() == 0 or (hk == 0 and "k" in name.split("_")[1]):
+            continue
+        grade(mine, nat, tru, dtype, f"{name} {batch}x{hq}/{hk}x{seq}x{dim}")
+
+
 def test_registry_serves_training_calls():
     x = randn(1300, 8, 256, dtype=torch.bfloat16).to(DEV).requires_grad_(True)
     out = kernels.swiglu(x, x, backend="b200")
