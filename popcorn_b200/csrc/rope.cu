@@ -808,62 +808,112 @@ __global__ void __launch_bounds__(256, 2) norm_rope_bwd_kernel(const NormRopeBwd
 
   const T* cos = static_cast<const T*>(p.cos) + b * p.cs_stride_b + pos * p.head_dim + unit * V;
   const T* sin = static_cast<const T*>(p.sin) + b * p.cs_stride_b + pos * p.head_dim + unit * V;
-  float c1[V], c2[V], s1[V], s2[V];
-  Num<T>::unpack(ld_reuse(cos), c1);
-  Num<T>::unpack(ld_reuse(cos + half), c2);
-  Num<T>::unpack(ld_reuse(sin), s1);
-  Num<T>::unpack(ld_reuse(sin + half), s2);
+  const uint4 c1w = ld_reuse(cos), c2w = ld_reuse(cos + half), s1w = ld_reuse(sin), s2w = ld_reuse(sin + half);
 
+  // g = round_T(round_T(d * c) + round_T(+-e * s)) on one 128-bit word: the transpose of the rotation, in T
+  auto rotate_back = [](uint4 d, uint4 c, uint4 e, uint4 sn, bool negate_e) {
+    if constexpr (sizeof(T) == 4) {
+      float fd[4], fc[4], fe[4], fs[4];
+      Num<T>::unpack(d, fd);
+      Num<T>::unpack(c, fc);
+      Num<T>::unpack(e, fe);
+      Num<T>::unpack(sn, fs);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) fd[j] = __fadd_rn(__fmul_rn(fd[j], fc[j]), __fmul_rn(negate_e ? -fe[j] : fe[j], fs[j]));
+      return Num<T>::pack(fd);
+    } else {
+      const uint32_t flip = negate_e ? 0x80008000u : 0u;
+      const uint32_t wd[4] = {d.x, d.y, d.z, d.w}, wc[4] = {c.x, c.y, c.z, c.w};
+      const uint32_t we[4] = {e.x, e.y, e.z, e.w}, ws[4] = {sn.x, sn.y, sn.z, sn.w};
+      uint32_t wo[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) wo[j] = Num<T>::add2(Num<T>::mul2(wd[j], wc[j]), Num<T>::mul2(we[j] ^ flip, ws[j]));
+      return make_uint4(wo[0], wo[1], wo[2], wo[3]);
+    }
+  };
+  // One half row (a 128-bit word x, the matching word g of the rotated-back gradient, the weight word w):
+  // adds round_T(g * round_T(x r)) to the column sums, leaves u = round_T(g * w) in `u` and returns <u, x>.
+  auto half_row = [](uint4 xw, uint4 gw, uint4 ww, float r, bool active, float (&acc)[V], float (&x)[V], float (&u)[V]) {
+    Num<T>::unpack(xw, x);
+    float dot = 0.f;
+    if constexpr (sizeof(T) == 4) {
+      float g[V], w[V];
+      Num<T>::unpack(gw, g);
+      Num<T>::unpack(ww, w);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        if (active) acc[j] = __fadd_rn(acc[j], __fmul_rn(g[j], __fmul_rn(x[j], r)));
+        u[j] = __fmul_rn(g[j], w[j]);
+        dot = __fmaf_rn(u[j], x[j], dot);
+      }
+    } else {
+      const uint32_t wg[4] = {gw.x, gw.y, gw.z, gw.w}, wwt[4] = {ww.x, ww.y, ww.z, ww.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float a0, a1;
+        Num<T>::unpack2(Num<T>::mul2(wg[j], Num<T>::pack2(__fmul_rn(x[2 * j], r), __fmul_rn(x[2 * j + 1], r))), a0, a1);
+        if (active) {
+          acc[2 * j] = __fadd_rn(acc[2 * j], a0);
+          acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], a1);
+        }
+        Num<T>::unpack2(Num<T>::mul2(wg[j], wwt[j]), u[2 * j], u[2 * j + 1]);
+        dot = __fmaf_rn(u[2 * j + 1], x[2 * j + 1], __fmaf_rn(u[2 * j], x[2 * j], dot));
+      }
+    }
+    return dot;
+  };
+
+  constexpr int UNROLL = 2;  // heads in flight per thread
   for (int ti = 0; ti < 2; ++ti) {
     const PairedTensor& t = p.t[ti];
     float acc_lo[V], acc_hi[V];
 #pragma unroll
     for (int j = 0; j < V; ++j) acc_lo[j] = acc_hi[j] = 0.f;
     if (t.heads > 0) {
-      float w1[V], w2[V];
-      Num<T>::unpack(ld_reuse(static_cast<const T*>(p.weight[ti]) + unit * V), w1);
-      Num<T>::unpack(ld_reuse(static_cast<const T*>(p.weight[ti]) + unit * V + half), w2);
+      const uint4 w1 = ld_reuse(static_cast<const T*>(p.weight[ti]) + unit * V);
+      const uint4 w2 = ld_reuse(static_cast<const T*>(p.weight[ti]) + unit * V + half);
       const T* xin = static_cast<const T*>(t.x) + b * t.xs_b + pos * t.xs_s + unit * V;
       T* dx = static_cast<T*>(t.out) + b * t.os_b + pos * t.os_s + unit * V;
       const T* dy = static_cast<const T*>(a.dy[ti]) + (static_cast<int64_t>(b) * t.heads * p.seq + pos) * p.head_dim + unit * V;
-      for (int h = 0; h < t.heads; ++h) {
-        const uint4 x_lo = ld_stream(xin + h * t.xs_h), x_hi = ld_stream(xin + h * t.xs_h + half);
-        const uint4 d_lo = ld_stream(dy + static_cast<int64_t>(h) * p.seq * p.head_dim);
-        const uint4 d_hi = ld_stream(dy + static_cast<int64_t>(h) * p.seq * p.head_dim + half);
-        float x1[V], x2[V], d1[V], d2[V];
-        Num<T>::unpack(x_lo, x1);
-        Num<T>::unpack(x_hi, x2);
-        Num<T>::unpack(d_lo, d1);
-        Num<T>::unpack(d_hi, d2);
-        float ss = 0.f;
+      const int64_t dy_h = static_cast<int64_t>(p.seq) * p.head_dim;
+      for (int h0 = 0; h0 < t.heads; h0 += UNROLL) {
+        uint4 x_lo[UNROLL], x_hi[UNROLL], d_lo[UNROLL], d_hi[UNROLL];
 #pragma unroll
-        for (int j = 0; j < V; ++j) ss = __fmaf_rn(x2[j], x2[j], __fmaf_rn(x1[j], x1[j], ss));
-        for (int o = upr >> 1; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
-        const float r = inv_rms(ss, cols_f, inv_cols, p.eps);
-        float u1[V], u2[V], dot = 0.f;
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
-          const float g1 = Num<T>::rt(__fadd_rn(Num<T>::rt(__fmul_rn(d1[j], c1[j])), Num<T>::rt(__fmul_rn(d2[j], s2[j]))));
-          const float g2 = Num<T>::rt(__fsub_rn(Num<T>::rt(__fmul_rn(d2[j], c2[j])), Num<T>::rt(__fmul_rn(d1[j], s1[j]))));
-          if (active) {
-            acc_lo[j] = __fadd_rn(acc_lo[j], Num<T>::rt(__fmul_rn(g1, Num<T>::rt(__fmul_rn(x1[j], r)))));
-            acc_hi[j] = __fadd_rn(acc_hi[j], Num<T>::rt(__fmul_rn(g2, Num<T>::rt(__fmul_rn(x2[j], r)))));
+        for (int q = 0; q < UNROLL; ++q) {
+          if (h0 + q < t.heads) {
+            x_lo[q] = ld_stream(xin + (h0 + q) * t.xs_h);
+            x_hi[q] = ld_stream(xin + (h0 + q) * t.xs_h + half);
+            d_lo[q] = ld_stream(dy + (h0 + q) * dy_h);
+            d_hi[q] = ld_stream(dy + (h0 + q) * dy_h + half);
           }
-          u1[j] = Num<T>::rt(__fmul_rn(g1, w1[j]));
-          u2[j] = Num<T>::rt(__fmul_rn(g2, w2[j]));
-          dot = __fmaf_rn(u2[j], x2[j], __fmaf_rn(u1[j], x1[j], dot));
         }
-        for (int o = upr >> 1; o > 0; o >>= 1) dot = __fadd_rn(dot, __shfl_xor_sync(0xffffffffu, dot, o));
-        const float dot_over_n = inv_cols > 0.f ? __fmul_rn(dot, inv_cols) : __fdiv_rn(dot, cols_f);
-        const float coef = -__fmul_rn(__fmul_rn(__fmul_rn(r, r), r), dot_over_n);
 #pragma unroll
-        for (int j = 0; j < V; ++j) {
-          u1[j] = __fmaf_rn(u1[j], r, __fmul_rn(x1[j], coef));
-          u2[j] = __fmaf_rn(u2[j], r, __fmul_rn(x2[j], coef));
-        }
-        if (active) {
-          st_stream(dx + h * t.os_h, Num<T>::pack(u1));
-          st_stream(dx + h * t.os_h + half, Num<T>::pack(u2));
+        for (int q = 0; q < UNROLL; ++q) {
+          if (h0 + q < t.heads) {  // uniform over the CTA
+            float x1[V], x2[V], u1[V], u2[V];
+            Num<T>::unpack(x_lo[q], x1);
+            Num<T>::unpack(x_hi[q], x2);
+            float ss = 0.f;
+#pragma unroll
+            for (int j = 0; j < V; ++j) ss = __fmaf_rn(x2[j], x2[j], __fmaf_rn(x1[j], x1[j], ss));
+            for (int o = upr >> 1; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
+            const float r = inv_rms(ss, cols_f, inv_cols, p.eps);
+            const uint4 g1 = rotate_back(d_lo[q], c1w, d_hi[q], s2w, false);  // g1 = dy1 c1 + dy2 s2
+            const uint4 g2 = rotate_back(d_hi[q], c2w, d_lo[q], s1w, true);   // g2 = dy2 c2 - dy1 s1
+            float dot = half_row(x_lo[q], g1, w1, r, active, acc_lo, x1, u1) + half_row(x_hi[q], g2, w2, r, active, acc_hi, x2, u2);
+            for (int o = upr >> 1; o > 0; o >>= 1) dot = __fadd_rn(dot, __shfl_xor_sync(0xffffffffu, dot, o));
+            const float dot_over_n = inv_cols > 0.f ? __fmul_rn(dot, inv_cols) : __fdiv_rn(dot, cols_f);
+            const float coef = -__fmul_rn(__fmul_rn(__fmul_rn(r, r), r), dot_over_n);
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+              u1[j] = __fmaf_rn(u1[j], r, __fmul_rn(x1[j], coef));
+              u2[j] = __fmaf_rn(u2[j], r, __fmul_rn(x2[j], coef));
+            }
+            if (active) {
+              st_stream(dx + (h0 + q) * t.os_h, Num<T>::pack(u1));
+              st_stream(dx + (h0 + q) * t.os_h + half, Num<T>::pack(u2));
+            }
+          }
         }
       }
     }
