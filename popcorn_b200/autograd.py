@@ -81,6 +81,28 @@ class _QkNormRope(torch.autograd.Function):
         return dq, dk, dqw, dkw, None, None, None
 
 
+class _RmsNormGatedSwish(torch.autograd.Function):
+    """out = z * silu(g), z = rms_norm(x, weight, bias).  The backward is a composition of kernels that exist:
+    swiglu_backward(grad_out, g, z) yields (grad_g, grad_z) with autograd's roundings, and rms_norm_backward turns
+    grad_z into the gradients of x, weight and bias; z is recomputed by the forward norm kernel, not saved."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, g: Tensor, weight: Tensor, bias: Tensor | None, eps: float) -> Tensor:
+        ctx.save_for_backward(x, g, weight, bias)
+        ctx.eps = eps
+        with torch.no_grad():
+            return ops.rms_norm_gated(x, g, weight, bias, "swish", eps)
+
+    @staticmethod
+    def backward(ctx, grad_out: Tensor):
+        x, g, weight, bias = ctx.saved_tensors
+        with torch.no_grad():
+            z = ops.rms_norm(x, weight, bias, ctx.eps)
+            grad_g, grad_z = ops.swiglu_backward(grad_out.contiguous(), g, z)
+            grad_x, grad_w, grad_b = ops.rms_norm_backward(grad_z, x, weight, bias is not None, ctx.eps)
+        return grad_x, grad_g, grad_w, grad_b, None
+
+
 class _Llama4Rope(torch.autograd.Function):
     """Multiplication by unit complex numbers: the transpose multiplies by their conjugates."""
 
@@ -190,3 +212,10 @@ def llama4_rope(q: Tensor, k: Tensor, freqs: Tensor) -> tuple[Tensor, Tensor]:
 def qk_norm_rope(q: Tensor, k: Tensor, q_weight: Tensor, k_weight: Tensor, cos: Tensor, sin: Tensor, eps: float = 1e-6) -> tuple[Tensor, Tensor]:
     """Fused per-head RMSNorm + paired rotary embedding with gradients for q, k and both weights."""
     return _QkNormRope.apply(q, k, q_weight, k_weight, cos.detach(), sin.detach(), eps)
+
+
+def rms_norm_gated(x: Tensor, g: Tensor, weight: Tensor, bias: Tensor | None = None, activation: str = "swish", eps: float = 1e-6) -> Tensor:
+    """Gated RMS norm; with the swish gate, gradients for x, g, weight and bias (the sigmoid gate is forward-only)."""
+    if activation != "swish":
+        return ops.rms_norm_gated(x, g, weight, bias, activation, eps)
+    return _RmsNormGatedSwish.apply(x, g, weight, bias, eps)

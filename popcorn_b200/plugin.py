@@ -29,7 +29,7 @@ from torch import Tensor
 BACKEND = "b200"
 EXISTING_OPS = ("rms_norm", "add_rms_norm", "rotary_embedding", "rope", "llama4_rope", "swiglu", "geglu", "rms_norm_gated", "l2_norm", "layer_norm", "momoe")
 NEW_OPS = ("moe_route", "moe_permute", "moe_unpermute", "qk_norm_rope")
-DIFFERENTIABLE_OPS = ("rms_norm", "add_rms_norm", "swiglu", "geglu", "rotary_embedding", "rope", "llama4_rope", "qk_norm_rope")
+DIFFERENTIABLE_OPS = ("rms_norm", "add_rms_norm", "swiglu", "geglu", "rotary_embedding", "rope", "llama4_rope", "qk_norm_rope", "rms_norm_gated")
 
 _SUPPORTED = (torch.float32, torch.float16, torch.bfloat16)
 
@@ -51,7 +51,15 @@ def accepts_16bit(**arguments: Any) -> bool:
     return all(t.dtype == x.dtype for name, t in arguments.items() if isinstance(t, Tensor) and name.endswith("_weight"))
 
 
-PREDICATES = {"momoe": accepts_16bit}
+def accepts_gated(**arguments: Any) -> bool:
+    """`accepts`, except training calls with the sigmoid gate: only the swish gate has a backward."""
+    if not accepts(**arguments):
+        return False
+    needs_grad = torch.is_grad_enabled() and any(isinstance(v, Tensor) and v.requires_grad for v in arguments.values())
+    return arguments.get("activation", "swish") == "swish" or not needs_grad
+
+
+PREDICATES = {"momoe": accepts_16bit, "rms_norm_gated": accepts_gated}
 
 
 def _define_moe_ops(popcorn: Any) -> None:
