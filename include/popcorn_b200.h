@@ -278,6 +278,25 @@ int b200_layer_norm(const void* x, const void* weight, const void* bias, void* y
                     int dtype, double eps, void* stream);
 
 /*
+ * Backward of b200_l2_norm: grad_x = g s - x s^3 <g, x> per row, s = 1/sqrt(sum x^2 + eps), in fp32 with one
+ * rounding.  What autograd derives from the reference x * rsqrt(x.pow(2).sum(-1, keepdim=True) + eps),
+ * src/popcorn/kernels/l2_norm.py:14.
+ */
+int b200_l2_norm_backward(const void* grad_y, const void* x, void* grad_x, int64_t rows, int64_t cols,
+                          int64_t ldg, int64_t ldx, int64_t lddx, int dtype, double eps, void* stream);
+
+/*
+ * Backward of b200_layer_norm: grad_x = rstd (gw - mean(gw) - xhat mean(gw xhat)) with gw = g w, grad_weight =
+ * sum over rows of g xhat, grad_bias (may be NULL) = sum over rows of g.  What autograd derives from
+ * F.layer_norm, src/popcorn/kernels/layer_norm.py:20.  scratch: b200_layer_norm_backward_scratch_bytes(rows, cols)
+ * bytes of device memory, 16-byte aligned, written by the call.
+ */
+int b200_layer_norm_backward_scratch_bytes(int64_t rows, int64_t cols, size_t* bytes);
+int b200_layer_norm_backward(const void* grad_y, const void* x, const void* weight, void* grad_x, void* grad_weight,
+                             void* grad_bias, int64_t rows, int64_t cols, int64_t ldg, int64_t ldx, int64_t lddx,
+                             int dtype, double eps, void* scratch, size_t scratch_bytes, void* stream);
+
+/*
  * Backward of b200_swiglu: grad_a = round_T(round_T(g*b) * dsilu(a)), grad_b = round_T(g * round_T(silu(a))),
  * dsilu(a) = s * (1 + a * (1 - s)), s = sigmoid(a), in fp32.
  *

@@ -103,6 +103,37 @@ class _RmsNormGatedSwish(torch.autograd.Function):
         return grad_x, grad_g, grad_w, grad_b, None
 
 
+class _L2Norm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: Tensor, eps: float) -> Tensor:
+        ctx.save_for_backward(x)
+        ctx.eps = eps
+        with torch.no_grad():
+            return ops.l2_norm(x, eps)
+
+    @staticmethod
+    def backward(ctx, grad_y: Tensor):
+        (x,) = ctx.saved_tensors
+        with torch.no_grad():
+            return ops.l2_norm_backward(grad_y.contiguous(), x, ctx.eps), None
+
+
+class _LayerNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: Tensor, weight: Tensor, bias: Tensor | None, eps: float) -> Tensor:
+        ctx.save_for_backward(x, weight)
+        ctx.with_bias, ctx.eps = bias is not None, eps
+        with torch.no_grad():
+            return ops.layer_norm(x, weight, bias, eps)
+
+    @staticmethod
+    def backward(ctx, grad_y: Tensor):
+        x, weight = ctx.saved_tensors
+        with torch.no_grad():
+            grad_x, grad_w, grad_b = ops.layer_norm_backward(grad_y.contiguous(), x, weight, ctx.with_bias, ctx.eps)
+        return grad_x, grad_w, grad_b, None
+
+
 class _Llama4Rope(torch.autograd.Function):
     """Multiplication by unit complex numbers: the transpose multiplies by their conjugates."""
 
@@ -219,3 +250,13 @@ def rms_norm_gated(x: Tensor, g: Tensor, weight: Tensor, bias: Tensor | None = N
     if activation != "swish":
         return ops.rms_norm_gated(x, g, weight, bias, activation, eps)
     return _RmsNormGatedSwish.apply(x, g, weight, bias, eps)
+
+
+def l2_norm(x: Tensor, eps: float = 1e-6) -> Tensor:
+    """L2 normalization with a gradient for x."""
+    return _L2Norm.apply(x, eps)
+
+
+def layer_norm(x: Tensor, weight: Tensor, bias: Tensor | None = None, eps: float = 1e-6) -> Tensor:
+    """Layer normalization with gradients for x, weight and bias."""
+    return _LayerNorm.apply(x, weight, bias, eps)

@@ -459,6 +459,42 @@ def layer_norm(x: Tensor, weight: Tensor, bias: Tensor | None = None, eps: float
     return y
 
 
+def l2_norm_backward(grad_y: Tensor, x: Tensor, eps: float = 1e-6) -> Tensor:
+    """grad_x of l2_norm(x, eps) (what autograd derives from l2_norm.py:14)."""
+    device = _require_cuda(grad_y, x)
+    code = _dtype_code(x, "l2_norm_backward")
+    if grad_y.shape != x.shape or grad_y.dtype != x.dtype:
+        raise ValueError("l2_norm_backward: grad_y must match x")
+    width = x.shape[-1]
+    g2, ldg = _rows(grad_y)
+    x2, ldx = _rows(x)
+    grad_x = torch.empty(x.shape, dtype=x.dtype, device=device)
+    with torch.cuda.device(device):
+        _lib.call("b200_l2_norm_backward", _ptr(g2), _ptr(x2), _ptr(grad_x), x2.shape[0], width, ldg, ldx, max(width, 1), code, float(eps), _stream(device))
+    return grad_x
+
+
+def layer_norm_backward(grad_y: Tensor, x: Tensor, weight: Tensor, with_bias: bool = False, eps: float = 1e-6) -> tuple[Tensor, Tensor, Tensor | None]:
+    """(grad_x, grad_weight, grad_bias or None) of layer_norm(x, weight, bias, eps)."""
+    device = _require_cuda(grad_y, x, weight)
+    code = _dtype_code(x, "layer_norm_backward")
+    width = x.shape[-1]
+    if grad_y.shape != x.shape or weight.shape != (width,) or not (grad_y.dtype == weight.dtype == x.dtype):
+        raise ValueError("layer_norm_backward: grad_y must match x, and weight must be [hidden] of the same dtype")
+    g2, ldg = _rows(grad_y)
+    x2, ldx = _rows(x)
+    grad_x = torch.empty(x.shape, dtype=x.dtype, device=device)
+    grad_w = torch.empty(width, dtype=x.dtype, device=device)
+    grad_b = torch.empty(width, dtype=x.dtype, device=device) if with_bias else None
+    need = ctypes.c_size_t(0)
+    with torch.cuda.device(device):
+        _lib.call("b200_layer_norm_backward_scratch_bytes", x2.shape[0], width, ctypes.byref(need))
+        scratch = torch.empty(max(need.value, 16), dtype=torch.uint8, device=device)
+        _lib.call("b200_layer_norm_backward", _ptr(g2), _ptr(x2), _ptr(weight.contiguous()), _ptr(grad_x), _ptr(grad_w), _ptr(grad_b),
+                  x2.shape[0], width, ldg, ldx, max(width, 1), code, float(eps), _ptr(scratch), ctypes.c_size_t(scratch.numel()), _stream(device))
+    return grad_x, grad_w, grad_b
+
+
 def swiglu_backward(grad_out: Tensor, a: Tensor, b: Tensor) -> tuple[Tensor, Tensor]:
     """Gradients of swiglu(a, b) with respect to a and b (what autograd derives from swiglu.py:18)."""
     return _gate_backward("b200_swiglu_backward", grad_out, a, b)

@@ -45,7 +45,13 @@ REFERENCE_HASHES = {
     "moe_permute": "2d4425c300da",
     "moe_unpermute": "96a7326d99b2",
 }
-IMPLEMENTATION_HASH = "e5690e260cc5"
+IMPLEMENTATION_HASH = "e5690e260cc5"  # a bare source gated by plugin.accepts
+# ops registered with their own predicate hash differently
+IMPLEMENTATION_HASHES = {"rms_norm_gated": "1d8544b584b6"}
+
+
+def implementation_hash(op: str) -> str:
+    return IMPLEMENTATION_HASHES.get(op, IMPLEMENTATION_HASH)
 
 
 def make_config(dims: dict[str, int], batch: list[int], dtype: str, args: dict[str, Any], present: list[str]) -> dict[str, Any]:
@@ -88,7 +94,7 @@ def make_row(
         "schema": SCHEMA, "op": op, "impl": BACKEND, "case": case_label(config), "case_id": config_id(config), "config": config,
         "device": device, "torch": torch_version, "backend_version": None,  # undeclared backend: no version gate
         "ts": timestamp or datetime.datetime.now(datetime.timezone.utc).isoformat(timespec="seconds"),
-        "ref_hash": REFERENCE_HASHES.get(op), "impl_hash": IMPLEMENTATION_HASH,
+        "ref_hash": REFERENCE_HASHES.get(op), "impl_hash": implementation_hash(op),
         "status": status, "reason": reason, "grad": False,
         "fwd": {name: {"err": g["err"], "budget": g["budget"], "scale": g["scale"]} for name, g in gauges.items()},
         "bwd": {}, "bench": bench, "benchmarked": True, "bench_error": "", "reps": reps,

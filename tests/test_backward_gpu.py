@@ -16,6 +16,8 @@ from popcorn_b200 import autograd as diff, kernels, workloads
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 FLOOR = {torch.float32: 2e-5, torch.float16: 1e-3, torch.bfloat16: 2e-2}
+NORM_BWD_SHAPES = [(5, 64, torch.float32), (33, 256, torch.bfloat16), (64, 1024, torch.bfloat16), (40, 4096, torch.bfloat16), (300, 8192, torch.bfloat16),
+                   (7, 16384, torch.bfloat16), (9, 100, torch.float32), (6, 33, torch.bfloat16), (3, 40000, torch.float32), (130, 2048, torch.float16), (600, 512, torch.float32)]
 
 
 def randn(seed, *shape, dtype=torch.float32, scale=1.0):
@@ -180,6 +182,36 @@ def test_rms_norm_gated_swish_backward(rows, cols, dtype, with_bias):
         diff.rms_norm_gated(leaves[0], leaves[1], leaves[2], None, "sigmoid", 1e-5)
 
 
+@pytest.mark.parametrize("rows,cols,dtype", NORM_BWD_SHAPES)
+def test_l2_norm_backward(rows, cols, dtype):
+    x = randn(2400 + cols, rows, cols, dtype=dtype)
+    g = randn(2401 + cols, rows, cols, dtype=dtype)
+    dev = x.to(DEV).requires_grad_(True)
+    (mine,) = torch.autograd.grad(diff.l2_norm(dev, 1e-6), dev, g.to(DEV))
+    fn = lambda x_: oracle.l2_norm(x_, 1e-6)  # noqa: E731
+    (native,) = oracle_grads(fn, (x,), g)
+    (truth,) = oracle_grads(fn, (x,), g, wide=True)
+    grade(mine, native, truth, dtype, f"l2_norm grad_x {rows}x{cols}")
+
+
+@pytest.mark.parametrize("rows,cols,dtype", NORM_BWD_SHAPES)
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_layer_norm_backward(rows, cols, dtype, with_bias):
+    x = (randn(2500 + cols, rows, cols) + 0.3).to(dtype)
+    w = (1 + 0.1 * randn(2501, cols)).to(dtype)
+    b = randn(2502, cols, dtype=dtype) if with_bias else None
+    g = randn(2503 + cols, rows, cols, dtype=dtype)
+    tensors = (x, w, b) if with_bias else (x, w)
+    leaves = [t.to(DEV).requires_grad_(True) for t in tensors]
+    y = diff.layer_norm(leaves[0], leaves[1], leaves[2] if with_bias else None, 1e-5)
+    grads = torch.autograd.grad(y, leaves, g.to(DEV))
+    fn = (lambda x_, w_, b_: oracle.layer_norm(x_, w_, b_, 1e-5)) if with_bias else (lambda x_, w_: oracle.layer_norm(x_, w_, None, 1e-5))
+    native = oracle_grads(fn, tensors, g)
+    truth = oracle_grads(fn, tensors, g, wide=True)
+    for name, mine, nat, tru in zip(("grad_x", "grad_weight", "grad_bias"), grads, native, truth):
+        grade(mine, nat, tru, dtype, f"layer_norm {name} {rows}x{cols}")
+
+
 def test_registry_serves_training_calls():
     x = randn(1300, 8, 256, dtype=torch.bfloat16).to(DEV).requires_grad_(True)
     out = kernels.swiglu(x, x, backend="b200")
@@ -187,8 +219,6 @@ def test_registry_serves_training_calls():
     assert x.grad is not None and torch.isfinite(x.grad.float()).all()
 
 
-NORM_BWD_SHAPES = [(5, 64, torch.float32), (33, 256, torch.bfloat16), (64, 1024, torch.bfloat16), (40, 4096, torch.bfloat16), (300, 8192, torch.bfloat16),
-                   (7, 16384, torch.bfloat16), (9, 100, torch.float32), (6, 33, torch.bfloat16), (3, 40000, torch.float32), (130, 2048, torch.float16), (600, 512, torch.float32)]
 
 
 @pytest.mark.parametrize("rows,cols,dtype", NORM_BWD_SHAPES)
