@@ -483,6 +483,17 @@ int b200_moe_permute_multi(const void* x, const int32_t* dst_buf, const int32_t*
                            int64_t ldx, int64_t ldrows, int dtype, void* stream);
 
 /*
+ * Backward of b200_moe_unpermute: grad_rows[pos[t,k]] = round_T(weights[t,k] * grad_y[t]) and
+ * grad_weights[t,k] = <grad_y[t], rows[pos[t,k]]> (fp32).  What autograd derives from the reference's combine
+ * einsum, src/popcorn/kernels/momoe.py:52-53.  Rows no (token, slot) points to are left untouched; negative
+ * positions get a zero weight gradient.  The backward of b200_moe_permute is b200_moe_unpermute itself with unit
+ * weights (every token row collects the gradients of its top_k copies).
+ */
+int b200_moe_unpermute_backward(const void* grad_y, const void* rows, const float* weights, const int32_t* pos,
+                                void* grad_rows, float* grad_weights, int64_t tokens, int64_t top_k, int64_t hidden,
+                                int64_t ld_grad_y, int64_t ldrows, int64_t ld_grad_rows, int dtype, void* stream);
+
+/*
  * y[t, :] = round_T( sum_k weights[t, k] * fp32(bufs[src_buf[t, k]][src_row[t, k], :]) ), accumulated in
  * ascending (buffer, row) order, which is ascending expert index when buffers hold contiguous expert
  * blocks in rank order.  Same arithmetic as b200_moe_unpermute.

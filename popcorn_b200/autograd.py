@@ -134,6 +134,64 @@ class _LayerNorm(torch.autograd.Function):
         return grad_x, grad_w, grad_b, None
 
 
+class _MoeRoute(torch.autograd.Function):
+    """weights = softmax over the picked logits, so d logits[e_k] = w_k (d w_k - sum_j w_j d w_j) on the picked
+    experts and zero elsewhere (the selection itself carries no gradient, as in the reference, momoe.py:47-49)."""
+
+    @staticmethod
+    def forward(ctx, router_logits: Tensor, top_k: int):
+        with torch.no_grad():
+            indices, weights = ops.moe_route(router_logits, top_k)
+        ctx.save_for_backward(indices, weights)
+        ctx.shape, ctx.dtype = router_logits.shape, router_logits.dtype
+        ctx.mark_non_differentiable(indices)
+        return indices, weights
+
+    @staticmethod
+    def backward(ctx, _grad_indices, grad_weights: Tensor):
+        indices, weights = ctx.saved_tensors
+        inner = (weights * grad_weights).sum(-1, keepdim=True)
+        picked = weights * (grad_weights - inner)
+        grad_logits = torch.zeros(ctx.shape, dtype=torch.float32, device=weights.device)
+        grad_logits.scatter_(-1, indices.long(), picked)
+        return grad_logits.to(ctx.dtype), None
+
+
+class _MoePermute(torch.autograd.Function):
+    """rows[pos[t, k]] = x[t]: every token row collects the gradients of its top_k copies, which is the combine
+    kernel with unit weights."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, indices: Tensor, experts: int):
+        with torch.no_grad():
+            rows, counts, offsets, perm, pos = ops.moe_permute(x, indices, experts)
+        ctx.save_for_backward(pos)
+        ctx.mark_non_differentiable(counts, offsets, perm, pos)
+        return rows, counts, offsets, perm, pos
+
+    @staticmethod
+    def backward(ctx, grad_rows: Tensor, *_unused):
+        (pos,) = ctx.saved_tensors
+        with torch.no_grad():
+            grad_x = ops.moe_unpermute(grad_rows.contiguous(), torch.ones(pos.shape, dtype=torch.float32, device=pos.device), pos)
+        return grad_x, None, None
+
+
+class _MoeUnpermute(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, rows: Tensor, weights: Tensor, pos: Tensor) -> Tensor:
+        ctx.save_for_backward(rows, weights, pos)
+        with torch.no_grad():
+            return ops.moe_unpermute(rows, weights, pos)
+
+    @staticmethod
+    def backward(ctx, grad_y: Tensor):
+        rows, weights, pos = ctx.saved_tensors
+        with torch.no_grad():
+            grad_rows, grad_weights = ops.moe_unpermute_backward(grad_y.contiguous(), rows, weights, pos)
+        return grad_rows, grad_weights, None
+
+
 class _Llama4Rope(torch.autograd.Function):
     """Multiplication by unit complex numbers: the transpose multiplies by their conjugates."""
 
@@ -260,3 +318,18 @@ def l2_norm(x: Tensor, eps: float = 1e-6) -> Tensor:
 def layer_norm(x: Tensor, weight: Tensor, bias: Tensor | None = None, eps: float = 1e-6) -> Tensor:
     """Layer normalization with gradients for x, weight and bias."""
     return _LayerNorm.apply(x, weight, bias, eps)
+
+
+def moe_route(router_logits: Tensor, top_k: int = 2) -> tuple[Tensor, Tensor]:
+    """Routing with a gradient from the gate weights back to the logits of the picked experts."""
+    return _MoeRoute.apply(router_logits, top_k)
+
+
+def moe_permute(x: Tensor, indices: Tensor, experts: int) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
+    """Permutation into expert-major rows with a gradient for x."""
+    return _MoePermute.apply(x, indices, experts)
+
+
+def moe_unpermute(rows: Tensor, weights: Tensor, pos: Tensor) -> Tensor:
+    """Weighted combine with gradients for the expert rows and the gate weights."""
+    return _MoeUnpermute.apply(rows, weights, pos)

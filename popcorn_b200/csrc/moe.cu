@@ -845,6 +845,118 @@ extern "C" int b200_moe_unpermute_multi(void* const* bufs, int64_t n_bufs, const
   return unpermute_impl(__func__, bufs, n_bufs, src_buf, src_row, weights, y, tokens, top_k, hidden, ldrows, ldy, dtype, stream);
 }
 
+// ------------------------------------------------------ unpermute backward --
+
+namespace b200 {
+namespace {
+// y[t] = round_T(sum_k w[t,k] rows[pos[t,k]]) (fp32 inside), so
+//   d_rows[pos[t,k]] = round_T(w[t,k] * dy[t]),   d_w[t,k] = <dy[t], rows[pos[t,k]]>   (fp32).
+// One warp per token; for every slot the token's gradient row is re-read (it stays in L1), the expert row is
+// streamed once for the dot product and the scaled gradient row is streamed out.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256)
+unpermute_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ rows, const float* __restrict__ weights,
+                     const int32_t* __restrict__ pos, T* __restrict__ d_rows, float* __restrict__ d_weights,
+                     int64_t tokens, int top_k, int hidden, int64_t lddy, int64_t ldrows, int64_t lddrows) {
+  pdl_prologue();
+  constexpr int V = VEC ? Num<T>::kVec : 1;
+  constexpr int UNROLL = 4;
+  const int lane = threadIdx.x & 31;
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (t >= tokens) return;  // whole warps leave together
+  const int words = hidden / V;
+  const T* g = dy + t * lddy;
+  for (int k = 0; k < top_k; ++k) {
+    const int p = pos[t * top_k + k];  // the same for all lanes
+    if (p < 0) {
+      if (lane == 0) d_weights[t * top_k + k] = 0.f;
+      continue;
+    }
+    const float w = weights[t * top_k + k];
+    const T* src = rows + static_cast<int64_t>(p) * ldrows;
+    T* dst = d_rows + static_cast<int64_t>(p) * lddrows;
+    float dot = 0.f;
+    for (int w0 = lane; w0 < words; w0 += 32 * UNROLL) {
+      if constexpr (VEC) {
+        uint4 vg[UNROLL], vr[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          if (w0 + 32 * u < words) {
+            vg[u] = ld_reuse(g + static_cast<int64_t>(w0 + 32 * u) * V);
+            vr[u] = ld_stream(src + static_cast<int64_t>(w0 + 32 * u) * V);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          if (w0 + 32 * u < words) {
+            float fg[Num<T>::kVec], fr[Num<T>::kVec];
+            Num<T>::unpack(vg[u], fg);
+            Num<T>::unpack(vr[u], fr);
+#pragma unroll
+            for (int j = 0; j < Num<T>::kVec; ++j) {
+              dot = __fmaf_rn(fg[j], fr[j], dot);
+              fg[j] = __fmul_rn(w, fg[j]);
+            }
+            st_stream(dst + static_cast<int64_t>(w0 + 32 * u) * V, Num<T>::pack(fg));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const int i = w0 + 32 * u;
+          if (i < words) {
+            const float fg = Num<T>::up(g[i]);
+            dot = __fmaf_rn(fg, Num<T>::up(src[i]), dot);
+            dst[i] = Num<T>::down(__fmul_rn(w, fg));
+          }
+        }
+      }
+    }
+    dot = warp_sum(dot);
+    if (lane == 0) d_weights[t * top_k + k] = dot;
+  }
+}
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_moe_unpermute_backward(const void* grad_y, const void* rows, const float* weights, const int32_t* pos,
+                                           void* grad_rows, float* grad_weights, int64_t tokens, int64_t top_k, int64_t hidden,
+                                           int64_t ld_grad_y, int64_t ldrows, int64_t ld_grad_rows, int dtype, void* stream) {
+  if (!dtype_ok(dtype)) return fail(B200_ERR_DTYPE, "%s: unsupported dtype %d", __func__, dtype);
+  if (tokens < 0 || top_k < 0 || hidden < 0) return fail(B200_ERR_SHAPE, "%s: negative size", __func__);
+  if (top_k > kMaxTopK) return fail(B200_ERR_SHAPE, "%s: top_k=%lld exceeds %d", __func__, (long long)top_k, kMaxTopK);
+  if (tokens > 0x7fffffffLL * 8 || hidden > 0x7fffffffLL) return fail(B200_ERR_SHAPE, "%s: size out of range", __func__);
+  if (tokens == 0 || top_k == 0) return B200_OK;
+  B200_REQUIRE_PTR(weights);
+  B200_REQUIRE_PTR(pos);
+  B200_REQUIRE_PTR(grad_weights);
+  if (hidden > 0) {
+    B200_REQUIRE_PTR(grad_y);
+    B200_REQUIRE_PTR(rows);
+    B200_REQUIRE_PTR(grad_rows);
+  }
+  if (ld_grad_y < hidden || ldrows < hidden || ld_grad_rows < hidden) return fail(B200_ERR_SHAPE, "%s: leading dimension smaller than hidden", __func__);
+  const size_t es = dtype_size(dtype);
+  if (!aligned(grad_y, es) || !aligned(rows, es) || !aligned(grad_rows, es) || !aligned(weights, 4) || !aligned(pos, 4) || !aligned(grad_weights, 4))
+    return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to the element size", __func__);
+  if (int rc = check_device()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>(ceil_div(tokens, 8));
+  const int K = static_cast<int>(top_k), H = static_cast<int>(hidden);
+  B200_DISPATCH_DTYPE(dtype, T, {
+    constexpr int V = Num<T>::kVec;
+    const bool vec = hidden % V == 0 && ld_grad_y % V == 0 && ldrows % V == 0 && ld_grad_rows % V == 0 && aligned(grad_y, 16) &&
+                     aligned(rows, 16) && aligned(grad_rows, 16);
+    if (vec)
+      launch(unpermute_bwd_kernel<T, true>, grid, 256, 0, st, static_cast<const T*>(grad_y), static_cast<const T*>(rows), weights, pos,
+             static_cast<T*>(grad_rows), grad_weights, tokens, K, H, ld_grad_y, ldrows, ld_grad_rows);
+    else
+      launch(unpermute_bwd_kernel<T, false>, grid, 256, 0, st, static_cast<const T*>(grad_y), static_cast<const T*>(rows), weights, pos,
+             static_cast<T*>(grad_rows), grad_weights, tokens, K, H, ld_grad_y, ldrows, ld_grad_rows);
+  });
+  return after_launch("unpermute_bwd_kernel");
+}
+
 // --------------------------------------------------- expert-parallel plan --
 
 namespace b200 {

@@ -632,6 +632,28 @@ def moe_unpermute(rows: Tensor, weights: Tensor, pos: Tensor) -> Tensor:
     return y
 
 
+def moe_unpermute_backward(grad_y: Tensor, rows: Tensor, weights: Tensor, pos: Tensor) -> tuple[Tensor, Tensor]:
+    """(grad_rows, grad_weights) of moe_unpermute(rows, weights, pos) (what autograd derives from momoe.py:52-53)."""
+    device = _require_cuda(grad_y, rows, weights, pos)
+    code = _dtype_code(rows, "moe_unpermute_backward")
+    if rows.dim() != 2 or weights.shape != pos.shape or pos.dim() != 2 or grad_y.shape != (pos.shape[0], rows.shape[1]):
+        raise ValueError("moe_unpermute_backward: rows [n, hidden], weights / pos [tokens, top_k], grad_y [tokens, hidden]")
+    if weights.dtype != torch.float32 or pos.dtype != torch.int32 or grad_y.dtype != rows.dtype:
+        raise TypeError("moe_unpermute_backward: weights float32, pos int32, grad_y in the dtype of rows")
+    tokens, top_k = pos.shape
+    hidden = rows.shape[1]
+    g2, ldg = _rows(grad_y)
+    r2, ldr = _rows(rows)
+    # every row is written when pos is a permutation of all rows (the normal case); otherwise the rest must read as zero
+    make = torch.empty if pos.numel() == rows.shape[0] else torch.zeros
+    grad_rows = make(rows.shape, dtype=rows.dtype, device=device)
+    grad_weights = torch.empty(pos.shape, dtype=torch.float32, device=device)
+    with torch.cuda.device(device):
+        _lib.call("b200_moe_unpermute_backward", _ptr(g2), _ptr(r2), _ptr(weights.contiguous()), _ptr(pos.contiguous()), _ptr(grad_rows),
+                  _ptr(grad_weights), tokens, top_k, hidden, ldg, ldr, max(hidden, 1), code, _stream(device))
+    return grad_rows, grad_weights
+
+
 def moe_grouped_gemm(rows: Tensor, weight: Tensor, offsets: Tensor, up_weight: Tensor | None = None, out: Tensor | None = None) -> Tensor:
     """Expert MLP projection over the expert-major rows of `moe_permute` (momoe.py:50-52, momoe_tl.py:90-330).
 

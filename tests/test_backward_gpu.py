@@ -212,6 +212,37 @@ def test_layer_norm_backward(rows, cols, dtype, with_bias):
         grade(mine, nat, tru, dtype, f"layer_norm {name} {rows}x{cols}")
 
 
+@pytest.mark.parametrize("tokens,hidden,experts,top_k,dtype", [(64, 256, 8, 2, torch.bfloat16), (37, 72, 4, 3, torch.float16), (50, 33, 8, 4, torch.bfloat16),
+                                                             (16, 64, 2, 1, torch.float32), (300, 4096, 64, 8, torch.bfloat16)])
+def test_moe_steps_backward(tokens, hidden, experts, top_k, dtype):
+    """route -> permute -> (an elementwise stand-in for the expert MLPs) -> unpermute, differentiated end to end."""
+    x = randn(2600 + hidden, tokens, hidden, dtype=dtype)
+    logits = randn(2601 + hidden, tokens, experts)
+    grad = randn(2602 + hidden, tokens, hidden, dtype=dtype)
+    assert oracle.route_is_unambiguous(logits, top_k)
+
+    def chain(route, permute, unpermute, x_, logits_):
+        indices, weights = route(logits_, top_k)
+        rows, _, _, _, pos = permute(x_, indices, experts)
+        return unpermute(rows * 1.5, weights, pos)
+
+    def oracle_chain(x_, logits_):
+        indices, weights = oracle.moe_route(logits_, top_k)
+        rows, _, _, _, pos = oracle.moe_permute(x_, indices, experts)
+        return oracle.moe_unpermute(rows * 1.5, weights, pos)
+
+    leaves = [x.to(DEV).requires_grad_(True), logits.to(DEV).requires_grad_(True)]
+    y = chain(diff.moe_route, diff.moe_permute, diff.moe_unpermute, *leaves)
+    grads = torch.autograd.grad(y, leaves, grad.to(DEV))
+    native = oracle_grads(oracle_chain, (x, logits), grad)
+    truth = oracle_grads(oracle_chain, (x, logits), grad, wide=True)
+    grade(grads[0], native[0], truth[0], dtype, f"grad_x {tokens}x{hidden}")
+    # the logits are fp32 whatever the activations are; their gradient inherits the activations' rounding noise
+    err = float((grads[1].cpu().double() - truth[1]).abs().max())
+    budget = float((native[1].double() - truth[1]).abs().max())
+    assert err <= max(4 * budget, FLOOR[dtype] * max(1.0, float(truth[1].abs().max()))), f"grad_logits: {err:.3e} vs budget {budget:.3e}"
+
+
 def test_registry_serves_training_calls():
     x = randn(1300, 8, 256, dtype=torch.bfloat16).to(DEV).requires_grad_(True)
     out = kernels.swiglu(x, x, backend="b200")

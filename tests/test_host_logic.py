@@ -86,14 +86,15 @@ def test_mirror_dispatch_forced_scoped_and_ordered():
 
 
 def test_forward_only_backend_declines_grad():
-    x = torch.ones(4, 8, requires_grad=True)
-    pos = torch.zeros(4, 1, dtype=torch.int32)
+    x = torch.ones(8, 8, requires_grad=True)
+    offsets = torch.tensor([0, 8], dtype=torch.int32)
     with pytest.raises(registry.DispatchError, match="no backward implementation"):
-        kernels.moe_unpermute(x, torch.ones(4, 1), pos, backend="b200")
+        kernels.moe_grouped_gemm(x, torch.ones(1, 8, 8), offsets, backend="b200")
     with pytest.raises(registry.DispatchError, match="no registered backend"):
-        kernels.moe_unpermute(x, torch.ones(4, 1), pos)
+        kernels.moe_grouped_gemm(x, torch.ones(1, 8, 8), offsets)
     for op in (kernels.rms_norm, kernels.add_rms_norm, kernels.swiglu, kernels.geglu, kernels.rotary_embedding, kernels.rope, kernels.llama4_rope,
-               kernels.qk_norm_rope, kernels.l2_norm, kernels.layer_norm, kernels.rms_norm_gated):
+               kernels.qk_norm_rope, kernels.l2_norm, kernels.layer_norm, kernels.rms_norm_gated,
+               kernels.moe_route, kernels.moe_permute, kernels.moe_unpermute):
         assert not op["b200"].forward_only
 
 
