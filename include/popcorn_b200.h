@@ -465,6 +465,42 @@ int b200_moe_grouped_gemm(const void* rows, const void* weight, const void* weig
                           int dtype, void* stream);
 
 /*
+ * Both projections of the expert MLP's first step without the activation, for training calls that keep the
+ * pre-activations: out[p, 0:n] = rows[p, :] @ gate_weight[e(p)], out[p, n:2n] = rows[p, :] @ up_weight[e(p)].
+ * One pass over rows like the fused form of b200_moe_grouped_gemm; out: [total_rows, 2n] with row stride
+ * ld_out >= 2n.  Everything else as for b200_moe_grouped_gemm.
+ */
+int b200_moe_grouped_gemm_gate_up(const void* rows, const void* gate_weight, const void* up_weight, const int32_t* offsets,
+                                  void* out, int64_t total_rows, int64_t k, int64_t n, int64_t experts, int64_t ld_rows,
+                                  int64_t ld_out, int dtype, void* stream);
+
+/*
+ * Gradient of b200_moe_grouped_gemm with respect to its rows (what autograd derives from the reference's einsums,
+ * src/popcorn/kernels/momoe.py:50-52, restricted to the routed pairs; the incumbent's counterparts are
+ * swiglu_backward_kernel and lin1_backward_kernel, src/popcorn/impls/momoe_tl.py:567-700, 835-950):
+ *   grad_rows[p, :] = grad_out[p, :] @ weight[e(p)]^T  (+ grad_out2[p, :] @ weight2[e(p)]^T)
+ * The weights are read in place along their rows (no transposed copy); the optional second pair sums the gate
+ * and up branches into one result in the same accumulator.  grad_out, grad_out2: [total_rows, n], row stride
+ * ld_grad (both); weight, weight2: [experts, k, n]; grad_rows: [total_rows, k], row stride ld_out.  grad_out2
+ * and weight2 are both NULL or both given.  Limits as for b200_moe_grouped_gemm.
+ */
+int b200_moe_grouped_gemm_dgrad(const void* grad_out, const void* weight, const void* grad_out2, const void* weight2,
+                                const int32_t* offsets, void* grad_rows, int64_t total_rows, int64_t k, int64_t n,
+                                int64_t experts, int64_t ld_grad, int64_t ld_out, int dtype, void* stream);
+
+/*
+ * Gradient with respect to the weights: grad_weight[e] = rows[segment e]^T @ grad_out[segment e] (the incumbent's
+ * weights_update_kernel, src/popcorn/impls/momoe_tl.py:484-550), an [k, n] matrix per expert contracted over the expert's rows (fp32 accumulation, one rounding); experts without
+ * rows get zeros.  rows: [total_rows, k], row stride ld_rows; grad_out: [total_rows, n], row stride ld_grad;
+ * grad_weight: [experts, k, n] contiguous, every element is written.  Both operands are read in place: the
+ * tensor maps address them by (row, line within the K slice), so the last slice of a segment is padded with
+ * zeros instead of the next expert's rows.  experts * k < 2^31.
+ */
+int b200_moe_grouped_gemm_wgrad(const void* rows, const void* grad_out, const int32_t* offsets, void* grad_weight,
+                                int64_t total_rows, int64_t k, int64_t n, int64_t experts, int64_t ld_rows, int64_t ld_grad,
+                                int dtype, void* stream);
+
+/*
  * For each (token, slot) pair: dst_rank = indices / experts_per_rank and
  * dst_row = dst_base[expert] + (pos - local_offsets[expert]), the pair's row in the
  * owning rank's buffer.  dst_base[e] is the row at which this rank's block for

@@ -263,3 +263,39 @@ def moe_grouped_gemm(rows: Tensor, weight: Tensor, offsets: Tensor, up_weight: T
             y = F.silu(y) * (segment @ up_weight[e].float())
         out[lo:hi] = y.to(rows.dtype)
     return out
+
+
+def moe_grouped_gemm_gate_up(rows: Tensor, gate_weight: Tensor, up_weight: Tensor, offsets: Tensor) -> Tensor:
+    """[rows @ gate_weight[e] | rows @ up_weight[e]], each rounded once: the two pre-activations of the expert MLP
+    (the operands of F.silu(...) * ... in src/popcorn/kernels/momoe.py:51)."""
+    return torch.cat((moe_grouped_gemm(rows, gate_weight, offsets), moe_grouped_gemm(rows, up_weight, offsets)), dim=1)
+
+
+def moe_grouped_gemm_dgrad(grad_out: Tensor, weight: Tensor, offsets: Tensor, grad_out2: Tensor | None = None,
+                           weight2: Tensor | None = None) -> Tensor:
+    """What autograd derives for the rows of moe_grouped_gemm: grad_out @ weight[e]^T (+ grad_out2 @ weight2[e]^T),
+    fp32, rounded once (the derivative of the einsums in src/popcorn/kernels/momoe.py:50-52)."""
+    out = torch.zeros(grad_out.shape[0], weight.shape[1], dtype=grad_out.dtype)
+    bounds = offsets.tolist()
+    for e in range(weight.shape[0]):
+        lo, hi = bounds[e], bounds[e + 1]
+        if hi <= lo:
+            continue
+        y = grad_out[lo:hi].float() @ weight[e].float().t()
+        if grad_out2 is not None:
+            y = y + grad_out2[lo:hi].float() @ weight2[e].float().t()
+        out[lo:hi] = y.to(grad_out.dtype)
+    return out
+
+
+def moe_grouped_gemm_wgrad(rows: Tensor, grad_out: Tensor, offsets: Tensor) -> Tensor:
+    """What autograd derives for the weight of moe_grouped_gemm: per expert rows[segment]^T @ grad_out[segment] in
+    fp32, rounded once; zeros for an expert without rows."""
+    experts = offsets.numel() - 1
+    out = torch.zeros(experts, rows.shape[1], grad_out.shape[1], dtype=rows.dtype)
+    bounds = offsets.tolist()
+    for e in range(experts):
+        lo, hi = bounds[e], bounds[e + 1]
+        if hi > lo:
+            out[e] = (rows[lo:hi].float().t() @ grad_out[lo:hi].float()).to(rows.dtype)
+    return out

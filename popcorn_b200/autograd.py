@@ -192,6 +192,52 @@ class _MoeUnpermute(torch.autograd.Function):
         return grad_rows, grad_weights, None
 
 
+class _GroupedGemm(torch.autograd.Function):
+    """out = rows @ weight[e]: the gradients are two more grouped GEMMs on the same tensor-core kernel, one that reads
+    the weights along their rows and one that contracts over each expert's rows."""
+
+    @staticmethod
+    def forward(ctx, rows: Tensor, weight: Tensor, offsets: Tensor) -> Tensor:
+        ctx.save_for_backward(rows, weight, offsets)
+        with torch.no_grad():
+            return ops.moe_grouped_gemm(rows, weight, offsets)
+
+    @staticmethod
+    def backward(ctx, grad_out: Tensor):
+        rows, weight, offsets = ctx.saved_tensors
+        grad_out = grad_out.contiguous()
+        with torch.no_grad():
+            grad_rows = ops.moe_grouped_gemm_dgrad(grad_out, weight, offsets) if ctx.needs_input_grad[0] else None
+            grad_weight = ops.moe_grouped_gemm_wgrad(rows, grad_out, offsets) if ctx.needs_input_grad[1] else None
+        return grad_rows, grad_weight, None
+
+
+class _GroupedGateUp(torch.autograd.Function):
+    """silu(rows @ gate[e]) * (rows @ up[e]) for training: one pass computes both projections and keeps them (16-bit,
+    like the incumbent's saved activations, src/popcorn/impls/momoe_tl.py:180-190), the SwiGLU kernel forms the
+    product; backward = SwiGLU backward, one GEMM summing both branches into grad_rows, two weight gradients."""
+
+    @staticmethod
+    def forward(ctx, rows: Tensor, gate_weight: Tensor, up_weight: Tensor, offsets: Tensor) -> Tensor:
+        width = gate_weight.shape[2]
+        with torch.no_grad():
+            both = ops.moe_grouped_gemm_gate_up(rows, gate_weight, up_weight, offsets)
+            out = ops.swiglu(both[:, :width], both[:, width:])
+        ctx.save_for_backward(rows, gate_weight, up_weight, offsets, both)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out: Tensor):
+        rows, gate_weight, up_weight, offsets, both = ctx.saved_tensors
+        width = gate_weight.shape[2]
+        with torch.no_grad():
+            grad_gate, grad_up = ops.swiglu_backward(grad_out.contiguous(), both[:, :width], both[:, width:])
+            grad_rows = ops.moe_grouped_gemm_dgrad(grad_gate, gate_weight, offsets, grad_up, up_weight) if ctx.needs_input_grad[0] else None
+            grad_gate_weight = ops.moe_grouped_gemm_wgrad(rows, grad_gate, offsets) if ctx.needs_input_grad[1] else None
+            grad_up_weight = ops.moe_grouped_gemm_wgrad(rows, grad_up, offsets) if ctx.needs_input_grad[2] else None
+        return grad_rows, grad_gate_weight, grad_up_weight, None
+
+
 class _Llama4Rope(torch.autograd.Function):
     """Multiplication by unit complex numbers: the transpose multiplies by their conjugates."""
 
@@ -333,3 +379,32 @@ def moe_permute(x: Tensor, indices: Tensor, experts: int) -> tuple[Tensor, Tenso
 def moe_unpermute(rows: Tensor, weights: Tensor, pos: Tensor) -> Tensor:
     """Weighted combine with gradients for the expert rows and the gate weights."""
     return _MoeUnpermute.apply(rows, weights, pos)
+
+
+def _needs_grad(*tensors: Tensor | None) -> bool:
+    return torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)
+
+
+def moe_grouped_gemm(rows: Tensor, weight: Tensor, offsets: Tensor, up_weight: Tensor | None = None) -> Tensor:
+    """Per-expert projection with gradients for rows and weights.  Inference calls take the fused kernel; a training call
+    with `up_weight` keeps the two 16-bit pre-activations, so its SwiGLU input is rounded once more than the fused form's."""
+    if not _needs_grad(rows, weight, up_weight):
+        return ops.moe_grouped_gemm(rows, weight, offsets, up_weight)
+    if up_weight is None:
+        return _GroupedGemm.apply(rows, weight, offsets)
+    return _GroupedGateUp.apply(rows, weight, up_weight, offsets)
+
+
+def momoe(x: Tensor, gate_weight: Tensor, up_weight: Tensor, down_weight: Tensor, router_logits: Tensor, top_k: int = 2) -> Tensor:
+    """Mixture of SwiGLU expert MLPs with gradients for x, the three weights and the router logits: the chain of
+    `ops.momoe` built from the differentiable steps (the routed experts only; gradients of unrouted pairs are zero in
+    the reference too, where their gate weight is exactly zero, src/popcorn/kernels/momoe.py:47-53)."""
+    if not _needs_grad(x, gate_weight, up_weight, down_weight, router_logits):
+        return ops.momoe(x, gate_weight, up_weight, down_weight, router_logits, top_k)
+    ops.check_momoe(x, gate_weight, up_weight, down_weight, router_logits)
+    experts, hidden, _ = gate_weight.shape
+    indices, weights = moe_route(router_logits.reshape(-1, experts).float(), int(top_k))
+    rows, _, offsets, _, pos = moe_permute(x.reshape(-1, hidden), indices, experts)
+    hidden_act = moe_grouped_gemm(rows, gate_weight, offsets, up_weight)
+    out_rows = moe_grouped_gemm(hidden_act, down_weight, offsets)
+    return moe_unpermute(out_rows, weights, pos).reshape(x.shape)

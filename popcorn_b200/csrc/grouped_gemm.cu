@@ -198,34 +198,48 @@ __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::l
 
 // Shared-memory matrix descriptors (sm_100 format: start >> 4 in bits 0-13, leading byte offset >> 4
 // in 16-29, stride byte offset >> 4 in 32-45, version 1 in 46-47, swizzle mode in 61-63; 2 = 128 bytes).
-//  A, K-major, rows of 128 bytes (64 K values): 8-row groups 1024 bytes apart (stride offset); the
-//     leading offset is not used by swizzled K-major layouts and is set to its canonical 1.
-//  B, N-major, rows of 128 bytes (64 N values) per K index: 8-row K groups 1024 bytes apart (stride
-//     offset), 64-column chunks one whole [64 x 128 B] block apart (leading offset).
+//  K-major operand (the contraction index is contiguous in memory): rows of 128 bytes (64 K values), 8-row
+//     groups 1024 bytes apart (stride offset); the leading offset is not used by swizzled K-major layouts and
+//     is set to its canonical 1.
+//  MN-major operand (the M or N index is contiguous): per K index a 128-byte line of 64 M/N values, 8-line K
+//     groups 1024 bytes apart (stride offset), 64-value chunks one whole [slot K x 128 B] block apart (leading
+//     offset).
 constexpr uint64_t kDescFixed = (uint64_t(1) << 46) | (uint64_t(2) << 61);
-constexpr uint64_t kDescA = kDescFixed | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32);
+constexpr uint64_t kDescKMajor = kDescFixed | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32);
 template <int CTAS>
-constexpr uint64_t kDescB = kDescFixed | (uint64_t(Ring<CTAS>::kBChunkBytes >> 4) << 16) | (uint64_t(1024 >> 4) << 32);
+constexpr uint64_t kDescMnMajor = kDescFixed | (uint64_t(Ring<CTAS>::kBChunkBytes >> 4) << 16) | (uint64_t(1024 >> 4) << 32);
 
 // Instruction descriptor of kind::f16: fp32 accumulate (bit 4), A/B format (0 fp16, 1 bf16) at bits 7
-// and 10, A K-major (bit 15 = 0), B N-major (bit 16 = 1), N >> 3 at bit 17, M >> 4 at bit 24 (M = 256 for a pair).
-__host__ __device__ constexpr uint32_t instr_desc(uint32_t format, int ctas) {
-  return (1u << 4) | (format << 7) | (format << 10) | (1u << 16) | (uint32_t(kBN >> 3) << 17) | (uint32_t((kBM * ctas) >> 4) << 24);
+// and 10, A / B MN-major at bits 15 / 16, N >> 3 at bit 17, M >> 4 at bit 24 (M = 256 for a pair).
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t format, int ctas, bool a_mn_major, bool b_mn_major) {
+  return (1u << 4) | (format << 7) | (format << 10) | (uint32_t(a_mn_major) << 15) | (uint32_t(b_mn_major) << 16) |
+         (uint32_t(kBN >> 3) << 17) | (uint32_t((kBM * ctas) >> 4) << 24);
 }
+
+// What one launch computes.  Operand layouts as staged in shared memory:
+//   kPlain   out = rows @ w                              A K-major,  B N-major
+//   kSwiglu  out = silu(rows @ w) * (rows @ w2)          same; the two projections share one accumulator
+//   kGateUp  out = [rows @ w | rows @ w2]                same; both halves stored, no activation
+//   kDgrad   out = g @ w^T (+ g2 @ w2^T)                 A K-major,  B K-major (the weight read along its rows)
+//   kWgrad   out[e] = rows[segment e]^T @ g[segment e]   A MN-major, B N-major; the contraction runs over the segment
+enum Mode : int { kPlain = 0, kSwiglu = 1, kGateUp = 2, kDgrad = 3, kWgrad = 4 };
 
 struct GemmArgs {
   const int32_t* offsets;  // [experts + 1], device
   void* out;
   int64_t ld_out;
   int experts;
-  int n;        // output columns (per projection)
-  int k;
-  int total_rows;  // rows of `rows` and `out`: nothing is stored past them, whatever `offsets` says
+  int n;           // output columns (per projection)
+  int k;           // contraction length (kWgrad: unused, the segment length)
+  int m;           // kWgrad: output rows per expert (the features of `rows`)
+  int sources;     // kDgrad: 1 or 2 (A, B) operand pairs summed into one result
+  int total_rows;  // rows of the token-major operands: nothing is read or stored past them, whatever `offsets` says
   uint32_t idesc;
 };
 
 struct Tile {
-  int expert, row0, row_end, n0;
+  int expert, row0, row_end, n0;  // output rows [row0, row_end) x columns from n0
+  int k_lo, k_hi;                 // kWgrad: the segment's rows
 };
 
 // tile -> (expert, m tile, n tile): tiles of one expert are consecutive, n fastest, so that the CTAs running
@@ -247,18 +261,41 @@ __device__ __forceinline__ Tile decode_tile(int tile, const int* tile_start, con
   t.row0 = first + (local / tiles_n) * tile_rows;
   t.row_end = end;
   t.n0 = (local % tiles_n) * out_tile_n;
+  t.k_lo = t.k_hi = 0;
   return t;
 }
 
-template <typename T, bool DUAL, int CTAS>
+// kWgrad: every expert owns tiles_m x tiles_n tiles of its [m, n] gradient, n fastest; an expert without rows
+// still gets its tiles (they are written as zeros).  The CTAs running together then stream the SAME rows of the
+// segment (all feature and gradient columns of a few hundred rows), so the operands come from DRAM once.
+__device__ __forceinline__ Tile decode_wgrad_tile(int tile, const int* offsets, int tiles_per_expert, int tiles_n, int tile_rows, int m) {
+  Tile t;
+  t.expert = tile / tiles_per_expert;
+  const int local = tile - t.expert * tiles_per_expert;
+  const int mt = local / tiles_n;
+  t.n0 = (local - mt * tiles_n) * kBN;
+  t.row0 = t.expert * m + mt * tile_rows;
+  t.row_end = (t.expert + 1) * m;
+  t.k_lo = offsets[t.expert];
+  t.k_hi = offsets[t.expert + 1];
+  return t;
+}
+
+template <typename T, int MODE, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
-grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_w,
-                    const __grid_constant__ CUtensorMap map_w2, const GemmArgs p) {
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2, const GemmArgs p) {
   using R = Ring<CTAS>;
   constexpr bool PAIR = CTAS == 2;
-  constexpr int OUT_N = DUAL ? kBN / 2 : kBN;  // output columns per tile
+  constexpr bool DUAL = MODE == kSwiglu || MODE == kGateUp;  // two weight tensors, 128 columns of each per tile
+  constexpr bool WGRAD = MODE == kWgrad;
+  constexpr bool B_K_MAJOR = MODE == kDgrad;
+  constexpr int OUT_N = DUAL ? kBN / 2 : kBN;  // output columns per tile (and per projection)
+  constexpr int ACC_COLS = MODE == kSwiglu ? kBN / 2 : kBN;  // accumulator columns the epilogue walks
   constexpr int STAGES = R::kStages;
   constexpr int TILE_ROWS = kBM * CTAS;
+  constexpr int B_ROWS = kBN / CTAS;                 // kDgrad: weight rows (= accumulator columns) this CTA stages
+  constexpr int kBSpanBytes = B_ROWS * 128;          // kDgrad: one 64-wide K span of them
   pdl_prologue();
   extern __shared__ unsigned char smem_raw[];
   __shared__ uint64_t full[kMaxStages], empty[kMaxStages], acc_full[2], acc_empty[2];
@@ -273,6 +310,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
   const int tile_step = PAIR ? gridDim.x / 2 : gridDim.x;
   unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tiles_n = (p.n + OUT_N - 1) / OUT_N;
+  const int tiles_per_expert = WGRAD ? ((p.m + TILE_ROWS - 1) / TILE_ROWS) * tiles_n : 0;
+  const int fixed_slots = p.sources * ((p.k + R::kSlotK - 1) / R::kSlotK);  // ring slots per tile unless kWgrad
 
   if (threadIdx.x == 0) {
     aborted = 0;
@@ -282,7 +321,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
       tile_start[e] = total;
       const int hi = min(p.offsets[e + 1], p.total_rows);
       seg[e + 1] = hi;
-      total += (hi > lo ? (hi - lo + TILE_ROWS - 1) / TILE_ROWS : 0) * tiles_n;
+      if constexpr (WGRAD) total += tiles_per_expert;
+      else total += (hi > lo ? (hi - lo + TILE_ROWS - 1) / TILE_ROWS : 0) * tiles_n;
       lo = hi;
     }
     tile_start[p.experts] = total;
@@ -305,6 +345,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
   const int total_tiles = tile_start[p.experts];
   volatile int* abort_flag = &aborted;
   const uint32_t ring_addr = smem_addr(ring), full_addr = smem_addr(&full[0]), empty_addr = smem_addr(&empty[0]);
+  auto tile_at = [&](int tile) {
+    if constexpr (WGRAD) return decode_wgrad_tile(tile, seg, tiles_per_expert, tiles_n, TILE_ROWS, p.m);
+    else return decode_tile(tile, tile_start, seg, p.experts, OUT_N, TILE_ROWS, tiles_n);
+  };
+  // ring slots of the tile's main loop; a kWgrad tile of an expert without rows has none and never touches an accumulator
+  auto slots_of = [&](const Tile& t) {
+    if constexpr (WGRAD) return t.k_hi > t.k_lo ? (t.k_hi - t.k_lo + R::kSlotK - 1) / R::kSlotK : 0;
+    else return fixed_slots;
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------- producer --
@@ -312,32 +361,72 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
       uint32_t stage = 0, phase = 0, issued = 0;
       // the barrier the copies complete on: this CTA's own, or in a pair the leader's
       const uint32_t signal_addr = PAIR ? map_to_rank(full_addr, 0) : full_addr;
-      const uint64_t rows_map = reinterpret_cast<uint64_t>(&map_rows), w2_map = reinterpret_cast<uint64_t>(&map_w2);
-      // this CTA's share of the 256 accumulator columns: all of them alone, one half in a pair
-      // (DUAL: columns 0-127 are the gate projection, 128-255 the up projection of the same output columns)
-      const uint64_t b_map = (DUAL && PAIR && rank == 1) ? w2_map : reinterpret_cast<uint64_t>(&map_w);
+      const uint64_t a_map = reinterpret_cast<uint64_t>(&map_a), a2_map = reinterpret_cast<uint64_t>(&map_a2);
+      const uint64_t b_map = reinterpret_cast<uint64_t>(&map_b), b2_map = reinterpret_cast<uint64_t>(&map_b2);
+      // claims the next ring slot; false after a wait that ran out
+      auto acquire = [&](uint32_t& a_dst, uint32_t& b_dst, uint32_t& bar) {
+        if (!mbar_wait_addr(empty_addr + stage * 8, phase ^ 1u)) {
+          *abort_flag = 1;
+          return false;
+        }
+        a_dst = ring_addr + stage * R::kStageBytes;
+        b_dst = a_dst + R::kABytes;
+        bar = signal_addr + stage * 8;
+        if (rank == 0) mbar_arrive_expect_addr(full_addr + stage * 8, CTAS * R::kStageBytes);  // in a pair both CTAs' bytes land here
+        ++issued;
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+        return true;
+      };
       for (int tile = first_tile; tile < total_tiles && !*abort_flag; tile += tile_step) {
-        const Tile t = decode_tile(tile, tile_start, seg, p.experts, OUT_N, TILE_ROWS, tiles_n);
-        const int row0 = t.row0 + static_cast<int>(rank) * kBM;
-        const int col0 = t.n0 + ((!DUAL && PAIR) ? static_cast<int>(rank) * (kBN / 2) : 0);
-        for (int k0 = 0; k0 < p.k; k0 += R::kSlotK) {
-          if (!mbar_wait_addr(empty_addr + stage * 8, phase ^ 1u)) {
-            *abort_flag = 1;
-            break;
-          }
-          const uint32_t a_dst = ring_addr + stage * R::kStageBytes, b_dst = a_dst + R::kABytes, bar = signal_addr + stage * 8;
-          if (rank == 0) mbar_arrive_expect_addr(full_addr + stage * 8, CTAS * R::kStageBytes);  // in a pair both CTAs' bytes land here
+        const Tile t = tile_at(tile);
+        uint32_t a_dst, b_dst, bar;
+        if constexpr (WGRAD) {
+          // A: 64-feature chunks of rows^T, B: 64-column chunks of the gradient, both indexed by the segment's rows.
+          // The maps see the buffers as [row][window line][feature] with the SAME stride for the two outer
+          // dimensions, so a box placed at window line -(pad) reads zeros into its first `pad` lines and rows
+          // row0 .. row0 + valid - 1 into the rest: the last slot of a segment is padded with zeros, not with the
+          // next expert's rows.
+          const int m0 = t.row0 - t.expert * p.m + static_cast<int>(rank) * kBM;
+          const int col0 = t.n0 + (PAIR ? static_cast<int>(rank) * (kBN / 2) : 0);
+          for (int r0 = t.k_lo; r0 < t.k_hi; r0 += R::kSlotK) {
+            if (!acquire(a_dst, b_dst, bar)) break;
+            const int line0 = min(t.k_hi - r0, R::kSlotK) - R::kSlotK;  // <= 0
 #pragma unroll
-          for (int j = 0; j < R::kSub; ++j) tma_2d<PAIR>(a_dst + j * kASubBytes, rows_map, k0 + j * kBK, row0, bar);  // past K: zero fill
+            for (int c = 0; c < kBM / 64; ++c) tma_3d<PAIR>(a_dst + c * R::kBChunkBytes, a_map, m0 + c * 64, line0, r0, bar);
 #pragma unroll
-          for (int c = 0; c < R::kChunks; ++c) {
-            if (DUAL && !PAIR && c >= R::kChunks / 2) tma_3d<PAIR>(b_dst + c * R::kBChunkBytes, w2_map, t.n0 + (c - R::kChunks / 2) * 64, k0, t.expert, bar);
-            else tma_3d<PAIR>(b_dst + c * R::kBChunkBytes, b_map, col0 + c * 64, k0, t.expert, bar);
+            for (int c = 0; c < R::kChunks; ++c) tma_3d<PAIR>(b_dst + c * R::kBChunkBytes, b_map, col0 + c * 64, line0, r0, bar);
           }
-          ++issued;
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1u;
+        } else if constexpr (B_K_MAJOR) {
+          const int row0 = t.row0 + static_cast<int>(rank) * kBM;
+          const int col0 = t.n0 + (PAIR ? static_cast<int>(rank) * (kBN / 2) : 0);
+          for (int s = 0; s < p.sources && !*abort_flag; ++s) {
+            const uint64_t am = s ? a2_map : a_map, bm = s ? b2_map : b_map;
+            for (int k0 = 0; k0 < p.k; k0 += R::kSlotK) {
+              if (!acquire(a_dst, b_dst, bar)) break;
+#pragma unroll
+              for (int j = 0; j < R::kSub; ++j) tma_2d<PAIR>(a_dst + j * kASubBytes, am, k0 + j * kBK, row0, bar);  // past K: zero fill
+#pragma unroll
+              for (int j = 0; j < R::kSub; ++j) tma_3d<PAIR>(b_dst + j * kBSpanBytes, bm, k0 + j * kBK, col0, t.expert, bar);
+            }
+          }
+        } else {
+          // this CTA's share of the 256 accumulator columns: all of them alone, one half in a pair
+          // (DUAL: columns 0-127 are the first projection, 128-255 the second projection of the same output columns)
+          const uint64_t bm = (DUAL && PAIR && rank == 1) ? b2_map : b_map;
+          const int row0 = t.row0 + static_cast<int>(rank) * kBM;
+          const int col0 = t.n0 + ((!DUAL && PAIR) ? static_cast<int>(rank) * (kBN / 2) : 0);
+          for (int k0 = 0; k0 < p.k; k0 += R::kSlotK) {
+            if (!acquire(a_dst, b_dst, bar)) break;
+#pragma unroll
+            for (int j = 0; j < R::kSub; ++j) tma_2d<PAIR>(a_dst + j * kASubBytes, a_map, k0 + j * kBK, row0, bar);  // past K: zero fill
+#pragma unroll
+            for (int c = 0; c < R::kChunks; ++c) {
+              if (DUAL && !PAIR && c >= R::kChunks / 2) tma_3d<PAIR>(b_dst + c * R::kBChunkBytes, b2_map, t.n0 + (c - R::kChunks / 2) * 64, k0, t.expert, bar);
+              else tma_3d<PAIR>(b_dst + c * R::kBChunkBytes, bm, col0 + c * 64, k0, t.expert, bar);
+            }
           }
         }
       }
@@ -352,33 +441,43 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
       uint32_t stage = 0, phase = 0, local = 0;
       bool pending = false;
       const uint32_t acc_full_addr = smem_addr(&acc_full[0]), acc_empty_addr = smem_addr(&acc_empty[0]);
-      const uint32_t a_hi = static_cast<uint32_t>(kDescA >> 32), b_hi = static_cast<uint32_t>(kDescB<CTAS> >> 32);
-      const uint32_t a_lo0 = static_cast<uint32_t>(kDescA) | (ring_addr >> 4);
-      const uint32_t b_lo0 = static_cast<uint32_t>(kDescB<CTAS>) | ((ring_addr + R::kABytes) >> 4);
+      constexpr uint64_t desc_a = WGRAD ? kDescMnMajor<CTAS> : kDescKMajor;
+      constexpr uint64_t desc_b = B_K_MAJOR ? kDescKMajor : kDescMnMajor<CTAS>;
+      const uint32_t a_hi = static_cast<uint32_t>(desc_a >> 32), b_hi = static_cast<uint32_t>(desc_b >> 32);
+      const uint32_t a_lo0 = static_cast<uint32_t>(desc_a) | (ring_addr >> 4);
+      const uint32_t b_lo0 = static_cast<uint32_t>(desc_b) | ((ring_addr + R::kABytes) >> 4);
       const uint32_t idesc = p.idesc;
-      for (int tile = first_tile; tile < total_tiles && !*abort_flag; tile += tile_step, ++local) {
+      for (int tile = first_tile; tile < total_tiles && !*abort_flag; tile += tile_step) {
+        int slots = fixed_slots;
+        if constexpr (WGRAD) {
+          slots = slots_of(tile_at(tile));
+          if (slots == 0) continue;
+        }
         const uint32_t acc = local & 1u;
         if (!mbar_wait_addr(acc_empty_addr + acc * 8, ((local >> 1) & 1u) ^ 1u)) {
           *abort_flag = 1;
           break;
         }
+        ++local;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kBN;
         uint32_t accumulate = 0;
-        for (int k0 = 0; k0 < p.k; k0 += R::kSlotK) {
+        for (int s = 0; s < slots; ++s) {
           if (!mbar_wait_addr(full_addr + stage * 8, phase)) {
             *abort_flag = 1;
             break;
           }
           tc_fence_after();
-          // descriptor start fields advance in 16-byte units: a ring slot, then per MMA 16 K values = 32 bytes along
-          // A's swizzled 128-byte rows (a new 16 KiB block every 64 K values) and 16 K rows = 2048 bytes of B
+          // descriptor start fields advance in 16-byte units: a ring slot, then per MMA (16 K values) 32 bytes along a
+          // K-major operand's swizzled 128-byte rows (a new block every 64 K values) or 16 lines = 2048 bytes of an
+          // MN-major operand
           const uint32_t a_lo = a_lo0 + stage * (R::kStageBytes >> 4), b_lo = b_lo0 + stage * (R::kStageBytes >> 4);
 #pragma unroll
           for (int k = 0; k < R::kSlotK / kUmmaK; ++k) {
             constexpr int kPerSpan = kBK / kUmmaK;
-            mma_issue<PAIR>(d_tmem, a_lo + (k / kPerSpan) * (kASubBytes >> 4) + (k % kPerSpan) * (kUmmaK * 2 >> 4), b_lo + k * (kUmmaK * 128 >> 4),
-                            a_hi, b_hi, idesc, accumulate);
+            const uint32_t a_step = WGRAD ? k * (kUmmaK * 128 >> 4) : (k / kPerSpan) * (kASubBytes >> 4) + (k % kPerSpan) * (kUmmaK * 2 >> 4);
+            const uint32_t b_step = B_K_MAJOR ? (k / kPerSpan) * (kBSpanBytes >> 4) + (k % kPerSpan) * (kUmmaK * 2 >> 4) : k * (kUmmaK * 128 >> 4);
+            mma_issue<PAIR>(d_tmem, a_lo + a_step, b_lo + b_step, a_hi, b_hi, idesc, accumulate);
             accumulate = 1;
           }
           mma_commit_addr<PAIR>(empty_addr + stage * 8);  // the slot (in both CTAs of a pair) is free once these MMAs have read it
@@ -403,35 +502,43 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     const int quarter = warp & 3;  // the 32 tensor-memory lanes this warp may read
     uint32_t local = 0;
     T* out = static_cast<T*>(p.out);
-    for (int tile = first_tile; tile < total_tiles && !*abort_flag; tile += tile_step, ++local) {
-      const Tile t = decode_tile(tile, tile_start, seg, p.experts, OUT_N, TILE_ROWS, tiles_n);
+    for (int tile = first_tile; tile < total_tiles && !*abort_flag; tile += tile_step) {
+      const Tile t = tile_at(tile);
+      const bool zeros = slots_of(t) == 0;  // kWgrad, expert without rows: no accumulator was produced
       const uint32_t acc = local & 1u;
-      // one lane polls for the whole warp
-      const int ready = __shfl_sync(0xffffffffu, lane == 0 ? static_cast<int>(mbar_wait(&acc_full[acc], (local >> 1) & 1u)) : 0, 0);
-      if (!ready) {
-        *abort_flag = 1;
-        break;
+      if (!zeros) {
+        // one lane polls for the whole warp
+        const int ready = __shfl_sync(0xffffffffu, lane == 0 ? static_cast<int>(mbar_wait(&acc_full[acc], (local >> 1) & 1u)) : 0, 0);
+        if (!ready) {
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
       }
-      tc_fence_after();
       const uint32_t taddr = tmem_base + acc * kBN + (static_cast<uint32_t>(quarter * 32) << 16);
       const int warp_row0 = t.row0 + static_cast<int>(rank) * kBM + quarter * 32;
       uint4(*mine)[8] = staging[quarter];
 #pragma unroll 1
-      for (int c = 0; c < OUT_N / 32; ++c) {
-        uint32_t v[32], u[32];
-        tmem_load_32(taddr + c * 32, v);
-        if constexpr (DUAL) tmem_load_32(taddr + OUT_N + c * 32, u);
-        tmem_load_wait();
+      for (int c = 0; c < ACC_COLS / 32; ++c) {
         uint32_t packed[16];
+        if (zeros) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          float lo = __uint_as_float(v[2 * j]), hi = __uint_as_float(v[2 * j + 1]);
-          if constexpr (DUAL) {
-            // columns 0..127 of the accumulator hold rows @ gate, 128..255 rows @ up
-            lo = __fmul_rn(silu_f32<1>(lo), __uint_as_float(u[2 * j]));
-            hi = __fmul_rn(silu_f32<1>(hi), __uint_as_float(u[2 * j + 1]));
+          for (int j = 0; j < 16; ++j) packed[j] = 0u;
+        } else {
+          uint32_t v[32], u[32];
+          tmem_load_32(taddr + c * 32, v);
+          if constexpr (MODE == kSwiglu) tmem_load_32(taddr + OUT_N + c * 32, u);
+          tmem_load_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float lo = __uint_as_float(v[2 * j]), hi = __uint_as_float(v[2 * j + 1]);
+            if constexpr (MODE == kSwiglu) {
+              // columns 0..127 of the accumulator hold rows @ gate, 128..255 rows @ up
+              lo = __fmul_rn(silu_f32<1>(lo), __uint_as_float(u[2 * j]));
+              hi = __fmul_rn(silu_f32<1>(hi), __uint_as_float(u[2 * j + 1]));
+            }
+            packed[j] = Num<T>::pack2(lo, hi);
           }
-          packed[j] = Num<T>::pack2(lo, hi);
         }
         // lane = row: its 32 columns are four 16-byte pieces of the 128-byte staging row (piece index
         // xor-ed with the row so that neither these writes nor the transposed reads conflict on banks)
@@ -442,22 +549,30 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
           // 64 finished columns of 32 rows: write them out as whole 128-byte row segments, four rows per instruction
           __syncwarp();
           const int piece = lane & 7;
-          const int col = t.n0 + (c - 1) * 32 + piece * 8;
+          int tile_col = (c - 1) * 32 + piece * 8, shift = 0;  // column within the tile; kGateUp: the second projection lies n columns further
+          if (MODE == kGateUp && tile_col >= OUT_N) {
+            tile_col -= OUT_N;
+            shift = p.n;
+          }
+          const int col = t.n0 + tile_col;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int r = i * 4 + (lane >> 3);
             const int row = warp_row0 + r;
             if (row < t.row_end && col < p.n)
-              st_stream(out + static_cast<int64_t>(row) * p.ld_out + col, mine[r][piece ^ (r & 7)]);
+              st_stream(out + static_cast<int64_t>(row) * p.ld_out + col + shift, mine[r][piece ^ (r & 7)]);
           }
           __syncwarp();
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        if constexpr (PAIR) remote_arrive(map_to_rank(smem_addr(&acc_empty[acc]), 0));  // the leader issues the MMAs
-        else mbar_arrive(&acc_empty[acc]);
+      if (!zeros) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (PAIR) remote_arrive(map_to_rank(smem_addr(&acc_empty[acc]), 0));  // the leader issues the MMAs
+          else mbar_arrive(&acc_empty[acc]);
+        }
+        ++local;
       }
     }
   }
@@ -490,22 +605,40 @@ EncodeTiled encoder() {
   return fn;
 }
 
-// rows [total_rows, k], row stride ld: box 64 (K) x 128 (rows), 128-byte swizzle, zero fill outside.
-bool encode_rows(CUtensorMap* map, CUtensorMapDataType type, const void* base, int64_t total_rows, int64_t k, int64_t ld) {
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(total_rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
-  const cuuint32_t box[2] = {kBK, kBM}, elem[2] = {1, 1};
-  return encoder()(map, type, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+// A 2- or 3-dimensional map of 16-bit elements: 128-byte swizzle, zero fill outside; strides in elements.
+bool encode(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* base, const int64_t (&dims)[3], const int64_t (&strides)[2],
+            const int (&box)[3]) {
+  cuuint64_t d[3], s[2];
+  cuuint32_t b[3], elem[3] = {1, 1, 1};
+  for (int i = 0; i < 3; ++i) {
+    d[i] = static_cast<cuuint64_t>(dims[i]);
+    b[i] = static_cast<cuuint32_t>(box[i]);
+  }
+  for (int i = 0; i < 2; ++i) s[i] = static_cast<cuuint64_t>(strides[i]) * 2;
+  return encoder()(map, type, static_cast<cuuint32_t>(rank), const_cast<void*>(base), d, s, b, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// weight [experts, k, n], n contiguous: box 64 (N) x slot_k (K) x 1 (expert).
+// token-major operand [total_rows, width], row stride ld: box 64 (contraction values) x 128 (rows).
+bool encode_rows(CUtensorMap* map, CUtensorMapDataType type, const void* base, int64_t total_rows, int64_t width, int64_t ld) {
+  return encode(map, type, 2, base, {width, total_rows, 1}, {ld, 0}, {kBK, kBM, 1});
+}
+
+// weight [experts, k, n], n contiguous, read along n: box 64 (n) x slot_k (k) x 1 (expert).
 bool encode_weight(CUtensorMap* map, CUtensorMapDataType type, const void* base, int64_t experts, int64_t k, int64_t n, int slot_k) {
-  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(experts)};
-  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(n) * 2, static_cast<cuuint64_t>(n) * static_cast<cuuint64_t>(k) * 2};
-  const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(slot_k), 1}, elem[3] = {1, 1, 1};
-  return encoder()(map, type, 3, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return encode(map, type, 3, base, {n, k, experts}, {n, n * k}, {64, slot_k, 1});
+}
+
+// the same weight read along its rows (the contraction runs over n): box 64 (n) x rows (k) x 1 (expert).
+bool encode_weight_rows(CUtensorMap* map, CUtensorMapDataType type, const void* base, int64_t experts, int64_t k, int64_t n, int rows) {
+  return encode(map, type, 3, base, {n, k, experts}, {n, n * k}, {64, rows, 1});
+}
+
+// token-major operand [total_rows, width] for a contraction over rows: seen as [row][window line][column] with the
+// row stride for BOTH outer dimensions, element (row r, line j, column c) = buffer[r + j][c].  A box of slot_k lines
+// placed at line -(pad) of row r0 reads `pad` lines of zeros and then rows r0 .. r0 + slot_k - pad - 1.
+bool encode_window(CUtensorMap* map, CUtensorMapDataType type, const void* base, int64_t total_rows, int64_t width, int64_t ld, int slot_k) {
+  return encode(map, type, 3, base, {width, slot_k, total_rows}, {ld, ld}, {64, slot_k, 1});
 }
 
 // B200_GEMM_PAIR=0 in the environment runs every CTA on its own (cta_group::1); read at every call.
@@ -516,28 +649,46 @@ bool pair_enabled() {
 
 constexpr int kNoClusters = -1000;  // run_with<., ., 2>: no cluster of two CTAs can be resident; the caller runs single CTAs instead
 
-// What the tensor maps of one call describe.
+// What the tensor maps of one call describe (widths and strides in elements).
 struct Operands {
-  const void *rows, *weight, *weight2;
-  int64_t total_rows, k, n, experts, ld_rows;
+  const void *a, *b, *a2, *b2;  // a: token-major [total_rows, .]; b: weight (kWgrad: the token-major gradient)
+  int64_t total_rows, experts;
+  int64_t k, n;                 // the WEIGHT's shape [experts, k, n], whichever way the mode contracts
+  int64_t ld_a, ld_b;           // row strides of the token-major operands (ld_b: kWgrad only)
   CUtensorMapDataType type;
 };
 
-template <typename T, bool DUAL, int CTAS>
-int run_with(const Operands& op, GemmArgs args, uint32_t format, cudaStream_t st) {
-  alignas(64) CUtensorMap rows, w, w2;
+template <int MODE, int CTAS>
+bool encode_operands(const Operands& op, CUtensorMap* a, CUtensorMap* b, CUtensorMap* a2, CUtensorMap* b2) {
   constexpr int slot_k = Ring<CTAS>::kSlotK;
-  if (!encode_rows(&rows, op.type, op.rows, op.total_rows, op.k, op.ld_rows) ||
-      !encode_weight(&w, op.type, op.weight, op.experts, op.k, op.n, slot_k) ||
-      !encode_weight(&w2, op.type, op.weight2 ? op.weight2 : op.weight, op.experts, op.k, op.n, slot_k))
-    return fail(B200_ERR_LAUNCH, "b200_moe_grouped_gemm: tensor map encoding failed");
-  auto kernel = grouped_gemm_kernel<T, DUAL, CTAS>;
+  const void* second_a = op.a2 ? op.a2 : op.a;
+  const void* second_b = op.b2 ? op.b2 : op.b;
+  if constexpr (MODE == kWgrad) {
+    return encode_window(a, op.type, op.a, op.total_rows, op.k, op.ld_a, slot_k) &&
+           encode_window(b, op.type, op.b, op.total_rows, op.n, op.ld_b, slot_k) &&
+           encode_window(a2, op.type, op.a, op.total_rows, op.k, op.ld_a, slot_k) &&
+           encode_window(b2, op.type, op.b, op.total_rows, op.n, op.ld_b, slot_k);
+  } else if constexpr (MODE == kDgrad) {
+    return encode_rows(a, op.type, op.a, op.total_rows, op.n, op.ld_a) && encode_rows(a2, op.type, second_a, op.total_rows, op.n, op.ld_a) &&
+           encode_weight_rows(b, op.type, op.b, op.experts, op.k, op.n, kBN / CTAS) &&
+           encode_weight_rows(b2, op.type, second_b, op.experts, op.k, op.n, kBN / CTAS);
+  } else {
+    return encode_rows(a, op.type, op.a, op.total_rows, op.k, op.ld_a) && encode_rows(a2, op.type, op.a, op.total_rows, op.k, op.ld_a) &&
+           encode_weight(b, op.type, op.b, op.experts, op.k, op.n, slot_k) && encode_weight(b2, op.type, second_b, op.experts, op.k, op.n, slot_k);
+  }
+}
+
+template <typename T, int MODE, int CTAS>
+int run_with(const char* what, const Operands& op, GemmArgs args, uint32_t format, cudaStream_t st) {
+  alignas(64) CUtensorMap a, b, a2, b2;
+  if (!encode_operands<MODE, CTAS>(op, &a, &b, &a2, &b2)) return fail(B200_ERR_LAUNCH, "%s: tensor map encoding failed", what);
+  auto kernel = grouped_gemm_kernel<T, MODE, CTAS>;
   constexpr int smem = Ring<CTAS>::kSmemBytes;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
     (void)cudaGetLastError();
-    return fail(B200_ERR_LAUNCH, "b200_moe_grouped_gemm: cannot reserve %d bytes of shared memory", smem);
+    return fail(B200_ERR_LAUNCH, "%s: cannot reserve %d bytes of shared memory", what, smem);
   }
-  args.idesc = instr_desc(format, CTAS);
+  args.idesc = instr_desc(format, CTAS, MODE == kWgrad, MODE != kDgrad);
   cudaLaunchConfig_t config = {};
   config.blockDim = dim3(kThreads);
   config.dynamicSmemBytes = smem;
@@ -570,18 +721,43 @@ int run_with(const Operands& op, GemmArgs args, uint32_t format, cudaStream_t st
     attrs[n_attrs].val.programmaticStreamSerializationAllowed = 1;
     config.numAttrs = ++n_attrs;
   }
-  (void)cudaLaunchKernelEx(&config, kernel, rows, w, w2, args);
+  (void)cudaLaunchKernelEx(&config, kernel, a, b, a2, b2, args);
   return after_launch(CTAS == 2 ? "grouped_gemm_kernel (pairs)" : "grouped_gemm_kernel");
 }
 
-template <typename T, bool DUAL>
-int run(const Operands& op, const GemmArgs& args, uint32_t format, cudaStream_t st) {
+template <typename T, int MODE>
+int run(const char* what, const Operands& op, const GemmArgs& args, uint32_t format, cudaStream_t st) {
   if (pair_enabled()) {
-    const int rc = run_with<T, DUAL, 2>(op, args, format, st);
+    const int rc = run_with<T, MODE, 2>(what, op, args, format, st);
     if (rc != kNoClusters) return rc;
   }
-  return run_with<T, DUAL, 1>(op, args, format, st);
+  return run_with<T, MODE, 1>(what, op, args, format, st);
 }
+
+template <int MODE>
+int run_typed(const char* what, int dtype, const Operands& op, const GemmArgs& args, cudaStream_t st) {
+  if (dtype == B200_BF16) return run<__nv_bfloat16, MODE>(what, op, args, 1u, st);
+  return run<__half, MODE>(what, op, args, 0u, st);
+}
+
+// Checks shared by the four entry points; B200_OK with *skip = true when there is nothing to compute.
+int check_common(const char* what, int dtype, int64_t total_rows, int64_t k, int64_t n, int64_t experts, const int64_t (&lds)[2],
+                 const int64_t (&ld_min)[2], const void* const (&ptrs)[6], const int32_t* offsets) {
+  if (dtype != B200_BF16 && dtype != B200_F16)
+    return fail(B200_ERR_DTYPE, "%s: dtype %d not supported (bf16 or fp16 operands, fp32 accumulation)", what, dtype);
+  if (total_rows < 0 || k < 0 || n < 0 || experts < 0) return fail(B200_ERR_SHAPE, "%s: negative size", what);
+  if (experts > kMaxExperts) return fail(B200_ERR_SHAPE, "%s: experts=%lld exceeds %d", what, (long long)experts, kMaxExperts);
+  if (total_rows > 0x7fffffffLL - 2 * kBM || k > 0x3fffffffLL || n > 0x3fffffffLL) return fail(B200_ERR_SHAPE, "%s: size out of range", what);
+  if (k % 8 != 0 || n % 8 != 0 || lds[0] % 8 != 0 || lds[1] % 8 != 0)
+    return fail(B200_ERR_SHAPE, "%s: k, n and the row strides must be multiples of 8 elements (16-byte rows for the tensor maps)", what);
+  if (lds[0] < ld_min[0] || lds[1] < ld_min[1]) return fail(B200_ERR_SHAPE, "%s: leading dimension smaller than the row", what);
+  for (const void* ptr : ptrs)
+    if (ptr && !aligned(ptr, 16)) return fail(B200_ERR_ALIGNMENT, "%s: operands and results must be 16-byte aligned", what);
+  if (!aligned(offsets, 4)) return fail(B200_ERR_ALIGNMENT, "%s: offsets must be 4-byte aligned", what);
+  return B200_OK;
+}
+
+CUtensorMapDataType map_type(int dtype) { return dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16; }
 
 }  // namespace
 
@@ -591,31 +767,20 @@ unsigned int gemm_wait_timeouts() { return read_wait_timeouts(); }
 
 using namespace b200;
 
-extern "C" int b200_moe_grouped_gemm(const void* rows, const void* weight, const void* weight2, const int32_t* offsets, void* out,
-                                     int64_t total_rows, int64_t k, int64_t n, int64_t experts, int64_t ld_rows, int64_t ld_out,
-                                     int dtype, void* stream) {
-  if (dtype != B200_BF16 && dtype != B200_F16)
-    return fail(B200_ERR_DTYPE, "%s: dtype %d not supported (bf16 or fp16 operands, fp32 accumulation)", __func__, dtype);
-  if (total_rows < 0 || k < 0 || n < 0 || experts < 0) return fail(B200_ERR_SHAPE, "%s: negative size", __func__);
-  if (experts > kMaxExperts) return fail(B200_ERR_SHAPE, "%s: experts=%lld exceeds %d", __func__, (long long)experts, kMaxExperts);
-  if (total_rows > 0x7fffffffLL - kBM || k > 0x7fffffffLL || n > 0x7fffffffLL) return fail(B200_ERR_SHAPE, "%s: size out of range", __func__);
+namespace {
+
+// The three forward forms: out = rows @ weight, the fused SwiGLU of two projections, or both projections side by side.
+int forward(const char* what, int mode, const void* rows, const void* weight, const void* weight2, const int32_t* offsets, void* out,
+            int64_t total_rows, int64_t k, int64_t n, int64_t experts, int64_t ld_rows, int64_t ld_out, int dtype, void* stream) {
+  if (int rc = check_common(what, dtype, total_rows, k, n, experts, {ld_rows, ld_out}, {k, mode == kGateUp ? 2 * n : n},
+                            {rows, weight, weight2, out, nullptr, nullptr}, offsets))
+    return rc;
   if (total_rows == 0 || n == 0 || experts == 0) return B200_OK;
-  B200_REQUIRE_PTR(rows);
-  B200_REQUIRE_PTR(weight);
-  B200_REQUIRE_PTR(offsets);
-  B200_REQUIRE_PTR(out);
-  if (k == 0) return fail(B200_ERR_SHAPE, "%s: k must be positive", __func__);
-  if (k % 8 != 0 || n % 8 != 0 || ld_rows % 8 != 0 || ld_out % 8 != 0)
-    return fail(B200_ERR_SHAPE, "%s: k, n and the row strides must be multiples of 8 elements (16-byte rows for the tensor maps)", __func__);
-  if (ld_rows < k || ld_out < n) return fail(B200_ERR_SHAPE, "%s: leading dimension smaller than the row", __func__);
-  if (!aligned(rows, 16) || !aligned(weight, 16) || !aligned(out, 16) || (weight2 && !aligned(weight2, 16)) || !aligned(offsets, 4))
-    return fail(B200_ERR_ALIGNMENT, "%s: rows, weights and out must be 16-byte aligned", __func__);
+  if (!rows || !weight || !offsets || !out || (mode != kPlain && !weight2)) return fail(B200_ERR_NULL_POINTER, "%s: null pointer", what);
+  if (k == 0) return fail(B200_ERR_SHAPE, "%s: k must be positive", what);
   if (int rc = check_device()) return rc;
-  if (encoder() == nullptr) return fail(B200_ERR_LAUNCH, "%s: the driver does not provide cuTensorMapEncodeTiled", __func__);
-
-  const CUtensorMapDataType type = dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  const Operands op{rows, weight, weight2, total_rows, k, n, experts, ld_rows, type};
-
+  if (encoder() == nullptr) return fail(B200_ERR_LAUNCH, "%s: the driver does not provide cuTensorMapEncodeTiled", what);
+  const Operands op{rows, weight, nullptr, weight2, total_rows, experts, k, n, ld_rows, 0, map_type(dtype)};
   GemmArgs args{};
   args.offsets = offsets;
   args.out = out;
@@ -623,9 +788,84 @@ extern "C" int b200_moe_grouped_gemm(const void* rows, const void* weight, const
   args.experts = static_cast<int>(experts);
   args.n = static_cast<int>(n);
   args.k = static_cast<int>(k);
+  args.sources = 1;
   args.total_rows = static_cast<int>(total_rows);
-  const uint32_t format = dtype == B200_BF16 ? 1u : 0u;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == B200_BF16) return weight2 ? run<__nv_bfloat16, true>(op, args, format, st) : run<__nv_bfloat16, false>(op, args, format, st);
-  return weight2 ? run<__half, true>(op, args, format, st) : run<__half, false>(op, args, format, st);
+  if (mode == kSwiglu) return run_typed<kSwiglu>(what, dtype, op, args, st);
+  if (mode == kGateUp) return run_typed<kGateUp>(what, dtype, op, args, st);
+  return run_typed<kPlain>(what, dtype, op, args, st);
+}
+
+}  // namespace
+
+extern "C" int b200_moe_grouped_gemm(const void* rows, const void* weight, const void* weight2, const int32_t* offsets, void* out,
+                                     int64_t total_rows, int64_t k, int64_t n, int64_t experts, int64_t ld_rows, int64_t ld_out,
+                                     int dtype, void* stream) {
+  return forward(__func__, weight2 ? kSwiglu : kPlain, rows, weight, weight2, offsets, out, total_rows, k, n, experts, ld_rows, ld_out, dtype, stream);
+}
+
+extern "C" int b200_moe_grouped_gemm_gate_up(const void* rows, const void* gate_weight, const void* up_weight, const int32_t* offsets, void* out,
+                                             int64_t total_rows, int64_t k, int64_t n, int64_t experts, int64_t ld_rows, int64_t ld_out,
+                                             int dtype, void* stream) {
+  return forward(__func__, kGateUp, rows, gate_weight, up_weight, offsets, out, total_rows, k, n, experts, ld_rows, ld_out, dtype, stream);
+}
+
+extern "C" int b200_moe_grouped_gemm_dgrad(const void* grad_out, const void* weight, const void* grad_out2, const void* weight2,
+                                           const int32_t* offsets, void* grad_rows, int64_t total_rows, int64_t k, int64_t n, int64_t experts,
+                                           int64_t ld_grad, int64_t ld_out, int dtype, void* stream) {
+  if (int rc = check_common(__func__, dtype, total_rows, k, n, experts, {ld_grad, ld_out}, {n, k},
+                            {grad_out, weight, grad_out2, weight2, grad_rows, nullptr}, offsets))
+    return rc;
+  if ((grad_out2 == nullptr) != (weight2 == nullptr)) return fail(B200_ERR_NULL_POINTER, "%s: grad_out2 and weight2 go together", __func__);
+  if (total_rows == 0 || k == 0 || experts == 0) return B200_OK;
+  if (!grad_out || !weight || !offsets || !grad_rows) return fail(B200_ERR_NULL_POINTER, "%s: null pointer", __func__);
+  if (n == 0) return fail(B200_ERR_SHAPE, "%s: n must be positive", __func__);
+  if (int rc = check_device()) return rc;
+  if (encoder() == nullptr) return fail(B200_ERR_LAUNCH, "%s: the driver does not provide cuTensorMapEncodeTiled", __func__);
+  const Operands op{grad_out, weight, grad_out2, weight2, total_rows, experts, k, n, ld_grad, 0, map_type(dtype)};
+  GemmArgs args{};
+  args.offsets = offsets;
+  args.out = grad_rows;
+  args.ld_out = ld_out;
+  args.experts = static_cast<int>(experts);
+  args.n = static_cast<int>(k);  // the result has the weight's k columns, the contraction runs over its n
+  args.k = static_cast<int>(n);
+  args.sources = grad_out2 ? 2 : 1;
+  args.total_rows = static_cast<int>(total_rows);
+  return run_typed<kDgrad>(__func__, dtype, op, args, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_moe_grouped_gemm_wgrad(const void* rows, const void* grad_out, const int32_t* offsets, void* grad_weight,
+                                           int64_t total_rows, int64_t k, int64_t n, int64_t experts, int64_t ld_rows, int64_t ld_grad,
+                                           int dtype, void* stream) {
+  if (int rc = check_common(__func__, dtype, total_rows, k, n, experts, {ld_rows, ld_grad}, {k, n},
+                            {rows, grad_out, grad_weight, nullptr, nullptr, nullptr}, offsets))
+    return rc;
+  if (k == 0 || n == 0 || experts == 0) return B200_OK;
+  if (experts * k > 0x7fffffffLL - 2 * kBM) return fail(B200_ERR_SHAPE, "%s: experts * k out of range", __func__);
+  const int64_t tiles = experts * ((k + kBM - 1) / kBM) * ((n + kBN - 1) / kBN);
+  if (tiles > 0x7fffffffLL) return fail(B200_ERR_SHAPE, "%s: too many output tiles", __func__);
+  if (!offsets || !grad_weight || (total_rows > 0 && (!rows || !grad_out))) return fail(B200_ERR_NULL_POINTER, "%s: null pointer", __func__);
+  if (int rc = check_device()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (total_rows == 0) {  // no rows at all: every expert's gradient is zero
+    if (cudaMemsetAsync(grad_weight, 0, static_cast<size_t>(experts * k * n) * 2, st) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return fail(B200_ERR_LAUNCH, "%s: clearing the result failed", __func__);
+    }
+    return B200_OK;
+  }
+  if (encoder() == nullptr) return fail(B200_ERR_LAUNCH, "%s: the driver does not provide cuTensorMapEncodeTiled", __func__);
+  const Operands op{rows, grad_out, nullptr, nullptr, total_rows, experts, k, n, ld_rows, ld_grad, map_type(dtype)};
+  GemmArgs args{};
+  args.offsets = offsets;
+  args.out = grad_weight;
+  args.ld_out = n;
+  args.experts = static_cast<int>(experts);
+  args.n = static_cast<int>(n);
+  args.k = 0;
+  args.m = static_cast<int>(k);
+  args.sources = 1;
+  args.total_rows = static_cast<int>(total_rows);
+  return run_typed<kWgrad>(__func__, dtype, op, args, st);
 }

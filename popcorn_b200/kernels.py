@@ -97,9 +97,7 @@ def momoe(x, gate_weight, up_weight, down_weight, router_logits, top_k=2):
 
 
 # ops with backward kernels are registered in their differentiable form
-for _op in (moe_grouped_gemm, momoe):
-    _op.register(BACKEND, source=f"popcorn_b200.ops.{_op.name}", forward_only=True)
 for _op in (rms_norm, add_rms_norm, rms_norm_gated, l2_norm, layer_norm, rotary_embedding, rope, llama4_rope, qk_norm_rope, swiglu, geglu,
-            moe_route, moe_permute, moe_unpermute):
+            moe_route, moe_permute, moe_unpermute, moe_grouped_gemm, momoe):
     _op.register(BACKEND, source=f"popcorn_b200.autograd.{_op.name}")
 del _op

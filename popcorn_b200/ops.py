@@ -689,15 +689,91 @@ def moe_grouped_gemm(rows: Tensor, weight: Tensor, offsets: Tensor, up_weight: T
     return out
 
 
-def momoe(x: Tensor, gate_weight: Tensor, up_weight: Tensor, down_weight: Tensor, router_logits: Tensor, top_k: int = 2) -> Tensor:
-    """Mixture of SwiGLU expert MLPs, routed to the top-k experts by softmax probability (momoe.py:34-53).
+def _gemm_operands(name: str, rows: Tensor, weight: Tensor, offsets: Tensor, width: int, *more: Tensor | None):
+    """Common checks of the grouped-GEMM calls: a 16-bit [n, width] token-major operand, [experts, k, n] weights, int32 offsets."""
+    device = _require_cuda(rows, weight, offsets, *[t for t in more if t is not None])
+    _forbid_grad(rows, weight, *more)
+    code = _dtype_code(rows, name)
+    if rows.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError(f"{name}: bf16 or fp16 operands only (fp32 accumulation)")
+    if weight.dim() != 3 or rows.dim() != 2 or rows.shape[1] != width:
+        raise ValueError(f"{name}: expected a [rows, {width}] operand against [experts, in_features, out_features] weights")
+    for t in (weight, *more):
+        if t is not None and t.dtype != rows.dtype:
+            raise TypeError(f"{name}: all operands must share a dtype")
+    if offsets.dtype != torch.int32 or offsets.shape != (weight.shape[0] + 1,):
+        raise TypeError(f"{name}: offsets must be int32 [experts + 1]")
+    return device, code
 
-    The reference evaluates every expert on every token in fp32; here only the routed (token, expert) pairs are
-    computed: route -> permute into expert-major rows -> gate/up projection + SwiGLU and down projection on the tensor
-    cores (16-bit operands, fp32 accumulation, 16-bit intermediate, like the incumbent kernels,
-    momoe_tl.py:90-330) -> weighted unpermute in fp32.  x: [batch, seq, hidden] bf16 or fp16."""
-    device = _require_cuda(x, gate_weight, up_weight, down_weight, router_logits)
-    _forbid_grad(x, gate_weight, up_weight, down_weight, router_logits)
+
+def moe_grouped_gemm_gate_up(rows: Tensor, gate_weight: Tensor, up_weight: Tensor, offsets: Tensor) -> Tensor:
+    """[rows @ gate_weight[e] | rows @ up_weight[e]] as one [n, 2 * out_features] buffer: the pre-activations a
+    training call keeps for the SwiGLU backward (momoe_tl.py:180-190 saves the same two tensors)."""
+    experts, k, n = gate_weight.shape
+    device, code = _gemm_operands("moe_grouped_gemm_gate_up", rows, gate_weight, offsets, k, up_weight)
+    if up_weight.shape != gate_weight.shape:
+        raise ValueError("moe_grouped_gemm_gate_up: gate and up weights must have one shape")
+    r2, ldr = _rows(rows)
+    total = r2.shape[0]
+    out = torch.zeros((total, 2 * n), dtype=rows.dtype, device=device)
+    with torch.cuda.device(device):
+        _lib.call("b200_moe_grouped_gemm_gate_up", _ptr(r2), _ptr(gate_weight.contiguous()), _ptr(up_weight.contiguous()),
+                  _ptr(offsets.contiguous()), _ptr(out), total, k, n, experts, ldr, max(2 * n, 1), code, _stream(device))
+    return out
+
+
+def moe_grouped_gemm_dgrad(grad_out: Tensor, weight: Tensor, offsets: Tensor, grad_out2: Tensor | None = None,
+                           weight2: Tensor | None = None) -> Tensor:
+    """grad_rows[p] = grad_out[p] @ weight[e(p)]^T (+ grad_out2[p] @ weight2[e(p)]^T): the gradient of
+    `moe_grouped_gemm` with respect to its rows; rows outside every segment get zeros.  The two gradients may be
+    column halves of one buffer (they must share a row stride)."""
+    experts, k, n = weight.shape
+    device, code = _gemm_operands("moe_grouped_gemm_dgrad", grad_out, weight, offsets, n, grad_out2, weight2)
+    if (grad_out2 is None) != (weight2 is None):
+        raise ValueError("moe_grouped_gemm_dgrad: grad_out2 and weight2 go together")
+    g1, ld = _rows(grad_out)
+    g2 = None
+    if grad_out2 is not None:
+        if grad_out2.shape != grad_out.shape or weight2.shape != weight.shape:
+            raise ValueError("moe_grouped_gemm_dgrad: the second pair must have the shapes of the first")
+        g2, ld2 = _rows(grad_out2)
+        if ld2 != ld:
+            g1, g2 = g1.contiguous(), g2.contiguous()
+            ld = max(n, 1)
+    total = g1.shape[0]
+    out = torch.zeros((total, k), dtype=grad_out.dtype, device=device)
+    with torch.cuda.device(device):
+        _lib.call("b200_moe_grouped_gemm_dgrad", _ptr(g1), _ptr(weight.contiguous()), _ptr(g2), _ptr(None if weight2 is None else weight2.contiguous()),
+                  _ptr(offsets.contiguous()), _ptr(out), total, k, n, experts, ld, max(k, 1), code, _stream(device))
+    return out
+
+
+def moe_grouped_gemm_wgrad(rows: Tensor, grad_out: Tensor, offsets: Tensor) -> Tensor:
+    """grad_weight[e] = rows[segment e]^T @ grad_out[segment e], [experts, in_features, out_features]: the gradient of
+    `moe_grouped_gemm` with respect to its weight (experts without rows get zeros)."""
+    device = _require_cuda(rows, grad_out, offsets)
+    _forbid_grad(rows, grad_out)
+    code = _dtype_code(rows, "moe_grouped_gemm_wgrad")
+    if rows.dtype not in (torch.bfloat16, torch.float16) or grad_out.dtype != rows.dtype:
+        raise TypeError("moe_grouped_gemm_wgrad: bf16 or fp16 operands of one dtype only (fp32 accumulation)")
+    if rows.dim() != 2 or grad_out.dim() != 2 or rows.shape[0] != grad_out.shape[0]:
+        raise ValueError("moe_grouped_gemm_wgrad: rows [n, in_features] and grad_out [n, out_features] must have the same n")
+    if offsets.dtype != torch.int32 or offsets.dim() != 1 or offsets.numel() < 1:
+        raise TypeError("moe_grouped_gemm_wgrad: offsets must be int32 [experts + 1]")
+    experts = offsets.numel() - 1
+    r2, ldr = _rows(rows)
+    g2, ldg = _rows(grad_out)
+    total, k, n = r2.shape[0], r2.shape[1], g2.shape[1]
+    out = torch.empty((experts, k, n), dtype=rows.dtype, device=device)
+    with torch.cuda.device(device):
+        _lib.call("b200_moe_grouped_gemm_wgrad", _ptr(r2), _ptr(g2), _ptr(offsets.contiguous()), _ptr(out), total, k, n, experts, ldr, ldg,
+                  code, _stream(device))
+    return out
+
+
+def check_momoe(x: Tensor, gate_weight: Tensor, up_weight: Tensor, down_weight: Tensor, router_logits: Tensor) -> None:
+    """Argument checks of `momoe`, shared with its differentiable form."""
+    _require_cuda(x, gate_weight, up_weight, down_weight, router_logits)
     if x.dtype not in (torch.bfloat16, torch.float16):
         raise TypeError("momoe: bf16 or fp16 activations and weights only (the expert projections run on 16-bit tensor-core operands)")
     if not (gate_weight.dtype == up_weight.dtype == down_weight.dtype == x.dtype):
@@ -707,6 +783,18 @@ def momoe(x: Tensor, gate_weight: Tensor, up_weight: Tensor, down_weight: Tensor
         raise ValueError("momoe: expected x [..., hidden], gate/up [experts, hidden, intermediate], down [experts, intermediate, hidden]")
     if router_logits.shape != (*x.shape[:-1], experts):
         raise ValueError("momoe: router_logits must be [..., experts] over the tokens of x")
+
+
+def momoe(x: Tensor, gate_weight: Tensor, up_weight: Tensor, down_weight: Tensor, router_logits: Tensor, top_k: int = 2) -> Tensor:
+    """Mixture of SwiGLU expert MLPs, routed to the top-k experts by softmax probability (momoe.py:34-53).
+
+    The reference evaluates every expert on every token in fp32; here only the routed (token, expert) pairs are
+    computed: route -> permute into expert-major rows -> gate/up projection + SwiGLU and down projection on the tensor
+    cores (16-bit operands, fp32 accumulation, 16-bit intermediate, like the incumbent kernels,
+    momoe_tl.py:90-330) -> weighted unpermute in fp32.  x: [batch, seq, hidden] bf16 or fp16."""
+    _forbid_grad(x, gate_weight, up_weight, down_weight, router_logits)
+    check_momoe(x, gate_weight, up_weight, down_weight, router_logits)
+    experts, hidden, _ = gate_weight.shape
     flat = x.reshape(-1, hidden)
     indices, weights = moe_route(router_logits.reshape(-1, experts).float(), int(top_k))
     rows, _, offsets, _, pos = moe_permute(flat, indices, experts)
