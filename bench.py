@@ -390,8 +390,9 @@ def bench_grouped_gemm(device, sampler, scale: float = 1.0, steps: int = 10, war
     """The expert MLP on the rows of config 5: 65536 tokens x top-8 = 524288 rows of 4096 over 64 experts (8192 rows each
     on average, routed by the config's own seeded logits), SwiGLU MLP with an intermediate size of 1536 per expert.
 
-    Two launches per step: gate/up projection + SwiGLU (2 * rows * 4096 * 3072 flop), down projection
-    (2 * rows * 1536 * 4096 flop).  Tensor-core bound: TFLOP/s against the measured cuBLAS bf16 peak."""
+    Two launches per forward step: gate/up projection + SwiGLU (2 * rows * 4096 * 3072 flop), down projection
+    (2 * rows * 1536 * 4096 flop); then the training launches, each timed on its own: both pre-activations kept,
+    the two row gradients and the weight gradients.  Tensor-core bound: TFLOP/s against the measured cuBLAS bf16 peak."""
     import ctypes
 
     from popcorn_b200 import _lib, ops, workloads
@@ -424,9 +425,37 @@ def bench_grouped_gemm(device, sampler, scale: float = 1.0, steps: int = 10, war
     def down_proj(i):
         check(lib.b200_moe_grouped_gemm(p(act), p(down), ctypes.c_void_p(0), p(offsets), p(out), total, inter, hidden, experts, inter, hidden, _lib.BF16, stream))
 
+    # the training launches: both pre-activations kept, then the gradients (the values of the "gradients" do not
+    # matter for the timing: the finished outputs stand in for them)
+    both = torch.empty(total, 2 * inter, device=device, dtype=torch.bfloat16)
+    grad_act = torch.empty(total, inter, device=device, dtype=torch.bfloat16)
+    grad_rows = torch.empty(total, hidden, device=device, dtype=torch.bfloat16)
+    grad_down = torch.empty_like(down)
+    grad_gate = torch.empty_like(gate)
+    null = ctypes.c_void_p(0)
+    half = ctypes.c_void_p(both.data_ptr() + inter * 2)  # the up half of `both`
+
+    def gate_up_kept(i):
+        check(lib.b200_moe_grouped_gemm_gate_up(p(rows), p(gate), p(up), p(offsets), p(both), total, hidden, inter, experts, hidden, 2 * inter, _lib.BF16, stream))
+
+    def down_dgrad(i):
+        check(lib.b200_moe_grouped_gemm_dgrad(p(out), p(down), null, null, p(offsets), p(grad_act), total, inter, hidden, experts, hidden, inter, _lib.BF16, stream))
+
+    def down_wgrad(i):
+        check(lib.b200_moe_grouped_gemm_wgrad(p(act), p(out), p(offsets), p(grad_down), total, inter, hidden, experts, inter, hidden, _lib.BF16, stream))
+
+    def gate_up_dgrad(i):
+        check(lib.b200_moe_grouped_gemm_dgrad(p(both), p(gate), half, p(up), p(offsets), p(grad_rows), total, hidden, inter, experts, 2 * inter, hidden, _lib.BF16, stream))
+
+    def gate_wgrad(i):
+        check(lib.b200_moe_grouped_gemm_wgrad(p(rows), p(both), p(offsets), p(grad_gate), total, hidden, inter, experts, hidden, 2 * inter, _lib.BF16, stream))
+
     burst, sustained, kind = measured_tensor_peak()
     result = {"rows": total, "hidden": hidden, "intermediate": inter, "experts": experts, "peak_kind": kind}
-    for name, fn, flop in (("gate_up_swiglu", gate_up, 2.0 * total * hidden * 2 * inter), ("down", down_proj, 2.0 * total * inter * hidden)):
+    for name, fn, flop in (("gate_up_swiglu", gate_up, 2.0 * total * hidden * 2 * inter), ("down", down_proj, 2.0 * total * inter * hidden),
+                           ("gate_up_kept", gate_up_kept, 2.0 * total * hidden * 2 * inter), ("down_dgrad", down_dgrad, 2.0 * total * inter * hidden),
+                           ("down_wgrad", down_wgrad, 2.0 * total * inter * hidden), ("gate_up_dgrad", gate_up_dgrad, 2.0 * total * hidden * 2 * inter),
+                           ("gate_wgrad", gate_wgrad, 2.0 * total * hidden * inter)):
         t0 = time.time()
         ms = time_launches(fn, steps, warmup, device)
         if sampler is not None:

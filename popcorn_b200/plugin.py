@@ -30,7 +30,7 @@ BACKEND = "b200"
 EXISTING_OPS = ("rms_norm", "add_rms_norm", "rotary_embedding", "rope", "llama4_rope", "swiglu", "geglu", "rms_norm_gated", "l2_norm", "layer_norm", "momoe")
 NEW_OPS = ("moe_route", "moe_permute", "moe_unpermute", "qk_norm_rope")
 DIFFERENTIABLE_OPS = ("rms_norm", "add_rms_norm", "swiglu", "geglu", "rotary_embedding", "rope", "llama4_rope", "qk_norm_rope", "rms_norm_gated", "l2_norm", "layer_norm",
-                      "moe_route", "moe_permute", "moe_unpermute")
+                      "moe_route", "moe_permute", "moe_unpermute", "momoe")
 
 _SUPPORTED = (torch.float32, torch.float16, torch.bfloat16)
 

@@ -86,16 +86,24 @@ def test_mirror_dispatch_forced_scoped_and_ordered():
 
 
 def test_forward_only_backend_declines_grad():
-    x = torch.ones(8, 8, requires_grad=True)
-    offsets = torch.tensor([0, 8], dtype=torch.int32)
-    with pytest.raises(registry.DispatchError, match="no backward implementation"):
-        kernels.moe_grouped_gemm(x, torch.ones(1, 8, 8), offsets, backend="b200")
-    with pytest.raises(registry.DispatchError, match="no registered backend"):
-        kernels.moe_grouped_gemm(x, torch.ones(1, 8, 8), offsets)
-    for op in (kernels.rms_norm, kernels.add_rms_norm, kernels.swiglu, kernels.geglu, kernels.rotary_embedding, kernels.rope, kernels.llama4_rope,
-               kernels.qk_norm_rope, kernels.l2_norm, kernels.layer_norm, kernels.rms_norm_gated,
-               kernels.moe_route, kernels.moe_permute, kernels.moe_unpermute):
-        assert not op["b200"].forward_only
+    @registry.register_kernel(name="_test_forward_only")
+    def double(x):
+        """Twice x."""
+
+    try:
+        double.register("b200", forward_only=True)(lambda x: x * 2)
+        x = torch.ones(8, requires_grad=True)
+        with pytest.raises(registry.DispatchError, match="no backward implementation"):
+            double(x, backend="b200")
+        with pytest.raises(registry.DispatchError, match="no registered backend"):
+            double(x)
+        assert torch.equal(double(x.detach()), torch.full((8,), 2.0))
+    finally:
+        del registry.KERNELS["_test_forward_only"]
+    # every op of the backend has backward kernels and serves training calls
+    for name in ("rms_norm", "add_rms_norm", "swiglu", "geglu", "rotary_embedding", "rope", "llama4_rope", "qk_norm_rope", "l2_norm", "layer_norm",
+                 "rms_norm_gated", "moe_route", "moe_permute", "moe_unpermute", "moe_grouped_gemm", "momoe"):
+        assert not registry.KERNELS[name]["b200"].forward_only
 
 
 def test_workload_shapes_and_bytes():
@@ -150,10 +158,9 @@ def test_plugin_registers_on_real_popcorn(tmp_path, monkeypatch):
         impl = popcorn.KERNELS[name]["b200"]
         impl._prepare()  # the bare source must accept the reference's parameters positionally
         assert impl.source_fn is getattr(differentiable, name)
-    for name in ("momoe",):
-        impl = popcorn.KERNELS[name]["b200"]
-        impl._prepare()
-        assert impl.source_fn is getattr(ops, name)
+    impl = popcorn.KERNELS["momoe"]["b200"]
+    impl._prepare()
+    assert impl.source_fn is differentiable.momoe
     # momoe is served for 16-bit activations only (tensor-core operands)
     assert not plugin.accepts_16bit(x=torch.zeros(1, 2, 8), gate_weight=torch.zeros(2, 8, 8))
     # CPU calls are declined by the predicate rather than served by a fallback
