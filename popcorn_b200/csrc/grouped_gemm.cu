@@ -3,8 +3,12 @@
 //   out[p, :] = rows[p, :] @ weight[e(p)]            (one weight matrix per expert)
 //   out[p, :] = (rows[p, :] @ up[e]) * silu(rows[p, :] @ gate[e])   (DUAL: both projections and SwiGLU in one pass)
 //
+//   grad_rows[p, :] = grad_out[p, :] @ weight[e(p)]^T (+ a second pair)   (the weight read along its rows, in place)
+//   grad_weight[e]  = rows[segment e]^T @ grad_out[segment e]             (contraction over the expert's rows)
+//
 // where e(p) is the expert whose segment offsets[e] <= p < offsets[e + 1] holds row p of the
-// expert-major `rows` buffer that b200_moe_permute writes.  This is what the reference's
+// expert-major `rows` buffer that b200_moe_permute writes.  The gradients differ from the forward only in how
+// the operands lie in shared memory (enum Mode below); roles, ring and accumulators are the same.  This is what the reference's
 // lin1_kernel / lin2_kernel compute (src/popcorn/impls/momoe_tl.py:90-212 and 225-330) and what the
 // registered reference states as two einsums over a dense [batch, seq, experts, .] tensor
 // (src/popcorn/kernels/momoe.py:50-52); weights keep the reference's layout
