@@ -222,11 +222,15 @@ class ExpertParallel:
         self._order_ranks()  # every rank's expert outputs are complete
         return self.ops.moe_unpermute_multi(out_ptrs, state.dst_rank, state.dst_row, state.weights, hidden, dtype)
 
-    def dispatch(self, x: Tensor, router_logits: Tensor) -> Dispatched:
+    def dispatch(self, x: Tensor, router_logits: Tensor, routing: tuple[Tensor, Tensor] | None = None) -> Dispatched:
+        """Route, exchange, reorder.  `routing` = (indices, weights) computed by the caller replaces the routing step
+        (training calls pass weights that carry a gradient path to the logits); exchange="nccl" only."""
         if self.exchange == "p2p":
+            if routing is not None:
+                raise ValueError("precomputed routing is only taken by exchange='nccl'")
             return self._dispatch_p2p(x, router_logits)
         ops = self.ops
-        indices, weights = ops.moe_route(router_logits, self.top_k)
+        indices, weights = routing if routing is not None else ops.moe_route(router_logits, self.top_k)
         counts, _, _, pos = ops.moe_index(indices, self.experts)
         # metadata exchange: every rank's per-expert counts
         gathered = torch.empty(self.world * self.experts, dtype=torch.int32, device=counts.device)
@@ -241,17 +245,43 @@ class ExpertParallel:
         rows = ops.moe_gather(arrived, reorder)
         return Dispatched(rows, expert_offsets, weights, pos, send_counts, recv_counts, reorder, counts_all)
 
-    def combine(self, expert_rows: Tensor, state: Dispatched) -> Tensor:
-        if self.exchange == "p2p":
-            return self._combine_p2p(expert_rows, state)
-        ops = self.ops
+    def _deliver(self, send: Tensor, state: Dispatched) -> Tensor:
+        """Rows in this rank's send order -> the expert owners, in (expert, source rank, token) order (exchange="nccl")."""
+        arrived = torch.empty((sum(state.recv_counts), send.shape[1]), dtype=send.dtype, device=send.device)
+        dist.all_to_all_single(arrived, send, state.recv_counts, state.send_counts, group=self.group)
+        return self.ops.moe_gather(arrived, state.reorder)
+
+    def _return(self, expert_rows: Tensor, state: Dispatched) -> Tensor:
+        """The mirror image: expert-major rows back to the ranks they came from, in those ranks' send order."""
         total = expert_rows.shape[0]
         inverse = torch.empty(total, dtype=torch.int32, device=expert_rows.device)
         inverse[state.reorder.long()] = torch.arange(total, dtype=torch.int32, device=expert_rows.device)
-        outbound = ops.moe_gather(expert_rows, inverse)  # back to (source rank, expert, token)
+        outbound = self.ops.moe_gather(expert_rows, inverse)  # back to (source rank, expert, token)
         returned = torch.empty((sum(state.send_counts), expert_rows.shape[1]), dtype=expert_rows.dtype, device=expert_rows.device)
         dist.all_to_all_single(returned, outbound, state.send_counts, state.recv_counts, group=self.group)
-        return ops.moe_unpermute(returned, state.weights, state.pos)
+        return returned
+
+    def combine(self, expert_rows: Tensor, state: Dispatched) -> Tensor:
+        if self.exchange == "p2p":
+            return self._combine_p2p(expert_rows, state)
+        return self.ops.moe_unpermute(self._return(expert_rows, state), state.weights, state.pos)
+
+    # -- training calls (exchange="nccl"): the two exchanges are each other's transposes ------------------------------
+
+    def rows_with_grad(self, x: Tensor, state: Dispatched) -> Tensor:
+        """`state.rows` with a gradient path back to `x` (the tokens `state` was dispatched from): the gradient rows
+        travel back through the combine exchange and are summed per token with unit weights."""
+        self._require_nccl()
+        return _DispatchedRows.apply(x, self, state)
+
+    def combine_with_grad(self, expert_rows: Tensor, weights: Tensor, state: Dispatched) -> Tensor:
+        """combine() with gradients for the expert rows (delivered through the dispatch exchange) and the gate weights."""
+        self._require_nccl()
+        return _CombinedRows.apply(expert_rows, weights, self, state)
+
+    def _require_nccl(self) -> None:
+        if self.exchange != "nccl":
+            raise NotImplementedError("training calls go through exchange='nccl'; the fused peer-memory exchange is inference-only")
 
     def momoe(self, x: Tensor, router_logits: Tensor, gate_weight: Tensor, up_weight: Tensor, down_weight: Tensor) -> Tensor:
         """The whole expert-parallel MoE layer for this rank's tokens: dispatch, the SwiGLU expert MLPs of this rank's
@@ -262,8 +292,60 @@ class ExpertParallel:
         symmetric buffer the peers combine from."""
         if gate_weight.shape[0] != self.local_experts:
             raise ValueError(f"expected the weights of this rank's {self.local_experts} experts, got {gate_weight.shape[0]}")
+        if torch.is_grad_enabled() and any(t.requires_grad for t in (x, router_logits, gate_weight, up_weight, down_weight)):
+            return self._momoe_with_grad(x, router_logits, gate_weight, up_weight, down_weight)
         state = self.dispatch(x, router_logits)
         offsets = state.expert_offsets.to(x.device, non_blocking=True)
         hidden_act = self.ops.moe_grouped_gemm(state.rows, gate_weight, offsets, up_weight)
         expert_rows = self.ops.moe_grouped_gemm(hidden_act, down_weight, offsets, None, state.out_rows)
         return self.combine(expert_rows, state)
+
+    def _momoe_with_grad(self, x: Tensor, router_logits: Tensor, gate_weight: Tensor, up_weight: Tensor, down_weight: Tensor) -> Tensor:
+        """The same layer for a training call: gradients for the local tokens, their router logits and this rank's expert
+        weights (which collect the contributions of every rank's tokens, since the rows were exchanged).  Every rank
+        must call backward: the gradient rows cross the same two exchanges in the opposite direction."""
+        from popcorn_b200 import autograd as differentiable
+
+        self._require_nccl()
+        indices, weights = differentiable.moe_route(router_logits.float(), self.top_k)
+        state = self.dispatch(x.detach(), router_logits.detach(), routing=(indices, weights.detach()))
+        rows = self.rows_with_grad(x, state)
+        offsets = state.expert_offsets.to(x.device, non_blocking=True)
+        hidden_act = differentiable.moe_grouped_gemm(rows, gate_weight, offsets, up_weight)
+        expert_rows = differentiable.moe_grouped_gemm(hidden_act, down_weight, offsets)
+        return self.combine_with_grad(expert_rows, weights, state)
+
+
+class _DispatchedRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: Tensor, ep: ExpertParallel, state: Dispatched) -> Tensor:
+        ctx.ep, ctx.state = ep, state
+        return state.rows.view_as(state.rows)
+
+    @staticmethod
+    def backward(ctx, grad_rows: Tensor):
+        ep, state = ctx.ep, ctx.state
+        with torch.no_grad():
+            returned = ep._return(grad_rows.contiguous(), state)
+            grad_x = ep.ops.moe_unpermute(returned, torch.ones_like(state.weights), state.pos)
+        return grad_x, None, None
+
+
+class _CombinedRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, expert_rows: Tensor, weights: Tensor, ep: ExpertParallel, state: Dispatched) -> Tensor:
+        with torch.no_grad():
+            returned = ep._return(expert_rows, state)
+            y = ep.ops.moe_unpermute(returned, weights, state.pos)
+        ctx.ep, ctx.state = ep, state
+        ctx.save_for_backward(returned, weights)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_y: Tensor):
+        ep, state = ctx.ep, ctx.state
+        returned, weights = ctx.saved_tensors
+        with torch.no_grad():
+            grad_returned, grad_weights = ep.ops.moe_unpermute_backward(grad_y.contiguous(), returned, weights, state.pos)
+            grad_expert_rows = ep._deliver(grad_returned, state)
+        return grad_expert_rows, grad_weights, None, None

@@ -220,3 +220,72 @@ def test_every_rank_derives_the_same_receive_sizes():
     out = mp.Manager().dict()
     mp.spawn(_capacity_worker, args=(2, _free_port(), out), nprocs=2, join=True)
     assert out[0] == out[1] == [65, 1]
+
+
+def _cpu_unpermute_backward(grad_y, rows, weights, pos):
+    """(grad_rows, grad_weights) by autograd through the oracle's combine: the CPU stand-in of the backward kernel."""
+    rows_leaf, weights_leaf = rows.detach().clone().requires_grad_(), weights.detach().clone().requires_grad_()
+    with torch.enable_grad():
+        oracle.moe_unpermute(rows_leaf, weights_leaf, pos).backward(grad_y)
+    return rows_leaf.grad, weights_leaf.grad
+
+
+CPU_TRAINING_OPS = types.SimpleNamespace(**vars(CPU_OPS), moe_unpermute_backward=_cpu_unpermute_backward)
+
+
+def _expert_scale(offsets, first_expert):
+    scale = torch.ones(int(offsets[-1]))
+    for e in range(len(offsets) - 1):
+        scale[int(offsets[e]):int(offsets[e + 1])] = 1 + (first_expert + e) / 8
+    return scale[:, None]
+
+
+def _grad_worker(rank, world, port, tokens, hidden, experts, top_k, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        x, logits = _inputs(tokens, hidden, experts)
+        grad_y, _ = _inputs(tokens, hidden, experts, seed=12)
+        lo, hi = tokens * rank // world, tokens * (rank + 1) // world
+        ep = ExpertParallel(experts, top_k, local_ops=CPU_TRAINING_OPS)
+        mine = x[lo:hi].clone().requires_grad_()
+        state = ep.dispatch(mine.detach(), logits[lo:hi])
+        weights = state.weights.clone().requires_grad_()
+        rows = ep.rows_with_grad(mine, state)
+        processed = (rows.float() * _expert_scale(state.expert_offsets, rank * ep.local_experts)).to(torch.bfloat16)
+        ep.combine_with_grad(processed, weights, state).backward(grad_y[lo:hi])
+        out[rank] = (mine.grad, weights.grad)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,tokens,experts,top_k", [(2, 64, 8, 2), (2, 37, 4, 3), (4, 50, 8, 4), (2, 16, 2, 1)])
+def test_gradients_cross_the_exchanges_in_reverse(world, tokens, experts, top_k):
+    """rows_with_grad / combine_with_grad: each exchange's backward is the other exchange; token and gate-weight
+    gradients equal autograd through the single-process chain."""
+    hidden = 24
+    out = mp.Manager().dict()
+    mp.spawn(_grad_worker, args=(world, _free_port(), tokens, hidden, experts, top_k, out), nprocs=world, join=True)
+
+    x, logits = _inputs(tokens, hidden, experts)
+    grad_y, _ = _inputs(tokens, hidden, experts, seed=12)
+    indices, weights = oracle.moe_route(logits, top_k)
+    x_leaf, w_leaf = x.clone().requires_grad_(), weights.clone().requires_grad_()
+    rows, _, offsets, _, pos = oracle.moe_permute(x_leaf, indices, experts)
+    processed = (rows.float() * _expert_scale(offsets, 0)).to(torch.bfloat16)
+    oracle.moe_unpermute(processed, w_leaf, pos).backward(grad_y)
+    got_x = torch.cat([out[rank][0] for rank in range(world)])
+    got_w = torch.cat([out[rank][1] for rank in range(world)])
+    assert torch.equal(got_w, w_leaf.grad)
+    # the distributed path sums a token's top_k gradient rows in fp32 and rounds once; torch's index_select backward
+    # accumulates in bf16, which is the same number for up to two rows
+    if top_k <= 2:
+        assert torch.equal(got_x, x_leaf.grad)
+    assert float((got_x.float() - x_leaf.grad.float()).abs().max()) <= 2e-2 * max(1.0, float(x_leaf.grad.abs().max()))
+
+
+def test_training_calls_need_the_nccl_exchange():
+    ep = ExpertParallel.__new__(ExpertParallel)
+    ep.exchange = "p2p"
+    with pytest.raises(NotImplementedError, match="inference-only"):
+        ep._require_nccl()

@@ -114,3 +114,54 @@ def test_whole_moe_layer_on_two_gpus(exchange):
     assert got.shape == want.shape
     assert float((got.float() - want.float()).abs().max()) <= 2e-2
     assert float((got == want).float().mean()) > 0.97
+
+
+def _training_worker(rank, world, port, tokens, hidden, inter, experts, top_k, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    device = torch.device("cuda", rank)
+    torch.cuda.set_device(device)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        from popcorn_b200.expert_parallel import ExpertParallel
+
+        x, logits = _inputs(tokens, hidden, experts)
+        grad_y, _ = _inputs(tokens, hidden, experts)
+        gate, up, down = _mlp_weights(experts, hidden, inter)
+        lo, hi = tokens * rank // world, tokens * (rank + 1) // world
+        per = experts // world
+        mine = slice(rank * per, (rank + 1) * per)
+        leaves = [t.to(device).requires_grad_() for t in (x[lo:hi], logits[lo:hi], gate[mine], up[mine], down[mine])]
+        ep = ExpertParallel(experts, top_k, exchange="nccl")
+        y = ep.momoe(*leaves)
+        y.backward(grad_y[lo:hi].flip(0).to(device))
+        torch.cuda.synchronize(device)
+        out[rank] = (y.detach().cpu(), *[t.grad.cpu() for t in leaves])
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_whole_moe_layer_trains_on_two_gpus():
+    """Gradients of the sharded layer (tokens, router logits, each rank's expert weights) equal the single-device
+    `autograd.momoe` gradients: the rows reach the experts in the same global order, so even the weight gradients,
+    contracted over rows that came from both ranks, are the same sums."""
+    from popcorn_b200 import autograd as differentiable
+
+    world, tokens, hidden, inter, experts, top_k = 2, 1024, 256, 128, 8, 2
+    out = mp.Manager().dict()
+    mp.spawn(_training_worker, args=(world, _free_port(), tokens, hidden, inter, experts, top_k, out), nprocs=world, join=True)
+    x, logits = _inputs(tokens, hidden, experts)
+    grad_y, _ = _inputs(tokens, hidden, experts)
+    gate, up, down = _mlp_weights(experts, hidden, inter)
+    half = tokens // world
+    grad_y = torch.cat([grad_y[r * half:(r + 1) * half].flip(0) for r in range(world)])
+    leaves = [t.cuda().requires_grad_() for t in (x, gate, up, down, logits)]
+    y = differentiable.momoe(*leaves, top_k)
+    y.backward(grad_y.cuda())
+    want_x, want_gate, want_up, want_down, want_logits = (t.grad.cpu() for t in leaves)
+    assert torch.equal(torch.cat([out[r][0] for r in range(world)]), y.detach().cpu())
+    assert torch.equal(torch.cat([out[r][1] for r in range(world)]), want_x)
+    assert torch.equal(torch.cat([out[r][2] for r in range(world)]), want_logits)
+    assert torch.equal(torch.cat([out[r][3] for r in range(world)]), want_gate)
+    assert torch.equal(torch.cat([out[r][4] for r in range(world)]), want_up)
+    assert torch.equal(torch.cat([out[r][5] for r in range(world)]), want_down)
