@@ -320,6 +320,18 @@ int b200_geglu_backward(const void* grad_out, const void* a, const void* b, void
                         int64_t ldda, int64_t lddb, int dtype, void* stream);
 
 /*
+ * Backward of out = sigmoid(a) * b, same shapes as b200_swiglu_backward:
+ * grad_b = round_T(g * s), grad_a = round_T((round_T(g*b) * (1 - s)) * s) with s = round_T(sigmoid(a)), the
+ * sequence of PyTorch's sigmoid backward on the saved 16-bit gate.
+ *
+ * Replaces what autograd derives from the sigmoid branch of the gated RMS norm, out * torch.sigmoid(g),
+ * src/popcorn/kernels/rms_norm_gated.py:29 (a = g, b = the normalised, scaled row).
+ */
+int b200_sigmoid_gate_backward(const void* grad_out, const void* a, const void* b, void* grad_a, void* grad_b,
+                               int64_t rows, int64_t cols, int64_t ldg, int64_t lda, int64_t ldb,
+                               int64_t ldda, int64_t lddb, int dtype, void* stream);
+
+/*
  * MoE routing: probs = softmax(fp32(logits)) over experts; the top_k largest
  * (descending, ties to the lower expert index); weights = picked / sum(picked).
  *

@@ -53,6 +53,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "b200_layer_norm_backward": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _int, _dbl, _ptr, _size, _ptr]),
     "b200_swiglu_backward": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _int, _ptr]),
     "b200_geglu_backward": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _int, _ptr]),
+    "b200_sigmoid_gate_backward": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _int, _ptr]),
     "b200_moe_route": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _int, _ptr]),
     "b200_moe_index_scratch_bytes": (_int, [_i64, _i64, _i64, ctypes.POINTER(_size)]),
     "b200_moe_index": (_int, [_ptr, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _size, _ptr]),

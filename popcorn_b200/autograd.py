@@ -81,26 +81,28 @@ class _QkNormRope(torch.autograd.Function):
         return dq, dk, dqw, dkw, None, None, None
 
 
-class _RmsNormGatedSwish(torch.autograd.Function):
-    """out = z * silu(g), z = rms_norm(x, weight, bias).  The backward is a composition of kernels that exist:
-    swiglu_backward(grad_out, g, z) yields (grad_g, grad_z) with autograd's roundings, and rms_norm_backward turns
-    grad_z into the gradients of x, weight and bias; z is recomputed by the forward norm kernel, not saved."""
+class _RmsNormGated(torch.autograd.Function):
+    """out = z * gate(g), z = rms_norm(x, weight, bias), gate = silu or sigmoid.  The backward is a composition of kernels
+    that exist: the gate backward (swiglu_backward or sigmoid_gate_backward on (grad_out, g, z)) yields (grad_g, grad_z)
+    with autograd's roundings, and rms_norm_backward turns grad_z into the gradients of x, weight and bias; z is
+    recomputed by the forward norm kernel, not saved."""
 
     @staticmethod
-    def forward(ctx, x: Tensor, g: Tensor, weight: Tensor, bias: Tensor | None, eps: float) -> Tensor:
+    def forward(ctx, x: Tensor, g: Tensor, weight: Tensor, bias: Tensor | None, activation: str, eps: float) -> Tensor:
         ctx.save_for_backward(x, g, weight, bias)
-        ctx.eps = eps
+        ctx.eps, ctx.activation = eps, activation
         with torch.no_grad():
-            return ops.rms_norm_gated(x, g, weight, bias, "swish", eps)
+            return ops.rms_norm_gated(x, g, weight, bias, activation, eps)
 
     @staticmethod
     def backward(ctx, grad_out: Tensor):
         x, g, weight, bias = ctx.saved_tensors
+        gate_backward = ops.swiglu_backward if ctx.activation == "swish" else ops.sigmoid_gate_backward
         with torch.no_grad():
             z = ops.rms_norm(x, weight, bias, ctx.eps)
-            grad_g, grad_z = ops.swiglu_backward(grad_out.contiguous(), g, z)
+            grad_g, grad_z = gate_backward(grad_out.contiguous(), g, z)
             grad_x, grad_w, grad_b = ops.rms_norm_backward(grad_z, x, weight, bias is not None, ctx.eps)
-        return grad_x, grad_g, grad_w, grad_b, None
+        return grad_x, grad_g, grad_w, grad_b, None, None
 
 
 class _L2Norm(torch.autograd.Function):
@@ -350,10 +352,10 @@ def qk_norm_rope(q: Tensor, k: Tensor, q_weight: Tensor, k_weight: Tensor, cos: 
 
 
 def rms_norm_gated(x: Tensor, g: Tensor, weight: Tensor, bias: Tensor | None = None, activation: str = "swish", eps: float = 1e-6) -> Tensor:
-    """Gated RMS norm; with the swish gate, gradients for x, g, weight and bias (the sigmoid gate is forward-only)."""
-    if activation != "swish":
-        return ops.rms_norm_gated(x, g, weight, bias, activation, eps)
-    return _RmsNormGatedSwish.apply(x, g, weight, bias, eps)
+    """Gated RMS norm (swish or sigmoid gate) with gradients for x, g, weight and bias."""
+    if activation not in ("swish", "sigmoid"):
+        raise ValueError(f"rms_norm_gated: activation must be 'swish' or 'sigmoid', got {activation!r}")
+    return _RmsNormGated.apply(x, g, weight, bias, activation, eps)
 
 
 def l2_norm(x: Tensor, eps: float = 1e-6) -> Tensor:

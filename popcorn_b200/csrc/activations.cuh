@@ -48,7 +48,7 @@ __device__ __forceinline__ float exp_neg(float a) {
 }
 // Argument t of the gate x / (1 + exp(-t)): t = x gives silu(x); t = 2*sqrt(2/pi)*(x + 0.044715*x^3)
 // gives the tanh-approximate gelu, since 0.5*(1 + tanh(u)) = 1 / (1 + exp(-2u)).
-enum Act { kSilu = 0, kGeluTanh = 1 };
+enum Act { kSilu = 0, kGeluTanh = 1, kSigmoidGate = 2 };  // kSigmoidGate: the gate is sigmoid(x) itself, not x * sigmoid(t)
 template <int ACT>
 __device__ __forceinline__ float gate_argument(float x) {
   if constexpr (ACT == kSilu) {

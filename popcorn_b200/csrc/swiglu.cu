@@ -107,6 +107,20 @@ __device__ __forceinline__ float dsilu_f32(float a) {
   }
 }
 
+// The gate's value as the forward computes it, and the gradient of out = gate(a) * b with respect to a, given
+// gs = grad * b rounded to T and s = gate(a) rounded to T (what autograd keeps).  For the sigmoid gate PyTorch's
+// sigmoid backward evaluates (gs * (1 - s)) * s on the ROUNDED s; the other gates differentiate the fp32 value.
+template <int MATH, int ACT>
+__device__ __forceinline__ float gate_value(float a) {
+  if constexpr (ACT == kSigmoidGate) return sigmoid_f32<MATH>(a);
+  else return silu_f32<MATH, ACT>(a);
+}
+template <int MATH, int ACT>
+__device__ __forceinline__ float gate_grad(float gs, float s, float a) {
+  if constexpr (ACT == kSigmoidGate) return __fmul_rn(__fmul_rn(gs, __fsub_rn(1.0f, s)), s);
+  else return __fmul_rn(gs, dsilu_f32<MATH, ACT>(a));
+}
+
 template <typename T, int UNROLL, typename Index, int MATH, int ACT>
 __global__ void __launch_bounds__(256)
 swiglu_bwd_vec_kernel(const T* g, const T* a, const T* b, T* da, T* db, Index total_words, Index words_per_row,
@@ -142,10 +156,10 @@ swiglu_bwd_vec_kernel(const T* g, const T* a, const T* b, T* da, T* db, Index to
     Num<T>::unpack(vb[u], fb);
 #pragma unroll
     for (int j = 0; j < V; ++j) {
-      const float s = Num<T>::rt(silu_f32<MATH, ACT>(fa[j]));
+      const float s = Num<T>::rt(gate_value<MATH, ACT>(fa[j]));
       rb[j] = __fmul_rn(fg[j], s);
       const float gs = Num<T>::rt(__fmul_rn(fg[j], fb[j]));
-      ra[j] = __fmul_rn(gs, dsilu_f32<MATH, ACT>(fa[j]));
+      ra[j] = gate_grad<MATH, ACT>(gs, s, fa[j]);
     }
     if (ok[u]) {
       st_stream(da + off_da[u], Num<T>::pack(ra));
@@ -164,8 +178,9 @@ swiglu_bwd_scalar_kernel(const T* g, const T* a, const T* b, T* da, T* db, int64
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t r = i / cols, c = i - r * cols;
     const float fg = Num<T>::up(g[r * ldg + c]), fa = Num<T>::up(a[r * lda + c]), fb = Num<T>::up(b[r * ldb + c]);
-    db[r * lddb + c] = Num<T>::down(__fmul_rn(fg, Num<T>::rt(silu_f32<0, ACT>(fa))));
-    da[r * ldda + c] = Num<T>::down(__fmul_rn(Num<T>::rt(__fmul_rn(fg, fb)), dsilu_f32<0, ACT>(fa)));
+    const float s = Num<T>::rt(gate_value<0, ACT>(fa));
+    db[r * lddb + c] = Num<T>::down(__fmul_rn(fg, s));
+    da[r * ldda + c] = Num<T>::down(gate_grad<0, ACT>(Num<T>::rt(__fmul_rn(fg, fb)), s, fa));
   }
 }
 
@@ -297,6 +312,8 @@ int gate_backward(const char* fn, int act, const void* grad_out, const void* a, 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (act == kSilu) {
     B200_DISPATCH_DTYPE(dtype, T, return (run_bwd<T, kSilu>(grad_out, a, b, grad_a, grad_b, rows, cols, ldg, lda, ldb, ldda, lddb, st)));
+  } else if (act == kSigmoidGate) {
+    B200_DISPATCH_DTYPE(dtype, T, return (run_bwd<T, kSigmoidGate>(grad_out, a, b, grad_a, grad_b, rows, cols, ldg, lda, ldb, ldda, lddb, st)));
   } else {
     B200_DISPATCH_DTYPE(dtype, T, return (run_bwd<T, kGeluTanh>(grad_out, a, b, grad_a, grad_b, rows, cols, ldg, lda, ldb, ldda, lddb, st)));
   }
@@ -315,4 +332,10 @@ extern "C" int b200_geglu_backward(const void* grad_out, const void* a, const vo
                                    int64_t rows, int64_t cols, int64_t ldg, int64_t lda, int64_t ldb,
                                    int64_t ldda, int64_t lddb, int dtype, void* stream) {
   return gate_backward(__func__, kGeluTanh, grad_out, a, b, grad_a, grad_b, rows, cols, ldg, lda, ldb, ldda, lddb, dtype, stream);
+}
+
+extern "C" int b200_sigmoid_gate_backward(const void* grad_out, const void* a, const void* b, void* grad_a, void* grad_b,
+                                          int64_t rows, int64_t cols, int64_t ldg, int64_t lda, int64_t ldb,
+                                          int64_t ldda, int64_t lddb, int dtype, void* stream) {
+  return gate_backward(__func__, kSigmoidGate, grad_out, a, b, grad_a, grad_b, rows, cols, ldg, lda, ldb, ldda, lddb, dtype, stream);
 }

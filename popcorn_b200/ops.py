@@ -505,6 +505,11 @@ def geglu_backward(grad_out: Tensor, a: Tensor, b: Tensor) -> tuple[Tensor, Tens
     return _gate_backward("b200_geglu_backward", grad_out, a, b)
 
 
+def sigmoid_gate_backward(grad_out: Tensor, a: Tensor, b: Tensor) -> tuple[Tensor, Tensor]:
+    """Gradients of sigmoid(a) * b with respect to a and b (the sigmoid gate of rms_norm_gated.py:29)."""
+    return _gate_backward("b200_sigmoid_gate_backward", grad_out, a, b)
+
+
 def _gate_backward(entry: str, grad_out: Tensor, a: Tensor, b: Tensor) -> tuple[Tensor, Tensor]:
     device = _require_cuda(grad_out, a, b)
     code = _dtype_code(a, entry)

@@ -52,15 +52,7 @@ def accepts_16bit(**arguments: Any) -> bool:
     return all(t.dtype == x.dtype for name, t in arguments.items() if isinstance(t, Tensor) and name.endswith("_weight"))
 
 
-def accepts_gated(**arguments: Any) -> bool:
-    """`accepts`, except training calls with the sigmoid gate: only the swish gate has a backward."""
-    if not accepts(**arguments):
-        return False
-    needs_grad = torch.is_grad_enabled() and any(isinstance(v, Tensor) and v.requires_grad for v in arguments.values())
-    return arguments.get("activation", "swish") == "swish" or not needs_grad
-
-
-PREDICATES = {"momoe": accepts_16bit, "rms_norm_gated": accepts_gated}
+PREDICATES = {"momoe": accepts_16bit}
 
 
 def _define_moe_ops(popcorn: Any) -> None:

@@ -163,23 +163,23 @@ def test_qk_norm_rope_backward(batch, hq, hk, seq, dim, dtype):
 
 @pytest.mark.parametrize("rows,cols,dtype", [(33, 256, torch.bfloat16), (40, 4096, torch.bfloat16), (9, 100, torch.float32), (6, 33, torch.bfloat16), (130, 2048, torch.float16)])
 @pytest.mark.parametrize("with_bias", [False, True])
-def test_rms_norm_gated_swish_backward(rows, cols, dtype, with_bias):
+@pytest.mark.parametrize("activation", ["swish", "sigmoid"])
+def test_rms_norm_gated_backward(rows, cols, dtype, with_bias, activation):
     x, gate = randn(2300 + cols, rows, cols, dtype=dtype), randn(2301 + cols, rows, cols, dtype=dtype, scale=2.0)
     w = (1 + 0.1 * randn(2302, cols)).to(dtype)
     b = randn(2303, cols, dtype=dtype) if with_bias else None
     grad = randn(2304 + cols, rows, cols, dtype=dtype)
     tensors = (x, gate, w, b) if with_bias else (x, gate, w)
     leaves = [t.to(DEV).requires_grad_(True) for t in tensors]
-    y = diff.rms_norm_gated(leaves[0], leaves[1], leaves[2], leaves[3] if with_bias else None, "swish", 1e-5)
+    y = diff.rms_norm_gated(leaves[0], leaves[1], leaves[2], leaves[3] if with_bias else None, activation, 1e-5)
     grads = torch.autograd.grad(y, leaves, grad.to(DEV))
-    fn = (lambda x_, g_, w_, b_: oracle.rms_norm_gated(x_, g_, w_, b_, "swish", 1e-5)) if with_bias else (lambda x_, g_, w_: oracle.rms_norm_gated(x_, g_, w_, None, "swish", 1e-5))
+    fn = (lambda x_, g_, w_, b_: oracle.rms_norm_gated(x_, g_, w_, b_, activation, 1e-5)) if with_bias else (lambda x_, g_, w_: oracle.rms_norm_gated(x_, g_, w_, None, activation, 1e-5))
     native = oracle_grads(fn, tensors, grad)
     truth = oracle_grads(fn, tensors, grad, wide=True)
     for name, mine, nat, tru in zip(("grad_x", "grad_gate", "grad_weight", "grad_bias"), grads, native, truth):
         grade(mine, nat, tru, dtype, f"{name} {rows}x{cols}")
-    # the sigmoid gate stays forward-only
-    with pytest.raises(RuntimeError):
-        diff.rms_norm_gated(leaves[0], leaves[1], leaves[2], None, "sigmoid", 1e-5)
+    with pytest.raises(ValueError):
+        diff.rms_norm_gated(leaves[0], leaves[1], leaves[2], None, "tanh", 1e-5)
 
 
 @pytest.mark.parametrize("rows,cols,dtype", NORM_BWD_SHAPES)
