@@ -475,6 +475,27 @@ def bench_grouped_gemm(device, sampler, scale: float = 1.0, steps: int = 10, war
                                ("cublas_bmm_down", lambda i: torch.bmm(act3, down), 2.0 * total * inter * hidden)):
             ms = time_launches(fn, steps, warmup, device)
             result[name] = {"ms": round(ms, 4), "tflop_s": round(flop / (ms * 1e-3) / 1e12, 1)}
+    # the whole layer through the registered op: inference (route, permute, two launches, unpermute) and a training
+    # step (forward with the pre-activations kept, then every gradient: tokens, router logits, three weight tensors)
+    del both, grad_act, grad_rows, grad_down, grad_gate, act, out, rows
+    torch.cuda.empty_cache()
+    from popcorn_b200 import autograd as differentiable
+
+    w = workloads.moe_bf16(scale=scale).to(device)
+    x, logits = w.inputs["x"], w.inputs["router_logits"]
+    layer_flop = 3 * 2.0 * total * hidden * inter
+    ms = time_launches(lambda i: ops.momoe(x, gate, up, down, logits, top_k), steps, warmup, device)
+    result["layer_forward"] = {"ms": round(ms, 4), "tflop_s": round(layer_flop / (ms * 1e-3) / 1e12, 1), "flop": layer_flop}
+    leaves = [t.detach().requires_grad_() for t in (x, gate, up, down, logits)]
+    grad_y = torch.ones_like(x)
+
+    def train_step(i):
+        for leaf in leaves:
+            leaf.grad = None
+        differentiable.momoe(*leaves, top_k).backward(grad_y)
+
+    ms = time_launches(train_step, steps, warmup, device)
+    result["layer_forward_backward"] = {"ms": round(ms, 4), "tflop_s": round(3 * layer_flop / (ms * 1e-3) / 1e12, 1), "flop": 3 * layer_flop}
     return result
 
 
