@@ -266,6 +266,7 @@ def torch_eager_incumbent(device, per_op: dict, records_root: str | None) -> Non
     `records_root` is given, writes popcorn report rows (schema 3) for the configurations popcorn can
     represent as a case, with error gauges measured against an fp64 evaluation on a 512-token sample."""
     from oracle import reference_ops as reference
+    from popcorn_b200 import autograd as differentiable
     from popcorn_b200 import ops, records, workloads
 
     def timed(fn, reps=10):
@@ -307,8 +308,45 @@ def torch_eager_incumbent(device, per_op: dict, records_root: str | None) -> Non
             wide = {k: v.double() for k, v in sample.items()}
             mine, native, truth = call(ops, sample), call(reference, sample), call(reference, wide)
             gauges = {str(n): gauge(m, nat, tr) for n, (m, nat, tr) in enumerate(zip(mine, native, truth))}
+            status, reason = records.grade(config["dtype"], gauges)
             rows.append(records.make_row(op_name, config, device=torch.cuda.get_device_name(device), torch_version=torch.__version__,
-                                         fwd_ms=per_op[key]["ms"], ref_fwd_ms=eager_ms, gauges=gauges, reps=per_op[key]["steps"]))
+                                         fwd_ms=per_op[key]["ms"], ref_fwd_ms=eager_ms, gauges=gauges, reps=per_op[key]["steps"],
+                                         status=status, reason=reason))
+            # the training-call row of the same case: forward with gradients enabled, the backward pass alone
+            # (bench/compare.py:135-174), and gradient gauges named after the op's parameters, on the sample
+            if key == "swiglu_bf16":
+                named = lambda t: {"a": t["gate_up"][:, :c], "b": t["gate_up"][:, c:]}  # noqa: E731
+                grad_call = lambda f, t: (f.swiglu(t["a"], t["b"]),)  # noqa: E731
+            else:
+                named, grad_call = (lambda t: t), call
+
+            def leaves_of(tensors, cast=lambda t: t):
+                return {k: cast(v).detach().clone().requires_grad_() for k, v in named(tensors).items()}
+
+            def passes(f, tensors):
+                held = leaves_of(tensors)
+                fwd = timed(lambda: grad_call(f, held))
+                outs = grad_call(f, held)
+                seeds = [torch.ones_like(o) for o in outs]
+                bwd = timed(lambda: torch.autograd.grad(outs, list(held.values()), seeds, retain_graph=True, allow_unused=True))
+                return fwd, bwd
+
+            def grads_of(f, tensors, cast=lambda t: t):
+                held = leaves_of(tensors, cast)
+                outs = grad_call(f, held)
+                found = torch.autograd.grad(outs, list(held.values()), [torch.ones_like(o) for o in outs], allow_unused=True)
+                return dict(zip(held, found))
+
+            fwd_ms, bwd_ms = passes(differentiable, i)
+            ref_fwd_ms, ref_bwd_ms = passes(reference, i)
+            mine_g, native_g, truth_g = grads_of(differentiable, sample), grads_of(reference, sample), grads_of(reference, sample, lambda t: t.double())
+            grad_gauges = {k: gauge(mine_g[k], native_g[k], truth_g[k]) for k in truth_g if truth_g[k] is not None}
+            status, reason = records.grade(config["dtype"], gauges, grad_gauges)
+            rows.append(records.make_row(op_name, config, device=torch.cuda.get_device_name(device), torch_version=torch.__version__,
+                                         fwd_ms=fwd_ms, ref_fwd_ms=ref_fwd_ms, gauges=gauges, reps=10, status=status, reason=reason,
+                                         grad_gauges=grad_gauges, bwd_ms=bwd_ms, ref_bwd_ms=ref_bwd_ms))
+            per_op[key]["training_call"] = {"fwd_ms": round(fwd_ms, 4), "bwd_ms": round(bwd_ms, 4), "torch_eager_fwd_ms": round(ref_fwd_ms, 4),
+                                            "torch_eager_bwd_ms": round(ref_bwd_ms, 4)}
         del w, i
         torch.cuda.empty_cache()
     if records_root and rows:

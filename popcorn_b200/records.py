@@ -83,22 +83,52 @@ def make_row(
     op: str, config: dict[str, Any], *, device: str, torch_version: str, fwd_ms: float, ref_fwd_ms: float,
     gauges: dict[str, dict[str, float]], reps: int, status: str = "pass", reason: str = "",
     peak_gb: float | None = None, ref_peak_gb: float | None = None, timestamp: str | None = None,
+    grad_gauges: dict[str, dict[str, float]] | None = None, bwd_ms: float | None = None, ref_bwd_ms: float | None = None,
 ) -> dict[str, Any]:
-    """One report row for the b200 implementation of `op` on the case `config` (forward only)."""
+    """One report row for the b200 implementation of `op` on the case `config`.
+
+    Without `grad_gauges` it is an inference row (grad = False).  With them it is the training-call row of the same case
+    (model.py:75-89: `grad` is part of the row's identity): per-input gradient gauges and the time of the backward pass
+    alone next to the forward time, the pair popcorn's tuner adds up (tuning.py:54-61)."""
     bench = {"fwd_ms": fwd_ms, "ref_fwd_ms": ref_fwd_ms}
+    if grad_gauges is not None:
+        if bwd_ms is None or ref_bwd_ms is None:
+            raise ValueError("a training-call row needs bwd_ms and ref_bwd_ms")
+        bench.update(bwd_ms=bwd_ms, ref_bwd_ms=ref_bwd_ms)
     if peak_gb is not None:
         bench["fwd_peak_gb"] = peak_gb
     if ref_peak_gb is not None:
         bench["ref_fwd_peak_gb"] = ref_peak_gb
+
+    def plain(table: dict[str, dict[str, float]] | None) -> dict[str, dict[str, float]]:
+        return {name: {"err": g["err"], "budget": g["budget"], "scale": g["scale"]} for name, g in (table or {}).items()}
+
     return {
         "schema": SCHEMA, "op": op, "impl": BACKEND, "case": case_label(config), "case_id": config_id(config), "config": config,
         "device": device, "torch": torch_version, "backend_version": None,  # undeclared backend: no version gate
         "ts": timestamp or datetime.datetime.now(datetime.timezone.utc).isoformat(timespec="seconds"),
         "ref_hash": REFERENCE_HASHES.get(op), "impl_hash": implementation_hash(op),
-        "status": status, "reason": reason, "grad": False,
-        "fwd": {name: {"err": g["err"], "budget": g["budget"], "scale": g["scale"]} for name, g in gauges.items()},
-        "bwd": {}, "bench": bench, "benchmarked": True, "bench_error": "", "reps": reps,
+        "status": status, "reason": reason, "grad": grad_gauges is not None,
+        "fwd": plain(gauges), "bwd": plain(grad_gauges), "bench": bench, "benchmarked": True, "bench_error": "", "reps": reps,
     }
+
+
+FLOORS = {"float64": 1e-10, "float32": 2e-5, "float16": 1e-3, "bfloat16": 2e-2}  # compare.py:14
+
+
+def grade(dtype: str, gauges: dict[str, dict[str, float]], grad_gauges: dict[str, dict[str, float]] | None = None) -> tuple[str, str]:
+    """popcorn's verdict on a set of gauges (model.py:66-71, compare.py:279-293): an output or gradient passes when its
+    error against fp64 is at most twice the reference's own error or the dtype's floor times the size of the values.
+    Returns (status, reason) for `make_row`."""
+    floor = FLOORS.get(dtype.removeprefix("torch."), FLOORS["float32"])
+    failures = []
+    for prefix, table in (("", gauges), ("grad ", grad_gauges or {})):
+        for name, g in table.items():
+            if not g["err"] == g["err"] or g["err"] in (float("inf"), float("-inf")):
+                failures.append(f"{prefix}{name}: err is non-finite")
+            elif g["err"] > max(2 * g["budget"], floor * g["scale"]):
+                failures.append(f"{prefix}{name}: err {g['err']:.3e} > max(2*{g['budget']:.3e}, {floor:.0e}*{g['scale']:.1f})")
+    return ("fail", "; ".join(failures)) if failures else ("pass", "")
 
 
 def row_key(row: dict[str, Any]) -> tuple[Any, ...]:
