@@ -382,6 +382,8 @@ def bench_extra_ops(device, peak_gbs: float, sampler, scale: float = 1.0, steps:
     n = a.numel() * 2
     run("geglu_bf16 [32768, 2x14336]", lambda: ops.geglu(a, b), 3 * n)
     run("swiglu_backward_bf16 [32768, 14336]", lambda: ops.swiglu_backward(grad, a, b), 5 * n)
+    run("geglu_backward_bf16 [32768, 14336]", lambda: ops.geglu_backward(grad, a, b), 5 * n)
+    run("sigmoid_gate_backward_bf16 [32768, 14336]", lambda: ops.sigmoid_gate_backward(grad, a, b), 5 * n)
     del w, gu, a, b, grad
     torch.cuda.empty_cache()
 
@@ -392,9 +394,23 @@ def bench_extra_ops(device, peak_gbs: float, sampler, scale: float = 1.0, steps:
     run("layer_norm_bf16 [16384, 8192]", lambda: ops.layer_norm(x, weight, weight), 2 * n)
     run("rms_norm_backward_bf16 [16384, 8192]", lambda: ops.rms_norm_backward(r, x, weight), 3 * n)
     run("add_rms_norm_backward_bf16 [16384, 8192]", lambda: ops.add_rms_norm_backward(r, r, x, weight, 1e-5), 4 * n)
+    run("layer_norm_backward_bf16 [16384, 8192]", lambda: ops.layer_norm_backward(r, x, weight, True), 3 * n)
+    run("l2_norm_backward_bf16 [16384, 8192]", lambda: ops.l2_norm_backward(r, x), 3 * n)
     heads = x.view(-1, 128)  # per-head q/k normalisation: 1,048,576 rows of 128
     run("l2_norm_bf16 [1048576, 128]", lambda: ops.l2_norm(heads), 2 * n)
+    run("l2_norm_backward_bf16 [1048576, 128]", lambda: ops.l2_norm_backward(r.view(-1, 128), heads), 3 * n)
     del w, x, r, weight, heads
+    torch.cuda.empty_cache()
+
+    # the combine's backward on the rows of config 5: reads grad_y once per token and the expert rows, writes the
+    # scaled gradient rows and the per-slot dot products
+    w = workloads.moe_bf16(scale).to(device)
+    idx, wts = ops.moe_route(w.inputs["router_logits"], w.args["top_k"])
+    rows, _, _, _, pos = ops.moe_permute(w.inputs["x"], idx, w.args["experts"])
+    grad_y = torch.randn_like(w.inputs["x"])
+    run("moe_unpermute_backward_bf16 [65536 x 8, 4096]", lambda: ops.moe_unpermute_backward(grad_y, rows, wts, pos),
+        2 * rows.numel() * 2 + grad_y.numel() * 2 + 3 * pos.numel() * 4)
+    del w, idx, wts, rows, pos, grad_y
     torch.cuda.empty_cache()
 
     # the rotary siblings at the shapes of config 3 (8 x 4096 positions, 32 + 8 heads of 128)

@@ -466,6 +466,207 @@ family_bwd_kernel(const T* __restrict__ gy, const T* __restrict__ x, const T* __
   }
 }
 
+// Two sums over the TPR threads of a row with one barrier (TPR == 256) or shuffles only; `slot` is [2][8].
+template <int TPR>
+__device__ __forceinline__ void row_sum2(float& a, float& b, float (*slot)[8]) {
+#pragma unroll
+  for (int o = (TPR < 32 ? TPR : 32) / 2; o > 0; o >>= 1) {
+    a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, o));
+    b = __fadd_rn(b, __shfl_xor_sync(0xffffffffu, b, o));
+  }
+  if constexpr (TPR > 32) {
+    if ((threadIdx.x & 31) == 0) {
+      slot[0][threadIdx.x >> 5] = a;
+      slot[1][threadIdx.x >> 5] = b;
+    }
+    __syncthreads();
+    float ta = 0.f, tb = 0.f;
+#pragma unroll
+    for (int k = 0; k < TPR / 32; ++k) {
+      ta = __fadd_rn(ta, slot[0][k]);
+      tb = __fadd_rn(tb, slot[1][k]);
+    }
+    a = ta;
+    b = tb;
+  }
+}
+
+// The fast path of the backward: rows of up to 1024 128-bit words, held in registers.  TPR threads share a row
+// (TPR <= 32: several rows per warp, RU of them in flight per group; 256: one row per CTA), each thread keeps its
+// ITEMS words of x and of the incoming gradient, so both are read from HBM once and nothing is re-read.  Persistent
+// CTAs walk the rows; for LayerNorm every thread adds its columns' contributions to dw (and db) in registers, the
+// CTA folds its row groups in a fixed order through shared memory and writes ONE line of partial sums, which
+// family_sum_lines_kernel adds up, so the result does not depend on timing.
+template <typename T, int TPR, int ITEMS, int MODE, int RU>
+__global__ void __launch_bounds__(256, 2)
+family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const T* __restrict__ weight, T* __restrict__ dx,
+                       float* __restrict__ partial, int64_t rows, int nvec, int64_t ldg, int64_t ldx, int64_t lddx,
+                       float cols_f, float eps, int has_bias) {
+  constexpr int V = Num<T>::kVec;
+  constexpr int GROUPS = 256 / TPR;
+  constexpr bool LAYER = MODE == kLayer;
+  constexpr bool KEEP_W = ITEMS < 4;  // wide rows re-read their weight words (L1 hits) instead of holding them in registers
+  static_assert(RU == 1 || TPR <= 32, "several rows per group only for rows that fit a warp");
+  pdl_prologue();
+  __shared__ float slots[4][8];
+  __shared__ float fold[LAYER && GROUPS > 1 ? 2 * TPR * ITEMS * V : 1];
+  const int tid = threadIdx.x;
+  const int sub = tid / TPR, lane_in_row = tid % TPR;
+  bool col_ok[ITEMS];
+  uint4 wv[LAYER && KEEP_W ? ITEMS : 1];
+  auto weight_word = [&](int i) { return KEEP_W ? wv[KEEP_W ? i : 0] : ld_reuse(weight + static_cast<int64_t>(lane_in_row + i * TPR) * V); };
+  float dw[LAYER ? ITEMS : 1][V], db[LAYER ? ITEMS : 1][V];
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    col_ok[i] = lane_in_row + i * TPR < nvec;
+    if constexpr (LAYER) {
+      if constexpr (KEEP_W) {
+        wv[i] = make_uint4(0, 0, 0, 0);
+        if (col_ok[i]) wv[i] = ld_reuse(weight + static_cast<int64_t>(lane_in_row + i * TPR) * V);
+      }
+#pragma unroll
+      for (int j = 0; j < V; ++j) dw[i][j] = db[i][j] = 0.f;
+    }
+  }
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * GROUPS * RU;
+  // every thread of the CTA runs the same number of iterations (barriers and full-warp shuffles inside)
+  int parity = 0;  // the L2 mode has one barrier per row: consecutive rows alternate between two slot pairs
+  for (int64_t base = static_cast<int64_t>(blockIdx.x) * GROUPS * RU; base < rows; base += stride, parity ^= 1) {
+    uint4 xv[RU][ITEMS], gv[RU][ITEMS];
+#pragma unroll
+    for (int u = 0; u < RU; ++u) {
+      const int64_t row = base + static_cast<int64_t>(sub) * RU + u;
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) {
+        xv[u][i] = gv[u][i] = make_uint4(0, 0, 0, 0);
+        if (row < rows && col_ok[i]) {
+          const int64_t col = static_cast<int64_t>(lane_in_row + i * TPR) * V;
+          xv[u][i] = ld_stream(x + row * ldx + col);
+          gv[u][i] = ld_stream(gy + row * ldg + col);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < RU; ++u) {
+      const int64_t row = base + static_cast<int64_t>(sub) * RU + u;
+      const bool live = row < rows;
+      if constexpr (MODE == kL2) {
+        float ss = 0.f, dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+          float fx[V], fg[V];
+          Num<T>::unpack(xv[u][i], fx);
+          Num<T>::unpack(gv[u][i], fg);
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            ss = __fmaf_rn(fx[j], fx[j], ss);
+            dot = __fmaf_rn(fg[j], fx[j], dot);
+          }
+        }
+        row_sum2<TPR>(ss, dot, &slots[parity * 2]);
+        const float sc = __frcp_rn(__fsqrt_rn(__fadd_rn(ss, eps)));
+        const float coef = -__fmul_rn(__fmul_rn(__fmul_rn(sc, sc), sc), dot);
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+          float fx[V], fg[V];
+          Num<T>::unpack(xv[u][i], fx);
+          Num<T>::unpack(gv[u][i], fg);
+#pragma unroll
+          for (int j = 0; j < V; ++j) fg[j] = __fmaf_rn(fg[j], sc, __fmul_rn(fx[j], coef));
+          if (live && col_ok[i]) st_stream(dx + row * lddx + static_cast<int64_t>(lane_in_row + i * TPR) * V, Num<T>::pack(fg));
+        }
+      } else {
+        float sx = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+          if (!col_ok[i]) continue;
+          float fx[V], fg[V], fw[V];
+          Num<T>::unpack(xv[u][i], fx);
+          Num<T>::unpack(gv[u][i], fg);
+          Num<T>::unpack(weight_word(i), fw);
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            sx = __fadd_rn(sx, fx[j]);
+            s1 = __fmaf_rn(fg[j], fw[j], s1);
+          }
+        }
+        row_sum2<TPR>(sx, s1, &slots[0]);
+        const float mean = __fdiv_rn(sx, cols_f);
+        float var = 0.f, t = 0.f;
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+          if (!col_ok[i]) continue;  // padding columns must not see -mean
+          float fx[V], fg[V], fw[V];
+          Num<T>::unpack(xv[u][i], fx);
+          Num<T>::unpack(gv[u][i], fg);
+          Num<T>::unpack(weight_word(i), fw);
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            const float d = __fsub_rn(fx[j], mean);
+            var = __fmaf_rn(d, d, var);
+            t = __fmaf_rn(__fmul_rn(fg[j], fw[j]), d, t);
+          }
+        }
+        row_sum2<TPR>(var, t, &slots[2]);
+        const float rstd = __frcp_rn(__fsqrt_rn(__fadd_rn(fmaxf(__fdiv_rn(var, cols_f), 0.f), eps)));
+        const float m1 = __fdiv_rn(s1, cols_f);                   // mean of g w
+        const float m2 = __fdiv_rn(__fmul_rn(t, rstd), cols_f);   // mean of g w xhat
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+          if (!col_ok[i]) continue;
+          float fx[V], fg[V], fw[V];
+          Num<T>::unpack(xv[u][i], fx);
+          Num<T>::unpack(gv[u][i], fg);
+          Num<T>::unpack(weight_word(i), fw);
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            const float xhat = live ? __fmul_rn(__fsub_rn(fx[j], mean), rstd) : 0.f;
+            dw[i][j] = __fmaf_rn(fg[j], xhat, dw[i][j]);
+            db[i][j] = __fadd_rn(db[i][j], fg[j]);
+            fx[j] = __fmul_rn(rstd, __fsub_rn(__fsub_rn(__fmul_rn(fg[j], fw[j]), m1), __fmul_rn(xhat, m2)));
+          }
+          if (live) st_stream(dx + row * lddx + static_cast<int64_t>(lane_in_row + i * TPR) * V, Num<T>::pack(fx));
+        }
+      }
+    }
+  }
+  if constexpr (LAYER) {
+    // this CTA's line of the partial sums: [0][cols] for dw, [1][cols] for db
+    float* line = partial + static_cast<int64_t>(blockIdx.x) * 2 * nvec * V;
+    if constexpr (GROUPS > 1) {
+      // fold the row groups in group order: group 0 stores, every later group adds, one barrier per group
+      for (int g = 0; g < GROUPS; ++g) {
+        if (sub == g) {
+#pragma unroll
+          for (int i = 0; i < ITEMS; ++i)
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+              const int c = (lane_in_row + i * TPR) * V + j;
+              fold[c] = g == 0 ? dw[i][j] : __fadd_rn(fold[c], dw[i][j]);
+              fold[TPR * ITEMS * V + c] = g == 0 ? db[i][j] : __fadd_rn(fold[TPR * ITEMS * V + c], db[i][j]);
+            }
+        }
+        __syncthreads();
+      }
+      for (int c = tid; c < nvec * V; c += 256) {
+        line[c] = fold[c];
+        if (has_bias) line[nvec * V + c] = fold[TPR * ITEMS * V + c];
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) {
+        if (!col_ok[i]) continue;
+        const int64_t c = static_cast<int64_t>(lane_in_row + i * TPR) * V;
+#pragma unroll
+        for (int j = 0; j < V; j += 4) {
+          *reinterpret_cast<float4*>(line + c + j) = make_float4(dw[i][j], dw[i][j + 1], dw[i][j + 2], dw[i][j + 3]);
+          if (has_bias) *reinterpret_cast<float4*>(line + nvec * V + c + j) = make_float4(db[i][j], db[i][j + 1], db[i][j + 2], db[i][j + 3]);
+        }
+      }
+    }
+  }
+}
+
 // dw[c] = round_T(sum over lines of partial[line][0][c]), db likewise from partial[line][1][c].
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -487,19 +688,49 @@ int family_bwd_lines(int64_t rows) {
   return static_cast<int>(rows < cap ? (rows > 0 ? rows : 1) : cap);
 }
 
+// CTAs of the persistent backward launch for `groups` rows per CTA pass; also the number of partial lines.
+int family_bwd_ctas(int64_t rows, int groups) {
+  const int64_t want = ceil_div(rows > 0 ? rows : 1, static_cast<int64_t>(groups));
+  const int64_t cap = family_bwd_lines(rows);
+  return static_cast<int>(want < cap ? want : cap);
+}
+
 template <typename T, int MODE>
 int run_bwd(const void* gy, const void* x, const void* w, void* dx, void* dw, void* db, float* scratch, int64_t rows, int64_t cols,
             int64_t ldg, int64_t ldx, int64_t lddx, float eps, cudaStream_t st) {
   constexpr int V = Num<T>::kVec;
   const bool vec = cols % V == 0 && ldg % V == 0 && ldx % V == 0 && lddx % V == 0 && aligned(gy, 16) && aligned(x, 16) && aligned(dx, 16) &&
                    (w == nullptr || aligned(w, 16));
-  const int lines = family_bwd_lines(rows);
   const T *tg = static_cast<const T*>(gy), *tx = static_cast<const T*>(x), *tw = static_cast<const T*>(w);
   T* tdx = static_cast<T*>(dx);
   const float cols_f = static_cast<float>(cols);
-  if (vec) launch(family_bwd_kernel<T, MODE, true>, lines, 256, 0, st, tg, tx, tw, tdx, scratch, rows, cols, ldg, ldx, lddx, cols_f, eps, db != nullptr ? 1 : 0);
-  else launch(family_bwd_kernel<T, MODE, false>, lines, 256, 0, st, tg, tx, tw, tdx, scratch, rows, cols, ldg, ldx, lddx, cols_f, eps, db != nullptr ? 1 : 0);
-  if (int rc = after_launch("family_bwd_kernel")) return rc;
+  const int bias = db != nullptr ? 1 : 0;
+  const int64_t nvec64 = cols / V;
+  int lines = 0;
+  if (vec && nvec64 <= 1024) {
+    const int nvec = static_cast<int>(nvec64);
+#define B200_FAMILY_BWD(TPR, ITEMS, RU)                                                                                          \
+  do {                                                                                                                           \
+    lines = family_bwd_ctas(rows, 256 / TPR * RU);                                                                               \
+    launch(family_bwd_rows_kernel<T, TPR, ITEMS, MODE, RU>, static_cast<unsigned>(lines), 256, 0, st, tg, tx, tw, tdx, scratch, rows, \
+           nvec, ldg, ldx, lddx, cols_f, eps, bias);                                                                             \
+  } while (0)
+    if (nvec <= 8) B200_FAMILY_BWD(8, 1, 4);
+    else if (nvec <= 16) B200_FAMILY_BWD(16, 1, 4);
+    else if (nvec <= 32) B200_FAMILY_BWD(32, 1, 4);
+    else if (nvec <= 64) B200_FAMILY_BWD(32, 2, 1);
+    else if (nvec <= 128) B200_FAMILY_BWD(32, 4, 1);
+    else if (nvec <= 256) B200_FAMILY_BWD(256, 1, 1);
+    else if (nvec <= 512) B200_FAMILY_BWD(256, 2, 1);
+    else B200_FAMILY_BWD(256, 4, 1);
+#undef B200_FAMILY_BWD
+    if (int rc = after_launch("family_bwd_rows_kernel")) return rc;
+  } else {
+    lines = family_bwd_lines(rows);
+    if (vec) launch(family_bwd_kernel<T, MODE, true>, lines, 256, 0, st, tg, tx, tw, tdx, scratch, rows, cols, ldg, ldx, lddx, cols_f, eps, bias);
+    else launch(family_bwd_kernel<T, MODE, false>, lines, 256, 0, st, tg, tx, tw, tdx, scratch, rows, cols, ldg, ldx, lddx, cols_f, eps, bias);
+    if (int rc = after_launch("family_bwd_kernel")) return rc;
+  }
   if (MODE == kLayer) {
     launch(family_sum_lines_kernel<T>, static_cast<unsigned>(ceil_div(cols, 256)), 256, 0, st, static_cast<const float*>(scratch), lines, cols,
            static_cast<T*>(dw), static_cast<T*>(db));
