@@ -466,29 +466,42 @@ family_bwd_kernel(const T* __restrict__ gy, const T* __restrict__ x, const T* __
   }
 }
 
-// Two sums over the TPR threads of a row with one barrier (TPR == 256) or shuffles only; `slot` is [2][8].
-template <int TPR>
-__device__ __forceinline__ void row_sum2(float& a, float& b, float (*slot)[8]) {
+// N sums over the TPR threads of a row with one barrier (TPR == 256) or shuffles only; `slot` is [N][8].
+template <int TPR, int N>
+__device__ __forceinline__ void row_sums(float (&v)[N], float (*slot)[8]) {
 #pragma unroll
   for (int o = (TPR < 32 ? TPR : 32) / 2; o > 0; o >>= 1) {
-    a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, o));
-    b = __fadd_rn(b, __shfl_xor_sync(0xffffffffu, b, o));
+#pragma unroll
+    for (int n = 0; n < N; ++n) v[n] = __fadd_rn(v[n], __shfl_xor_sync(0xffffffffu, v[n], o));
   }
   if constexpr (TPR > 32) {
     if ((threadIdx.x & 31) == 0) {
-      slot[0][threadIdx.x >> 5] = a;
-      slot[1][threadIdx.x >> 5] = b;
+#pragma unroll
+      for (int n = 0; n < N; ++n) slot[n][threadIdx.x >> 5] = v[n];
     }
     __syncthreads();
-    float ta = 0.f, tb = 0.f;
 #pragma unroll
-    for (int k = 0; k < TPR / 32; ++k) {
-      ta = __fadd_rn(ta, slot[0][k]);
-      tb = __fadd_rn(tb, slot[1][k]);
+    for (int n = 0; n < N; ++n) {
+      float total = 0.f;
+#pragma unroll
+      for (int k = 0; k < TPR / 32; ++k) total = __fadd_rn(total, slot[n][k]);
+      v[n] = total;
     }
-    a = ta;
-    b = tb;
   }
+}
+
+// A 128-bit word of T as V / 2 pairs of fp32 (the operands of the two-element fp32 instructions).
+template <typename T>
+__device__ __forceinline__ void unpack_pairs(const uint4& word, Float2x (&out)[Num<T>::kVec / 2]) {
+  float f[Num<T>::kVec];
+  Num<T>::unpack(word, f);
+#pragma unroll
+  for (int j = 0; j < Num<T>::kVec / 2; ++j) out[j] = pack_f2(f[2 * j], f[2 * j + 1]);
+}
+__device__ __forceinline__ float pair_total(Float2x v) {
+  float lo, hi;
+  unpack_f2(v, lo, hi);
+  return __fadd_rn(lo, hi);
 }
 
 // The fast path of the backward: rows of up to 1024 128-bit words, held in registers.  TPR threads share a row
@@ -496,13 +509,18 @@ __device__ __forceinline__ void row_sum2(float& a, float& b, float (*slot)[8]) {
 // ITEMS words of x and of the incoming gradient, so both are read from HBM once and nothing is re-read.  Persistent
 // CTAs walk the rows; for LayerNorm every thread adds its columns' contributions to dw (and db) in registers, the
 // CTA folds its row groups in a fixed order through shared memory and writes ONE line of partial sums, which
-// family_sum_lines_kernel adds up, so the result does not depend on timing.
+// family_sum_lines_kernel adds up, so the result does not depend on timing.  The arithmetic is fp32 with two
+// elements per instruction; gradients are compared within a tolerance, so products and sums may be fused:
+//   LayerNorm, per row:  mean = sum x / n;  var = sum (x - mean)^2 / n;  rstd = 1 / sqrt(var + eps)
+//                        m1 = sum gw / n;  m2 = rstd (sum gw x - mean sum gw) / n            (gw = g w)
+//                        xhat = x rstd - mean rstd;  dx = gw rstd - m1 rstd - xhat m2 rstd;  dw += g xhat;  db += g
 template <typename T, int TPR, int ITEMS, int MODE, int RU>
 __global__ void __launch_bounds__(256, 2)
 family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const T* __restrict__ weight, T* __restrict__ dx,
                        float* __restrict__ partial, int64_t rows, int nvec, int64_t ldg, int64_t ldx, int64_t lddx,
                        float cols_f, float eps, int has_bias) {
   constexpr int V = Num<T>::kVec;
+  constexpr int P = V / 2;  // fp32 pairs per word
   constexpr int GROUPS = 256 / TPR;
   constexpr bool LAYER = MODE == kLayer;
   constexpr bool KEEP_W = ITEMS < 4;  // wide rows re-read their weight words (L1 hits) instead of holding them in registers
@@ -515,7 +533,7 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
   bool col_ok[ITEMS];
   uint4 wv[LAYER && KEEP_W ? ITEMS : 1];
   auto weight_word = [&](int i) { return KEEP_W ? wv[KEEP_W ? i : 0] : ld_reuse(weight + static_cast<int64_t>(lane_in_row + i * TPR) * V); };
-  float dw[LAYER ? ITEMS : 1][V], db[LAYER ? ITEMS : 1][V];
+  Float2x dw[LAYER ? ITEMS : 1][P], db[LAYER ? ITEMS : 1][P];
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
     col_ok[i] = lane_in_row + i * TPR < nvec;
@@ -525,12 +543,12 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
         if (col_ok[i]) wv[i] = ld_reuse(weight + static_cast<int64_t>(lane_in_row + i * TPR) * V);
       }
 #pragma unroll
-      for (int j = 0; j < V; ++j) dw[i][j] = db[i][j] = 0.f;
+      for (int j = 0; j < P; ++j) dw[i][j] = db[i][j] = pack_f2(0.f, 0.f);
     }
   }
   const int64_t stride = static_cast<int64_t>(gridDim.x) * GROUPS * RU;
-  // every thread of the CTA runs the same number of iterations (barriers and full-warp shuffles inside)
   int parity = 0;  // the L2 mode has one barrier per row: consecutive rows alternate between two slot pairs
+  // every thread of the CTA runs the same number of iterations (barriers and full-warp shuffles inside)
   for (int64_t base = static_cast<int64_t>(blockIdx.x) * GROUPS * RU; base < rows; base += stride, parity ^= 1) {
     uint4 xv[RU][ITEMS], gv[RU][ITEMS];
 #pragma unroll
@@ -551,81 +569,89 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
       const int64_t row = base + static_cast<int64_t>(sub) * RU + u;
       const bool live = row < rows;
       if constexpr (MODE == kL2) {
-        float ss = 0.f, dot = 0.f;
+        Float2x ss2 = pack_f2(0.f, 0.f), dot2 = ss2;
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
-          float fx[V], fg[V];
-          Num<T>::unpack(xv[u][i], fx);
-          Num<T>::unpack(gv[u][i], fg);
+          Float2x fx[P], fg[P];
+          unpack_pairs<T>(xv[u][i], fx);
+          unpack_pairs<T>(gv[u][i], fg);
 #pragma unroll
-          for (int j = 0; j < V; ++j) {
-            ss = __fmaf_rn(fx[j], fx[j], ss);
-            dot = __fmaf_rn(fg[j], fx[j], dot);
+          for (int j = 0; j < P; ++j) {
+            ss2 = fma_f2(fx[j], fx[j], ss2);
+            dot2 = fma_f2(fg[j], fx[j], dot2);
           }
         }
-        row_sum2<TPR>(ss, dot, &slots[parity * 2]);
-        const float sc = __frcp_rn(__fsqrt_rn(__fadd_rn(ss, eps)));
-        const float coef = -__fmul_rn(__fmul_rn(__fmul_rn(sc, sc), sc), dot);
+        float sums[2] = {pair_total(ss2), pair_total(dot2)};
+        row_sums<TPR, 2>(sums, &slots[parity * 2]);
+        const float sc = __frcp_rn(__fsqrt_rn(__fadd_rn(sums[0], eps)));
+        const float coef = -__fmul_rn(__fmul_rn(__fmul_rn(sc, sc), sc), sums[1]);
+        const Float2x sc2 = pack_f2(sc, sc), coef2 = pack_f2(coef, coef);
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
-          float fx[V], fg[V];
-          Num<T>::unpack(xv[u][i], fx);
-          Num<T>::unpack(gv[u][i], fg);
+          Float2x fx[P], fg[P];
+          unpack_pairs<T>(xv[u][i], fx);
+          unpack_pairs<T>(gv[u][i], fg);
+          float out[V];
 #pragma unroll
-          for (int j = 0; j < V; ++j) fg[j] = __fmaf_rn(fg[j], sc, __fmul_rn(fx[j], coef));
-          if (live && col_ok[i]) st_stream(dx + row * lddx + static_cast<int64_t>(lane_in_row + i * TPR) * V, Num<T>::pack(fg));
+          for (int j = 0; j < P; ++j) unpack_f2(fma_f2(fg[j], sc2, mul_f2(fx[j], coef2)), out[2 * j], out[2 * j + 1]);
+          if (live && col_ok[i]) st_stream(dx + row * lddx + static_cast<int64_t>(lane_in_row + i * TPR) * V, Num<T>::pack(out));
         }
       } else {
-        float sx = 0.f, s1 = 0.f;
+        Float2x sx2 = pack_f2(0.f, 0.f), s12 = sx2, sgx2 = sx2;
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
           if (!col_ok[i]) continue;
-          float fx[V], fg[V], fw[V];
-          Num<T>::unpack(xv[u][i], fx);
-          Num<T>::unpack(gv[u][i], fg);
-          Num<T>::unpack(weight_word(i), fw);
+          Float2x fx[P], fg[P], fw[P];
+          unpack_pairs<T>(xv[u][i], fx);
+          unpack_pairs<T>(gv[u][i], fg);
+          unpack_pairs<T>(weight_word(i), fw);
 #pragma unroll
-          for (int j = 0; j < V; ++j) {
-            sx = __fadd_rn(sx, fx[j]);
-            s1 = __fmaf_rn(fg[j], fw[j], s1);
+          for (int j = 0; j < P; ++j) {
+            const Float2x gw = mul_f2(fg[j], fw[j]);
+            sx2 = add_f2(sx2, fx[j]);
+            s12 = add_f2(s12, gw);
+            sgx2 = fma_f2(gw, fx[j], sgx2);
           }
         }
-        row_sum2<TPR>(sx, s1, &slots[0]);
-        const float mean = __fdiv_rn(sx, cols_f);
-        float var = 0.f, t = 0.f;
+        float first[3] = {pair_total(sx2), pair_total(s12), pair_total(sgx2)};
+        row_sums<TPR, 3>(first, &slots[0]);
+        const float mean = __fdiv_rn(first[0], cols_f);
+        const Float2x mean2 = pack_f2(mean, mean);
+        Float2x var2 = pack_f2(0.f, 0.f);
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
           if (!col_ok[i]) continue;  // padding columns must not see -mean
-          float fx[V], fg[V], fw[V];
-          Num<T>::unpack(xv[u][i], fx);
-          Num<T>::unpack(gv[u][i], fg);
-          Num<T>::unpack(weight_word(i), fw);
+          Float2x fx[P];
+          unpack_pairs<T>(xv[u][i], fx);
 #pragma unroll
-          for (int j = 0; j < V; ++j) {
-            const float d = __fsub_rn(fx[j], mean);
-            var = __fmaf_rn(d, d, var);
-            t = __fmaf_rn(__fmul_rn(fg[j], fw[j]), d, t);
+          for (int j = 0; j < P; ++j) {
+            const Float2x d = sub_f2(fx[j], mean2);
+            var2 = fma_f2(d, d, var2);
           }
         }
-        row_sum2<TPR>(var, t, &slots[2]);
-        const float rstd = __frcp_rn(__fsqrt_rn(__fadd_rn(fmaxf(__fdiv_rn(var, cols_f), 0.f), eps)));
-        const float m1 = __fdiv_rn(s1, cols_f);                   // mean of g w
-        const float m2 = __fdiv_rn(__fmul_rn(t, rstd), cols_f);   // mean of g w xhat
+        float second[1] = {pair_total(var2)};
+        row_sums<TPR, 1>(second, &slots[3]);
+        const float rstd = __frcp_rn(__fsqrt_rn(__fadd_rn(fmaxf(__fdiv_rn(second[0], cols_f), 0.f), eps)));
+        const float m1 = __fdiv_rn(first[1], cols_f);                                                     // mean of g w
+        const float m2 = __fdiv_rn(__fmul_rn(__fsub_rn(first[2], __fmul_rn(mean, first[1])), rstd), cols_f);  // mean of g w xhat
+        const float shift = -__fmul_rn(mean, rstd), c1 = -__fmul_rn(m1, rstd), c2 = -__fmul_rn(m2, rstd);
+        const Float2x rstd2 = pack_f2(rstd, rstd), shift2 = pack_f2(shift, shift), c12 = pack_f2(c1, c1), c22 = pack_f2(c2, c2);
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
           if (!col_ok[i]) continue;
-          float fx[V], fg[V], fw[V];
-          Num<T>::unpack(xv[u][i], fx);
-          Num<T>::unpack(gv[u][i], fg);
-          Num<T>::unpack(weight_word(i), fw);
+          Float2x fx[P], fg[P], fw[P];
+          unpack_pairs<T>(xv[u][i], fx);
+          unpack_pairs<T>(gv[u][i], fg);
+          unpack_pairs<T>(weight_word(i), fw);
+          float out[V];
 #pragma unroll
-          for (int j = 0; j < V; ++j) {
-            const float xhat = live ? __fmul_rn(__fsub_rn(fx[j], mean), rstd) : 0.f;
-            dw[i][j] = __fmaf_rn(fg[j], xhat, dw[i][j]);
-            db[i][j] = __fadd_rn(db[i][j], fg[j]);
-            fx[j] = __fmul_rn(rstd, __fsub_rn(__fsub_rn(__fmul_rn(fg[j], fw[j]), m1), __fmul_rn(xhat, m2)));
+          for (int j = 0; j < P; ++j) {
+            const Float2x xhat = fma_f2(fx[j], rstd2, shift2);  // a row past the end is all zeros: mean, shift and xhat are 0
+            dw[i][j] = fma_f2(fg[j], xhat, dw[i][j]);
+            db[i][j] = add_f2(db[i][j], fg[j]);
+            unpack_f2(fma_f2(xhat, c22, fma_f2(mul_f2(fg[j], fw[j]), rstd2, c12)), out[2 * j], out[2 * j + 1]);
           }
-          if (live) st_stream(dx + row * lddx + static_cast<int64_t>(lane_in_row + i * TPR) * V, Num<T>::pack(fx));
+          if (live) st_stream(dx + row * lddx + static_cast<int64_t>(lane_in_row + i * TPR) * V, Num<T>::pack(out));
         }
       }
     }
@@ -640,10 +666,17 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
 #pragma unroll
           for (int i = 0; i < ITEMS; ++i)
 #pragma unroll
-            for (int j = 0; j < V; ++j) {
-              const int c = (lane_in_row + i * TPR) * V + j;
-              fold[c] = g == 0 ? dw[i][j] : __fadd_rn(fold[c], dw[i][j]);
-              fold[TPR * ITEMS * V + c] = g == 0 ? db[i][j] : __fadd_rn(fold[TPR * ITEMS * V + c], db[i][j]);
+            for (int j = 0; j < P; ++j) {
+              const int c = (lane_in_row + i * TPR) * V + 2 * j;
+              float w0, w1, b0, b1;
+              unpack_f2(dw[i][j], w0, w1);
+              unpack_f2(db[i][j], b0, b1);
+              float* fw = fold + c;
+              float* fb = fold + TPR * ITEMS * V + c;
+              fw[0] = g == 0 ? w0 : __fadd_rn(fw[0], w0);
+              fw[1] = g == 0 ? w1 : __fadd_rn(fw[1], w1);
+              fb[0] = g == 0 ? b0 : __fadd_rn(fb[0], b0);
+              fb[1] = g == 0 ? b1 : __fadd_rn(fb[1], b1);
             }
         }
         __syncthreads();
@@ -658,33 +691,56 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
         if (!col_ok[i]) continue;
         const int64_t c = static_cast<int64_t>(lane_in_row + i * TPR) * V;
 #pragma unroll
-        for (int j = 0; j < V; j += 4) {
-          *reinterpret_cast<float4*>(line + c + j) = make_float4(dw[i][j], dw[i][j + 1], dw[i][j + 2], dw[i][j + 3]);
-          if (has_bias) *reinterpret_cast<float4*>(line + nvec * V + c + j) = make_float4(db[i][j], db[i][j + 1], db[i][j + 2], db[i][j + 3]);
+        for (int j = 0; j < P; j += 2) {
+          float a0, a1, a2, a3;
+          unpack_f2(dw[i][j], a0, a1);
+          unpack_f2(dw[i][j + 1], a2, a3);
+          *reinterpret_cast<float4*>(line + c + 2 * j) = make_float4(a0, a1, a2, a3);
+          if (has_bias) {
+            unpack_f2(db[i][j], a0, a1);
+            unpack_f2(db[i][j + 1], a2, a3);
+            *reinterpret_cast<float4*>(line + nvec * V + c + 2 * j) = make_float4(a0, a1, a2, a3);
+          }
         }
       }
     }
   }
 }
 
-// dw[c] = round_T(sum over lines of partial[line][0][c]), db likewise from partial[line][1][c].
+// dw[c] = round_T(sum over lines of partial[line][0][c]), db likewise from partial[line][1][c].  A CTA owns 32
+// columns; its eight warps each add every eighth line (a warp load is one 128-byte segment of a line), then the
+// eight partial sums are added in warp order, so the result does not depend on timing.
 template <typename T>
 __global__ void __launch_bounds__(256)
 family_sum_lines_kernel(const float* __restrict__ partial, int lines, int64_t cols, T* __restrict__ dw, T* __restrict__ db) {
   pdl_prologue();
-  const int64_t c = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
-  if (c >= cols) return;
+  __shared__ float part[2][8][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t c = static_cast<int64_t>(blockIdx.x) * 32 + lane;
   float aw = 0.f, ab = 0.f;
-  for (int l = 0; l < lines; ++l) {
-    aw = __fadd_rn(aw, partial[(static_cast<int64_t>(l) * 2) * cols + c]);
-    ab = __fadd_rn(ab, partial[(static_cast<int64_t>(l) * 2 + 1) * cols + c]);
+  if (c < cols) {
+    for (int l = warp; l < lines; l += 8) {
+      aw = __fadd_rn(aw, partial[(static_cast<int64_t>(l) * 2) * cols + c]);
+      if (db != nullptr) ab = __fadd_rn(ab, partial[(static_cast<int64_t>(l) * 2 + 1) * cols + c]);
+    }
   }
-  dw[c] = Num<T>::down(aw);
-  if (db != nullptr) db[c] = Num<T>::down(ab);
+  part[0][warp][lane] = aw;
+  part[1][warp][lane] = ab;
+  __syncthreads();
+  if (warp == 0 && c < cols) {
+    float tw = 0.f, tb = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      tw = __fadd_rn(tw, part[0][k][lane]);
+      tb = __fadd_rn(tb, part[1][k][lane]);
+    }
+    dw[c] = Num<T>::down(tw);
+    if (db != nullptr) db[c] = Num<T>::down(tb);
+  }
 }
 
 int family_bwd_lines(int64_t rows) {
-  const int64_t cap = static_cast<int64_t>(sm_count()) * 4;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 2;  // the row kernels run two CTAs per SM
   return static_cast<int>(rows < cap ? (rows > 0 ? rows : 1) : cap);
 }
 
@@ -732,7 +788,7 @@ int run_bwd(const void* gy, const void* x, const void* w, void* dx, void* dw, vo
     if (int rc = after_launch("family_bwd_kernel")) return rc;
   }
   if (MODE == kLayer) {
-    launch(family_sum_lines_kernel<T>, static_cast<unsigned>(ceil_div(cols, 256)), 256, 0, st, static_cast<const float*>(scratch), lines, cols,
+    launch(family_sum_lines_kernel<T>, static_cast<unsigned>(ceil_div(cols, 32)), 256, 0, st, static_cast<const float*>(scratch), lines, cols,
            static_cast<T*>(dw), static_cast<T*>(db));
     return after_launch("family_sum_lines_kernel");
   }
