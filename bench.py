@@ -428,6 +428,12 @@ def bench_extra_ops(device, peak_gbs: float, sampler, scale: float = 1.0, steps:
     q3, k3 = w3.inputs["q"], w3.inputs["k"]
     freqs = torch.stack((w3.inputs["cos"], w3.inputs["sin"]), -1).to(torch.bfloat16)
     run("llama4_rope_bf16 q[8,4096,32,128] k[8,4096,8,128]", lambda: ops.llama4_rope(q3, k3, freqs), n + freqs.numel() * 2)
+    cos3, sin3 = w3.inputs["cos"], w3.inputs["sin"]
+    table = 2 * cos3.numel() * cos3.element_size()
+    run("rotary_interleaved_bf16 q[8,4096,32,128]", lambda: ops.rotary_embedding(q3, cos3, sin3, True), 2 * q3.numel() * 2 + table)
+    half = cos3[:, : cos3.shape[1] // 2].contiguous(), sin3[:, : sin3.shape[1] // 2].contiguous()
+    run("rotary_partial_bf16 q[8,4096,32,128] (first 64 channels rotated)", lambda: ops.rotary_embedding(q3, half[0], half[1]),
+        2 * q3.numel() * 2 + table // 2)
     return out
 
 
