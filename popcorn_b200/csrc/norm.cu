@@ -608,16 +608,27 @@ rms_bwd_stream_kernel(const T* __restrict__ gy, const T* __restrict__ gs, const 
   }
 }
 
-// out[c] = round_T(sum over lines of part[line][c]), lines added in order.
+// out[c] = round_T(sum over lines of part[line][c]).  A CTA owns 32 columns; its eight warps each add every eighth
+// line (a warp load is one 128-byte segment of a line), then the eight partial sums are added in warp order, so the
+// result does not depend on timing.
 template <typename T>
 __global__ void __launch_bounds__(256)
 rms_bwd_reduce_kernel(const float* __restrict__ part, int lines, int64_t cols, T* __restrict__ out) {
   pdl_prologue();
-  const int64_t c = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
-  if (c >= cols) return;
+  __shared__ float sums[8][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t c = static_cast<int64_t>(blockIdx.x) * 32 + lane;
   float acc = 0.f;
-  for (int l = 0; l < lines; ++l) acc = __fadd_rn(acc, part[l * cols + c]);
-  out[c] = Num<T>::down(acc);
+  if (c < cols)
+    for (int l = warp; l < lines; l += 8) acc = __fadd_rn(acc, part[static_cast<int64_t>(l) * cols + c]);
+  sums[warp][lane] = acc;
+  __syncthreads();
+  if (warp == 0 && c < cols) {
+    float total = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) total = __fadd_rn(total, sums[k][lane]);
+    out[c] = Num<T>::down(total);
+  }
 }
 
 // Shared memory a backward CTA may use for its ring: two CTAs share an SM's 227 KB with their static buffers.
@@ -688,7 +699,7 @@ int run_bwd(const void* gy, const void* gs, const void* x, const void* w, void* 
            ldx, lddx, cols_f, eps, offset);
     if (int rc = after_launch("rms_bwd_stream_kernel")) return rc;
   }
-  const unsigned grid = static_cast<unsigned>(ceil_div(cols, 256));
+  const unsigned grid = static_cast<unsigned>(ceil_div(cols, 32));
   launch(rms_bwd_reduce_kernel<T>, grid, 256, 0, st, static_cast<const float*>(part_w), lines, cols, static_cast<T*>(dw));
   if (int rc = after_launch("rms_bwd_reduce_kernel")) return rc;
   if (db) {

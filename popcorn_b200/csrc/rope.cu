@@ -948,16 +948,27 @@ __global__ void __launch_bounds__(256, 2) norm_rope_bwd_kernel(const NormRopeBwd
 
 // out[ti][c] = round_T(sum over lines of partial[line][ti][c]), lines added in order.
 template <typename T>
-__global__ void __launch_bounds__(256) sum_lines_kernel(const float* __restrict__ partial, int lines, int head_dim, T* __restrict__ dw0, T* __restrict__ dw1) {
+__global__ void __launch_bounds__(1024) sum_lines_kernel(const float* __restrict__ partial, int lines, int head_dim, T* __restrict__ dw0, T* __restrict__ dw1) {
+  // A CTA owns 32 of the 2 x head_dim columns; each of its 32 warps adds every 32nd line (one 128-byte segment per
+  // load), then the 32 partial sums are added in warp order: the result does not depend on timing.
   pdl_prologue();
-  const int idx = blockIdx.x * 256 + threadIdx.x;
-  if (idx >= 2 * head_dim) return;
-  const int ti = idx / head_dim, c = idx % head_dim;
-  T* out = ti == 0 ? dw0 : dw1;
-  if (out == nullptr) return;
+  __shared__ float part[32][33];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int idx = blockIdx.x * 32 + lane;
+  const bool in_range = idx < 2 * head_dim;
+  const int ti = in_range ? idx / head_dim : 0, c = in_range ? idx % head_dim : 0;
   float acc = 0.f;
-  for (int l = 0; l < lines; ++l) acc = __fadd_rn(acc, partial[(static_cast<int64_t>(l) * 2 + ti) * head_dim + c]);
-  out[c] = Num<T>::down(acc);
+  if (in_range)
+    for (int l = warp; l < lines; l += 32) acc = __fadd_rn(acc, partial[(static_cast<int64_t>(l) * 2 + ti) * head_dim + c]);
+  part[warp][lane] = acc;
+  __syncthreads();
+  T* out = ti == 0 ? dw0 : dw1;
+  if (warp == 0 && in_range && out != nullptr) {
+    float total = 0.f;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) total = __fadd_rn(total, part[k][lane]);
+    out[c] = Num<T>::down(total);
+  }
 }
 
 // Any even head_dim, any alignment: one warp per (batch, head, position) row, column sums by atomic adds into
@@ -1052,7 +1063,7 @@ int run_norm_rope_bwd(const NormRopeBwdArgs& a, void* dw0, void* dw1, float* scr
     launch(norm_rope_bwd_scalar_kernel<T>, static_cast<unsigned>(grid), 256, 0, st, a, scratch);
     if (int rc = after_launch("norm_rope_bwd_scalar_kernel")) return rc;
   }
-  launch(sum_lines_kernel<T>, static_cast<unsigned>(ceil_div(2 * p.head_dim, 256)), 256, 0, st, static_cast<const float*>(scratch), lines,
+  launch(sum_lines_kernel<T>, static_cast<unsigned>(ceil_div(2 * p.head_dim, 32)), 1024, 0, st, static_cast<const float*>(scratch), lines,
          p.head_dim, static_cast<T*>(dw0), static_cast<T*>(dw1));
   return after_launch("sum_lines_kernel");
 }
