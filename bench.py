@@ -399,6 +399,10 @@ def bench_extra_ops(device, peak_gbs: float, sampler, scale: float = 1.0, steps:
     heads = x.view(-1, 128)  # per-head q/k normalisation: 1,048,576 rows of 128
     run("l2_norm_bf16 [1048576, 128]", lambda: ops.l2_norm(heads), 2 * n)
     run("l2_norm_backward_bf16 [1048576, 128]", lambda: ops.l2_norm_backward(r.view(-1, 128), heads), 3 * n)
+    head_weight_row = weight[:128].contiguous()
+    run("rms_norm_bf16 [1048576, 128]", lambda: ops.rms_norm(heads, head_weight_row), 2 * n)
+    run("rms_norm_backward_bf16 [1048576, 128]", lambda: ops.rms_norm_backward(r.view(-1, 128), heads, head_weight_row), 3 * n)
+    run("layer_norm_backward_bf16 [1048576, 128]", lambda: ops.layer_norm_backward(r.view(-1, 128), heads, head_weight_row, True), 3 * n)
     del w, x, r, weight, heads
     torch.cuda.empty_cache()
 

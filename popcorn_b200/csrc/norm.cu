@@ -12,6 +12,8 @@
 #include <algorithm>
 #include <cstdlib>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "tma.cuh"
 
@@ -662,6 +664,11 @@ int run_bwd(const void* gy, const void* gs, const void* x, const void* w, void* 
   if (gs) vec = vec && ldgs % V == 0 && aligned(gs, 16);
   const T *tgy = static_cast<const T*>(gy), *tgs = static_cast<const T*>(gs), *tx = static_cast<const T*>(x), *tw = static_cast<const T*>(w);
   T* tdx = static_cast<T*>(dx);
+  if (vec && !ADD && cols / V <= 128) {
+    // narrow rows (per-head norms): a 256-thread CTA per row would leave most lanes idle; several rows per warp instead
+    const int dtype = sizeof(T) == 4 ? B200_F32 : (std::is_same<T, __half>::value ? B200_F16 : B200_BF16);
+    return rms_backward_narrow_rows(dtype, gy, x, w, dx, dw, db, static_cast<float*>(scratch), rows, cols, ldg, ldx, lddx, eps, st);
+  }
   if (vec) {
     const int nvec = static_cast<int>(cols / V);
     // ring of bulk-copied rows: as many slots as fit twice into an SM's shared memory (two CTAs per SM), at least two

@@ -17,7 +17,7 @@
 namespace b200 {
 namespace {
 
-enum Mode { kGatedSwish = 0, kGatedSigmoid = 1, kL2 = 2, kLayer = 3 };
+enum Mode { kGatedSwish = 0, kGatedSigmoid = 1, kL2 = 2, kLayer = 3, kRms = 4 };  // kRms: backward only (narrow rows of rms_norm)
 
 // Gate of the gated RMSNorm in fp32: the reference's operation sequence for fp32 tensors, the
 // corrected-ex2 / Newton forms (activations.cuh) for 16-bit ones, whose result is rounded to T anyway.
@@ -518,11 +518,11 @@ template <typename T, int TPR, int ITEMS, int MODE, int RU>
 __global__ void __launch_bounds__(256, 2)
 family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const T* __restrict__ weight, T* __restrict__ dx,
                        float* __restrict__ partial, int64_t rows, int nvec, int64_t ldg, int64_t ldx, int64_t lddx,
-                       float cols_f, float eps, int has_bias) {
+                       float cols_f, float eps, int has_bias, int line_arrays) {
   constexpr int V = Num<T>::kVec;
   constexpr int P = V / 2;  // fp32 pairs per word
   constexpr int GROUPS = 256 / TPR;
-  constexpr bool LAYER = MODE == kLayer;
+  constexpr bool LAYER = MODE == kLayer || MODE == kRms;  // modes with a weight: dw (and db) partials per thread
   constexpr bool KEEP_W = ITEMS < 4;  // wide rows re-read their weight words (L1 hits) instead of holding them in registers
   static_assert(RU == 1 || TPR <= 32, "several rows per group only for rows that fit a warp");
   pdl_prologue();
@@ -596,6 +596,43 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
           for (int j = 0; j < P; ++j) unpack_f2(fma_f2(fg[j], sc2, mul_f2(fx[j], coef2)), out[2 * j], out[2 * j + 1]);
           if (live && col_ok[i]) st_stream(dx + row * lddx + static_cast<int64_t>(lane_in_row + i * TPR) * V, Num<T>::pack(out));
         }
+      } else if constexpr (MODE == kRms) {
+        // y = x r w (+ b), r = 1 / sqrt(mean x^2 + eps):  dx = gw r - x r^3 <gw, x> / n,  dw += g x r,  db += g
+        Float2x ss2 = pack_f2(0.f, 0.f), dot2 = ss2;
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+          if (!col_ok[i]) continue;
+          Float2x fx[P], fg[P], fw[P];
+          unpack_pairs<T>(xv[u][i], fx);
+          unpack_pairs<T>(gv[u][i], fg);
+          unpack_pairs<T>(weight_word(i), fw);
+#pragma unroll
+          for (int j = 0; j < P; ++j) {
+            ss2 = fma_f2(fx[j], fx[j], ss2);
+            dot2 = fma_f2(mul_f2(fg[j], fw[j]), fx[j], dot2);
+          }
+        }
+        float sums[2] = {pair_total(ss2), pair_total(dot2)};
+        row_sums<TPR, 2>(sums, &slots[parity * 2]);
+        const float r = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(sums[0], cols_f), eps)));
+        const float coef = -__fdiv_rn(__fmul_rn(__fmul_rn(__fmul_rn(r, r), r), sums[1]), cols_f);
+        const Float2x r2 = pack_f2(r, r), coef2 = pack_f2(coef, coef);
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+          if (!col_ok[i]) continue;
+          Float2x fx[P], fg[P], fw[P];
+          unpack_pairs<T>(xv[u][i], fx);
+          unpack_pairs<T>(gv[u][i], fg);
+          unpack_pairs<T>(weight_word(i), fw);
+          float out[V];
+#pragma unroll
+          for (int j = 0; j < P; ++j) {
+            dw[i][j] = fma_f2(fg[j], mul_f2(fx[j], r2), dw[i][j]);
+            db[i][j] = add_f2(db[i][j], fg[j]);
+            unpack_f2(fma_f2(mul_f2(fg[j], fw[j]), r2, mul_f2(fx[j], coef2)), out[2 * j], out[2 * j + 1]);
+          }
+          if (live) st_stream(dx + row * lddx + static_cast<int64_t>(lane_in_row + i * TPR) * V, Num<T>::pack(out));
+        }
       } else {
         Float2x sx2 = pack_f2(0.f, 0.f), s12 = sx2, sgx2 = sx2;
 #pragma unroll
@@ -657,8 +694,8 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
     }
   }
   if constexpr (LAYER) {
-    // this CTA's line of the partial sums: [0][cols] for dw, [1][cols] for db
-    float* line = partial + static_cast<int64_t>(blockIdx.x) * 2 * nvec * V;
+    // this CTA's line of the partial sums: [0][cols] for dw, [1][cols] for db (line_arrays = 1: dw only)
+    float* line = partial + static_cast<int64_t>(blockIdx.x) * line_arrays * nvec * V;
     if constexpr (GROUPS > 1) {
       // fold the row groups in group order: group 0 stores, every later group adds, one barrier per group
       for (int g = 0; g < GROUPS; ++g) {
@@ -712,7 +749,7 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
 // eight partial sums are added in warp order, so the result does not depend on timing.
 template <typename T>
 __global__ void __launch_bounds__(256)
-family_sum_lines_kernel(const float* __restrict__ partial, int lines, int64_t cols, T* __restrict__ dw, T* __restrict__ db) {
+family_sum_lines_kernel(const float* __restrict__ partial, int lines, int line_arrays, int64_t cols, T* __restrict__ dw, T* __restrict__ db) {
   pdl_prologue();
   __shared__ float part[2][8][32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -720,8 +757,8 @@ family_sum_lines_kernel(const float* __restrict__ partial, int lines, int64_t co
   float aw = 0.f, ab = 0.f;
   if (c < cols) {
     for (int l = warp; l < lines; l += 8) {
-      aw = __fadd_rn(aw, partial[(static_cast<int64_t>(l) * 2) * cols + c]);
-      if (db != nullptr) ab = __fadd_rn(ab, partial[(static_cast<int64_t>(l) * 2 + 1) * cols + c]);
+      aw = __fadd_rn(aw, partial[(static_cast<int64_t>(l) * line_arrays) * cols + c]);
+      if (db != nullptr) ab = __fadd_rn(ab, partial[(static_cast<int64_t>(l) * line_arrays + 1) * cols + c]);
     }
   }
   part[0][warp][lane] = aw;
@@ -769,7 +806,7 @@ int run_bwd(const void* gy, const void* x, const void* w, void* dx, void* dw, vo
   do {                                                                                                                           \
     lines = family_bwd_ctas(rows, 256 / TPR * RU);                                                                               \
     launch(family_bwd_rows_kernel<T, TPR, ITEMS, MODE, RU>, static_cast<unsigned>(lines), 256, 0, st, tg, tx, tw, tdx, scratch, rows, \
-           nvec, ldg, ldx, lddx, cols_f, eps, bias);                                                                             \
+           nvec, ldg, ldx, lddx, cols_f, eps, bias, 2);                                                                          \
   } while (0)
     if (nvec <= 8) B200_FAMILY_BWD(8, 1, 4);
     else if (nvec <= 16) B200_FAMILY_BWD(16, 1, 4);
@@ -788,11 +825,39 @@ int run_bwd(const void* gy, const void* x, const void* w, void* dx, void* dw, vo
     if (int rc = after_launch("family_bwd_kernel")) return rc;
   }
   if (MODE == kLayer) {
-    launch(family_sum_lines_kernel<T>, static_cast<unsigned>(ceil_div(cols, 32)), 256, 0, st, static_cast<const float*>(scratch), lines, cols,
+    launch(family_sum_lines_kernel<T>, static_cast<unsigned>(ceil_div(cols, 32)), 256, 0, st, static_cast<const float*>(scratch), lines, 2, cols,
            static_cast<T*>(dw), static_cast<T*>(db));
     return after_launch("family_sum_lines_kernel");
   }
   return B200_OK;
+}
+
+template <typename T>
+int run_rms_narrow(const void* gy, const void* x, const void* w, void* dx, void* dw, void* db, float* scratch, int64_t rows, int nvec,
+                   int64_t ldg, int64_t ldx, int64_t lddx, float eps, cudaStream_t st) {
+  constexpr int V = Num<T>::kVec;
+  const T *tg = static_cast<const T*>(gy), *tx = static_cast<const T*>(x), *tw = static_cast<const T*>(w);
+  T* tdx = static_cast<T*>(dx);
+  const int64_t cols = static_cast<int64_t>(nvec) * V;
+  const float cols_f = static_cast<float>(cols);
+  const int bias = db != nullptr ? 1 : 0, arrays = bias ? 2 : 1;
+  int lines = 0;
+#define B200_RMS_NARROW(TPR, ITEMS, RU)                                                                                       \
+  do {                                                                                                                        \
+    lines = family_bwd_ctas(rows, 256 / TPR * RU);                                                                            \
+    launch(family_bwd_rows_kernel<T, TPR, ITEMS, kRms, RU>, static_cast<unsigned>(lines), 256, 0, st, tg, tx, tw, tdx, scratch, rows, \
+           nvec, ldg, ldx, lddx, cols_f, eps, bias, arrays);                                                                  \
+  } while (0)
+  if (nvec <= 8) B200_RMS_NARROW(8, 1, 4);
+  else if (nvec <= 16) B200_RMS_NARROW(16, 1, 4);
+  else if (nvec <= 32) B200_RMS_NARROW(32, 1, 4);
+  else if (nvec <= 64) B200_RMS_NARROW(32, 2, 1);
+  else B200_RMS_NARROW(32, 4, 1);
+#undef B200_RMS_NARROW
+  if (int rc = after_launch("family_bwd_rows_kernel")) return rc;
+  launch(family_sum_lines_kernel<T>, static_cast<unsigned>(ceil_div(cols, 32)), 256, 0, st, static_cast<const float*>(scratch), lines, arrays, cols,
+         static_cast<T*>(dw), static_cast<T*>(db));
+  return after_launch("family_sum_lines_kernel");
 }
 
 int bwd_entry(const char* fn, int mode, const void* gy, const void* x, const void* weight, void* dx, void* dw, void* db,
@@ -826,6 +891,15 @@ int bwd_entry(const char* fn, int mode, const void* gy, const void* x, const voi
 }
 
 }  // namespace
+
+int rms_backward_narrow_rows(int dtype, const void* gy, const void* x, const void* w, void* dx, void* dw, void* db, float* scratch,
+                             int64_t rows, int64_t cols, int64_t ldg, int64_t ldx, int64_t lddx, float eps, cudaStream_t st) {
+  B200_DISPATCH_DTYPE(dtype, T, {
+    return run_rms_narrow<T>(gy, x, w, dx, dw, db, scratch, rows, static_cast<int>(cols / Num<T>::kVec), ldg, ldx, lddx, eps, st);
+  });
+  return B200_ERR_DTYPE;
+}
+
 }  // namespace b200
 
 using namespace b200;
