@@ -832,32 +832,40 @@ __global__ void __launch_bounds__(256, 2) norm_rope_bwd_kernel(const NormRopeBwd
     }
   };
   // One half row (a 128-bit word x, the matching word g of the rotated-back gradient, the weight word w):
-  // adds round_T(g * round_T(x r)) to the column sums, leaves u = round_T(g * w) in `u` and returns <u, x>.
-  auto half_row = [](uint4 xw, uint4 gw, uint4 ww, float r, bool active, float (&acc)[V], float (&x)[V], float (&u)[V]) {
-    Num<T>::unpack(xw, x);
-    float dot = 0.f;
+  // adds round_T(g * round_T(x r)) to the column sums, leaves u = round_T(g * w) and x as fp32 pairs and returns the
+  // two partial sums of <u, x>.  fp32 arithmetic two elements per instruction, every element rounded on its own.
+  constexpr int P = V / 2;
+  auto half_row = [](uint4 xw, uint4 gw, uint4 ww, Float2x r2, bool active, Float2x (&acc)[P], Float2x (&x)[P], Float2x (&u)[P], Float2x dot) {
+    float fx[V];
+    Num<T>::unpack(xw, fx);
+#pragma unroll
+    for (int j = 0; j < P; ++j) x[j] = pack_f2(fx[2 * j], fx[2 * j + 1]);
     if constexpr (sizeof(T) == 4) {
       float g[V], w[V];
       Num<T>::unpack(gw, g);
       Num<T>::unpack(ww, w);
 #pragma unroll
-      for (int j = 0; j < V; ++j) {
-        if (active) acc[j] = __fadd_rn(acc[j], __fmul_rn(g[j], __fmul_rn(x[j], r)));
-        u[j] = __fmul_rn(g[j], w[j]);
-        dot = __fmaf_rn(u[j], x[j], dot);
+      for (int j = 0; j < P; ++j) {
+        const Float2x g2 = pack_f2(g[2 * j], g[2 * j + 1]);
+        const Float2x term = mul_f2(g2, mul_f2(x[j], r2));
+        float t0, t1, a0, a1;
+        unpack_f2(term, t0, t1);
+        unpack_f2(acc[j], a0, a1);
+        if (active) acc[j] = pack_f2(__fadd_rn(a0, t0), __fadd_rn(a1, t1));  // separate product and sum, as in the reference
+        u[j] = mul_f2(g2, pack_f2(w[2 * j], w[2 * j + 1]));
+        dot = fma_f2(u[j], x[j], dot);
       }
     } else {
       const uint32_t wg[4] = {gw.x, gw.y, gw.z, gw.w}, wwt[4] = {ww.x, ww.y, ww.z, ww.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        float a0, a1;
-        Num<T>::unpack2(Num<T>::mul2(wg[j], Num<T>::pack2(__fmul_rn(x[2 * j], r), __fmul_rn(x[2 * j + 1], r))), a0, a1);
-        if (active) {
-          acc[2 * j] = __fadd_rn(acc[2 * j], a0);
-          acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], a1);
-        }
-        Num<T>::unpack2(Num<T>::mul2(wg[j], wwt[j]), u[2 * j], u[2 * j + 1]);
-        dot = __fmaf_rn(u[2 * j + 1], x[2 * j + 1], __fmaf_rn(u[2 * j], x[2 * j], dot));
+        float n0, n1, a0, a1, u0, u1;
+        unpack_f2(mul_f2(x[j], r2), n0, n1);
+        Num<T>::unpack2(Num<T>::mul2(wg[j], Num<T>::pack2(n0, n1)), a0, a1);
+        if (active) acc[j] = add_f2(acc[j], pack_f2(a0, a1));
+        Num<T>::unpack2(Num<T>::mul2(wg[j], wwt[j]), u0, u1);
+        u[j] = pack_f2(u0, u1);
+        dot = fma_f2(u[j], x[j], dot);
       }
     }
     return dot;
@@ -866,9 +874,9 @@ __global__ void __launch_bounds__(256, 2) norm_rope_bwd_kernel(const NormRopeBwd
   constexpr int UNROLL = 2;  // heads in flight per thread
   for (int ti = 0; ti < 2; ++ti) {
     const PairedTensor& t = p.t[ti];
-    float acc_lo[V], acc_hi[V];
+    Float2x acc_lo2[P], acc_hi2[P];
 #pragma unroll
-    for (int j = 0; j < V; ++j) acc_lo[j] = acc_hi[j] = 0.f;
+    for (int j = 0; j < P; ++j) acc_lo2[j] = acc_hi2[j] = pack_f2(0.f, 0.f);
     if (t.heads > 0) {
       const uint4 w1 = ld_reuse(static_cast<const T*>(p.weight[ti]) + unit * V);
       const uint4 w2 = ld_reuse(static_cast<const T*>(p.weight[ti]) + unit * V + half);
@@ -890,32 +898,55 @@ __global__ void __launch_bounds__(256, 2) norm_rope_bwd_kernel(const NormRopeBwd
 #pragma unroll
         for (int q = 0; q < UNROLL; ++q) {
           if (h0 + q < t.heads) {  // uniform over the CTA
-            float x1[V], x2[V], u1[V], u2[V];
-            Num<T>::unpack(x_lo[q], x1);
-            Num<T>::unpack(x_hi[q], x2);
-            float ss = 0.f;
+            Float2x x1[P], x2[P], u1[P], u2[P];
+            float ss;
+            {
+              float f1[V], f2[V];
+              Num<T>::unpack(x_lo[q], f1);
+              Num<T>::unpack(x_hi[q], f2);
+              Float2x ss2 = pack_f2(0.f, 0.f);
 #pragma unroll
-            for (int j = 0; j < V; ++j) ss = __fmaf_rn(x2[j], x2[j], __fmaf_rn(x1[j], x1[j], ss));
+              for (int j = 0; j < P; ++j) {
+                const Float2x p1 = pack_f2(f1[2 * j], f1[2 * j + 1]), p2 = pack_f2(f2[2 * j], f2[2 * j + 1]);
+                ss2 = fma_f2(p2, p2, fma_f2(p1, p1, ss2));
+              }
+              float s0, s1;
+              unpack_f2(ss2, s0, s1);
+              ss = __fadd_rn(s0, s1);
+            }
             for (int o = upr >> 1; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
             const float r = inv_rms(ss, cols_f, inv_cols, p.eps);
+            const Float2x r2 = pack_f2(r, r);
             const uint4 g1 = rotate_back(d_lo[q], c1w, d_hi[q], s2w, false);  // g1 = dy1 c1 + dy2 s2
             const uint4 g2 = rotate_back(d_hi[q], c2w, d_lo[q], s1w, true);   // g2 = dy2 c2 - dy1 s1
-            float dot = half_row(x_lo[q], g1, w1, r, active, acc_lo, x1, u1) + half_row(x_hi[q], g2, w2, r, active, acc_hi, x2, u2);
+            Float2x dot2 = half_row(x_lo[q], g1, w1, r2, active, acc_lo2, x1, u1, pack_f2(0.f, 0.f));
+            dot2 = half_row(x_hi[q], g2, w2, r2, active, acc_hi2, x2, u2, dot2);
+            float dot, dot_hi;
+            unpack_f2(dot2, dot, dot_hi);
+            dot = __fadd_rn(dot, dot_hi);
             for (int o = upr >> 1; o > 0; o >>= 1) dot = __fadd_rn(dot, __shfl_xor_sync(0xffffffffu, dot, o));
             const float dot_over_n = inv_cols > 0.f ? __fmul_rn(dot, inv_cols) : __fdiv_rn(dot, cols_f);
             const float coef = -__fmul_rn(__fmul_rn(__fmul_rn(r, r), r), dot_over_n);
+            const Float2x coef2 = pack_f2(coef, coef);
+            float o1[V], o2[V];
 #pragma unroll
-            for (int j = 0; j < V; ++j) {
-              u1[j] = __fmaf_rn(u1[j], r, __fmul_rn(x1[j], coef));
-              u2[j] = __fmaf_rn(u2[j], r, __fmul_rn(x2[j], coef));
+            for (int j = 0; j < P; ++j) {
+              unpack_f2(fma_f2(u1[j], r2, mul_f2(x1[j], coef2)), o1[2 * j], o1[2 * j + 1]);
+              unpack_f2(fma_f2(u2[j], r2, mul_f2(x2[j], coef2)), o2[2 * j], o2[2 * j + 1]);
             }
             if (active) {
-              st_stream(dx + (h0 + q) * t.os_h, Num<T>::pack(u1));
-              st_stream(dx + (h0 + q) * t.os_h + half, Num<T>::pack(u2));
+              st_stream(dx + (h0 + q) * t.os_h, Num<T>::pack(o1));
+              st_stream(dx + (h0 + q) * t.os_h + half, Num<T>::pack(o2));
             }
           }
         }
       }
+    }
+    float acc_lo[V], acc_hi[V];
+#pragma unroll
+    for (int j = 0; j < P; ++j) {
+      unpack_f2(acc_lo2[j], acc_lo[2 * j], acc_lo[2 * j + 1]);
+      unpack_f2(acc_hi2[j], acc_hi[2 * j], acc_hi[2 * j + 1]);
     }
     // column sums of this CTA: lanes with the same unit sit `upr` apart inside a warp
 #pragma unroll
