@@ -466,25 +466,30 @@ family_bwd_kernel(const T* __restrict__ gy, const T* __restrict__ x, const T* __
   }
 }
 
-// N sums over the TPR threads of a row with one barrier (TPR == 256) or shuffles only; `slot` is [N][8].
+// N sums over the TPR threads of a row: shuffles only (TPR <= 32), or one barrier per call: the CTA-wide one when the
+// row owns the CTA (TPR == 256), a named barrier of the row's TPR threads when several rows share it (TPR 64 or 128;
+// `group` is the row's index in the CTA).  `slot` is this row's [N][8] piece of shared memory.
 template <int TPR, int N>
-__device__ __forceinline__ void row_sums(float (&v)[N], float (*slot)[8]) {
+__device__ __forceinline__ void row_sums(float (&v)[N], float (*slot)[8], int group) {
 #pragma unroll
   for (int o = (TPR < 32 ? TPR : 32) / 2; o > 0; o >>= 1) {
 #pragma unroll
     for (int n = 0; n < N; ++n) v[n] = __fadd_rn(v[n], __shfl_xor_sync(0xffffffffu, v[n], o));
   }
   if constexpr (TPR > 32) {
+    constexpr int WARPS = TPR / 32;
+    const int warp_in_row = (threadIdx.x >> 5) % WARPS;
     if ((threadIdx.x & 31) == 0) {
 #pragma unroll
-      for (int n = 0; n < N; ++n) slot[n][threadIdx.x >> 5] = v[n];
+      for (int n = 0; n < N; ++n) slot[n][warp_in_row] = v[n];
     }
-    __syncthreads();
+    if constexpr (TPR == 256) __syncthreads();
+    else asm volatile("bar.sync %0, %1;" ::"r"(1 + group), "r"(TPR) : "memory");
 #pragma unroll
     for (int n = 0; n < N; ++n) {
       float total = 0.f;
 #pragma unroll
-      for (int k = 0; k < TPR / 32; ++k) total = __fadd_rn(total, slot[n][k]);
+      for (int k = 0; k < WARPS; ++k) total = __fadd_rn(total, slot[n][k]);
       v[n] = total;
     }
   }
@@ -518,7 +523,7 @@ template <typename T, int TPR, int ITEMS, int MODE, int RU>
 __global__ void __launch_bounds__(256, 2)
 family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const T* __restrict__ weight, T* __restrict__ dx,
                        float* __restrict__ partial, int64_t rows, int nvec, int64_t ldg, int64_t ldx, int64_t lddx,
-                       float cols_f, float eps, int has_bias, int line_arrays) {
+                       float cols_f, float eps, int has_bias, int line_arrays, const T* __restrict__ gs, int64_t ldgs, float offset) {
   constexpr int V = Num<T>::kVec;
   constexpr int P = V / 2;  // fp32 pairs per word
   constexpr int GROUPS = 256 / TPR;
@@ -526,10 +531,12 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
   constexpr bool KEEP_W = ITEMS < 4;  // wide rows re-read their weight words (L1 hits) instead of holding them in registers
   static_assert(RU == 1 || TPR <= 32, "several rows per group only for rows that fit a warp");
   pdl_prologue();
-  __shared__ float slots[4][8];
+  constexpr int SLOT_GROUPS = (TPR > 32 && TPR < 256) ? GROUPS : 1;  // rows that meet at a barrier of their own
+  __shared__ float slot_store[SLOT_GROUPS][4][8];
   __shared__ float fold[LAYER && GROUPS > 1 ? 2 * TPR * ITEMS * V : 1];
   const int tid = threadIdx.x;
   const int sub = tid / TPR, lane_in_row = tid % TPR;
+  float(*slots)[8] = slot_store[SLOT_GROUPS > 1 ? sub : 0];
   bool col_ok[ITEMS];
   uint4 wv[LAYER && KEEP_W ? ITEMS : 1];
   auto weight_word = [&](int i) { return KEEP_W ? wv[KEEP_W ? i : 0] : ld_reuse(weight + static_cast<int64_t>(lane_in_row + i * TPR) * V); };
@@ -582,7 +589,7 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
           }
         }
         float sums[2] = {pair_total(ss2), pair_total(dot2)};
-        row_sums<TPR, 2>(sums, &slots[parity * 2]);
+        row_sums<TPR, 2>(sums, &slots[parity * 2], sub);
         const float sc = __frcp_rn(__fsqrt_rn(__fadd_rn(sums[0], eps)));
         const float coef = -__fmul_rn(__fmul_rn(__fmul_rn(sc, sc), sc), sums[1]);
         const Float2x sc2 = pack_f2(sc, sc), coef2 = pack_f2(coef, coef);
@@ -597,7 +604,22 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
           if (live && col_ok[i]) st_stream(dx + row * lddx + static_cast<int64_t>(lane_in_row + i * TPR) * V, Num<T>::pack(out));
         }
       } else if constexpr (MODE == kRms) {
-        // y = x r w (+ b), r = 1 / sqrt(mean x^2 + eps):  dx = gw r - x r^3 <gw, x> / n,  dw += g x r,  db += g
+        // y = x r w (+ b), r = 1 / sqrt(mean x^2 + eps):  dx = gw r - x r^3 <gw, x> / n,  dw += g x r,  db += g.
+        // add_rms_norm's backward is the same on s = x + residual with w = round_T(weight + offset), plus the
+        // gradient that arrived for s itself (gs): dx = round_T(dx) + gs.
+        const Float2x offset2 = pack_f2(offset, offset);
+        auto effective_weight = [&](int i, Float2x (&fw)[P]) {
+          unpack_pairs<T>(weight_word(i), fw);
+          if (offset != 0.f) {
+#pragma unroll
+            for (int j = 0; j < P; ++j) {
+              float lo, hi;
+              unpack_f2(add_f2(fw[j], offset2), lo, hi);
+              if constexpr (sizeof(T) == 2) Num<T>::round2(lo, hi);
+              fw[j] = pack_f2(lo, hi);
+            }
+          }
+        };
         Float2x ss2 = pack_f2(0.f, 0.f), dot2 = ss2;
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
@@ -605,7 +627,7 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
           Float2x fx[P], fg[P], fw[P];
           unpack_pairs<T>(xv[u][i], fx);
           unpack_pairs<T>(gv[u][i], fg);
-          unpack_pairs<T>(weight_word(i), fw);
+          effective_weight(i, fw);
 #pragma unroll
           for (int j = 0; j < P; ++j) {
             ss2 = fma_f2(fx[j], fx[j], ss2);
@@ -613,7 +635,7 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
           }
         }
         float sums[2] = {pair_total(ss2), pair_total(dot2)};
-        row_sums<TPR, 2>(sums, &slots[parity * 2]);
+        row_sums<TPR, 2>(sums, &slots[parity * 2], sub);
         const float r = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(sums[0], cols_f), eps)));
         const float coef = -__fdiv_rn(__fmul_rn(__fmul_rn(__fmul_rn(r, r), r), sums[1]), cols_f);
         const Float2x r2 = pack_f2(r, r), coef2 = pack_f2(coef, coef);
@@ -623,13 +645,23 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
           Float2x fx[P], fg[P], fw[P];
           unpack_pairs<T>(xv[u][i], fx);
           unpack_pairs<T>(gv[u][i], fg);
-          unpack_pairs<T>(weight_word(i), fw);
+          effective_weight(i, fw);
           float out[V];
 #pragma unroll
           for (int j = 0; j < P; ++j) {
             dw[i][j] = fma_f2(fg[j], mul_f2(fx[j], r2), dw[i][j]);
             db[i][j] = add_f2(db[i][j], fg[j]);
             unpack_f2(fma_f2(mul_f2(fg[j], fw[j]), r2, mul_f2(fx[j], coef2)), out[2 * j], out[2 * j + 1]);
+          }
+          if (gs != nullptr && live) {
+            float extra[V];
+            Num<T>::unpack(ld_stream(gs + row * ldgs + static_cast<int64_t>(lane_in_row + i * TPR) * V), extra);
+#pragma unroll
+            for (int j = 0; j < V; j += 2) {
+              if constexpr (sizeof(T) == 2) Num<T>::round2(out[j], out[j + 1]);
+              out[j] = __fadd_rn(out[j], extra[j]);
+              out[j + 1] = __fadd_rn(out[j + 1], extra[j + 1]);
+            }
           }
           if (live) st_stream(dx + row * lddx + static_cast<int64_t>(lane_in_row + i * TPR) * V, Num<T>::pack(out));
         }
@@ -651,7 +683,7 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
           }
         }
         float first[3] = {pair_total(sx2), pair_total(s12), pair_total(sgx2)};
-        row_sums<TPR, 3>(first, &slots[0]);
+        row_sums<TPR, 3>(first, &slots[0], sub);
         const float mean = __fdiv_rn(first[0], cols_f);
         const Float2x mean2 = pack_f2(mean, mean);
         Float2x var2 = pack_f2(0.f, 0.f);
@@ -667,7 +699,7 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
           }
         }
         float second[1] = {pair_total(var2)};
-        row_sums<TPR, 1>(second, &slots[3]);
+        row_sums<TPR, 1>(second, &slots[3], sub);
         const float rstd = __frcp_rn(__fsqrt_rn(__fadd_rn(fmaxf(__fdiv_rn(second[0], cols_f), 0.f), eps)));
         const float m1 = __fdiv_rn(first[1], cols_f);                                                     // mean of g w
         const float m2 = __fdiv_rn(__fmul_rn(__fsub_rn(first[2], __fmul_rn(mean, first[1])), rstd), cols_f);  // mean of g w xhat
@@ -806,15 +838,15 @@ int run_bwd(const void* gy, const void* x, const void* w, void* dx, void* dw, vo
   do {                                                                                                                           \
     lines = family_bwd_ctas(rows, 256 / TPR * RU);                                                                               \
     launch(family_bwd_rows_kernel<T, TPR, ITEMS, MODE, RU>, static_cast<unsigned>(lines), 256, 0, st, tg, tx, tw, tdx, scratch, rows, \
-           nvec, ldg, ldx, lddx, cols_f, eps, bias, 2);                                                                          \
+           nvec, ldg, ldx, lddx, cols_f, eps, bias, 2, static_cast<const T*>(nullptr), 0, 0.f);                                  \
   } while (0)
     if (nvec <= 8) B200_FAMILY_BWD(8, 1, 4);
     else if (nvec <= 16) B200_FAMILY_BWD(16, 1, 4);
     else if (nvec <= 32) B200_FAMILY_BWD(32, 1, 4);
     else if (nvec <= 64) B200_FAMILY_BWD(32, 2, 1);
     else if (nvec <= 128) B200_FAMILY_BWD(32, 4, 1);
-    else if (nvec <= 256) B200_FAMILY_BWD(256, 1, 1);
-    else if (nvec <= 512) B200_FAMILY_BWD(256, 2, 1);
+    else if (nvec <= 256) B200_FAMILY_BWD(64, 4, 1);
+    else if (nvec <= 512) B200_FAMILY_BWD(128, 4, 1);
     else B200_FAMILY_BWD(256, 4, 1);
 #undef B200_FAMILY_BWD
     if (int rc = after_launch("family_bwd_rows_kernel")) return rc;
@@ -833,8 +865,8 @@ int run_bwd(const void* gy, const void* x, const void* w, void* dx, void* dw, vo
 }
 
 template <typename T>
-int run_rms_narrow(const void* gy, const void* x, const void* w, void* dx, void* dw, void* db, float* scratch, int64_t rows, int nvec,
-                   int64_t ldg, int64_t ldx, int64_t lddx, float eps, cudaStream_t st) {
+int run_rms_narrow(const void* gy, const void* gs, const void* x, const void* w, void* dx, void* dw, void* db, float* scratch, int64_t rows,
+                   int nvec, int64_t ldg, int64_t ldgs, int64_t ldx, int64_t lddx, float eps, float offset, cudaStream_t st) {
   constexpr int V = Num<T>::kVec;
   const T *tg = static_cast<const T*>(gy), *tx = static_cast<const T*>(x), *tw = static_cast<const T*>(w);
   T* tdx = static_cast<T*>(dx);
@@ -846,13 +878,16 @@ int run_rms_narrow(const void* gy, const void* x, const void* w, void* dx, void*
   do {                                                                                                                        \
     lines = family_bwd_ctas(rows, 256 / TPR * RU);                                                                            \
     launch(family_bwd_rows_kernel<T, TPR, ITEMS, kRms, RU>, static_cast<unsigned>(lines), 256, 0, st, tg, tx, tw, tdx, scratch, rows, \
-           nvec, ldg, ldx, lddx, cols_f, eps, bias, arrays);                                                                  \
+           nvec, ldg, ldx, lddx, cols_f, eps, bias, arrays, static_cast<const T*>(gs), ldgs, offset);                         \
   } while (0)
   if (nvec <= 8) B200_RMS_NARROW(8, 1, 4);
   else if (nvec <= 16) B200_RMS_NARROW(16, 1, 4);
   else if (nvec <= 32) B200_RMS_NARROW(32, 1, 4);
   else if (nvec <= 64) B200_RMS_NARROW(32, 2, 1);
-  else B200_RMS_NARROW(32, 4, 1);
+  else if (nvec <= 128) B200_RMS_NARROW(32, 4, 1);
+  else if (nvec <= 256) B200_RMS_NARROW(64, 4, 1);
+  else if (nvec <= 512) B200_RMS_NARROW(128, 4, 1);
+  else B200_RMS_NARROW(256, 4, 1);
 #undef B200_RMS_NARROW
   if (int rc = after_launch("family_bwd_rows_kernel")) return rc;
   launch(family_sum_lines_kernel<T>, static_cast<unsigned>(ceil_div(cols, 32)), 256, 0, st, static_cast<const float*>(scratch), lines, arrays, cols,
@@ -892,10 +927,11 @@ int bwd_entry(const char* fn, int mode, const void* gy, const void* x, const voi
 
 }  // namespace
 
-int rms_backward_narrow_rows(int dtype, const void* gy, const void* x, const void* w, void* dx, void* dw, void* db, float* scratch,
-                             int64_t rows, int64_t cols, int64_t ldg, int64_t ldx, int64_t lddx, float eps, cudaStream_t st) {
+int rms_backward_narrow_rows(int dtype, const void* gy, const void* gs, const void* x, const void* w, void* dx, void* dw, void* db,
+                             float* scratch, int64_t rows, int64_t cols, int64_t ldg, int64_t ldgs, int64_t ldx, int64_t lddx, float eps,
+                             float offset, cudaStream_t st) {
   B200_DISPATCH_DTYPE(dtype, T, {
-    return run_rms_narrow<T>(gy, x, w, dx, dw, db, scratch, rows, static_cast<int>(cols / Num<T>::kVec), ldg, ldx, lddx, eps, st);
+    return run_rms_narrow<T>(gy, gs, x, w, dx, dw, db, scratch, rows, static_cast<int>(cols / Num<T>::kVec), ldg, ldgs, ldx, lddx, eps, offset, st);
   });
   return B200_ERR_DTYPE;
 }
