@@ -31,12 +31,12 @@ unsigned int norm_wait_timeouts();
 unsigned int gemm_wait_timeouts();
 // rms_norm / add_rms_norm backward through the row-bucket kernel of norm_family.cu (rows of at most 1024 128-bit
 // words held in registers; narrow rows several per warp).  gs: the gradient that arrived for the sum s of
-// add_rms_norm, or nullptr; offset: added to the weight (0 for rms_norm).  All pointers 16-byte aligned, cols and
+// add_rms_norm, or nullptr; offset: added to the weight; add = false ignores both (rms_norm).  All pointers 16-byte aligned, cols and
 // the strides multiples of the word; scratch as for b200_rms_norm_backward.  Called from norm.cu, which decides
 // which shapes take this path.
 int rms_backward_narrow_rows(int dtype, const void* gy, const void* gs, const void* x, const void* w, void* dx, void* dw, void* db,
                              float* scratch, int64_t rows, int64_t cols, int64_t ldg, int64_t ldgs, int64_t ldx, int64_t lddx, float eps,
-                             float offset, cudaStream_t st);
+                             float offset, bool add, cudaStream_t st);
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 inline size_t dtype_size(int dtype) { return dtype == B200_F32 ? 4 : 2; }

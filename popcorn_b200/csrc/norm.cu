@@ -682,7 +682,7 @@ int run_bwd(const void* gy, const void* gs, const void* x, const void* w, void* 
     // short rows: a 256-thread CTA per row would leave lanes idle or spend its time at barriers; 8 to 128 threads per row instead
     const int dtype = sizeof(T) == 4 ? B200_F32 : (std::is_same<T, __half>::value ? B200_F16 : B200_BF16);
     return rms_backward_narrow_rows(dtype, gy, gs, x, w, dx, dw, db, static_cast<float*>(scratch), rows, cols, ldg, ldgs, ldx, lddx, eps,
-                                    ADD ? offset : 0.f, st);
+                                    offset, ADD, st);
   }
   if (vec) {
     const int nvec = static_cast<int>(cols / V);

@@ -17,7 +17,7 @@
 namespace b200 {
 namespace {
 
-enum Mode { kGatedSwish = 0, kGatedSigmoid = 1, kL2 = 2, kLayer = 3, kRms = 4 };  // kRms: backward only (narrow rows of rms_norm)
+enum Mode { kGatedSwish = 0, kGatedSigmoid = 1, kL2 = 2, kLayer = 3, kRms = 4, kRmsAdd = 5 };  // kRms / kRmsAdd: backward only (rms_norm, add_rms_norm on short rows)
 
 // Gate of the gated RMSNorm in fp32: the reference's operation sequence for fp32 tensors, the
 // corrected-ex2 / Newton forms (activations.cuh) for 16-bit ones, whose result is rounded to T anyway.
@@ -527,7 +527,7 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
   constexpr int V = Num<T>::kVec;
   constexpr int P = V / 2;  // fp32 pairs per word
   constexpr int GROUPS = 256 / TPR;
-  constexpr bool LAYER = MODE == kLayer || MODE == kRms;  // modes with a weight: dw (and db) partials per thread
+  constexpr bool LAYER = MODE == kLayer || MODE == kRms || MODE == kRmsAdd;  // modes with a weight: dw (and db) partials per thread
   constexpr bool KEEP_W = ITEMS < 4;  // wide rows re-read their weight words (L1 hits) instead of holding them in registers
   static_assert(RU == 1 || TPR <= 32, "several rows per group only for rows that fit a warp");
   pdl_prologue();
@@ -603,14 +603,14 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
           for (int j = 0; j < P; ++j) unpack_f2(fma_f2(fg[j], sc2, mul_f2(fx[j], coef2)), out[2 * j], out[2 * j + 1]);
           if (live && col_ok[i]) st_stream(dx + row * lddx + static_cast<int64_t>(lane_in_row + i * TPR) * V, Num<T>::pack(out));
         }
-      } else if constexpr (MODE == kRms) {
+      } else if constexpr (MODE == kRms || MODE == kRmsAdd) {
         // y = x r w (+ b), r = 1 / sqrt(mean x^2 + eps):  dx = gw r - x r^3 <gw, x> / n,  dw += g x r,  db += g.
         // add_rms_norm's backward is the same on s = x + residual with w = round_T(weight + offset), plus the
         // gradient that arrived for s itself (gs): dx = round_T(dx) + gs.
         const Float2x offset2 = pack_f2(offset, offset);
         auto effective_weight = [&](int i, Float2x (&fw)[P]) {
           unpack_pairs<T>(weight_word(i), fw);
-          if (offset != 0.f) {
+          if constexpr (MODE == kRmsAdd) {
 #pragma unroll
             for (int j = 0; j < P; ++j) {
               float lo, hi;
@@ -653,7 +653,7 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
             db[i][j] = add_f2(db[i][j], fg[j]);
             unpack_f2(fma_f2(mul_f2(fg[j], fw[j]), r2, mul_f2(fx[j], coef2)), out[2 * j], out[2 * j + 1]);
           }
-          if (gs != nullptr && live) {
+          if (MODE == kRmsAdd && gs != nullptr && live) {
             float extra[V];
             Num<T>::unpack(ld_stream(gs + row * ldgs + static_cast<int64_t>(lane_in_row + i * TPR) * V), extra);
 #pragma unroll
@@ -864,7 +864,7 @@ int run_bwd(const void* gy, const void* x, const void* w, void* dx, void* dw, vo
   return B200_OK;
 }
 
-template <typename T>
+template <typename T, int MODE>
 int run_rms_narrow(const void* gy, const void* gs, const void* x, const void* w, void* dx, void* dw, void* db, float* scratch, int64_t rows,
                    int nvec, int64_t ldg, int64_t ldgs, int64_t ldx, int64_t lddx, float eps, float offset, cudaStream_t st) {
   constexpr int V = Num<T>::kVec;
@@ -877,7 +877,7 @@ int run_rms_narrow(const void* gy, const void* gs, const void* x, const void* w,
 #define B200_RMS_NARROW(TPR, ITEMS, RU)                                                                                       \
   do {                                                                                                                        \
     lines = family_bwd_ctas(rows, 256 / TPR * RU);                                                                            \
-    launch(family_bwd_rows_kernel<T, TPR, ITEMS, kRms, RU>, static_cast<unsigned>(lines), 256, 0, st, tg, tx, tw, tdx, scratch, rows, \
+    launch(family_bwd_rows_kernel<T, TPR, ITEMS, MODE, RU>, static_cast<unsigned>(lines), 256, 0, st, tg, tx, tw, tdx, scratch, rows, \
            nvec, ldg, ldx, lddx, cols_f, eps, bias, arrays, static_cast<const T*>(gs), ldgs, offset);                         \
   } while (0)
   if (nvec <= 8) B200_RMS_NARROW(8, 1, 4);
@@ -929,9 +929,10 @@ int bwd_entry(const char* fn, int mode, const void* gy, const void* x, const voi
 
 int rms_backward_narrow_rows(int dtype, const void* gy, const void* gs, const void* x, const void* w, void* dx, void* dw, void* db,
                              float* scratch, int64_t rows, int64_t cols, int64_t ldg, int64_t ldgs, int64_t ldx, int64_t lddx, float eps,
-                             float offset, cudaStream_t st) {
+                             float offset, bool add, cudaStream_t st) {
   B200_DISPATCH_DTYPE(dtype, T, {
-    return run_rms_narrow<T>(gy, gs, x, w, dx, dw, db, scratch, rows, static_cast<int>(cols / Num<T>::kVec), ldg, ldgs, ldx, lddx, eps, offset, st);
+    if (add) return run_rms_narrow<T, kRmsAdd>(gy, gs, x, w, dx, dw, db, scratch, rows, static_cast<int>(cols / Num<T>::kVec), ldg, ldgs, ldx, lddx, eps, offset, st);
+    return run_rms_narrow<T, kRms>(gy, nullptr, x, w, dx, dw, db, scratch, rows, static_cast<int>(cols / Num<T>::kVec), ldg, 0, ldx, lddx, eps, 0.f, st);
   });
   return B200_ERR_DTYPE;
 }
