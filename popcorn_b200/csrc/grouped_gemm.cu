@@ -522,52 +522,69 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const uint32_t taddr = tmem_base + acc * kBN + (static_cast<uint32_t>(quarter * 32) << 16);
       const int warp_row0 = t.row0 + static_cast<int>(rank) * kBM + quarter * 32;
       uint4(*mine)[8] = staging[quarter];
-#pragma unroll 1
-      for (int c = 0; c < ACC_COLS / 32; ++c) {
-        uint32_t packed[16];
+      // 64 output columns per step (one 128-byte staging row per lane).  The tensor-memory loads of the NEXT step are
+      // issued before this step's conversion, transpose and stores, so their latency hides behind them (the fused
+      // SwiGLU form needs both projections' columns per step and does not prefetch: its main loop is long anyway).
+      constexpr int STEPS = ACC_COLS / 64;
+      constexpr bool PREFETCH = MODE != kSwiglu;
+      uint32_t held[2][64], second[MODE == kSwiglu ? 64 : 1];
+      auto fetch = [&](uint32_t (&v)[64], int step) {
+        tmem_load_32(taddr + step * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+        tmem_load_32(taddr + step * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+      };
+      if (!zeros) fetch(held[0], 0);
+#pragma unroll
+      for (int step = 0; step < STEPS; ++step) {
+        uint32_t(&v)[64] = held[PREFETCH ? (step & 1) : 0];
+        uint32_t packed[32];
         if (zeros) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) packed[j] = 0u;
+          for (int j = 0; j < 32; ++j) packed[j] = 0u;
         } else {
-          uint32_t v[32], u[32];
-          tmem_load_32(taddr + c * 32, v);
-          if constexpr (MODE == kSwiglu) tmem_load_32(taddr + OUT_N + c * 32, u);
+          if constexpr (MODE == kSwiglu) {
+            tmem_load_32(taddr + OUT_N + step * 64, *reinterpret_cast<uint32_t(*)[32]>(&second[0]));
+            tmem_load_32(taddr + OUT_N + step * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&second[32]));
+          }
           tmem_load_wait();
+          if constexpr (PREFETCH) {
+            if (step + 1 < STEPS) fetch(held[(step + 1) & 1], step + 1);
+          }
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
+          for (int j = 0; j < 32; ++j) {
             float lo = __uint_as_float(v[2 * j]), hi = __uint_as_float(v[2 * j + 1]);
             if constexpr (MODE == kSwiglu) {
               // columns 0..127 of the accumulator hold rows @ gate, 128..255 rows @ up
-              lo = __fmul_rn(silu_f32<1>(lo), __uint_as_float(u[2 * j]));
-              hi = __fmul_rn(silu_f32<1>(hi), __uint_as_float(u[2 * j + 1]));
+              lo = __fmul_rn(silu_f32<1>(lo), __uint_as_float(second[2 * j]));
+              hi = __fmul_rn(silu_f32<1>(hi), __uint_as_float(second[2 * j + 1]));
             }
             packed[j] = Num<T>::pack2(lo, hi);
           }
-        }
-        // lane = row: its 32 columns are four 16-byte pieces of the 128-byte staging row (piece index
-        // xor-ed with the row so that neither these writes nor the transposed reads conflict on banks)
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-          mine[lane][((c & 1) * 4 + q) ^ (lane & 7)] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-        if (c & 1) {
-          // 64 finished columns of 32 rows: write them out as whole 128-byte row segments, four rows per instruction
-          __syncwarp();
-          const int piece = lane & 7;
-          int tile_col = (c - 1) * 32 + piece * 8, shift = 0;  // column within the tile; kGateUp: the second projection lies n columns further
-          if (MODE == kGateUp && tile_col >= OUT_N) {
-            tile_col -= OUT_N;
-            shift = p.n;
+          if constexpr (!PREFETCH) {
+            if (step + 1 < STEPS) fetch(held[0], step + 1);  // the registers are free again
           }
-          const int col = t.n0 + tile_col;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int r = i * 4 + (lane >> 3);
-            const int row = warp_row0 + r;
-            if (row < t.row_end && col < p.n)
-              st_stream(out + static_cast<int64_t>(row) * p.ld_out + col + shift, mine[r][piece ^ (r & 7)]);
-          }
-          __syncwarp();
         }
+        // lane = row: its 64 columns are eight 16-byte pieces of the 128-byte staging row (piece index xor-ed with
+        // the row so that neither these writes nor the transposed reads conflict on banks)
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          mine[lane][q ^ (lane & 7)] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+        // 64 finished columns of 32 rows: write them out as whole 128-byte row segments, four rows per instruction
+        __syncwarp();
+        const int piece = lane & 7;
+        int tile_col = step * 64 + piece * 8, shift = 0;  // column within the tile; kGateUp: the second projection lies n columns further
+        if (MODE == kGateUp && tile_col >= OUT_N) {
+          tile_col -= OUT_N;
+          shift = p.n;
+        }
+        const int col = t.n0 + tile_col;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = i * 4 + (lane >> 3);
+          const int row = warp_row0 + r;
+          if (row < t.row_end && col < p.n)
+            st_stream(out + static_cast<int64_t>(row) * p.ld_out + col + shift, mine[r][piece ^ (r & 7)]);
+        }
+        __syncwarp();
       }
       if (!zeros) {
         tc_fence_before();
