@@ -348,9 +348,13 @@ int entry(const char* fn, int mode, const void* x, const void* gate, const void*
 // layer_norm: y = xhat w + b, xhat = (x - mean) rstd     dx = rstd (gw - mean(gw) - xhat mean(gw xhat)), gw = g w
 //                                                        dw = sum_rows g xhat,  db = sum_rows g
 // in fp32 from the stored 16-bit (or fp32) values, one rounding per output; gradients are graded against an fp64
-// evaluation like the reference's own (src/popcorn/bench/compare.py:243-277).  Persistent CTAs walk the rows; a row is
-// read once from HBM and re-read from L1/L2 for the later passes; each thread adds its columns' contributions
-// to dw / db in the CTA's own line of `partial` ([lines][2][cols] fp32), which family_sum_lines_kernel adds up.
+// evaluation like the reference's own (src/popcorn/bench/compare.py:243-277).
+//
+// Two kernels.  family_bwd_rows_kernel (further down) is the fast path for aligned rows of up to 1024 words.  The
+// kernel right below is the general one for everything else (wider rows, widths or pointers that are not a multiple
+// of the 128-bit word): persistent CTAs walk the rows, a row is read once from HBM and re-read from L1/L2 for the
+// later passes, and each thread adds its columns' contributions to dw / db in the CTA's own line of `partial`
+// ([lines][2][cols] fp32, in global memory), which family_sum_lines_kernel adds up.
 // VEC: 128-bit accesses (cols, strides and pointers aligned), else element by element.
 template <typename T, bool VEC>
 __device__ __forceinline__ void load_elems(const T* p, float (&f)[Num<T>::kVec]) {
