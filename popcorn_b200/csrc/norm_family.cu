@@ -523,16 +523,16 @@ __device__ __forceinline__ float pair_total(Float2x v) {
 //   LayerNorm, per row:  mean = sum x / n;  var = sum (x - mean)^2 / n;  rstd = 1 / sqrt(var + eps)
 //                        m1 = sum gw / n;  m2 = rstd (sum gw x - mean sum gw) / n            (gw = g w)
 //                        xhat = x rstd - mean rstd;  dx = gw rstd - m1 rstd - xhat m2 rstd;  dw += g xhat;  db += g
-template <typename T, int TPR, int ITEMS, int MODE, int RU>
+template <typename T, int TPR, int ITEMS, int MODE, int RU, bool BIAS>
 __global__ void __launch_bounds__(256, 2)
 family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const T* __restrict__ weight, T* __restrict__ dx,
                        float* __restrict__ partial, int64_t rows, int nvec, int64_t ldg, int64_t ldx, int64_t lddx,
-                       float cols_f, float eps, int has_bias, int line_arrays, const T* __restrict__ gs, int64_t ldgs, float offset) {
+                       float cols_f, float eps, int line_arrays, const T* __restrict__ gs, int64_t ldgs, float offset) {
   constexpr int V = Num<T>::kVec;
   constexpr int P = V / 2;  // fp32 pairs per word
   constexpr int GROUPS = 256 / TPR;
   constexpr bool LAYER = MODE == kLayer || MODE == kRms || MODE == kRmsAdd;  // modes with a weight: dw (and db) partials per thread
-  constexpr bool KEEP_W = ITEMS < 4;  // wide rows re-read their weight words (L1 hits) instead of holding them in registers
+  constexpr bool KEEP_W = ITEMS < 4 || !BIAS;  // wide rows with a bias gradient re-read their weight words (L1 hits): no registers left
   static_assert(RU == 1 || TPR <= 32, "several rows per group only for rows that fit a warp");
   pdl_prologue();
   constexpr int SLOT_GROUPS = (TPR > 32 && TPR < 256) ? GROUPS : 1;  // rows that meet at a barrier of their own
@@ -544,7 +544,7 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
   bool col_ok[ITEMS];
   uint4 wv[LAYER && KEEP_W ? ITEMS : 1];
   auto weight_word = [&](int i) { return KEEP_W ? wv[KEEP_W ? i : 0] : ld_reuse(weight + static_cast<int64_t>(lane_in_row + i * TPR) * V); };
-  Float2x dw[LAYER ? ITEMS : 1][P], db[LAYER ? ITEMS : 1][P];
+  Float2x dw[LAYER ? ITEMS : 1][P], db[LAYER && BIAS ? ITEMS : 1][P];  // BIAS: the op has a bias, so db is wanted
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
     col_ok[i] = lane_in_row + i * TPR < nvec;
@@ -554,7 +554,10 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
         if (col_ok[i]) wv[i] = ld_reuse(weight + static_cast<int64_t>(lane_in_row + i * TPR) * V);
       }
 #pragma unroll
-      for (int j = 0; j < P; ++j) dw[i][j] = db[i][j] = pack_f2(0.f, 0.f);
+      for (int j = 0; j < P; ++j) {
+        dw[i][j] = pack_f2(0.f, 0.f);
+        if constexpr (BIAS) db[i][j] = pack_f2(0.f, 0.f);
+      }
     }
   }
   const int64_t stride = static_cast<int64_t>(gridDim.x) * GROUPS * RU;
@@ -654,7 +657,7 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
 #pragma unroll
           for (int j = 0; j < P; ++j) {
             dw[i][j] = fma_f2(fg[j], mul_f2(fx[j], r2), dw[i][j]);
-            db[i][j] = add_f2(db[i][j], fg[j]);
+            if constexpr (BIAS) db[i][j] = add_f2(db[i][j], fg[j]);
             unpack_f2(fma_f2(mul_f2(fg[j], fw[j]), r2, mul_f2(fx[j], coef2)), out[2 * j], out[2 * j + 1]);
           }
           if (MODE == kRmsAdd && gs != nullptr && live) {
@@ -721,7 +724,7 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
           for (int j = 0; j < P; ++j) {
             const Float2x xhat = fma_f2(fx[j], rstd2, shift2);  // a row past the end is all zeros: mean, shift and xhat are 0
             dw[i][j] = fma_f2(fg[j], xhat, dw[i][j]);
-            db[i][j] = add_f2(db[i][j], fg[j]);
+            if constexpr (BIAS) db[i][j] = add_f2(db[i][j], fg[j]);
             unpack_f2(fma_f2(xhat, c22, fma_f2(mul_f2(fg[j], fw[j]), rstd2, c12)), out[2 * j], out[2 * j + 1]);
           }
           if (live) st_stream(dx + row * lddx + static_cast<int64_t>(lane_in_row + i * TPR) * V, Num<T>::pack(out));
@@ -741,22 +744,25 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
 #pragma unroll
             for (int j = 0; j < P; ++j) {
               const int c = (lane_in_row + i * TPR) * V + 2 * j;
-              float w0, w1, b0, b1;
+              float w0, w1;
               unpack_f2(dw[i][j], w0, w1);
-              unpack_f2(db[i][j], b0, b1);
               float* fw = fold + c;
-              float* fb = fold + TPR * ITEMS * V + c;
               fw[0] = g == 0 ? w0 : __fadd_rn(fw[0], w0);
               fw[1] = g == 0 ? w1 : __fadd_rn(fw[1], w1);
-              fb[0] = g == 0 ? b0 : __fadd_rn(fb[0], b0);
-              fb[1] = g == 0 ? b1 : __fadd_rn(fb[1], b1);
+              if constexpr (BIAS) {
+                float b0, b1;
+                unpack_f2(db[i][j], b0, b1);
+                float* fb = fold + TPR * ITEMS * V + c;
+                fb[0] = g == 0 ? b0 : __fadd_rn(fb[0], b0);
+                fb[1] = g == 0 ? b1 : __fadd_rn(fb[1], b1);
+              }
             }
         }
         __syncthreads();
       }
       for (int c = tid; c < nvec * V; c += 256) {
         line[c] = fold[c];
-        if (has_bias) line[nvec * V + c] = fold[TPR * ITEMS * V + c];
+        if constexpr (BIAS) line[nvec * V + c] = fold[TPR * ITEMS * V + c];
       }
     } else {
 #pragma unroll
@@ -769,7 +775,7 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
           unpack_f2(dw[i][j], a0, a1);
           unpack_f2(dw[i][j + 1], a2, a3);
           *reinterpret_cast<float4*>(line + c + 2 * j) = make_float4(a0, a1, a2, a3);
-          if (has_bias) {
+          if constexpr (BIAS) {
             unpack_f2(db[i][j], a0, a1);
             unpack_f2(db[i][j + 1], a2, a3);
             *reinterpret_cast<float4*>(line + nvec * V + c + 2 * j) = make_float4(a0, a1, a2, a3);
@@ -841,8 +847,12 @@ int run_bwd(const void* gy, const void* x, const void* w, void* dx, void* dw, vo
 #define B200_FAMILY_BWD(TPR, ITEMS, RU)                                                                                          \
   do {                                                                                                                           \
     lines = family_bwd_ctas(rows, 256 / TPR * RU);                                                                               \
-    launch(family_bwd_rows_kernel<T, TPR, ITEMS, MODE, RU>, static_cast<unsigned>(lines), 256, 0, st, tg, tx, tw, tdx, scratch, rows, \
-           nvec, ldg, ldx, lddx, cols_f, eps, bias, 2, static_cast<const T*>(nullptr), 0, 0.f);                                  \
+    if (bias)                                                                                                                    \
+      launch(family_bwd_rows_kernel<T, TPR, ITEMS, MODE, RU, true>, static_cast<unsigned>(lines), 256, 0, st, tg, tx, tw, tdx,   \
+             scratch, rows, nvec, ldg, ldx, lddx, cols_f, eps, 2, static_cast<const T*>(nullptr), 0, 0.f);                       \
+    else                                                                                                                         \
+      launch(family_bwd_rows_kernel<T, TPR, ITEMS, MODE, RU, false>, static_cast<unsigned>(lines), 256, 0, st, tg, tx, tw, tdx,  \
+             scratch, rows, nvec, ldg, ldx, lddx, cols_f, eps, 2, static_cast<const T*>(nullptr), 0, 0.f);                       \
   } while (0)
     if (nvec <= 8) B200_FAMILY_BWD(8, 1, 4);
     else if (nvec <= 16) B200_FAMILY_BWD(16, 1, 4);
@@ -881,8 +891,12 @@ int run_rms_narrow(const void* gy, const void* gs, const void* x, const void* w,
 #define B200_RMS_NARROW(TPR, ITEMS, RU)                                                                                       \
   do {                                                                                                                        \
     lines = family_bwd_ctas(rows, 256 / TPR * RU);                                                                            \
-    launch(family_bwd_rows_kernel<T, TPR, ITEMS, MODE, RU>, static_cast<unsigned>(lines), 256, 0, st, tg, tx, tw, tdx, scratch, rows, \
-           nvec, ldg, ldx, lddx, cols_f, eps, bias, arrays, static_cast<const T*>(gs), ldgs, offset);                         \
+    if (bias)                                                                                                                 \
+      launch(family_bwd_rows_kernel<T, TPR, ITEMS, MODE, RU, true>, static_cast<unsigned>(lines), 256, 0, st, tg, tx, tw, tdx, \
+             scratch, rows, nvec, ldg, ldx, lddx, cols_f, eps, arrays, static_cast<const T*>(gs), ldgs, offset);              \
+    else                                                                                                                      \
+      launch(family_bwd_rows_kernel<T, TPR, ITEMS, MODE, RU, false>, static_cast<unsigned>(lines), 256, 0, st, tg, tx, tw, tdx, \
+             scratch, rows, nvec, ldg, ldx, lddx, cols_f, eps, arrays, static_cast<const T*>(gs), ldgs, offset);              \
   } while (0)
   if (nvec <= 8) B200_RMS_NARROW(8, 1, 4);
   else if (nvec <= 16) B200_RMS_NARROW(16, 1, 4);
