@@ -21,6 +21,28 @@ from torch import Tensor
 from popcorn_b200 import ops
 
 
+def chunk_bounds(rows: int, chunk_rows: int) -> list[tuple[int, int]]:
+    """[lo, hi) row ranges of the pipeline's chunks.  The first copy in and the last copy out have nothing to overlap
+    with, so the chunks ramp up from chunk_rows / 8 at the start and back down at the end (each ramp costs four
+    extra launches and shortens the exposed copy eightfold); short inputs are cut evenly."""
+    if rows <= 0:
+        return []
+    ramp = [chunk_rows // 8, chunk_rows // 4, chunk_rows // 2] if chunk_rows >= 8 else []
+    if rows < 4 * chunk_rows or not ramp:
+        return [(lo, min(lo + chunk_rows, rows)) for lo in range(0, rows, chunk_rows)]
+    sizes = list(ramp)
+    middle = rows - 2 * sum(ramp)
+    sizes += [chunk_rows] * (middle // chunk_rows)
+    if middle % chunk_rows:
+        sizes.append(middle % chunk_rows)
+    sizes += ramp[::-1]
+    bounds, lo = [], 0
+    for size in sizes:
+        bounds.append((lo, lo + size))
+        lo += size
+    return bounds
+
+
 def run_rows(
     fn: Callable[..., Tensor | Sequence[Tensor]],
     inputs: Sequence[Tensor],
@@ -43,6 +65,7 @@ def run_rows(
     if rows == 0:
         return
     chunk_rows = max(1, min(chunk_rows, rows))
+    bounds = chunk_bounds(rows, chunk_rows)
     with torch.cuda.device(device):
         copy_in, compute, copy_out = (torch.cuda.Stream(device) for _ in range(3))
         ring = [[torch.empty((chunk_rows, *t.shape[1:]), dtype=t.dtype, device=device) for t in inputs] for _ in range(depth)]
@@ -50,8 +73,7 @@ def run_rows(
         start = torch.cuda.current_stream(device).record_event()
         copy_in.wait_event(start)
         last_out = None
-        for index, lo in enumerate(range(0, rows, chunk_rows)):
-            hi = min(lo + chunk_rows, rows)
+        for index, (lo, hi) in enumerate(bounds):
             slot = ring[index % depth]
             with torch.cuda.stream(copy_in):
                 if drained[index % depth] is not None:

@@ -181,3 +181,15 @@ def test_plugin_registers_on_real_popcorn(tmp_path, monkeypatch):
     assert all(torch.equal(g, w_) for g, w_ in zip(got, want))
     y = popcorn.KERNELS["moe_unpermute"].reference(want[0], ow, want[4])
     torch.testing.assert_close(y, oracle.moe_unpermute(want[0], ow, want[4]), rtol=1e-5, atol=1e-6)
+
+
+def test_host_pipeline_chunks_cover_the_rows_once():
+    from popcorn_b200.host import chunk_bounds
+
+    ramped = chunk_bounds(16384, 1024)
+    assert ramped[:3] == [(0, 128), (128, 384), (384, 896)] and ramped[-1] == (16256, 16384) and len(ramped) == 21
+    for rows, chunk in [(1, 1024), (1000, 1024), (4095, 1024), (4096, 1024), (4097, 1024), (5000, 7), (100000, 1000), (9, 1)]:
+        bounds = chunk_bounds(rows, chunk)
+        assert bounds[0][0] == 0 and bounds[-1][1] == rows
+        assert all(a[1] == b[0] for a, b in zip(bounds, bounds[1:])) and all(0 < hi - lo <= chunk for lo, hi in bounds)
+    assert chunk_bounds(0, 64) == []
