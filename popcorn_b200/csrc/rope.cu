@@ -34,6 +34,7 @@ struct RopeArgs {
   int batch_split;  // warps per position; warp w of a position takes batches w, w + split, ...
   int half;
   int head_dim;
+  int tail_elsewhere;  // the channels past the rotated ones are copied by rope_tail_kernel, not by the rotation kernel
 };
 
 // N consecutive cos (or sin) values -> fp32 registers.
@@ -240,7 +241,7 @@ __global__ void __launch_bounds__(512, 2) rope_tile_kernel(const RopeArgs p, int
       }
     }
     // channels past the rotated ones pass through (nothing to do in place)
-    if (tail_words > 0) {
+    if (tail_words > 0 && !p.tail_elsewhere) {
       for (int ti = 0; ti < p.n_tensors; ++ti) {
         const RopeTensor& t = p.t[ti];
         if (t.x == t.out) continue;
@@ -261,6 +262,43 @@ __global__ void __launch_bounds__(512, 2) rope_tile_kernel(const RopeArgs p, int
 }
 
 // Any shape, any alignment: one thread per (batch, position, head, channel pair or tail channel).
+// Out-of-place partial rotary: the channels past the rotated ones are a strided copy, four 128-bit words in flight
+// per thread (inside rope_tile_kernel, which has no registers to spare, the same copy ran one word at a time).
+template <typename T>
+__global__ void __launch_bounds__(256) rope_tail_kernel(const RopeArgs p) {
+  constexpr int V = Num<T>::kVec;
+  constexpr int U = 4;
+  pdl_prologue();
+  const int tail_words = (p.head_dim - 2 * p.half) / V;
+  for (int ti = 0; ti < p.n_tensors; ++ti) {
+    const RopeTensor& t = p.t[ti];
+    if (t.x == t.out || t.heads == 0) continue;
+    const int64_t per_pos = static_cast<int64_t>(t.heads) * tail_words;
+    const int64_t total = static_cast<int64_t>(p.batch) * p.seq * per_pos;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * 256;
+    for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i0 < total; i0 += stride * U) {
+      uint4 held[U];
+      int64_t dst[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int64_t i = i0 + u * stride;
+        if (i < total) {
+          const int64_t bp = i / per_pos;
+          const int rem = static_cast<int>(i - bp * per_pos);
+          const int h = rem / tail_words, w = rem - h * tail_words;
+          const int64_t b = bp / p.seq, pos = bp - b * p.seq;
+          const int64_t j = 2 * p.half + static_cast<int64_t>(w) * V;
+          held[u] = ld_stream(static_cast<const T*>(t.x) + b * t.xs_b + pos * t.xs_s + h * t.xs_h + j);
+          dst[u] = b * t.os_b + pos * t.os_s + h * t.os_h + j;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i0 + u * stride < total) st_stream(static_cast<T*>(t.out) + dst[u], held[u]);
+    }
+  }
+}
+
 template <typename T, typename CS, bool INTERLEAVED>
 __global__ void __launch_bounds__(256) rope_scalar_kernel(const RopeArgs p) {
   pdl_prologue();
@@ -328,6 +366,13 @@ int run(RopeArgs& p, cudaStream_t st) {
     if (grid > 0x7fffffffLL) return fail(B200_ERR_SHAPE, "b200_rope: problem too large for one launch");
     const size_t smem = 2 * static_cast<size_t>(tile_positions) * p.half * sizeof(CS);
     if (smem <= 48 * 1024) {
+      bool out_of_place = false;
+      for (int i = 0; i < p.n_tensors; ++i) out_of_place = out_of_place || p.t[i].x != p.t[i].out;
+      p.tail_elsewhere = (p.head_dim > 2 * p.half && out_of_place) ? 1 : 0;
+      if (p.tail_elsewhere) {
+        launch(rope_tail_kernel<T>, static_cast<unsigned>(sm_count()) * 8, 256, 0, st, p);
+        if (int rc = after_launch("rope_tail_kernel")) return rc;
+      }
       launch(rope_tile_kernel<T, CS, INTERLEAVED>, static_cast<unsigned>(grid), threads, smem, st, p, tpp, groups);
       return after_launch("rope_tile_kernel");
     }
