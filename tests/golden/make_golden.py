@@ -260,6 +260,52 @@ def momoe_cases() -> None:
         )
 
 
+def gradient_cases() -> None:
+    """Gradients by autograd through the registered references: in the case dtype (what a training call gets) and in
+    fp64 (what popcorn's harness grades against, src/popcorn/bench/compare.py:243-277)."""
+
+    def record(name, op, tensors, constants, meta):
+        ref = KERNELS[op].reference
+
+        def grads(cast):
+            leaves = {k: cast(v).detach().clone().requires_grad_() for k, v in tensors.items()}
+            outs = ref(*leaves.values(), *constants)
+            outs = outs if isinstance(outs, tuple) else (outs,)
+            gen = torch.Generator().manual_seed(meta["seed"] + 1000)
+            seeds = [randn(gen, *o.shape).to(o.dtype) for o in outs]
+            found = torch.autograd.grad(outs, list(leaves.values()), seeds, allow_unused=True)
+            return seeds, dict(zip(leaves, found))
+
+        seeds, native = grads(lambda t: t)
+        _, truth = grads(lambda t: t.double())
+        stored = dict(tensors)
+        stored.update({f"cotangent{i}": c for i, c in enumerate(seeds)})
+        stored.update({f"grad_{k}": g for k, g in native.items() if g is not None})
+        stored.update({f"truth_{k}": g for k, g in truth.items() if g is not None})
+        save_case(name, stored, {"op": op, **meta})
+
+    gen = torch.Generator().manual_seed(60)
+    x, w, b = randn(gen, 24, 256).to(BF16), (1 + 0.1 * randn(gen, 256)).to(BF16), randn(gen, 256).to(BF16)
+    record("grad_rms_norm_bf16_24x256_bias", "rms_norm", {"x": x, "weight": w, "bias": b}, (1e-5,), {"seed": 60, "eps": 1e-5})
+    gen = torch.Generator().manual_seed(61)
+    x, r, w = randn(gen, 24, 512).to(BF16), randn(gen, 24, 512).to(BF16), (1 + 0.1 * randn(gen, 512)).to(BF16)
+    record("grad_add_rms_norm_bf16_24x512_offset1", "add_rms_norm", {"x": x, "residual": r, "weight": w}, (1e-6, 1.0),
+           {"seed": 61, "eps": 1e-6, "offset": 1.0})
+    gen = torch.Generator().manual_seed(62)
+    a, bb = randn(gen, 24, 256).to(BF16), randn(gen, 24, 256).to(BF16)
+    record("grad_swiglu_bf16_24x256", "swiglu", {"a": a, "b": bb}, (), {"seed": 62})
+    gen = torch.Generator().manual_seed(63)
+    batch, seq, hidden, inter, experts, top_k = 1, 48, 64, 32, 8, 2
+    tensors = {
+        "x": randn(gen, batch, seq, hidden).to(BF16),
+        "gate_weight": (randn(gen, experts, hidden, inter) / hidden**0.5).to(BF16),
+        "up_weight": (randn(gen, experts, hidden, inter) / hidden**0.5).to(BF16),
+        "down_weight": (randn(gen, experts, inter, hidden) / inter**0.5).to(BF16),
+        "router_logits": randn(gen, batch, seq, experts),
+    }
+    record("grad_momoe_bf16_e8_k2", "momoe", tensors, (top_k,), {"seed": 63, "top_k": top_k})
+
+
 def main() -> None:
     torch.manual_seed(0)
     rms_norm_cases()
@@ -271,6 +317,7 @@ def main() -> None:
     swiglu_cases()
     sibling_cases()
     momoe_cases()
+    gradient_cases()
     import popcorn
 
     print("popcorn", getattr(popcorn, "__version__", "?"), "torch", torch.__version__)

@@ -10,6 +10,8 @@ every element must also be bit-identical to the native-precision oracle.
 import pytest
 import torch
 
+from tests.golden.golden_io import case_names, load_case
+
 from oracle import reference_ops as oracle
 from popcorn_b200 import autograd as diff, kernels, workloads
 
@@ -307,3 +309,26 @@ def test_norm_backward_full_width_sample():
         m = m.cpu()
         print(f"\n[add_rms_norm backward {name}] elements={n.numel()} not-bit-identical={int((m != n).sum())} max-abs={float((m.float() - n.float()).abs().max()):.3e}")
     assert float((mine[0].cpu().float() - native[0].float()).abs().max()) <= 2e-2
+
+
+@pytest.mark.parametrize("name", [n for n in case_names() if n.startswith("grad_")])
+def test_gradients_against_the_references_own(name):
+    """Fixtures written by autograd through the real popcorn references (case dtype and fp64): every gradient of the
+    CUDA path is within popcorn's own bound of the fp64 one, twice the reference's error or the dtype's floor."""
+    t, meta = load_case(name)
+    keys = [k for k in t if f"grad_{k}" in t]
+    leaves = {k: t[k].to(DEV).requires_grad_(True) for k in keys}
+    op = meta["op"]
+    if op == "rms_norm":
+        outs = (diff.rms_norm(leaves["x"], leaves["weight"], leaves["bias"], meta["eps"]),)
+    elif op == "add_rms_norm":
+        outs = diff.add_rms_norm(leaves["x"], leaves["residual"], leaves["weight"], meta["eps"], meta["offset"])
+    elif op == "swiglu":
+        outs = (diff.swiglu(leaves["a"], leaves["b"]),)
+    else:
+        outs = (diff.momoe(leaves["x"], leaves["gate_weight"], leaves["up_weight"], leaves["down_weight"], leaves["router_logits"], meta["top_k"]),)
+    seeds = [t[f"cotangent{i}"].to(DEV) for i in range(len(outs))]
+    grads = torch.autograd.grad(outs, list(leaves.values()), seeds)
+    for key, mine in zip(keys, grads):
+        dtype = torch.bfloat16 if op == "momoe" else t[key].dtype  # momoe: 16-bit intermediates bound the fp32 logits' gradient too
+        grade(mine, t[f"grad_{key}"], t[f"truth_{key}"], dtype, f"{name} grad {key}")

@@ -176,3 +176,37 @@ def test_moe16_chain_with_expert_projections(name):
     assert float((y.float() - t["y"].float()).abs().max()) <= 2e-2
     exact = oracle.momoe_from_steps(t["x"], t["gate_weight"], t["up_weight"], t["down_weight"], t["router_logits"], top_k)
     assert float((exact.float() - t["y"].float()).abs().max()) <= 2e-2 and float((exact == t["y"]).float().mean()) > 0.99
+
+
+def _oracle_call(op, t, meta):
+    """The oracle's restatement of `op` on the tensors of a gradient fixture (leaves given by name)."""
+    if op == "rms_norm":
+        return lambda x, weight, bias: oracle.rms_norm(x, weight, bias, meta["eps"])
+    if op == "add_rms_norm":
+        return lambda x, residual, weight: oracle.add_rms_norm(x, residual, weight, meta["eps"], meta["offset"])
+    if op == "swiglu":
+        return oracle.swiglu
+    return lambda x, gate_weight, up_weight, down_weight, router_logits: oracle.momoe_from_steps(
+        x, gate_weight, up_weight, down_weight, router_logits, meta["top_k"])
+
+
+@pytest.mark.parametrize("name", names("grad_"))
+def test_autograd_through_the_oracle_gives_the_references_gradients(name):
+    """The backward kernels are checked against autograd through the oracle; this pins that autograd to the gradients
+    the real references produce (fixtures: autograd through KERNELS[op].reference in the case dtype and in fp64)."""
+    t, meta = load_case(name)
+    leaves = {k: v.clone().requires_grad_() for k, v in t.items() if f"grad_{k}" in t}
+    outs = _oracle_call(meta["op"], t, meta)(*leaves.values())
+    outs = outs if isinstance(outs, tuple) else (outs,)
+    seeds = [t[f"cotangent{i}"] for i in range(len(outs))]
+    grads = torch.autograd.grad(outs, list(leaves.values()), seeds)
+    for key, got in zip(leaves, grads):
+        want, truth = t[f"grad_{key}"], t[f"truth_{key}"]
+        if meta["op"] == "momoe":
+            # the oracle evaluates the routed pairs only and sums them in another order than the dense reference
+            budget = float((want.double() - truth).abs().max())
+            err = float((got.double() - truth).abs().max())
+            floor = (2e-2 if got.dtype != torch.float32 else 2e-5) * max(1.0, float(truth.abs().max()))
+            assert err <= max(2 * budget, floor), f"{name} grad {key}: {err:.3e} vs the reference's own {budget:.3e}"
+        else:
+            assert_close_ulps(got, want, 1.0)
