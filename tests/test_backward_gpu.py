@@ -10,10 +10,9 @@ every element must also be bit-identical to the native-precision oracle.
 import pytest
 import torch
 
-from tests.golden.golden_io import case_names, load_case
-
 from oracle import reference_ops as oracle
 from popcorn_b200 import autograd as diff, kernels, workloads
+from tests.golden.golden_io import case_names, load_case
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
