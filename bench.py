@@ -778,23 +778,31 @@ def main() -> None:
                                y=host_out[0], s=host_out[1], device=device)
 
     e2e_steps = max(3, min(args.steps, 10))
-    for _ in range(2):
+    # warm-up: the link idled during the device-only headline loop and needs a few hundred milliseconds of traffic
+    # to run at full speed again (measured: the first 20 steps at half the rate of the later ones)
+    for _ in range(30):
         e2e_step()
     torch.cuda.synchronize(device)
-    if dist is not None:
-        dist.barrier()
+    # Five timed windows of e2e_steps steps each; the reported figure is the MEDIAN window (the PCIe path is shared
+    # with the machine's other tenants: about one window in four runs at 60 % of the others), all five are listed.
     t0 = time.time()
-    start.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    end.record()
-    torch.cuda.synchronize(device)
-    e2e_ms = torch.tensor([start.elapsed_time(end) / e2e_steps], device=device, dtype=torch.float64)
-    if dist is not None:
-        dist.barrier()
-        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    window_ms = []
+    for _ in range(5):
+        if dist is not None:
+            dist.barrier()
+        start.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        end.record()
+        torch.cuda.synchronize(device)
+        one = torch.tensor([start.elapsed_time(end) / e2e_steps], device=device, dtype=torch.float64)
+        if dist is not None:
+            dist.barrier()
+            dist.all_reduce(one, op=dist.ReduceOp.MAX)
+        window_ms.append(float(one.item()))
     if sampler is not None:
         sampler.mark(t0, time.time())
+    e2e_ms = torch.tensor([sorted(window_ms)[len(window_ms) // 2]], dtype=torch.float64)
     e2e_value = world * w.tokens / (float(e2e_ms.item()) * 1e-3)
     del host_in, host_out, run
     torch.cuda.empty_cache()
@@ -847,7 +855,9 @@ def main() -> None:
                          "frac_of_8tbs": round(achieved / SPEC_HBM_GBS, 4), "algorithmic_bytes_per_launch": nbytes,
                          "traffic": None if traffic is None else int(traffic * args.scale)},
             "cpu_baseline": cpu,
-            "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+            "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                    "windows": len(window_ms), "rule": "median window",
+                    "window_values": [round(world * w.tokens / (ms * 1e-3), 1) for ms in window_ms]},
             "gpu_launches": int(launches),
             "clocks": clocks,
             "per_op": per_op,
