@@ -650,12 +650,15 @@ bool ring_enabled() {
 // bf16 [65536, 2048] 5701 / 5683 vs 2386 / 3485, bf16 [32768, 4096] 5607 / 5501 vs 4272 / 5122, fp32 [200000, 768]
 // 5688 / 6643 vs 1829 / 2734); wider rows keep the ring (bf16 [32768, 5120] 4522 vs 4667, [16384, 8192] 5455 vs 5912).
 // B200_BWD_FAMILY_WORDS=<n> in the environment replaces the rule by "rows of at most n words".
-bool takes_family_path(int64_t words) {
+// With a bias gradient the row-bucket kernel also wins up to 1024 words (bf16 [32768, 5120] 3906 vs 3332,
+// [16384, 8192] 4486 vs 4223): the ring kernel re-reads its weight words per row in that case.
+bool takes_family_path(int64_t words, bool bias_gradient) {
   static const int forced = [] {
     const char* v = std::getenv("B200_BWD_FAMILY_WORDS");
     return v ? std::atoi(v) : -1;
   }();
-  return words <= (forced >= 0 ? forced : 512);
+  if (forced >= 0) return words <= forced;
+  return words <= (bias_gradient ? 1024 : 512);
 }
 
 int bwd_lines(int64_t rows) {
@@ -677,7 +680,7 @@ int run_bwd(const void* gy, const void* gs, const void* x, const void* w, void* 
   if (gs) vec = vec && ldgs % V == 0 && aligned(gs, 16);
   const T *tgy = static_cast<const T*>(gy), *tgs = static_cast<const T*>(gs), *tx = static_cast<const T*>(x), *tw = static_cast<const T*>(w);
   T* tdx = static_cast<T*>(dx);
-  if (vec && takes_family_path(cols / V)) {
+  if (vec && takes_family_path(cols / V, db != nullptr)) {
     // short rows: a 256-thread CTA per row would leave lanes idle or spend its time at barriers; 8 to 128 threads per row instead
     const int dtype = sizeof(T) == 4 ? B200_F32 : (std::is_same<T, __half>::value ? B200_F16 : B200_BF16);
     return rms_backward_narrow_rows(dtype, gy, gs, x, w, dx, dw, db, static_cast<float*>(scratch), rows, cols, ldg, ldgs, ldx, lddx, eps,
