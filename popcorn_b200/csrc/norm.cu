@@ -709,6 +709,7 @@ int run_bwd(const void* gy, const void* gs, const void* x, const void* w, void* 
   do {                                       \
     if (nvec <= 256) B200_BWD(1, BIAS);      \
     else if (nvec <= 512) B200_BWD(2, BIAS); \
+    else if (nvec <= 768) B200_BWD(3, BIAS); \
     else if (nvec <= 1024) B200_BWD(4, BIAS);\
     else B200_BWD(8, BIAS);                  \
   } while (0)

@@ -860,7 +860,9 @@ int run_bwd(const void* gy, const void* x, const void* w, void* dx, void* dw, vo
     else if (nvec <= 64) B200_FAMILY_BWD(32, 2, 1);
     else if (nvec <= 128) B200_FAMILY_BWD(32, 4, 1);
     else if (nvec <= 256) B200_FAMILY_BWD(64, 4, 1);
+    else if (nvec <= 384) B200_FAMILY_BWD(128, 3, 1);
     else if (nvec <= 512) B200_FAMILY_BWD(128, 4, 1);
+    else if (nvec <= 768) B200_FAMILY_BWD(256, 3, 1);
     else B200_FAMILY_BWD(256, 4, 1);
 #undef B200_FAMILY_BWD
     if (int rc = after_launch("family_bwd_rows_kernel")) return rc;
@@ -904,7 +906,9 @@ int run_rms_narrow(const void* gy, const void* gs, const void* x, const void* w,
   else if (nvec <= 64) B200_RMS_NARROW(32, 2, 1);
   else if (nvec <= 128) B200_RMS_NARROW(32, 4, 1);
   else if (nvec <= 256) B200_RMS_NARROW(64, 4, 1);
+  else if (nvec <= 384) B200_RMS_NARROW(128, 3, 1);
   else if (nvec <= 512) B200_RMS_NARROW(128, 4, 1);
+  else if (nvec <= 768) B200_RMS_NARROW(256, 3, 1);
   else B200_RMS_NARROW(256, 4, 1);
 #undef B200_RMS_NARROW
   if (int rc = after_launch("family_bwd_rows_kernel")) return rc;

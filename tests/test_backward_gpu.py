@@ -18,7 +18,8 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 FLOOR = {torch.float32: 2e-5, torch.float16: 1e-3, torch.bfloat16: 2e-2}
 NORM_BWD_SHAPES = [(5, 64, torch.float32), (33, 256, torch.bfloat16), (12, 1032, torch.bfloat16), (70, 1544, torch.float32), (64, 1024, torch.bfloat16), (40, 4096, torch.bfloat16), (300, 8192, torch.bfloat16),
-                   (7, 16384, torch.bfloat16), (9, 100, torch.float32), (6, 33, torch.bfloat16), (3, 40000, torch.float32), (130, 2048, torch.float16), (600, 512, torch.float32)]
+                   (7, 16384, torch.bfloat16), (9, 100, torch.float32), (6, 33, torch.bfloat16), (3, 40000, torch.float32), (130, 2048, torch.float16), (600, 512, torch.float32),
+                   (40, 3072, torch.bfloat16), (20, 5120, torch.bfloat16), (11, 6144, torch.float16)]
 
 
 def randn(seed, *shape, dtype=torch.float32, scale=1.0):
@@ -271,7 +272,7 @@ def test_rms_norm_backward(rows, cols, dtype, with_bias):
         grade(mine, nat, tru, dtype, f"{name} {rows}x{cols}")
 
 
-@pytest.mark.parametrize("rows,cols,dtype", NORM_BWD_SHAPES[:10] + [(130, 2048, torch.float16), (1000, 128, torch.bfloat16)])
+@pytest.mark.parametrize("rows,cols,dtype", NORM_BWD_SHAPES[:10] + [(130, 2048, torch.float16), (1000, 128, torch.bfloat16), (40, 3072, torch.bfloat16), (20, 5120, torch.bfloat16)])
 @pytest.mark.parametrize("offset,use_s", [(0.0, True), (1.0, True), (0.0, False)])
 def test_add_rms_norm_backward(rows, cols, dtype, offset, use_s):
     x = randn(1600 + cols, rows, cols, dtype=dtype)
