@@ -13,7 +13,17 @@ the job processes N batches per step: weak scaling.
 
 The same line also carries, under `per_op`, achieved GB/s, the fraction of the
 measured HBM peak and tokens/s for all five configurations (RMSNorm fp32,
-add+RMSNorm bf16, rotary q/k bf16, SwiGLU bf16, MoE route/index/permute/unpermute).
+add+RMSNorm bf16, rotary q/k bf16, SwiGLU bf16, MoE route/index/permute/unpermute),
+with the five fractions repeated compactly in `roofline.per_config_frac_of_measured`;
+beside them the incumbents on the same GPU (PyTorch eager, and popcorn's own CUDA
+SwiGLU and Triton rotary kernels from the unmodified package under baseline/_ref).
+With N > 1 GPUs `strong_scaling` times every configuration on 1/N of its tokens
+per GPU (max over ranks, every rank's time listed) and the expert-parallel MoE
+exchange is timed and checked for bit-equality with the single-GPU chain
+(`per_op.moe_bf16_expert_parallel_*.ep_check`).
+
+`--impl reference` runs popcorn's registered PyTorch reference of the headline op
+from the unmodified package on the host cores, one full configuration per step.
 
 Timing: CUDA events on the launching stream (torch's current stream), warm-up
 first, a device synchronize and a barrier on both sides, max over ranks.  Every
@@ -41,9 +51,28 @@ FALLBACK_HBM_GBS = 6650.0  # used only when MEASURED_PEAKS.json is absent
 SPEC_HBM_GBS = 8000.0
 L2_BYTES = 126 * 1024 * 1024
 
-# DRAM bytes (read + write) per launch of the dominant kernel at the headline
-# configuration, from an ncu capture; the summary it comes from is under profiles/.
-NCU_TRAFFIC_BYTES: dict[str, int | None] = {"add_rms_norm": 1_019_583_488}  # profiles/rms_rows_kernel_add_rms_norm_bf16.md
+HEADLINE_PROFILE = REPO / "profiles" / "rms_rows_kernel_add_rms_norm_bf16.md"
+
+
+def profiled_traffic_bytes() -> int | None:
+    """DRAM bytes (read + write) per launch of the headline kernel at the full configuration, from the line
+    `dram_bytes_per_launch: <n>` of the committed ncu summary; None when the summary or the line is missing."""
+    import re
+
+    try:
+        found = re.search(r"^dram_bytes_per_launch:\s*([0-9_,]+)", HEADLINE_PROFILE.read_text(), re.MULTILINE)
+    except OSError:
+        return None
+    return int(found.group(1).replace(",", "").replace("_", "")) if found else None
+
+
+def headline_config(tokens: int) -> dict:
+    """The `config` object of the JSON line; both arms print the same one."""
+    return {
+        "workload": f"add_rms_norm bf16 x,residual [{tokens}, 8192], weight [8192], eps 1e-5 (benchmark configuration 2), per GPU",
+        "sharding": "tokens, one full batch per GPU, no collective", "l2": "inputs_larger_than_L2 (1 GiB streamed per launch)",
+        "timing": "CUDA events on the launching stream, max over ranks",
+    }
 
 
 def measured_peak() -> tuple[float, str]:
@@ -354,6 +383,60 @@ def torch_eager_incumbent(device, per_op: dict, records_root: str | None) -> Non
         per_op["popcorn_report_rows"] = [str(path) for path in paths]
 
 
+def popcorn_incumbents(device, per_op: dict) -> None:
+    """popcorn's own first-party GPU kernels for two of the five configurations, on the same GPU in the same run:
+    the CUDA SwiGLU (src/popcorn/impls/swiglu.cu:25-41, 77-101, built by popcorn's own JIT loader) on configuration 4
+    and the Triton rotary kernel (src/popcorn/impls/rotary_embedding_tl.py:17-110) on configuration 3.  They are
+    imported directly from the unmodified package: popcorn's dispatcher gates its `popcorn` backend on a Triton
+    version this image does not have.  Adds `popcorn_incumbent` to the two entries of `per_op`."""
+    from popcorn_b200 import workloads
+
+    if reference_popcorn() is None:
+        note = {"unavailable": "the popcorn package is not installed under baseline/_ref"}
+        per_op["swiglu_bf16"]["popcorn_incumbent"] = per_op["rotary_bf16"]["popcorn_incumbent"] = note
+        return
+
+    def guarded(key, body):
+        try:
+            per_op[key]["popcorn_incumbent"] = body()
+        except Exception as error:  # a JIT build or a Triton compile that fails on this box is a finding, not a crash
+            per_op[key]["popcorn_incumbent"] = {"error": f"{type(error).__name__}: {error}"[:300]}
+        torch.cuda.empty_cache()
+
+    def swiglu_leg():
+        from popcorn.impls.swiglu_cu import swiglu as incumbent
+
+        w = workloads.swiglu_bf16().to(device)
+        cols, gate_up = w.args["cols"], w.inputs["gate_up"]
+        a, b = gate_up[:, :cols], gate_up[:, cols:]
+        t0 = time.time()
+        incumbent(a[:8], b[:8])
+        load_s = time.time() - t0
+        strided = time_launches(lambda i: incumbent(a, b), 20, 3, device)
+        a_c, b_c = a.contiguous(), b.contiguous()
+        contiguous = time_launches(lambda i: incumbent(a_c, b_c), 20, 3, device)
+        mine = per_op["swiglu_bf16"]["ms"]
+        return {"kernel": "popcorn.impls.swiglu_cu.swiglu (impls/swiglu.cu fwd_kernel)", "load_s": round(load_s, 1),
+                "ms_on_the_configs_strided_halves": round(strided, 4), "ms_on_contiguous_copies": round(contiguous, 4),
+                "b200_speedup_strided": round(strided / mine, 2), "b200_speedup_contiguous": round(contiguous / mine, 2),
+                "note": "the incumbent copies strided inputs to contiguous tensors first (swiglu.cu:80-81) and rounds once, "
+                        "so it is not bit-equal to popcorn's registered reference"}
+
+    def rotary_leg():
+        from popcorn.impls.rotary_embedding_tl import rotary_embedding as incumbent
+
+        w = workloads.rotary_bf16().to(device)
+        q, k, cos, sin = (w.inputs[name] for name in ("q", "k", "cos", "sin"))
+        incumbent(q[:1], cos, sin, False)
+        both = time_launches(lambda i: (incumbent(q, cos, sin, False), incumbent(k, cos, sin, False)), 20, 5, device)
+        mine = per_op["rotary_bf16"]["ms"]
+        return {"kernel": "popcorn.impls.rotary_embedding_tl.rotary_embedding (Triton _rotary_kernel), q then k, out of place",
+                "ms": round(both, 4), "b200_speedup": round(both / mine, 2)}
+
+    guarded("swiglu_bf16", swiglu_leg)
+    guarded("rotary_bf16", rotary_leg)
+
+
 def bench_extra_ops(device, peak_gbs: float, sampler, scale: float = 1.0, steps: int = 50, match: str = "") -> dict:
     """The ops beyond the five benchmark configurations, at the benchmark shapes they correspond to.
 
@@ -438,6 +521,17 @@ def bench_extra_ops(device, peak_gbs: float, sampler, scale: float = 1.0, steps:
     half = cos3[:, : cos3.shape[1] // 2].contiguous(), sin3[:, : sin3.shape[1] // 2].contiguous()
     run("rotary_partial_bf16 q[8,4096,32,128] (first 64 channels rotated)", lambda: ops.rotary_embedding(q3, half[0], half[1]),
         2 * q3.numel() * 2 + table // 2)
+    return out
+
+
+def per_config_fractions(per_op: dict) -> dict | None:
+    """achieved GB/s / measured copy peak for the kernels of all five configurations, compactly (same run, rank 0)."""
+    if not per_op:
+        return None
+    out = {key: per_op[key]["frac_of_measured_peak"] for key in ("rms_norm_fp32", "add_rms_norm_bf16", "rotary_bf16", "swiglu_bf16") if key in per_op}
+    for phase in ("route", "index", "permute", "unpermute"):
+        if phase in per_op.get("moe_bf16", {}):
+            out[f"moe_{phase}"] = per_op["moe_bf16"][phase]["frac_of_measured_peak"]
     return out
 
 
@@ -604,6 +698,70 @@ def bench_moe_expert_parallel(device, world: int, rank: int, dist, exchange: str
             else "fused: permute kernel stores into peer memory, unpermute kernel loads from peer memory"}
 
 
+def bench_strong_scaling(device, world: int, rank: int, dist, peak_gbs: float, full: dict) -> dict:
+    """Configurations 1-4 (and the MoE steps over all 64 experts, without an exchange) on 1 / world of the tokens per
+    GPU: the job's token count is fixed, so this is strong scaling.  Every rank times its own shard; the step time is
+    the max over ranks, all ranks' times are listed, and the speed-up is against the full configuration on one GPU
+    timed by rank 0 in this same run (`full`).  Configuration 1 is also reported weak (the whole configuration per GPU)."""
+    keys = ["rms_norm_fp32", "add_rms_norm_bf16", "rotary_bf16", "swiglu_bf16"]
+    mine = bench_single_kernel_ops(device, peak_gbs, None, keys, scale=1.0 / world)
+    moe = bench_moe(device, peak_gbs, None, scale=1.0 / world)
+    weak = bench_single_kernel_ops(device, peak_gbs, None, ["rms_norm_fp32"])["rms_norm_fp32"]["ms"]
+    times = torch.tensor([mine[k]["ms"] for k in keys] + [moe["ms"], weak], device=device, dtype=torch.float64)
+    gathered = [torch.empty_like(times) for _ in range(world)]
+    dist.all_gather(gathered, times)
+    table = torch.stack(gathered).cpu()  # [rank, entry]
+    worst = table.max(0).values.tolist()
+    out = {"scaling": "strong", "tokens_per_gpu": "1/%d of each configuration" % world}
+    totals = {"rms_norm_fp32": 4096, "add_rms_norm_bf16": 16384, "rotary_bf16": 32768, "swiglu_bf16": 32768, "moe_bf16_token_sharded": 65536}
+    for column, key in enumerate([*keys, "moe_bf16_token_sharded"]):
+        one_gpu = full.get("moe_bf16" if key.startswith("moe") else key, {}).get("ms")
+        out[key] = {"ms_max_over_ranks": round(worst[column], 5), "ms_per_rank": [round(v, 5) for v in table[:, column].tolist()],
+                    "tokens_per_s": round(totals[key] / (worst[column] * 1e-3), 1), "ms_one_gpu_same_run": one_gpu,
+                    "speedup_vs_one_gpu": round(one_gpu / worst[column], 2) if one_gpu else None}
+    out["rms_norm_fp32_weak"] = {"scaling": "weak (the whole configuration on every GPU)", "ms_max_over_ranks": round(worst[-1], 5),
+                                 "ms_per_rank": [round(v, 5) for v in table[:, -1].tolist()],
+                                 "tokens_per_s": round(world * 4096 / (worst[-1] * 1e-3), 1)}
+    out["note"] = ("configuration 1 on 1/%d of its rows is a %d KiB kernel of a few microseconds: launch latency, not HBM, "
+                   "bounds its strong-scaling figure" % (world, 2 * 4096 * 4096 * 4 // world // 1024))
+    return out
+
+
+def expert_parallel_check(device, world: int, rank: int, dist, exchange: str) -> dict:
+    """Correctness of the expert-parallel exchange at this world size, recorded in the bench line: on its own token shard
+    every rank runs the single-GPU chain (route -> permute -> unpermute) and the expert-parallel one (dispatch -> combine,
+    the experts passing the rows through) and the two results must be bit-equal; the per-expert row counts summed over
+    ranks must equal what the owners received."""
+    from popcorn_b200 import ops, workloads
+    from popcorn_b200.expert_parallel import ExpertParallel
+
+    w = workloads.moe_bf16(scale=1 / 8).shard(rank, world)
+    x, logits = w.inputs["x"].to(device), w.inputs["router_logits"].to(device)
+    experts, top_k = w.args["experts"], w.args["top_k"]
+    indices, weights = ops.moe_route(logits, top_k)
+    rows, counts, _, _, pos = ops.moe_permute(x, indices, experts)
+    want = ops.moe_unpermute(rows, weights, pos)
+    ep = ExpertParallel(experts, top_k, exchange=exchange)
+    state = ep.dispatch(x, logits)
+    if exchange == "p2p":
+        state.out_rows.copy_(state.rows)
+        got = ep.combine(state.out_rows, state)
+    else:
+        got = ep.combine(state.rows, state)
+    total = counts.to(torch.int64)
+    dist.all_reduce(total)
+    local = ep.local_experts
+    offsets = state.expert_offsets.to(device).to(torch.int64)
+    received = offsets[1:] - offsets[:-1]
+    flags = torch.tensor([int(torch.equal(got, want)), int(torch.equal(received, total[rank * local:(rank + 1) * local])),
+                          int(state.rows.shape[0] == int(received.sum()))], device=device)
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    output_equal, counts_equal, rows_equal = (bool(v) for v in flags.tolist())
+    return {"pass": output_equal and counts_equal and rows_equal, "output_bit_equal_to_single_gpu_chain": output_equal,
+            "per_expert_counts_equal_allreduced_bincount": counts_equal, "received_rows_equal_counts": rows_equal,
+            "tokens_per_rank": int(x.shape[0]), "ranks": world}
+
+
 # ------------------------------------------------------------ CPU baseline --
 
 def cpu_reference_fn(key: str, fraction: float):
@@ -644,13 +802,76 @@ def cpu_reference_time(key: str, fraction: float, repeats: int = 5) -> tuple[flo
     return best, tokens, f"{tokens} tokens ({fraction:g} of the configuration), best of {repeats}"
 
 
+def reference_popcorn():
+    """The unmodified popcorn package: already importable, else the install under baseline/_ref; None when absent."""
+    import importlib.util
+    import tempfile
+    import warnings
+
+    os.environ.setdefault("POPCORN_CACHE_DIR", tempfile.mkdtemp(prefix="popcorn-cache-"))
+    if importlib.util.find_spec("popcorn") is None:
+        from oracle import install_reference
+
+        if not install_reference.installed():
+            return None
+        package, extensions = install_reference.stable_locations()
+        sys.path.insert(0, str(package))
+        os.environ.setdefault("TORCH_EXTENSIONS_DIR", str(extensions))
+    warnings.filterwarnings("ignore")
+    import popcorn
+    import popcorn.kernels  # noqa: F401
+
+    return popcorn
+
+
+def cpu_headline_baseline() -> dict:
+    """The `cpu_baseline` object of the GPU arm: the headline configuration on the host cores, best of 5, through the
+    unmodified popcorn package when it is installed (kind "reference"), else through the CPU restatement ("port")."""
+    from popcorn_b200 import workloads
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    w = workloads.add_rms_norm_bf16()
+    popcorn = reference_popcorn()
+    if popcorn is not None:
+        reference, kind, what = popcorn.KERNELS["add_rms_norm"].reference, "reference", "popcorn's add_rms_norm reference called from the unmodified package"
+    else:
+        from oracle import reference_ops
+
+        reference, kind, what = reference_ops.add_rms_norm, "port", "PyTorch CPU restatement of popcorn's add_rms_norm reference"
+    i = w.inputs
+    best = float("inf")
+    with torch.no_grad():
+        for attempt in range(6):
+            t0 = time.perf_counter()
+            reference(i["x"], i["residual"], i["weight"], w.args["eps"], w.args["offset"])
+            if attempt:
+                best = min(best, time.perf_counter() - t0)
+    return {"value": round(w.tokens / best, 1), "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": kind,
+            "sample": f"{w.tokens} tokens (the whole configuration), best of 5; {what}, PyTorch CPU, {torch.get_num_threads()} threads"}
+
+
 def run_reference_arm(args) -> None:
-    """The reference's own CPU implementation of the headline path (the oracle port), all host threads."""
+    """The reference's own implementation of the headline path on the host cores: popcorn's registered PyTorch
+    reference of add_rms_norm (src/popcorn/kernels/add_rms_norm.py:8-23) called from the unmodified package, all host
+    threads, one full configuration (16384 tokens) per step.  Without the package the CPU restatement stands in."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    fraction = 1 / 4
-    fn, tokens = cpu_reference_fn("add_rms_norm_bf16", fraction)
+    from popcorn_b200 import workloads
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    w = workloads.add_rms_norm_bf16(scale=args.scale)
+    x, residual, weight = w.inputs["x"], w.inputs["residual"], w.inputs["weight"]
+    popcorn = reference_popcorn()
+    if popcorn is not None:
+        reference, kind = popcorn.KERNELS["add_rms_norm"].reference, "reference"
+        what = f"popcorn {getattr(popcorn, '__version__', '')} add_rms_norm reference called from the unmodified package, PyTorch CPU".replace("  ", " ")
+    else:
+        from oracle import reference_ops
+
+        reference, kind = reference_ops.add_rms_norm, "port"
+        what = "PyTorch CPU restatement of popcorn's add_rms_norm reference (the package is not installed)"
+    fn = lambda: reference(x, residual, weight, w.args["eps"], w.args["offset"])  # noqa: E731
     with torch.no_grad():
         for _ in range(max(args.warmup, 0)):
             fn()
@@ -659,16 +880,15 @@ def run_reference_arm(args) -> None:
             fn()
         seconds = time.perf_counter() - t0
     ms = seconds * 1e3 / args.steps
-    value = tokens / (ms * 1e-3)
+    value = w.tokens / (ms * 1e-3)
     cores = os.cpu_count() or 1
     line = {
         "impl": "reference", "metric": "tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": 0,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "add_rms_norm bf16 x,residual [16384, 8192], weight [8192], eps 1e-5 (benchmark configuration 2)"},
-        "cpu_baseline": {"value": round(value, 1), "unit": "tokens/s", "cores": cores, "kind": "port",
-                         "sample": f"each step = {tokens} tokens ({fraction:g} of the configuration); "
-                                   "PyTorch CPU restatement of popcorn's add_rms_norm reference, all host threads"},
+        "config": headline_config(w.tokens),
+        "cpu_baseline": {"value": round(value, 1), "unit": "tokens/s", "cores": cores, "kind": kind,
+                         "sample": f"each step = {w.tokens} tokens (the whole configuration); {what}, {torch.get_num_threads()} threads"},
         "e2e": {"value": round(value, 1), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -688,6 +908,7 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", choices=["b200", "reference"], default="b200")
     parser.add_argument("--skip-per-op", action="store_true", help="only the headline loop (used for profiling captures)")
+    parser.add_argument("--skip-incumbents", action="store_true", help="do not time popcorn's own CUDA / Triton kernels beside the b200 ones")
     parser.add_argument("--scale", type=float, default=1.0, help="shrink the token count (profiling captures only)")
     parser.add_argument("--records", metavar="DIR", help="also write popcorn report rows (schema 3) under DIR/v3/reports")
     parser.add_argument("--only", choices=["rms_norm_fp32", "add_rms_norm_bf16", "rotary_bf16", "swiglu_bf16", "paired_rope_bf16", "moe_bf16", "extras", "grouped_gemm"],
@@ -814,6 +1035,8 @@ def main() -> None:
         per_op["moe_bf16"] = bench_moe(device, peak_gbs, sampler)
         if world == 1:
             torch_eager_incumbent(device, per_op, args.records)
+            if not args.skip_incumbents:
+                popcorn_incumbents(device, per_op)
             per_op["beyond_the_five_configs"] = bench_extra_ops(device, peak_gbs, sampler)
             per_op["moe_expert_mlp_bf16"] = bench_grouped_gemm(device, sampler)
             # the CPU reference of every configuration on a bounded token sample, beside the GPU number
@@ -822,12 +1045,19 @@ def main() -> None:
                 cpu_rate = cpu_tokens / seconds
                 per_op[key]["cpu_reference"] = {"tokens_per_s": round(cpu_rate, 1), "cores": os.cpu_count() or 1, "sample": note,
                                                 "gpu_over_cpu": round(per_op[key]["tokens_per_s"] / cpu_rate, 1)}
+    strong = None
     if dist is not None:
         dist.barrier()
         if not args.skip_per_op:
+            full = torch.tensor([per_op[k]["ms"] if rank == 0 else 0.0 for k in
+                                 ("rms_norm_fp32", "add_rms_norm_bf16", "rotary_bf16", "swiglu_bf16", "moe_bf16")], device=device, dtype=torch.float64)
+            dist.broadcast(full, 0)
+            full = {k: {"ms": v} for k, v in zip(("rms_norm_fp32", "add_rms_norm_bf16", "rotary_bf16", "swiglu_bf16", "moe_bf16"), full.tolist())}
+            strong = bench_strong_scaling(device, world, rank, dist, peak_gbs, full)
             for exchange in ("nccl", "p2p"):
                 try:
                     ep_result = bench_moe_expert_parallel(device, world, rank, dist, exchange)
+                    ep_result["ep_check"] = expert_parallel_check(device, world, rank, dist, exchange)
                 except Exception as error:  # symmetric memory may be unavailable on a given box: report, do not hide
                     ep_result = {"error": f"{type(error).__name__}: {error}"}
                 if rank == 0:
@@ -837,29 +1067,25 @@ def main() -> None:
         clocks = sampler.finish()
         cpu = None
         if world == 1 and not args.skip_per_op:
-            seconds, cpu_tokens, note = cpu_reference_time("add_rms_norm_bf16", 1.0)
-            cpu = {"value": round(cpu_tokens / seconds, 1), "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
-                   "sample": note + "; PyTorch CPU restatement of popcorn's add_rms_norm reference, all host threads"}
-        traffic = NCU_TRAFFIC_BYTES["add_rms_norm"]
+            cpu = cpu_headline_baseline()
+        traffic = profiled_traffic_bytes()
         line = {
             "metric": "tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {
-                "workload": f"add_rms_norm bf16 x,residual [{w.tokens}, 8192], weight [8192], eps 1e-5 (benchmark configuration 2), per GPU",
-                "sharding": "tokens, one full batch per GPU, no collective", "l2": "inputs_larger_than_L2 (1 GiB streamed per launch)",
-                "timing": "CUDA events on the launching stream, max over ranks",
-            },
+            "config": headline_config(w.tokens),
             "roofline": {"bound": "hbm", "kernel": "rms_rows_kernel<bf16,256,4,add>", "achieved": round(achieved, 1), "peak": peak_gbs,
                          "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": round(achieved / peak_gbs, 4),
                          "frac_of_8tbs": round(achieved / SPEC_HBM_GBS, 4), "algorithmic_bytes_per_launch": nbytes,
-                         "traffic": None if traffic is None else int(traffic * args.scale)},
+                         "traffic": None if traffic is None else int(traffic * args.scale),
+                         "per_config_frac_of_measured": per_config_fractions(per_op)},
             "cpu_baseline": cpu,
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "windows": len(window_ms), "rule": "median window",
                     "window_values": [round(world * w.tokens / (ms * 1e-3), 1) for ms in window_ms]},
             "gpu_launches": int(launches),
             "clocks": clocks,
+            "strong_scaling": strong,
             "per_op": per_op,
         }
         print(json.dumps(line), flush=True)

@@ -10,13 +10,19 @@ Parity status
     momoe restate registered popcorn references; they are pinned by the golden
     vectors in tests/golden/, which were produced by running the real reference
     (popcorn 0.1.1 imported from its source tree; see tests/golden/make_golden.py).
-  * moe_index / moe_permute / moe_unpermute have NO standalone counterpart in
+  * moe_index / moe_permute / moe_unpermute have no standalone registered op in
     the reference (the steps exist only fused inside the Triton `momoe`
-    implementation), and the reference holds no test that pins their indices:
-    for those three the index-level parity is unpinned.  What is pinned is the
-    end-to-end chain: route -> permute -> per-expert MLP -> unpermute built from
-    these functions reproduces the registered `momoe` reference output on the
-    golden cases (tests/test_oracle_golden.py).
+    implementation).  Their index semantics are pinned against the reference's
+    own kernel: tests/golden/moeindex_*.npz hold the `counts`, `cumsums_N` and
+    `col_idx` outputs of `find_used_experts` + `scatter_cols_kernel`
+    (src/popcorn/impls/momoe_tl.py:1071-1161) run on a B200 on the routing of
+    every momoe fixture and of the MoE benchmark configuration
+    (tests/golden/make_moe_index_golden.py); `moe_index` reproduces them
+    bit-for-bit (tests/test_oracle_golden.py).  `pos`, the inverse map, is not
+    materialised by the reference and is checked as the inverse of `perm`.
+    The weighted combine is pinned through the chain: route -> permute ->
+    per-expert MLP -> unpermute built from these functions reproduces the
+    registered `momoe` reference output on the golden cases.
 
 Every function runs on CPU tensors with plain torch ops, in the same order of
 operations (and therefore the same intermediate roundings) as the reference.

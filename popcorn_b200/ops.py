@@ -78,8 +78,22 @@ def _rows(t: Tensor) -> tuple[Tensor, int]:
     return flat, max(width, 1)
 
 
+class _DevicePointer(ctypes.c_void_p):
+    """A device address that keeps its tensor alive for as long as the pointer object exists.
+
+    Call sites write `_ptr(weight.contiguous())` inside the argument list of `_lib.call`.  When the tensor
+    is not contiguous that expression makes a copy whose only reference is this object; without it the copy
+    would go back to the caching allocator before the launch, and the next `.contiguous()` in the same
+    argument list could be handed the same block (two operands would then alias).  The argument tuple holds
+    every pointer until the call has enqueued its kernels, after which stream order protects the block."""
+
+    tensor: Tensor | None = None
+
+
 def _ptr(t: Tensor | None) -> ctypes.c_void_p:
-    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+    pointer = _DevicePointer(0 if t is None else t.data_ptr())
+    pointer.tensor = t
+    return pointer
 
 
 def _stream(device: torch.device) -> ctypes.c_void_p:

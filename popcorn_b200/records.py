@@ -27,8 +27,8 @@ SCHEMA = 3
 BACKEND = "b200"
 
 # Fingerprints popcorn 0.1.1 computes for the references of its four ops, for the
-# three op definitions in popcorn_b200/plugin.py, and for the dispatch predicate
-# `plugin.accepts` (the implementation hash of a bare external source).  A row whose
+# three op definitions in popcorn_b200/plugin.py, and for the dispatch predicates
+# `plugin.PREDICATES` (the implementation hash of a bare external source is the hash of its predicate).  A row whose
 # hashes differ from the live ones is ignored by popcorn as stale;
 # tests/test_records.py recomputes them whenever popcorn is importable.
 REFERENCE_HASHES = {
@@ -45,7 +45,7 @@ REFERENCE_HASHES = {
     "moe_permute": "2d4425c300da",
     "moe_unpermute": "96a7326d99b2",
 }
-IMPLEMENTATION_HASH = "e5690e260cc5"  # a bare source gated by plugin.accepts
+IMPLEMENTATION_HASH = "1c417c864f16"  # a bare source gated by one of plugin.PREDICATES (one closure body, so one hash)
 # ops registered with their own predicate hash differently
 IMPLEMENTATION_HASHES: dict[str, str] = {}
 

@@ -17,14 +17,14 @@ GOLDEN_DIR = Path(__file__).resolve().parent
 _BITS = {torch.bfloat16: torch.int16, torch.float16: torch.int16}
 
 
-def save_case(name: str, tensors: dict[str, torch.Tensor], meta: dict[str, Any]) -> Path:
+def save_case(name: str, tensors: dict[str, torch.Tensor], meta: dict[str, Any], directory: Path | None = None) -> Path:
     arrays: dict[str, np.ndarray] = {"meta": np.array(json.dumps(meta))}
     for key, value in tensors.items():
         value = value.detach().cpu().contiguous()
         dtype_name = str(value.dtype).removeprefix("torch.")
         raw = value.view(_BITS[value.dtype]) if value.dtype in _BITS else value
         arrays[f"{key}|{dtype_name}"] = raw.numpy()
-    path = GOLDEN_DIR / f"{name}.npz"
+    path = (directory or GOLDEN_DIR) / f"{name}.npz"
     np.savez_compressed(path, **arrays)
     return path
 

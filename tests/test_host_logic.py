@@ -1,14 +1,9 @@
 """Host-side behaviour that needs no GPU: the registry mirror, the popcorn plugin, input checks."""
 
-import importlib.util
-import os
-import sys
-import warnings
-from pathlib import Path
-
 import pytest
 import torch
 
+from tests import popcorn_location
 from popcorn_b200 import kernels, ops, registry, workloads
 
 
@@ -125,17 +120,11 @@ def test_workload_shapes_and_bytes():
     assert r.shard(0, 2).inputs["q"].shape[0] == 1 and r.shard(0, 2).inputs["cos"].shape == (64, 64)
 
 
-REFERENCE_SRC = Path(os.environ.get("POPCORN_SOURCE_TREE", "/root/reference/src"))
-HAVE_POPCORN = importlib.util.find_spec("popcorn") is not None or (REFERENCE_SRC / "popcorn").is_dir()
 
 
-@pytest.mark.skipif(not HAVE_POPCORN, reason="popcorn itself is not importable on this machine")
+@pytest.mark.skipif(not popcorn_location.available(), reason=popcorn_location.MISSING)
 def test_plugin_registers_on_real_popcorn(tmp_path, monkeypatch):
-    if importlib.util.find_spec("popcorn") is None:
-        monkeypatch.syspath_prepend(str(REFERENCE_SRC))
-    monkeypatch.setenv("POPCORN_CACHE_DIR", str(tmp_path))
-    warnings.filterwarnings("ignore")
-    import popcorn
+    popcorn = popcorn_location.import_popcorn(tmp_path, monkeypatch)
 
     from popcorn_b200 import plugin
 
@@ -193,3 +182,58 @@ def test_host_pipeline_chunks_cover_the_rows_once():
         assert bounds[0][0] == 0 and bounds[-1][1] == rows
         assert all(a[1] == b[0] for a, b in zip(bounds, bounds[1:])) and all(0 < hi - lo <= chunk for lo, hi in bounds)
     assert chunk_bounds(0, 64) == []
+
+
+def test_dispatch_rules_mirror_the_ops_argument_checks():
+    """`plugin.RULES[op]` names a reason for every call the op itself would refuse (shape, dtype and limit checks;
+    placement is `plugin.accepts`, which needs a GPU), and none for the calls it takes."""
+    from popcorn_b200 import plugin
+
+    bf16, f32 = torch.bfloat16, torch.float32
+    x, w = torch.zeros(4, 64, dtype=bf16), torch.ones(64, dtype=bf16)
+    taken = {
+        "rms_norm": dict(x=x, weight=w, bias=None, eps=1e-6),
+        "layer_norm": dict(x=x, weight=w, bias=w, eps=1e-6),
+        "add_rms_norm": dict(x=x, residual=x, weight=w, eps=1e-6, offset=0.0),
+        "rms_norm_gated": dict(x=x, g=x, weight=w, bias=None, activation="sigmoid", eps=1e-6),
+        "l2_norm": dict(x=x, eps=1e-6),
+        "swiglu": dict(a=x, b=x), "geglu": dict(a=x, b=x),
+        "rotary_embedding": dict(x=torch.zeros(2, 8, 4, 64, dtype=bf16), cos=torch.zeros(8, 16), sin=torch.zeros(8, 16), interleaved=False),
+        "rope": dict(q=torch.zeros(2, 4, 8, 64, dtype=bf16), k=torch.zeros(2, 1, 8, 64, dtype=bf16), cos=torch.zeros(1, 8, 64, dtype=bf16), sin=torch.zeros(1, 8, 64, dtype=bf16)),
+        "qk_norm_rope": dict(q=torch.zeros(2, 4, 8, 64, dtype=bf16), k=torch.zeros(2, 1, 8, 64, dtype=bf16), q_weight=w, k_weight=w,
+                             cos=torch.zeros(2, 8, 64, dtype=bf16), sin=torch.zeros(2, 8, 64, dtype=bf16), eps=1e-6),
+        "llama4_rope": dict(q=torch.zeros(2, 8, 4, 64, dtype=bf16), k=torch.zeros(2, 8, 1, 64, dtype=bf16), freqs=torch.zeros(8, 32, 2, dtype=bf16)),
+        "moe_route": dict(router_logits=torch.zeros(4, 64), top_k=8),
+        "moe_permute": dict(x=x, indices=torch.zeros(4, 2, dtype=torch.int32), experts=8),
+        "moe_unpermute": dict(rows=torch.zeros(8, 64, dtype=bf16), weights=torch.zeros(4, 2), pos=torch.zeros(4, 2, dtype=torch.int32)),
+        "momoe": dict(x=torch.zeros(1, 4, 64, dtype=bf16), gate_weight=torch.zeros(8, 64, 32, dtype=bf16), up_weight=torch.zeros(8, 64, 32, dtype=bf16),
+                      down_weight=torch.zeros(8, 32, 64, dtype=bf16), router_logits=torch.zeros(1, 4, 8), top_k=2),
+    }
+    assert set(taken) == set(plugin.RULES) == {*plugin.EXISTING_OPS, *plugin.NEW_OPS}
+    for name, arguments in taken.items():
+        assert plugin.RULES[name](**arguments) is None, name
+    refused = [
+        ("rms_norm", dict(weight=w.float())), ("rms_norm", dict(bias=w.float())), ("rms_norm", dict(weight=torch.ones(32, dtype=bf16))),
+        ("layer_norm", dict(weight=w.float())), ("add_rms_norm", dict(residual=x.float())), ("add_rms_norm", dict(residual=x[:2])),
+        ("rms_norm_gated", dict(activation="relu")), ("rms_norm_gated", dict(g=x.float())),
+        ("swiglu", dict(b=x.float())), ("geglu", dict(b=x[:, :32])),
+        ("rotary_embedding", dict(x=torch.zeros(2, 8, 64, 4, dtype=bf16).transpose(2, 3))),      # head_dim strided
+        ("rotary_embedding", dict(cos=torch.zeros(8, 48), sin=torch.zeros(8, 48))),               # 2 * half > head_dim
+        ("rotary_embedding", dict(cos=torch.zeros(8, 16, dtype=torch.float16), sin=torch.zeros(8, 16, dtype=torch.float16))),
+        ("rotary_embedding", dict(cos=torch.zeros(1, 8, 1, 16), sin=torch.zeros(1, 8, 1, 16))),   # broadcastable, not [seq, half]
+        ("rope", dict(cos=torch.zeros(1, 8, 64), sin=torch.zeros(1, 8, 64))),                     # fp32 tables on bf16 q
+        ("rope", dict(k=torch.zeros(2, 1, 9, 64, dtype=bf16))),
+        ("qk_norm_rope", dict(q_weight=w.float())), ("llama4_rope", dict(freqs=torch.zeros(8, 32, 2))),
+        ("moe_route", dict(router_logits=torch.zeros(4, 2048))), ("moe_route", dict(top_k=40)), ("moe_route", dict(top_k=0)),
+        ("moe_permute", dict(indices=torch.zeros(4, 2, dtype=torch.int64))), ("moe_permute", dict(experts=4096)),
+        ("moe_unpermute", dict(weights=torch.zeros(4, 2, dtype=bf16))), ("moe_unpermute", dict(pos=torch.zeros(4, 2, dtype=torch.int64))),
+        ("momoe", dict(x=torch.zeros(1, 4, 64))), ("momoe", dict(down_weight=torch.zeros(8, 32, 64))),
+        ("momoe", dict(router_logits=torch.zeros(1, 4, 9))),
+    ]
+    for name, change in refused:
+        reason = plugin.RULES[name](**{**taken[name], **change})
+        assert isinstance(reason, str) and reason, (name, sorted(change))
+    # on a machine without a GPU every predicate declines (placement comes first) instead of raising
+    for name, arguments in taken.items():
+        assert plugin.PREDICATES[name](**arguments) is False
+        assert "CUDA" in plugin.declined(name, **arguments)

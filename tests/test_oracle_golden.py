@@ -138,6 +138,38 @@ def test_index_is_a_stable_sort_by_expert():
     assert torch.equal(flat[(pos.reshape(-1).argsort())], flat.sort(stable=True).values)
 
 
+def sha256(t):
+    import hashlib
+
+    return hashlib.sha256(t.contiguous().numpy().tobytes()).hexdigest()
+
+
+@pytest.mark.parametrize("name", names("moeindex_"))
+def test_index_equals_the_references_own_kernel(name):
+    """counts / cumsums / col_idx written by the reference's find_used_experts + scatter_cols_kernel
+    (src/popcorn/impls/momoe_tl.py:1071-1161) on a GPU, fixtures made by tests/golden/make_moe_index_golden.py."""
+    t, meta = load_case(name)
+    if "topk_indices" in t:
+        if "router_logits" in t:
+            routed, _ = oracle.moe_route(t["router_logits"], meta["top_k"])
+            assert torch.equal(routed, t["topk_indices"])
+        indices = t["topk_indices"]
+    else:  # the full-size configuration: inputs from the seed, long outputs kept as digests
+        from popcorn_b200 import workloads
+
+        w = workloads.moe_bf16()
+        indices, _ = oracle.moe_route(w.inputs["router_logits"], meta["top_k"])
+        assert sha256(indices) == meta["topk_indices_sha256"]
+    counts, offsets, perm, pos = oracle.moe_index(indices, meta["experts"])
+    assert torch.equal(counts, t["counts"]) and torch.equal(offsets, t["cumsums"])
+    if "col_idx" in t:
+        assert torch.equal(perm, t["col_idx"])
+    else:
+        edge = t["col_idx_head"].numel()
+        assert torch.equal(perm[:edge], t["col_idx_head"]) and torch.equal(perm[-edge:], t["col_idx_tail"])
+        assert sha256(perm) == meta["col_idx_sha256"]
+
+
 def test_unpermute_matches_einsum():
     """The fixed summation order stays within fp32 rounding of the reference's einsum (momoe.py:53)."""
     gen = torch.Generator().manual_seed(8)

@@ -380,3 +380,89 @@ def test_host_tensor_pipeline_matches_the_device_op():
     y2, s2 = torch.empty_like(y).pin_memory(), torch.empty_like(s).pin_memory()
     host.add_rms_norm_host(x, r, gpu(w), 1e-5, 0.0, y=y2, s=s2, chunk_rows=1 << 20)
     assert torch.equal(y2, y) and torch.equal(s2, s)
+
+
+# ------------------------------------------- parameters that are not contiguous --
+# Every parameter below is a strided view, so the op has to make contiguous copies of TWO operands for one
+# launch; both copies must be alive (and distinct) when the kernel runs.
+
+def strided(t):
+    """The same values as `t`, stored with a gap after every element (last stride 2)."""
+    wide = torch.empty(*t.shape[:-1], t.shape[-1] * 2, dtype=t.dtype, device=DEV)
+    view = wide[..., ::2]
+    view.copy_(t)
+    assert not view.is_contiguous() or view.numel() <= 1
+    return view
+
+
+def test_strided_cos_and_sin():
+    x = randn(2100, 2, 48, 4, 64, dtype=BF16, scale=2.0)
+    cos, sin = torch.cos(randn(2101, 48, 32)), torch.sin(randn(2102, 48, 32))
+    want = oracle.rotary_embedding(x, cos, sin)
+    assert torch.equal(ops.rotary_embedding(gpu(x), strided(cos), strided(sin)).cpu(), want)
+    q, k = gpu(x).clone(), gpu(x[:, :, :2]).clone()
+    ops.rotary_embedding_qk_(q, k, strided(cos), strided(sin))
+    assert torch.equal(q.cpu(), want) and torch.equal(k.cpu(), want[:, :, :2])
+    # the paired op and the fused norm + rope: cos, sin (and both weights) strided at once
+    qp, kp = randn(2103, 2, 4, 48, 64, dtype=BF16), randn(2104, 2, 2, 48, 64, dtype=BF16)
+    cosp, sinp = torch.cos(randn(2105, 1, 48, 64)).to(BF16), torch.sin(randn(2106, 1, 48, 64)).to(BF16)
+    want_q, want_k = oracle.rope(qp, kp, cosp, sinp)
+    got_q, got_k = ops.rope(gpu(qp), gpu(kp), strided(cosp), strided(sinp))
+    assert torch.equal(got_q.cpu(), want_q) and torch.equal(got_k.cpu(), want_k)
+    wq, wk = 1 + 0.1 * randn(2107, 64), 1 + 0.1 * randn(2108, 64)
+    want_q, want_k = oracle.qk_norm_rope(qp, kp, wq.to(BF16), wk.to(BF16), cosp, sinp, 1e-6)
+    got_q, got_k = ops.qk_norm_rope(gpu(qp), gpu(kp), strided(wq.to(BF16)), strided(wk.to(BF16)), strided(cosp), strided(sinp), 1e-6)
+    check(got_q, want_q, what="qk_norm_rope q, strided parameters")
+    check(got_k, want_k, what="qk_norm_rope k, strided parameters")
+
+
+@pytest.mark.parametrize("dtype", [BF16, F32])
+def test_strided_weight_and_bias(dtype):
+    x = randn(2110, 24, 1024, dtype=dtype)
+    w, b = (1 + 0.1 * randn(2111, 1024)).to(dtype), (0.5 * randn(2112, 1024)).to(dtype)
+    check(ops.rms_norm(gpu(x), strided(w), strided(b), 1e-6), oracle.rms_norm(x, w, b, 1e-6), what="rms_norm, strided weight and bias")
+    check(ops.layer_norm(gpu(x), strided(w), strided(b), 1e-6), oracle.layer_norm(x, w, b, 1e-6), what="layer_norm, strided weight and bias")
+    g = randn(2113, 24, 1024, dtype=dtype)
+    check(ops.rms_norm_gated(gpu(x), gpu(g), strided(w), strided(b), "swish", 1e-6), oracle.rms_norm_gated(x, g, w, b, "swish", 1e-6),
+          what="rms_norm_gated, strided weight and bias")
+
+
+def test_gate_and_up_weights_sliced_from_one_tensor():
+    experts, hidden, inter, rows_per = 4, 256, 128, 96
+    both = (randn(2120, experts, hidden, 2 * inter) / hidden ** 0.5).to(BF16)
+    rows = randn(2121, experts * rows_per, hidden, dtype=BF16)
+    offsets = torch.arange(0, experts * rows_per + 1, rows_per, dtype=torch.int32)
+    gate, up = both[..., :inter], both[..., inter:]
+    want = oracle.moe_grouped_gemm(rows, gate.contiguous(), offsets, up.contiguous())
+    fused = gpu(both)
+    got = ops.moe_grouped_gemm(gpu(rows), fused[..., :inter], gpu(offsets), fused[..., inter:])
+    excess = (got.cpu().float() - want.float()).abs() / want.float().abs().clamp(min=1.0)
+    assert float(excess.max()) <= 2e-2, float(excess.max())
+
+
+# ------------------------------------------------ index build against the reference's own kernel --
+
+@pytest.mark.parametrize("name", [n for n in case_names() if n.startswith("moeindex_")])
+def test_index_equals_the_references_own_kernel(name):
+    """b200_moe_index against counts / cumsums / col_idx written by the reference's find_used_experts
+    (src/popcorn/impls/momoe_tl.py:1126-1161) on the same routing; bit-exact."""
+    import hashlib
+
+    t, meta = load_case(name)
+    if "topk_indices" in t:
+        indices = gpu(t["topk_indices"])
+    else:
+        w = workloads.moe_bf16()
+        indices, _ = ops.moe_route(gpu(w.inputs["router_logits"]), meta["top_k"])
+        assert hashlib.sha256(indices.cpu().numpy().tobytes()).hexdigest() == meta["topk_indices_sha256"]
+    counts, offsets, perm, pos = (r.cpu() for r in ops.moe_index(indices, meta["experts"]))
+    assert torch.equal(counts, t["counts"]) and torch.equal(offsets, t["cumsums"])
+    if "col_idx" in t:
+        assert torch.equal(perm, t["col_idx"])
+    else:
+        edge = t["col_idx_head"].numel()
+        assert torch.equal(perm[:edge], t["col_idx_head"]) and torch.equal(perm[-edge:], t["col_idx_tail"])
+        assert hashlib.sha256(perm.numpy().tobytes()).hexdigest() == meta["col_idx_sha256"]
+    # pos is the inverse map the reference does not materialise: it must invert perm
+    tokens, top_k = pos.shape
+    assert torch.equal(perm[pos.reshape(-1).long()], torch.arange(tokens, dtype=torch.int32).repeat_interleave(top_k))

@@ -1,18 +1,13 @@
 """Report rows written by popcorn_b200.records are rows popcorn itself reads, trusts and ranks."""
 
-import importlib.util
 import json
-import os
-import warnings
-from pathlib import Path
 
 import pytest
 import torch
 
+from tests import popcorn_location
 from popcorn_b200 import records
 
-REFERENCE_SRC = Path(os.environ.get("POPCORN_SOURCE_TREE", "/root/reference/src"))
-HAVE_POPCORN = importlib.util.find_spec("popcorn") is not None or (REFERENCE_SRC / "popcorn").is_dir()
 
 
 def example_row(op="add_rms_norm", name="add_rms_norm_bf16", device="NVIDIA B200", fwd_ms=0.157, ref_fwd_ms=2.9, training=False):
@@ -61,13 +56,9 @@ def test_grade_follows_popcorns_verdict():
     assert records.grade("float32", floor)[0] == "fail" and records.grade("float32", {"0": {"err": float("nan"), "budget": 0, "scale": 1}})[0] == "fail"
 
 
-@pytest.mark.skipif(not HAVE_POPCORN, reason="popcorn itself is not importable on this machine")
+@pytest.mark.skipif(not popcorn_location.available(), reason=popcorn_location.MISSING)
 def test_popcorn_reads_and_ranks_the_rows(tmp_path, monkeypatch):
-    if importlib.util.find_spec("popcorn") is None:
-        monkeypatch.syspath_prepend(str(REFERENCE_SRC))
-    monkeypatch.setenv("POPCORN_CACHE_DIR", str(tmp_path))
-    warnings.filterwarnings("ignore")
-    import popcorn
+    popcorn = popcorn_location.import_popcorn(tmp_path, monkeypatch)
     from popcorn.bench.model import Case, Record
     from popcorn.core.config import config_id
 
