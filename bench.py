@@ -263,9 +263,16 @@ def bench_moe(device, peak_gbs: float, sampler, scale: float = 1.0, fixed_steps:
     stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
     y = torch.empty_like(x)
     p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    need = ctypes.c_size_t(0)
+    _lib.call("b200_moe_index_scratch_bytes", tokens, top_k, experts, ctypes.byref(need))
+    scratch = torch.empty(max(need.value, 16), dtype=torch.uint8, device=device)
+    idx2, wts2 = torch.empty_like(idx), torch.empty_like(wts)
+    counts2, offsets2, perm2, pos2 = (torch.empty_like(t) for t in (counts, offsets, perm, pos))
     phases = {
-        "route": lambda i: ops.moe_route(logits, top_k),
-        "index": lambda i: ops.moe_index(idx, experts),
+        # every phase straight through the C ABI into outputs allocated up front, like the other configurations
+        "route": lambda i: _lib.call("b200_moe_route", p(logits), p(idx2), p(wts2), tokens, experts, top_k, experts, _lib.F32, stream),
+        "index": lambda i: _lib.call("b200_moe_index", p(idx), tokens, top_k, experts, p(counts2), p(offsets2), p(perm2), p(pos2),
+                                     p(scratch), ctypes.c_size_t(scratch.numel()), stream),
         # permute and unpermute alone, straight through the C ABI (moe_permute the op also rebuilds the index)
         "permute": lambda i: _lib.call("b200_moe_permute", p(x), p(pos), p(rows), tokens, top_k, hidden, hidden, hidden, _lib.BF16, stream),
         "unpermute": lambda i: _lib.call("b200_moe_unpermute", p(rows), p(wts), p(pos), p(y), tokens, top_k, hidden, hidden, hidden, _lib.BF16, stream),

@@ -54,9 +54,11 @@ def outputs(value):
 
 def close(got, want, what, row_sums=False):
     """max-abs within the dtype's bound.  `row_sums`: the output scales every element by a per-row fp32 sum that this
-    backend and torch's GPU kernels add up in different orders; a last-bit difference in that factor moves a few
-    products across a 16-bit rounding boundary, and where |y| >= 4 one bf16 step is 0.03125 > 2e-2.  Such elements may
-    differ by exactly one step of the output dtype, and there must be at most a handful per million."""
+    backend and torch's GPU kernels add up in different orders.  A last-bit difference in that factor moves a few of
+    the reference's intermediate roundings (normalised value to 16 bits, then times the weight to 16 bits again) to the
+    neighbouring 16-bit value; times a weight above one and rounded again that is up to two steps of the output, and
+    from |y| >= 2 two bf16 steps (0.03125) are more than 2e-2.  Such elements may differ by at most two steps of the
+    output dtype, and there must be at most a handful per million; everything else is within the bound."""
     assert got.shape == want.shape and got.dtype == want.dtype and got.device == want.device, what
     if not want.is_floating_point():
         assert torch.equal(got, want), f"{what}: integer output differs"
@@ -66,8 +68,9 @@ def close(got, want, what, row_sums=False):
     diff = (got.double() - want.double()).abs()
     over = diff > MAX_ABS[want.dtype]
     if row_sums and want.dtype != torch.float32 and bool(over.any()):
-        step = torch.finfo(want.dtype).eps * 2.0 ** torch.floor(torch.log2(want.double().abs()[over]))
-        assert bool((diff[over] <= step).all()), f"{what}: a difference larger than one {want.dtype} step"
+        larger = torch.maximum(want.double().abs(), got.double().abs())[over]
+        step = torch.finfo(want.dtype).eps * 2.0 ** torch.floor(torch.log2(larger))
+        assert bool((diff[over] <= 2 * step).all()), f"{what}: a difference larger than two {want.dtype} steps"
         assert int(over.sum()) <= max(4, want.numel() // 250_000), f"{what}: {int(over.sum())} one-step differences above {MAX_ABS[want.dtype]:.0e}"
         return
     worst = float(diff.max())
