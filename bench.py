@@ -694,7 +694,11 @@ def bench_moe_expert_parallel(device, world: int, rank: int, dist, exchange: str
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms = float(ms.item())
     hidden_bytes = x.shape[1] * x.element_size()
-    sent_remote = (sum(state.send_counts) - state.send_counts[rank]) * hidden_bytes
+    if exchange == "p2p":
+        ep.check()  # no wait ran out, nothing over capacity
+        sent_remote = int(state.info[1]) * hidden_bytes  # counted by the exchange kernel on the device
+    else:
+        sent_remote = (sum(state.send_counts) - state.send_counts[rank]) * hidden_bytes
     link = torch.tensor([float(sent_remote)], device=device, dtype=torch.float64)
     dist.all_reduce(link, op=dist.ReduceOp.MAX)
     return {"ms": round(ms, 4), "tokens_per_s": round(65536 / (ms * 1e-3), 1), "scaling": "strong (65536 tokens over all ranks)",
@@ -760,8 +764,11 @@ def expert_parallel_check(device, world: int, rank: int, dist, exchange: str) ->
     local = ep.local_experts
     offsets = state.expert_offsets.to(device).to(torch.int64)
     received = offsets[1:] - offsets[:-1]
+    in_use = int(state.info[0]) if exchange == "p2p" else state.rows.shape[0]
+    if exchange == "p2p":
+        ep.check()
     flags = torch.tensor([int(torch.equal(got, want)), int(torch.equal(received, total[rank * local:(rank + 1) * local])),
-                          int(state.rows.shape[0] == int(received.sum()))], device=device)
+                          int(in_use == int(received.sum()))], device=device)
     dist.all_reduce(flags, op=dist.ReduceOp.MIN)
     output_equal, counts_equal, rows_equal = (bool(v) for v in flags.tolist())
     return {"pass": output_equal and counts_equal and rows_equal, "output_bit_equal_to_single_gpu_chain": output_equal,

@@ -513,6 +513,35 @@ int b200_moe_grouped_gemm_wgrad(const void* rows, const void* grad_out, const in
                                 int dtype, void* stream);
 
 /*
+ * Expert-parallel exchange without the host in the loop (no counterpart in the reference, which is single-GPU:
+ * src/popcorn/kernels/momoe.py:34-53).  Every rank owns a "meta" buffer of b200_moe_ep_meta_bytes() bytes, zeroed
+ * once, 128-byte aligned and mapped by all ranks (symmetric memory); meta[r] is rank r's buffer as mapped into this
+ * process.  Epochs must grow by one per step and start above zero.
+ *
+ * b200_moe_ep_exchange publishes this rank's per-expert `counts` (the output of b200_moe_index) into every rank's
+ * meta buffer, waits for every rank's counts and derives this rank's addressing on the device:
+ *   dst_base[experts]                 row in the buffer of the expert's owner at which THIS rank's rows for that
+ *                                     expert start (expert-major, source ranks in rank order inside an expert): the
+ *                                     dst_base input of b200_moe_ep_destinations
+ *   expert_offsets[experts/world + 1] segment starts of this rank's own experts in its own buffer
+ *   info[4]                           rows this rank receives, rows it sends to other ranks, largest receive, world
+ * b200_moe_ep_barrier (channel 1 .. 3) announces that this rank has reached `epoch` on `channel` and waits until
+ * every rank has: after a kernel that stored rows into peer memory, and before a kernel that loads them.
+ *
+ * Waits are bounded by budget_ns.  A wait that runs out, or a rank that would receive more than capacity_rows rows,
+ * makes no kernel trap or hang: status[0] (int32, device memory, zeroed by the caller) gets 1 (count exchange timed
+ * out), 2 (rendezvous timed out) or 3 (over capacity), status[1] the peer or the row count, and after a failed
+ * exchange every dst_base entry is negative, so that the row kernels skip every pair.  Ranks must be separate GPUs:
+ * two ranks launched on one GPU would wait for each other without a guarantee of running at the same time.
+ */
+int b200_moe_ep_meta_bytes(size_t* bytes);
+int b200_moe_ep_exchange(const int32_t* counts, void* const* meta, int64_t world, int64_t rank, int64_t experts,
+                         int64_t capacity_rows, int32_t epoch, int64_t budget_ns, int32_t* dst_base,
+                         int32_t* expert_offsets, int32_t* info, int32_t* status, void* stream);
+int b200_moe_ep_barrier(void* const* meta, int64_t world, int64_t rank, int64_t channel, int32_t epoch, int64_t budget_ns,
+                        int32_t* status, void* stream);
+
+/*
  * For each (token, slot) pair: dst_rank = indices / experts_per_rank and
  * dst_row = dst_base[expert] + (pos - local_offsets[expert]), the pair's row in the
  * owning rank's buffer.  dst_base[e] is the row at which this rank's block for

@@ -68,6 +68,9 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "b200_moe_grouped_gemm_dgrad": (_int, [_ptr] * 6 + [_i64] * 6 + [_int, _ptr]),
     "b200_moe_grouped_gemm_wgrad": (_int, [_ptr] * 4 + [_i64] * 6 + [_int, _ptr]),
     "b200_moe_ep_destinations": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr, _ptr, _ptr]),
+    "b200_moe_ep_meta_bytes": (_int, [ctypes.POINTER(_size)]),
+    "b200_moe_ep_exchange": (_int, [_ptr, ctypes.POINTER(_ptr), _i64, _i64, _i64, _i64, ctypes.c_int32, _i64, _ptr, _ptr, _ptr, _ptr, _ptr]),
+    "b200_moe_ep_barrier": (_int, [ctypes.POINTER(_ptr), _i64, _i64, _i64, ctypes.c_int32, _i64, _ptr, _ptr]),
     "b200_moe_permute_multi": (_int, [_ptr, _ptr, _ptr, ctypes.POINTER(_ptr), _i64, _i64, _i64, _i64, _i64, _i64, _int, _ptr]),
     "b200_moe_unpermute_multi": (_int, [ctypes.POINTER(_ptr), _i64, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _int, _ptr]),
 }

@@ -25,15 +25,17 @@ The per-rank compute steps come from `local_ops` (default: popcorn_b200.ops, the
 CUDA kernels).  Tests of the exchange logic on CPU processes pass a namespace of
 CPU functions with the same signatures and run it over the gloo backend.
 
-exchange="p2p" (CUDA only) fuses each exchange into the kernel next to it.  Every
-rank owns two symmetric buffers that all ranks map (torch symmetric memory over
-NVLink): `recv`, which the ranks' permute kernels fill with ordinary stores
-straight from their token rows, already in the final (expert, source rank, token)
-order, and `out`, from which the token owners' unpermute kernels load the expert
-outputs while they accumulate.  A step then has no bulk collective, no send or
-receive staging buffer and no reorder pass: only the small all-gather of the
-counts and one tiny all-reduce per direction that orders the ranks around the
-kernel.
+exchange="p2p" (CUDA only) fuses each exchange into the kernel next to it and keeps the host out of the step.
+Every rank owns symmetric buffers that all ranks map (torch symmetric memory over NVLink): `recv`, which the
+ranks' permute kernels fill with ordinary stores straight from their token rows, already in the final
+(expert, source rank, token) order; `out`, from which the token owners' unpermute kernels load the expert outputs
+while they accumulate; and a small `meta` buffer of counts and flags.  A step is then: route, index, one kernel that
+writes this rank's per-expert counts into every rank's meta buffer, waits (bounded) for everybody's and derives the
+addressing on the device, the destinations kernel, the permute kernel, a flag rendezvous; and for the combine a flag
+rendezvous and the unpermute kernel.  No bulk collective, no NCCL call, no staging buffer, no reorder pass and no
+device-to-host copy: `Dispatched.rows` is the whole receive buffer and `expert_offsets` (a device tensor) says which
+rows are in use, which is what the grouped expert GEMM reads.  A wait that runs out or a receive beyond the buffers'
+capacity is recorded in a status word (`ExpertParallel.check()` reads it) instead of hanging or trapping.
 """
 
 from __future__ import annotations
@@ -90,16 +92,18 @@ class Dispatched:
     """What dispatch() hands to the expert computation, plus what combine() needs later."""
 
     rows: Tensor            # [received, hidden], grouped by local expert, global stable order inside
-    expert_offsets: Tensor  # int32 [local_experts + 1] into rows (host tensor)
+                            # (exchange="p2p": the whole receive buffer; expert_offsets[-1] rows of it are in use)
+    expert_offsets: Tensor  # int32 [local_experts + 1] into rows (host tensor; exchange="p2p": device tensor)
     weights: Tensor         # fp32 [local_tokens, top_k]
     pos: Tensor             # int32 [local_tokens, top_k] positions in this rank's send buffer
     send_counts: list[int]  # rows sent to each rank
     recv_counts: list[int]  # rows received from each rank
     reorder: Tensor | None  # int32 [received]: rows[p] = arrived[reorder[p]]  (exchange="nccl")
-    counts_all: Tensor      # int32 [world, experts] (host tensor)
+    counts_all: Tensor | None  # int32 [world, experts] (host tensor; None with exchange="p2p", whose counts stay on the device)
     dst_rank: Tensor | None = None  # int32 [local_tokens, top_k]: owner of each pair's expert   (exchange="p2p")
     dst_row: Tensor | None = None   # int32 [local_tokens, top_k]: row in the owner's buffer      (exchange="p2p")
-    out_rows: Tensor | None = None  # [received, hidden] view of the symmetric output buffer: write expert results here
+    out_rows: Tensor | None = None  # the symmetric output buffer, rows as in `rows`: write expert results here
+    info: Tensor | None = None      # int32 [4] on the device: rows received, rows sent to other ranks, largest receive, world
 
 
 def exchange_plan(counts_all: Tensor, rank: int) -> tuple[list[int], list[int], Tensor, Tensor, Tensor]:
@@ -158,7 +162,9 @@ class ExpertParallel:
         self.exchange = exchange
         self.capacity_rows = capacity_rows
         self._symmetric = None  # (recv, out, recv_ptrs, out_ptrs, capacity, hidden, dtype), built on first use
-        self._flag: Tensor | None = None
+        self._meta_ptrs: list[int] = []
+        self._status: Tensor | None = None  # int32 [2] on the device: first failure of a fused-exchange kernel
+        self._epoch = 0
 
     # -- fused exchange over peer memory ------------------------------------------------------------
 
@@ -187,39 +193,47 @@ class ExpertParallel:
         out_handle = symm_mem.rendezvous(out, group)
         self._symmetric = (recv, out, [int(p) for p in recv_handle.buffer_ptrs], [int(p) for p in out_handle.buffer_ptrs],
                            capacity, hidden, x.dtype)
-        self._handles = (recv_handle, out_handle)  # keep the mappings alive
-        self._flag = torch.zeros(1, dtype=torch.int32, device=x.device)
+        meta = symm_mem.empty(self.ops.moe_ep_meta_bytes() // 4, dtype=torch.int32, device=x.device)
+        meta.zero_()
+        meta_handle = symm_mem.rendezvous(meta, group)
+        self._meta, self._meta_ptrs = meta, [int(p) for p in meta_handle.buffer_ptrs]
+        self._handles = (recv_handle, out_handle, meta_handle)  # keep the mappings alive
+        self._status = torch.zeros(2, dtype=torch.int32, device=x.device)
+        torch.cuda.synchronize(x.device)
+        dist.barrier(group=self.group)  # every rank's flags are zero before anybody's first step
         return self._symmetric
 
-    def _order_ranks(self) -> None:
-        """Stream-ordered rendezvous: returns (on the stream) once every rank's earlier work has completed."""
-        dist.all_reduce(self._flag, group=self.group)
+    def check(self) -> None:
+        """Raise if a kernel of the fused exchange gave up waiting for a peer or found a receive over the buffers'
+        capacity since the last check (synchronises; call it where a step's result is consumed, not inside the step)."""
+        if self._status is None:
+            return
+        code, detail = self._status.tolist()
+        if code:
+            self._status.zero_()
+            reason = {1: f"the count exchange timed out waiting for rank {detail}", 2: f"a rendezvous timed out waiting for rank {detail}",
+                      3: f"a rank would receive {detail} rows, over the exchange capacity of {self._symmetric[4]}"}.get(code, f"code {code}")
+            raise RuntimeError(f"expert-parallel exchange failed on rank {self.rank}: {reason}")
 
     def _dispatch_p2p(self, x: Tensor, router_logits: Tensor) -> Dispatched:
         ops = self.ops
         recv, out, recv_ptrs, _, capacity, _, _ = self._buffers(x)
         indices, weights = ops.moe_route(router_logits, self.top_k)
         counts, offsets, _, pos = ops.moe_index(indices, self.experts)
-        gathered = torch.empty(self.world * self.experts, dtype=torch.int32, device=counts.device)
-        # also orders the ranks: nobody overwrites a buffer that a peer is still reading from the last step
-        dist.all_gather_into_tensor(gathered, counts.contiguous(), group=self.group)
-        counts_all = gathered.view(self.world, self.experts).cpu()
-        dst_base, rows_per_rank, expert_offsets = p2p_plan(counts_all, self.rank)
-        if max(rows_per_rank) > capacity:
-            raise RuntimeError(f"a rank would receive {max(rows_per_rank)} rows, over the exchange capacity of {capacity}")
-        dst_rank, dst_row = ops.moe_ep_destinations(indices, pos, offsets, dst_base.to(x.device, non_blocking=True), self.local_experts)
+        self._epoch += 1
+        # counts to every rank, everybody's counts back, the plan: one kernel, nothing leaves the device.  Waiting for
+        # every rank's counts also orders the ranks: a rank writes them after its previous step's last read of `out`.
+        dst_base, expert_offsets, info = ops.moe_ep_exchange(counts, self._meta_ptrs, self.rank, capacity, self._epoch, self._status)
+        dst_rank, dst_row = ops.moe_ep_destinations(indices, pos, offsets, dst_base, self.local_experts)
         ops.moe_permute_multi(x, dst_rank, dst_row, recv_ptrs)  # rows go straight into their owners' memory
-        self._order_ranks()  # every rank's stores have landed
-        received = rows_per_rank[self.rank]
-        send_counts = counts_all[self.rank].view(self.world, self.local_experts).sum(1).tolist()
-        return Dispatched(recv[:received], expert_offsets, weights, pos, send_counts, [], None, counts_all,
-                          dst_rank, dst_row, out[:received])
+        ops.moe_ep_barrier(self._meta_ptrs, self.rank, 1, self._epoch, self._status)  # every rank's stores have landed
+        return Dispatched(recv, expert_offsets, weights, pos, [], [], None, None, dst_rank, dst_row, out, info)
 
     def _combine_p2p(self, expert_rows: Tensor, state: Dispatched) -> Tensor:
         _, out, _, out_ptrs, _, hidden, dtype = self._symmetric
         if expert_rows.data_ptr() != out.data_ptr():
             out[: expert_rows.shape[0]].copy_(expert_rows)  # results computed elsewhere: stage them for the peers
-        self._order_ranks()  # every rank's expert outputs are complete
+        self.ops.moe_ep_barrier(self._meta_ptrs, self.rank, 2, self._epoch, self._status)  # every rank's expert outputs are complete
         return self.ops.moe_unpermute_multi(out_ptrs, state.dst_rank, state.dst_row, state.weights, hidden, dtype)
 
     def dispatch(self, x: Tensor, router_logits: Tensor, routing: tuple[Tensor, Tensor] | None = None) -> Dispatched:
@@ -296,8 +310,9 @@ class ExpertParallel:
             return self._momoe_with_grad(x, router_logits, gate_weight, up_weight, down_weight)
         state = self.dispatch(x, router_logits)
         offsets = state.expert_offsets.to(x.device, non_blocking=True)
-        hidden_act = self.ops.moe_grouped_gemm(state.rows, gate_weight, offsets, up_weight)
-        expert_rows = self.ops.moe_grouped_gemm(hidden_act, down_weight, offsets, None, state.out_rows)
+        # only the rows inside the segments are ever read again (by the down projection, then by the combine)
+        hidden_act = self.ops.moe_grouped_gemm(state.rows, gate_weight, offsets, up_weight, zero_fill=False)
+        expert_rows = self.ops.moe_grouped_gemm(hidden_act, down_weight, offsets, None, state.out_rows, zero_fill=False)
         return self.combine(expert_rows, state)
 
     def _momoe_with_grad(self, x: Tensor, router_logits: Tensor, gate_weight: Tensor, up_weight: Tensor, down_weight: Tensor) -> Tensor:

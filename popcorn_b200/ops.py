@@ -673,14 +673,16 @@ def moe_unpermute_backward(grad_y: Tensor, rows: Tensor, weights: Tensor, pos: T
     return grad_rows, grad_weights
 
 
-def moe_grouped_gemm(rows: Tensor, weight: Tensor, offsets: Tensor, up_weight: Tensor | None = None, out: Tensor | None = None) -> Tensor:
+def moe_grouped_gemm(rows: Tensor, weight: Tensor, offsets: Tensor, up_weight: Tensor | None = None, out: Tensor | None = None,
+                     zero_fill: bool = True) -> Tensor:
     """Expert MLP projection over the expert-major rows of `moe_permute` (momoe.py:50-52, momoe_tl.py:90-330).
 
     out[p] = rows[p] @ weight[e(p)], or silu(rows[p] @ weight[e(p)]) * (rows[p] @ up_weight[e(p)]) when `up_weight`
     is given (`weight` is then the gate projection); e(p) is the expert whose segment [offsets[e], offsets[e+1])
     holds row p.  weight: [experts, in_features, out_features] as in the reference; fp32 accumulation on the tensor
     cores, one rounding to the dtype of rows.  Rows outside every segment are zero, or left as they are when the
-    caller supplies `out` ([n, out_features], contiguous rows)."""
+    caller supplies `out` ([n, out_features], contiguous rows) or passes zero_fill=False (callers whose segments
+    cover every row, or that never read the rows outside them, save a full write pass over the output)."""
     device = _require_cuda(rows, weight, offsets, *([up_weight] if up_weight is not None else []))
     _forbid_grad(rows, weight)
     code = _dtype_code(rows, "moe_grouped_gemm")
@@ -696,7 +698,8 @@ def moe_grouped_gemm(rows: Tensor, weight: Tensor, offsets: Tensor, up_weight: T
     r2, ldr = _rows(rows)
     total = r2.shape[0]
     if out is None:
-        out = torch.zeros((total, n), dtype=rows.dtype, device=device) if total else torch.empty((0, n), dtype=rows.dtype, device=device)
+        make = torch.zeros if zero_fill and total else torch.empty
+        out = make((total, n), dtype=rows.dtype, device=device)
     elif out.shape != (total, n) or out.dtype != rows.dtype or out.device != device or (total and n > 1 and out.stride(1) != 1):
         raise ValueError("moe_grouped_gemm: out must be [n, out_features] in the dtype and on the device of rows")
     ldo = out.stride(0) if total > 1 else max(n, 1)
@@ -817,8 +820,9 @@ def momoe(x: Tensor, gate_weight: Tensor, up_weight: Tensor, down_weight: Tensor
     flat = x.reshape(-1, hidden)
     indices, weights = moe_route(router_logits.reshape(-1, experts).float(), int(top_k))
     rows, _, offsets, _, pos = moe_permute(flat, indices, experts)
-    hidden_act = moe_grouped_gemm(rows, gate_weight, offsets, up_weight)
-    out_rows = moe_grouped_gemm(hidden_act, down_weight, offsets)
+    # the offsets of moe_permute cover every row, so no row of either output needs a zero fill
+    hidden_act = moe_grouped_gemm(rows, gate_weight, offsets, up_weight, zero_fill=False)
+    out_rows = moe_grouped_gemm(hidden_act, down_weight, offsets, zero_fill=False)
     return moe_unpermute(out_rows, weights, pos).reshape(x.shape)
 
 
@@ -846,6 +850,45 @@ def moe_ep_destinations(
             _ptr(dst_base.contiguous()), tokens, top_k, experts, int(experts_per_rank), _ptr(dst_rank), _ptr(dst_row), _stream(device),
         )
     return dst_rank, dst_row
+
+
+EP_WAIT_BUDGET_NS = 2_000_000_000  # how long a rank waits for its peers inside a kernel before it gives up
+
+
+def moe_ep_meta_bytes() -> int:
+    """Size of the per-rank flag-and-counts buffer of the expert-parallel exchange (to be zeroed and mapped by all ranks)."""
+    need = ctypes.c_size_t(0)
+    _lib.call("b200_moe_ep_meta_bytes", ctypes.byref(need))
+    return int(need.value)
+
+
+def moe_ep_exchange(counts: Tensor, meta_ptrs: list[int], rank: int, capacity_rows: int, epoch: int, status: Tensor,
+                    budget_ns: int = EP_WAIT_BUDGET_NS) -> tuple[Tensor, Tensor, Tensor]:
+    """Exchange the per-expert counts with every rank through peer memory and derive this rank's addressing on the device.
+
+    counts: int32 [experts] of this rank (moe_index); meta_ptrs: every rank's meta buffer as mapped here; status: int32 [2]
+    device tensor that collects the first failure (see the header).  Returns (dst_base int32 [experts], expert_offsets
+    int32 [experts / world + 1], info int32 [4] = rows received, rows sent to other ranks, largest receive, world), all
+    on the device: nothing is read back."""
+    device = _require_cuda(counts, status)
+    if counts.dtype != torch.int32 or counts.dim() != 1 or status.dtype != torch.int32 or status.numel() < 2:
+        raise TypeError("moe_ep_exchange: counts must be int32 [experts] and status int32 [2]")
+    world, experts = len(meta_ptrs), counts.shape[0]
+    dst_base = torch.empty(experts, dtype=torch.int32, device=device)
+    expert_offsets = torch.empty(experts // max(world, 1) + 1, dtype=torch.int32, device=device)
+    info = torch.empty(4, dtype=torch.int32, device=device)
+    with torch.cuda.device(device):
+        _lib.call("b200_moe_ep_exchange", _ptr(counts.contiguous()), _pointer_array(meta_ptrs), world, int(rank), experts, int(capacity_rows),
+                  ctypes.c_int32(int(epoch) & 0xffffffff), int(budget_ns), _ptr(dst_base), _ptr(expert_offsets), _ptr(info), _ptr(status), _stream(device))
+    return dst_base, expert_offsets, info
+
+
+def moe_ep_barrier(meta_ptrs: list[int], rank: int, channel: int, epoch: int, status: Tensor, budget_ns: int = EP_WAIT_BUDGET_NS) -> None:
+    """Stream-ordered rendezvous of all ranks through flags in peer memory (bounded wait; failures go to `status`)."""
+    device = _require_cuda(status)
+    with torch.cuda.device(device):
+        _lib.call("b200_moe_ep_barrier", _pointer_array(meta_ptrs), len(meta_ptrs), int(rank), int(channel), ctypes.c_int32(int(epoch) & 0xffffffff),
+                  int(budget_ns), _ptr(status), _stream(device))
 
 
 def moe_permute_multi(x: Tensor, dst_buf: Tensor, dst_row: Tensor, buffer_ptrs: list[int], ld_rows: int | None = None) -> None:

@@ -37,10 +37,12 @@ def _worker(rank, world, port, tokens, hidden, experts, top_k, exchange, out):
         ep = ExpertParallel(experts, top_k, exchange=exchange)
         for _ in range(2):  # the second step reuses the exchange buffers
             state = ep.dispatch(x[lo:hi].to(device), logits[lo:hi].to(device))
-            rows = state.rows.clone()
+            # exchange="p2p" hands out its whole receive buffer; expert_offsets[-1] rows of it are in use
+            rows = state.rows[: int(state.expert_offsets[-1])].clone()
             processed = (state.rows.float() * 1.5).to(torch.bfloat16)
             y = ep.combine(processed, state)
         torch.cuda.synchronize(device)
+        ep.check()
         out[rank] = (rows.cpu(), state.expert_offsets.cpu(), y.cpu())
     finally:
         dist.destroy_process_group()
