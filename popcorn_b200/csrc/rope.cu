@@ -111,13 +111,17 @@ __device__ __forceinline__ void rotate(float x1, float x2, float c, float s, flo
 // once.  The CTA's cos/sin rows (groups * TS positions, contiguous in the table)
 // are staged in shared memory by two bulk asynchronous copies while the first
 // loads of x are already in flight.
-constexpr int kRopeTS = 4;
+// TS positions per thread: four for the NeoX form (two words per position = eight 128-bit loads in flight per thread),
+// eight for the interleaved form, whose unit is a single word (with four it kept only 64 bytes per thread in flight
+// and ran at 0.85 of the copy peak).
+template <bool INTERLEAVED>
+constexpr int rope_ts() { return INTERLEAVED ? 8 : 4; }
 
 template <typename T, typename CS, bool INTERLEAVED>
 __global__ void __launch_bounds__(512, 2) rope_tile_kernel(const RopeArgs p, int tpp, int groups) {
   constexpr int V = Num<T>::kVec;
   constexpr int NCS = INTERLEAVED ? V / 2 : V;  // cos values per unit
-  constexpr int TS = kRopeTS;
+  constexpr int TS = rope_ts<INTERLEAVED>();
   extern __shared__ __align__(16) unsigned char rope_smem[];
   __shared__ __align__(8) uint64_t bar;
 
@@ -355,7 +359,7 @@ int run(RopeArgs& p, cudaStream_t st) {
     int tpp = static_cast<int>(upp < 512 ? (upp + 31) / 32 * 32 : 512);
     int groups = 256 / tpp > 0 ? 256 / tpp : 1;
     const int threads = tpp * groups;
-    const int tile_positions = groups * kRopeTS;
+    const int tile_positions = groups * rope_ts<INTERLEAVED>();
     const int64_t tiles = ceil_div(p.seq, tile_positions);
     // one CTA per (tile, batch entry) unless that is far more CTAs than the machine needs
     const int64_t want = static_cast<int64_t>(sm_count()) * 64;
