@@ -567,8 +567,9 @@ def bench_grouped_gemm(device, sampler, scale: float = 1.0, steps: int = 10, war
     experts, top_k = w.args["experts"], w.args["top_k"]
     hidden = x.shape[1]
     idx, _ = ops.moe_route(logits, top_k)
-    rows, _, offsets, _, _ = ops.moe_permute(x, idx, experts)
-    del x, logits, idx
+    rows, _, offsets, perm, _ = ops.moe_permute(x, idx, experts)
+    tokens_x = x  # the token-order rows, for the projection that gathers them through `perm`
+    del logits, idx
     gen = torch.Generator(device=device).manual_seed(5)
     gate = (torch.randn(experts, hidden, inter, device=device, generator=gen) / hidden ** 0.5).to(torch.bfloat16)
     up = (torch.randn(experts, hidden, inter, device=device, generator=gen) / hidden ** 0.5).to(torch.bfloat16)
@@ -586,6 +587,10 @@ def bench_grouped_gemm(device, sampler, scale: float = 1.0, steps: int = 10, war
 
     def gate_up(i):
         check(lib.b200_moe_grouped_gemm(p(rows), p(gate), p(up), p(offsets), p(act), total, hidden, inter, experts, hidden, inter, _lib.BF16, stream))
+
+    def gate_up_gathered(i):
+        check(lib.b200_moe_grouped_gemm_gathered(p(tokens_x), p(perm), p(gate), p(up), p(offsets), p(act), tokens_x.shape[0], total, hidden, inter,
+                                                 experts, hidden, inter, _lib.BF16, stream))
 
     def down_proj(i):
         check(lib.b200_moe_grouped_gemm(p(act), p(down), ctypes.c_void_p(0), p(offsets), p(out), total, inter, hidden, experts, inter, hidden, _lib.BF16, stream))
@@ -617,7 +622,9 @@ def bench_grouped_gemm(device, sampler, scale: float = 1.0, steps: int = 10, war
 
     burst, sustained, kind = measured_tensor_peak()
     result = {"rows": total, "hidden": hidden, "intermediate": inter, "experts": experts, "peak_kind": kind}
-    for name, fn, flop in (("gate_up_swiglu", gate_up, 2.0 * total * hidden * 2 * inter), ("down", down_proj, 2.0 * total * inter * hidden),
+    for name, fn, flop in (("gate_up_swiglu", gate_up, 2.0 * total * hidden * 2 * inter),
+                           ("gate_up_swiglu_rows_gathered_in_the_operand_load", gate_up_gathered, 2.0 * total * hidden * 2 * inter),
+                           ("down", down_proj, 2.0 * total * inter * hidden),
                            ("gate_up_kept", gate_up_kept, 2.0 * total * hidden * 2 * inter), ("down_dgrad", down_dgrad, 2.0 * total * inter * hidden),
                            ("down_wgrad", down_wgrad, 2.0 * total * inter * hidden), ("gate_up_dgrad", gate_up_dgrad, 2.0 * total * hidden * 2 * inter),
                            ("gate_wgrad", gate_wgrad, 2.0 * total * hidden * inter)):
@@ -642,7 +649,7 @@ def bench_grouped_gemm(device, sampler, scale: float = 1.0, steps: int = 10, war
             result[name] = {"ms": round(ms, 4), "tflop_s": round(flop / (ms * 1e-3) / 1e12, 1)}
     # the whole layer through the registered op: inference (route, permute, two launches, unpermute) and a training
     # step (forward with the pre-activations kept, then every gradient: tokens, router logits, three weight tensors)
-    del both, grad_act, grad_rows, grad_down, grad_gate, act, out, rows
+    del both, grad_act, grad_rows, grad_down, grad_gate, act, out, rows, tokens_x, perm
     torch.cuda.empty_cache()
     from popcorn_b200 import autograd as differentiable
 

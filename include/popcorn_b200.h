@@ -477,6 +477,18 @@ int b200_moe_grouped_gemm(const void* rows, const void* weight, const void* weig
                           int dtype, void* stream);
 
 /*
+ * b200_moe_grouped_gemm with the row gather fused into the operand load, the way the reference's lin1_kernel
+ * addresses its A rows through idx_ptr_Msum (src/popcorn/impls/momoe_tl.py:156-158): row p of the A operand is
+ * x[perm[p], :], fetched straight from the token-order activations x [tokens, k] (row stride ldx) by four-row
+ * gathered bulk-tensor copies, so no expert-major copy of the rows (b200_moe_permute) has to exist.  perm: int32
+ * [total_rows], the `perm_token` output of b200_moe_index (every entry below offsets[experts] must be a valid token
+ * id); out: [total_rows, n] expert-major as for b200_moe_grouped_gemm, bit-identical to it on permuted rows.
+ */
+int b200_moe_grouped_gemm_gathered(const void* x, const int32_t* perm, const void* weight, const void* weight2, const int32_t* offsets,
+                                   void* out, int64_t tokens, int64_t total_rows, int64_t k, int64_t n, int64_t experts, int64_t ldx,
+                                   int64_t ld_out, int dtype, void* stream);
+
+/*
  * Both projections of the expert MLP's first step without the activation, for training calls that keep the
  * pre-activations: out[p, 0:n] = rows[p, :] @ gate_weight[e(p)], out[p, n:2n] = rows[p, :] @ up_weight[e(p)].
  * One pass over rows like the fused form of b200_moe_grouped_gemm; out: [total_rows, 2n] with row stride

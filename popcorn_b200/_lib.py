@@ -64,6 +64,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "b200_moe_unpermute": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _int, _ptr]),
     "b200_moe_unpermute_backward": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _i64, _int, _ptr]),
     "b200_moe_grouped_gemm": (_int, [_ptr] * 5 + [_i64] * 6 + [_int, _ptr]),
+    "b200_moe_grouped_gemm_gathered": (_int, [_ptr] * 6 + [_i64] * 7 + [_int, _ptr]),
     "b200_moe_grouped_gemm_gate_up": (_int, [_ptr] * 5 + [_i64] * 6 + [_int, _ptr]),
     "b200_moe_grouped_gemm_dgrad": (_int, [_ptr] * 6 + [_i64] * 6 + [_int, _ptr]),
     "b200_moe_grouped_gemm_wgrad": (_int, [_ptr] * 4 + [_i64] * 6 + [_int, _ptr]),

@@ -108,6 +108,17 @@ __device__ __forceinline__ void tma_2d(uint32_t dst, uint64_t map, int x, int y,
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
+// Four rows of a 2-D tensor, given by four row coordinates, x columns on: 4 x (box width) elements land as four
+// consecutive rows of the swizzled tile at `dst` (sm_100 tile::gather4).  The map's box is (box width, 1).
+template <bool PAIR>
+__device__ __forceinline__ void tma_gather4(uint32_t dst, uint64_t map, int x, int r0, int r1, int r2, int r3, uint32_t bar) {
+  if constexpr (PAIR)
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes.cta_group::2 [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar) : "memory");
+  else
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar) : "memory");
+}
 template <bool PAIR>
 __device__ __forceinline__ void tma_3d(uint32_t dst, uint64_t map, int x, int y, int z, uint32_t bar) {
   if constexpr (PAIR)
@@ -239,6 +250,9 @@ struct GemmArgs {
   int sources;     // kDgrad: 1 or 2 (A, B) operand pairs summed into one result
   int total_rows;  // rows of the token-major operands: nothing is read or stored past them, whatever `offsets` says
   uint32_t idesc;
+  // forward modes only: when set, row p of the A operand is row gather[p] of the tensor map_a describes (the token
+  // rows, in token order), fetched four rows per copy, and no expert-major copy of the rows has to exist
+  const int32_t* gather;
 };
 
 struct Tile {
@@ -359,7 +373,75 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     else return fixed_slots;
   };
 
-  if (warp == 0) {
+  bool gathering = false;
+  if constexpr (!WGRAD && !B_K_MAJOR) gathering = p.gather != nullptr;
+  if (warp == 0 && gathering) {
+    // ------------------------------------------- producer, A rows gathered --
+    // What the reference's lin1_kernel does with idx_ptr_Msum (src/popcorn/impls/momoe_tl.py:156-158): the tile's rows
+    // are addressed through the permutation.  Lane l owns rows 4 l .. 4 l + 3 of this CTA's 128: it reads their token
+    // ids once per tile and issues one four-row copy per 64-wide K span, so a whole span is ONE warp instruction;
+    // lane 0 claims the ring slots and issues the weight copies as in the plain producer.  Measured: the copy engine
+    // completes about one four-row copy per 45 cycles per SM, a third of what this tile shape consumes (gate/up +
+    // SwiGLU on 524288 x 4096 x 1536: 26.6 ms against 9.5 ms from materialised rows), so the layer keeps its permute
+    // pass and this path serves callers that cannot afford the expert-major copy of the rows.
+    if constexpr (!WGRAD && !B_K_MAJOR) {
+      uint32_t stage = 0, phase = 0, issued = 0;
+      const uint32_t signal_addr = PAIR ? map_to_rank(full_addr, 0) : full_addr;
+      const uint64_t a_map = reinterpret_cast<uint64_t>(&map_a);
+      const uint64_t b_map = reinterpret_cast<uint64_t>(&map_b), b2_map = reinterpret_cast<uint64_t>(&map_b2);
+      const int last_row = seg[p.experts] - 1;  // rows past a tile's segment still need a valid token id (results unused)
+      bool stop = false;
+      for (int tile = first_tile; tile < total_tiles && !stop; tile += tile_step) {
+        const Tile t = tile_at(tile);
+        const int row0 = t.row0 + static_cast<int>(rank) * kBM;
+        int token[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) token[q] = __ldg(p.gather + min(row0 + 4 * lane + q, last_row));
+        const uint64_t bm = (DUAL && PAIR && rank == 1) ? b2_map : b_map;
+        const int col0 = t.n0 + ((!DUAL && PAIR) ? static_cast<int>(rank) * (kBN / 2) : 0);
+        for (int k0 = 0; k0 < p.k; k0 += R::kSlotK) {
+          uint32_t a_dst = 0, bar = 0;
+          int ok = 1;
+          if (lane == 0) {
+            if (*abort_flag || !mbar_wait_addr(empty_addr + stage * 8, phase ^ 1u)) {
+              *abort_flag = 1;
+              ok = 0;
+            } else {
+              a_dst = ring_addr + stage * R::kStageBytes;
+              bar = signal_addr + stage * 8;
+              if (rank == 0) mbar_arrive_expect_addr(full_addr + stage * 8, CTAS * R::kStageBytes);
+              ++issued;
+              if (++stage == STAGES) {
+                stage = 0;
+                phase ^= 1u;
+              }
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) {
+            stop = true;
+            break;
+          }
+          a_dst = __shfl_sync(0xffffffffu, a_dst, 0);
+          bar = __shfl_sync(0xffffffffu, bar, 0);
+#pragma unroll
+          for (int j = 0; j < R::kSub; ++j)  // past K: zero fill
+            tma_gather4<PAIR>(a_dst + j * kASubBytes + lane * 512, a_map, k0 + j * kBK, token[0], token[1], token[2], token[3], bar);
+          if (lane == 0) {
+            const uint32_t b_dst = a_dst + R::kABytes;
+#pragma unroll
+            for (int c = 0; c < R::kChunks; ++c) {
+              if (DUAL && !PAIR && c >= R::kChunks / 2) tma_3d<PAIR>(b_dst + c * R::kBChunkBytes, b2_map, t.n0 + (c - R::kChunks / 2) * 64, k0, t.expert, bar);
+              else tma_3d<PAIR>(b_dst + c * R::kBChunkBytes, bm, col0 + c * 64, k0, t.expert, bar);
+            }
+          }
+        }
+      }
+      if (lane == 0 && *abort_flag && rank == 0) {
+        for (uint32_t k = issued > STAGES ? issued - STAGES : 0; k < issued; ++k) (void)mbar_wait(&full[k % STAGES], (k / STAGES) & 1u);
+      }
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------- producer --
     if (lane == 0) {
       uint32_t stage = 0, phase = 0, issued = 0;
@@ -645,6 +727,13 @@ bool encode_rows(CUtensorMap* map, CUtensorMapDataType type, const void* base, i
   return encode(map, type, 2, base, {width, total_rows, 1}, {ld, 0}, {kBK, kBM, 1});
 }
 
+// the same operand for four-row gathered copies (tile::gather4): the box is ONE row of 64 contraction values; the
+// instruction names four row coordinates and copies the box once per row.  (A box of four rows makes the copy an
+// illegal instruction.)
+bool encode_gathered_rows(CUtensorMap* map, CUtensorMapDataType type, const void* base, int64_t rows, int64_t width, int64_t ld) {
+  return encode(map, type, 2, base, {width, rows, 1}, {ld, 0}, {kBK, 1, 1});
+}
+
 // weight [experts, k, n], n contiguous, read along n: box 64 (n) x slot_k (k) x 1 (expert).
 bool encode_weight(CUtensorMap* map, CUtensorMapDataType type, const void* base, int64_t experts, int64_t k, int64_t n, int slot_k) {
   return encode(map, type, 3, base, {n, k, experts}, {n, n * k}, {64, slot_k, 1});
@@ -662,11 +751,21 @@ bool encode_window(CUtensorMap* map, CUtensorMapDataType type, const void* base,
   return encode(map, type, 3, base, {width, slot_k, total_rows}, {ld, ld}, {64, slot_k, 1});
 }
 
-// B200_GEMM_PAIR=0 in the environment runs every CTA on its own (cta_group::1); read at every call.
+// B200_GEMM_PAIR=0 in the environment runs every CTA on its own (cta_group::1); read at every call (a getenv is a
+// short scan of the environment block; tests flip the switch between calls).
 bool pair_enabled() {
   const char* v = std::getenv("B200_GEMM_PAIR");
   return !(v && v[0] == '0');
 }
+
+// Per (kernel instantiation, device): the dynamic shared-memory attribute has been raised, and how many CTAs a launch
+// gets (for pairs: twice the number of clusters that can be resident, or kNoClusters).  Both are properties of the
+// kernel and the device, so a call pays for them once instead of on every launch.
+constexpr int kMaxDevicesGemm = 64;
+struct LaunchPlan {
+  std::mutex mutex;
+  int ctas[kMaxDevicesGemm] = {};  // 0: not looked up yet
+};
 
 constexpr int kNoClusters = -1000;  // run_with<., ., 2>: no cluster of two CTAs can be resident; the caller runs single CTAs instead
 
@@ -677,6 +776,7 @@ struct Operands {
   int64_t k, n;                 // the WEIGHT's shape [experts, k, n], whichever way the mode contracts
   int64_t ld_a, ld_b;           // row strides of the token-major operands (ld_b: kWgrad only)
   CUtensorMapDataType type;
+  int64_t gather_rows = 0;      // forward modes: > 0 when `a` is the token-order tensor [gather_rows, k] read through an index
 };
 
 template <int MODE, int CTAS>
@@ -694,8 +794,11 @@ bool encode_operands(const Operands& op, CUtensorMap* a, CUtensorMap* b, CUtenso
            encode_weight_rows(b, op.type, op.b, op.experts, op.k, op.n, kBN / CTAS) &&
            encode_weight_rows(b2, op.type, second_b, op.experts, op.k, op.n, kBN / CTAS);
   } else {
-    return encode_rows(a, op.type, op.a, op.total_rows, op.k, op.ld_a) && encode_rows(a2, op.type, op.a, op.total_rows, op.k, op.ld_a) &&
-           encode_weight(b, op.type, op.b, op.experts, op.k, op.n, slot_k) && encode_weight(b2, op.type, second_b, op.experts, op.k, op.n, slot_k);
+    const bool rows_ok = op.gather_rows > 0
+                             ? encode_gathered_rows(a, op.type, op.a, op.gather_rows, op.k, op.ld_a) &&
+                                   encode_gathered_rows(a2, op.type, op.a, op.gather_rows, op.k, op.ld_a)
+                             : encode_rows(a, op.type, op.a, op.total_rows, op.k, op.ld_a) && encode_rows(a2, op.type, op.a, op.total_rows, op.k, op.ld_a);
+    return rows_ok && encode_weight(b, op.type, op.b, op.experts, op.k, op.n, slot_k) && encode_weight(b2, op.type, second_b, op.experts, op.k, op.n, slot_k);
   }
 }
 
@@ -705,9 +808,11 @@ int run_with(const char* what, const Operands& op, GemmArgs args, uint32_t forma
   if (!encode_operands<MODE, CTAS>(op, &a, &b, &a2, &b2)) return fail(B200_ERR_LAUNCH, "%s: tensor map encoding failed", what);
   auto kernel = grouped_gemm_kernel<T, MODE, CTAS>;
   constexpr int smem = Ring<CTAS>::kSmemBytes;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+  static LaunchPlan plan;  // one per instantiation
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevicesGemm) {
     (void)cudaGetLastError();
-    return fail(B200_ERR_LAUNCH, "%s: cannot reserve %d bytes of shared memory", what, smem);
+    return fail(B200_ERR_DEVICE, "%s: no usable CUDA device is current", what);
   }
   args.idesc = instr_desc(format, CTAS, MODE == kWgrad, MODE != kDgrad);
   cudaLaunchConfig_t config = {};
@@ -725,17 +830,31 @@ int run_with(const char* what, const Operands& op, GemmArgs args, uint32_t forma
   }
   config.attrs = attrs;
   config.numAttrs = n_attrs;
-  int ctas = sm_count();
-  if (CTAS == 2) {
-    // persistent pairs: as many clusters as can be resident at once (an odd SM of a processing cluster has no partner)
-    config.gridDim = dim3(static_cast<unsigned>(ctas & ~1));
-    int clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess || clusters < 1) {
-      (void)cudaGetLastError();
-      return kNoClusters;
+  int ctas = 0;
+  {
+    std::lock_guard<std::mutex> lock(plan.mutex);
+    if (plan.ctas[device] == 0) {
+      if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return fail(B200_ERR_LAUNCH, "%s: cannot reserve %d bytes of shared memory", what, smem);
+      }
+      int found = sm_count();
+      if (CTAS == 2) {
+        // persistent pairs: as many clusters as can be resident at once (an odd SM of a processing cluster has no partner)
+        config.gridDim = dim3(static_cast<unsigned>(found & ~1));
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess || clusters < 1) {
+          (void)cudaGetLastError();
+          found = kNoClusters;
+        } else {
+          found = 2 * std::min(clusters, found / 2);
+        }
+      }
+      plan.ctas[device] = found;
     }
-    ctas = 2 * std::min(clusters, ctas / 2);
+    ctas = plan.ctas[device];
   }
+  if (ctas == kNoClusters) return kNoClusters;
   config.gridDim = dim3(static_cast<unsigned>(ctas));
   if (pdl_enabled()) {
     attrs[n_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -792,7 +911,8 @@ namespace {
 
 // The three forward forms: out = rows @ weight, the fused SwiGLU of two projections, or both projections side by side.
 int forward(const char* what, int mode, const void* rows, const void* weight, const void* weight2, const int32_t* offsets, void* out,
-            int64_t total_rows, int64_t k, int64_t n, int64_t experts, int64_t ld_rows, int64_t ld_out, int dtype, void* stream) {
+            int64_t total_rows, int64_t k, int64_t n, int64_t experts, int64_t ld_rows, int64_t ld_out, int dtype, void* stream,
+            const int32_t* gather = nullptr, int64_t gather_rows = 0) {
   if (int rc = check_common(what, dtype, total_rows, k, n, experts, {ld_rows, ld_out}, {k, mode == kGateUp ? 2 * n : n},
                             {rows, weight, weight2, out, nullptr, nullptr}, offsets))
     return rc;
@@ -801,7 +921,8 @@ int forward(const char* what, int mode, const void* rows, const void* weight, co
   if (k == 0) return fail(B200_ERR_SHAPE, "%s: k must be positive", what);
   if (int rc = check_device()) return rc;
   if (encoder() == nullptr) return fail(B200_ERR_LAUNCH, "%s: the driver does not provide cuTensorMapEncodeTiled", what);
-  const Operands op{rows, weight, nullptr, weight2, total_rows, experts, k, n, ld_rows, 0, map_type(dtype)};
+  Operands op{rows, weight, nullptr, weight2, total_rows, experts, k, n, ld_rows, 0, map_type(dtype)};
+  op.gather_rows = gather ? gather_rows : 0;
   GemmArgs args{};
   args.offsets = offsets;
   args.out = out;
@@ -811,6 +932,7 @@ int forward(const char* what, int mode, const void* rows, const void* weight, co
   args.k = static_cast<int>(k);
   args.sources = 1;
   args.total_rows = static_cast<int>(total_rows);
+  args.gather = gather;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (mode == kSwiglu) return run_typed<kSwiglu>(what, dtype, op, args, st);
   if (mode == kGateUp) return run_typed<kGateUp>(what, dtype, op, args, st);
@@ -823,6 +945,19 @@ extern "C" int b200_moe_grouped_gemm(const void* rows, const void* weight, const
                                      int64_t total_rows, int64_t k, int64_t n, int64_t experts, int64_t ld_rows, int64_t ld_out,
                                      int dtype, void* stream) {
   return forward(__func__, weight2 ? kSwiglu : kPlain, rows, weight, weight2, offsets, out, total_rows, k, n, experts, ld_rows, ld_out, dtype, stream);
+}
+
+extern "C" int b200_moe_grouped_gemm_gathered(const void* x, const int32_t* perm, const void* weight, const void* weight2, const int32_t* offsets,
+                                              void* out, int64_t tokens, int64_t total_rows, int64_t k, int64_t n, int64_t experts, int64_t ldx,
+                                              int64_t ld_out, int dtype, void* stream) {
+  if (tokens < 0 || tokens > 0x7fffffffLL) return fail(B200_ERR_SHAPE, "%s: tokens out of range", __func__);
+  if (total_rows > 0 && n > 0 && experts > 0) {
+    if (!perm) return fail(B200_ERR_NULL_POINTER, "%s: perm is NULL", __func__);
+    if (!aligned(perm, 4)) return fail(B200_ERR_ALIGNMENT, "%s: perm must be 4-byte aligned", __func__);
+    if (tokens == 0) return fail(B200_ERR_SHAPE, "%s: rows to gather but no tokens", __func__);
+  }
+  return forward(__func__, weight2 ? kSwiglu : kPlain, x, weight, weight2, offsets, out, total_rows, k, n, experts, ldx, ld_out, dtype, stream,
+                 perm, tokens);
 }
 
 extern "C" int b200_moe_grouped_gemm_gate_up(const void* rows, const void* gate_weight, const void* up_weight, const int32_t* offsets, void* out,

@@ -179,9 +179,11 @@ __global__ void __launch_bounds__(512, 2) rope_tile_kernel(const RopeArgs p, int
 
   // Wait for the tables (every thread, at this one place).  If the bounded wait
   // runs out anywhere in the CTA, all threads fill the tables with ordinary loads.
+  bool tables_late = false;  // the same in every thread of the CTA
   {
     const bool ok = mbar_wait(&bar, 0);
-    if (__syncthreads_or(!ok)) {
+    tables_late = __syncthreads_or(!ok);
+    if (tables_late) {
       const int n = n_pos * p.half;
       for (int i = threadIdx.x; i < n; i += blockDim.x) {
         cos_s[i] = cos_g[i];
@@ -262,6 +264,13 @@ __global__ void __launch_bounds__(512, 2) rope_tile_kernel(const RopeArgs p, int
         }
       }
     }
+  }
+  if (tables_late) {
+    // the two bulk copies may still be in flight into this CTA's shared memory (they bring the same bytes the plain
+    // loads wrote): thread 0 gives them one more bounded wait and the CTA stays resident until it returns, so that
+    // a late copy cannot land in shared memory that already belongs to another CTA
+    if (threadIdx.x == 0) (void)mbar_wait(&bar, 0);
+    __syncthreads();
   }
 }
 

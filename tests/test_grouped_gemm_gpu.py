@@ -64,6 +64,29 @@ def test_gate_up_swiglu_projection(counts, k, n, dtype):
     assert _lib.wait_timeouts() == 0
 
 
+@pytest.mark.parametrize("pair", ["1", "0"])
+@pytest.mark.parametrize("counts,k,n,dtype", CASES)
+def test_gathered_operand_equals_the_permuted_rows(counts, k, n, dtype, pair, monkeypatch):
+    """The A rows fetched through the permutation by four-row gathered copies: bit-identical to the projection of the
+    materialised rows, alone and fused with SwiGLU, as CTA pairs and as single CTAs."""
+    monkeypatch.setenv("B200_GEMM_PAIR", pair)
+    rows, gate, up, offsets = make(counts, k, n, dtype, 5300 + k)
+    total = int(offsets[-1])
+    tokens = max(total // 2, 1) + 5
+    gen = torch.Generator().manual_seed(5301 + k)
+    x = randn(5302 + k, tokens, k, dtype=dtype)
+    perm = torch.randint(0, tokens, (total,), generator=gen, dtype=torch.int32)  # tokens repeat, like top_k > 1
+    gathered_rows = x[perm.long()]
+    for second in (None, up):
+        want = ops.moe_grouped_gemm(gpu(gathered_rows), gpu(gate), gpu(offsets), gpu(second))
+        got = ops.moe_grouped_gemm_gathered(gpu(x), gpu(perm), gpu(gate), gpu(offsets), gpu(second))
+        assert torch.equal(got, want), f"gathered {counts} k={k} n={n} dual={second is not None}"
+    wide = gpu(torch.cat((x, x), dim=1))  # token rows given as a column slice
+    got = ops.moe_grouped_gemm_gathered(wide[:, :k], gpu(perm), gpu(gate), gpu(offsets))
+    assert torch.equal(got, ops.moe_grouped_gemm(gpu(gathered_rows), gpu(gate), gpu(offsets)))
+    assert _lib.wait_timeouts() == 0
+
+
 def test_strided_rows_and_many_tiles_per_cta():
     """More tiles than SMs (persistent CTAs reuse both accumulators and wrap the ring) and rows given as a column slice."""
     counts = [257] * 40
