@@ -94,6 +94,7 @@ class ClockSampler:
     def __init__(self, index: int) -> None:
         self.proc = None
         self.windows: list[tuple[float, float]] = []
+        self.labelled: list[tuple[str, float, float]] = []
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
@@ -102,8 +103,11 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
-    def mark(self, start: float, end: float) -> None:
+    def mark(self, start: float, end: float, label: str | None = None) -> None:
+        """A timed window; a labelled one also gets its own median clock and power in `finish()["by_window"]`."""
         self.windows.append((start, end))
+        if label is not None:
+            self.labelled.append((label, start, end))
 
     def finish(self) -> dict:
         if self.proc is None:
@@ -117,6 +121,7 @@ class ClockSampler:
         import datetime
 
         clocks, max_clocks, power, reasons = [], [], [], set()
+        per_window: dict[str, list[tuple[float, float]]] = {label: [] for label, _, _ in self.labelled}
         for line in out.splitlines():
             parts = [p.strip() for p in line.split(",")]
             if len(parts) != 8:
@@ -126,6 +131,9 @@ class ClockSampler:
                 sm, sm_max, watts = float(parts[1]), float(parts[2]), float(parts[3])
             except ValueError:
                 continue
+            for label, lo, hi in self.labelled:
+                if lo <= stamp <= hi:
+                    per_window[label].append((sm, watts))
             if self.windows and not any(lo <= stamp <= hi for lo, hi in self.windows):
                 continue
             clocks.append(sm)
@@ -136,8 +144,12 @@ class ClockSampler:
                     reasons.add(name)
         if not clocks:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples inside the timed windows"]}
-        return {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max(max_clocks), "power_w_max": max(power),
-                "samples": len(clocks), "reasons": sorted(reasons)}
+        result = {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max(max_clocks), "power_w_max": max(power),
+                  "samples": len(clocks), "reasons": sorted(reasons)}
+        if per_window:
+            result["by_window"] = {label: {"sm_mhz": statistics.median(v[0] for v in found), "power_w": round(statistics.median(v[1] for v in found), 1),
+                                           "samples": len(found)} for label, found in per_window.items() if found}
+        return result
 
 
 # ------------------------------------------------------------- op runners --
@@ -636,6 +648,21 @@ def bench_grouped_gemm(device, sampler, scale: float = 1.0, steps: int = 10, war
         result[name] = {"ms": round(ms, 4), "tflop_s": round(tflops, 1), "flop": flop, "frac_of_measured_burst": round(tflops / burst, 4),
                         "frac_of_measured_sustained": round(tflops / sustained, 4)}
     result["wait_timeouts"] = _lib.wait_timeouts()
+    # The same flop count through this kernel and through cuBLAS, one second each, with the SM clock sampled inside each
+    # window: both run under the 1 kW power cap, where the clock each settles at is part of its speed.  time x clock
+    # = SM cycles per launch, the figure that compares the two kernels' use of the tensor pipe.
+    if sampler is not None and total % experts == 0:
+        per = total // experts
+        a3, gate_up_w = rows.view(experts, per, hidden), torch.cat((gate, up), dim=2)
+        study = {}
+        for name, fn in (("gate_up_swiglu", gate_up), ("cublas_bmm_gate_up", lambda i: torch.bmm(a3, gate_up_w))):
+            long_steps = max(steps, int(1.2e3 / max(result.get(name, {}).get("ms", 9.0), 1.0)))
+            t0 = time.time()
+            ms = time_launches(fn, long_steps, warmup, device)
+            sampler.mark(t0, time.time(), label=f"clock_study_{name}")
+            study[name] = {"ms": round(ms, 4), "steps": long_steps}
+        result["clock_study"] = study
+        del a3, gate_up_w
     # the library GEMM on the same box in the same run, same flop count: one batched cuBLAS matmul per projection over
     # equal-size experts (total / experts rows each), without the SwiGLU epilogue and writing both projections out
     if total % experts == 0:
@@ -1086,6 +1113,13 @@ def main() -> None:
 
     if rank == 0:
         clocks = sampler.finish()
+        study = per_op.get("moe_expert_mlp_bf16", {}).get("clock_study")
+        if study:
+            for name, entry in study.items():
+                seen = clocks.get("by_window", {}).get(f"clock_study_{name}")
+                if seen:
+                    entry.update(sm_mhz=seen["sm_mhz"], power_w=seen["power_w"], clock_samples=seen["samples"],
+                                 sm_mcycles_per_launch=round(entry["ms"] * seen["sm_mhz"] / 1e3, 2))
         cpu = None
         if world == 1 and not args.skip_per_op:
             cpu = cpu_headline_baseline()
