@@ -94,7 +94,6 @@ class ClockSampler:
     def __init__(self, index: int) -> None:
         self.proc = None
         self.windows: list[tuple[float, float]] = []
-        self.labelled: list[tuple[str, float, float]] = []
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
@@ -103,11 +102,8 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
-    def mark(self, start: float, end: float, label: str | None = None) -> None:
-        """A timed window; a labelled one also gets its own median clock and power in `finish()["by_window"]`."""
+    def mark(self, start: float, end: float) -> None:
         self.windows.append((start, end))
-        if label is not None:
-            self.labelled.append((label, start, end))
 
     def finish(self) -> dict:
         if self.proc is None:
@@ -121,7 +117,6 @@ class ClockSampler:
         import datetime
 
         clocks, max_clocks, power, reasons = [], [], [], set()
-        per_window: dict[str, list[tuple[float, float]]] = {label: [] for label, _, _ in self.labelled}
         for line in out.splitlines():
             parts = [p.strip() for p in line.split(",")]
             if len(parts) != 8:
@@ -131,9 +126,6 @@ class ClockSampler:
                 sm, sm_max, watts = float(parts[1]), float(parts[2]), float(parts[3])
             except ValueError:
                 continue
-            for label, lo, hi in self.labelled:
-                if lo <= stamp <= hi:
-                    per_window[label].append((sm, watts))
             if self.windows and not any(lo <= stamp <= hi for lo, hi in self.windows):
                 continue
             clocks.append(sm)
@@ -144,12 +136,8 @@ class ClockSampler:
                     reasons.add(name)
         if not clocks:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples inside the timed windows"]}
-        result = {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max(max_clocks), "power_w_max": max(power),
-                  "samples": len(clocks), "reasons": sorted(reasons)}
-        if per_window:
-            result["by_window"] = {label: {"sm_mhz": statistics.median(v[0] for v in found), "power_w": round(statistics.median(v[1] for v in found), 1),
-                                           "samples": len(found)} for label, found in per_window.items() if found}
-        return result
+        return {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max(max_clocks), "power_w_max": max(power),
+                "samples": len(clocks), "reasons": sorted(reasons)}
 
 
 # ------------------------------------------------------------- op runners --
@@ -228,6 +216,38 @@ def time_launches(run, steps: int, warmup: int, device) -> float:
     end.record()
     torch.cuda.synchronize(device)
     return start.elapsed_time(end) / steps
+
+
+def time_launches_with_clock(run, steps: int, warmup: int, device) -> dict:
+    """time_launches, with the SM clock and the board power read through NVML every few milliseconds while the GPU works
+    through the queued launches (reads only).  time x median clock = SM cycles per launch."""
+    for i in range(warmup):
+        run(i)
+    torch.cuda.synchronize(device)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(steps):
+        run(i)
+    end.record()
+    clocks, watts = [], []
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(device.index or 0)
+        while not end.query():
+            clocks.append(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            watts.append(pynvml.nvmlDeviceGetPowerUsage(handle) / 1000.0)
+            time.sleep(0.005)
+    except Exception:  # no NVML on this machine: the time alone
+        pass
+    torch.cuda.synchronize(device)
+    ms = start.elapsed_time(end) / steps
+    out = {"ms": round(ms, 4), "steps": steps}
+    if clocks:
+        mhz = statistics.median(clocks)
+        out.update(sm_mhz=mhz, power_w=round(statistics.median(watts), 1), clock_samples=len(clocks), sm_mcycles_per_launch=round(ms * mhz / 1e3, 2))
+    return out
 
 
 def steps_for(nbytes: int, target_s: float = 0.4, lo: int = 20, hi: int = 2000) -> int:
@@ -651,16 +671,15 @@ def bench_grouped_gemm(device, sampler, scale: float = 1.0, steps: int = 10, war
     # The same flop count through this kernel and through cuBLAS, one second each, with the SM clock sampled inside each
     # window: both run under the 1 kW power cap, where the clock each settles at is part of its speed.  time x clock
     # = SM cycles per launch, the figure that compares the two kernels' use of the tensor pipe.
-    if sampler is not None and total % experts == 0:
+    if total % experts == 0:
         per = total // experts
         a3, gate_up_w = rows.view(experts, per, hidden), torch.cat((gate, up), dim=2)
         study = {}
         for name, fn in (("gate_up_swiglu", gate_up), ("cublas_bmm_gate_up", lambda i: torch.bmm(a3, gate_up_w))):
-            long_steps = max(steps, int(1.2e3 / max(result.get(name, {}).get("ms", 9.0), 1.0)))
-            t0 = time.time()
-            ms = time_launches(fn, long_steps, warmup, device)
-            sampler.mark(t0, time.time(), label=f"clock_study_{name}")
-            study[name] = {"ms": round(ms, 4), "steps": long_steps}
+            study[name] = time_launches_with_clock(fn, 120, warmup, device)
+        if all("sm_mhz" in entry for entry in study.values()):
+            ours, theirs = study["gate_up_swiglu"], study["cublas_bmm_gate_up"]
+            study["sm_cycles_ratio_ours_over_cublas"] = round(ours["sm_mcycles_per_launch"] / theirs["sm_mcycles_per_launch"], 4)
         result["clock_study"] = study
         del a3, gate_up_w
     # the library GEMM on the same box in the same run, same flop count: one batched cuBLAS matmul per projection over
@@ -1113,13 +1132,6 @@ def main() -> None:
 
     if rank == 0:
         clocks = sampler.finish()
-        study = per_op.get("moe_expert_mlp_bf16", {}).get("clock_study")
-        if study:
-            for name, entry in study.items():
-                seen = clocks.get("by_window", {}).get(f"clock_study_{name}")
-                if seen:
-                    entry.update(sm_mhz=seen["sm_mhz"], power_w=seen["power_w"], clock_samples=seen["samples"],
-                                 sm_mcycles_per_launch=round(entry["ms"] * seen["sm_mhz"] / 1e3, 2))
         cpu = None
         if world == 1 and not args.skip_per_op:
             cpu = cpu_headline_baseline()

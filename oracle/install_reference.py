@@ -15,7 +15,7 @@ first-party SwiGLU CUDA source and Triton rotary / MoMoE kernels) depends on tho
 
 `prebuild_incumbents()` additionally compiles popcorn's first-party SwiGLU CUDA source the way popcorn itself does
 (torch.utils.cpp_extension.load through popcorn/impls/_cuda.py:17-23, `-O3`, no architecture flags of its own; the
-architecture list is the one torch detects on a B200: compute capability 10.0 plus its PTX) into `baseline/_ext/`, so that a
+architecture list is the environment's TORCH_CUDA_ARCH_LIST when it is set, as the benchmark run will see it too, else what torch detects on a B200: compute capability 10.0 plus its PTX) into `baseline/_ext/`, so that a
 benchmark run on a GPU machine does not spend a minute in nvcc.  ninja keys a build on the absolute paths of source and
 output, so both trees are reached through `stable_locations()`: two symlinks under the system temp directory whose
 names are the same on every machine.
@@ -109,7 +109,7 @@ def prebuild_incumbents(force: bool = False) -> Path:
     if built.is_file() and not force:
         return built
     package, extensions = stable_locations()
-    env = {**os.environ, "TORCH_EXTENSIONS_DIR": str(extensions), "TORCH_CUDA_ARCH_LIST": "10.0+PTX", "PYTHONPATH": str(package),
+    env = {**os.environ, "TORCH_EXTENSIONS_DIR": str(extensions), "TORCH_CUDA_ARCH_LIST": os.environ.get("TORCH_CUDA_ARCH_LIST") or "10.0+PTX", "PYTHONPATH": str(package),
            "POPCORN_CACHE_DIR": tempfile.mkdtemp(prefix="popcorn-cache-")}
     done = subprocess.run([sys.executable, "-W", "ignore", "-c", "from popcorn.impls import _cuda; print(_cuda.load('swiglu').__file__)"],
                           env=env, capture_output=True, text=True)
