@@ -109,10 +109,13 @@ def prebuild_incumbents(force: bool = False) -> Path:
     if built.is_file() and not force:
         return built
     package, extensions = stable_locations()
+    lock = EXTENSIONS / "popcorn_swiglu" / "lock"
+    if lock.is_file():  # left by an interrupted build: torch's loader would wait for it for ever
+        lock.unlink()
     env = {**os.environ, "TORCH_EXTENSIONS_DIR": str(extensions), "TORCH_CUDA_ARCH_LIST": os.environ.get("TORCH_CUDA_ARCH_LIST") or "10.0+PTX", "PYTHONPATH": str(package),
            "POPCORN_CACHE_DIR": tempfile.mkdtemp(prefix="popcorn-cache-")}
     done = subprocess.run([sys.executable, "-W", "ignore", "-c", "from popcorn.impls import _cuda; print(_cuda.load('swiglu').__file__)"],
-                          env=env, capture_output=True, text=True)
+                          env=env, capture_output=True, text=True, timeout=1200)
     if done.returncode != 0 or not built.is_file():
         raise RuntimeError(f"could not build popcorn's swiglu extension:\n{done.stdout}\n{done.stderr}")
     return built
