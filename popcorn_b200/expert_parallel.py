@@ -63,7 +63,9 @@ def check_counts(counts_all: Tensor, rank: int) -> None:
 
 
 def p2p_plan(counts_all: Tensor, rank: int) -> tuple[Tensor, list[int], Tensor]:
-    """Addressing for the fused exchange, from the gathered counts (host arithmetic).
+    """Addressing for the fused exchange, from the [world, experts] count table, as host arithmetic: the statement of
+    what `b200_moe_ep_exchange` computes on the device (the step itself no longer runs this; the tests hold the kernel
+    to it, and a host that already has the table can use it).
 
     Returns (dst_base int32 [experts], rows_per_rank, expert_offsets int32 [local_experts + 1]):
     dst_base[e] is the row in the buffer of e's owner at which THIS rank's rows for expert e start:
