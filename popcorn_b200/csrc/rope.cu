@@ -111,11 +111,11 @@ __device__ __forceinline__ void rotate(float x1, float x2, float c, float s, flo
 // once.  The CTA's cos/sin rows (groups * TS positions, contiguous in the table)
 // are staged in shared memory by two bulk asynchronous copies while the first
 // loads of x are already in flight.
-// TS positions per thread: four for the NeoX form (two words per position = eight 128-bit loads in flight per thread),
-// eight for the interleaved form, whose unit is a single word (with four it kept only 64 bytes per thread in flight
-// and ran at 0.85 of the copy peak).
+// TS positions per thread.  Eight for the interleaved form (whose unit is one word, so four positions keep only 64
+// bytes per thread in flight) was measured again and again at 0.83-0.85 of the copy peak, like four: no gain, a few
+// spilled registers; both forms use four.
 template <bool INTERLEAVED>
-constexpr int rope_ts() { return INTERLEAVED ? 8 : 4; }
+constexpr int rope_ts() { return 4; }
 
 template <typename T, typename CS, bool INTERLEAVED>
 __global__ void __launch_bounds__(512, 2) rope_tile_kernel(const RopeArgs p, int tpp, int groups) {
