@@ -367,11 +367,32 @@ int b200_moe_index_scratch_bytes(int64_t tokens, int64_t top_k, int64_t experts,
  * with an out-of-range expert is left out of counts, perm_token and pos.  Limits:
  * experts <= 1024, tokens*top_k < 2^31.  `scratch` needs
  * b200_moe_index_scratch_bytes() bytes, 16-byte aligned; its contents are
- * overwritten.
+ * overwritten, it need not be cleared, and two calls that may run at the same
+ * time (different streams) must not share it.
+ *
+ * Up to 256 experts this is ONE cooperative kernel launch (one CTA per SM; the
+ * CTAs meet once, through flags in `scratch`, with a wait bounded at two
+ * seconds: if it ever ran out, offsets[experts] would read -1); above that, or
+ * with B200_INDEX_CHAIN=1 in the environment, three dependent launches
+ * (histogram, scan, scatter).  The results are the same either way.
  */
 int b200_moe_index(const int32_t* indices, int64_t tokens, int64_t top_k, int64_t experts,
                    int32_t* counts, int32_t* offsets, int32_t* perm_token, int32_t* pos,
                    void* scratch, size_t scratch_bytes, void* stream);
+
+/*
+ * b200_moe_route followed by b200_moe_index on its indices as one call: same
+ * arguments, same results, same scratch as b200_moe_index.  Every momoe forward
+ * runs the two back to back (momoe.py:47-49, then find_used_experts,
+ * momoe_tl.py:1071-1161).  Two kernel launches up to 256 experts.  (Routing inside
+ * the index kernel was built and measured: 33-35 us for 65536 tokens x top-8 over
+ * 64 experts against 15 + 12 us for the two launches, because the routing is
+ * bound by the integer pipe and loses occupancy inside the cooperative kernel.)
+ */
+int b200_moe_route_index(const void* logits, int32_t* indices, float* weights,
+                         int64_t tokens, int64_t experts, int64_t top_k, int64_t ld_logits, int logits_dtype,
+                         int32_t* counts, int32_t* offsets, int32_t* perm_token, int32_t* pos,
+                         void* scratch, size_t scratch_bytes, void* stream);
 
 /*
  * b200_moe_index for callers that cannot hand over a workspace.  (This entry point

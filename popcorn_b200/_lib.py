@@ -57,6 +57,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "b200_moe_route": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _int, _ptr]),
     "b200_moe_index_scratch_bytes": (_int, [_i64, _i64, _i64, ctypes.POINTER(_size)]),
     "b200_moe_index": (_int, [_ptr, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _size, _ptr]),
+    "b200_moe_route_index": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _int, _ptr, _ptr, _ptr, _ptr, _ptr, _size, _ptr]),
     "b200_moe_index_static": (_int, [_ptr, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _ptr]),
     "b200_moe_index_static_max_bytes": (_int, [ctypes.POINTER(_size)]),
     "b200_moe_permute": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _int, _ptr]),

@@ -9,6 +9,7 @@
 // Bound: HBM for permute / gather / unpermute (pure row traffic, 128-bit
 // accesses, a warp moves 512 contiguous bytes per step); route and index move
 // only a few MB and are latency-bound.
+#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
@@ -111,15 +112,12 @@ route_kernel(const L* __restrict__ logits, int32_t* __restrict__ indices, float*
 // Same arithmetic for the weights: exp(l_k - l_top) / sum_j exp(l_j - l_top) over the picked logits, in pick order.
 constexpr int kQuadTopK = 8;
 
+// The picks of token t as seen by lane q of its quad: sel[k] / prob[k] (every lane of the quad ends with the same
+// values) and the sum of the picked probabilities.  All 32 lanes of the warp must call it together.
 template <typename L, int KPL>
-__global__ void __launch_bounds__(256)
-route_quad_kernel(const L* __restrict__ logits, int32_t* __restrict__ indices, float* __restrict__ weights,
-                  int64_t tokens, int experts, int top_k, int64_t ld, int vectorised) {
-  pdl_prologue();
-  const int q = threadIdx.x & 3;
-  const int64_t token = (static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x) >> 2;
-  const bool live = token < tokens;  // whole quads; dead quads still take part in the shuffles
-  const int64_t t = live ? token : tokens - 1;
+__device__ __forceinline__ void route_quad_token(const L* __restrict__ logits, int64_t t, int q, int experts, int top_k,
+                                                 int64_t ld, int vectorised, int (&sel)[kQuadTopK], float (&prob)[kQuadTopK],
+                                                 float& denom) {
   uint32_t key[KPL];
   if (vectorised) {  // fp32 logits, rows and row pitch multiples of four: one 128-bit load per four slots
 #pragma unroll
@@ -142,9 +140,8 @@ route_quad_kernel(const L* __restrict__ logits, int32_t* __restrict__ indices, f
   // NaN logits have key 0 and so has every expert already picked: a round whose best key is 0 has only those left
   // and takes the lowest index not picked yet (the bit mask), like the warp form.
   unsigned long long picked = 0;
-  int sel[kQuadTopK];
-  float prob[kQuadTopK];
-  float top_logit = 0.f, denom = 0.f;
+  float top_logit = 0.f;
+  denom = 0.f;
 #pragma unroll
   for (int k = 0; k < kQuadTopK; ++k) {
     sel[k] = 0;
@@ -193,6 +190,21 @@ route_quad_kernel(const L* __restrict__ logits, int32_t* __restrict__ indices, f
       prob[k] = p;
     }
   }
+}
+
+template <typename L, int KPL>
+__global__ void __launch_bounds__(256)
+route_quad_kernel(const L* __restrict__ logits, int32_t* __restrict__ indices, float* __restrict__ weights,
+                  int64_t tokens, int experts, int top_k, int64_t ld, int vectorised) {
+  pdl_prologue();
+  const int q = threadIdx.x & 3;
+  const int64_t token = (static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x) >> 2;
+  const bool live = token < tokens;  // whole quads; dead quads still take part in the shuffles
+  const int64_t t = live ? token : tokens - 1;
+  int sel[kQuadTopK];
+  float prob[kQuadTopK];
+  float denom;
+  route_quad_token<L, KPL>(logits, t, q, experts, top_k, ld, vectorised, sel, prob, denom);
   if (live) {
 #pragma unroll
     for (int k = 0; k < kQuadTopK; ++k) {
@@ -368,6 +380,224 @@ index_scatter_kernel(const int32_t* __restrict__ idx, int64_t pairs, int top_k, 
       if (dst >= 0) perm_token[dst] = static_cast<int32_t>(static_cast<uint32_t>(i) / static_cast<uint32_t>(top_k));
     }
   }
+}
+
+// ------------------------------------------------ index in one launch --
+//
+// One cooperative launch of at most one CTA per SM replaces the three launches above, whose cost at MoE sizes is
+// launch latency, not traffic.  CTA b owns a contiguous range of tokens and warp w of it a contiguous sub-range, so
+// (CTA, warp, step, lane) order is pair order and the permutation stays stable:
+//   1  each warp counts the experts of its pairs in a shared-memory histogram of its own;
+//   2  the CTA turns the warp histograms into exclusive prefixes over its warps and publishes its per-expert totals;
+//   3  grid rendezvous: every CTA stores a tag into a flag of its own; CTA 0 waits for all flags (one thread per
+//      flag) and then stores the tag into one word that a single thread of every other CTA waits for.  All waits are
+//      bounded.  The tag is a generation counter kept in the workspace and advanced by CTA 0 after the rendezvous,
+//      so replaying the same launch (a CUDA graph) works and nothing has to be cleared between calls;
+//   4  every CTA sums the published totals (pairs of each expert in earlier CTAs, and overall), scans the overall
+//      counts over the experts, and ranks its own pairs with __match_any_sync like index_scatter_kernel.
+// The cooperative launch attribute guarantees that all CTAs are resident together, which is what makes step 3 legal.
+// If a wait runs out all the same, the kernel writes -1 into offsets[experts] and returns.
+//
+// Routing stays a launch of its own: fused in front of step 1 (tried) it runs at 32 warps per SM instead of 46 and
+// the whole kernel took 33-35 us against 15 + 12 for the two launches; the routing is bound by the integer pipe
+// (a compare-and-select tree per pick), not by its launch.
+constexpr int kCoopThreads = 1024;
+constexpr int kCoopWarps = kCoopThreads / 32;
+constexpr int kCoopExperts = 256;
+constexpr int kCoopMaxGrid = 256;   // CTAs (flags in the workspace header)
+constexpr int kCoopGoWord = 1 + kCoopMaxGrid + 15;  // on a 128-byte line of its own behind the flags
+constexpr size_t kCoopHeaderBytes = 8 * (kCoopMaxGrid + 64);  // generation word, one flag per CTA, the go word, spare
+constexpr unsigned long long kCoopWaitNs = 2000000000ull;
+constexpr int kRankBatch = 4;  // steps of 32 pairs whose experts are loaded before the first is ranked
+
+__device__ __forceinline__ unsigned long long coop_timer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Polls *word until it holds `tag`; false when `budget_ns` ran out first.
+__device__ __forceinline__ bool coop_wait(const unsigned long long* word, unsigned long long tag, unsigned long long budget_ns) {
+  const unsigned long long start = coop_timer();
+  for (;;) {
+    unsigned long long seen;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(word) : "memory");
+    if (seen == tag) return true;
+    if (coop_timer() - start > budget_ns) return false;
+  }
+}
+__device__ __forceinline__ void coop_post(unsigned long long* word, unsigned long long tag) {
+  __threadfence();
+  asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(word), "l"(tag) : "memory");
+}
+
+__global__ void __launch_bounds__(kCoopThreads, 1)
+index_one_launch_kernel(const int32_t* __restrict__ indices, int64_t tokens, int experts, int top_k,
+                        int64_t tokens_per_cta, int tokens_per_warp,
+                        int32_t* __restrict__ counts, int32_t* __restrict__ offsets,
+                        int32_t* __restrict__ perm_token, int32_t* __restrict__ pos,
+                        unsigned long long* header, int32_t* grid_hist, unsigned long long budget_ns) {
+  extern __shared__ int coop_smem[];
+  int* whist = coop_smem;                            // [32 warps][experts]
+  int* s_before = coop_smem + kCoopWarps * experts;  // [experts] pairs of the expert in earlier CTAs
+  int* s_offset = s_before + experts;                // [experts] totals, then their exclusive scan
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int grid = static_cast<int>(gridDim.x), cta = static_cast<int>(blockIdx.x);
+#ifdef B200_COOP_STAMPS  // phase times of the last CTA into spare header words (a build for measuring only)
+#define B200_STAMP(n) do { if (cta == grid - 1 && tid == 0) header[kCoopGoWord + 16 + (n)] = coop_timer(); } while (0)
+#else
+#define B200_STAMP(n) do { } while (0)
+#endif
+  B200_STAMP(0);
+  for (int i = tid; i < kCoopWarps * experts; i += kCoopThreads) whist[i] = 0;
+  // the generation this launch answers to; CTA 0 advances it only after every CTA has passed the rendezvous
+  const unsigned long long tag = __ldcg(header) + 1ull;
+  __syncthreads();
+
+  const int64_t cta_begin = static_cast<int64_t>(cta) * tokens_per_cta;
+  const int64_t cta_end = cta_begin + tokens_per_cta < tokens ? cta_begin + tokens_per_cta : tokens;
+  int64_t warp_begin = cta_begin + static_cast<int64_t>(warp) * tokens_per_warp;
+  if (warp_begin > cta_end) warp_begin = cta_end;
+  const int64_t warp_end = warp_begin + tokens_per_warp < cta_end ? warp_begin + tokens_per_warp : cta_end;
+  const int64_t pair_begin = warp_begin * top_k, pair_end = warp_end * top_k;
+  int* mine = whist + warp * experts;
+
+  for (int64_t i = pair_begin + lane; i < pair_end; i += 32) {
+    const int e = indices[i];
+    if (e >= 0 && e < experts) atomicAdd(&mine[e], 1);
+  }
+  __syncthreads();
+  B200_STAMP(1);
+  for (int e = tid; e < experts; e += kCoopThreads) {
+    int running = 0;
+#pragma unroll 4
+    for (int w = 0; w < kCoopWarps; ++w) {
+      const int c = whist[w * experts + e];
+      whist[w * experts + e] = running;
+      running += c;
+    }
+    __stcg(grid_hist + static_cast<int64_t>(e) * grid + cta, running);
+  }
+  __syncthreads();
+
+  // ---- rendezvous of the whole grid
+  B200_STAMP(2);
+  unsigned long long* flags = header + 1;
+  unsigned long long* go = header + kCoopGoWord;
+  int gave_up = 0;
+  if (cta != 0) {
+    if (tid == 0) {
+      coop_post(flags + cta, tag);
+      gave_up = coop_wait(go, tag, budget_ns) ? 0 : 1;
+    }
+  } else if (tid > 0 && tid < grid) {
+    gave_up = coop_wait(flags + tid, tag, budget_ns) ? 0 : 1;
+  }
+  if (__syncthreads_or(gave_up)) {  // CTA 0 never posts the go word then, so every CTA ends up here
+    if (tid == 0) {
+      offsets[experts] = -1;
+      if (cta == 0) *header = tag;  // the flags of this launch must not satisfy the next one
+    }
+    return;
+  }
+  if (cta == 0 && tid == 0) coop_post(go, tag);
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  B200_STAMP(3);
+
+  // ---- pairs of every expert in earlier CTAs and overall
+  for (int e = warp; e < experts; e += kCoopWarps) {
+    int before = 0, total = 0;
+    for (int g = lane; g < grid; g += 32) {
+      const int c = __ldcg(grid_hist + static_cast<int64_t>(e) * grid + g);
+      total += c;
+      before += g < cta ? c : 0;
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) {
+      before += __shfl_xor_sync(kFull, before, o);
+      total += __shfl_xor_sync(kFull, total, o);
+    }
+    if (lane == 0) {
+      s_before[e] = before;
+      s_offset[e] = total;
+    }
+  }
+  __syncthreads();
+  if (warp == 0) {  // exclusive scan of the totals: lane l owns experts l * per .. l * per + per - 1
+    constexpr int kPer = kCoopExperts / 32;
+    const int per = (experts + 31) / 32;
+    int c[kPer];
+    int sum = 0;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+      const int e = lane * per + i;
+      c[i] = (i < per && e < experts) ? s_offset[e] : 0;
+      sum += c[i];
+    }
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(kFull, incl, o);
+      if (lane >= o) incl += up;
+    }
+    int excl = incl - sum;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+      const int e = lane * per + i;
+      if (i < per && e < experts) {
+        s_offset[e] = excl;
+        if (cta == 0) {
+          counts[e] = c[i];
+          offsets[e] = excl;
+          if (e == experts - 1) offsets[experts] = excl + c[i];
+        }
+        excl += c[i];
+      }
+    }
+    if (cta == 0 && lane == 0) *header = tag;  // every CTA read the old generation before it posted its flag
+  }
+  __syncthreads();
+  for (int e = tid; e < experts; e += kCoopThreads) s_offset[e] += s_before[e];
+  __syncthreads();
+
+  // ---- rank this warp's pairs: cursor of (warp, expert) = expert base + earlier CTAs + earlier warps of this CTA
+  B200_STAMP(4);
+  for (int64_t i0 = pair_begin; i0 < pair_end; i0 += 32 * kRankBatch) {
+    int ev[kRankBatch];
+#pragma unroll
+    for (int u = 0; u < kRankBatch; ++u) {
+      const int64_t i = i0 + u * 32 + lane;
+      int e = -1;
+      if (i < pair_end) {
+        e = indices[i];
+        if (e < 0 || e >= experts) e = -1;
+      }
+      ev[u] = e;
+    }
+#pragma unroll
+    for (int u = 0; u < kRankBatch; ++u) {
+      if (i0 + u * 32 < pair_end) {  // the same for the whole warp
+        const int64_t i = i0 + u * 32 + lane;
+        const int e = ev[u];
+        const unsigned same = __match_any_sync(kFull, e);
+        const int rank = __popc(same & ((1u << lane) - 1u));
+        int dst = -1;
+        if (e >= 0) dst = s_offset[e] + mine[e] + rank;
+        __syncwarp();
+        if (e >= 0 && rank == 0) mine[e] += __popc(same);
+        __syncwarp();
+        if (i < pair_end) {
+          pos[i] = dst;
+          if (dst >= 0) perm_token[dst] = static_cast<int32_t>(static_cast<uint32_t>(i) / static_cast<uint32_t>(top_k));
+        }
+      }
+    }
+  }
+#ifdef B200_COOP_STAMPS
+  __syncthreads();
+  B200_STAMP(5);
+#endif
+#undef B200_STAMP
 }
 
 // ---------------------------------------------------- permute / gather --
@@ -732,6 +962,75 @@ bool rows_aligned(const void* a, const void* b, int64_t row_bytes, int64_t lda_b
 
 int nblk_for(int64_t pairs) { return static_cast<int>(ceil_div(pairs, kPairsPerBlock)); }
 
+// Workspace of the index entry points: a header (generation word and per-CTA flags of the one-launch kernel), then the
+// histogram table of whichever kernels run: [experts][CTAs] for the one-launch kernel, [experts][blocks of 2048 pairs]
+// for the three-kernel chain.
+int64_t coop_grid_bound(int64_t tokens) {
+  const int64_t want = ceil_div(tokens, 64);
+  return want < 1 ? 1 : (want > kCoopMaxGrid ? kCoopMaxGrid : want);
+}
+size_t index_scratch_need(int64_t tokens, int64_t top_k, int64_t experts) {
+  const int64_t nblk = nblk_for(tokens * top_k);
+  const int64_t floor_cols = experts <= kCoopExperts ? coop_grid_bound(tokens) : 1;
+  const int64_t cols = nblk > floor_cols ? nblk : floor_cols;
+  return kCoopHeaderBytes + static_cast<size_t>(cols * experts) * sizeof(int32_t);
+}
+
+// Whether the current device can run the one-launch kernel (cooperative launch, one CTA of 1024 threads per SM).
+bool coop_supported() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  if (cached[dev] == 0) {
+    int flag = 0;
+    const bool ok = cudaDeviceGetAttribute(&flag, cudaDevAttrCooperativeLaunch, dev) == cudaSuccess && flag != 0;
+    (void)cudaGetLastError();
+    cached[dev] = ok ? 1 : -1;
+  }
+  return cached[dev] > 0;
+}
+
+template <typename... Params, typename... Args>
+void launch_cooperative(void (*kernel)(Params...), unsigned grid, unsigned block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(grid);
+  config.blockDim = dim3(block);
+  config.dynamicSmemBytes = smem;
+  config.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  (void)cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
+// B200_INDEX_CHAIN=1 in the environment keeps the separate route / histogram / scan / scatter launches (read at every
+// call: a getenv is a few tens of nanoseconds).
+bool one_launch_index(int64_t experts) {
+  const char* v = std::getenv("B200_INDEX_CHAIN");
+  if (v != nullptr && v[0] == '1') return false;
+  return experts <= kCoopExperts && coop_supported();
+}
+
+// The index as one cooperative launch.  The caller has checked shapes and pointers.
+int launch_index_one(const int32_t* indices, int64_t tokens, int E, int K, int32_t* counts, int32_t* offsets,
+                     int32_t* perm_token, int32_t* pos, void* scratch, cudaStream_t st) {
+  int64_t grid = coop_grid_bound(tokens);
+  if (grid > sm_count()) grid = sm_count();
+  const int64_t tokens_per_cta = ceil_div(tokens > 0 ? tokens : 1, grid);
+  const int tokens_per_warp = static_cast<int>(ceil_div(tokens_per_cta, kCoopWarps));
+  unsigned long long* header = static_cast<unsigned long long*>(scratch);
+  int32_t* grid_hist = reinterpret_cast<int32_t*>(static_cast<unsigned char*>(scratch) + kCoopHeaderBytes);
+  const size_t smem = static_cast<size_t>(kCoopWarps + 2) * E * sizeof(int);
+  launch_cooperative(index_one_launch_kernel, static_cast<unsigned>(grid), kCoopThreads, smem, st, indices, tokens, E, K, tokens_per_cta,
+                     tokens_per_warp, counts, offsets, perm_token, pos, header, grid_hist, kCoopWaitNs);
+  return after_launch("index_one_launch_kernel");
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -801,8 +1100,7 @@ static int index_check(const char* fn, int64_t tokens, int64_t top_k, int64_t ex
 extern "C" int b200_moe_index_scratch_bytes(int64_t tokens, int64_t top_k, int64_t experts, size_t* bytes) {
   B200_REQUIRE_PTR(bytes);
   if (int rc = index_check(__func__, tokens, top_k, experts)) return rc;
-  const int64_t nblk = nblk_for(tokens * top_k);
-  *bytes = static_cast<size_t>((nblk > 0 ? nblk : 1) * experts) * sizeof(int32_t);
+  *bytes = index_scratch_need(tokens, top_k, experts);
   return B200_OK;
 }
 
@@ -820,7 +1118,7 @@ extern "C" int b200_moe_index(const int32_t* indices, int64_t tokens, int64_t to
     B200_REQUIRE_PTR(pos);
   }
   const int nblk = nblk_for(pairs);
-  const size_t need = static_cast<size_t>((nblk > 0 ? nblk : 1) * experts) * sizeof(int32_t);
+  const size_t need = index_scratch_need(tokens, top_k, experts);
   if (scratch_bytes < need || !aligned(scratch, 16))
     return fail(B200_ERR_SCRATCH, "%s: scratch needs %zu bytes, 16-byte aligned (got %zu)", __func__, need, scratch_bytes);
   if (!aligned(indices, 4) || !aligned(counts, 4) || !aligned(offsets, 4) || !aligned(perm_token, 4) || !aligned(pos, 4))
@@ -828,7 +1126,9 @@ extern "C" int b200_moe_index(const int32_t* indices, int64_t tokens, int64_t to
   if (int rc = check_device()) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int E = static_cast<int>(experts);
-  int32_t* block_hist = static_cast<int32_t*>(scratch);
+  if (one_launch_index(experts))
+    return launch_index_one(indices, tokens, E, static_cast<int>(top_k), counts, offsets, perm_token, pos, scratch, st);
+  int32_t* block_hist = reinterpret_cast<int32_t*>(static_cast<unsigned char*>(scratch) + kCoopHeaderBytes);
   if (nblk > 0) {
     launch(index_hist_kernel, nblk, kIndexThreads, 8 * E * sizeof(int), st, indices, pairs, E, nblk, block_hist);
     if (int rc = after_launch("index_hist_kernel")) return rc;
@@ -843,6 +1143,20 @@ extern "C" int b200_moe_index(const int32_t* indices, int64_t tokens, int64_t to
   return B200_OK;
 }
 
+// Routing and the index in one call: b200_moe_route, then b200_moe_index on its picks (two or four kernel launches).
+extern "C" int b200_moe_route_index(const void* logits, int32_t* indices, float* weights,
+                                    int64_t tokens, int64_t experts, int64_t top_k, int64_t ld_logits, int logits_dtype,
+                                    int32_t* counts, int32_t* offsets, int32_t* perm_token, int32_t* pos,
+                                    void* scratch, size_t scratch_bytes, void* stream) {
+  if (int rc = index_check(__func__, tokens, top_k, experts)) return rc;
+  B200_REQUIRE_PTR(scratch);
+  if (scratch_bytes < index_scratch_need(tokens, top_k, experts) || !aligned(scratch, 16))  // before anything is launched
+    return fail(B200_ERR_SCRATCH, "%s: scratch needs %zu bytes, 16-byte aligned (got %zu)", __func__,
+                index_scratch_need(tokens, top_k, experts), scratch_bytes);
+  if (int rc = b200_moe_route(logits, indices, weights, tokens, experts, top_k, ld_logits, logits_dtype, stream)) return rc;
+  return b200_moe_index(indices, tokens, top_k, experts, counts, offsets, perm_token, pos, scratch, scratch_bytes, stream);
+}
+
 // ------------------------------------------------- index without a workspace --
 
 namespace b200 {
@@ -852,7 +1166,7 @@ namespace {
 // held until the process exits.  On the host this name is only a stand-in for the
 // symbol; the device address comes from cudaGetSymbolAddress, once per device.
 constexpr size_t kStaticScratchBytes = size_t{1} << 20;
-static __device__ __align__(256) unsigned char g_index_scratch[kStaticScratchBytes];
+static __device__ __align__(256) unsigned char g_index_scratch[kCoopHeaderBytes + kStaticScratchBytes];
 
 constexpr int kMaxDevicesStatic = 64;
 std::mutex g_static_mutex;
@@ -900,12 +1214,12 @@ extern "C" int b200_moe_index_static(const int32_t* indices, int64_t tokens, int
     B200_REQUIRE_PTR(pos);
   }
   const int nblk = nblk_for(pairs);
-  const size_t need = static_cast<size_t>((nblk > 0 ? nblk : 1) * experts) * sizeof(int32_t);
-  if (need > kStaticScratchBytes)
+  const size_t need = index_scratch_need(tokens, top_k, experts);
+  if (need - kCoopHeaderBytes > kStaticScratchBytes)
     return fail(B200_ERR_SCRATCH,
                 "%s: tokens*top_k=%lld with %lld experts needs %zu bytes of scratch, over the built-in %zu; "
                 "use b200_moe_index with a caller-provided workspace",
-                __func__, (long long)pairs, (long long)experts, need, kStaticScratchBytes);
+                __func__, (long long)pairs, (long long)experts, need - kCoopHeaderBytes, kStaticScratchBytes);
   if (!aligned(indices, 4) || !aligned(counts, 4) || !aligned(offsets, 4) || !aligned(perm_token, 4) || !aligned(pos, 4))
     return fail(B200_ERR_ALIGNMENT, "%s: pointer not aligned to 4 bytes", __func__);
   if (int rc = check_device()) return rc;
@@ -913,9 +1227,11 @@ extern "C" int b200_moe_index_static(const int32_t* indices, int64_t tokens, int
   if (int rc = static_scratch(&scratch)) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int E = static_cast<int>(experts);
-  // The histogram kernel writes every entry the two later kernels read, so nothing
-  // left over from an earlier call has to be cleared first.
-  int32_t* block_hist = static_cast<int32_t*>(scratch);
+  // The histogram kernels write every entry the later steps read, and the one-launch kernel's generation word only has
+  // to differ from its flags' last value, so nothing left over from an earlier call has to be cleared first.
+  if (one_launch_index(experts))
+    return launch_index_one(indices, tokens, E, static_cast<int>(top_k), counts, offsets, perm_token, pos, scratch, st);
+  int32_t* block_hist = reinterpret_cast<int32_t*>(static_cast<unsigned char*>(scratch) + kCoopHeaderBytes);
   if (nblk > 0) {
     launch(index_hist_kernel, nblk, kIndexThreads, 8 * E * sizeof(int), st, indices, pairs, E, nblk, block_hist);
     if (int rc = after_launch("index_hist_kernel")) return rc;

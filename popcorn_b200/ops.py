@@ -585,6 +585,36 @@ def moe_index(indices: Tensor, experts: int) -> tuple[Tensor, Tensor, Tensor, Te
     return counts, offsets, perm, pos
 
 
+def moe_route_index(router_logits: Tensor, top_k: int) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+    """moe_route followed by moe_index on its picks, as one call: (indices, weights, counts, offsets, perm, pos).
+
+    router_logits: [tokens, experts].  Same results as the two calls, one trip through the C ABI (momoe.py:47-49 and
+    find_used_experts, momoe_tl.py:1071-1161, run back to back in every momoe forward)."""
+    device = _require_cuda(router_logits)
+    _forbid_grad(router_logits)
+    code = _dtype_code(router_logits, "moe_route_index")
+    if router_logits.dim() != 2:
+        raise ValueError("moe_route_index: router_logits must be [tokens, experts]")
+    tokens, experts = router_logits.shape
+    top_k = int(top_k)
+    logits2, ld = _rows(router_logits)
+    indices = torch.empty((tokens, top_k), dtype=torch.int32, device=device)
+    weights = torch.empty((tokens, top_k), dtype=torch.float32, device=device)
+    counts = torch.empty(experts, dtype=torch.int32, device=device)
+    offsets = torch.empty(experts + 1, dtype=torch.int32, device=device)
+    perm = torch.empty(tokens * top_k, dtype=torch.int32, device=device)
+    pos = torch.empty((tokens, top_k), dtype=torch.int32, device=device)
+    need = ctypes.c_size_t(0)
+    _lib.call("b200_moe_index_scratch_bytes", tokens, top_k, int(experts), ctypes.byref(need))
+    scratch = torch.empty(max(need.value, 16), dtype=torch.uint8, device=device)
+    with torch.cuda.device(device):
+        _lib.call(
+            "b200_moe_route_index", _ptr(logits2), _ptr(indices), _ptr(weights), tokens, int(experts), top_k, ld, code,
+            _ptr(counts), _ptr(offsets), _ptr(perm), _ptr(pos), _ptr(scratch), ctypes.c_size_t(scratch.numel()), _stream(device),
+        )
+    return indices, weights, counts, offsets, perm, pos
+
+
 def moe_scatter_rows(x: Tensor, pos: Tensor) -> Tensor:
     """rows[pos[t, k]] = x[t] for every slot k: each token row is read once and written top_k times.
 
@@ -851,8 +881,8 @@ def momoe(x: Tensor, gate_weight: Tensor, up_weight: Tensor, down_weight: Tensor
     check_momoe(x, gate_weight, up_weight, down_weight, router_logits)
     experts, hidden, _ = gate_weight.shape
     flat = x.reshape(-1, hidden)
-    indices, weights = moe_route(router_logits.reshape(-1, experts).float(), int(top_k))
-    rows, _, offsets, _, pos = moe_permute(flat, indices, experts)
+    _, weights, _, offsets, _, pos = moe_route_index(router_logits.reshape(-1, experts).float(), int(top_k))
+    rows = moe_scatter_rows(flat, pos)
     # The rows are permuted by a pass of their own (0.74 ms for 65536 tokens x top-8 x 4096): fetching them through the
     # permutation inside the first projection (moe_grouped_gemm_gathered) is bit-identical but its four-row gathered
     # copies feed a 128 x 256 tile at a third of the rate the tensor pipe consumes it (26.6 ms against 9.5 + 0.74).

@@ -71,7 +71,12 @@ def test_argument_validation_needs_no_device(built_library):
 def test_scratch_size_query(built_library):
     need = ctypes.c_size_t(0)
     _lib.call("b200_moe_index_scratch_bytes", 65536, 8, 64, ctypes.byref(need))
-    assert need.value == (65536 * 8 // 2048) * 64 * 4
+    header = 8 * (256 + 64)  # generation word, per-CTA flags and go word of the one-launch kernel
+    assert need.value == header + (65536 * 8 // 2048) * 64 * 4
+    _lib.call("b200_moe_index_scratch_bytes", 4096, 1, 64, ctypes.byref(need))   # 2 blocks of pairs, 64 CTAs of tokens
+    assert need.value == header + 64 * 64 * 4
+    _lib.call("b200_moe_index_scratch_bytes", 4096, 1, 1024, ctypes.byref(need))  # beyond the one-launch kernel: blocks only
+    assert need.value == header + 2 * 1024 * 4
     with pytest.raises(_lib.B200Error) as err:
         _lib.call("b200_moe_index", ctypes.c_void_p(4096), 16, 2, 8, ctypes.c_void_p(4096), ctypes.c_void_p(4096),
                   ctypes.c_void_p(4096), ctypes.c_void_p(4096), ctypes.c_void_p(4096), ctypes.c_size_t(4), ctypes.c_void_p(0))
