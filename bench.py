@@ -333,9 +333,10 @@ def bench_moe(device, peak_gbs: float, sampler, scale: float = 1.0, fixed_steps:
         "route": lambda i: _lib.call("b200_moe_route", p(logits), p(idx2), p(wts2), tokens, experts, top_k, experts, _lib.F32, stream),
         "index": lambda i: _lib.call("b200_moe_index", p(idx), tokens, top_k, experts, p(counts2), p(offsets2), p(perm2), p(pos2),
                                      p(scratch), ctypes.c_size_t(scratch.numel()), stream),
-        # what a layer runs: routing and the index as ONE cooperative launch
+        # what a layer runs: routing and the index through one call, without the list of token ids per sorted row
+        # (permute and unpermute read the inverse map `pos` only)
         "route_index": lambda i: _lib.call("b200_moe_route_index", p(logits), p(idx2), p(wts2), tokens, experts, top_k, experts, _lib.F32,
-                                           p(counts2), p(offsets2), p(perm2), p(pos2), p(scratch), ctypes.c_size_t(scratch.numel()), stream),
+                                           p(counts2), p(offsets2), ctypes.c_void_p(0), p(pos2), p(scratch), ctypes.c_size_t(scratch.numel()), stream),
         # permute and unpermute alone, straight through the C ABI (moe_permute the op also rebuilds the index)
         "permute": lambda i: _lib.call("b200_moe_permute", p(x), p(pos), p(rows), tokens, top_k, hidden, hidden, hidden, _lib.BF16, stream),
         "unpermute": lambda i: _lib.call("b200_moe_unpermute", p(rows), p(wts), p(pos), p(y), tokens, top_k, hidden, hidden, hidden, _lib.BF16, stream),

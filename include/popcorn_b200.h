@@ -359,6 +359,8 @@ int b200_moe_index_scratch_bytes(int64_t tokens, int64_t top_k, int64_t experts,
  *                 by (expert, token), i.e. a stable sort of the flattened
  *                 indices by expert
  *   pos[t, k]   = sorted position of pair (t, k)  (inverse map)
+ * perm_token may be NULL for callers that only need pos (the permute and
+ * unpermute kernels do); it is one scattered 4-byte store per pair.
  *
  * Replaces find_used_experts + scatter_cols_kernel,
  * src/popcorn/impls/momoe_tl.py:1071-1161 (counts :1135, prefix :1094-1101,

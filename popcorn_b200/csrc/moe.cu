@@ -370,14 +370,14 @@ index_scatter_kernel(const int32_t* __restrict__ idx, int64_t pairs, int top_k, 
     const int e = my_e[r];
     const unsigned same = __match_any_sync(kFull, e);
     const int rank = __popc(same & ((1u << lane) - 1u));
-    int dst = -1;
-    if (e >= 0) dst = cursor[e] + rank;
-    __syncwarp();
-    if (e >= 0 && rank == 0) cursor[e] += __popc(same);
-    __syncwarp();
+    const int leader = __ffs(same) - 1;  // advances the cursor for its group
+    int base = 0;
+    if (e >= 0 && lane == leader) base = atomicAdd(&cursor[e], __popc(same));
+    base = __shfl_sync(kFull, base, leader);
+    const int dst = e >= 0 ? base + rank : -1;
     if (i < pairs) {
       pos[i] = dst;
-      if (dst >= 0) perm_token[dst] = static_cast<int32_t>(static_cast<uint32_t>(i) / static_cast<uint32_t>(top_k));
+      if (dst >= 0 && perm_token != nullptr) perm_token[dst] = static_cast<int32_t>(static_cast<uint32_t>(i) / static_cast<uint32_t>(top_k));
     }
   }
 }
@@ -408,7 +408,6 @@ constexpr int kCoopMaxGrid = 256;   // CTAs (flags in the workspace header)
 constexpr int kCoopGoWord = 1 + kCoopMaxGrid + 15;  // on a 128-byte line of its own behind the flags
 constexpr size_t kCoopHeaderBytes = 8 * (kCoopMaxGrid + 64);  // generation word, one flag per CTA, the go word, spare
 constexpr unsigned long long kCoopWaitNs = 2000000000ull;
-constexpr int kRankBatch = 4;  // steps of 32 pairs whose experts are loaded before the first is ranked
 
 __device__ __forceinline__ unsigned long long coop_timer() {
   unsigned long long t;
@@ -431,6 +430,67 @@ __device__ __forceinline__ void coop_post(unsigned long long* word, unsigned lon
   asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(word), "l"(tag) : "memory");
 }
 
+// Exclusive scan of a[0 .. n) in place by ONE warp (n <= 32 * kPer); returns the total to every lane.
+template <int kPer>
+__device__ __forceinline__ int warp_exclusive_scan(int* a, int n, int lane) {
+  const int per = (n + 31) / 32;  // lane l owns a[l * per .. l * per + per - 1]
+  int c[kPer];
+  int sum = 0;
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    const int e = lane * per + i;
+    c[i] = (i < per && e < n) ? a[e] : 0;
+    sum += c[i];
+  }
+  int incl = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int up = __shfl_up_sync(kFull, incl, o);
+    if (lane >= o) incl += up;
+  }
+  int excl = incl - sum;
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    const int e = lane * per + i;
+    if (i < per && e < n) {
+      a[e] = excl;
+      excl += c[i];
+    }
+  }
+  return __shfl_sync(kFull, incl, 31);
+}
+
+// Ranks the pairs [first, last) of one warp, 32 consecutive pairs per step: destination = base[e] + the warp's cursor
+// + the number of lower lanes with the same expert.  The first lane of every group of equal experts advances the
+// cursor with a shared-memory atomic and hands the old value to its group by shuffle.  pair numbers fit in 31 bits.
+__device__ __forceinline__ void rank_pairs_by_match(const int32_t* __restrict__ indices, int first, int last, int experts, int top_k,
+                                                    int lane, const int* base_of, int* cursor, int32_t* __restrict__ pos,
+                                                    int32_t* __restrict__ perm_token) {
+  const int shift = (top_k & (top_k - 1)) == 0 ? __ffs(top_k) - 1 : -1;
+  int e_next = -1;
+  if (first + lane < last) e_next = indices[first + lane];
+#pragma unroll 1
+  for (int i0 = first; i0 < last; i0 += 32) {
+    const int i = i0 + lane;
+    int e = e_next;
+    if (e < 0 || e >= experts) e = -1;
+    e_next = -1;
+    if (i + 32 < last) e_next = indices[i + 32];
+    const unsigned same = __match_any_sync(kFull, e);
+    const int rank = __popc(same & ((1u << lane) - 1u));
+    const int leader = __ffs(same) - 1;
+    int base = 0;
+    if (e >= 0 && lane == leader) base = atomicAdd(&cursor[e], __popc(same));
+    base = __shfl_sync(kFull, base, leader);
+    const int dst = e >= 0 ? base_of[e] + base + rank : -1;
+    if (i < last) {
+      pos[i] = dst;
+      if (dst >= 0 && perm_token != nullptr)  // optional: one scattered 4-byte store per pair
+        perm_token[dst] = shift >= 0 ? i >> shift : static_cast<int>(static_cast<unsigned>(i) / static_cast<unsigned>(top_k));
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kCoopThreads, 1)
 index_one_launch_kernel(const int32_t* __restrict__ indices, int64_t tokens, int experts, int top_k,
                         int64_t tokens_per_cta, int tokens_per_warp,
@@ -440,7 +500,8 @@ index_one_launch_kernel(const int32_t* __restrict__ indices, int64_t tokens, int
   extern __shared__ int coop_smem[];
   int* whist = coop_smem;                            // [32 warps][experts]
   int* s_before = coop_smem + kCoopWarps * experts;  // [experts] pairs of the expert in earlier CTAs
-  int* s_offset = s_before + experts;                // [experts] totals, then their exclusive scan
+  int* s_offset = s_before + experts;                // [experts] totals, then first destination of this CTA's pairs
+  constexpr int kPer = kCoopExperts / 32;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int grid = static_cast<int>(gridDim.x), cta = static_cast<int>(blockIdx.x);
 #ifdef B200_COOP_STAMPS  // phase times of the last CTA into spare header words (a build for measuring only)
@@ -462,7 +523,7 @@ index_one_launch_kernel(const int32_t* __restrict__ indices, int64_t tokens, int
   const int64_t pair_begin = warp_begin * top_k, pair_end = warp_end * top_k;
   int* mine = whist + warp * experts;
 
-  for (int64_t i = pair_begin + lane; i < pair_end; i += 32) {
+  for (int i = static_cast<int>(pair_begin) + lane; i < static_cast<int>(pair_end); i += 32) {  // tokens * top_k < 2^31
     const int e = indices[i];
     if (e >= 0 && e < experts) atomicAdd(&mine[e], 1);
   }
@@ -504,95 +565,61 @@ index_one_launch_kernel(const int32_t* __restrict__ indices, int64_t tokens, int
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   B200_STAMP(3);
 
-  // ---- pairs of every expert in earlier CTAs and overall
-  for (int e = warp; e < experts; e += kCoopWarps) {
-    int before = 0, total = 0;
+  // ---- pairs of every expert in earlier CTAs and overall; a warp takes experts w and w + 32 together
+  for (int e0 = warp; e0 < experts; e0 += 2 * kCoopWarps) {
+    const int e1 = e0 + kCoopWarps;
+    int before0 = 0, total0 = 0, before1 = 0, total1 = 0;
     for (int g = lane; g < grid; g += 32) {
-      const int c = __ldcg(grid_hist + static_cast<int64_t>(e) * grid + g);
-      total += c;
-      before += g < cta ? c : 0;
+      const int c0 = __ldcg(grid_hist + static_cast<int64_t>(e0) * grid + g);
+      const int c1 = e1 < experts ? __ldcg(grid_hist + static_cast<int64_t>(e1) * grid + g) : 0;
+      total0 += c0;
+      total1 += c1;
+      before0 += g < cta ? c0 : 0;
+      before1 += g < cta ? c1 : 0;
     }
 #pragma unroll
     for (int o = 16; o >= 1; o >>= 1) {
-      before += __shfl_xor_sync(kFull, before, o);
-      total += __shfl_xor_sync(kFull, total, o);
+      before0 += __shfl_xor_sync(kFull, before0, o);
+      total0 += __shfl_xor_sync(kFull, total0, o);
+      before1 += __shfl_xor_sync(kFull, before1, o);
+      total1 += __shfl_xor_sync(kFull, total1, o);
     }
     if (lane == 0) {
-      s_before[e] = before;
-      s_offset[e] = total;
+      s_before[e0] = before0;
+      s_offset[e0] = total0;
+      if (e1 < experts) {
+        s_before[e1] = before1;
+        s_offset[e1] = total1;
+      }
     }
   }
   __syncthreads();
-  if (warp == 0) {  // exclusive scan of the totals: lane l owns experts l * per .. l * per + per - 1
-    constexpr int kPer = kCoopExperts / 32;
-    const int per = (experts + 31) / 32;
-    int c[kPer];
-    int sum = 0;
-#pragma unroll
-    for (int i = 0; i < kPer; ++i) {
-      const int e = lane * per + i;
-      c[i] = (i < per && e < experts) ? s_offset[e] : 0;
-      sum += c[i];
-    }
-    int incl = sum;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int up = __shfl_up_sync(kFull, incl, o);
-      if (lane >= o) incl += up;
-    }
-    int excl = incl - sum;
-#pragma unroll
-    for (int i = 0; i < kPer; ++i) {
-      const int e = lane * per + i;
-      if (i < per && e < experts) {
-        s_offset[e] = excl;
-        if (cta == 0) {
-          counts[e] = c[i];
-          offsets[e] = excl;
-          if (e == experts - 1) offsets[experts] = excl + c[i];
-        }
-        excl += c[i];
+  if (warp == 0) {
+    if (cta == 0)
+      for (int e = lane; e < experts; e += 32) counts[e] = s_offset[e];
+    __syncwarp();  // the scan's lanes own other entries than the loops around it
+    const int all = warp_exclusive_scan<kPer>(s_offset, experts, lane);
+    __syncwarp();
+    if (cta == 0) {
+      for (int e = lane; e < experts; e += 32) offsets[e] = s_offset[e];
+      if (lane == 0) {
+        offsets[experts] = all;
+        *header = tag;  // every CTA read the old generation before it posted its flag
       }
     }
-    if (cta == 0 && lane == 0) *header = tag;  // every CTA read the old generation before it posted its flag
   }
   __syncthreads();
   for (int e = tid; e < experts; e += kCoopThreads) s_offset[e] += s_before[e];
   __syncthreads();
 
-  // ---- rank this warp's pairs: cursor of (warp, expert) = expert base + earlier CTAs + earlier warps of this CTA
+  // ---- rank this warp's pairs: destination = first destination of this CTA's pairs of the expert + earlier warps of
+  // this CTA (the cursor in `mine`) + rank inside the step
   B200_STAMP(4);
-  for (int64_t i0 = pair_begin; i0 < pair_end; i0 += 32 * kRankBatch) {
-    int ev[kRankBatch];
-#pragma unroll
-    for (int u = 0; u < kRankBatch; ++u) {
-      const int64_t i = i0 + u * 32 + lane;
-      int e = -1;
-      if (i < pair_end) {
-        e = indices[i];
-        if (e < 0 || e >= experts) e = -1;
-      }
-      ev[u] = e;
-    }
-#pragma unroll
-    for (int u = 0; u < kRankBatch; ++u) {
-      if (i0 + u * 32 < pair_end) {  // the same for the whole warp
-        const int64_t i = i0 + u * 32 + lane;
-        const int e = ev[u];
-        const unsigned same = __match_any_sync(kFull, e);
-        const int rank = __popc(same & ((1u << lane) - 1u));
-        int dst = -1;
-        if (e >= 0) dst = s_offset[e] + mine[e] + rank;
-        __syncwarp();
-        if (e >= 0 && rank == 0) mine[e] += __popc(same);
-        __syncwarp();
-        if (i < pair_end) {
-          pos[i] = dst;
-          if (dst >= 0) perm_token[dst] = static_cast<int32_t>(static_cast<uint32_t>(i) / static_cast<uint32_t>(top_k));
-        }
-      }
-    }
-  }
+  // (Tried instead of the match: seven votes, one per bit of the expert number - the same time; one token per lane
+  // with per-expert token masks built by shared-memory atomicOr - 2.7 instead of 3.8 us for this phase at 3544 pairs per
+  // SM when the permutation is not stored, but 2 us slower on small inputs, whose time is the length of the dependent
+  // chain; staging the permutation in shared memory to store it in runs - slower.)
+  rank_pairs_by_match(indices, static_cast<int>(pair_begin), static_cast<int>(pair_end), experts, top_k, lane, s_offset, mine, pos, perm_token);
 #ifdef B200_COOP_STAMPS
   __syncthreads();
   B200_STAMP(5);
@@ -1025,7 +1052,7 @@ int launch_index_one(const int32_t* indices, int64_t tokens, int E, int K, int32
   const int tokens_per_warp = static_cast<int>(ceil_div(tokens_per_cta, kCoopWarps));
   unsigned long long* header = static_cast<unsigned long long*>(scratch);
   int32_t* grid_hist = reinterpret_cast<int32_t*>(static_cast<unsigned char*>(scratch) + kCoopHeaderBytes);
-  const size_t smem = static_cast<size_t>(kCoopWarps + 2) * E * sizeof(int);
+  const size_t smem = static_cast<size_t>(kCoopWarps + 2) * E * sizeof(int);  // at most 34 KiB
   launch_cooperative(index_one_launch_kernel, static_cast<unsigned>(grid), kCoopThreads, smem, st, indices, tokens, E, K, tokens_per_cta,
                      tokens_per_warp, counts, offsets, perm_token, pos, header, grid_hist, kCoopWaitNs);
   return after_launch("index_one_launch_kernel");
@@ -1114,7 +1141,6 @@ extern "C" int b200_moe_index(const int32_t* indices, int64_t tokens, int64_t to
   const int64_t pairs = tokens * top_k;
   if (pairs > 0) {
     B200_REQUIRE_PTR(indices);
-    B200_REQUIRE_PTR(perm_token);
     B200_REQUIRE_PTR(pos);
   }
   const int nblk = nblk_for(pairs);
@@ -1210,7 +1236,6 @@ extern "C" int b200_moe_index_static(const int32_t* indices, int64_t tokens, int
   const int64_t pairs = tokens * top_k;
   if (pairs > 0) {
     B200_REQUIRE_PTR(indices);
-    B200_REQUIRE_PTR(perm_token);
     B200_REQUIRE_PTR(pos);
   }
   const int nblk = nblk_for(pairs);

@@ -220,7 +220,7 @@ class ExpertParallel:
     def _dispatch_p2p(self, x: Tensor, router_logits: Tensor) -> Dispatched:
         ops = self.ops
         recv, out, recv_ptrs, _, capacity, _, _ = self._buffers(x)
-        indices, weights, counts, offsets, _, pos = ops.moe_route_index(router_logits, self.top_k)
+        indices, weights, counts, offsets, _, pos = ops.moe_route_index(router_logits, self.top_k, want_perm=False)
         self._epoch += 1
         # counts to every rank, everybody's counts back, the plan: one kernel, nothing leaves the device.  Waiting for
         # every rank's counts also orders the ranks: a rank writes them after its previous step's last read of `out`.

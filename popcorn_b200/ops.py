@@ -585,8 +585,9 @@ def moe_index(indices: Tensor, experts: int) -> tuple[Tensor, Tensor, Tensor, Te
     return counts, offsets, perm, pos
 
 
-def moe_route_index(router_logits: Tensor, top_k: int) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+def moe_route_index(router_logits: Tensor, top_k: int, want_perm: bool = True) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor | None, Tensor]:
     """moe_route followed by moe_index on its picks, as one call: (indices, weights, counts, offsets, perm, pos).
+    want_perm=False leaves `perm` out (None): the permute / unpermute kernels only read `pos`.
 
     router_logits: [tokens, experts].  Same results as the two calls, one trip through the C ABI (momoe.py:47-49 and
     find_used_experts, momoe_tl.py:1071-1161, run back to back in every momoe forward)."""
@@ -602,7 +603,7 @@ def moe_route_index(router_logits: Tensor, top_k: int) -> tuple[Tensor, Tensor, 
     weights = torch.empty((tokens, top_k), dtype=torch.float32, device=device)
     counts = torch.empty(experts, dtype=torch.int32, device=device)
     offsets = torch.empty(experts + 1, dtype=torch.int32, device=device)
-    perm = torch.empty(tokens * top_k, dtype=torch.int32, device=device)
+    perm = torch.empty(tokens * top_k, dtype=torch.int32, device=device) if want_perm else None
     pos = torch.empty((tokens, top_k), dtype=torch.int32, device=device)
     need = ctypes.c_size_t(0)
     _lib.call("b200_moe_index_scratch_bytes", tokens, top_k, int(experts), ctypes.byref(need))
@@ -881,7 +882,7 @@ def momoe(x: Tensor, gate_weight: Tensor, up_weight: Tensor, down_weight: Tensor
     check_momoe(x, gate_weight, up_weight, down_weight, router_logits)
     experts, hidden, _ = gate_weight.shape
     flat = x.reshape(-1, hidden)
-    _, weights, _, offsets, _, pos = moe_route_index(router_logits.reshape(-1, experts).float(), int(top_k))
+    _, weights, _, offsets, _, pos = moe_route_index(router_logits.reshape(-1, experts).float(), int(top_k), want_perm=False)
     rows = moe_scatter_rows(flat, pos)
     # The rows are permuted by a pass of their own (0.74 ms for 65536 tokens x top-8 x 4096): fetching them through the
     # permutation inside the first projection (moe_grouped_gemm_gathered) is bit-identical but its four-row gathered

@@ -52,6 +52,16 @@ def test_route_index_equals_the_oracle_and_the_two_calls(tokens, experts, top_k,
         assert torch.equal(one, two), "the results differ from moe_route + moe_index"
 
 
+def test_the_token_list_is_optional():
+    tokens, experts, top_k = 5000, 64, 8
+    logits = seeded_logits(tokens, experts, top_k, torch.float32, seed=8).to(DEV)
+    full = ops.moe_route_index(logits, top_k)
+    lean = ops.moe_route_index(logits, top_k, want_perm=False)
+    assert lean[4] is None
+    for i in (0, 1, 2, 3, 5):
+        assert torch.equal(full[i], lean[i])
+
+
 def test_route_index_reads_strided_logits():
     tokens, experts, top_k = 3000, 64, 8
     wide = torch.zeros(tokens, 96)
