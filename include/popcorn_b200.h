@@ -407,7 +407,8 @@ int b200_moe_route_index(const void* logits, int32_t* indices, float* weights,
  * an allocator nor a scratch pointer.  Such a caller still owns the inputs and the
  * four outputs; only the intermediate per-block histogram, which b200_moe_index
  * takes as `scratch`, lives inside the library here, in a fixed 1 MiB device array
- * that every GPU loading the library holds until the process exits.
+ * (plus 2.5 KiB for the generation word and flags of the one-launch kernel) that
+ * every GPU loading the library holds until the process exits.
  *
  * Limit: ceil(tokens*top_k / 2048) * experts * 4 bytes must fit in that array
  * (b200_moe_index_static_max_bytes reports its size); e.g. 64 experts allow up to
