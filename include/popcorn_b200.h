@@ -388,7 +388,7 @@ int b200_moe_index(const int32_t* indices, int64_t tokens, int64_t top_k, int64_
  * runs the two back to back (momoe.py:47-49, then find_used_experts,
  * momoe_tl.py:1071-1161).  Two kernel launches up to 256 experts.  (Routing inside
  * the index kernel was built and measured: 33-35 us for 65536 tokens x top-8 over
- * 64 experts against 15 + 12 us for the two launches, because the routing is
+ * 64 experts against 15 + 15 us for the two launches, because the routing is
  * bound by the integer pipe and loses occupancy inside the cooperative kernel.)
  */
 int b200_moe_route_index(const void* logits, int32_t* indices, float* weights,

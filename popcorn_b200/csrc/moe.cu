@@ -399,7 +399,7 @@ index_scatter_kernel(const int32_t* __restrict__ idx, int64_t pairs, int top_k, 
 // If a wait runs out all the same, the kernel writes -1 into offsets[experts] and returns.
 //
 // Routing stays a launch of its own: fused in front of step 1 (tried) it runs at 32 warps per SM instead of 46 and
-// the whole kernel took 33-35 us against 15 + 12 for the two launches; the routing is bound by the integer pipe
+// the whole kernel took 33-35 us against 15 + 15 for the two launches; the routing is bound by the integer pipe
 // (a compare-and-select tree per pick), not by its launch.
 constexpr int kCoopThreads = 1024;
 constexpr int kCoopWarps = kCoopThreads / 32;
