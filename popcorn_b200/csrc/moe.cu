@@ -112,9 +112,10 @@ route_kernel(const L* __restrict__ logits, int32_t* __restrict__ indices, float*
 // Same arithmetic for the weights: exp(l_k - l_top) / sum_j exp(l_j - l_top) over the picked logits, in pick order.
 constexpr int kQuadTopK = 8;
 
-// The picks of token t as seen by lane q of its quad: sel[k] / prob[k] (every lane of the quad ends with the same
-// values) and the sum of the picked probabilities.  All 32 lanes of the warp must call it together.
-template <typename L, int KPL>
+// The picks of token t as seen by lane q of its group of LPT lanes (a quad in the launched form): sel[k] / prob[k]
+// (every lane of the group ends with the same values) and the sum of the picked probabilities.  Slot s of lane q holds
+// expert 4 LPT (s / 4) + 4 q + s % 4.  All 32 lanes of the warp must call it together.
+template <typename L, int KPL, int LPT>
 __device__ __forceinline__ void route_quad_token(const L* __restrict__ logits, int64_t t, int q, int experts, int top_k,
                                                  int64_t ld, int vectorised, int (&sel)[kQuadTopK], float (&prob)[kQuadTopK],
                                                  float& denom) {
@@ -122,7 +123,7 @@ __device__ __forceinline__ void route_quad_token(const L* __restrict__ logits, i
   if (vectorised) {  // fp32 logits, rows and row pitch multiples of four: one 128-bit load per four slots
 #pragma unroll
     for (int j = 0; j < KPL / 4; ++j) {
-      const int e = 16 * j + 4 * q;
+      const int e = 4 * LPT * j + 4 * q;
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
       if (e < experts) v = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(logits) + t * ld + e));
       key[4 * j + 0] = e < experts ? order_key(v.x) : 0u;
@@ -133,7 +134,7 @@ __device__ __forceinline__ void route_quad_token(const L* __restrict__ logits, i
   } else {
 #pragma unroll
     for (int s = 0; s < KPL; ++s) {
-      const int e = 16 * (s >> 2) + 4 * q + (s & 3);
+      const int e = 4 * LPT * (s >> 2) + 4 * q + (s & 3);
       key[s] = e < experts ? order_key(logit_to_float<L>(logits, t * ld + e)) : 0u;
     }
   }
@@ -165,9 +166,9 @@ __device__ __forceinline__ void route_quad_token(const L* __restrict__ logits, i
         }
       }
       uint32_t best = val[0];
-      int who = 16 * (arg[0] >> 2) + 4 * q + (arg[0] & 3);
+      int who = 4 * LPT * (arg[0] >> 2) + 4 * q + (arg[0] & 3);
 #pragma unroll
-      for (int mask = 1; mask <= 2; mask <<= 1) {
+      for (int mask = 1; mask < LPT; mask <<= 1) {
         const uint32_t other = __shfl_xor_sync(kFull, best, mask);
         const int other_who = __shfl_xor_sync(kFull, who, mask);
         const bool take = other > best || (other == best && other_who < who);
@@ -181,7 +182,7 @@ __device__ __forceinline__ void route_quad_token(const L* __restrict__ logits, i
       picked |= 1ull << who;
       const int mine = who - 4 * q;  // slot s of this lane holds expert 16 (s / 4) + 4 q + s % 4
 #pragma unroll
-      for (int s = 0; s < KPL; ++s) key[s] = mine == 16 * (s >> 2) + (s & 3) ? 0u : key[s];
+      for (int s = 0; s < KPL; ++s) key[s] = mine == 4 * LPT * (s >> 2) + (s & 3) ? 0u : key[s];
       const float logit = key_value(best);
       if (k == 0) top_logit = logit;
       const float p = expf(__fsub_rn(logit, top_logit));
@@ -192,23 +193,23 @@ __device__ __forceinline__ void route_quad_token(const L* __restrict__ logits, i
   }
 }
 
-template <typename L, int KPL>
+template <typename L, int KPL, int LPT>
 __global__ void __launch_bounds__(256)
 route_quad_kernel(const L* __restrict__ logits, int32_t* __restrict__ indices, float* __restrict__ weights,
                   int64_t tokens, int experts, int top_k, int64_t ld, int vectorised) {
   pdl_prologue();
-  const int q = threadIdx.x & 3;
-  const int64_t token = (static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x) >> 2;
+  const int q = threadIdx.x & (LPT - 1);
+  const int64_t token = (static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x) / LPT;
   const bool live = token < tokens;  // whole quads; dead quads still take part in the shuffles
   const int64_t t = live ? token : tokens - 1;
   int sel[kQuadTopK];
   float prob[kQuadTopK];
   float denom;
-  route_quad_token<L, KPL>(logits, t, q, experts, top_k, ld, vectorised, sel, prob, denom);
+  route_quad_token<L, KPL, LPT>(logits, t, q, experts, top_k, ld, vectorised, sel, prob, denom);
   if (live) {
 #pragma unroll
     for (int k = 0; k < kQuadTopK; ++k) {
-      if ((k >> 1) == q && k < top_k) {  // lane q stores picks 2 q and 2 q + 1
+      if (k / (kQuadTopK / LPT) == q && k < top_k) {  // with four lanes, lane q stores picks 2 q and 2 q + 1
         indices[t * top_k + k] = sel[k];
         weights[t * top_k + k] = __fdiv_rn(prob[k], denom);
       }
@@ -1004,8 +1005,9 @@ size_t index_scratch_need(int64_t tokens, int64_t top_k, int64_t experts) {
 }
 
 // Whether the current device can run the one-launch kernel (cooperative launch, one CTA of 1024 threads per SM).
+int g_coop_state[64] = {};  // per device: 0 not looked at yet, 1 usable, -1 not usable (or a launch did not fit once)
 bool coop_supported() {
-  static int cached[64] = {};
+  int* cached = g_coop_state;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
     (void)cudaGetLastError();
@@ -1021,7 +1023,7 @@ bool coop_supported() {
 }
 
 template <typename... Params, typename... Args>
-void launch_cooperative(void (*kernel)(Params...), unsigned grid, unsigned block, size_t smem, cudaStream_t st, Args&&... args) {
+cudaError_t launch_cooperative(void (*kernel)(Params...), unsigned grid, unsigned block, size_t smem, cudaStream_t st, Args&&... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(grid);
   config.blockDim = dim3(block);
@@ -1032,7 +1034,7 @@ void launch_cooperative(void (*kernel)(Params...), unsigned grid, unsigned block
   attr[0].val.cooperative = 1;
   config.attrs = attr;
   config.numAttrs = 1;
-  (void)cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+  return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
 }
 
 // B200_INDEX_CHAIN=1 in the environment keeps the separate route / histogram / scan / scatter launches (read at every
@@ -1043,7 +1045,10 @@ bool one_launch_index(int64_t experts) {
   return experts <= kCoopExperts && coop_supported();
 }
 
-// The index as one cooperative launch.  The caller has checked shapes and pointers.
+// The index as one cooperative launch.  The caller has checked shapes and pointers.  Returns kCoopDoesNotFit (and
+// launches nothing) when the device cannot hold the grid at once, e.g. because part of its SMs is reserved for another
+// client: the caller then runs the three-kernel chain, and so do later calls on that device.
+constexpr int kCoopDoesNotFit = -1;
 int launch_index_one(const int32_t* indices, int64_t tokens, int E, int K, int32_t* counts, int32_t* offsets,
                      int32_t* perm_token, int32_t* pos, void* scratch, cudaStream_t st) {
   int64_t grid = coop_grid_bound(tokens);
@@ -1053,8 +1058,14 @@ int launch_index_one(const int32_t* indices, int64_t tokens, int E, int K, int32
   unsigned long long* header = static_cast<unsigned long long*>(scratch);
   int32_t* grid_hist = reinterpret_cast<int32_t*>(static_cast<unsigned char*>(scratch) + kCoopHeaderBytes);
   const size_t smem = static_cast<size_t>(kCoopWarps + 2) * E * sizeof(int);  // at most 34 KiB
-  launch_cooperative(index_one_launch_kernel, static_cast<unsigned>(grid), kCoopThreads, smem, st, indices, tokens, E, K, tokens_per_cta,
-                     tokens_per_warp, counts, offsets, perm_token, pos, header, grid_hist, kCoopWaitNs);
+  const cudaError_t err = launch_cooperative(index_one_launch_kernel, static_cast<unsigned>(grid), kCoopThreads, smem, st, indices, tokens, E,
+                                             K, tokens_per_cta, tokens_per_warp, counts, offsets, perm_token, pos, header, grid_hist, kCoopWaitNs);
+  if (err == cudaErrorCooperativeLaunchTooLarge || err == cudaErrorLaunchOutOfResources || err == cudaErrorNotSupported) {
+    (void)cudaGetLastError();
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) g_coop_state[dev] = -1;
+    return kCoopDoesNotFit;
+  }
   return after_launch("index_one_launch_kernel");
 }
 
@@ -1082,12 +1093,14 @@ extern "C" int b200_moe_route(const void* logits, int32_t* indices, float* weigh
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int E = static_cast<int>(experts), K = static_cast<int>(top_k);
   if (E <= 64 && K <= kQuadTopK) {
+    // Four lanes per token.  (Two lanes with 16 / 32 keys each execute fewer instructions per token but run at 64
+    // registers and 32 warps per SM: 14.9-15.2 us for 65536 tokens against 14.9, and 1-1.5 us slower below 16384 tokens.)
     const unsigned blocks = static_cast<unsigned>(ceil_div(tokens, 64));
     const int vec = logits_dtype == B200_F32 && E % 4 == 0 && ld_logits % 4 == 0 && aligned(logits, 16);
 #define B200_ROUTE_QUAD(L)                                                                                             \
   do {                                                                                                                 \
-    if (E <= 32) launch(route_quad_kernel<L, 8>, blocks, 256, 0, st, static_cast<const L*>(logits), indices, weights, tokens, E, K, ld_logits, vec); \
-    else launch(route_quad_kernel<L, 16>, blocks, 256, 0, st, static_cast<const L*>(logits), indices, weights, tokens, E, K, ld_logits, vec);       \
+    if (E <= 32) launch(route_quad_kernel<L, 8, 4>, blocks, 256, 0, st, static_cast<const L*>(logits), indices, weights, tokens, E, K, ld_logits, vec); \
+    else launch(route_quad_kernel<L, 16, 4>, blocks, 256, 0, st, static_cast<const L*>(logits), indices, weights, tokens, E, K, ld_logits, vec);       \
   } while (0)
     if (logits_dtype == B200_F32) B200_ROUTE_QUAD(float);
     else if (logits_dtype == B200_F16) B200_ROUTE_QUAD(__half);
@@ -1152,8 +1165,10 @@ extern "C" int b200_moe_index(const int32_t* indices, int64_t tokens, int64_t to
   if (int rc = check_device()) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int E = static_cast<int>(experts);
-  if (one_launch_index(experts))
-    return launch_index_one(indices, tokens, E, static_cast<int>(top_k), counts, offsets, perm_token, pos, scratch, st);
+  if (one_launch_index(experts)) {
+    const int rc = launch_index_one(indices, tokens, E, static_cast<int>(top_k), counts, offsets, perm_token, pos, scratch, st);
+    if (rc != kCoopDoesNotFit) return rc;
+  }
   int32_t* block_hist = reinterpret_cast<int32_t*>(static_cast<unsigned char*>(scratch) + kCoopHeaderBytes);
   if (nblk > 0) {
     launch(index_hist_kernel, nblk, kIndexThreads, 8 * E * sizeof(int), st, indices, pairs, E, nblk, block_hist);
@@ -1254,8 +1269,10 @@ extern "C" int b200_moe_index_static(const int32_t* indices, int64_t tokens, int
   const int E = static_cast<int>(experts);
   // The histogram kernels write every entry the later steps read, and the one-launch kernel's generation word only has
   // to differ from its flags' last value, so nothing left over from an earlier call has to be cleared first.
-  if (one_launch_index(experts))
-    return launch_index_one(indices, tokens, E, static_cast<int>(top_k), counts, offsets, perm_token, pos, scratch, st);
+  if (one_launch_index(experts)) {
+    const int rc = launch_index_one(indices, tokens, E, static_cast<int>(top_k), counts, offsets, perm_token, pos, scratch, st);
+    if (rc != kCoopDoesNotFit) return rc;
+  }
   int32_t* block_hist = reinterpret_cast<int32_t*>(static_cast<unsigned char*>(scratch) + kCoopHeaderBytes);
   if (nblk > 0) {
     launch(index_hist_kernel, nblk, kIndexThreads, 8 * E * sizeof(int), st, indices, pairs, E, nblk, block_hist);
